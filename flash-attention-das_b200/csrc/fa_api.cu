@@ -1,0 +1,412 @@
+// C-ABI layer of libfa_b200.so: argument validation, TMA descriptor construction, partition sizing and
+// kernel launches.  Nothing in this file allocates device memory or synchronises the stream (except
+// fa_b200_device_status, which is a diagnostic read).
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "fa_common.cuh"
+#include "fa_kernels.h"
+
+namespace fa {
+namespace {
+
+// Device-side status word (one per device that loads the library).
+__device__ int g_device_status = 0;
+
+std::atomic<uint64_t> g_launches{0};
+thread_local char g_last_error[256] = "";
+
+void set_error(const char* what, const char* detail) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, detail ? detail : "");
+}
+int cuda_fail(const char* what, cudaError_t e) {
+  set_error(what, cudaGetErrorString(e));
+  return FA_B200_ERR_CUDA;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return static_cast<EncodeTiledFn>(nullptr);
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+int* status_ptr() {
+  static int* ptrs[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<int*>(ptr);
+  }
+  return ptrs[dev];
+}
+
+int elem_size(int dtype) { return dtype == FA_B200_E4M3 ? 1 : 2; }
+
+// 4-D tile descriptor over (d, heads, rows, batch) with a 128-byte-swizzled box of (128 bytes, 1, box_rows, 1).
+// Strides are in elements.  Out-of-range rows read as zero.
+int make_tmap(CUtensorMap* out, const void* base, int dtype, int64_t heads, int64_t rows, int64_t batch,
+              int64_t head_stride, int64_t row_stride, int64_t batch_stride, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) { set_error("cuTensorMapEncodeTiled", "driver entry point not found"); return FA_B200_ERR_CUDA; }
+  const int es = elem_size(dtype);
+  static const uint8_t dummy[64] __attribute__((aligned(64))) = {};
+  void* addr = const_cast<void*>(base ? base : static_cast<const void*>(dummy));
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(heads > 0 ? heads : 1),
+                        static_cast<cuuint64_t>(rows > 0 ? rows : 1), static_cast<cuuint64_t>(batch > 0 ? batch : 1)};
+  auto fix = [&](int64_t s) { return static_cast<cuuint64_t>((s > 0 ? s : kHeadDim) * es); };
+  cuuint64_t strides[3] = {fix(head_stride), fix(row_stride), fix(batch_stride)};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / es), 1u, static_cast<cuuint32_t>(box_rows), 1u};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMapDataType dt = dtype == FA_B200_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : dtype == FA_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                   : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(out, dt, 4, addr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_error("cuTensorMapEncodeTiled", buf);
+    return FA_B200_ERR_CUDA;
+  }
+  return FA_B200_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+bool stride_ok(int64_t s, int es) { return s >= 0 && (s * es) % 16 == 0; }
+
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+
+struct DecodePlan {
+  int status;
+  int group, tile, box_tok, partition_tokens, num_partitions, max_len;
+  bool split;
+};
+
+DecodePlan plan_decode(const fa_b200_decode_params* p) {
+  DecodePlan pl{};
+  pl.status = FA_B200_OK;
+  if (!p) { pl.status = FA_B200_ERR_NULL; return pl; }
+  if (p->d != kHeadDim) { pl.status = FA_B200_ERR_HEADDIM; return pl; }
+  if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) { pl.status = FA_B200_ERR_DTYPE; return pl; }
+  if (p->b < 0 || p->h <= 0 || p->h_k <= 0 || p->max_blocks_per_seq < 0 || p->num_blocks < 0) { pl.status = FA_B200_ERR_SHAPE; return pl; }
+  if (p->h % p->h_k != 0 || p->h / p->h_k > 16) { pl.status = FA_B200_ERR_HEADS; return pl; }
+  pl.group = p->h / p->h_k;
+  pl.tile = p->dtype == FA_B200_E4M3 ? 128 : 64;
+  const int page = p->page_size;
+  if (page >= 64) {
+    if (page % 64 != 0) { pl.status = FA_B200_ERR_PAGE; return pl; }
+    pl.box_tok = 64;
+  } else {
+    if (page != 16 && page != 32) { pl.status = FA_B200_ERR_PAGE; return pl; }
+    pl.box_tok = page;
+  }
+  int64_t max_len = static_cast<int64_t>(p->max_blocks_per_seq) * page;
+  if (p->max_seqlen_k > 0 && p->max_seqlen_k < max_len) max_len = p->max_seqlen_k;
+  if (max_len > (1ll << 30)) { pl.status = FA_B200_ERR_TOO_LARGE; return pl; }
+  pl.max_len = static_cast<int>(max_len);
+  const int unit = pl.tile > page ? (pl.tile % page == 0 ? pl.tile : pl.tile * page) : (page % pl.tile == 0 ? page : pl.tile * page);
+  int part = p->partition_tokens > 0 ? p->partition_tokens : env_int("FA_B200_DECODE_PARTITION", 0);
+  if (part > 0) {
+    if (part % pl.tile != 0 || (part % page != 0 && page % part != 0)) { pl.status = FA_B200_ERR_SHAPE; return pl; }
+  } else {
+    // Aim for >= 32 work items per resident CTA slot (148 SMs x 2) so that ragged lengths balance, but keep
+    // at least 8 tiles per partition so the pipeline fill is amortised.
+    const int64_t bound = static_cast<int64_t>(p->b) * p->h_k * max_len;
+    const int64_t want = bound / (296 * 32);
+    const int min_part = 8 * pl.tile;
+    part = min_part;
+    while (part * 2 <= want) part *= 2;
+    if (part < unit) part = unit;
+  }
+  // keep the per-partition page list within the kernel's shared-memory table
+  while (part / page > decode_max_pages_per_partition()) part /= 2;
+  if (part <= 0 || part % pl.tile != 0) { pl.status = FA_B200_ERR_PAGE; return pl; }
+  pl.partition_tokens = part;
+  pl.num_partitions = max_len > 0 ? static_cast<int>((max_len + part - 1) / part) : 1;
+  pl.split = pl.num_partitions > 1 || p->o_partial_out != nullptr;
+  return pl;
+}
+
+size_t decode_ws_bytes(const fa_b200_decode_params* p, const DecodePlan& pl) {
+  if (!pl.split) return 0;
+  return static_cast<size_t>(pl.num_partitions) * p->b * p->h * (kHeadDim + 1) * sizeof(float);
+}
+
+}  // namespace
+}  // namespace fa
+
+using namespace fa;
+
+extern "C" {
+
+int fa_b200_abi_version(void) { return FA_B200_ABI_VERSION; }
+uint64_t fa_b200_launch_count(void) { return g_launches.load(); }
+const char* fa_b200_last_cuda_error(void) { return g_last_error; }
+
+const char* fa_b200_status_string(int s) {
+  switch (s) {
+    case FA_B200_OK: return "ok";
+    case FA_B200_ERR_NULL: return "a required pointer is null";
+    case FA_B200_ERR_DTYPE: return "unsupported element type";
+    case FA_B200_ERR_HEADDIM: return "head dimension must be 128";
+    case FA_B200_ERR_HEADS: return "Number of heads in key/value must divide number of heads in query (group <= 16 for decode)";
+    case FA_B200_ERR_STRIDE: return "Input tensor must have contiguous last dimension and 16-byte aligned strides";
+    case FA_B200_ERR_SHAPE: return "inconsistent or negative sizes";
+    case FA_B200_ERR_PAGE: return "Paged KV cache block size must be 16, 32 or a multiple of 64";
+    case FA_B200_ERR_WORKSPACE: return "workspace missing or too small";
+    case FA_B200_ERR_UNSUPPORTED: return "option not supported on this path";
+    case FA_B200_ERR_CUDA: return "CUDA call failed";
+    case FA_B200_ERR_ALIGN: return "pointer must be 16-byte aligned";
+    case FA_B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case FA_B200_ERR_TOO_LARGE: return "size beyond a built-in limit";
+  }
+  return "unknown status";
+}
+
+int fa_b200_device_status(void) {
+  int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return FA_B200_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return FA_B200_ERR_CUDA;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    return FA_B200_ERR_DEVICE_TIMEOUT;
+  }
+  return FA_B200_OK;
+}
+
+size_t fa_b200_decode_workspace_bytes(const fa_b200_decode_params* p) {
+  DecodePlan pl = plan_decode(p);
+  if (pl.status != FA_B200_OK) return 0;
+  return decode_ws_bytes(p, pl);
+}
+
+int32_t fa_b200_decode_partition_tokens(const fa_b200_decode_params* p) {
+  DecodePlan pl = plan_decode(p);
+  return pl.status == FA_B200_OK ? pl.partition_tokens : 0;
+}
+
+int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
+  if (!p || !p->o_partial || !p->lse_partial) return FA_B200_ERR_NULL;
+  if (p->d != kHeadDim) return FA_B200_ERR_HEADDIM;
+  if (p->rows < 0 || p->num_parts < 0 || p->h <= 0 || p->rows % p->h != 0) return FA_B200_ERR_SHAPE;
+  if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16 && p->out_dtype >= 0) return FA_B200_ERR_DTYPE;
+  if (!aligned16(p->o_partial) || (p->out && !aligned16(p->out))) return FA_B200_ERR_ALIGN;
+  if (p->out && p->out_row_stride % 8 != 0) return FA_B200_ERR_STRIDE;
+  CombineKernelParams k{};
+  k.o_partial = p->o_partial;
+  k.lse_partial = p->lse_partial;
+  k.out = p->out;
+  k.lse = p->lse;
+  k.seqlens = nullptr;
+  k.parts_per_row = p->parts_per_row;
+  k.out_row_stride = p->out_row_stride;
+  k.out_batch_stride = p->out_row_stride * p->h;
+  k.num_parts = p->num_parts;
+  k.rows = p->rows;
+  k.h = p->h;
+  k.partition_tokens = 1;
+  k.out_dtype = p->out_dtype;
+  k.lse_empty_is_neg = 0;
+  k.out_scale = p->out_scale;
+  cudaError_t e = launch_combine(k, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("combine launch", e);
+  if (p->rows > 0) g_launches++;
+  return FA_B200_OK;
+}
+
+int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  DecodePlan pl = plan_decode(p);
+  if (pl.status != FA_B200_OK) return pl.status;
+  if (!p->q || !p->k_cache || !p->v_cache || !p->block_table || !p->cache_seqlens) return FA_B200_ERR_NULL;
+  if (!p->out && !p->o_partial_out) return FA_B200_ERR_NULL;
+  if (p->o_partial_out && !p->lse_partial_out) return FA_B200_ERR_NULL;
+  if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
+  const int es = elem_size(p->dtype);
+  if (!aligned16(p->q) || !aligned16(p->k_cache) || !aligned16(p->v_cache) || (p->out && !aligned16(p->out)))
+    return FA_B200_ERR_ALIGN;
+  if (!stride_ok(p->k_block_stride, es) || !stride_ok(p->k_row_stride, es) || !stride_ok(p->k_head_stride, es) ||
+      !stride_ok(p->v_block_stride, es) || !stride_ok(p->v_row_stride, es) || !stride_ok(p->v_head_stride, es) ||
+      (p->q_batch_stride * es) % 4 != 0 || (p->q_head_stride * es) % 4 != 0 || p->o_batch_stride % 8 != 0 ||
+      p->o_head_stride % 8 != 0)
+    return FA_B200_ERR_STRIDE;
+  if (p->b == 0) return FA_B200_OK;
+  const size_t need = decode_ws_bytes(p, pl);
+  if (need > 0 && (!p->workspace || p->workspace_bytes < need || !aligned16(p->workspace))) return FA_B200_ERR_WORKSPACE;
+
+  CUtensorMap tk, tv;
+  int st = make_tmap(&tk, p->k_cache, p->dtype, p->h_k, p->page_size, p->num_blocks, p->k_head_stride, p->k_row_stride,
+                     p->k_block_stride, pl.box_tok);
+  if (st != FA_B200_OK) return st;
+  st = make_tmap(&tv, p->v_cache, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
+                 p->v_block_stride, pl.box_tok);
+  if (st != FA_B200_OK) return st;
+
+  DecodeKernelParams k{};
+  k.status = status_ptr();
+  if (!k.status) return cuda_fail("status word", cudaGetLastError());
+  k.q = p->q;
+  k.out = p->out;
+  k.lse_out = p->softmax_lse;
+  k.block_table = p->block_table;
+  k.seqlens = p->cache_seqlens;
+  k.q_descale = p->q_descale;
+  k.k_descale = p->k_descale;
+  k.v_descale = p->v_descale;
+  k.qds_b = p->q_descale_batch_stride; k.qds_h = p->q_descale_head_stride;
+  k.kds_b = p->k_descale_batch_stride; k.kds_h = p->k_descale_head_stride;
+  k.vds_b = p->v_descale_batch_stride; k.vds_h = p->v_descale_head_stride;
+  k.q_batch_stride = p->q_batch_stride;
+  k.q_head_stride = p->q_head_stride;
+  k.o_batch_stride = p->o_batch_stride;
+  k.o_head_stride = p->o_head_stride;
+  k.bt_stride = p->block_table_batch_stride;
+  k.b = p->b; k.h = p->h; k.h_k = p->h_k; k.group = pl.group;
+  k.page_size = p->page_size;
+  k.box_tok = pl.box_tok;
+  k.partition_tokens = pl.partition_tokens;
+  k.num_partitions = pl.num_partitions;
+  k.out_dtype = p->out_dtype;
+  k.write_final = pl.split ? 0 : 1;
+  k.scale_log2 = p->softmax_scale * kLog2e;
+  if (pl.split) {
+    k.o_partial = static_cast<float*>(p->workspace);
+    k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * kHeadDim;
+  }
+  cudaError_t e = launch_decode(p->dtype, tk, tv, k, stream);
+  if (e != cudaSuccess) return cuda_fail("decode launch", e);
+  g_launches++;
+  if (pl.split) {
+    CombineKernelParams c{};
+    c.o_partial = k.o_partial;
+    c.lse_partial = k.lse_partial;
+    c.seqlens = p->cache_seqlens;
+    c.parts_per_row = nullptr;
+    c.num_parts = pl.num_partitions;
+    c.rows = p->b * p->h;
+    c.h = p->h;
+    c.partition_tokens = pl.partition_tokens;
+    c.out_scale = 1.f;
+    if (p->o_partial_out) {
+      c.out = p->o_partial_out;
+      c.lse = p->lse_partial_out;
+      c.out_row_stride = kHeadDim;
+      c.out_batch_stride = static_cast<int64_t>(p->h) * kHeadDim;
+      c.out_dtype = -1;
+      c.lse_empty_is_neg = 1;
+    } else {
+      c.out = p->out;
+      c.lse = p->softmax_lse;
+      c.out_row_stride = p->o_head_stride;
+      c.out_batch_stride = p->o_batch_stride;
+      c.out_dtype = p->out_dtype;
+      c.lse_empty_is_neg = 0;
+    }
+    e = launch_combine(c, stream);
+    if (e != cudaSuccess) return cuda_fail("combine launch", e);
+    g_launches++;
+  }
+  return FA_B200_OK;
+}
+
+static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!p) return FA_B200_ERR_NULL;
+  if (p->d != kHeadDim) return FA_B200_ERR_HEADDIM;
+  if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) return FA_B200_ERR_DTYPE;
+  if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
+  if (p->b < 0 || p->h <= 0 || p->h_k <= 0 || p->seqlen_q < 0 || p->seqlen_k < 0) return FA_B200_ERR_SHAPE;
+  if (p->h % p->h_k != 0) return FA_B200_ERR_HEADS;
+  const bool varlen = p->cu_seqlens_q != nullptr;
+  if (varlen != (p->cu_seqlens_k != nullptr)) return FA_B200_ERR_NULL;
+  if (varlen && (p->total_q < 0 || p->total_k < 0)) return FA_B200_ERR_SHAPE;
+  if (p->b == 0 || p->seqlen_q == 0 || (varlen && p->total_q == 0)) return FA_B200_OK;
+  if (!p->q || !p->out) return FA_B200_ERR_NULL;
+  const bool has_k = varlen ? p->total_k > 0 : p->seqlen_k > 0;
+  if (has_k && (!p->k || !p->v)) return FA_B200_ERR_NULL;
+  const int es = elem_size(p->dtype);
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return FA_B200_ERR_ALIGN;
+  if (!stride_ok(p->q_row_stride, es) || !stride_ok(p->q_head_stride, es) || !stride_ok(p->k_row_stride, es) ||
+      !stride_ok(p->k_head_stride, es) || !stride_ok(p->v_row_stride, es) || !stride_ok(p->v_head_stride, es) ||
+      (!varlen && (!stride_ok(p->q_batch_stride, es) || !stride_ok(p->k_batch_stride, es) || !stride_ok(p->v_batch_stride, es))) ||
+      p->o_row_stride % 8 != 0 || p->o_head_stride % 8 != 0 || (!varlen && p->o_batch_stride % 8 != 0))
+    return FA_B200_ERR_STRIDE;
+  if (sparse) {
+    if (!p->block_count || !p->block_offset) return FA_B200_ERR_NULL;
+    if (varlen) return FA_B200_ERR_UNSUPPORTED;
+    if ((p->block_m != 64 && p->block_m != 128) || p->nnz_s <= 0 || p->nnz_s > 512) return FA_B200_ERR_SHAPE;
+    if (p->num_q_blocks != (p->seqlen_q + p->block_m - 1) / p->block_m) return FA_B200_ERR_SHAPE;
+  }
+
+  CUtensorMap tq, tk, tv;
+  const int64_t q_rows = varlen ? p->total_q : p->seqlen_q, k_rows = varlen ? p->total_k : p->seqlen_k;
+  const int64_t nb = varlen ? 1 : p->b;
+  int st = make_tmap(&tq, p->q, p->dtype, p->h, q_rows, nb, p->q_head_stride, p->q_row_stride,
+                     varlen ? p->q_row_stride * (q_rows > 0 ? q_rows : 1) : p->q_batch_stride, 128);
+  if (st != FA_B200_OK) return st;
+  st = make_tmap(&tk, p->k, p->dtype, p->h_k, k_rows, nb, p->k_head_stride, p->k_row_stride,
+                 varlen ? p->k_row_stride * (k_rows > 0 ? k_rows : 1) : p->k_batch_stride, 128);
+  if (st != FA_B200_OK) return st;
+  st = make_tmap(&tv, p->v, p->dtype, p->h_k, k_rows, nb, p->v_head_stride, p->v_row_stride,
+                 varlen ? p->v_row_stride * (k_rows > 0 ? k_rows : 1) : p->v_batch_stride, 128);
+  if (st != FA_B200_OK) return st;
+
+  PrefillKernelParams k{};
+  k.status = status_ptr();
+  if (!k.status) return cuda_fail("status word", cudaGetLastError());
+  k.out = p->out;
+  k.lse = p->softmax_lse;
+  k.cu_seqlens_q = p->cu_seqlens_q;
+  k.cu_seqlens_k = p->cu_seqlens_k;
+  k.q_descale = p->q_descale; k.k_descale = p->k_descale; k.v_descale = p->v_descale;
+  k.qds_b = p->q_descale_batch_stride; k.qds_h = p->q_descale_head_stride;
+  k.kds_b = p->k_descale_batch_stride; k.kds_h = p->k_descale_head_stride;
+  k.vds_b = p->v_descale_batch_stride; k.vds_h = p->v_descale_head_stride;
+  k.o_batch_stride = varlen ? 0 : p->o_batch_stride;
+  k.o_row_stride = p->o_row_stride;
+  k.o_head_stride = p->o_head_stride;
+  k.total_q = p->total_q;
+  k.b = p->b; k.h = p->h; k.h_k = p->h_k;
+  k.seqlen_q = p->seqlen_q; k.seqlen_k = p->seqlen_k;
+  k.is_causal = p->is_causal ? 1 : 0;
+  k.out_dtype = p->out_dtype;
+  k.scale_log2 = p->softmax_scale * kLog2e;
+  k.sparse = sparse ? 1 : 0;
+  if (sparse) {
+    k.block_count = p->block_count;
+    k.block_offset = p->block_offset;
+    k.num_q_blocks = p->num_q_blocks;
+    k.nnz_s = p->nnz_s;
+    k.block_m = p->block_m;
+    k.num_m_blocks = p->num_q_blocks;
+  } else {
+    k.num_m_blocks = (p->seqlen_q + 127) / 128;
+  }
+  cudaError_t e = launch_prefill(p->dtype, tq, tk, tv, k, stream);
+  if (e != cudaSuccess) return cuda_fail("prefill launch", e);
+  g_launches++;
+  return FA_B200_OK;
+}
+
+int fa_b200_fwd(const fa_b200_fwd_params* p, void* stream) { return fwd_common(p, stream, false); }
+int fa_b200_fwd_sparse(const fa_b200_fwd_params* p, void* stream) { return fwd_common(p, stream, true); }
+
+}  // extern "C"

@@ -1,0 +1,419 @@
+// Paged-KV decode for sm_100a: HBM-bound split-KV kernel.
+//
+// One CTA handles one (token partition, kv head, sequence).  A producer warp walks the sequence's
+// block_table and streams the partition's K and V pages into a shared-memory ring with TMA tile loads
+// (128-byte swizzle, one mbarrier pair per stage); four consumer warps each own 16 (or 32, e4m3) token
+// rows of every tile and run S = Q K^T, an online softmax and O += P V with register-level MMAs on the
+// GQA group's query heads packed into one 16-row query tile.  Each K/V byte is read from HBM once.
+// The CTA writes either the final output (single partition) or an fp32 partial (O normalised by its
+// own sum, natural-log LSE) that the combine kernel merges.
+//
+// Follows the data flow of the reference's partitioned paged attention
+// (csrc/flash_attn_cutlass/src/paged_attention.cu:61-558) but with exact softmax (no epsilon) and fp32
+// partials, as the reference's PyTorch oracle defines the result.
+#include "fa_common.cuh"
+#include "fa_kernels.h"
+
+namespace fa {
+
+namespace {
+
+constexpr int kConsumerWarps = 4;
+constexpr int kDecodeThreads = 32 * (1 + kConsumerWarps);
+constexpr int kStageBytes = 32768;      // K tile 16 KB + V tile 16 KB
+constexpr int kMaxPagesPerPartition = 512;
+
+template <int DT>
+struct DecodeTraits {
+  static constexpr bool kFp8 = (DT == FA_B200_E4M3);
+  static constexpr int kElem = kFp8 ? 1 : 2;
+  static constexpr int kTile = kFp8 ? 128 : 64;            // tokens per stage
+  static constexpr int kRowsPerWarp = kTile / kConsumerWarps;
+  static constexpr int kSub = kRowsPerWarp / 16;            // 16-token sub-blocks per warp per tile
+  static constexpr int kHalves = kFp8 ? 1 : 2;             // 128-byte column groups per K/V row
+  static constexpr int kQSteps = kFp8 ? 4 : 8;             // MMA k-steps over d = 128
+};
+
+template <int DT>
+__device__ __forceinline__ void mma_qk(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (DT == FA_B200_E4M3) mma_e4m3_16832(c, a, b0, b1);
+  else if constexpr (DT == FA_B200_BF16) mma_bf16_16816(c, a, b0, b1);
+  else mma_f16_16816(c, a, b0, b1);
+}
+template <int DT>
+__device__ __forceinline__ void mma_pv(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (DT == FA_B200_BF16) mma_bf16_16816(c, a, b0, b1);
+  else mma_f16_16816(c, a, b0, b1);
+}
+template <int DT>
+__device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
+  if constexpr (DT == FA_B200_BF16) return pack_bf16(lo, hi);
+  else return pack_f16(lo, hi);
+}
+
+template <int DT, int STAGES>
+__global__ void __launch_bounds__(kDecodeThreads, 2)
+decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                    const DecodeKernelParams p) {
+  using T = DecodeTraits<DT>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10).
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stages = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  float* sm_m = reinterpret_cast<float*>(empty_bar + STAGES);       // [4][16]
+  float* sm_l = sm_m + kConsumerWarps * 16;                          // [4][16]
+  int* sm_pages = reinterpret_cast<int*>(sm_l + kConsumerWarps * 16);  // [kMaxPagesPerPartition]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm_pages + kMaxPagesPerPartition);
+  const WaitCtx wctx{abort_flag, p.status};
+
+  const int part = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int len = p.seqlens[b];
+  const int tok_begin = part * p.partition_tokens;
+  // Partitions past the end of this sequence have nothing to do; partition 0 of an empty sequence
+  // still runs to publish "no keys" (zero output, LSE marker).
+  if (tok_begin >= len && !(part == 0)) return;
+  const int tok_end = min(len, tok_begin + p.partition_tokens);
+  const int n_tiles = (tok_end > tok_begin) ? (tok_end - tok_begin + T::kTile - 1) / T::kTile : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), kConsumerWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 0) {
+    // This partition's slice of the block table -> shared memory, 16-byte vector loads where aligned.
+    const int first_page = tok_begin / p.page_size;
+    const int n_pages = (tok_end > tok_begin) ? (tok_end - 1) / p.page_size - first_page + 1 : 0;
+    const int32_t* bt = p.block_table + static_cast<int64_t>(b) * p.bt_stride + first_page;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(bt) & 15) == 0);
+    if (vec_ok) {
+      const int nv = n_pages >> 2;
+      for (int i = lane; i < nv; i += 32) {
+        int4 v = __ldg(reinterpret_cast<const int4*>(bt) + i);
+        *reinterpret_cast<int4*>(sm_pages + 4 * i) = v;
+      }
+      for (int i = (nv << 2) + lane; i < n_pages; i += 32) sm_pages[i] = __ldg(bt + i);
+    } else {
+      for (int i = lane; i < n_pages; i += 32) sm_pages[i] = __ldg(bt + i);
+    }
+  }
+  __syncthreads();
+
+  const int group = p.group;  // query heads per kv head (rows of the packed query tile), <= 16
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      const int box_tok = p.box_tok;
+      const uint32_t box_bytes = static_cast<uint32_t>(box_tok) * 128u;  // one 128-byte column group
+      const int boxes_per_tile = T::kTile / box_tok;
+      const int first_page = tok_begin / p.page_size;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, wctx)) break;
+        const int tok0 = tok_begin + t * T::kTile;
+        int nvalid = 0;
+        for (int j = 0; j < boxes_per_tile; ++j) nvalid += (tok0 + j * box_tok < tok_end) ? 1 : 0;
+        const uint32_t fb = smem_u32(&full_bar[s]);
+        mbar_expect_tx(fb, 2u * T::kHalves * nvalid * box_bytes);
+        const uint32_t kdst = smem_u32(stages + s * kStageBytes);
+        const uint32_t vdst = kdst + kStageBytes / 2;
+        for (int j = 0; j < nvalid; ++j) {
+          const int tok = tok0 + j * box_tok;
+          const int page = sm_pages[tok / p.page_size - first_page];
+          const int row = tok % p.page_size;
+          const uint32_t off = j * box_bytes;
+#pragma unroll
+          for (int hf = 0; hf < T::kHalves; ++hf) {
+            tma_load_4d(kdst + hf * (T::kTile * 128) + off, &tmap_k, fb, hf * 64, hk, row, page);
+            tma_load_4d(vdst + hf * (T::kTile * 128) + off, &tmap_v, fb, hf * 64, hk, row, page);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    const int cw = warp - 1;
+    const int g = lane >> 2, qd = lane & 3;
+    const int head0 = hk * group;
+
+    // Query fragments (A operand, rows = heads of the group, zero beyond the group).
+    uint32_t qf[T::kQSteps][4];
+    {
+      const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) +
+                          (static_cast<int64_t>(b) * p.q_batch_stride + static_cast<int64_t>(head0) * p.q_head_stride) * T::kElem;
+      const int64_t hs = p.q_head_stride * T::kElem;
+#pragma unroll
+      for (int ks = 0; ks < T::kQSteps; ++ks) {
+        // bytes of the two 4-byte groups this thread holds per row in k-step ks
+        const int c0 = T::kFp8 ? (ks * 32 + 4 * qd) : (ks * 32 + 4 * qd);
+        const int c1 = c0 + 16;
+        qf[ks][0] = (g < group) ? __ldg(reinterpret_cast<const uint32_t*>(qb + g * hs + c0)) : 0u;
+        qf[ks][1] = (g + 8 < group) ? __ldg(reinterpret_cast<const uint32_t*>(qb + (g + 8) * hs + c0)) : 0u;
+        qf[ks][2] = (g < group) ? __ldg(reinterpret_cast<const uint32_t*>(qb + g * hs + c1)) : 0u;
+        qf[ks][3] = (g + 8 < group) ? __ldg(reinterpret_cast<const uint32_t*>(qb + (g + 8) * hs + c1)) : 0u;
+      }
+    }
+    float scale_log2 = p.scale_log2;
+    if (p.q_descale) scale_log2 *= p.q_descale[b * p.qds_b + hk * p.qds_h];
+    if (p.k_descale) scale_log2 *= p.k_descale[b * p.kds_b + hk * p.kds_h];
+
+    for (int t = 0; t < n_tiles; ++t) {
+      const int s = t % STAGES;
+      const uint32_t ph = (t / STAGES) & 1;
+      if (!mbar_wait(smem_u32(&full_bar[s]), ph, wctx)) break;
+      const uint32_t kbase = smem_u32(stages + s * kStageBytes);
+      const uint32_t vbase = kbase + kStageBytes / 2;
+      const int tok0 = tok_begin + t * T::kTile;
+      const int wrow0 = cw * T::kRowsPerWarp;
+      // Rows at or past the end of the sequence were not loaded (or hold other tokens): their V must
+      // be zero so that 0 * garbage cannot poison the PV product; their scores are masked by index.
+      if (tok0 + wrow0 + T::kRowsPerWarp > tok_end) {
+        const int first_bad = max(tok_end - tok0, wrow0);
+        const int nchunk = T::kHalves * 8;
+        for (int r = first_bad; r < wrow0 + T::kRowsPerWarp; ++r) {
+          if (lane < nchunk) {
+            const uint32_t a = vbase + (lane >> 3) * (T::kTile * 128) + r * 128 + ((lane & 7) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0u) : "memory");
+          }
+        }
+        __syncwarp();
+      }
+#pragma unroll
+      for (int sb = 0; sb < T::kSub; ++sb) {
+        const int r0 = wrow0 + sb * 16;
+        if (tok0 + r0 >= tok_end) continue;  // warp-uniform: nothing valid in this sub-block
+        // ---- S = Q K^T for 16 tokens (two 8-token n-tiles)
+        float sc[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
+        {
+          const int row = r0 + ((lane >> 4) << 3) + (lane & 7);
+          const uint32_t rbase = kbase + row * 128;
+          const int rsw = row & 7;
+#pragma unroll
+          for (int ks = 0; ks < T::kQSteps; ++ks) {
+            const int chunk = ks * 2 + ((lane >> 3) & 1);
+            const uint32_t addr = rbase + (chunk >> 3) * (T::kTile * 128) + (((chunk & 7) ^ rsw) << 4);
+            uint32_t b00, b01, b10, b11;
+            ldsm_x4(addr, b00, b01, b10, b11);
+            mma_qk<DT>(sc[0], qf[ks], b00, b01);
+            mma_qk<DT>(sc[1], qf[ks], b10, b11);
+          }
+        }
+        // ---- online softmax (base-2 domain), rows g and g+8
+        const int tokb = tok0 + r0 + 2 * qd;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const bool ok = (tokb + nt * 8 + e) < tok_end;
+            sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
+            sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+            mx0 = fmaxf(mx0, sc[nt][e]);
+            mx1 = fmaxf(mx1, sc[nt][2 + e]);
+          }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0, ms1 = (mn1 == -INFINITY) ? 0.f : mn1;
+        const float al0 = fast_exp2(m_run[0] - ms0), al1 = fast_exp2(m_run[1] - ms1);
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            sc[nt][e] = fast_exp2(sc[nt][e] - ms0);
+            sc[nt][2 + e] = fast_exp2(sc[nt][2 + e] - ms1);
+            ps0 += sc[nt][e];
+            ps1 += sc[nt][2 + e];
+          }
+        }
+        l_run[0] = l_run[0] * al0 + ps0;
+        l_run[1] = l_run[1] * al1 + ps1;
+        if (__any_sync(0xffffffffu, (al0 != 1.f) || (al1 != 1.f))) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1;
+          }
+        }
+        // ---- O += P V
+        uint32_t pa[4];
+        pa[0] = pack_p<DT>(sc[0][0], sc[0][1]);
+        pa[1] = pack_p<DT>(sc[0][2], sc[0][3]);
+        pa[2] = pack_p<DT>(sc[1][0], sc[1][1]);
+        pa[3] = pack_p<DT>(sc[1][2], sc[1][3]);
+        {
+          const int mi = lane >> 3;
+          const int row = r0 + ((mi & 1) << 3) + (lane & 7);
+          const uint32_t rbase = vbase + row * 128;
+          const int rsw = row & 7;
+          if constexpr (!T::kFp8) {
+#pragma unroll
+            for (int nd = 0; nd < 16; nd += 2) {
+              const int chunk = nd + (mi >> 1);
+              const uint32_t addr = rbase + (chunk >> 3) * (T::kTile * 128) + (((chunk & 7) ^ rsw) << 4);
+              uint32_t v0, v1, v2, v3;
+              ldsm_x4_trans(addr, v0, v1, v2, v3);
+              mma_pv<DT>(o[nd], pa, v0, v1);
+              mma_pv<DT>(o[nd + 1], pa, v2, v3);
+            }
+          } else {
+            // e4m3 V: a transposed 16-bit ldmatrix yields, per thread, the bytes
+            // {V[2q][2g], V[2q][2g+1], V[2q+1][2g], V[2q+1][2g+1]}; a byte permute separates the even
+            // and odd d columns, each converted to an f16x2 B fragment.  Output n-tile 2c+par covers
+            // d = 16c + 2n + par.
+#pragma unroll
+            for (int cc = 0; cc < 8; cc += 2) {
+              const int chunk = cc + (mi >> 1);
+              const uint32_t addr = rbase + ((chunk ^ rsw) << 4);
+              uint32_t w0, w1, w2, w3;
+              ldsm_x4_trans(addr, w0, w1, w2, w3);
+              const uint32_t t0 = __byte_perm(w0, 0u, 0x3120), t1 = __byte_perm(w1, 0u, 0x3120);
+              const uint32_t t2 = __byte_perm(w2, 0u, 0x3120), t3 = __byte_perm(w3, 0u, 0x3120);
+              mma_pv<DT>(o[2 * cc], pa, cvt_e4m3x2_to_f16x2(t0), cvt_e4m3x2_to_f16x2(t1));
+              mma_pv<DT>(o[2 * cc + 1], pa, cvt_e4m3x2_to_f16x2(t0 >> 16), cvt_e4m3x2_to_f16x2(t1 >> 16));
+              mma_pv<DT>(o[2 * cc + 2], pa, cvt_e4m3x2_to_f16x2(t2), cvt_e4m3x2_to_f16x2(t3));
+              mma_pv<DT>(o[2 * cc + 3], pa, cvt_e4m3x2_to_f16x2(t2 >> 16), cvt_e4m3x2_to_f16x2(t3 >> 16));
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
+    }
+    // per-warp row sums: reduce over the quad
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+    if (qd == 0) {
+      sm_m[cw * 16 + g] = m_run[0];
+      sm_m[cw * 16 + g + 8] = m_run[1];
+      sm_l[cw * 16 + g] = l_run[0];
+      sm_l[cw * 16 + g + 8] = l_run[1];
+    }
+  }
+  __syncthreads();  // every tile consumed: the ring is free to be reused as the cross-warp reduce buffer
+  const bool aborted = (*abort_flag != 0);
+  float* red = reinterpret_cast<float*>(stages);  // [4 warps][16 rows][128]
+  if (warp > 0 && !aborted) {
+    const int cw = warp - 1;
+    const int g = lane >> 2, qd = lane & 3;
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int row = g + rr * 8;
+      if (row < group) {
+        float mg = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) mg = fmaxf(mg, sm_m[w * 16 + row]);
+        const float f = (mg == -INFINITY) ? 0.f : fast_exp2(m_run[rr] - mg);
+        float* dst = red + (cw * 16 + row) * kHeadDim;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          int d0, d1;
+          if constexpr (T::kFp8) {
+            d0 = (j >> 1) * 16 + 4 * qd + (j & 1);
+            d1 = d0 + 2;
+          } else {
+            d0 = j * 8 + 2 * qd;
+            d1 = d0 + 1;
+          }
+          dst[d0] = o[j][2 * rr] * f;
+          dst[d1] = o[j][2 * rr + 1] * f;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (warp > 0 && !aborted) {
+    const int tid = threadIdx.x - 32;  // 0..127 = d
+    float vds = 1.f;
+    if (p.v_descale) vds = p.v_descale[b * p.vds_b + hk * p.vds_h];
+    for (int row = 0; row < group; ++row) {
+      float mg = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) mg = fmaxf(mg, sm_m[w * 16 + row]);
+      float L = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float mw = sm_m[w * 16 + row];
+        L += (mw == -INFINITY) ? 0.f : sm_l[w * 16 + row] * fast_exp2(mw - mg);
+        acc += red[(w * 16 + row) * kHeadDim + tid];
+      }
+      const bool empty = !(L > 0.f);
+      const float outv = empty ? 0.f : acc / L * vds;
+      const float lse = empty ? -INFINITY : (mg + log2f(L)) * kLn2;
+      const int head = hk * group + row;
+      if (p.write_final) {
+        const int64_t oi = static_cast<int64_t>(b) * p.o_batch_stride + static_cast<int64_t>(head) * p.o_head_stride + tid;
+        if (p.out_dtype == FA_B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(outv);
+        else reinterpret_cast<__half*>(p.out)[oi] = __float2half_rn(outv);
+        if (tid == 0 && p.lse_out) p.lse_out[b * p.h + head] = empty ? INFINITY : lse;
+      } else {
+        const int64_t slot = (static_cast<int64_t>(part) * p.b + b) * p.h + head;
+        p.o_partial[slot * kHeadDim + tid] = outv;
+        if (tid == 0) p.lse_partial[slot] = lse;
+      }
+    }
+  }
+}
+
+}  // namespace
+
+size_t decode_smem_bytes(int stages) {
+  return 1024 + static_cast<size_t>(stages) * kStageBytes + 2 * stages * 8 + 2 * kConsumerWarps * 16 * 4 +
+         kMaxPagesPerPartition * 4 + 16;
+}
+int decode_max_pages_per_partition() { return kMaxPagesPerPartition; }
+
+template <int DT>
+static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
+                                    cudaStream_t stream) {
+  constexpr int STAGES = 3;
+  auto kern = decode_paged_kernel<DT, STAGES>;
+  const size_t smem = decode_smem_bytes(STAGES);
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    attr_done[dev] = true;
+  }
+  dim3 grid(p.num_partitions, p.h_k, p.b);
+  kern<<<grid, kDecodeThreads, smem, stream>>>(tk, tv, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_decode(int dtype, const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
+                          cudaStream_t stream) {
+  switch (dtype) {
+    case FA_B200_F16: return launch_decode_dt<FA_B200_F16>(tk, tv, p, stream);
+    case FA_B200_BF16: return launch_decode_dt<FA_B200_BF16>(tk, tv, p, stream);
+    case FA_B200_E4M3: return launch_decode_dt<FA_B200_E4M3>(tk, tv, p, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fa

@@ -1,0 +1,84 @@
+// Internal launch interfaces between the C-ABI layer (fa_api.cu) and the kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace fa {
+
+struct DecodeKernelParams {
+  int* status;         // device status word
+  const void* q;
+  void* out;
+  float* lse_out;
+  const int32_t* block_table;
+  const int32_t* seqlens;
+  const float* q_descale;
+  const float* k_descale;
+  const float* v_descale;
+  float* o_partial;    // [partition][b][h][128] fp32
+  float* lse_partial;  // [partition][b][h] fp32, natural log, -inf = no keys
+  int64_t q_batch_stride, q_head_stride;
+  int64_t o_batch_stride, o_head_stride;
+  int64_t bt_stride;
+  int64_t qds_b, qds_h, kds_b, kds_h, vds_b, vds_h;
+  int32_t b, h, h_k, group;
+  int32_t page_size, box_tok;
+  int32_t partition_tokens, num_partitions;
+  int32_t out_dtype;
+  int32_t write_final;
+  float scale_log2;
+};
+
+size_t decode_smem_bytes(int stages);
+int decode_max_pages_per_partition();
+cudaError_t launch_decode(int dtype, const CUtensorMap& tmap_k, const CUtensorMap& tmap_v,
+                          const DecodeKernelParams& p, cudaStream_t stream);
+
+struct CombineKernelParams {
+  const float* o_partial;    // [num_parts][rows][128]
+  const float* lse_partial;  // [num_parts][rows]
+  void* out;
+  float* lse;
+  const int32_t* seqlens;    // optional: row r uses ceil(seqlens[r / h] / partition_tokens) parts
+  const int32_t* parts_per_row;  // optional explicit count per batch entry
+  int64_t out_row_stride;    // rows are (b, h): element offset = (r / h) * out_batch_stride + (r % h) * out_row_stride
+  int64_t out_batch_stride;
+  int32_t num_parts, rows, h;
+  int32_t partition_tokens;
+  int32_t out_dtype;         // FA_B200_F16 / BF16, or -1 for fp32
+  int32_t lse_empty_is_neg;  // write -inf (partial convention) instead of +inf for rows with no keys
+  float out_scale;
+};
+cudaError_t launch_combine(const CombineKernelParams& p, cudaStream_t stream);
+
+// Prefill (dense / varlen / block-sparse) on tcgen05.
+struct PrefillKernelParams {
+  int* status;         // device status word
+  void* out;
+  float* lse;
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  const float* q_descale;
+  const float* k_descale;
+  const float* v_descale;
+  const int32_t* block_count;
+  const int32_t* block_offset;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t qds_b, qds_h, kds_b, kds_h, vds_b, vds_h;
+  int64_t total_q;
+  int32_t b, h, h_k, seqlen_q, seqlen_k;
+  int32_t num_m_blocks;      // ceil(max seqlen_q / 128)
+  int32_t is_causal;
+  int32_t out_dtype;
+  int32_t num_q_blocks, nnz_s, block_m;  // sparse metadata geometry
+  int32_t sparse;
+  float scale_log2;
+};
+size_t prefill_smem_bytes();
+cudaError_t launch_prefill(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
+                           const CUtensorMap& tmap_v, const PrefillKernelParams& p, cudaStream_t stream);
+
+}  // namespace fa

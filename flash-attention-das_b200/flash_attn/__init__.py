@@ -1,0 +1,13 @@
+"""B200-native drop-in for the forward attention hot path of flash-attention-das.
+
+Same public names as the reference package (flash_attn/__init__.py:5-39) for the entries on the hot path;
+everything calls the sm_100a kernels of libfa_b200.so through ``flash_attn_2_cuda``.
+"""
+__version__ = "2.8.4+b200"
+
+from .flash_attn_interface import (  # noqa: F401
+    flash_attn_func,
+    flash_attn_varlen_func,
+    flash_attn_with_kvcache,
+    sparse_attn_func,
+)

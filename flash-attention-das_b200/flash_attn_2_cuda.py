@@ -1,0 +1,496 @@
+"""``flash_attn_2_cuda`` for B200: the binding module the reference's Python API imports
+(``import flash_attn_2_cuda as flash_attn_cuda``, flash_attn/flash_attn_interface.py:10), re-implemented as a
+thin ctypes layer over the C ABI of ``libfa_b200.so`` (include/fa_b200.h).
+
+It keeps the reference binding's function names, positional argument order and return arity
+(csrc/flash_attn_cutlass/flash_api.cpp:2993-3037):
+
+    fwd          -> 9 tensors  (flash_api.cpp:951-1215)
+    varlen_fwd   -> 8 tensors  (flash_api.cpp:1216-1685)
+    fwd_kvcache  -> [out, softmax_lse]  (flash_api.cpp:2530-2577)
+    fwd_sparse   -> [out, softmax_lse]  (flash_api_sparse.cpp:170-338)
+
+PyTorch is used for what the reference binding used ATen for: output / scratch allocation on the input's
+device and the current stream.  All compute happens in the library's sm_100a kernels; there is no CPU or
+eager fallback — if the shared library is missing the import fails.
+"""
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.environ.get("FA_B200_LIB", os.path.join(_HERE, "libfa_b200.so"))
+if not os.path.exists(_LIB_PATH):
+    raise ImportError(
+        f"{_LIB_PATH} not found: build it with `python {os.path.join(_HERE, 'build.py')}` "
+        "(there is no fallback implementation)")
+_lib = ctypes.CDLL(_LIB_PATH)
+
+F16, BF16, E4M3 = 0, 1, 2
+_DT = {torch.float16: F16, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3}
+
+_c_i64, _c_i32, _c_f32, _c_vp = ctypes.c_int64, ctypes.c_int32, ctypes.c_float, ctypes.c_void_p
+
+
+class FwdParams(ctypes.Structure):
+    """struct fa_b200_fwd_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("q", _c_vp), ("k", _c_vp), ("v", _c_vp), ("out", _c_vp), ("softmax_lse", _c_vp),
+        ("q_batch_stride", _c_i64), ("q_row_stride", _c_i64), ("q_head_stride", _c_i64),
+        ("k_batch_stride", _c_i64), ("k_row_stride", _c_i64), ("k_head_stride", _c_i64),
+        ("v_batch_stride", _c_i64), ("v_row_stride", _c_i64), ("v_head_stride", _c_i64),
+        ("o_batch_stride", _c_i64), ("o_row_stride", _c_i64), ("o_head_stride", _c_i64),
+        ("b", _c_i32), ("seqlen_q", _c_i32), ("seqlen_k", _c_i32), ("h", _c_i32), ("h_k", _c_i32), ("d", _c_i32),
+        ("total_q", _c_i64), ("total_k", _c_i64),
+        ("cu_seqlens_q", _c_vp), ("cu_seqlens_k", _c_vp),
+        ("softmax_scale", _c_f32), ("is_causal", _c_i32), ("dtype", _c_i32), ("out_dtype", _c_i32),
+        ("q_descale", _c_vp), ("k_descale", _c_vp), ("v_descale", _c_vp),
+        ("q_descale_batch_stride", _c_i64), ("q_descale_head_stride", _c_i64),
+        ("k_descale_batch_stride", _c_i64), ("k_descale_head_stride", _c_i64),
+        ("v_descale_batch_stride", _c_i64), ("v_descale_head_stride", _c_i64),
+        ("block_count", _c_vp), ("block_offset", _c_vp),
+        ("num_q_blocks", _c_i32), ("nnz_s", _c_i32), ("block_m", _c_i32),
+    ]
+
+
+class DecodeParams(ctypes.Structure):
+    """struct fa_b200_decode_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("q", _c_vp), ("k_cache", _c_vp), ("v_cache", _c_vp), ("out", _c_vp), ("softmax_lse", _c_vp),
+        ("q_batch_stride", _c_i64), ("q_head_stride", _c_i64),
+        ("o_batch_stride", _c_i64), ("o_head_stride", _c_i64),
+        ("k_block_stride", _c_i64), ("k_row_stride", _c_i64), ("k_head_stride", _c_i64),
+        ("v_block_stride", _c_i64), ("v_row_stride", _c_i64), ("v_head_stride", _c_i64),
+        ("block_table", _c_vp), ("block_table_batch_stride", _c_i64), ("cache_seqlens", _c_vp),
+        ("b", _c_i32), ("h", _c_i32), ("h_k", _c_i32), ("d", _c_i32),
+        ("num_blocks", _c_i32), ("page_size", _c_i32), ("max_blocks_per_seq", _c_i32),
+        ("softmax_scale", _c_f32), ("dtype", _c_i32), ("out_dtype", _c_i32),
+        ("q_descale", _c_vp), ("k_descale", _c_vp), ("v_descale", _c_vp),
+        ("q_descale_batch_stride", _c_i64), ("q_descale_head_stride", _c_i64),
+        ("k_descale_batch_stride", _c_i64), ("k_descale_head_stride", _c_i64),
+        ("v_descale_batch_stride", _c_i64), ("v_descale_head_stride", _c_i64),
+        ("partition_tokens", _c_i32), ("max_seqlen_k", _c_i32),
+        ("workspace", _c_vp), ("workspace_bytes", ctypes.c_size_t),
+        ("o_partial_out", _c_vp), ("lse_partial_out", _c_vp),
+    ]
+
+
+class CombineParams(ctypes.Structure):
+    """struct fa_b200_combine_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("o_partial", _c_vp), ("lse_partial", _c_vp), ("out", _c_vp), ("lse", _c_vp),
+        ("out_row_stride", _c_i64),
+        ("num_parts", _c_i32), ("rows", _c_i32), ("d", _c_i32), ("h", _c_i32),
+        ("parts_per_row", _c_vp), ("out_dtype", _c_i32), ("out_scale", _c_f32),
+    ]
+
+
+_lib.fa_b200_fwd.argtypes = [ctypes.POINTER(FwdParams), _c_vp]
+_lib.fa_b200_fwd.restype = ctypes.c_int
+_lib.fa_b200_fwd_sparse.argtypes = [ctypes.POINTER(FwdParams), _c_vp]
+_lib.fa_b200_fwd_sparse.restype = ctypes.c_int
+_lib.fa_b200_decode_paged.argtypes = [ctypes.POINTER(DecodeParams), _c_vp]
+_lib.fa_b200_decode_paged.restype = ctypes.c_int
+_lib.fa_b200_decode_workspace_bytes.argtypes = [ctypes.POINTER(DecodeParams)]
+_lib.fa_b200_decode_workspace_bytes.restype = ctypes.c_size_t
+_lib.fa_b200_decode_partition_tokens.argtypes = [ctypes.POINTER(DecodeParams)]
+_lib.fa_b200_decode_partition_tokens.restype = ctypes.c_int32
+_lib.fa_b200_combine.argtypes = [ctypes.POINTER(CombineParams), _c_vp]
+_lib.fa_b200_combine.restype = ctypes.c_int
+_lib.fa_b200_status_string.argtypes = [ctypes.c_int]
+_lib.fa_b200_status_string.restype = ctypes.c_char_p
+_lib.fa_b200_last_cuda_error.restype = ctypes.c_char_p
+_lib.fa_b200_device_status.restype = ctypes.c_int
+_lib.fa_b200_abi_version.restype = ctypes.c_int
+_lib.fa_b200_launch_count.restype = ctypes.c_uint64
+
+
+def lib():
+    """The loaded ctypes handle (tests call the C ABI through it)."""
+    return _lib
+
+
+def launch_count() -> int:
+    return int(_lib.fa_b200_launch_count())
+
+
+def device_status() -> int:
+    return int(_lib.fa_b200_device_status())
+
+
+def _check(status: int, what: str):
+    if status != 0:
+        msg = _lib.fa_b200_status_string(status).decode()
+        if status == 10:
+            msg += " (" + _lib.fa_b200_last_cuda_error().decode() + ")"
+        raise RuntimeError(f"{what}: {msg}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require(cond: bool, msg: str):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _unsupported(cond: bool, what: str):
+    if cond:
+        raise NotImplementedError(f"{what} is outside the B200 hot path of this build")
+
+
+def _check_qkv(q, k, v):
+    _require(q.dtype in _DT, "FlashAttention only support fp16, bf16 and fp8 e4m3 data type")
+    _require(k.dtype == q.dtype, "query and key must have the same dtype")
+    _require(v.dtype == q.dtype, "query and value must have the same dtype")
+    _require(q.is_cuda and k.is_cuda and v.is_cuda, "Input tensor must be on CUDA device")
+    for t in (q, k, v):
+        _require(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
+    _require(q.shape[-1] == 128 and v.shape[-1] == 128,
+             "this build implements head dimension 128 only (the hot path named by the B200 port)")
+
+
+def _descale(params, name, t: Optional[torch.Tensor], batch: int, h_k: int):
+    """fp32 descale of numel 1 (per tensor) or shape (batch, h_k) -> pointer + strides."""
+    if t is None:
+        return
+    _require(t.dtype == torch.float32 and t.is_cuda, f"{name} must be a float32 CUDA tensor")
+    setattr(params, name, t.data_ptr())
+    if t.numel() == 1:
+        bs = hs = 0
+    else:
+        _require(t.dim() == 2 and t.shape[0] == batch and t.shape[1] == h_k,
+                 f"{name} must have one element or shape (batch, nheads_k)")
+        bs, hs = t.stride(0), t.stride(1)
+    setattr(params, name + "_batch_stride", bs)
+    setattr(params, name + "_head_stride", hs)
+
+
+def _out_dtype(q, out_):
+    if out_ is not None:
+        _require(out_.dtype in (torch.float16, torch.bfloat16), "Output must be fp16 or bf16")
+        if q.dtype != torch.float8_e4m3fn:
+            _require(out_.dtype == q.dtype, "Output must have the same dtype as inputs")
+        return out_.dtype
+    return torch.bfloat16 if q.dtype == torch.float8_e4m3fn else q.dtype
+
+
+# ------------------------------------------------------------------------------------------------
+# fwd  (fixed length)
+# ------------------------------------------------------------------------------------------------
+def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, window_size_left, window_size_right,
+        softcap, return_softmax, gen_, is_bhsd=False, s_aux_=None, skip_softmax_threshold_scale_factor=0.0):
+    _check_qkv(q, k, v)
+    _unsupported(is_bhsd, "bhsd layout")
+    _unsupported(alibi_slopes_ is not None, "alibi")
+    _unsupported(p_dropout != 0.0, "dropout")
+    _unsupported(softcap != 0.0, "softcap")
+    _unsupported(return_softmax, "return_softmax")
+    _unsupported(s_aux_ is not None, "attention sinks (s_aux)")
+    _unsupported(skip_softmax_threshold_scale_factor != 0.0, "skip-softmax")
+    b, sq, h, d = q.shape
+    sk, h_k = k.shape[1], k.shape[2]
+    _require(b > 0, "batch size must be positive")
+    _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
+    _require(tuple(k.shape) == (b, sk, h_k, d) and tuple(v.shape) == (b, sk, h_k, d), "k/v shape mismatch")
+    # window normalisation as in mha_fwd (flash_api.cpp:1055-1060)
+    if window_size_left >= sk:
+        window_size_left = -1
+    if window_size_right >= sk:
+        window_size_right = -1
+    if sq == 1 and alibi_slopes_ is None:
+        is_causal = False
+    if is_causal:
+        window_size_right = 0
+    causal = window_size_left < 0 and window_size_right == 0
+    _unsupported(not causal and (window_size_left >= 0 or window_size_right >= 0), "sliding-window attention")
+    if q.data_ptr() == k.data_ptr():
+        q = q.clone()
+    odt = _out_dtype(q, out_)
+    if out_ is not None:
+        _require(tuple(out_.shape) == (b, sq, h, d), "out has wrong shape")
+        _require(out_.stride(-1) == 1, "Output tensor must have contiguous last dimension")
+        out = out_
+    else:
+        out = torch.empty((b, sq, h, d), dtype=odt, device=q.device)
+    lse = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
+    p = FwdParams()
+    p.q, p.k, p.v, p.out, p.softmax_lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    p.q_batch_stride, p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1), q.stride(2)
+    p.k_batch_stride, p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1), k.stride(2)
+    p.v_batch_stride, p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1), v.stride(2)
+    p.o_batch_stride, p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1), out.stride(2)
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = b, sq, sk, h, h_k, d
+    p.softmax_scale = softmax_scale
+    p.is_causal = 1 if causal else 0
+    p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
+    with torch.cuda.device(q.device):
+        _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "fwd")
+    rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
+    s_dmask = torch.empty((0,), dtype=q.dtype, device=q.device)
+    skip_blocks_info = torch.empty((0,), dtype=torch.int32, device=q.device)
+    return [out, q, k, v, out, lse, s_dmask, rng_state, skip_blocks_info]
+
+
+# ------------------------------------------------------------------------------------------------
+# varlen_fwd  (packed sequences)
+# ------------------------------------------------------------------------------------------------
+def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_, block_table_, alibi_slopes_,
+               max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
+               window_size_right, softcap, return_softmax, q_descale_=None, k_descale_=None, v_descale_=None,
+               gen_=None, s_aux_=None):
+    _check_qkv(q, k, v)
+    _unsupported(block_table_ is not None, "paged prefill through varlen_fwd")
+    _unsupported(seqused_k is not None, "seqused_k")
+    _unsupported(leftpad_k_ is not None, "leftpad_k")
+    _unsupported(alibi_slopes_ is not None, "alibi")
+    _unsupported(p_dropout != 0.0, "dropout")
+    _unsupported(softcap != 0.0, "softcap")
+    _unsupported(return_softmax, "return_softmax")
+    _unsupported(s_aux_ is not None, "attention sinks (s_aux)")
+    for name, t in (("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_k", cu_seqlens_k)):
+        _require(t.dtype == torch.int32, f"{name} must have dtype int32")
+        _require(t.is_cuda, f"{name} must be on CUDA device")
+        _require(t.is_contiguous(), f"{name} must be contiguous")
+    total_q, h, d = q.shape
+    total_k, h_k = k.shape[0], k.shape[1]
+    b = cu_seqlens_q.numel() - 1
+    _require(b > 0, "batch size must be positive")
+    _require(cu_seqlens_k.numel() == b + 1, "cu_seqlens_k must have shape (batch_size + 1)")
+    _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
+    if window_size_left >= max_seqlen_k:
+        window_size_left = -1
+    if window_size_right >= max_seqlen_k:
+        window_size_right = -1
+    if max_seqlen_q == 1 and alibi_slopes_ is None:
+        is_causal = False
+    if is_causal:
+        window_size_right = 0
+    causal = window_size_left < 0 and window_size_right == 0
+    _unsupported(not causal and (window_size_left >= 0 or window_size_right >= 0), "sliding-window attention")
+    if q.data_ptr() == k.data_ptr():
+        q = q.clone()
+    odt = _out_dtype(q, out_)
+    if out_ is not None:
+        _require(tuple(out_.shape) == (total_q, h, d), "out has wrong shape")
+        _require(out_.stride(-1) == 1, "Output tensor must have contiguous last dimension")
+        out = out_
+    else:
+        out = torch.empty((total_q, h, d), dtype=odt, device=q.device)
+    lse = torch.empty((h, total_q), dtype=torch.float32, device=q.device)
+    if zero_tensors:
+        out.zero_()
+        lse.fill_(float("-inf"))
+    p = FwdParams()
+    p.q, p.k, p.v, p.out, p.softmax_lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
+    p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1)
+    p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1)
+    p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1)
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = b, max_seqlen_q, max_seqlen_k, h, h_k, d
+    p.total_q, p.total_k = total_q, total_k
+    p.cu_seqlens_q, p.cu_seqlens_k = cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr()
+    p.softmax_scale = softmax_scale
+    p.is_causal = 1 if causal else 0
+    p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
+    _descale(p, "q_descale", q_descale_, b, h_k)
+    _descale(p, "k_descale", k_descale_, b, h_k)
+    _descale(p, "v_descale", v_descale_, b, h_k)
+    with torch.cuda.device(q.device):
+        _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "varlen_fwd")
+    rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
+    s_dmask = torch.empty((0,), dtype=q.dtype, device=q.device)
+    return [out, q, k, v, out, lse, s_dmask, rng_state]
+
+
+# ------------------------------------------------------------------------------------------------
+# fwd_kvcache  (paged decode)
+# ------------------------------------------------------------------------------------------------
+_workspaces = {}
+
+
+def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
+    """Scratch for split-KV partials.  Cached per (device, stream) and grown on demand, like the
+    reference's workspace cache (src/paged_attention.cu:712-745); under graph capture a fresh buffer is
+    taken from the caching allocator instead."""
+    if nbytes == 0:
+        return None
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out, lse, q_descale=None,
+                   k_descale=None, v_descale=None, partition_tokens=0, max_seqlen_k=0):
+    b, sq, h, d = q.shape
+    num_blocks, page, h_k = kcache.shape[0], kcache.shape[1], kcache.shape[2]
+    p = DecodeParams()
+    p.q, p.k_cache, p.v_cache = q.data_ptr(), kcache.data_ptr(), vcache.data_ptr()
+    p.out, p.softmax_lse = _ptr(out), _ptr(lse)
+    p.q_batch_stride, p.q_head_stride = q.stride(0), q.stride(2)
+    if out is not None:
+        p.o_batch_stride, p.o_head_stride = out.stride(0), out.stride(2)
+    p.k_block_stride, p.k_row_stride, p.k_head_stride = kcache.stride(0), kcache.stride(1), kcache.stride(2)
+    p.v_block_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
+    p.block_table, p.block_table_batch_stride = block_table.data_ptr(), block_table.stride(0)
+    p.cache_seqlens = seqlens_k.data_ptr()
+    p.b, p.h, p.h_k, p.d = b, h, h_k, d
+    p.num_blocks, p.page_size, p.max_blocks_per_seq = num_blocks, page, block_table.shape[1]
+    p.softmax_scale = softmax_scale
+    p.dtype = _DT[q.dtype]
+    p.out_dtype = _DT[out.dtype] if out is not None else BF16
+    _descale(p, "q_descale", q_descale, b, h_k)
+    _descale(p, "k_descale", k_descale, b, h_k)
+    _descale(p, "v_descale", v_descale, b, h_k)
+    p.partition_tokens = partition_tokens
+    p.max_seqlen_k = max_seqlen_k
+    return p
+
+
+def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_, cache_batch_idx_, leftpad_k_,
+                block_table_, alibi_slopes_, out_, softmax_scale, is_causal, window_size_left, window_size_right,
+                softcap, is_rotary_interleaved, num_splits, s_aux_=None, q_descale_=None, k_descale_=None,
+                v_descale_=None, max_seqlen_k=0):
+    """Paged decode.  Like the reference's mha_fwd_kvcache (flash_api.cpp:2530-2577) this path needs
+    ``block_table`` and ``seqlens_k`` and ignores nothing silently: the options the reference's wrapper drops
+    (new k/v append, rotary, cache_batch_idx, leftpad) raise instead.  Unlike the reference, the returned
+    softmax_lse is filled in."""
+    _check_qkv(q, kcache, vcache)
+    _unsupported(k_ is not None or v_ is not None, "appending new k/v in the decode call")
+    _unsupported(rotary_cos_ is not None or rotary_sin_ is not None, "rotary embedding in the decode call")
+    _unsupported(cache_batch_idx_ is not None, "cache_batch_idx")
+    _unsupported(leftpad_k_ is not None, "cache_leftpad")
+    _unsupported(alibi_slopes_ is not None, "alibi")
+    _unsupported(softcap != 0.0, "softcap")
+    _unsupported(s_aux_ is not None, "attention sinks (s_aux)")
+    _require(block_table_ is not None, "block_table is required (paged KV cache)")
+    _require(seqlens_k_ is not None, "cache_seqlens is required")
+    _require(block_table_.dtype == torch.int32, "block_table must have dtype torch.int32")
+    _require(block_table_.stride(-1) == 1, "block_table must have contiguous last dimension")
+    _require(seqlens_k_.dtype == torch.int32, "seqlens_k must have dtype int32")
+    _require(seqlens_k_.is_contiguous(), "seqlens_k must be contiguous")
+    b, sq, h, d = q.shape
+    _unsupported(sq != 1, "more than one query token per sequence in the decode call")
+    _unsupported(window_size_left >= 0 and window_size_left < kcache.shape[1] * block_table_.shape[1],
+                 "sliding-window attention")
+    _require(seqlens_k_.numel() == b and block_table_.shape[0] == b, "cache_seqlens / block_table batch mismatch")
+    _require(kcache.shape == vcache.shape, "k_cache and v_cache must have the same shape")
+    h_k = kcache.shape[2]
+    _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
+    odt = _out_dtype(q, out_)
+    if out_ is not None:
+        _require(tuple(out_.shape) == (b, sq, h, d), "out has wrong shape")
+        _require(out_.stride(-1) == 1, "Output tensor must have contiguous last dimension")
+        out = out_
+    else:
+        out = torch.empty((b, sq, h, d), dtype=odt, device=q.device)
+    lse = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
+    p = _decode_params(q, kcache, vcache, seqlens_k_, block_table_, softmax_scale, out, lse, q_descale_, k_descale_,
+                       v_descale_, 0, max_seqlen_k)
+    with torch.cuda.device(q.device):
+        ws = _workspace(q.device, int(_lib.fa_b200_decode_workspace_bytes(ctypes.byref(p))))
+        if ws is not None:
+            p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        _check(_lib.fa_b200_decode_paged(ctypes.byref(p), _stream(q)), "fwd_kvcache")
+    return [out, lse]
+
+
+def decode_partial(q, kcache, vcache, seqlens_k, block_table, softmax_scale, q_descale=None, k_descale=None,
+                   v_descale=None, max_seqlen_k=0):
+    """Decode over a LOCAL slice of each sequence's pages and return the unnormalised-merge inputs
+    (o_partial fp32 (b, h, d), lse fp32 (b, h)) for a cross-GPU combine (one sequence split-KV across GPUs)."""
+    _check_qkv(q, kcache, vcache)
+    b, sq, h, d = q.shape
+    _require(sq == 1, "decode_partial takes one query token per sequence")
+    o_part = torch.empty((b, h, d), dtype=torch.float32, device=q.device)
+    lse_part = torch.empty((b, h), dtype=torch.float32, device=q.device)
+    p = _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, None, None, q_descale, k_descale,
+                       v_descale, 0, max_seqlen_k)
+    p.o_partial_out, p.lse_partial_out = o_part.data_ptr(), lse_part.data_ptr()
+    with torch.cuda.device(q.device):
+        ws = _workspace(q.device, int(_lib.fa_b200_decode_workspace_bytes(ctypes.byref(p))))
+        if ws is not None:
+            p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        _check(_lib.fa_b200_decode_paged(ctypes.byref(p), _stream(q)), "decode_partial")
+    return o_part, lse_part
+
+
+def combine(o_partial, lse_partial, out_dtype=torch.bfloat16, h: Optional[int] = None, parts_per_row=None):
+    """LSE-combine: o_partial (parts, rows, 128) fp32, lse_partial (parts, rows) fp32 ->
+    (out (rows, 128) out_dtype, lse (rows) fp32)."""
+    _require(o_partial.dtype == torch.float32 and lse_partial.dtype == torch.float32, "partials must be fp32")
+    _require(o_partial.is_contiguous() and lse_partial.is_contiguous(), "partials must be contiguous")
+    parts, rows, d = o_partial.shape
+    out = torch.empty((rows, d), dtype=out_dtype, device=o_partial.device)
+    lse = torch.empty((rows,), dtype=torch.float32, device=o_partial.device)
+    p = CombineParams()
+    p.o_partial, p.lse_partial, p.out, p.lse = o_partial.data_ptr(), lse_partial.data_ptr(), out.data_ptr(), lse.data_ptr()
+    p.out_row_stride = d
+    p.num_parts, p.rows, p.d, p.h = parts, rows, d, (h or 1)
+    p.parts_per_row = _ptr(parts_per_row)
+    p.out_dtype = -1 if out_dtype == torch.float32 else _DT[out_dtype]
+    p.out_scale = 1.0
+    with torch.cuda.device(o_partial.device):
+        _check(_lib.fa_b200_combine(ctypes.byref(p), _stream(o_partial)), "combine")
+    return out, lse
+
+
+# ------------------------------------------------------------------------------------------------
+# fwd_sparse  (block-list attention)
+# ------------------------------------------------------------------------------------------------
+def fwd_sparse(q, k, v, block_count, block_offset, column_count, column_index, out_, alibi_slopes_, p_dropout,
+               softmax_scale, is_causal, softcap, return_softmax, gen_, is_sla=False, pv_threshold=50.0,
+               enable_dynamic_skip=False):
+    _check_qkv(q, k, v)
+    _unsupported(alibi_slopes_ is not None, "alibi")
+    _unsupported(p_dropout != 0.0, "dropout")
+    _unsupported(softcap != 0.0, "softcap")
+    _unsupported(return_softmax, "return_softmax")
+    _unsupported(is_sla, "SLA sparse attention")
+    _unsupported(enable_dynamic_skip, "dynamic PV skip")
+    b, sq, h, d = q.shape
+    sk, h_k = k.shape[1], k.shape[2]
+    _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
+    for name, t in (("block_count", block_count), ("block_offset", block_offset)):
+        _require(t.dtype == torch.int32 and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous int32 CUDA tensor")
+    if column_count is not None:
+        _require(column_count.dtype == torch.int32, "column_count must have dtype int32")
+        _unsupported(bool((column_count != 0).any().item()), "vertical (column_index) sparsity")
+    # host rule of the reference: NUM_ROWS == ceil(Sq / (Sq <= 2048 ? 64 : 128)) (flash_api_sparse.cpp:127-137)
+    block_m = 64 if sq <= 2048 else 128
+    num_rows = (sq + block_m - 1) // block_m
+    _require(tuple(block_count.shape) == (b, h, num_rows), "block_count must have shape (batch, nheads, NUM_ROWS)")
+    _require(block_offset.dim() == 4 and tuple(block_offset.shape[:3]) == (b, h, num_rows),
+             "block_offset must have shape (batch, nheads, NUM_ROWS, NNZ_S)")
+    if sq == 1:
+        is_causal = False
+    odt = _out_dtype(q, out_)
+    out = out_ if out_ is not None else torch.empty((b, sq, h, d), dtype=odt, device=q.device)
+    lse = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
+    p = FwdParams()
+    p.q, p.k, p.v, p.out, p.softmax_lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    p.q_batch_stride, p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1), q.stride(2)
+    p.k_batch_stride, p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1), k.stride(2)
+    p.v_batch_stride, p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1), v.stride(2)
+    p.o_batch_stride, p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1), out.stride(2)
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = b, sq, sk, h, h_k, d
+    p.softmax_scale = softmax_scale
+    p.is_causal = 1 if is_causal else 0
+    p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
+    p.block_count, p.block_offset = block_count.data_ptr(), block_offset.data_ptr()
+    p.num_q_blocks, p.nnz_s, p.block_m = num_rows, block_offset.shape[3], block_m
+    with torch.cuda.device(q.device):
+        _check(_lib.fa_b200_fwd_sparse(ctypes.byref(p), _stream(q)), "fwd_sparse")
+    return [out, lse]

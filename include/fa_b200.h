@@ -1,0 +1,198 @@
+/*
+ * fa_b200.h — C ABI of libfa_b200.so: the forward attention hot path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers to DEVICE memory, sizes and strides (in elements), and a
+ * CUDA stream passed as void* (a cudaStream_t).  Nothing here allocates, synchronises or throws:
+ * a call validates its arguments, enqueues kernels on the given stream and returns a status code
+ * (0 = ok).  Scratch memory is owned by the caller (see fa_b200_decode_workspace_bytes).
+ *
+ * The "replaces" notes name the interface of the reference project (HYGON-AI/flash-attention-das,
+ * paths relative to its root) that each entry point stands in for.
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define FA_B200_API __attribute__((visibility("default")))
+#else
+#define FA_B200_API
+#endif
+
+/* element types */
+enum { FA_B200_F16 = 0, FA_B200_BF16 = 1, FA_B200_E4M3 = 2 };
+
+/* status codes (host side).  fa_b200_status_string() gives the text. */
+enum {
+  FA_B200_OK = 0,
+  FA_B200_ERR_NULL = 1,          /* a required pointer is null */
+  FA_B200_ERR_DTYPE = 2,         /* unsupported element type combination */
+  FA_B200_ERR_HEADDIM = 3,       /* head dimension other than 128 */
+  FA_B200_ERR_HEADS = 4,         /* h not a multiple of h_k, or group too large for the decode tile */
+  FA_B200_ERR_STRIDE = 5,        /* last dim not contiguous / stride not 16-byte aligned */
+  FA_B200_ERR_SHAPE = 6,         /* negative or inconsistent sizes */
+  FA_B200_ERR_PAGE = 7,          /* page size not a multiple of 16 (or of 64 above 64) */
+  FA_B200_ERR_WORKSPACE = 8,     /* workspace missing or too small */
+  FA_B200_ERR_UNSUPPORTED = 9,   /* option outside the hot path */
+  FA_B200_ERR_CUDA = 10,         /* a CUDA runtime / driver call failed; see fa_b200_last_cuda_error */
+  FA_B200_ERR_ALIGN = 11,        /* base pointer not 16-byte aligned */
+  FA_B200_ERR_DEVICE_TIMEOUT = 12, /* a bounded device-side wait gave up (reported by fa_b200_device_status) */
+  FA_B200_ERR_TOO_LARGE = 13     /* size beyond a fixed built-in limit */
+};
+
+/*
+ * Dense and varlen forward (also the block-sparse forward when block_count/block_offset are set).
+ * Mirrors the fields of Flash_fwd_params that the forward path reads
+ * (csrc/flash_attn_cutlass/src/flash.h:52-206): pointers, batch/row/head strides in ELEMENTS,
+ * b, h, h_k, seqlen_q/k, d, total_q, cu_seqlens, scale, descale pointers and strides, is_causal.
+ *
+ * Fixed length: cu_seqlens_q == cu_seqlens_k == NULL; q is (b, seqlen_q, h, d), k/v (b, seqlen_k, h_k, d);
+ *               softmax_lse is (b, h, seqlen_q) fp32.
+ * Varlen:       q is (total_q, h, d), k/v (total_k, h_k, d) packed; cu_seqlens_* are int32 (b + 1);
+ *               seqlen_q/seqlen_k are the MAXIMUM lengths; softmax_lse is (h, total_q) fp32.
+ * Fully masked rows give out = 0 and lse = +inf.  The causal mask is bottom-right aligned.
+ */
+typedef struct fa_b200_fwd_params {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* softmax_lse;
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t k_batch_stride, k_row_stride, k_head_stride;
+  int64_t v_batch_stride, v_row_stride, v_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int32_t b, seqlen_q, seqlen_k, h, h_k, d;
+  int64_t total_q, total_k;            /* varlen only */
+  const int32_t* cu_seqlens_q;         /* NULL for fixed length */
+  const int32_t* cu_seqlens_k;
+  float softmax_scale;
+  int32_t is_causal;
+  int32_t dtype;                       /* of q, k, v: FA_B200_F16 / BF16 / E4M3 */
+  int32_t out_dtype;                   /* F16 or BF16 (BF16 for E4M3 inputs by default) */
+  /* FP8 descale, fp32, indexed [batch * batch_stride + kv_head * head_stride]; NULL = 1.0 */
+  const float* q_descale;
+  const float* k_descale;
+  const float* v_descale;
+  int64_t q_descale_batch_stride, q_descale_head_stride;
+  int64_t k_descale_batch_stride, k_descale_head_stride;
+  int64_t v_descale_batch_stride, v_descale_head_stride;
+  /* block-sparse lists (fa_b200_fwd_sparse only), int32:
+   *   block_count  (b, h, num_q_blocks), block_offset (b, h, num_q_blocks, nnz_s) = ascending K ROW
+   *   offsets of 64-row K tiles (csrc/flash_attn_cutlass/flash_api_sparse.cpp:70-138). */
+  const int32_t* block_count;
+  const int32_t* block_offset;
+  int32_t num_q_blocks, nnz_s, block_m;
+} fa_b200_fwd_params;
+
+/* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch
+ * (csrc/flash_attn_cutlass/flash_api.cpp:951-1215, 1216-1685; flash_c_api.cpp:96-144;
+ *  src/flash_fwd_kernel.h:2818-3328, FP8: 3330-3778). */
+FA_B200_API int fa_b200_fwd(const fa_b200_fwd_params* p, void* stream);
+
+/* Replaces mha_fwd_sparse -> run_mha_fwd_sparse -> sparse_attn_1rowblock
+ * (csrc/flash_attn_cutlass/flash_api_sparse.cpp:170-338, 140-149;
+ *  src/flash_fwd_sparse_kernel.h:36-775), block-list path only. */
+FA_B200_API int fa_b200_fwd_sparse(const fa_b200_fwd_params* p, void* stream);
+
+/*
+ * Paged-KV decode (one query token per sequence, GQA group packed into one query tile), split-KV
+ * over fixed-size token partitions plus an LSE-combine kernel.
+ * k_cache / v_cache: (num_blocks, page_size, h_k, d); block_table: int32 (b, max_blocks_per_seq);
+ * cache_seqlens: int32 (b).  Physical page of token t of sequence s is
+ * block_table[s * block_table_batch_stride + t / page_size], row t % page_size
+ * (same addressing as src/paged_attention.cu:146,209 and paged_attention_decode_arch.h:3992-3998).
+ */
+typedef struct fa_b200_decode_params {
+  const void* q;                       /* (b, 1, h, d) */
+  const void* k_cache;
+  const void* v_cache;
+  void* out;                           /* (b, 1, h, d) */
+  float* softmax_lse;                  /* (b, h) fp32 or NULL */
+  int64_t q_batch_stride, q_head_stride;
+  int64_t o_batch_stride, o_head_stride;
+  int64_t k_block_stride, k_row_stride, k_head_stride;
+  int64_t v_block_stride, v_row_stride, v_head_stride;
+  const int32_t* block_table;
+  int64_t block_table_batch_stride;
+  const int32_t* cache_seqlens;
+  int32_t b, h, h_k, d;
+  int32_t num_blocks, page_size, max_blocks_per_seq;
+  float softmax_scale;
+  int32_t dtype;                       /* of q and the cache */
+  int32_t out_dtype;
+  const float* q_descale;              /* as in fa_b200_fwd_params */
+  const float* k_descale;
+  const float* v_descale;
+  int64_t q_descale_batch_stride, q_descale_head_stride;
+  int64_t k_descale_batch_stride, k_descale_head_stride;
+  int64_t v_descale_batch_stride, v_descale_head_stride;
+  int32_t partition_tokens;            /* 0 = heuristic; else a multiple of 64 (128 for E4M3) */
+  int32_t max_seqlen_k;                /* upper bound on cache_seqlens; 0 = max_blocks_per_seq * page_size */
+  void* workspace;                     /* fa_b200_decode_workspace_bytes() bytes, 16-byte aligned */
+  size_t workspace_bytes;
+  /* If set, the call stops before the final normalisation/cast and returns, per sequence and head,
+   * the merged fp32 partial (o_partial_out (b, h, d), lse_partial_out (b, h)) for a cross-GPU
+   * combine; out may then be NULL. */
+  float* o_partial_out;
+  float* lse_partial_out;
+} fa_b200_decode_params;
+
+/* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)
+ * (csrc/flash_attn_cutlass/flash_api.cpp:2530-2577; src/paged_attention.cu:747-1149, 61-558;
+ *  src/paged_attention.h:356-445). */
+FA_B200_API int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream);
+
+/* Bytes of scratch fa_b200_decode_paged needs for these sizes (0 when no split is used).
+ * Replaces the per-(device, stream) workspace cache of src/paged_attention.cu:712-745. */
+FA_B200_API size_t fa_b200_decode_workspace_bytes(const fa_b200_decode_params* p);
+
+/* The partition size (tokens) the heuristic picks for these sizes. */
+FA_B200_API int32_t fa_b200_decode_partition_tokens(const fa_b200_decode_params* p);
+
+/*
+ * LSE-combine of split-KV partials: o_partial (num_parts, rows, d) fp32 (each normalised by its own
+ * partition), lse_partial (num_parts, rows) fp32 natural log (-inf / +inf = empty partition).
+ * rows = b * h.  If parts_per_row is non-NULL (int32 (b)), row r uses only its first
+ * parts_per_row[r / h] partitions.  Writes out (rows, d) in out_dtype (or fp32 when out_dtype < 0)
+ * and lse (rows) fp32 (either may be NULL).
+ * Replaces paged_attention_combine (src/paged_attention.h:356-445) and
+ * flash_fwd_splitkv_reduce_varlen_kernel (csrc/flash_attn_hipc/src/flash_fwd_reduce.h:313-464).
+ */
+typedef struct fa_b200_combine_params {
+  const float* o_partial;
+  const float* lse_partial;
+  void* out;
+  float* lse;
+  int64_t out_row_stride;              /* elements between consecutive rows of out */
+  int32_t num_parts, rows, d, h;
+  const int32_t* parts_per_row;
+  int32_t out_dtype;
+  float out_scale;                     /* multiplies out (v_descale); 1.0 normally */
+} fa_b200_combine_params;
+
+FA_B200_API int fa_b200_combine(const fa_b200_combine_params* p, void* stream);
+
+/* Text for a status code. */
+FA_B200_API const char* fa_b200_status_string(int status);
+/* Last cudaError_t / CUresult text recorded by a failing call on this thread ("" if none). */
+FA_B200_API const char* fa_b200_last_cuda_error(void);
+/* Reads (with a device synchronise) and clears the device-side status word of the current device:
+ * 0, or FA_B200_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up since the last call. */
+FA_B200_API int fa_b200_device_status(void);
+FA_B200_API int fa_b200_abi_version(void);
+/* Number of kernels this library has launched in this process (for launch accounting). */
+FA_B200_API uint64_t fa_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */

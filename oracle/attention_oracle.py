@@ -88,7 +88,7 @@ def attention_ref(q, k, v, causal=False, upcast=True, reorder_ops=False, softmax
 
 def attention_varlen_ref(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, upcast=True,
                          softmax_scale=None, q_descale=None, k_descale=None, v_descale=None,
-                         intermediate_dtype=None):
+                         intermediate_dtype=None, reorder_ops=False, out_dtype=None):
     """Packed varlen attention, one sequence at a time.  Follows attention_varlen_ref
     (tests/test_flash_attn.py:432-494): LSE is (h, total_q) with -inf replaced by +inf and empty
     key ranges give zeros.  Descales are (batch, heads_k) fp32 or None."""
@@ -103,11 +103,12 @@ def attention_varlen_ref(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, upca
         if ki.shape[1] == 0:
             is_fp8 = q.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
             outs.append(torch.zeros(qi.shape[1], q.shape[1], v.shape[-1],
-                                    dtype=torch.bfloat16 if is_fp8 else q.dtype))
+                                    dtype=out_dtype or (torch.bfloat16 if is_fp8 else q.dtype)))
             lses.append(torch.full((q.shape[1], qi.shape[1]), float("inf")))
             continue
         o, l = attention_ref(
             qi, ki, vi, causal=causal, upcast=upcast, softmax_scale=softmax_scale,
+            reorder_ops=reorder_ops, out_dtype=out_dtype,
             q_descale=None if q_descale is None else q_descale[b:b + 1],
             k_descale=None if k_descale is None else k_descale[b:b + 1],
             v_descale=None if v_descale is None else v_descale[b:b + 1],
@@ -142,7 +143,8 @@ def gather_paged_kv(cache: torch.Tensor, block_table_row: torch.Tensor, seqlen: 
 
 
 def paged_decode_ref(q, k_cache, v_cache, cache_seqlens, block_table, softmax_scale=None,
-                     causal=True, q_descale=None, k_descale=None, v_descale=None):
+                     causal=True, q_descale=None, k_descale=None, v_descale=None, upcast=True,
+                     reorder_ops=False, out_dtype=None):
     """Decode over a paged cache, one sequence at a time (a whole-batch call would need the GQA
     repeat of every sequence at once).  Follows the per-sequence loop of tests/test_pa.py:33-48,
     91-106 and the kvcache test (tests/test_flash_attn.py:3221-3236).
@@ -156,11 +158,12 @@ def paged_decode_ref(q, k_cache, v_cache, cache_seqlens, block_table, softmax_sc
         if L == 0:
             is_fp8 = q.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
             outs.append(torch.zeros(1, q.shape[1], q.shape[2], q.shape[3],
-                                    dtype=torch.bfloat16 if is_fp8 else q.dtype))
+                                    dtype=out_dtype or (torch.bfloat16 if is_fp8 else q.dtype)))
             lses.append(torch.full((1, q.shape[2], q.shape[1]), float("inf")))
             continue
         o, l = attention_ref(
-            q[i:i + 1], ki, vi, causal=causal, softmax_scale=softmax_scale,
+            q[i:i + 1], ki, vi, causal=causal, softmax_scale=softmax_scale, upcast=upcast,
+            reorder_ops=reorder_ops, out_dtype=out_dtype,
             q_descale=None if q_descale is None else q_descale[i:i + 1],
             k_descale=None if k_descale is None else k_descale[i:i + 1],
             v_descale=None if v_descale is None else v_descale[i:i + 1])

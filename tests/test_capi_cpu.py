@@ -1,0 +1,88 @@
+"""CPU: the C-ABI library loads and exports every symbol that include/fa_b200.h declares; host-side argument
+validation returns status codes without touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def binding():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_fa_build", os.path.join(ROOT, "flash-attention-das_b200", "build.py"))
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
+    b.build()
+    import flash_attn_2_cuda
+    return flash_attn_2_cuda
+
+
+def test_every_declared_symbol_is_exported(binding):
+    hdr = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
+    names = re.findall(r"FA_B200_API\s+[\w\s\*]+?\b(fa_b200_\w+)\s*\(", hdr)
+    assert len(names) >= 11
+    lib = binding.lib()
+    for n in names:
+        assert hasattr(lib, n), n
+    assert lib.fa_b200_abi_version() == 1
+
+
+def test_struct_sizes_match_header(binding):
+    # field counts guard against the ctypes mirrors drifting from the header
+    hdr = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
+    for struct, cls in (("fa_b200_fwd_params", binding.FwdParams), ("fa_b200_decode_params", binding.DecodeParams),
+                        ("fa_b200_combine_params", binding.CombineParams)):
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), hdr, re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        fields = []
+        for stmt in body.split(";"):
+            stmt = stmt.strip()
+            if not stmt:
+                continue
+            fields += [re.findall(r"(\w+)\s*$", x.strip())[0] for x in stmt.split(",")]
+        assert fields == [f[0] for f in cls._fields_], struct
+
+
+def test_status_strings(binding):
+    lib = binding.lib()
+    assert lib.fa_b200_status_string(0) == b"ok"
+    assert b"128" in lib.fa_b200_status_string(3)
+    assert lib.fa_b200_status_string(99) == b"unknown status"
+
+
+def test_host_validation_needs_no_gpu(binding):
+    lib = binding.lib()
+    assert lib.fa_b200_fwd(None, None) == 1
+    p = binding.FwdParams()
+    p.d = 64
+    assert lib.fa_b200_fwd(ctypes.byref(p), None) == 3          # head dim
+    p.d, p.dtype, p.out_dtype = 128, 7, 1
+    assert lib.fa_b200_fwd(ctypes.byref(p), None) == 2          # dtype
+    p.dtype, p.b, p.h, p.h_k, p.seqlen_q, p.seqlen_k = 1, 1, 6, 4, 8, 8
+    assert lib.fa_b200_fwd(ctypes.byref(p), None) == 4          # heads
+    d = binding.DecodeParams()
+    d.d, d.dtype, d.out_dtype, d.b, d.h, d.h_k, d.page_size, d.max_blocks_per_seq = 128, 1, 1, 2, 8, 2, 48, 4
+    assert lib.fa_b200_decode_paged(ctypes.byref(d), None) == 7  # page size
+    d.page_size = 256
+    d.h = 64
+    assert lib.fa_b200_decode_paged(ctypes.byref(d), None) == 4  # group of 32 > 16
+    d.h = 8
+    assert lib.fa_b200_decode_paged(ctypes.byref(d), None) == 1  # null pointers
+
+
+def test_partition_heuristic_and_workspace(binding):
+    lib = binding.lib()
+    d = binding.DecodeParams()
+    d.d, d.dtype, d.out_dtype = 128, 1, 1
+    d.b, d.h, d.h_k, d.page_size, d.max_blocks_per_seq = 64, 32, 8, 256, 128
+    part = lib.fa_b200_decode_partition_tokens(ctypes.byref(d))
+    assert part % 64 == 0 and 512 <= part <= 4096
+    nparts = (128 * 256 + part - 1) // part
+    assert lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) == nparts * 64 * 32 * 129 * 4
+    d.b, d.max_blocks_per_seq = 2, 1      # one page per sequence: no split, no scratch
+    assert lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) == 0
+    d.partition_tokens = 100               # not a multiple of the tile
+    assert lib.fa_b200_decode_partition_tokens(ctypes.byref(d)) == 0

@@ -1,0 +1,189 @@
+"""GPU parity: paged-KV decode (fa_b200_decode_paged through the reference-shaped Python API) and the
+LSE-combine kernel against the CPU oracle and the committed golden vectors."""
+import importlib.util
+import os
+
+import pytest
+import torch
+
+from oracle import attention_oracle as O
+from _util import assert_close_to_oracle, clean_nan, gen, make_paged, max_err, randn
+
+pytestmark = pytest.mark.gpu
+
+_spec = importlib.util.spec_from_file_location(
+    "make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
+_mg = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(_mg)
+
+
+@pytest.fixture(scope="module")
+def fa():
+    import flash_attn
+    import flash_attn_2_cuda
+    assert os.path.dirname(flash_attn.__file__).endswith(os.path.join("flash-attention-das_b200", "flash_attn"))
+    assert torch.cuda.is_available()
+    return flash_attn, flash_attn_2_cuda
+
+
+def _run_decode(fa, q, kc, vc, lens, bt, monkeypatch=None, partition=None, **kw):
+    flash_attn, cuda = fa
+    if partition is not None:
+        os.environ["FA_B200_DECODE_PARTITION"] = str(partition)
+    else:
+        os.environ.pop("FA_B200_DECODE_PARTITION", None)
+    try:
+        out, lse = flash_attn.flash_attn_with_kvcache(
+            q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=lens.cuda(), block_table=bt.cuda(), causal=True,
+            return_softmax_lse=True, **kw)
+        torch.cuda.synchronize()
+    finally:
+        os.environ.pop("FA_B200_DECODE_PARTITION", None)
+    assert cuda.device_status() == 0
+    return out.cpu(), lse.cpu()
+
+
+def test_combine_matches_oracle_and_indexing_is_exact(fa):
+    _, cuda = fa
+    g = gen(0)
+    parts, b, h, d = 9, 3, 8, 128
+    o = torch.randn(parts, b * h, d, generator=g)
+    lse = torch.randn(parts, b * h, generator=g) * 4
+    lse[2] = float("-inf")            # an empty partition
+    lse[5, 3] = float("inf")          # the other empty marker
+    o[2] = float("nan")               # must never leak through a zero weight
+    ref_o, ref_l = O.merge_partials_ref(torch.nan_to_num(o), lse)
+    out, l = cuda.combine(o.cuda(), lse.cuda(), out_dtype=torch.float32, h=h)
+    assert max_err(out.cpu(), ref_o) < 2e-6 * max(1.0, ref_o.abs().max().item())
+    assert max_err(l.cpu(), ref_l) < 1e-5
+    # bit-exact slot addressing: with one live partition per row the output must be that partial, bit for bit
+    sel = torch.randint(0, parts, (b * h,), generator=g)
+    lse1 = torch.full((parts, b * h), float("-inf"))
+    lse1[sel, torch.arange(b * h)] = torch.randn(b * h, generator=g)
+    o1 = torch.randn(parts, b * h, d, generator=g)
+    out1, l1 = cuda.combine(o1.cuda(), lse1.cuda(), out_dtype=torch.float32, h=h)
+    assert torch.equal(out1.cpu(), o1[sel, torch.arange(b * h)])
+    assert torch.equal(l1.cpu(), lse1[sel, torch.arange(b * h)])
+    # per-sequence partition counts: partials past the count are ignored even if they look valid
+    ppr = torch.tensor([9, 4, 0], dtype=torch.int32)
+    out2, l2 = cuda.combine(o1.cuda(), torch.zeros(parts, b * h).cuda(), out_dtype=torch.bfloat16, h=h,
+                            parts_per_row=ppr.cuda())
+    ref2, refl2 = O.merge_partials_ref(o1[:4, h:2 * h], torch.zeros(4, h))
+    assert max_err(out2.cpu()[h:2 * h], ref2) < 1e-2
+    assert torch.all(out2.cpu()[2 * h:] == 0) and torch.all(torch.isinf(l2.cpu()[2 * h:]))
+
+
+def test_decode_golden_cases(fa, golden):
+    for c in [c for c in golden["cases"] if c["kind"] == "paged"]:
+        q, kc, vc, lens, bt = _mg.gen_inputs(c)
+        out, _ = _run_decode(fa, q, kc, vc, lens, bt)
+        ref32, _ = O.paged_decode_ref(q, kc, vc, lens, bt, out_dtype=torch.float32)
+        pt, _ = O.paged_decode_ref(q, kc, vc, lens, bt, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out, ref32, pt, mult=3.0, eps=1e-5 + 2 ** -8, what=c["name"])
+        # and against the reference-made golden output itself (same dtype, so one rounding apart at most)
+        assert max_err(out, c["out"]) <= 2e-2, c["name"]
+
+
+CASES = [
+    # (dtype, batch lens, h, h_k, page, partition override)
+    (torch.bfloat16, [1, 63, 64, 65, 300, 1000], 32, 8, 64, None),
+    (torch.bfloat16, [517, 2048, 1, 130], 32, 8, 256, 512),
+    (torch.float16, [777, 90, 4000], 8, 1, 128, 1024),       # group 8, MQA
+    (torch.bfloat16, [40, 0, 257, 5], 16, 1, 16, None),       # group 16, tiny pages, an empty sequence
+    (torch.float16, [100, 3000], 4, 4, 32, 512),              # group 1 (MHA)
+    (torch.bfloat16, [9000], 32, 8, 256, 512),                # one sequence, 18 partitions
+]
+
+
+@pytest.mark.parametrize("dtype,lens,h,h_k,page,partition", CASES)
+def test_decode_matches_oracle(fa, dtype, lens, h, h_k, page, partition):
+    g = gen(sum(lens) * 31 + h * 7 + page)
+    kc, vc, bt, sl = make_paged(g, lens, h_k, page, dtype)
+    q = randn(g, len(lens), 1, h, 128, dtype=dtype)
+    out, lse = _run_decode(fa, q, kc, vc, sl, bt, partition=partition)
+    kcc, vcc = clean_nan(kc), clean_nan(vc)
+    ref32, ref_lse = O.paged_decode_ref(q, kcc, vcc, sl, bt, out_dtype=torch.float32)
+    ref_pt, _ = O.paged_decode_ref(q, kcc, vcc, sl, bt, upcast=False, reorder_ops=True)
+    assert_close_to_oracle(out, ref32, ref_pt, mult=3.0, eps=1e-5 + 2 ** -8, what=f"decode {lens}")
+    assert torch.allclose(out.float(), ref32.float(), atol=1e-2, rtol=1e-2)        # tests/test_pa.py:108-117
+    fin = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse), fin)
+    assert max_err(lse[fin], ref_lse[fin]) < 1e-3
+    assert torch.all(lse[~fin] == float("inf"))
+    for i, L in enumerate(lens):
+        if L == 0:
+            assert torch.all(out[i] == 0)
+
+
+def test_decode_split_invariance_and_determinism(fa):
+    g = gen(77)
+    lens = [5000, 123, 2500]
+    kc, vc, bt, sl = make_paged(g, lens, 8, 64, torch.bfloat16)
+    q = randn(g, 3, 1, 32, 128)
+    a, la = _run_decode(fa, q, kc, vc, sl, bt, partition=512)
+    b, lb = _run_decode(fa, q, kc, vc, sl, bt, partition=4096)
+    c, lc = _run_decode(fa, q, kc, vc, sl, bt, partition=512)
+    assert torch.equal(a, c) and torch.equal(la, lc)          # bit-identical across runs
+    assert max_err(a, b) <= 2 ** -7 and max_err(la, lb) < 1e-4
+    # doubling V doubles the output exactly (power-of-two scaling commutes with every rounding step)
+    d2, _ = _run_decode(fa, q, kc, (vc.float() * 2).to(vc.dtype), sl, bt, partition=512)
+    assert torch.equal(d2.float(), a.float() * 2)
+
+
+def test_decode_noncontiguous_views_and_out_arg(fa):
+    flash_attn, cuda = fa
+    g = gen(5)
+    lens = [200, 70]
+    kc, vc, bt, sl = make_paged(g, lens, 2, 64, torch.float16, poison=False)
+    # cache stored as one (pool, page, 2*h_k, d) buffer with K and V interleaved on the head axis
+    kv = torch.stack([kc, vc], dim=3).reshape(kc.shape[0], 64, 4, 128).cuda()
+    kview, vview = kv[:, :, 0::2], kv[:, :, 1::2]
+    q = randn(g, 2, 1, 8, 128, dtype=torch.float16)
+    out_buf = torch.zeros(2, 1, 8, 128, dtype=torch.float16, device="cuda")
+    ret = flash_attn.flash_attn_with_kvcache(q.cuda(), kview, vview, cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                             out=out_buf)
+    assert ret.data_ptr() == out_buf.data_ptr()
+    ref32, _ = O.paged_decode_ref(q, kc, vc, sl, bt, out_dtype=torch.float32)
+    assert torch.allclose(out_buf.cpu().float(), ref32, atol=1e-2, rtol=1e-2)
+
+
+def test_decode_fp8_tolerance(fa):
+    flash_attn, cuda = fa
+    g = gen(31)
+    lens = [8192, 100, 1500, 129]
+    h, h_k, page = 32, 8, 256
+    kc16, vc16, bt, sl = make_paged(g, lens, h_k, page, torch.bfloat16, poison=False)
+    q16 = randn(g, len(lens), 1, h, 128)
+    q8, qd = O.quantize_e4m3_per_tensor(q16)
+    k8, kd = O.quantize_e4m3_per_tensor(kc16)
+    v8, vd = O.quantize_e4m3_per_tensor(vc16)
+    out, lse = _run_decode(fa, q8, k8, v8, sl, bt, q_descale=qd.cuda(), k_descale=kd.cuda(), v_descale=vd.cuda())
+    assert out.dtype == torch.bfloat16
+    b = len(lens)
+    ref32, ref_lse = O.paged_decode_ref(q8, k8, v8, sl, bt, q_descale=qd.expand(b, h_k), k_descale=kd.expand(b, h_k),
+                                        v_descale=vd.expand(b, h_k), out_dtype=torch.float32)
+    # stated FP8 tolerance: atol 7e-2 / rtol 1e-2 against the fp32 oracle on the same quantised inputs
+    # (tests/test_pa.py:108-117); the kernel keeps P in f16, so it is in practice far tighter
+    assert torch.allclose(out.float(), ref32.float(), atol=7e-2, rtol=1e-2)
+    assert max_err(out, ref32) < 2e-2
+    assert max_err(lse, ref_lse) < 1e-3
+    # per-(batch, kv head) descale tensors give the same result as the one-element form
+    out2, _ = _run_decode(fa, q8, k8, v8, sl, bt, q_descale=qd.expand(b, h_k).contiguous().cuda(),
+                          k_descale=kd.expand(b, h_k).contiguous().cuda(), v_descale=vd.expand(b, h_k).contiguous().cuda())
+    assert torch.equal(out, out2)
+
+
+def test_decode_rejects_what_the_path_does_not_do(fa):
+    flash_attn, cuda = fa
+    g = gen(1)
+    kc, vc, bt, sl = make_paged(g, [64], 1, 64, torch.bfloat16, poison=False)
+    q = randn(g, 1, 1, 4, 128).cuda()
+    with pytest.raises(ValueError):
+        flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(), block_table=bt.cuda(), softcap=1.0)
+    with pytest.raises(NotImplementedError):
+        flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), k=q, v=q, cache_seqlens=sl.cuda(), block_table=bt.cuda())
+    with pytest.raises(RuntimeError):
+        flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(), block_table=None)
+    with pytest.raises(RuntimeError):
+        flash_attn.flash_attn_with_kvcache(q[..., :64].contiguous(), kc.cuda()[..., :64].contiguous(),
+                                           vc.cuda()[..., :64].contiguous(), cache_seqlens=sl.cuda(), block_table=bt.cuda())

@@ -1,0 +1,244 @@
+"""GPU parity: dense fixed-length, packed varlen, FP8 and block-sparse prefill (fa_b200_fwd /
+fa_b200_fwd_sparse through the reference-shaped Python API) against the CPU oracle and the golden vectors."""
+import importlib.util
+import os
+
+import pytest
+import torch
+
+from oracle import attention_oracle as O
+from _util import assert_close_to_oracle, cos_diff, gen, max_err, randn
+
+pytestmark = pytest.mark.gpu
+
+_spec = importlib.util.spec_from_file_location(
+    "make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
+_mg = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(_mg)
+
+
+@pytest.fixture(scope="module")
+def fa():
+    import flash_attn
+    import flash_attn_2_cuda
+    assert torch.cuda.is_available()
+    return flash_attn, flash_attn_2_cuda
+
+
+def _check_lse(lse, ref_lse):
+    fin = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse), fin)
+    if fin.any():
+        assert max_err(lse[fin], ref_lse[fin]) < 1e-3
+    assert torch.all(lse[~fin] == float("inf"))
+
+
+def test_fixed_golden_cases(fa, golden):
+    flash_attn, cuda = fa
+    for c in [c for c in golden["cases"] if c["kind"] == "fixed"]:
+        q, k, v = _mg.gen_inputs(c)
+        out, lse, _ = flash_attn.flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=c["causal"], return_attn_probs=True)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        ref32, ref_lse = O.attention_ref(q, k, v, causal=c["causal"], out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(q, k, v, causal=c["causal"], upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=c["name"])
+        _check_lse(lse.cpu(), c["lse"])
+        # against the reference-made fixture itself: the two differ by output rounding only
+        assert max_err(out.cpu(), c["out"]) <= 2 * c["err_pt"] + 2 ** -8, c["name"]
+
+
+def test_varlen_golden_cases(fa, golden):
+    flash_attn, cuda = fa
+    for c in [c for c in golden["cases"] if c["kind"] == "varlen"]:
+        q, k, v, cq, ck = _mg.gen_inputs(c)
+        out, lse = flash_attn.flash_attn_varlen_func(
+            q.cuda(), k.cuda(), v.cuda(), cq.cuda(), ck.cuda(), max(c["lens_q"]), max(c["lens_k"]),
+            causal=c["causal"], return_softmax_lse=True)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        ref32, ref_lse = O.attention_varlen_ref(q, k, v, cq, ck, causal=c["causal"], out_dtype=torch.float32)
+        ref_pt, _ = O.attention_varlen_ref(q, k, v, cq, ck, causal=c["causal"], upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=c["name"])
+        assert lse.shape == (c["h"], sum(c["lens_q"]))
+        _check_lse(lse.cpu(), c["lse"])
+
+
+SHAPES = [
+    # dtype, b, sq, sk, h, h_k, causal
+    (torch.bfloat16, 2, 128, 128, 4, 1, True),
+    (torch.bfloat16, 1, 384, 384, 8, 2, True),
+    (torch.float16, 2, 200, 333, 4, 4, False),
+    (torch.bfloat16, 1, 1000, 1000, 4, 2, True),
+    (torch.float16, 1, 64, 513, 2, 1, True),      # sq < sk, causal bottom-right
+    (torch.bfloat16, 1, 300, 100, 2, 2, True),    # sq > sk: the first rows see nothing
+    (torch.bfloat16, 3, 1, 257, 8, 2, True),      # single query row: causal is dropped
+]
+
+
+@pytest.mark.parametrize("dtype,b,sq,sk,h,h_k,causal", SHAPES)
+def test_fixed_matches_oracle(fa, dtype, b, sq, sk, h, h_k, causal):
+    flash_attn, cuda = fa
+    g = gen(sq * 7 + sk * 3 + h)
+    q, k, v = randn(g, b, sq, h, 128, dtype=dtype), randn(g, b, sk, h_k, 128, dtype=dtype), randn(g, b, sk, h_k, 128, dtype=dtype)
+    out, lse, _ = flash_attn.flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=causal, return_attn_probs=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    eff_causal = causal and sq > 1
+    ref32, ref_lse = O.attention_ref(q, k, v, causal=eff_causal, out_dtype=torch.float32)
+    ref_pt, _ = O.attention_ref(q, k, v, causal=eff_causal, upcast=False, reorder_ops=True)
+    assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"fixed {sq}x{sk}")
+    _check_lse(lse.cpu(), ref_lse)
+
+
+def test_varlen_ragged_batch_and_noncontiguous_qkv(fa):
+    flash_attn, cuda = fa
+    g = gen(99)
+    lens = [1, 127, 128, 129, 700, 33, 512]
+    h, h_k = 8, 2
+    total = sum(lens)
+    # q, k, v as views of one packed (total, h + 2 h_k, d) buffer: row stride differs from h * d
+    qkv = randn(g, total, h + 2 * h_k, 128)
+    q, k, v = qkv[:, :h], qkv[:, h:h + h_k], qkv[:, h + h_k:]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    qkv_d = qkv.cuda()
+    out, lse = flash_attn.flash_attn_varlen_func(
+        qkv_d[:, :h], qkv_d[:, h:h + h_k], qkv_d[:, h + h_k:], cu.cuda(), cu.cuda(), max(lens), max(lens), causal=True,
+        return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    ref32, ref_lse = O.attention_varlen_ref(q, k, v, cu, cu, causal=True, out_dtype=torch.float32)
+    ref_pt, _ = O.attention_varlen_ref(q, k, v, cu, cu, causal=True, upcast=False, reorder_ops=True)
+    assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what="varlen ragged")
+    _check_lse(lse.cpu(), ref_lse)
+    # determinism: a second run is bit-identical (the reference's race-condition test)
+    out2, lse2 = flash_attn.flash_attn_varlen_func(
+        qkv_d[:, :h], qkv_d[:, h:h + h_k], qkv_d[:, h + h_k:], cu.cuda(), cu.cuda(), max(lens), max(lens), causal=True,
+        return_softmax_lse=True)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)
+
+
+def test_fp8_golden_and_varlen(fa, golden):
+    flash_attn, cuda = fa
+    for c in [c for c in golden["cases"] if c["kind"] == "fp8" and c["sq"] > 1]:
+        q8, k8, v8, qd, kd, vd = _mg.gen_inputs(c)
+        b, sq, sk = c["b"], c["sq"], c["sk"]
+        cq = torch.arange(0, (b + 1) * sq, sq, dtype=torch.int32)
+        ck = torch.arange(0, (b + 1) * sk, sk, dtype=torch.int32)
+        out = flash_attn.flash_attn_varlen_func(
+            q8.reshape(b * sq, c["h"], 128).cuda(), k8.reshape(b * sk, c["hk"], 128).cuda(),
+            v8.reshape(b * sk, c["hk"], 128).cuda(), cq.cuda(), ck.cuda(), sq, sk, causal=c["causal"],
+            q_descale=qd.cuda(), k_descale=kd.cuda(), v_descale=vd.cuda())
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        assert out.dtype == torch.bfloat16
+        out = out.cpu().reshape(b, sq, c["h"], 128)
+        # FP8 rule of the reference's tests: error <= 2x the error of the same math with P round-tripped
+        # through e4m3 (tests/test_flash_attn_varlen_fp8.py:521-694), plus cosine-diff < 1e-3 (:477-484)
+        e = max_err(out, c["out"])
+        e_p8 = max_err(c["out_p8"], c["out"])
+        assert e <= 2 * e_p8 + 2 ** -7, (e, e_p8)
+        assert cos_diff(out, c["out"]) < 1e-3
+
+
+def test_fp8_prefill_larger(fa):
+    flash_attn, cuda = fa
+    g = gen(4242)
+    lens = [500, 129, 1024]
+    h, h_k = 8, 2
+    total = sum(lens)
+    q16, k16, v16 = randn(g, total, h, 128), randn(g, total, h_k, 128), randn(g, total, h_k, 128)
+    q8, qd = O.quantize_e4m3_per_tensor(q16)
+    k8, kd = O.quantize_e4m3_per_tensor(k16)
+    v8, vd = O.quantize_e4m3_per_tensor(v16)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    out, lse = flash_attn.flash_attn_varlen_func(q8.cuda(), k8.cuda(), v8.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens),
+                                                 causal=True, q_descale=qd.cuda(), k_descale=kd.cuda(), v_descale=vd.cuda(),
+                                                 return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    nb = len(lens)
+    kw = dict(q_descale=qd.expand(nb, h_k), k_descale=kd.expand(nb, h_k), v_descale=vd.expand(nb, h_k))
+    ref32, ref_lse = O.attention_varlen_ref(q8, k8, v8, cu, cu, causal=True, out_dtype=torch.float32, **kw)
+    ref_p8, _ = O.attention_varlen_ref(q8, k8, v8, cu, cu, causal=True, out_dtype=torch.float32,
+                                       intermediate_dtype=torch.float8_e4m3fn, **kw)
+    e, e_p8 = max_err(out.cpu(), ref32), max_err(ref_p8, ref32)
+    assert e <= 2 * e_p8 + 2 ** -7, (e, e_p8)
+    assert cos_diff(out.cpu(), ref32) < 1e-3
+    _check_lse(lse.cpu(), ref_lse)
+
+
+def _sparse_inputs(g, b, s, h, h_k, density, causal):
+    block_m = O.sparse_block_m(s)
+    nq = (s + block_m - 1) // block_m
+    nk = (s + 127) // 128
+    tm = torch.rand(b, h, nq, nk, generator=g) < density
+    if causal:
+        qi = torch.arange(nq).view(-1, 1) * block_m
+        ki = torch.arange(nk).view(1, -1) * 128
+        tm &= (ki <= qi + block_m - 1)
+        tm |= (ki <= qi) & (qi < ki + 128)        # always keep the diagonal tile
+    cnt, offs = O.tile_mask_to_block_lists(tm, block_m=block_m, block_n=64, tile_n=128)
+    q, k, v = randn(g, b, s, h, 128), randn(g, b, s, h_k, 128), randn(g, b, s, h_k, 128)
+    return q, k, v, cnt, offs, block_m
+
+
+@pytest.mark.parametrize("s,causal", [(256, False), (640, True), (2304, True)])
+def test_sparse_matches_oracle(fa, s, causal):
+    flash_attn, cuda = fa
+    g = gen(s)
+    b, h, h_k = 1, 4, 2
+    q, k, v, cnt, offs, block_m = _sparse_inputs(g, b, s, h, h_k, 0.4, causal)
+    nq = cnt.shape[2]
+    cc = torch.zeros(b, h, nq, dtype=torch.int32)
+    ci = torch.zeros(b, h, nq, 1, dtype=torch.int32)
+    out, lse = flash_attn.sparse_attn_func(q.cuda(), k.cuda(), v.cuda(), cnt.cuda(), offs.cuda(), cc.cuda(), ci.cuda(),
+                                           causal=causal, return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    ref32, ref_lse = O.sparse_attention_ref(q, k, v, cnt, offs, causal, block_m)
+    ref32f, _ = O.attention_ref(q, k, v, causal=causal, out_dtype=torch.float32,
+                                extra_mask=O.block_lists_to_dense_mask(cnt, offs, s, s, block_m))
+    ref_pt, _ = O.attention_ref(q, k, v, causal=causal, upcast=False, reorder_ops=True,
+                                extra_mask=O.block_lists_to_dense_mask(cnt, offs, s, s, block_m))
+    assert_close_to_oracle(out.cpu(), ref32f, ref_pt, mult=2.0, eps=2 ** -8, what=f"sparse {s}")
+    _check_lse(lse.cpu(), ref_lse)
+    cs = torch.nn.functional.cosine_similarity(out.cpu().float().flatten(), ref32f.flatten(), dim=0).item()
+    assert cs > 0.999999                                   # tests/test_spas_fa2_attn.py:189-245
+
+
+def test_sparse_manual_two_block_selection(fa):
+    """The reference's own sparse test case (tests/test_spas_fa2_attn.py:64-110): every q block attends K rows
+    [0, 64) and [128, 192) only."""
+    flash_attn, cuda = fa
+    g = gen(42)
+    b, s, h = 2, 256, 2
+    q, k, v = randn(g, b, s, h, 128), randn(g, b, s, h, 128), randn(g, b, s, h, 128)
+    nq = s // 64
+    cnt = torch.full((b, h, nq), 2, dtype=torch.int32)
+    offs = torch.full((b, h, nq, nq), 10_000_000, dtype=torch.int32)
+    offs[..., 0] = 0
+    offs[..., 1] = 128
+    cc = torch.zeros(b, h, nq, dtype=torch.int32)
+    ci = torch.zeros(b, h, nq, 1, dtype=torch.int32)
+    out = flash_attn.sparse_attn_func(q.cuda(), k.cuda(), v.cuda(), cnt.cuda(), offs.cuda(), cc.cuda(), ci.cuda(), causal=False)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    ks = torch.cat([k[:, 0:64], k[:, 128:192]], dim=1)
+    vs = torch.cat([v[:, 0:64], v[:, 128:192]], dim=1)
+    ref32, _ = O.attention_ref(q, ks, vs, out_dtype=torch.float32)
+    ref_pt, _ = O.attention_ref(q, ks, vs, upcast=False, reorder_ops=True)
+    assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what="sparse manual")
+
+
+def test_prefill_rejects_what_the_path_does_not_do(fa):
+    flash_attn, cuda = fa
+    q = torch.zeros(1, 16, 2, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NotImplementedError):
+        flash_attn.flash_attn_func(q, q, q, dropout_p=0.1)
+    with pytest.raises(NotImplementedError):
+        flash_attn.flash_attn_func(q, q, q, window_size=(4, 0))
+    with pytest.raises(RuntimeError):
+        flash_attn.flash_attn_func(q[..., :64], q[..., :64], q[..., :64])
+    with pytest.raises(RuntimeError):
+        flash_attn.flash_attn_func(q, q[:, :, :1].expand(1, 16, 3, 128), q)
