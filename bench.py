@@ -1,0 +1,605 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic input.  The default workload is the
+paged-KV bf16 decode configuration (batch 64, context 1024..32768, page 256, 32/8 heads, d 128): the
+`value` is whole-job HBM GB/s of ALGORITHMIC bytes (KV bytes read once + q/out + block table) with the cache
+resident in HBM; `e2e` is the same metric through the public Python API with the step's inputs (q,
+cache_seqlens, block_table) coming from pinned host memory and the output read back to the host inside the
+timed region.  The varlen causal bf16 prefill configuration is timed in the same run and reported under
+`also` (TFLOP/s, reference FLOP convention 4*S^2*H*D/2 per sequence).
+
+Multi-GPU (torchrun, one rank per GPU): every rank runs the same per-GPU workload on its own seeded data with
+no data-path collective ("weak" scaling); the time is the max over ranks of the CUDA-event time between two
+barriers.  `--workload longseq` is the one case with an exchange step: a single 1,048,576-token sequence is
+split-KV across the ranks and the partial (O, LSE) are all-gathered with NCCL before the combine kernel.
+
+`--impl reference` times the CPU oracle (the reference's PyTorch attention restated in oracle/) on the host
+cores over a bounded sample of the same workload; under torchrun only rank 0 runs it.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "flash-attention-das_b200")
+for _p in (PKG, ROOT):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+H, HK, D = 32, 8, 128
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, as a multiple of the
+# algorithmic bytes, from the ncu captures summarised under profiles/ (None = not captured yet).
+TRAFFIC_RATIO = {"decode_bf16": None, "decode_fp8": None, "prefill_bf16": None, "prefill_fp8": None,
+                 "sparse_bf16": None, "longseq": None}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["source"] = "fallback"
+    return d
+
+
+# --------------------------------------------------------------------------------------------------
+# clocks sampler
+# --------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thr = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thr.join(timeout=10)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = sorted(int(float(s[0])) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(float(self.samples[0][1])), "reasons": reasons,
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# workloads (seeded synthetic data, shapes of the baseline configurations)
+# --------------------------------------------------------------------------------------------------
+def _cuda_gen(dev, seed):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    return g
+
+
+def _randn_into(t, g, chunk=1 << 26):
+    flat = t.view(-1)
+    for i in range(0, flat.numel(), chunk):
+        n = min(chunk, flat.numel() - i)
+        flat[i:i + n] = torch.randn(n, generator=g, device=t.device, dtype=torch.float32).to(t.dtype)
+
+
+class DecodeWorkload:
+    """Paged-KV decode: batch of single-token queries over a paged pool; block_table is a seeded random
+    permutation of the pool."""
+
+    def __init__(self, dev, seed, fp8=False, batch=None, lens=None, page=256):
+        import flash_attn
+        self.fa = flash_attn
+        self.fp8 = fp8
+        self.name = "decode_fp8" if fp8 else "decode_bf16"
+        cg = torch.Generator().manual_seed(seed)
+        if lens is None:
+            if fp8:
+                batch = batch or 128
+                lens = torch.full((batch,), 8192, dtype=torch.int64)
+            else:
+                batch = batch or 64
+                lens = torch.randint(1024, 32769, (batch,), generator=cg)
+        self.lens = lens
+        self.batch = len(lens)
+        self.page = page
+        nblk = (lens + page - 1) // page
+        pool = int(nblk.sum())
+        perm = torch.randperm(pool, generator=cg).to(torch.int32)
+        bt = torch.full((self.batch, int(nblk.max())), -1, dtype=torch.int32)
+        p = 0
+        for i, n in enumerate(nblk.tolist()):
+            bt[i, :n] = perm[p:p + n]
+            p += n
+        dg = _cuda_gen(dev, seed + 1)
+        dt = torch.bfloat16
+        self.kc = torch.empty(pool, page, HK, D, dtype=dt, device=dev)
+        self.vc = torch.empty(pool, page, HK, D, dtype=dt, device=dev)
+        _randn_into(self.kc, dg)
+        _randn_into(self.vc, dg)
+        self.q_host = torch.randn(self.batch, 1, H, D, generator=cg).to(dt).pin_memory()
+        self.kw = {}
+        if fp8:
+            amax_k, amax_v = self.kc.abs().max().float(), self.vc.abs().max().float()
+            kd, vd = (amax_k / 448.0).reshape(1), (amax_v / 448.0).reshape(1)
+            self.kc = (self.kc.float() / kd).to(torch.float8_e4m3fn)
+            self.vc = (self.vc.float() / vd).to(torch.float8_e4m3fn)
+            qd = (self.q_host.float().abs().max() / 448.0).reshape(1)
+            self.q_host = (self.q_host.float() / qd).to(torch.float8_e4m3fn).pin_memory()
+            self.kw = dict(q_descale=qd.to(dev), k_descale=kd, v_descale=vd)
+        self.bt_host = bt.pin_memory()
+        self.sl_host = lens.to(torch.int32).pin_memory()
+        self.q = self.q_host.to(dev)
+        self.bt = self.bt_host.to(dev)
+        self.sl = self.sl_host.to(dev)
+        self.out_host = torch.empty(self.batch, 1, H, D, dtype=torch.bfloat16).pin_memory()
+        es = 1 if fp8 else 2
+        # algorithmic bytes: every K and V byte once + q + out + the used block-table entries
+        self.units = float(int(lens.sum()) * HK * D * 2 * es + self.batch * H * D * (es + 2) + 4 * pool)
+        self.unit_name = "bytes"
+        self.h2d = self.q_host.numel() * es + self.bt_host.numel() * 4 + self.sl_host.numel() * 4
+        self.d2h = self.out_host.numel() * 2
+        self.desc = {"workload": ("paged-KV decode e4m3: batch %d x context 8192" % self.batch) if fp8 else
+                     "paged-KV decode bf16: batch %d, context uniform[1024,32768]" % self.batch,
+                     "page_block_size": page, "nheads": H, "nheads_kv": HK, "headdim": D,
+                     "tokens": int(lens.sum()), "l2": "inputs larger than L2 (KV pool %.2f GB)" % (self.units / 1e9)}
+
+    def step(self):
+        return self.fa.flash_attn_with_kvcache(self.q, self.kc, self.vc, cache_seqlens=self.sl, block_table=self.bt,
+                                               causal=True, **self.kw)
+
+    def step_e2e(self):
+        q = self.q_host.to(self.q.device, non_blocking=True)
+        bt = self.bt_host.to(self.q.device, non_blocking=True)
+        sl = self.sl_host.to(self.q.device, non_blocking=True)
+        out = self.fa.flash_attn_with_kvcache(q, self.kc, self.vc, cache_seqlens=sl, block_table=bt, causal=True, **self.kw)
+        self.out_host.copy_(out, non_blocking=True)
+        return out
+
+
+class PrefillWorkload:
+    """Packed varlen causal GQA prefill."""
+
+    def __init__(self, dev, seed, fp8=False):
+        import flash_attn
+        self.fa = flash_attn
+        self.fp8 = fp8
+        self.name = "prefill_fp8" if fp8 else "prefill_bf16"
+        cg = torch.Generator().manual_seed(seed)
+        lens = torch.full((8,), 4096, dtype=torch.int64) if fp8 else torch.randint(512, 4097, (16,), generator=cg)
+        self.lens = lens
+        total = int(lens.sum())
+        dg = _cuda_gen(dev, seed + 1)
+        mk = lambda h: torch.randn(total, h, D, generator=dg, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        q, k, v = mk(H), mk(HK), mk(HK)
+        self.kw = {}
+        if fp8:
+            qd, kd, vd = [(t.abs().max().float() / 448.0).reshape(1) for t in (q, k, v)]
+            q, k, v = [(t.float() / s).to(torch.float8_e4m3fn) for t, s in ((q, qd), (k, kd), (v, vd))]
+            self.kw = dict(q_descale=qd, k_descale=kd, v_descale=vd)
+        self.q, self.k, self.v = q, k, v
+        self.cu_host = torch.cat([torch.zeros(1, dtype=torch.int64), lens.cumsum(0)]).to(torch.int32).pin_memory()
+        self.cu = self.cu_host.to(dev)
+        self.maxlen = int(lens.max())
+        self.q_host, self.k_host, self.v_host = [t.cpu().pin_memory() for t in (q, k, v)]
+        self.out_host = torch.empty(total, H, D, dtype=torch.bfloat16).pin_memory()
+        # reference FLOP convention: 4 * S^2 * H * D / 2 per causal sequence (benchmarks/benchmark_attnmask.py:24-30)
+        self.units = float((4 * lens.double() ** 2 * H * D / 2).sum())
+        self.unit_name = "flops"
+        es = 1 if fp8 else 2
+        self.h2d = (q.numel() + k.numel() + v.numel()) * es + self.cu_host.numel() * 4
+        self.d2h = self.out_host.numel() * 2
+        self.desc = {"workload": ("varlen causal prefill e4m3: 8 x 4096" if fp8 else
+                                  "varlen causal GQA prefill bf16: 16 sequences, length uniform[512,4096]"),
+                     "nheads": H, "nheads_kv": HK, "headdim": D, "tokens": total,
+                     "l2": "inputs larger than L2 (q+k+v %.0f MB)" % ((q.numel() + 2 * k.numel()) * es / 1e6)}
+
+    def step(self):
+        return self.fa.flash_attn_varlen_func(self.q, self.k, self.v, self.cu, self.cu, self.maxlen, self.maxlen,
+                                              causal=True, **self.kw)
+
+    def step_e2e(self):
+        dev = self.q.device
+        q, k, v = [t.to(dev, non_blocking=True) for t in (self.q_host, self.k_host, self.v_host)]
+        cu = self.cu_host.to(dev, non_blocking=True)
+        out = self.fa.flash_attn_varlen_func(q, k, v, cu, cu, self.maxlen, self.maxlen, causal=True, **self.kw)
+        self.out_host.copy_(out, non_blocking=True)
+        return out
+
+
+def tile_mask_to_block_lists(tile_mask):
+    """(b, h, nq, nk) bool over 128x128 tiles -> block_count (b, h, nq) and block_offset (b, h, nq, NNZ_S) int32:
+    ascending K row offsets, two 64-row entries per kept tile, unused slots = a large sentinel (the metadata
+    format sparse_attn_func takes)."""
+    fine = tile_mask.repeat_interleave(2, dim=-1)
+    count = fine.sum(dim=-1).to(torch.int32)
+    nnz = max(int(count.max()), 1)
+    idx = torch.arange(fine.shape[-1], dtype=torch.int64).expand_as(fine).clone()
+    idx[~fine] = 10_000_000
+    srt = torch.sort(idx, dim=-1).values[..., :nnz]
+    offs = torch.where(srt >= 10_000_000, srt, srt * 64)
+    return count, offs.to(torch.int32).contiguous()
+
+
+class SparseWorkload:
+    """Block-sparse causal GQA prefill, one 32768-token sequence, 128x128 tile mask at 25 % density per head
+    (diagonal tiles always kept)."""
+
+    def __init__(self, dev, seed, seqlen=32768, density=0.25):
+        import flash_attn
+        self.fa = flash_attn
+        self.name = "sparse_bf16"
+        cg = torch.Generator().manual_seed(seed)
+        n = seqlen // 128
+        tm = torch.rand(1, H, n, n, generator=cg) < density
+        tril = torch.tril(torch.ones(n, n, dtype=torch.bool))
+        tm = (tm & tril) | torch.eye(n, dtype=torch.bool)
+        cnt, offs = tile_mask_to_block_lists(tm)
+        self.kept = int(tm.sum())
+        dg = _cuda_gen(dev, seed + 1)
+        mk = lambda h: torch.randn(1, seqlen, h, D, generator=dg, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        self.q, self.k, self.v = mk(H), mk(HK), mk(HK)
+        self.cnt, self.offs = cnt.to(dev), offs.to(dev)
+        self.cc = torch.zeros(1, H, n, dtype=torch.int32, device=dev)
+        self.ci = torch.zeros(1, H, n, 1, dtype=torch.int32, device=dev)
+        self.q_host, self.k_host, self.v_host = [t.cpu().pin_memory() for t in (self.q, self.k, self.v)]
+        self.cnt_host, self.offs_host = cnt.pin_memory(), offs.pin_memory()
+        self.out_host = torch.empty(1, seqlen, H, D, dtype=torch.bfloat16).pin_memory()
+        # kept tiles x 4*128*128*128 FLOPs, diagonal tiles counted as full tiles
+        self.units = float(self.kept) * 4 * 128 * 128 * 128
+        self.unit_name = "flops"
+        self.h2d = (self.q.numel() + 2 * self.k.numel()) * 2 + (cnt.numel() + offs.numel()) * 4
+        self.d2h = self.out_host.numel() * 2
+        self.desc = {"workload": "block-sparse causal GQA prefill bf16: 1 x %d, 128x128 tiles at %.0f%% density" %
+                     (seqlen, density * 100), "kept_tiles": self.kept, "nheads": H, "nheads_kv": HK, "headdim": D,
+                     "l2": "inputs larger than L2 is NOT true here (q+k+v %.0f MB): L2 flushed between steps" %
+                     ((self.q.numel() + 2 * self.k.numel()) * 2 / 1e6)}
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step(self):
+        self.flush.zero_()
+        return self.fa.sparse_attn_func(self.q, self.k, self.v, self.cnt, self.offs, self.cc, self.ci, causal=True)
+
+    def step_e2e(self):
+        dev = self.q.device
+        q, k, v = [t.to(dev, non_blocking=True) for t in (self.q_host, self.k_host, self.v_host)]
+        cnt, offs = self.cnt_host.to(dev, non_blocking=True), self.offs_host.to(dev, non_blocking=True)
+        out = self.fa.sparse_attn_func(q, k, v, cnt, offs, self.cc, self.ci, causal=True)
+        self.out_host.copy_(out, non_blocking=True)
+        return out
+
+
+class LongSeqWorkload:
+    """One sequence of 1,048,576 tokens, split-KV across the ranks by page range; each rank decodes its slice to
+    an fp32 partial (O, LSE); the partials are all-gathered (NCCL) and combined on every rank."""
+
+    def __init__(self, dev, seed, rank, world, total_tokens=1 << 20, page=256):
+        import flash_attn_2_cuda
+        self.cuda = flash_attn_2_cuda
+        self.name = "longseq"
+        self.world = world
+        local = total_tokens // world
+        pool = local // page
+        cg = torch.Generator().manual_seed(seed)  # same q on every rank
+        dg = _cuda_gen(dev, seed + 1 + rank)
+        self.kc = torch.empty(pool, page, HK, D, dtype=torch.bfloat16, device=dev)
+        self.vc = torch.empty(pool, page, HK, D, dtype=torch.bfloat16, device=dev)
+        _randn_into(self.kc, dg)
+        _randn_into(self.vc, dg)
+        self.q = torch.randn(1, 1, H, D, generator=cg).to(torch.bfloat16).to(dev)
+        self.bt = torch.randperm(pool, generator=torch.Generator().manual_seed(seed + 7 + rank)).to(torch.int32).view(1, pool).to(dev)
+        self.sl = torch.tensor([local], dtype=torch.int32, device=dev)
+        self.gather_o = torch.empty(world, H, D, dtype=torch.float32, device=dev)
+        self.gather_l = torch.empty(world, H, dtype=torch.float32, device=dev)
+        self.units = float(local * HK * D * 2 * 2 + H * D * 4 + 4 * pool)   # this rank's bytes
+        self.unit_name = "bytes"
+        self.h2d, self.d2h = self.q.numel() * 2, H * D * 2
+        self.q_host = self.q.cpu().pin_memory()
+        self.out_host = torch.empty(H, D, dtype=torch.bfloat16).pin_memory()
+        self.desc = {"workload": "single-sequence %d-token bf16 decode, split-KV across %d GPU(s), NCCL allgather of (O, LSE)" %
+                     (total_tokens, world), "page_block_size": page, "nheads": H, "nheads_kv": HK, "headdim": D,
+                     "l2": "inputs larger than L2 (%.2f GB per GPU)" % (self.units / 1e9)}
+
+    def _run(self, q):
+        o, l = self.cuda.decode_partial(q, self.kc, self.vc, self.sl, self.bt, D ** -0.5)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.gather_o.view(-1), o.view(-1))
+            dist.all_gather_into_tensor(self.gather_l.view(-1), l.view(-1))
+        else:
+            self.gather_o.copy_(o)
+            self.gather_l.copy_(l)
+        return self.cuda.combine(self.gather_o, self.gather_l, out_dtype=torch.bfloat16, h=H)[0]
+
+    def step(self):
+        return self._run(self.q)
+
+    def step_e2e(self):
+        out = self._run(self.q_host.to(self.q.device, non_blocking=True))
+        self.out_host.copy_(out, non_blocking=True)
+        return out
+
+
+def make_workload(name, dev, seed, rank, world):
+    if name == "decode_bf16":
+        return DecodeWorkload(dev, seed)
+    if name == "decode_fp8":
+        return DecodeWorkload(dev, seed, fp8=True)
+    if name == "prefill_bf16":
+        return PrefillWorkload(dev, seed)
+    if name == "prefill_fp8":
+        return PrefillWorkload(dev, seed, fp8=True)
+    if name == "sparse_bf16":
+        return SparseWorkload(dev, seed)
+    if name == "longseq":
+        return LongSeqWorkload(dev, seed, rank, world)
+    raise ValueError(name)
+
+
+METRIC = {"bytes": ("paged decode HBM GB/s", "GB/s", 1e9), "flops": ("varlen prefill TFLOPS", "TFLOP/s", 1e12)}
+
+
+# --------------------------------------------------------------------------------------------------
+# timing
+# --------------------------------------------------------------------------------------------------
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x, world, dev):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x, world, dev):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def time_steps(fn, steps, warmup, world, dev):
+    for _ in range(warmup):
+        fn()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world, dev) / steps
+
+
+def time_kernel_alone(wl, steps, warmup):
+    """Average duration of the dominant kernel alone: the library records a CUDA event right before and right
+    after it on the launching stream (profile_start_event / profile_stop_event of the C ABI)."""
+    import flash_attn_2_cuda
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in pairs:      # create the handles
+        a.record()
+        b.record()
+    for _ in range(warmup):
+        wl.step()
+    torch.cuda.synchronize()
+    for a, b in pairs:
+        flash_attn_2_cuda.set_profile_events(a, b)
+        wl.step()
+    flash_attn_2_cuda.set_profile_events(None, None)
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in pairs)
+    return sum(ts) / len(ts), ts[len(ts) // 2]
+
+
+def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
+    import flash_attn_2_cuda
+    wl = make_workload(name, dev, args.seed + 1000 * rank, rank, world)
+    metric, unit, div = METRIC[wl.unit_name]
+    with ClockSampler(dev.index) as cs:
+        l0 = flash_attn_2_cuda.launch_count()
+        ms = time_steps(wl.step, args.steps, args.warmup, world, dev)
+        launches = (flash_attn_2_cuda.launch_count() - l0) // (args.steps + args.warmup) * args.steps
+        ms_e2e = time_steps(wl.step_e2e, args.steps, args.warmup, world, dev)
+    clocks = cs.summary()
+    total_units = sum_over_ranks(wl.units, world, dev)
+    value = total_units / (ms * 1e-3) / div
+    e2e = total_units / (ms_e2e * 1e-3) / div
+    k_avg, k_med = time_kernel_alone(wl, max(args.steps, 5), 2)
+    achieved = wl.units / (k_avg * 1e-3) / div
+    if wl.unit_name == "bytes":
+        peak, bound, punit = peaks["hbm_gbs"], "hbm", "GB/s"
+    else:
+        # a kernel timed alone: burst figure; fp8 has no measured peak, 2x the bf16 figure is used and said so
+        peak = peaks["bf16_tflops"] * (2.0 if "fp8" in name else 1.0)
+        bound, punit = "tensor", "TFLOP/s"
+    ratio = TRAFFIC_RATIO.get(name)
+    res = {
+        "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "e4m3" if "fp8" in name else "bf16", "data": "synthetic (seeded)",
+        "config": wl.desc,
+        "e2e": {"value": round(e2e, 2), "unit": unit, "h2d_bytes_per_step": int(wl.h2d), "d2h_bytes_per_step": int(wl.d2h),
+                "ms_per_step": round(ms_e2e, 4)},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": bound, "achieved": round(achieved, 2), "peak": peak, "unit": punit,
+                     "frac": round(achieved / peak, 4), "peak_source": peaks["source"] + (" (2x bf16 for fp8)" if "fp8" in name and bound == "tensor" else ""),
+                     "traffic": None if ratio is None else ratio * wl.units,
+                     "kernel_ms_avg": round(k_avg, 4), "kernel_ms_median": round(k_med, 4),
+                     "algorithmic_per_launch": wl.units},
+        "clocks": clocks,
+    }
+    if with_cpu_baseline and rank == 0:
+        res["cpu_baseline"] = cpu_baseline(name, args.seed, budget_s=args.cpu_budget)
+    del wl
+    torch.cuda.empty_cache()
+    return res
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU baseline: the oracle (port of the reference's PyTorch attention) on the host cores
+# --------------------------------------------------------------------------------------------------
+def cpu_baseline(name, seed, budget_s=15.0):
+    from oracle import attention_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(seed)
+    metric, unit, div = METRIC["bytes" if ("decode" in name or name == "longseq") else "flops"]
+    done_units, t_used, n = 0.0, 0.0, 0
+    if "decode" in name or name == "longseq":
+        fp8 = "fp8" in name
+        # sample: sequences of the workload's length distribution, one at a time, until the budget is spent
+        while t_used < budget_s and n < 256:
+            L = 8192 if fp8 else int(torch.randint(1024, 32769, (1,), generator=g))
+            if name == "longseq":
+                L = 32768
+            page = 256
+            nb = (L + page - 1) // page
+            kc = torch.randn(nb, page, HK, D, generator=g).to(torch.bfloat16)
+            vc = torch.randn(nb, page, HK, D, generator=g).to(torch.bfloat16)
+            q = torch.randn(1, 1, H, D, generator=g).to(torch.bfloat16)
+            bt = torch.randperm(nb, generator=g).to(torch.int32).view(1, nb)
+            sl = torch.tensor([L], dtype=torch.int32)
+            t0 = time.perf_counter()
+            O.paged_decode_ref(q, kc, vc, sl, bt)
+            t_used += time.perf_counter() - t0
+            done_units += L * HK * D * 2 * (1 if fp8 else 2) + H * D * 4 + 4 * nb
+            n += 1
+        sample = "%d sequence(s) of the workload's length distribution, bf16 math in fp32 (fp8 inputs dequantised)" % n
+    else:
+        # sample: one causal sequence of 1024 tokens per call (cost grows with S^2; FLOP rate is what is compared)
+        S = 1024
+        while t_used < budget_s and n < 256:
+            q = torch.randn(S, H, D, generator=g).to(torch.bfloat16)
+            k = torch.randn(S, HK, D, generator=g).to(torch.bfloat16)
+            v = torch.randn(S, HK, D, generator=g).to(torch.bfloat16)
+            cu = torch.tensor([0, S], dtype=torch.int32)
+            t0 = time.perf_counter()
+            O.attention_varlen_ref(q, k, v, cu, cu, causal=True)
+            t_used += time.perf_counter() - t0
+            done_units += 4.0 * S * S * H * D / 2
+            n += 1
+        sample = "%d causal sequence(s) of 1024 tokens (dense masked evaluation), FLOP rate compared" % n
+    return {"value": round(done_units / max(t_used, 1e-9) / div, 4), "unit": unit, "cores": cores, "kind": "port",
+            "sample": sample, "seconds": round(t_used, 2)}
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the CPU restatement of the reference's PyTorch attention on the host cores."""
+    if rank != 0:
+        return
+    name = "decode_bf16" if args.workload in ("default", "all") else args.workload
+    metric, unit, _ = METRIC["bytes" if ("decode" in name or name == "longseq") else "flops"]
+    vals = []
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_baseline(name, args.seed, budget_s=2.0)
+    t0 = time.perf_counter()
+    for i in range(max(1, min(args.steps, 5))):
+        vals.append(cpu_baseline(name, args.seed + i, budget_s=args.cpu_budget / 2))
+    dt = time.perf_counter() - t0
+    v = sum(x["value"] for x in vals) / len(vals)
+    cb = dict(vals[-1])
+    cb["value"] = round(v, 4)
+    line = {"impl": "reference", "metric": metric, "value": round(v, 4), "unit": unit, "n_gpus": world,
+            "steps": len(vals), "warmup": 1, "ms_per_step": round(dt / len(vals) * 1e3, 2), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+            "config": {"workload": name + " (bounded CPU sample: " + cb["sample"] + ")"},
+            "cpu_baseline": cb,
+            "e2e": {"value": round(v, 4), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="default",
+                    choices=["default", "all", "decode_bf16", "prefill_bf16", "decode_fp8", "prefill_fp8", "sparse_bf16", "longseq"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    if args.workload == "default":
+        names = ["decode_bf16", "prefill_bf16"]
+    elif args.workload == "all":
+        names = ["decode_bf16", "prefill_bf16", "decode_fp8", "prefill_fp8", "sparse_bf16", "longseq"]
+    else:
+        names = [args.workload]
+    results = []
+    for i, n in enumerate(names):
+        results.append(run_workload(n, args, dev, rank, world, peaks,
+                                    with_cpu_baseline=(world == 1 and not args.no_cpu_baseline)))
+    if rank == 0:
+        line = results[0]
+        if len(results) > 1:
+            line["also"] = [{k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "config", "e2e",
+                                                 "gpu_launches", "roofline", "cpu_baseline") if k in r}
+                            for r in results[1:]]
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -291,8 +291,10 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
     k.o_partial = static_cast<float*>(p->workspace);
     k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * kHeadDim;
   }
+  if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
   cudaError_t e = launch_decode(p->dtype, tk, tv, k, stream);
   if (e != cudaSuccess) return cuda_fail("decode launch", e);
+  if (p->profile_stop_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_stop_event), stream);
   g_launches++;
   if (pl.split) {
     CombineKernelParams c{};
@@ -400,8 +402,10 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   } else {
     k.num_m_blocks = (p->seqlen_q + 127) / 128;
   }
+  if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
   cudaError_t e = launch_prefill(p->dtype, tq, tk, tv, k, stream);
   if (e != cudaSuccess) return cuda_fail("prefill launch", e);
+  if (p->profile_stop_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_stop_event), stream);
   g_launches++;
   return FA_B200_OK;
 }

@@ -52,6 +52,7 @@ class FwdParams(ctypes.Structure):
         ("v_descale_batch_stride", _c_i64), ("v_descale_head_stride", _c_i64),
         ("block_count", _c_vp), ("block_offset", _c_vp),
         ("num_q_blocks", _c_i32), ("nnz_s", _c_i32), ("block_m", _c_i32),
+        ("profile_start_event", _c_vp), ("profile_stop_event", _c_vp),
     ]
 
 
@@ -74,6 +75,7 @@ class DecodeParams(ctypes.Structure):
         ("partition_tokens", _c_i32), ("max_seqlen_k", _c_i32),
         ("workspace", _c_vp), ("workspace_bytes", ctypes.c_size_t),
         ("o_partial_out", _c_vp), ("lse_partial_out", _c_vp),
+        ("profile_start_event", _c_vp), ("profile_stop_event", _c_vp),
     ]
 
 
@@ -110,6 +112,22 @@ _lib.fa_b200_launch_count.restype = ctypes.c_uint64
 def lib():
     """The loaded ctypes handle (tests call the C ABI through it)."""
     return _lib
+
+
+_profile_events = None
+
+
+def set_profile_events(start: Optional["torch.cuda.Event"], stop: Optional["torch.cuda.Event"]):
+    """Benchmark hook: while set, every attention call records these two (already created) CUDA events
+    right before and right after its main kernel, so the dominant kernel can be timed alone."""
+    global _profile_events
+    _profile_events = None if start is None else (start, stop)
+
+
+def _apply_profile_events(p):
+    if _profile_events is not None:
+        p.profile_start_event = _profile_events[0].cuda_event
+        p.profile_stop_event = _profile_events[1].cuda_event
 
 
 def launch_count() -> int:
@@ -231,6 +249,7 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     p.softmax_scale = softmax_scale
     p.is_causal = 1 if causal else 0
     p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
+    _apply_profile_events(p)
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "fwd")
     rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
@@ -303,6 +322,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     _descale(p, "q_descale", q_descale_, b, h_k)
     _descale(p, "k_descale", k_descale_, b, h_k)
     _descale(p, "v_descale", v_descale_, b, h_k)
+    _apply_profile_events(p)
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "varlen_fwd")
     rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
@@ -356,6 +376,7 @@ def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out
     _descale(p, "v_descale", v_descale, b, h_k)
     p.partition_tokens = partition_tokens
     p.max_seqlen_k = max_seqlen_k
+    _apply_profile_events(p)
     return p
 
 
@@ -491,6 +512,7 @@ def fwd_sparse(q, k, v, block_count, block_offset, column_count, column_index, o
     p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
     p.block_count, p.block_offset = block_count.data_ptr(), block_offset.data_ptr()
     p.num_q_blocks, p.nnz_s, p.block_m = num_rows, block_offset.shape[3], block_m
+    _apply_profile_events(p)
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd_sparse(ctypes.byref(p), _stream(q)), "fwd_sparse")
     return [out, lse]

@@ -91,6 +91,10 @@ typedef struct fa_b200_fwd_params {
   const int32_t* block_count;
   const int32_t* block_offset;
   int32_t num_q_blocks, nnz_s, block_m;
+  /* Optional cudaEvent_t handles recorded on the stream right before and right after the attention
+   * kernel (timing of the dominant kernel alone); NULL = off. */
+  void* profile_start_event;
+  void* profile_stop_event;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch
@@ -144,6 +148,10 @@ typedef struct fa_b200_decode_params {
    * combine; out may then be NULL. */
   float* o_partial_out;
   float* lse_partial_out;
+  /* Optional cudaEvent_t handles recorded right before and right after the partition kernel (the
+   * combine kernel runs after the stop event); NULL = off. */
+  void* profile_start_event;
+  void* profile_stop_event;
 } fa_b200_decode_params;
 
 /* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)
