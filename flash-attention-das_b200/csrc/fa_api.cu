@@ -329,6 +329,49 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   return FA_B200_OK;
 }
 
+// ---- decode without caller-provided scratch ------------------------------------------------------
+// Split-KV partials for fa_b200_decode_paged_static.  One copy per device that loads the library.
+static __device__ __align__(256) unsigned char g_static_scratch[FA_B200_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use: the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static void* static_scratch_ptr(cudaError_t* err) {
+  static void* ptrs[64] = {};
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+  if (!ptrs[dev]) {
+    void* ptr = nullptr;
+    *err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (*err != cudaSuccess) return nullptr;
+    ptrs[dev] = ptr;
+  }
+  return ptrs[dev];
+}
+
+int fa_b200_decode_paged_static(const fa_b200_decode_params* p, void* stream) {
+  if (!p) return FA_B200_ERR_NULL;
+  DecodePlan pl = plan_decode(p);
+  if (pl.status != FA_B200_OK) return pl.status;
+  const size_t need = decode_ws_bytes(p, pl);
+  if (need > FA_B200_STATIC_SCRATCH_BYTES) {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "needs %zu bytes of scratch, the built-in array holds %u", need,
+             static_cast<unsigned>(FA_B200_STATIC_SCRATCH_BYTES));
+    set_error("fa_b200_decode_paged_static", buf);
+    return FA_B200_ERR_TOO_LARGE;
+  }
+  cudaError_t err = cudaSuccess;
+  void* scratch = static_scratch_ptr(&err);
+  if (!scratch) return cuda_fail("cudaGetSymbolAddress(static scratch)", err);
+  fa_b200_decode_params q = *p;
+  q.workspace = scratch;
+  q.workspace_bytes = FA_B200_STATIC_SCRATCH_BYTES;
+  return fa_b200_decode_paged(&q, stream);
+}
+
 static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!p) return FA_B200_ERR_NULL;

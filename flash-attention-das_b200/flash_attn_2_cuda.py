@@ -95,6 +95,8 @@ _lib.fa_b200_fwd_sparse.argtypes = [ctypes.POINTER(FwdParams), _c_vp]
 _lib.fa_b200_fwd_sparse.restype = ctypes.c_int
 _lib.fa_b200_decode_paged.argtypes = [ctypes.POINTER(DecodeParams), _c_vp]
 _lib.fa_b200_decode_paged.restype = ctypes.c_int
+_lib.fa_b200_decode_paged_static.argtypes = [ctypes.POINTER(DecodeParams), _c_vp]
+_lib.fa_b200_decode_paged_static.restype = ctypes.c_int
 _lib.fa_b200_decode_workspace_bytes.argtypes = [ctypes.POINTER(DecodeParams)]
 _lib.fa_b200_decode_workspace_bytes.restype = ctypes.c_size_t
 _lib.fa_b200_decode_partition_tokens.argtypes = [ctypes.POINTER(DecodeParams)]

@@ -159,6 +159,27 @@ typedef struct fa_b200_decode_params {
  *  src/paged_attention.h:356-445). */
 FA_B200_API int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream);
 
+/*
+ * fa_b200_decode_paged for callers that have no way to hand over scratch memory: a plugin that runs inside
+ * someone else's memory plan (an inference server that forbids allocation after start-up, a runtime whose
+ * allocator is not reachable from the extension, code running between the nodes of a captured graph) cannot
+ * call cudaMalloc and may not own a buffer to pass as `workspace`.  This variant takes the same parameters,
+ * ignores `workspace` / `workspace_bytes`, and keeps the split-KV partials in a fixed array that lives inside
+ * the library image: FA_B200_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the process
+ * exits.  It has no counterpart in the reference, whose decode always allocates or caches a workspace.
+ *
+ *  - Sizes whose partials need more than FA_B200_STATIC_SCRATCH_BYTES
+ *    (= fa_b200_decode_workspace_bytes(p)) are refused with FA_B200_ERR_TOO_LARGE; nothing is launched.
+ *  - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that
+ *    device current).  Make that first call outside any stream capture.
+ *  - It calls no allocating routine: no cudaMalloc / cudaFree, nothing from an allocating library.
+ *  - All calls on a device share the one array, and it keeps whatever the previous call left there (every
+ *    slot a call reads is written by that call first, so nothing needs clearing).  Two calls whose kernels can
+ *    overlap on the GPU (different streams, no ordering between them) race on it: serialise them.
+ */
+#define FA_B200_STATIC_SCRATCH_BYTES (32u << 20)
+FA_B200_API int fa_b200_decode_paged_static(const fa_b200_decode_params* p, void* stream);
+
 /* Bytes of scratch fa_b200_decode_paged needs for these sizes (0 when no split is used).
  * Replaces the per-(device, stream) workspace cache of src/paged_attention.cu:712-745. */
 FA_B200_API size_t fa_b200_decode_workspace_bytes(const fa_b200_decode_params* p);
