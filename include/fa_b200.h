@@ -162,7 +162,7 @@ FA_B200_API int fa_b200_decode_paged(const fa_b200_decode_params* p, void* strea
 /*
  * fa_b200_decode_paged for callers that have no way to hand over scratch memory: a plugin that runs inside
  * someone else's memory plan (an inference server that forbids allocation after start-up, a runtime whose
- * allocator is not reachable from the extension, code running between the nodes of a captured graph) cannot
+ * allocator is not reachable from the extension) cannot
  * call cudaMalloc and may not own a buffer to pass as `workspace`.  This variant takes the same parameters,
  * ignores `workspace` / `workspace_bytes`, and keeps the split-KV partials in a fixed array that lives inside
  * the library image: FA_B200_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the process
