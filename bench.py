@@ -193,13 +193,14 @@ class DecodeWorkload:
 class PrefillWorkload:
     """Packed varlen causal GQA prefill."""
 
-    def __init__(self, dev, seed, fp8=False):
+    def __init__(self, dev, seed, fp8=False, nseq=None):
         import flash_attn
         self.fa = flash_attn
         self.fp8 = fp8
         self.name = "prefill_fp8" if fp8 else "prefill_bf16"
         cg = torch.Generator().manual_seed(seed)
-        lens = torch.full((8,), 4096, dtype=torch.int64) if fp8 else torch.randint(512, 4097, (16,), generator=cg)
+        nseq = nseq or (8 if fp8 else 16)
+        lens = torch.full((nseq,), 4096, dtype=torch.int64) if fp8 else torch.randint(512, 4097, (nseq,), generator=cg)
         self.lens = lens
         total = int(lens.sum())
         dg = _cuda_gen(dev, seed + 1)
@@ -222,8 +223,8 @@ class PrefillWorkload:
         es = 1 if fp8 else 2
         self.h2d = (q.numel() + k.numel() + v.numel()) * es + self.cu_host.numel() * 4
         self.d2h = self.out_host.numel() * 2
-        self.desc = {"workload": ("varlen causal prefill e4m3: 8 x 4096" if fp8 else
-                                  "varlen causal GQA prefill bf16: 16 sequences, length uniform[512,4096]"),
+        self.desc = {"workload": ("varlen causal prefill e4m3: %d x 4096" % nseq if fp8 else
+                                  "varlen causal GQA prefill bf16: %d sequences, length uniform[512,4096]" % nseq),
                      "nheads": H, "nheads_kv": HK, "headdim": D, "tokens": total,
                      "l2": "inputs larger than L2 (q+k+v %.0f MB)" % ((q.numel() + 2 * k.numel()) * es / 1e6)}
 
@@ -353,15 +354,15 @@ class LongSeqWorkload:
         return out
 
 
-def make_workload(name, dev, seed, rank, world):
+def make_workload(name, dev, seed, rank, world, scale=1.0):
     if name == "decode_bf16":
-        return DecodeWorkload(dev, seed)
+        return DecodeWorkload(dev, seed, batch=max(1, int(64 * scale)))
     if name == "decode_fp8":
-        return DecodeWorkload(dev, seed, fp8=True)
+        return DecodeWorkload(dev, seed, fp8=True, batch=max(1, int(128 * scale)))
     if name == "prefill_bf16":
-        return PrefillWorkload(dev, seed)
+        return PrefillWorkload(dev, seed, nseq=max(1, int(16 * scale)))
     if name == "prefill_fp8":
-        return PrefillWorkload(dev, seed, fp8=True)
+        return PrefillWorkload(dev, seed, fp8=True, nseq=max(1, int(8 * scale)))
     if name == "sparse_bf16":
         return SparseWorkload(dev, seed)
     if name == "longseq":
@@ -435,7 +436,7 @@ def time_kernel_alone(wl, steps, warmup):
 
 def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
     import flash_attn_2_cuda
-    wl = make_workload(name, dev, args.seed + 1000 * rank, rank, world)
+    wl = make_workload(name, dev, args.seed + 1000 * rank, rank, world, args.scale)
     metric, unit, div = METRIC[wl.unit_name]
     with ClockSampler(dev.index) as cs:
         l0 = flash_attn_2_cuda.launch_count()
@@ -562,6 +563,8 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scale", type=float, default=1.0,
+                    help="shrink the batch / sequence count (profiler captures on a small case); 1.0 = the baseline configuration")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

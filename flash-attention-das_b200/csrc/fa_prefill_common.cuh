@@ -1,0 +1,190 @@
+// Pieces shared by the two tcgen05 prefill kernels (one-tile CTAs in fa_prefill.cu, persistent two-tile CTAs
+// in fa_prefill_pair.cu): tile traits, MMA issue sequences, the per-row softmax step and the epilogue.
+#pragma once
+
+#include "fa_common.cuh"
+#include "fa_kernels.h"
+
+namespace fa {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: O in TMEM is rescaled only when the max grew by more
+
+template <int DT>
+struct TileTraits {
+  static constexpr bool kFp8 = (DT == FA_B200_E4M3);
+  static constexpr int kElem = kFp8 ? 1 : 2;
+  static constexpr int kTileBytes = kBlockN * kHeadDim * kElem;   // one Q, K or V tile
+  static constexpr int kHalves = kFp8 ? 1 : 2;                    // 128-byte column groups per row
+  static constexpr int kHalfBytes = kTileBytes / kHalves;
+  static constexpr int kUmmaK = kFp8 ? 32 : 16;
+  static constexpr int kKSteps = kHeadDim / kUmmaK;               // k-steps of Q K^T
+  static constexpr int kPVSteps = kBlockN / kUmmaK;               // k-steps of P V
+  static constexpr uint32_t kFormat = kFp8 ? 0u : (DT == FA_B200_BF16 ? 1u : 0u);
+  static constexpr uint32_t kIdescQK = make_idesc(kFormat, false, kBlockM, kBlockN);
+  static constexpr uint32_t kIdescPV = make_idesc(kFormat, true, kBlockM, kHeadDim);
+};
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int dt) {
+  return dt == FA_B200_BF16 ? pack_bf16(lo, hi) : pack_f16(lo, hi);
+}
+// four floats -> four e4m3 bytes (byte i = value i)
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  uint32_t lo, hi;
+  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(lo) : "f"(a), "f"(b));
+  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(hi) : "f"(c), "f"(d));
+  return lo | (hi << 16);
+}
+
+// S[tmem] = Q[smem] K^T[smem]: both operands K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+template <int DT>
+__device__ __forceinline__ void issue_qk(uint32_t q_smem, uint32_t k_smem, uint32_t s_tmem) {
+  using T = TileTraits<DT>;
+#pragma unroll
+  for (int ks = 0; ks < T::kKSteps; ++ks) {
+    // bytes along the row: ks * 32; 16-bit types cross into the second 128-byte column group at ks = 4
+    const uint32_t off = T::kFp8 ? ks * 32u : ((ks >> 2) * T::kHalfBytes + (ks & 3) * 32u);
+    tc_mma_ss(s_tmem, make_smem_desc_sw128(q_smem + off, 16, 1024), make_smem_desc_sw128(k_smem + off, 16, 1024),
+              T::kIdescQK, ks > 0 ? 1u : 0u, T::kFp8);
+  }
+}
+// O[tmem] (+)= P[tmem] V[smem]: V is MN-major (d contiguous); a k-step spans kUmmaK key rows of 128 bytes; the
+// two 64-column groups of a 16-bit tile are kHalfBytes apart (leading-dimension offset).
+template <int DT>
+__device__ __forceinline__ void issue_pv(uint32_t p_tmem, uint32_t v_smem, uint32_t o_tmem, bool overwrite) {
+  using T = TileTraits<DT>;
+#pragma unroll
+  for (int ks = 0; ks < T::kPVSteps; ++ks) {
+    tc_mma_ts(o_tmem, p_tmem + ks * 8, make_smem_desc_sw128(v_smem + ks * (T::kUmmaK * 128), T::kHalfBytes, 1024),
+              T::kIdescPV, (overwrite && ks == 0) ? 0u : 1u, T::kFp8);
+  }
+}
+
+// Running softmax state of one query row (one thread).
+struct RowState {
+  float m_ref;   // reference max (scaled, log2 units) that the stored P and O are relative to
+  float l_sum;   // sum of P relative to m_ref
+};
+
+// One key tile for one row: S (TMEM, 128 fp32 columns at t_s) -> masked, scaled, exponentiated P written back
+// over the first columns of S in the input dtype; O (at t_o) rescaled when the row max grew past the threshold.
+//   lim        number of leading columns of this tile the row may see (<= 0: none; >= 128: all)
+//   need_mask  warp-uniform: some row of the warp has lim < 128
+//   first      first tile of this row's sweep (O holds nothing yet)
+template <int DT>
+__device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float scale_log2, int lim, bool need_mask,
+                                             bool first, RowState& st) {
+  using T = TileTraits<DT>;
+  uint32_t u[4][32];
+  tmem_ld_32x32(t_s + 0, u[0]);
+  tmem_ld_32x32(t_s + 32, u[1]);
+  tmem_ld_32x32(t_s + 64, u[2]);
+  tmem_ld_32x32(t_s + 96, u[3]);
+  tmem_wait_ld();
+#define FA_S_AT(idx) __uint_as_float(u[(idx) >> 5][(idx) & 31])
+  if (need_mask) {
+#pragma unroll
+    for (int c = 0; c < 128; ++c) u[c >> 5][c & 31] = (c < lim) ? u[c >> 5][c & 31] : 0xff800000u;
+  }
+  float mx0 = FA_S_AT(0), mx1 = FA_S_AT(1), mx2 = FA_S_AT(2), mx3 = FA_S_AT(3);
+#pragma unroll
+  for (int c = 4; c < 128; c += 4) {
+    mx0 = fmaxf(mx0, FA_S_AT(c));
+    mx1 = fmaxf(mx1, FA_S_AT(c + 1));
+    mx2 = fmaxf(mx2, FA_S_AT(c + 2));
+    mx3 = fmaxf(mx3, FA_S_AT(c + 3));
+  }
+  const float mx_scaled = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;   // scale > 0
+  if (first) {
+    st.m_ref = mx_scaled;
+  } else {
+    const bool grow = mx_scaled > st.m_ref + kRescaleThreshold;
+    if (__any_sync(0xffffffffu, grow)) {
+      const float m_new = grow ? mx_scaled : st.m_ref;
+      const float alpha = grow ? fast_exp2(st.m_ref - m_new) : 1.f;   // m_ref = -inf -> 0
+      st.l_sum *= alpha;
+      st.m_ref = m_new;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(t_o + c * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st_32x32(t_o + c * 32, o);
+      }
+    }
+  }
+  const float m_safe = (st.m_ref == -INFINITY) ? 0.f : st.m_ref;
+  float rs0 = 0.f, rs1 = 0.f;
+  if constexpr (!T::kFp8) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = fast_exp2(fmaf(FA_S_AT(c * 32 + 2 * i), scale_log2, -m_safe));
+        const float p1 = fast_exp2(fmaf(FA_S_AT(c * 32 + 2 * i + 1), scale_log2, -m_safe));
+        rs0 += p0;
+        rs1 += p1;
+        pk[i] = pack2(p0, p1, DT);
+      }
+      tmem_st_32x16(t_s + c * 16, pk);
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t pk[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p0 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i), scale_log2, -m_safe));
+        const float p1 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 1), scale_log2, -m_safe));
+        const float p2 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 2), scale_log2, -m_safe));
+        const float p3 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 3), scale_log2, -m_safe));
+        rs0 += p0 + p2;
+        rs1 += p1 + p3;
+        pk[i] = pack4_e4m3(p0, p1, p2, p3);
+      }
+      tmem_st_32x8(t_s + c * 8, pk);
+    }
+  }
+#undef FA_S_AT
+  st.l_sum += rs0 + rs1;
+  tmem_wait_st();
+}
+
+// Byte pointer of output row `grow`, head `head`.
+__device__ __forceinline__ uint8_t* out_row_ptr(const PrefillKernelParams& p, int coord_b, int64_t grow, int head) {
+  return reinterpret_cast<uint8_t*>(p.out) +
+         2 * (static_cast<int64_t>(coord_b) * p.o_batch_stride + grow * p.o_row_stride + static_cast<int64_t>(head) * p.o_head_stride);
+}
+__device__ __forceinline__ int64_t lse_index(const PrefillKernelParams& p, int bidb, int head, int64_t grow, int row_in_seq) {
+  return p.cu_seqlens_q ? (static_cast<int64_t>(head) * p.total_q + grow)
+                        : ((static_cast<int64_t>(bidb) * p.h + head) * p.seqlen_q + row_in_seq);
+}
+
+// 32 accumulator columns [c*32, c*32+32) of one row -> 64 bytes of 16-bit output.
+__device__ __forceinline__ void store_o_chunk(uint8_t* op, int c, const uint32_t (&o)[32], float inv, int out_dtype) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 v;
+    v.x = pack2(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv, out_dtype);
+    v.y = pack2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv, out_dtype);
+    v.z = pack2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv, out_dtype);
+    v.w = pack2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv, out_dtype);
+    reinterpret_cast<uint4*>(op)[c * 4 + i] = v;
+  }
+}
+
+// A row that sees no key at all: out = 0, lse = +inf.
+__device__ __forceinline__ void store_empty_row(const PrefillKernelParams& p, int coord_b, int bidb, int head, int64_t grow,
+                                                int row_in_seq) {
+  uint8_t* op = out_row_ptr(p, coord_b, grow, head);
+  const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) reinterpret_cast<uint4*>(op)[i] = z;
+  if (p.lse) p.lse[lse_index(p, bidb, head, grow, row_in_seq)] = INFINITY;
+}
+
+}  // namespace fa

@@ -1,0 +1,334 @@
+// Dense / varlen GQA attention forward for sm_100a on tcgen05 tensor cores — persistent CTAs, two query tiles each.
+//
+// One CTA per SM.  A work item is (sequence, 128-row query block, PAIR of query heads of one GQA group): the two
+// heads see the same keys under the same mask, so every K/V tile is loaded once and used by both
+// (half the L2->SM traffic of one-tile CTAs), and while one tile's softmax runs the tensor pipe works on the other:
+//   warps 0-3     softmax + epilogue of tile 0 (one thread per query row)
+//   warps 4-7     softmax + epilogue of tile 1
+//   warp 8        TMA producer: Q_0, Q_1 per item; K_j, V_j tiles into a four-slot ring, running ahead across items
+//   warp 9        MMA issuer, order per key tile j:  O_0 += P_0 V_j,  S_0 = Q_0 K_{j+1}^T,  O_1 += P_1 V_j,  S_1 = Q_1 K_{j+1}^T
+//   warps 10-11   idle (they complete the third warpgroup so that it can hand its registers to the softmax warps)
+// TMEM (all 512 columns): S_0, S_1, O_0, O_1 of 128 fp32 columns each; P overwrites the head of S.
+// CTAs stride over the virtual item list ordered by descending query block (for causal masks: heaviest first), so
+// prologue, Q loads and epilogue of one item overlap the main loop of its neighbours.  All mbarrier phases simply
+// keep counting across items.  Every wait is bounded; a CTA that gives up raises the device status word and leaves
+// through the common teardown (TMEM is always released).
+//
+// Same math as the reference's dense forward (csrc/flash_attn_cutlass/src/flash_fwd_kernel.h:2818-3328, FP8
+// 3330-3778; softmax.h:592-640,932-964); the heaviest-first order plays the role of the reference's reversed
+// m_block launch order (flash_fwd_kernel.h:8684).
+#include "fa_prefill_common.cuh"
+
+namespace fa {
+namespace {
+
+constexpr int kSlots = 4;
+constexpr int kThreads = 32 * 12;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kTmemCols = 512;
+
+struct PairSmem {
+  int q_off, ring_off, bar_off, misc_off, total;
+};
+template <int DT>
+__host__ __device__ constexpr PairSmem pair_smem() {
+  using T = TileTraits<DT>;
+  PairSmem s{};
+  s.q_off = 0;
+  s.ring_off = 2 * T::kTileBytes;
+  s.bar_off = s.ring_off + kSlots * T::kTileBytes;
+  s.misc_off = s.bar_off + 8 * (12 + 2 * kSlots);
+  s.total = s.misc_off + 32;
+  return s;
+}
+
+struct Item {
+  int bidb, head0, hk, m0, rows_valid, q_row0, k_row0, sk, coord_b, n_tiles, causal_shift;
+};
+
+// Virtual item L -> geometry.  false: the item does not exist (query block past the end of its sequence).
+__device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, Item& it) {
+  const int hp = p.h >> 1;
+  const int x = L % hp;
+  const int r = L / hp;
+  it.bidb = r % p.b;
+  const int mrev = r / p.b;
+  const int m_block = p.is_causal ? (p.num_m_blocks - 1 - mrev) : mrev;
+  it.head0 = 2 * x;
+  it.hk = it.head0 / (p.h / p.h_k);
+  int sq;
+  if (p.cu_seqlens_q) {
+    it.q_row0 = p.cu_seqlens_q[it.bidb];
+    sq = p.cu_seqlens_q[it.bidb + 1] - it.q_row0;
+    it.k_row0 = p.cu_seqlens_k[it.bidb];
+    it.sk = p.cu_seqlens_k[it.bidb + 1] - it.k_row0;
+    it.coord_b = 0;
+  } else {
+    it.q_row0 = 0; it.k_row0 = 0; sq = p.seqlen_q; it.sk = p.seqlen_k; it.coord_b = it.bidb;
+  }
+  it.m0 = m_block * kBlockM;
+  if (it.m0 >= sq) return false;
+  it.rows_valid = min(kBlockM, sq - it.m0);
+  it.causal_shift = it.sk - sq;
+  const int col_end = p.is_causal ? min(it.sk, it.m0 + it.rows_valid + it.causal_shift) : it.sk;
+  it.n_tiles = col_end > 0 ? (col_end + kBlockN - 1) / kBlockN : 0;
+  return true;
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const PrefillKernelParams p) {
+  using T = TileTraits<DT>;
+  constexpr PairSmem L = pair_smem<DT>();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bar_off);
+  uint64_t* q_full = bars;            // [2]
+  uint64_t* q_empty = q_full + 2;     // [2]
+  uint64_t* s_full = q_empty + 2;     // [2]
+  uint64_t* p_full = s_full + 2;      // [2]
+  uint64_t* o_full = p_full + 2;      // [2]
+  uint64_t* o_empty = o_full + 2;     // [2]
+  uint64_t* kv_full = o_empty + 2;    // [kSlots]
+  uint64_t* kv_empty = kv_full + kSlots;
+  uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc_off + 8);
+  const WaitCtx wctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_items = (p.h >> 1) * p.b * p.num_m_blocks;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&q_full[t]), 1);
+      mbar_init(smem_u32(&q_empty[t]), 1);
+      mbar_init(smem_u32(&s_full[t]), 1);
+      mbar_init(smem_u32(&p_full[t]), 128);
+      mbar_init(smem_u32(&o_full[t]), 1);
+      mbar_init(smem_u32(&o_empty[t]), 128);
+    }
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(smem_u32(&kv_full[s]), 1);
+      mbar_init(smem_u32(&kv_empty[s]), 1);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(sm_tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *sm_tmem_base;
+  // Register hand-over between warpgroups: the producer/MMA warpgroup keeps 72 registers per thread, each softmax
+  // warpgroup (128 score registers per row live at once) grows to 216.  128 * (216 + 216 + 72) <= 65536.
+  const uint32_t q_smem = smem_u32(smem + L.q_off);
+  const uint32_t ring_smem = smem_u32(smem + L.ring_off);
+
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (warp == kProducerWarp) {
+    // ================================================================== TMA producer
+    if (lane == 0) {
+      uint32_t kv_cnt = 0, item_cnt = 0;
+      bool ok = true;
+      for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
+        Item it;
+        if (!get_item(p, li, it) || it.n_tiles == 0) continue;
+        for (int t = 0; t < 2; ++t) {
+          if (!mbar_wait(smem_u32(&q_empty[t]), (item_cnt & 1u) ^ 1u, wctx)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&q_full[t]);
+          mbar_expect_tx(bar, T::kTileBytes);
+#pragma unroll
+          for (int hf = 0; hf < T::kHalves; ++hf)
+            tma_load_4d(q_smem + t * T::kTileBytes + hf * T::kHalfBytes, &tmap_q, bar, hf * 64, it.head0 + t,
+                        it.q_row0 + it.m0, it.coord_b);
+        }
+        for (int j = 0; ok && j < it.n_tiles; ++j) {
+#pragma unroll
+          for (int kv = 0; kv < 2; ++kv) {
+            const uint32_t slot = kv_cnt % kSlots, ph = (kv_cnt / kSlots) & 1u;
+            if (!mbar_wait(smem_u32(&kv_empty[slot]), ph ^ 1u, wctx)) { ok = false; break; }
+            const uint32_t bar = smem_u32(&kv_full[slot]);
+            mbar_expect_tx(bar, T::kTileBytes);
+            const CUtensorMap* tm = kv ? &tmap_v : &tmap_k;
+#pragma unroll
+            for (int hf = 0; hf < T::kHalves; ++hf)
+              tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, it.hk,
+                          it.k_row0 + j * kBlockN, it.coord_b);
+            ++kv_cnt;
+          }
+        }
+        ++item_cnt;
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ================================================================== MMA issuer
+    if (lane == 0) {
+      uint32_t kv_cnt = 0, item_cnt = 0, sp_cnt = 0;
+      bool ok = true;
+      for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
+        Item it;
+        if (!get_item(p, li, it) || it.n_tiles == 0) continue;
+        const int n = it.n_tiles;
+        {  // S_t(0) = Q_t K_0^T
+          const uint32_t slot = kv_cnt % kSlots;
+          if (!mbar_wait(smem_u32(&kv_full[slot]), (kv_cnt / kSlots) & 1u, wctx)) { ok = false; break; }
+          for (int t = 0; t < 2; ++t) {
+            if (!mbar_wait(smem_u32(&q_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
+            tc_fence_after();
+            issue_qk<DT>(q_smem + t * T::kTileBytes, ring_smem + slot * T::kTileBytes, tmem_base + t * 128);
+            tc_commit(smem_u32(&s_full[t]));
+            if (n == 1) tc_commit(smem_u32(&q_empty[t]));
+          }
+          if (!ok) break;
+          tc_commit(smem_u32(&kv_empty[slot]));
+          ++kv_cnt;
+        }
+        for (int j = 0; ok && j < n; ++j) {
+          const uint32_t vslot = kv_cnt % kSlots;
+          if (!mbar_wait(smem_u32(&kv_full[vslot]), (kv_cnt / kSlots) & 1u, wctx)) { ok = false; break; }
+          const bool more = (j + 1 < n);
+          const uint32_t kslot = (kv_cnt + 1) % kSlots, kph = ((kv_cnt + 1) / kSlots) & 1u;
+          for (int t = 0; t < 2; ++t) {
+            if (!mbar_wait(smem_u32(&p_full[t]), sp_cnt & 1u, wctx)) { ok = false; break; }
+            // O_t still holds the previous item's result until its epilogue has read it
+            if (j == 0 && !mbar_wait(smem_u32(&o_empty[t]), (item_cnt & 1u) ^ 1u, wctx)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv<DT>(tmem_base + t * 128, ring_smem + vslot * T::kTileBytes, tmem_base + 256 + t * 128, j == 0);
+            if (t == 1) tc_commit(smem_u32(&kv_empty[vslot]));
+            if (more) {
+              if (t == 0) {
+                if (!mbar_wait(smem_u32(&kv_full[kslot]), kph, wctx)) { ok = false; break; }
+                tc_fence_after();
+              }
+              // the tensor pipe executes in issue order: this overwrite of S_t/P_t follows the P_t V read above
+              issue_qk<DT>(q_smem + t * T::kTileBytes, ring_smem + kslot * T::kTileBytes, tmem_base + t * 128);
+              tc_commit(smem_u32(&s_full[t]));
+              if (j + 2 == n) tc_commit(smem_u32(&q_empty[t]));
+              if (t == 1) tc_commit(smem_u32(&kv_empty[kslot]));
+            } else {
+              tc_commit(smem_u32(&o_full[t]));
+            }
+          }
+          ++sp_cnt;
+          kv_cnt += more ? 2u : 1u;
+        }
+        ++item_cnt;
+      }
+    }
+    __syncwarp();
+  }
+  } else {
+    // ================================================================== softmax / correction / epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    const int t = warp >> 2;
+    const int lane_grp = warp & 3;
+    const int row = lane_grp * 32 + lane;
+    const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + t * 128;
+    const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + 256 + t * 128;
+    uint32_t sp_cnt = 0, item_cnt = 0;
+    bool ok = true;
+    for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
+      Item it;
+      if (!get_item(p, li, it)) continue;
+      const int head = it.head0 + t;
+      const int row_in_seq = it.m0 + row;
+      const int64_t grow = static_cast<int64_t>(it.q_row0) + row_in_seq;
+      if (it.n_tiles == 0) {
+        if (row < it.rows_valid) store_empty_row(p, it.coord_b, it.bidb, head, grow, row_in_seq);
+        continue;
+      }
+      const int row_limit = p.is_causal ? min(it.sk, row_in_seq + 1 + it.causal_shift) : it.sk;
+      const int warp_limit = p.is_causal ? min(it.sk, it.m0 + lane_grp * 32 + 1 + it.causal_shift) : it.sk;
+      float scale_log2 = p.scale_log2;
+      if (p.q_descale) scale_log2 *= p.q_descale[it.bidb * p.qds_b + it.hk * p.qds_h];
+      if (p.k_descale) scale_log2 *= p.k_descale[it.bidb * p.kds_b + it.hk * p.kds_h];
+      RowState st{-INFINITY, 0.f};
+      for (int j = 0; j < it.n_tiles; ++j) {
+        if (!mbar_wait(smem_u32(&s_full[t]), sp_cnt & 1u, wctx)) { ok = false; break; }
+        tc_fence_after();
+        const int start = j * kBlockN;
+        softmax_tile<DT>(t_s, t_o, scale_log2, row_limit - start, start + kBlockN > warp_limit, j == 0, st);
+        tc_fence_before();
+        mbar_arrive(smem_u32(&p_full[t]));
+        ++sp_cnt;
+      }
+      if (!ok) break;
+      if (!mbar_wait(smem_u32(&o_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t o[4][32];
+      tmem_ld_32x32(t_o + 0, o[0]);
+      tmem_ld_32x32(t_o + 32, o[1]);
+      tmem_ld_32x32(t_o + 64, o[2]);
+      tmem_ld_32x32(t_o + 96, o[3]);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&o_empty[t]));   // O_t may be overwritten by the next item from here on
+      ++item_cnt;
+      if (row < it.rows_valid) {
+        float vds = 1.f;
+        if (p.v_descale) vds = p.v_descale[it.bidb * p.vds_b + it.hk * p.vds_h];
+        const bool empty = !(st.l_sum > 0.f);
+        const float inv = empty ? 0.f : vds / st.l_sum;
+        uint8_t* op = out_row_ptr(p, it.coord_b, grow, head);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) store_o_chunk(op, c, o[c], inv, p.out_dtype);
+        if (p.lse)
+          p.lse[lse_index(p, it.bidb, head, grow, row_in_seq)] = empty ? INFINITY : (st.m_ref + log2f(st.l_sum)) * kLn2;
+      }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int DT>
+cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                          const PrefillKernelParams& p, cudaStream_t stream) {
+  auto kern = prefill_pair_kernel<DT>;
+  const size_t smem = 1024 + pair_smem<DT>().total;
+  static bool attr_done[64] = {};
+  static int num_sms[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    attr_done[dev] = true;
+  }
+  const long long total = static_cast<long long>(p.h / 2) * p.b * p.num_m_blocks;
+  if (total <= 0) return cudaSuccess;
+  const int grid = static_cast<int>(total < num_sms[dev] ? total : num_sms[dev]);
+  kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_prefill_pair(int dtype, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                                const PrefillKernelParams& p, cudaStream_t stream) {
+  switch (dtype) {
+    case FA_B200_F16: return launch_pair_t<FA_B200_F16>(tq, tk, tv, p, stream);
+    case FA_B200_BF16: return launch_pair_t<FA_B200_BF16>(tq, tk, tv, p, stream);
+    case FA_B200_E4M3: return launch_pair_t<FA_B200_E4M3>(tq, tk, tv, p, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fa
