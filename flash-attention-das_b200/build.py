@@ -7,7 +7,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libfa_b200.so")
-SOURCES = ["fa_api.cu", "fa_combine.cu", "fa_decode.cu", "fa_prefill.cu", "fa_prefill_pair.cu"]
+SOURCES = ["fa_api.cu", "fa_combine.cu", "fa_decode.cu", "fa_prefill.cu", "fa_prefill_pair.cu", "fa_prefill_dense.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
@@ -43,7 +43,7 @@ def build(force=False, verbose=False):
             sys.stderr.write(r.stderr)
         return obj
 
-    with ThreadPoolExecutor(max_workers=5) as ex:
+    with ThreadPoolExecutor(max_workers=6) as ex:
         objs = list(ex.map(compile_one, SOURCES))
     cmd = [NVCC, "-shared", "-o", OUT, *objs, "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)

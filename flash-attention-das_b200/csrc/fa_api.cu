@@ -446,14 +446,18 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     k.num_m_blocks = (p->seqlen_q + 127) / 128;
   }
   if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
-  // Two heads of one GQA group share every K/V tile in the persistent kernel; tile lists are per head, and an
-  // odd group has no pair, so those run one tile per CTA.  FA_B200_PREFILL_KERNEL=single|pair overrides (tests).
-  bool use_pair = !sparse && ((p->h / p->h_k) % 2 == 0);
+  // Dense / varlen prefill runs on the persistent kernel with double-buffered scores; tile lists (per head) run
+  // one tile per CTA.  FA_B200_PREFILL_KERNEL=single|pair|dense overrides the choice (tests, comparisons); "pair"
+  // needs an even GQA group.
+  int which = sparse ? 0 : 2;
   if (const char* ov = getenv("FA_B200_PREFILL_KERNEL")) {
-    if (!strcmp(ov, "single")) use_pair = false;
+    if (!strcmp(ov, "single")) which = 0;
+    else if (!strcmp(ov, "pair") && !sparse && (p->h / p->h_k) % 2 == 0) which = 1;
+    else if (!strcmp(ov, "dense") && !sparse) which = 2;
   }
-  cudaError_t e = use_pair ? launch_prefill_pair(p->dtype, tq, tk, tv, k, stream)
-                           : launch_prefill_single(p->dtype, tq, tk, tv, k, stream);
+  cudaError_t e = which == 2   ? launch_prefill_dense(p->dtype, tq, tk, tv, k, stream)
+                  : which == 1 ? launch_prefill_pair(p->dtype, tq, tk, tv, k, stream)
+                               : launch_prefill_single(p->dtype, tq, tk, tv, k, stream);
   if (e != cudaSuccess) return cuda_fail("prefill launch", e);
   if (p->profile_stop_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_stop_event), stream);
   g_launches++;

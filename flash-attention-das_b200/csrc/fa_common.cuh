@@ -16,17 +16,11 @@ constexpr int kHeadDim = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
-// A wait on an mbarrier gives up after this many nanoseconds (global timer).
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+// A wait on an mbarrier gives up after this many SM clock cycles (about two seconds).
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -64,20 +58,24 @@ struct WaitCtx {
   int* status;               // global memory, one per device
 };
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
+  // The common case costs one try_wait; the clock and the abort flag are looked at only every 256 failed polls
+  // (a clock read on the fast path would add its latency to every hand-off of the pipeline).
   uint32_t it = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++it & 63u) == 0u) {
+  long long t0 = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 255u) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
         *ctx.abort_flag = 1;
         atomicOr(ctx.status, FA_B200_ERR_DEVICE_TIMEOUT);
         return false;
       }
     }
   }
+  return true;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -209,6 +207,11 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
+}
+// Copy 128 rows x 32 bytes from shared memory (matrix descriptor, same format as an MMA operand) into 8 TMEM
+// columns of all 128 lanes.  Executes in issue order with the issuing thread's tcgen05.mma instructions.
+__device__ __forceinline__ void tc_cp_128x256b(uint32_t taddr, uint64_t s_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(taddr), "l"(s_desc) : "memory");
 }
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (warp%4)*32 + t.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {

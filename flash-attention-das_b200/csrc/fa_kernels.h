@@ -80,6 +80,9 @@ struct PrefillKernelParams {
 // One 128-row query tile per CTA, two CTAs per SM: block-sparse lists and odd GQA groups.
 cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
                                   const CUtensorMap& tmap_v, const PrefillKernelParams& p, cudaStream_t stream);
+// Persistent CTAs, one query tile per work item, double-buffered scores: dense / varlen prefill (default).
+cudaError_t launch_prefill_dense(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
+                                 const CUtensorMap& tmap_v, const PrefillKernelParams& p, cudaStream_t stream);
 // Persistent CTAs, two query heads of one GQA group per work item: dense / varlen prefill with an even group.
 cudaError_t launch_prefill_pair(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
                                 const CUtensorMap& tmap_v, const PrefillKernelParams& p, cudaStream_t stream);

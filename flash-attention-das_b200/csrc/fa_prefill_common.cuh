@@ -7,6 +7,22 @@
 
 namespace fa {
 
+// Optional phase trace (compile with -DFA_B200_PHASE_TRACE): CTA 0 records clock64 stamps of its softmax warps'
+// and MMA thread's hand-offs into a device array read back by fa_b200_debug_trace().  Off in normal builds.
+#ifdef FA_B200_PHASE_TRACE
+static __device__ long long g_trace[3][2048];   // one copy per translation unit
+#define FA_TRACE(role, idx, tag)                                                  \
+  do {                                                                            \
+    if (blockIdx.x == 0 && (idx) < 1023) {                                        \
+      g_trace[role][2 * (idx)] = (tag);                                           \
+      g_trace[role][2 * (idx) + 1] = clock64();                                   \
+      ++(idx);                                                                    \
+    }                                                                             \
+  } while (0)
+#else
+#define FA_TRACE(role, idx, tag) do { } while (0)
+#endif
+
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: O in TMEM is rescaled only when the max grew by more
@@ -37,27 +53,117 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
   return lo | (hi << 16);
 }
 
-// S[tmem] = Q[smem] K^T[smem]: both operands K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+// ---- MMA issue sequences ---------------------------------------------------------------------------------------
+// One thread feeds the tensor pipe, and a 128x128x16 product takes only 64 cycles, so the issue path has to be a
+// handful of instructions per MMA: each sequence below is ONE asm block that derives the k-step descriptors with a
+// single 64-bit add (the start-address field is the low 14 bits, in 16-byte units; strides and swizzle mode stay
+// in the high word) and issues the 8 (16-bit) or 4 (e4m3) MMAs back to back.
+//   K-major operand (Q, K): k-step ks starts 32 bytes further along the row (+2 units); a 16-bit tile continues
+//     in the second 128-byte column group after 4 steps (+kHalfBytes).
+//   MN-major operand (V):   k-step ks starts kUmmaK key rows = kUmmaK * 128 bytes further.
+//   TMEM operand (Q, P):    k-step ks starts 8 columns further.
+
+// S[tmem] = Q[smem] K^T[smem]
 template <int DT>
 __device__ __forceinline__ void issue_qk(uint32_t q_smem, uint32_t k_smem, uint32_t s_tmem) {
   using T = TileTraits<DT>;
-#pragma unroll
-  for (int ks = 0; ks < T::kKSteps; ++ks) {
-    // bytes along the row: ks * 32; 16-bit types cross into the second 128-byte column group at ks = 4
-    const uint32_t off = T::kFp8 ? ks * 32u : ((ks >> 2) * T::kHalfBytes + (ks & 3) * 32u);
-    tc_mma_ss(s_tmem, make_smem_desc_sw128(q_smem + off, 16, 1024), make_smem_desc_sw128(k_smem + off, 16, 1024),
-              T::kIdescQK, ks > 0 ? 1u : 0u, T::kFp8);
+  const uint64_t a0 = make_smem_desc_sw128(q_smem, 16, 1024), b0 = make_smem_desc_sw128(k_smem, 16, 1024);
+  if constexpr (T::kFp8) {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, pf;\n\t"
+        "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, pt;\n\t}"
+        ::"r"(s_tmem), "l"(a0), "l"(b0), "r"(T::kIdescQK) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+        "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 1024;\n\tadd.s64 b, %2, 1024;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 1026;\n\tadd.s64 b, %2, 1026;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 1028;\n\tadd.s64 b, %2, 1028;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.s64 a, %1, 1030;\n\tadd.s64 b, %2, 1030;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t}"
+        ::"r"(s_tmem), "l"(a0), "l"(b0), "r"(T::kIdescQK) : "memory");
   }
 }
-// O[tmem] (+)= P[tmem] V[smem]: V is MN-major (d contiguous); a k-step spans kUmmaK key rows of 128 bytes; the
-// two 64-column groups of a 16-bit tile are kHalfBytes apart (leading-dimension offset).
+static_assert((TileTraits<FA_B200_BF16>::kHalfBytes >> 4) == 1024, "k-step offsets below assume 16 KB column groups");
+
+// Q tile (shared memory, K-major, 128-byte swizzle) -> TMEM as the A operand of Q K^T: one 128x256b copy per
+// k-step (32 bytes of every row), landing in 8 consecutive columns.
+template <int DT>
+__device__ __forceinline__ void issue_q_to_tmem(uint32_t q_smem, uint32_t q_tmem) {
+  using T = TileTraits<DT>;
+  const uint64_t d0 = make_smem_desc_sw128(q_smem, 16, 1024);
+#pragma unroll
+  for (int ks = 0; ks < T::kKSteps; ++ks) {
+    const uint32_t off16 = T::kFp8 ? ks * 2u : ((ks >> 2) * (T::kHalfBytes >> 4) + (ks & 3) * 2u);
+    tc_cp_128x256b(q_tmem + ks * 8, d0 + off16);
+  }
+}
+// S[tmem] = Q[tmem] K^T[smem]: only K is read from shared memory.
+template <int DT>
+__device__ __forceinline__ void issue_qk_ts(uint32_t q_tmem, uint32_t k_smem, uint32_t s_tmem) {
+  using T = TileTraits<DT>;
+  const uint64_t b0 = make_smem_desc_sw128(k_smem, 16, 1024);
+  if constexpr (T::kFp8) {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, pf;\n\t"
+        "add.u32 a, %1, 8;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 16;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 24;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a], b, %3, pt;\n\t}"
+        ::"r"(s_tmem), "r"(q_tmem), "l"(b0), "r"(T::kIdescQK) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pf;\n\t"
+        "add.u32 a, %1, 8;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 16;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 24;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 32;\n\tadd.s64 b, %2, 1024;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 40;\n\tadd.s64 b, %2, 1026;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 48;\n\tadd.s64 b, %2, 1028;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 56;\n\tadd.s64 b, %2, 1030;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t}"
+        ::"r"(s_tmem), "r"(q_tmem), "l"(b0), "r"(T::kIdescQK) : "memory");
+  }
+}
+// O[tmem] (+)= P[tmem] V[smem]: V is MN-major (d contiguous); the two 64-column groups of a 16-bit tile are
+// kHalfBytes apart (leading-dimension offset).  `overwrite`: the first k-step replaces O instead of accumulating.
 template <int DT>
 __device__ __forceinline__ void issue_pv(uint32_t p_tmem, uint32_t v_smem, uint32_t o_tmem, bool overwrite) {
   using T = TileTraits<DT>;
-#pragma unroll
-  for (int ks = 0; ks < T::kPVSteps; ++ks) {
-    tc_mma_ts(o_tmem, p_tmem + ks * 8, make_smem_desc_sw128(v_smem + ks * (T::kUmmaK * 128), T::kHalfBytes, 1024),
-              T::kIdescPV, (overwrite && ks == 0) ? 0u : 1u, T::kFp8);
+  const uint64_t b0 = make_smem_desc_sw128(v_smem, T::kHalfBytes, 1024);
+  const uint32_t acc0 = overwrite ? 0u : 1u;
+  if constexpr (T::kFp8) {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "setp.ne.b32 pf, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, pf;\n\t"
+        "add.u32 a, %1, 8;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 16;\n\tadd.s64 b, %2, 512;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 24;\n\tadd.s64 b, %2, 768;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a], b, %3, pt;\n\t}"
+        ::"r"(o_tmem), "r"(p_tmem), "l"(b0), "r"(T::kIdescPV), "r"(acc0) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "setp.ne.b32 pf, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pf;\n\t"
+        "add.u32 a, %1, 8;\n\tadd.s64 b, %2, 128;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 16;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 24;\n\tadd.s64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 32;\n\tadd.s64 b, %2, 512;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 40;\n\tadd.s64 b, %2, 640;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 48;\n\tadd.s64 b, %2, 768;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 56;\n\tadd.s64 b, %2, 896;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t}"
+        ::"r"(o_tmem), "r"(p_tmem), "l"(b0), "r"(T::kIdescPV), "r"(acc0) : "memory");
   }
 }
 

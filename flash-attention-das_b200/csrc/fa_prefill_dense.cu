@@ -1,0 +1,483 @@
+// Dense / varlen attention forward for sm_100a on tcgen05 tensor cores — persistent CTAs, score tile double-buffered.
+//
+// One CTA per SM walks work items (sequence, head, 128-row query block), heaviest query blocks first.  The score
+// accumulator S is double-buffered in TMEM, so S(c+1) = Q K_{c+1}^T is issued BEFORE the softmax of tile c has
+// finished: the tensor pipe computes the next scores (and the previous P V) while the softmax warps work, and the
+// softmax warps find their next tile ready when they finish the current one.  Work crosses item boundaries the same
+// way (the next item's Q is prefetched into a second Q buffer, its first S is issued before the current item's last
+// P V).
+//   warps 0-3   softmax, key columns  0..63  of every tile (thread = query row)
+//   warps 4-7   softmax, key columns 64..127 of every tile; the two threads of a row exchange their partial max
+//               through shared memory (one named barrier per tile) and keep partial row sums
+//   warp 8      TMA producer: one ring of 6 tiles carries Q, K_0, V_0, K_1, V_1, ... of item after item
+//               (128B swizzle, no multicast)
+//   warp 9      MMA issuer (one thread): per item: Q tile shared memory -> TMEM (tcgen05.cp); per tile c:
+//               S[(c+1)&1] = Q K_{c+1}^T ;  O += P_c V_c.  Both products take their A operand (Q, P_c) from TMEM, so
+//               the tensor pipe reads only K and V from shared memory: shared-memory bandwidth, not math, is what
+//               bounds a 128x128 tcgen05 tile whose two operands both come from shared memory.
+//   warps 10-11 idle
+// TMEM: S0 [0,128), S1 [128,256), O [256,384), Q of even items [384,448), Q of odd items [448,512).
+// P (input dtype) overwrites the head of its S buffer.
+// O in TMEM is rescaled only when a row max grew by more than 2^8 (and only after the previous P V has completed).
+// Every mbarrier wait is bounded; a CTA that gives up raises the device status word and leaves through the common
+// teardown (TMEM is always released).
+//
+// Same math as the reference's dense forward (csrc/flash_attn_cutlass/src/flash_fwd_kernel.h:2818-3328, FP8
+// 3330-3778; softmax.h:592-640,932-964); the heaviest-first order plays the role of the reference's reversed
+// m_block launch order (flash_fwd_kernel.h:8684).
+#include "fa_prefill_common.cuh"
+
+namespace fa {
+namespace {
+
+constexpr int kSlots = 6;         // ring of 32 KB (16 KB e4m3) tiles: Q, K_0, V_0, K_1, V_1, ... of item after item
+constexpr int kThreads = 32 * 12;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0, kColO = 256, kColQ = 384;
+
+struct DenseSmem {
+  int ring_off, bar_off, xch_off, misc_off, total;
+};
+template <int DT>
+__host__ __device__ constexpr DenseSmem dense_smem() {
+  using T = TileTraits<DT>;
+  DenseSmem s{};
+  s.ring_off = 0;
+  s.bar_off = s.ring_off + kSlots * T::kTileBytes;
+  // s_full[2] p_full[2] o_full o_empty ring_full[kSlots] ring_empty[kSlots]
+  s.xch_off = s.bar_off + 8 * (6 + 2 * kSlots);
+  s.misc_off = s.xch_off + 4 * 2 * 2 * 128;
+  s.total = s.misc_off + 32;
+  return s;
+}
+
+// Position in the tile ring: slot and the parity of that slot's current use.
+struct RingPos {
+  uint32_t slot, phase;
+  __device__ __forceinline__ void advance(uint32_t n) {   // n <= kSlots
+    slot += n;
+    if (slot >= kSlots) { slot -= kSlots; phase ^= 1u; }
+  }
+};
+
+struct Item {
+  int bidb, head, hk, m0, rows_valid, q_row0, k_row0, sk, coord_b, n_tiles, causal_shift;
+};
+
+// Virtual item L -> geometry.  false: the item does not exist (query block past the end of its sequence).
+__device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, Item& it) {
+  it.head = L % p.h;
+  const int r = L / p.h;
+  it.bidb = r % p.b;
+  const int mrev = r / p.b;
+  const int m_block = p.is_causal ? (p.num_m_blocks - 1 - mrev) : mrev;
+  it.hk = it.head / (p.h / p.h_k);
+  int sq;
+  if (p.cu_seqlens_q) {
+    it.q_row0 = p.cu_seqlens_q[it.bidb];
+    sq = p.cu_seqlens_q[it.bidb + 1] - it.q_row0;
+    it.k_row0 = p.cu_seqlens_k[it.bidb];
+    it.sk = p.cu_seqlens_k[it.bidb + 1] - it.k_row0;
+    it.coord_b = 0;
+  } else {
+    it.q_row0 = 0; it.k_row0 = 0; sq = p.seqlen_q; it.sk = p.seqlen_k; it.coord_b = it.bidb;
+  }
+  it.m0 = m_block * kBlockM;
+  if (it.m0 >= sq) return false;
+  it.rows_valid = min(kBlockM, sq - it.m0);
+  it.causal_shift = it.sk - sq;
+  const int col_end = p.is_causal ? min(it.sk, it.m0 + it.rows_valid + it.causal_shift) : it.sk;
+  it.n_tiles = col_end > 0 ? (col_end + kBlockN - 1) / kBlockN : 0;
+  return true;
+}
+
+// Next item of this CTA at or after virtual index li that has key tiles (the ones that use the pipeline).
+__device__ __forceinline__ bool next_work_item(const PrefillKernelParams& p, int& li, int total, Item& it) {
+  for (; li < total; li += gridDim.x) {
+    if (get_item(p, li, it) && it.n_tiles > 0) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void softmax_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const PrefillKernelParams p) {
+  using T = TileTraits<DT>;
+  constexpr DenseSmem L = dense_smem<DT>();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bar_off);
+  uint64_t* s_full = bars;              // [2]  S buffer holds fresh scores          (tcgen05.commit)
+  uint64_t* p_full = s_full + 2;        // [2]  P written, O rescaled if needed       (8 softmax warps)
+  uint64_t* o_full = p_full + 2;        //      last P V of the item complete         (tcgen05.commit)
+  uint64_t* o_empty = o_full + 1;       //      epilogue has read O                   (8 softmax warps)
+  uint64_t* ring_full = o_empty + 1;    // [kSlots] tile landed                       (TMA transaction bytes)
+  uint64_t* ring_empty = ring_full + kSlots;  // [kSlots] tile consumed: Q after its copy to TMEM and V after its P V
+                                        //      (tcgen05.commit), K after its scores are complete (a softmax thread)
+  float* xch = reinterpret_cast<float*>(smem + L.xch_off);   // [2 parity][2 column halves][128 rows]
+  uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc_off + 8);
+  const WaitCtx wctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_items = p.h * p.b * p.num_m_blocks;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&s_full[t]), 1);
+      mbar_init(smem_u32(&p_full[t]), 8);     // one elected lane per softmax warp
+    }
+    mbar_init(smem_u32(o_full), 1);
+    mbar_init(smem_u32(o_empty), 8);
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(smem_u32(&ring_full[s]), 1);
+      mbar_init(smem_u32(&ring_empty[s]), 1);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(sm_tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *sm_tmem_base;
+  const uint32_t ring_smem = smem_u32(smem + L.ring_off);
+
+  if (warp == kProducerWarp) {
+    // ================================================================== TMA producer
+    if (lane == 0) {
+      RingPos pos{0, 0};
+      bool ok = true;
+      // next ring tile: rows [row0, row0 + 128) of head `head` of tensor `tm`
+      auto load_tile = [&](const CUtensorMap* tm, int head, int row0, int coord_b) -> bool {
+        if (!mbar_wait(smem_u32(&ring_empty[pos.slot]), pos.phase ^ 1u, wctx)) return false;
+        const uint32_t bar = smem_u32(&ring_full[pos.slot]);
+        mbar_expect_tx(bar, T::kTileBytes);
+#pragma unroll
+        for (int hf = 0; hf < T::kHalves; ++hf)
+          tma_load_4d(ring_smem + pos.slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, head, row0, coord_b);
+        pos.advance(1);
+        return true;
+      };
+      Item it;
+      for (int li = blockIdx.x; ok && next_work_item(p, li, total_items, it); li += gridDim.x) {
+        ok = load_tile(&tmap_q, it.head, it.q_row0 + it.m0, it.coord_b);
+        for (int j = 0; ok && j < it.n_tiles; ++j) {
+          ok = load_tile(&tmap_k, it.hk, it.k_row0 + j * kBlockN, it.coord_b) &&
+               load_tile(&tmap_v, it.hk, it.k_row0 + j * kBlockN, it.coord_b);
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ================================================================== MMA issuer
+    // This one thread feeds the tensor pipe; every instruction it spends on anything else shows up as an idle pipe,
+    // so per tile it does three waits, sixteen MMAs and two commits and nothing more.
+    if (lane == 0) {
+      uint32_t c = 0, item_cnt = 0;
+      RingPos qk_pos{0, 0};     // next tile the Q K^T stream takes from the ring (a Q tile or a K tile)
+      RingPos v_pos{0, 0};      // next V tile
+      [[maybe_unused]] int tr = 0;
+      bool ok = true;
+      // item k's Q: ring -> TMEM.  The copy runs in issue order with the MMAs, so it cannot overtake the Q K^T
+      // products of item k-2 that read the same TMEM columns.
+      auto stage_q = [&](uint32_t k) -> bool {
+        if (!mbar_wait(smem_u32(&ring_full[qk_pos.slot]), qk_pos.phase, wctx)) return false;
+        tc_fence_after();
+        issue_q_to_tmem<DT>(ring_smem + qk_pos.slot * T::kTileBytes, tmem_base + kColQ + (k & 1u) * 64);
+        tc_commit(smem_u32(&ring_empty[qk_pos.slot]));
+        qk_pos.advance(1);
+        return true;
+      };
+      // S[c_next & 1] = Q(item k) K^T with the K tile at qk_pos; the K slot is released by the softmax warps
+      auto qk = [&](uint32_t k, uint32_t c_next) -> bool {
+        if (!mbar_wait(smem_u32(&ring_full[qk_pos.slot]), qk_pos.phase, wctx)) return false;
+        tc_fence_after();
+        issue_qk_ts<DT>(tmem_base + kColQ + (k & 1u) * 64, ring_smem + qk_pos.slot * T::kTileBytes,
+                        tmem_base + kColS + (c_next & 1u) * 128);
+        tc_commit(smem_u32(&s_full[c_next & 1u]));
+        qk_pos.advance(2);
+        return true;
+      };
+      int li = blockIdx.x;
+      Item it;
+      bool have = next_work_item(p, li, total_items, it);
+      if (have) {
+        ok = stage_q(0) && qk(0, 0);
+        v_pos.advance(2);                       // ring: Q K_0 [V_0]
+      }
+      while (ok && have) {
+        int li_n = li + gridDim.x;
+        Item nxt;
+        const bool have_n = next_work_item(p, li_n, total_items, nxt);
+        const int n = it.n_tiles;
+        for (int j = 0; ok && j < n; ++j) {
+          // scores of the NEXT tile first: they are computed while the softmax of tile c is still running
+          if (j + 1 < n) {
+            ok = qk(item_cnt, c + 1);
+          } else if (have_n) {
+            // after K_{n-1} the Q K^T stream's cursor already stands on the next item's Q tile
+            ok = stage_q(item_cnt + 1) && qk(item_cnt + 1, c + 1);
+          }
+          if (!ok) break;
+          FA_TRACE(2, tr, 10);
+          // O (+)= P_c V_j
+          if (!mbar_wait(smem_u32(&p_full[c & 1u]), (c >> 1) & 1u, wctx)) { ok = false; break; }
+          if (j == 0 && !mbar_wait(smem_u32(o_empty), (item_cnt & 1u) ^ 1u, wctx)) { ok = false; break; }
+          FA_TRACE(2, tr, 20);
+          if (!mbar_wait(smem_u32(&ring_full[v_pos.slot]), v_pos.phase, wctx)) { ok = false; break; }
+          tc_fence_after();
+          FA_TRACE(2, tr, 25);
+          issue_pv<DT>(tmem_base + kColS + (c & 1u) * 128, ring_smem + v_pos.slot * T::kTileBytes, tmem_base + kColO, j == 0);
+          tc_commit(smem_u32(&ring_empty[v_pos.slot]));
+          if (j + 1 == n) tc_commit(smem_u32(o_full));
+          FA_TRACE(2, tr, 30);
+          v_pos.advance(j + 1 == n ? 3 : 2);    // next V: two tiles on, or three across an item boundary (Q, K_0)
+          ++c;
+        }
+        ++item_cnt;
+        it = nxt;
+        li = li_n;
+        have = have_n;
+      }
+    }
+    __syncwarp();
+  } else if (warp < 8) {
+    // ================================================================== softmax / correction / epilogue
+    const int wg = warp >> 2;             // which 64 key columns of every tile
+    const int lane_grp = warp & 3;
+    const int row = lane_grp * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(lane_grp * 32) << 16;
+    const uint32_t t_o = tmem_base + lane_off + kColO + wg * 64;    // this thread's 64 accumulator columns
+    uint32_t c = 0, item_cnt = 0, xpar = 0;
+    RingPos k_pos{1, 0};      // K tile whose scores are awaited next (ring: Q K_0 V_0 K_1 V_1 ... Q K_0 ...)
+    RingPos v_prev{0, 0};     // V tile of the previous P V (valid from the second tile of an item on)
+    RingPos v_pos{2, 0};      // V tile of this tile's P V
+    const bool releaser = (warp == 0 && lane == 0);
+    [[maybe_unused]] int tr = 0;
+    [[maybe_unused]] const bool tracer = (lane == 0 && lane_grp == 0);
+    bool ok = true;
+    // A wait that gives up sets ok = false but the loops keep their shape (the named barriers below are not
+    // bounded, so every softmax thread must reach each of them); results are discarded.
+    for (int li = blockIdx.x; li < total_items; li += gridDim.x) {
+      Item it;
+      if (!get_item(p, li, it)) continue;
+      const int row_in_seq = it.m0 + row;
+      const int64_t grow = static_cast<int64_t>(it.q_row0) + row_in_seq;
+      if (it.n_tiles == 0) {
+        if (row < it.rows_valid) {
+          uint8_t* op = out_row_ptr(p, it.coord_b, grow, it.head) + wg * 128;
+          const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) reinterpret_cast<uint4*>(op)[i] = z;
+          if (wg == 0 && p.lse) p.lse[lse_index(p, it.bidb, it.head, grow, row_in_seq)] = INFINITY;
+        }
+        continue;
+      }
+      const int row_limit = p.is_causal ? min(it.sk, row_in_seq + 1 + it.causal_shift) : it.sk;
+      const int warp_limit = p.is_causal ? min(it.sk, it.m0 + lane_grp * 32 + 1 + it.causal_shift) : it.sk;
+      float scale_log2 = p.scale_log2;
+      if (p.q_descale) scale_log2 *= p.q_descale[it.bidb * p.qds_b + it.hk * p.qds_h];
+      if (p.k_descale) scale_log2 *= p.k_descale[it.bidb * p.kds_b + it.hk * p.kds_h];
+      float m_ref = -INFINITY, l_part = 0.f;
+      for (int j = 0; j < it.n_tiles; ++j) {
+        const uint32_t b = c & 1u;
+        if (tracer && wg == 0) FA_TRACE(wg, tr, 1);
+        if (!mbar_wait(smem_u32(&s_full[b]), (c >> 1) & 1u, wctx)) ok = false;
+        tc_fence_after();
+        if (tracer && wg == 0) FA_TRACE(wg, tr, 2);
+        // the scores are complete, so the K tile they were computed from may be refilled
+        if (releaser) mbar_arrive(smem_u32(&ring_empty[k_pos.slot]));
+        k_pos.advance(j + 1 == it.n_tiles ? 3 : 2);
+        const uint32_t t_s = tmem_base + lane_off + kColS + b * 128 + wg * 64;
+        uint32_t u[2][32];
+        tmem_ld_32x32(t_s, u[0]);
+        tmem_ld_32x32(t_s + 32, u[1]);
+        tmem_wait_ld();
+#define FA_S_AT(idx) __uint_as_float(u[(idx) >> 5][(idx) & 31])
+        const int col0 = j * kBlockN + wg * 64;
+        if (col0 + 64 > warp_limit) {
+          const int lim = row_limit - col0;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) u[i >> 5][i & 31] = (i < lim) ? u[i >> 5][i & 31] : 0xff800000u;
+        }
+        float mx0 = FA_S_AT(0), mx1 = FA_S_AT(1), mx2 = FA_S_AT(2), mx3 = FA_S_AT(3);
+#pragma unroll
+        for (int i = 4; i < 64; i += 4) {
+          mx0 = fmaxf(mx0, FA_S_AT(i));
+          mx1 = fmaxf(mx1, FA_S_AT(i + 1));
+          mx2 = fmaxf(mx2, FA_S_AT(i + 2));
+          mx3 = fmaxf(mx3, FA_S_AT(i + 3));
+        }
+        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        // the other half of the row: exchange partial maxima.  After this barrier both threads of the row have
+        // also finished READING their scores, so P may overwrite the head of the S buffer.
+        float* xc = xch + (xpar * 2) * 128;
+        xc[wg * 128 + row] = mx;
+        if (tracer && wg == 0) FA_TRACE(wg, tr, 7);
+        softmax_bar_sync();
+        if (tracer && wg == 0) FA_TRACE(wg, tr, 8);
+        mx = fmaxf(mx, xc[(wg ^ 1) * 128 + row]);
+        xpar ^= 1u;
+        const float mx_scaled = mx * scale_log2;   // scale > 0
+        if (j == 0) {
+          m_ref = mx_scaled;
+        } else {
+          const bool grow_max = mx_scaled > m_ref + kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow_max)) {
+            const float m_new = grow_max ? mx_scaled : m_ref;
+            const float alpha = grow_max ? fast_exp2(m_ref - m_new) : 1.f;   // m_ref = -inf -> 0
+            l_part *= alpha;
+            m_ref = m_new;
+            // O is being accumulated by the previous tile's P V until that product releases its V tile
+            if (!mbar_wait(smem_u32(&ring_empty[v_prev.slot]), v_prev.phase, wctx)) ok = false;
+            tc_fence_after();
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              uint32_t o[32];
+              tmem_ld_32x32(t_o + h2 * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_32x32(t_o + h2 * 32, o);
+            }
+          }
+        }
+        const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
+        float rs0 = 0.f, rs1 = 0.f;
+        if constexpr (!T::kFp8) {
+          const uint32_t t_p = tmem_base + lane_off + kColS + b * 128 + wg * 32;
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float p0 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 2 * i), scale_log2, -m_safe));
+              const float p1 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 2 * i + 1), scale_log2, -m_safe));
+              rs0 += p0;
+              rs1 += p1;
+              pk[i] = pack2(p0, p1, DT);
+            }
+            tmem_st_32x16(t_p + h2 * 16, pk);
+          }
+        } else {
+          const uint32_t t_p = tmem_base + lane_off + kColS + b * 128 + wg * 16;
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float p0 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i), scale_log2, -m_safe));
+              const float p1 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 1), scale_log2, -m_safe));
+              const float p2 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 2), scale_log2, -m_safe));
+              const float p3 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 3), scale_log2, -m_safe));
+              rs0 += p0 + p2;
+              rs1 += p1 + p3;
+              pk[i] = pack4_e4m3(p0, p1, p2, p3);
+            }
+            tmem_st_32x8(t_p + h2 * 8, pk);
+          }
+        }
+#undef FA_S_AT
+        l_part += rs0 + rs1;
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&p_full[b]));
+        if (tracer && wg == 0) FA_TRACE(wg, tr, 4);
+        v_prev = v_pos;
+        v_pos.advance(j + 1 == it.n_tiles ? 3 : 2);
+        ++c;
+      }
+      // ---- epilogue of this item: this thread owns output columns [64 wg, 64 wg + 64) of its row
+      if (!mbar_wait(smem_u32(o_full), item_cnt & 1u, wctx)) ok = false;
+      tc_fence_after();
+      uint32_t o[2][32];
+      tmem_ld_32x32(t_o, o[0]);
+      tmem_ld_32x32(t_o + 32, o[1]);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(o_empty));   // O may be overwritten by the next item from here on
+      ++item_cnt;
+      // total row sum = the two halves' partial sums (same reference max)
+      float* xc = xch + (xpar * 2) * 128;
+      xc[wg * 128 + row] = l_part;
+      softmax_bar_sync();
+      const float l_sum = l_part + xc[(wg ^ 1) * 128 + row];
+      xpar ^= 1u;
+      if (ok && row < it.rows_valid) {
+        float vds = 1.f;
+        if (p.v_descale) vds = p.v_descale[it.bidb * p.vds_b + it.hk * p.vds_h];
+        const bool empty = !(l_sum > 0.f);
+        const float inv = empty ? 0.f : vds / l_sum;
+        uint8_t* op = out_row_ptr(p, it.coord_b, grow, it.head) + wg * 128;
+        store_o_chunk(op, 0, o[0], inv, p.out_dtype);
+        store_o_chunk(op, 1, o[1], inv, p.out_dtype);
+        if (wg == 0 && p.lse)
+          p.lse[lse_index(p, it.bidb, it.head, grow, row_in_seq)] = empty ? INFINITY : (m_ref + log2f(l_sum)) * kLn2;
+      }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int DT>
+cudaError_t launch_dense_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const PrefillKernelParams& p, cudaStream_t stream) {
+  auto kern = prefill_dense_kernel<DT>;
+  const size_t smem = 1024 + dense_smem<DT>().total;
+  static bool attr_done[64] = {};
+  static int num_sms[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    attr_done[dev] = true;
+  }
+  const long long total = static_cast<long long>(p.h) * p.b * p.num_m_blocks;
+  if (total <= 0) return cudaSuccess;
+  const int grid = static_cast<int>(total < num_sms[dev] ? total : num_sms[dev]);
+  kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+#ifdef FA_B200_PHASE_TRACE
+extern "C" __attribute__((visibility("default"))) int fa_b200_debug_trace_dense(long long* out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)));
+}
+#endif
+
+cudaError_t launch_prefill_dense(int dtype, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                                 const PrefillKernelParams& p, cudaStream_t stream) {
+  switch (dtype) {
+    case FA_B200_F16: return launch_dense_t<FA_B200_F16>(tq, tk, tv, p, stream);
+    case FA_B200_BF16: return launch_dense_t<FA_B200_BF16>(tq, tk, tv, p, stream);
+    case FA_B200_E4M3: return launch_dense_t<FA_B200_E4M3>(tq, tk, tv, p, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fa

@@ -172,11 +172,13 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     // ================================================================== MMA issuer
     if (lane == 0) {
       uint32_t kv_cnt = 0, item_cnt = 0, sp_cnt = 0;
+      [[maybe_unused]] int tr = 0;
       bool ok = true;
       for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
         Item it;
         if (!get_item(p, li, it) || it.n_tiles == 0) continue;
         const int n = it.n_tiles;
+        FA_TRACE(2, tr, 100 + n);
         {  // S_t(0) = Q_t K_0^T
           const uint32_t slot = kv_cnt % kSlots;
           if (!mbar_wait(smem_u32(&kv_full[slot]), (kv_cnt / kSlots) & 1u, wctx)) { ok = false; break; }
@@ -197,7 +199,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           const bool more = (j + 1 < n);
           const uint32_t kslot = (kv_cnt + 1) % kSlots, kph = ((kv_cnt + 1) / kSlots) & 1u;
           for (int t = 0; t < 2; ++t) {
+            FA_TRACE(2, tr, 10 + t);
             if (!mbar_wait(smem_u32(&p_full[t]), sp_cnt & 1u, wctx)) { ok = false; break; }
+            FA_TRACE(2, tr, 20 + t);
             // O_t still holds the previous item's result until its epilogue has read it
             if (j == 0 && !mbar_wait(smem_u32(&o_empty[t]), (item_cnt & 1u) ^ 1u, wctx)) { ok = false; break; }
             tc_fence_after();
@@ -216,6 +220,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             } else {
               tc_commit(smem_u32(&o_full[t]));
             }
+            FA_TRACE(2, tr, 30 + t);
           }
           ++sp_cnt;
           kv_cnt += more ? 2u : 1u;
@@ -234,6 +239,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + t * 128;
     const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + 256 + t * 128;
     uint32_t sp_cnt = 0, item_cnt = 0;
+    [[maybe_unused]] int tr = 0;
+    [[maybe_unused]] const bool tracer = (lane == 0 && lane_grp == 0);
     bool ok = true;
     for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
       Item it;
@@ -252,17 +259,23 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       if (p.k_descale) scale_log2 *= p.k_descale[it.bidb * p.kds_b + it.hk * p.kds_h];
       RowState st{-INFINITY, 0.f};
       for (int j = 0; j < it.n_tiles; ++j) {
+        if (tracer) FA_TRACE(t, tr, 1);
         if (!mbar_wait(smem_u32(&s_full[t]), sp_cnt & 1u, wctx)) { ok = false; break; }
         tc_fence_after();
+        if (tracer) FA_TRACE(t, tr, 2);
         const int start = j * kBlockN;
         softmax_tile<DT>(t_s, t_o, scale_log2, row_limit - start, start + kBlockN > warp_limit, j == 0, st);
+        if (tracer) FA_TRACE(t, tr, 3);
         tc_fence_before();
         mbar_arrive(smem_u32(&p_full[t]));
+        if (tracer) FA_TRACE(t, tr, 4);
         ++sp_cnt;
       }
       if (!ok) break;
+      if (tracer) FA_TRACE(t, tr, 5);
       if (!mbar_wait(smem_u32(&o_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
       tc_fence_after();
+      if (tracer) FA_TRACE(t, tr, 6);
       uint32_t o[4][32];
       tmem_ld_32x32(t_o + 0, o[0]);
       tmem_ld_32x32(t_o + 32, o[1]);
@@ -320,6 +333,12 @@ cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CU
 }
 
 }  // namespace
+
+#ifdef FA_B200_PHASE_TRACE
+extern "C" __attribute__((visibility("default"))) int fa_b200_debug_trace(long long* out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)));
+}
+#endif
 
 cudaError_t launch_prefill_pair(int dtype, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                 const PrefillKernelParams& p, cudaStream_t stream) {

@@ -244,20 +244,23 @@ def test_prefill_rejects_what_the_path_does_not_do(fa):
         flash_attn.flash_attn_func(q, q[:, :, :1].expand(1, 16, 3, 128), q)
 
 
-def test_both_prefill_kernels_agree_on_gqa(fa, monkeypatch):
-    """Dense GQA prefill normally runs on the persistent two-head kernel; the one-tile kernel (block-sparse, odd
-    groups) must give the same answer on the same input when forced."""
+def test_all_prefill_kernels_agree_on_gqa(fa, monkeypatch):
+    """Dense GQA prefill normally runs on the persistent kernel with double-buffered scores; the two-head
+    persistent kernel and the one-tile kernel (block-sparse lists) must give the same answer when forced."""
     flash_attn, cuda = fa
     g = gen(2024)
-    lens = [300, 1, 650, 128]
+    lens = [300, 1, 650, 128, 1500]
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32).cuda()
     q, k, v = randn(g, sum(lens), 8, 128).cuda(), randn(g, sum(lens), 2, 128).cuda(), randn(g, sum(lens), 2, 128).cuda()
-    a, la = flash_attn.flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True, return_softmax_lse=True)
-    monkeypatch.setenv("FA_B200_PREFILL_KERNEL", "single")
-    b, lb = flash_attn.flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True, return_softmax_lse=True)
-    torch.cuda.synchronize()
-    assert cuda.device_status() == 0
-    assert max_err(a.cpu(), b.cpu()) <= 2 ** -7 and max_err(la.cpu(), lb.cpu()) < 1e-4
-    ref32, _ = O.attention_varlen_ref(q.cpu(), k.cpu(), v.cpu(), cu.cpu(), cu.cpu(), causal=True, out_dtype=torch.float32)
+    ref32, ref_lse = O.attention_varlen_ref(q.cpu(), k.cpu(), v.cpu(), cu.cpu(), cu.cpu(), causal=True, out_dtype=torch.float32)
     ref_pt, _ = O.attention_varlen_ref(q.cpu(), k.cpu(), v.cpu(), cu.cpu(), cu.cpu(), causal=True, upcast=False, reorder_ops=True)
-    assert_close_to_oracle(b.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what="single-tile kernel on GQA")
+    outs = {}
+    for kern in ("dense", "pair", "single"):
+        monkeypatch.setenv("FA_B200_PREFILL_KERNEL", kern)
+        o, l = flash_attn.flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True, return_softmax_lse=True)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        assert_close_to_oracle(o.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=kern)
+        _check_lse(l.cpu(), ref_lse)
+        outs[kern] = o.cpu()
+    assert max_err(outs["dense"], outs["pair"]) <= 2 ** -6 and max_err(outs["dense"], outs["single"]) <= 2 ** -6
