@@ -11,11 +11,11 @@
 //               through shared memory (one named barrier per tile) and keep partial row sums
 //   warp 8      TMA producer: one ring of 6 tiles carries Q, K_0, V_0, K_1, V_1, ... of item after item
 //               (128B swizzle, no multicast)
-//   warp 9      MMA issuer (one thread): per item: Q tile shared memory -> TMEM (tcgen05.cp); per tile c:
-//               S[(c+1)&1] = Q K_{c+1}^T ;  O += P_c V_c.  Both products take their A operand (Q, P_c) from TMEM, so
-//               the tensor pipe reads only K and V from shared memory: shared-memory bandwidth, not math, is what
-//               bounds a 128x128 tcgen05 tile whose two operands both come from shared memory.
-//   warps 10-11 idle
+//   warp 9      MMA issuer 1 (one thread): per item: Q tile shared memory -> TMEM (tcgen05.cp); per tile
+//               S[c&1] = Q K_c^T, running up to two tiles ahead of the softmax
+//   warp 10     MMA issuer 2 (one thread): O += P_c V_c.  Both products take their A operand (Q, P_c) from TMEM and
+//               only K / V from shared memory.
+//   warp 11     idle
 // TMEM: S0 [0,128), S1 [128,256), O [256,384), Q of even items [384,448), Q of odd items [448,512).
 // P (input dtype) overwrites the head of its S buffer.
 // O in TMEM is rescaled only when a row max grew by more than 2^8 (and only after the previous P V has completed).
@@ -32,7 +32,7 @@ namespace {
 
 constexpr int kSlots = 6;         // ring of 32 KB (16 KB e4m3) tiles: Q, K_0, V_0, K_1, V_1, ... of item after item
 constexpr int kThreads = 32 * 12;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;   // warp 10: second MMA issuer
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0, kColO = 256, kColQ = 384;
 
@@ -179,75 +179,73 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
     }
   } else if (warp == kMmaWarp) {
-    // ================================================================== MMA issuer
-    // This one thread feeds the tensor pipe; every instruction it spends on anything else shows up as an idle pipe,
-    // so per tile it does three waits, sixteen MMAs and two commits and nothing more.
+    // ================================================================== MMA issuer 1: Q staging and S = Q K^T
+    // The tensor pipe is fed by two threads in two warps (this one and the P V issuer below).  Issuing a product
+    // holds its thread for about as long as the product runs, so with a single issuer every mbarrier wait and commit
+    // between two products is a hole in the pipe; with two, one thread waits while the other one issues.
     if (lane == 0) {
-      uint32_t c = 0, item_cnt = 0;
-      RingPos qk_pos{0, 0};     // next tile the Q K^T stream takes from the ring (a Q tile or a K tile)
-      RingPos v_pos{0, 0};      // next V tile
+      uint32_t c_next = 0, item_cnt = 0;
+      RingPos qk_pos{0, 0};     // next tile this stream takes from the ring (a Q tile or a K tile)
+      RingPos v_m2{0, 0}, v_m1{0, 0};   // V tiles of the two tiles before the one being issued
       [[maybe_unused]] int tr = 0;
       bool ok = true;
-      // item k's Q: ring -> TMEM.  The copy runs in issue order with the MMAs, so it cannot overtake the Q K^T
-      // products of item k-2 that read the same TMEM columns.
-      auto stage_q = [&](uint32_t k) -> bool {
-        if (!mbar_wait(smem_u32(&ring_full[qk_pos.slot]), qk_pos.phase, wctx)) return false;
+      Item it;
+      for (int li = blockIdx.x; ok && next_work_item(p, li, total_items, it); li += gridDim.x) {
+        // item's Q: ring -> TMEM.  The copy runs in issue order with this thread's MMAs, so it cannot overtake the
+        // Q K^T products of the item before last, which read the same TMEM columns.
+        const uint32_t q_tmem = tmem_base + kColQ + (item_cnt & 1u) * 64;
+        if (!mbar_wait(smem_u32(&ring_full[qk_pos.slot]), qk_pos.phase, wctx)) { ok = false; break; }
         tc_fence_after();
-        issue_q_to_tmem<DT>(ring_smem + qk_pos.slot * T::kTileBytes, tmem_base + kColQ + (k & 1u) * 64);
+        issue_q_to_tmem<DT>(ring_smem + qk_pos.slot * T::kTileBytes, q_tmem);
         tc_commit(smem_u32(&ring_empty[qk_pos.slot]));
         qk_pos.advance(1);
-        return true;
-      };
-      // S[c_next & 1] = Q(item k) K^T with the K tile at qk_pos; the K slot is released by the softmax warps
-      auto qk = [&](uint32_t k, uint32_t c_next) -> bool {
-        if (!mbar_wait(smem_u32(&ring_full[qk_pos.slot]), qk_pos.phase, wctx)) return false;
-        tc_fence_after();
-        issue_qk_ts<DT>(tmem_base + kColQ + (k & 1u) * 64, ring_smem + qk_pos.slot * T::kTileBytes,
-                        tmem_base + kColS + (c_next & 1u) * 128);
-        tc_commit(smem_u32(&s_full[c_next & 1u]));
-        qk_pos.advance(2);
-        return true;
-      };
-      int li = blockIdx.x;
-      Item it;
-      bool have = next_work_item(p, li, total_items, it);
-      if (have) {
-        ok = stage_q(0) && qk(0, 0);
-        v_pos.advance(2);                       // ring: Q K_0 [V_0]
+        for (int j = 0; j < it.n_tiles; ++j) {
+          FA_TRACE(2, tr, 1);
+          // S[c_next & 1] still holds P of tile c_next - 2 until that tile's P V has completed (it then releases
+          // its V tile)
+          if (c_next >= 2 && !mbar_wait(smem_u32(&ring_empty[v_m2.slot]), v_m2.phase, wctx)) { ok = false; break; }
+          v_m2 = v_m1;
+          v_m1 = qk_pos;
+          v_m1.advance(1);                             // V_j sits right behind K_j in the ring
+          if (!mbar_wait(smem_u32(&ring_full[qk_pos.slot]), qk_pos.phase, wctx)) { ok = false; break; }
+          tc_fence_after();
+          FA_TRACE(2, tr, 3);
+          issue_qk_ts<DT>(q_tmem, ring_smem + qk_pos.slot * T::kTileBytes, tmem_base + kColS + (c_next & 1u) * 128);
+          FA_TRACE(2, tr, 4);
+          tc_commit(smem_u32(&s_full[c_next & 1u]));   // the K slot itself is released by the softmax warps
+          qk_pos.advance(2);                           // K_{j+1}, or the next item's Q after K_{n-1}
+          ++c_next;
+        }
+        ++item_cnt;
       }
-      while (ok && have) {
-        int li_n = li + gridDim.x;
-        Item nxt;
-        const bool have_n = next_work_item(p, li_n, total_items, nxt);
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarp + 1) {
+    // ================================================================== MMA issuer 2: O (+)= P V
+    if (lane == 0) {
+      uint32_t c = 0, item_cnt = 0;
+      RingPos v_pos{2, 0};      // ring: Q K_0 [V_0] K_1 V_1 ...
+      [[maybe_unused]] int tr = 600;
+      bool ok = true;
+      Item it;
+      for (int li = blockIdx.x; ok && next_work_item(p, li, total_items, it); li += gridDim.x) {
         const int n = it.n_tiles;
-        for (int j = 0; ok && j < n; ++j) {
-          // scores of the NEXT tile first: they are computed while the softmax of tile c is still running
-          if (j + 1 < n) {
-            ok = qk(item_cnt, c + 1);
-          } else if (have_n) {
-            // after K_{n-1} the Q K^T stream's cursor already stands on the next item's Q tile
-            ok = stage_q(item_cnt + 1) && qk(item_cnt + 1, c + 1);
-          }
-          if (!ok) break;
+        for (int j = 0; j < n; ++j) {
           FA_TRACE(2, tr, 10);
-          // O (+)= P_c V_j
           if (!mbar_wait(smem_u32(&p_full[c & 1u]), (c >> 1) & 1u, wctx)) { ok = false; break; }
+          // O still holds the previous item's result until its epilogue has read it
           if (j == 0 && !mbar_wait(smem_u32(o_empty), (item_cnt & 1u) ^ 1u, wctx)) { ok = false; break; }
-          FA_TRACE(2, tr, 20);
           if (!mbar_wait(smem_u32(&ring_full[v_pos.slot]), v_pos.phase, wctx)) { ok = false; break; }
           tc_fence_after();
           FA_TRACE(2, tr, 25);
           issue_pv<DT>(tmem_base + kColS + (c & 1u) * 128, ring_smem + v_pos.slot * T::kTileBytes, tmem_base + kColO, j == 0);
+          FA_TRACE(2, tr, 28);
           tc_commit(smem_u32(&ring_empty[v_pos.slot]));
           if (j + 1 == n) tc_commit(smem_u32(o_full));
-          FA_TRACE(2, tr, 30);
           v_pos.advance(j + 1 == n ? 3 : 2);    // next V: two tiles on, or three across an item boundary (Q, K_0)
           ++c;
         }
         ++item_cnt;
-        it = nxt;
-        li = li_n;
-        have = have_n;
       }
     }
     __syncwarp();
