@@ -126,13 +126,15 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   if (part > 0) {
     if (part % pl.tile != 0 || (part % page != 0 && page % part != 0)) { pl.status = FA_B200_ERR_SHAPE; return pl; }
   } else {
-    // Aim for >= 32 work items per resident CTA slot (148 SMs x 2) so that ragged lengths balance, but keep
-    // at least 8 tiles per partition so the pipeline fill is amortised.
+    // Aim for >= 16 work items per resident CTA slot (148 SMs x 2) so that ragged lengths balance, keep at least
+    // 8 tiles per partition so the pipeline fill is amortised, and at most 256 partitions per sequence so the
+    // combine stays short.
     const int64_t bound = static_cast<int64_t>(p->b) * p->h_k * max_len;
-    const int64_t want = bound / (296 * 32);
+    const int64_t want = bound / (296 * 16);
     const int min_part = 8 * pl.tile;
     part = min_part;
     while (part * 2 <= want) part *= 2;
+    while (static_cast<int64_t>(part) * 256 < max_len) part *= 2;
     if (part < unit) part = unit;
   }
   // keep the per-partition page list within the kernel's shared-memory table
@@ -446,13 +448,15 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     k.num_m_blocks = (p->seqlen_q + 127) / 128;
   }
   if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
-  // Dense / varlen prefill runs on the persistent kernel with double-buffered scores; tile lists (per head) run
-  // one tile per CTA.  FA_B200_PREFILL_KERNEL=single|pair|dense overrides the choice (tests, comparisons); "pair"
-  // needs an even GQA group.
-  int which = sparse ? 0 : 2;
+  // Kernel choice.  Dense / varlen prefill with an even GQA group: persistent CTAs that work on two heads of the
+  // group at once and share every K/V tile ("pair").  Other head layouts (MHA, odd groups): persistent CTAs with
+  // double-buffered scores ("dense").  Tile lists are per head and run one tile per CTA ("single").
+  // FA_B200_PREFILL_KERNEL=single|pair|dense overrides the choice where it is legal (tests, comparisons).
+  const bool even_group = (p->h / p->h_k) % 2 == 0;
+  int which = sparse ? 0 : (even_group ? 1 : 2);
   if (const char* ov = getenv("FA_B200_PREFILL_KERNEL")) {
     if (!strcmp(ov, "single")) which = 0;
-    else if (!strcmp(ov, "pair") && !sparse && (p->h / p->h_k) % 2 == 0) which = 1;
+    else if (!strcmp(ov, "pair") && !sparse && even_group) which = 1;
     else if (!strcmp(ov, "dense") && !sparse) which = 2;
   }
   cudaError_t e = which == 2   ? launch_prefill_dense(p->dtype, tq, tk, tv, k, stream)

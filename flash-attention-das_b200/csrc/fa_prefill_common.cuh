@@ -53,6 +53,32 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
   return lo | (hi << 16);
 }
 
+// 2^x on the FMA and integer pipes (no MUFU): round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic
+// minimax polynomial for 2^f on [-0.5, 0.5] (relative error 7.5e-5, far below the rounding of P to a 16-bit or
+// 8-bit type), and n added straight into the exponent field.  x is clamped at -125, so the result is never exactly
+// zero: use it only where every score is finite (tiles that need no masking).
+// The MUFU unit evaluates 16 ex2 per clock per SM, exactly what a 128x128 tile needs in the time the tensor pipe
+// needs for its two products; moving a share of the exponentials here takes the MUFU unit off the critical path.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.0551708378f, 0.2426093519f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999281764f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+// Which elements of a row take the polynomial path (pattern over 16 consecutive columns).
+constexpr uint32_t kPolyPattern = 0x0000u;   // share of columns on the polynomial path (bit i: column i mod 16)
+__host__ __device__ constexpr bool poly_lane(int idx) { return (kPolyPattern >> (idx & 15)) & 1u; }
+template <bool kPoly>
+__device__ __forceinline__ float exp2_sel(float x, int idx) {
+  if constexpr (kPoly) {
+    if (poly_lane(idx)) return exp2_poly(x);
+  }
+  return fast_exp2(x);
+}
+
 // ---- MMA issue sequences ---------------------------------------------------------------------------------------
 // One thread feeds the tensor pipe, and a 128x128x16 product takes only 64 cycles, so the issue path has to be a
 // handful of instructions per MMA: each sequence below is ONE asm block that derives the k-step descriptors with a

@@ -4,11 +4,11 @@
 // accumulator S is double-buffered in TMEM, so S(c+1) = Q K_{c+1}^T is issued BEFORE the softmax of tile c has
 // finished: the tensor pipe computes the next scores (and the previous P V) while the softmax warps work, and the
 // softmax warps find their next tile ready when they finish the current one.  Work crosses item boundaries the same
-// way (the next item's Q is prefetched into a second Q buffer, its first S is issued before the current item's last
+// way (the next item's Q tile follows in the same ring, its first S is issued before the current item's last
 // P V).
-//   warps 0-3   softmax, key columns  0..63  of every tile (thread = query row)
-//   warps 4-7   softmax, key columns 64..127 of every tile; the two threads of a row exchange their partial max
-//               through shared memory (one named barrier per tile) and keep partial row sums
+//   warps 0-7   softmax: warpgroup g (warps 4g..4g+3) takes key columns 64g..64g+63 of every tile, thread = query
+//               row; the threads of a row exchange their partial max through shared memory (one named barrier per
+//               tile) and keep partial row sums.  (kSoftmaxWGs = 4, 32 columns per thread, measured slower.)
 //   warp 8      TMA producer: one ring of 6 tiles carries Q, K_0, V_0, K_1, V_1, ... of item after item
 //               (128B swizzle, no multicast)
 //   warp 9      MMA issuer 1 (one thread): per item: Q tile shared memory -> TMEM (tcgen05.cp); per tile
@@ -25,14 +25,19 @@
 // Same math as the reference's dense forward (csrc/flash_attn_cutlass/src/flash_fwd_kernel.h:2818-3328, FP8
 // 3330-3778; softmax.h:592-640,932-964); the heaviest-first order plays the role of the reference's reversed
 // m_block launch order (flash_fwd_kernel.h:8684).
+#include <type_traits>
+
 #include "fa_prefill_common.cuh"
 
 namespace fa {
 namespace {
 
 constexpr int kSlots = 6;         // ring of 32 KB (16 KB e4m3) tiles: Q, K_0, V_0, K_1, V_1, ... of item after item
-constexpr int kThreads = 32 * 12;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;   // warp 10: second MMA issuer
+constexpr int kSoftmaxWGs = 2;                    // warpgroups sharing a tile's key columns
+constexpr int kCols = kBlockN / kSoftmaxWGs;      // key (and output) columns per softmax thread
+constexpr int kSoftmaxWarps = 4 * kSoftmaxWGs;
+constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;   // kMmaWarp + 1: second MMA issuer
+constexpr int kThreads = 32 * (kSoftmaxWarps + 4);
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0, kColO = 256, kColQ = 384;
 
@@ -47,7 +52,7 @@ __host__ __device__ constexpr DenseSmem dense_smem() {
   s.bar_off = s.ring_off + kSlots * T::kTileBytes;
   // s_full[2] p_full[2] o_full o_empty ring_full[kSlots] ring_empty[kSlots]
   s.xch_off = s.bar_off + 8 * (6 + 2 * kSlots);
-  s.misc_off = s.xch_off + 4 * 2 * 2 * 128;
+  s.misc_off = s.xch_off + 4 * 2 * kSoftmaxWGs * 128;
   s.total = s.misc_off + 32;
   return s;
 }
@@ -100,7 +105,9 @@ __device__ __forceinline__ bool next_work_item(const PrefillKernelParams& p, int
   return false;
 }
 
-__device__ __forceinline__ void softmax_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void softmax_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * kSoftmaxWarps) : "memory");
+}
 
 template <int DT>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -118,7 +125,7 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* ring_full = o_empty + 1;    // [kSlots] tile landed                       (TMA transaction bytes)
   uint64_t* ring_empty = ring_full + kSlots;  // [kSlots] tile consumed: Q after its copy to TMEM and V after its P V
                                         //      (tcgen05.commit), K after its scores are complete (a softmax thread)
-  float* xch = reinterpret_cast<float*>(smem + L.xch_off);   // [2 parity][2 column halves][128 rows]
+  float* xch = reinterpret_cast<float*>(smem + L.xch_off);   // [2 parity][kSoftmaxWGs column groups][128 rows]
   uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc_off + 8);
   const WaitCtx wctx{abort_flag, p.status};
@@ -130,10 +137,10 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     *abort_flag = 0;
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&s_full[t]), 1);
-      mbar_init(smem_u32(&p_full[t]), 8);     // one elected lane per softmax warp
+      mbar_init(smem_u32(&p_full[t]), kSoftmaxWarps);     // one elected lane per softmax warp
     }
     mbar_init(smem_u32(o_full), 1);
-    mbar_init(smem_u32(o_empty), 8);
+    mbar_init(smem_u32(o_empty), kSoftmaxWarps);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&ring_full[s]), 1);
       mbar_init(smem_u32(&ring_empty[s]), 1);
@@ -249,20 +256,20 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp < 8) {
+  } else if (warp < kSoftmaxWarps) {
     // ================================================================== softmax / correction / epilogue
-    const int wg = warp >> 2;             // which 64 key columns of every tile
+    const int wg = warp >> 2;             // which kCols key columns of every tile (and which output columns)
     const int lane_grp = warp & 3;
     const int row = lane_grp * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(lane_grp * 32) << 16;
-    const uint32_t t_o = tmem_base + lane_off + kColO + wg * 64;    // this thread's 64 accumulator columns
+    const uint32_t t_o = tmem_base + lane_off + kColO + wg * kCols;    // this thread's accumulator columns
     uint32_t c = 0, item_cnt = 0, xpar = 0;
     RingPos k_pos{1, 0};      // K tile whose scores are awaited next (ring: Q K_0 V_0 K_1 V_1 ... Q K_0 ...)
     RingPos v_prev{0, 0};     // V tile of the previous P V (valid from the second tile of an item on)
     RingPos v_pos{2, 0};      // V tile of this tile's P V
     const bool releaser = (warp == 0 && lane == 0);
     [[maybe_unused]] int tr = 0;
-    [[maybe_unused]] const bool tracer = (lane == 0 && lane_grp == 0);
+    [[maybe_unused]] const bool tracer = (lane == 0 && warp == 0);
     bool ok = true;
     // A wait that gives up sets ok = false but the loops keep their shape (the named barriers below are not
     // bounded, so every softmax thread must reach each of them); results are discarded.
@@ -273,10 +280,10 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const int64_t grow = static_cast<int64_t>(it.q_row0) + row_in_seq;
       if (it.n_tiles == 0) {
         if (row < it.rows_valid) {
-          uint8_t* op = out_row_ptr(p, it.coord_b, grow, it.head) + wg * 128;
+          uint8_t* op = out_row_ptr(p, it.coord_b, grow, it.head) + wg * (kCols * 2);
           const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) reinterpret_cast<uint4*>(op)[i] = z;
+          for (int i = 0; i < kCols / 8; ++i) reinterpret_cast<uint4*>(op)[i] = z;
           if (wg == 0 && p.lse) p.lse[lse_index(p, it.bidb, it.head, grow, row_in_seq)] = INFINITY;
         }
         continue;
@@ -289,42 +296,44 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       float m_ref = -INFINITY, l_part = 0.f;
       for (int j = 0; j < it.n_tiles; ++j) {
         const uint32_t b = c & 1u;
-        if (tracer && wg == 0) FA_TRACE(wg, tr, 1);
+        if (tracer) FA_TRACE(0, tr, 1);
         if (!mbar_wait(smem_u32(&s_full[b]), (c >> 1) & 1u, wctx)) ok = false;
         tc_fence_after();
-        if (tracer && wg == 0) FA_TRACE(wg, tr, 2);
+        if (tracer) FA_TRACE(0, tr, 2);
         // the scores are complete, so the K tile they were computed from may be refilled
         if (releaser) mbar_arrive(smem_u32(&ring_empty[k_pos.slot]));
         k_pos.advance(j + 1 == it.n_tiles ? 3 : 2);
-        const uint32_t t_s = tmem_base + lane_off + kColS + b * 128 + wg * 64;
-        uint32_t u[2][32];
-        tmem_ld_32x32(t_s, u[0]);
-        tmem_ld_32x32(t_s + 32, u[1]);
+        const uint32_t t_s = tmem_base + lane_off + kColS + b * 128 + wg * kCols;
+        uint32_t u[kCols / 32][32];
+#pragma unroll
+        for (int h2 = 0; h2 < kCols / 32; ++h2) tmem_ld_32x32(t_s + h2 * 32, u[h2]);
         tmem_wait_ld();
 #define FA_S_AT(idx) __uint_as_float(u[(idx) >> 5][(idx) & 31])
-        const int col0 = j * kBlockN + wg * 64;
-        if (col0 + 64 > warp_limit) {
+        const int col0 = j * kBlockN + wg * kCols;
+        const bool masked_tile = col0 + kCols > warp_limit;   // warp-uniform
+        if (masked_tile) {
           const int lim = row_limit - col0;
 #pragma unroll
-          for (int i = 0; i < 64; ++i) u[i >> 5][i & 31] = (i < lim) ? u[i >> 5][i & 31] : 0xff800000u;
+          for (int i = 0; i < kCols; ++i) u[i >> 5][i & 31] = (i < lim) ? u[i >> 5][i & 31] : 0xff800000u;
         }
         float mx0 = FA_S_AT(0), mx1 = FA_S_AT(1), mx2 = FA_S_AT(2), mx3 = FA_S_AT(3);
 #pragma unroll
-        for (int i = 4; i < 64; i += 4) {
+        for (int i = 4; i < kCols; i += 4) {
           mx0 = fmaxf(mx0, FA_S_AT(i));
           mx1 = fmaxf(mx1, FA_S_AT(i + 1));
           mx2 = fmaxf(mx2, FA_S_AT(i + 2));
           mx3 = fmaxf(mx3, FA_S_AT(i + 3));
         }
         float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        // the other half of the row: exchange partial maxima.  After this barrier both threads of the row have
-        // also finished READING their scores, so P may overwrite the head of the S buffer.
-        float* xc = xch + (xpar * 2) * 128;
+        // the other column groups of the row: exchange partial maxima.  After this barrier every thread of the row
+        // has also finished READING its scores, so P may overwrite the head of the S buffer.
+        float* xc = xch + (xpar * kSoftmaxWGs) * 128;
         xc[wg * 128 + row] = mx;
-        if (tracer && wg == 0) FA_TRACE(wg, tr, 7);
+        if (tracer) FA_TRACE(0, tr, 7);
         softmax_bar_sync();
-        if (tracer && wg == 0) FA_TRACE(wg, tr, 8);
-        mx = fmaxf(mx, xc[(wg ^ 1) * 128 + row]);
+        if (tracer) FA_TRACE(0, tr, 8);
+#pragma unroll
+        for (int w = 0; w < kSoftmaxWGs; ++w) mx = fmaxf(mx, xc[w * 128 + row]);
         xpar ^= 1u;
         const float mx_scaled = mx * scale_log2;   // scale > 0
         if (j == 0) {
@@ -340,7 +349,7 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             if (!mbar_wait(smem_u32(&ring_empty[v_prev.slot]), v_prev.phase, wctx)) ok = false;
             tc_fence_after();
 #pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
+            for (int h2 = 0; h2 < kCols / 32; ++h2) {
               uint32_t o[32];
               tmem_ld_32x32(t_o + h2 * 32, o);
               tmem_wait_ld();
@@ -352,75 +361,84 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
         float rs0 = 0.f, rs1 = 0.f;
-        if constexpr (!T::kFp8) {
-          const uint32_t t_p = tmem_base + lane_off + kColS + b * 128 + wg * 32;
+        // P = 2^(S * scale - m) in the input dtype, written over the head of the S buffer.  On tiles without masking
+        // a fixed share of the columns may take the polynomial path (exp2_poly) instead of the MUFU unit.
+        auto exp_store = [&](auto poly_tag) {
+          constexpr bool kPoly = decltype(poly_tag)::value;
+          if constexpr (!T::kFp8) {
+            const uint32_t t_p = tmem_base + lane_off + kColS + b * 128 + wg * (kCols / 2);
 #pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            uint32_t pk[16];
+            for (int h2 = 0; h2 < kCols / 32; ++h2) {
+              uint32_t pk[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float p0 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 2 * i), scale_log2, -m_safe));
-              const float p1 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 2 * i + 1), scale_log2, -m_safe));
-              rs0 += p0;
-              rs1 += p1;
-              pk[i] = pack2(p0, p1, DT);
+              for (int i = 0; i < 16; ++i) {
+                const float p0 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 2 * i), scale_log2, -m_safe), 2 * i);
+                const float p1 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 2 * i + 1), scale_log2, -m_safe), 2 * i + 1);
+                rs0 += p0;
+                rs1 += p1;
+                pk[i] = pack2(p0, p1, DT);
+              }
+              tmem_st_32x16(t_p + h2 * 16, pk);
             }
-            tmem_st_32x16(t_p + h2 * 16, pk);
-          }
-        } else {
-          const uint32_t t_p = tmem_base + lane_off + kColS + b * 128 + wg * 16;
+          } else {
+            const uint32_t t_p = tmem_base + lane_off + kColS + b * 128 + wg * (kCols / 4);
 #pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            uint32_t pk[8];
+            for (int h2 = 0; h2 < kCols / 32; ++h2) {
+              uint32_t pk[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float p0 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i), scale_log2, -m_safe));
-              const float p1 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 1), scale_log2, -m_safe));
-              const float p2 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 2), scale_log2, -m_safe));
-              const float p3 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 3), scale_log2, -m_safe));
-              rs0 += p0 + p2;
-              rs1 += p1 + p3;
-              pk[i] = pack4_e4m3(p0, p1, p2, p3);
+              for (int i = 0; i < 8; ++i) {
+                const float p0 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 4 * i), scale_log2, -m_safe), 4 * i);
+                const float p1 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 4 * i + 1), scale_log2, -m_safe), 4 * i + 1);
+                const float p2 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 4 * i + 2), scale_log2, -m_safe), 4 * i + 2);
+                const float p3 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 4 * i + 3), scale_log2, -m_safe), 4 * i + 3);
+                rs0 += p0 + p2;
+                rs1 += p1 + p3;
+                pk[i] = pack4_e4m3(p0, p1, p2, p3);
+              }
+              tmem_st_32x8(t_p + h2 * 8, pk);
             }
-            tmem_st_32x8(t_p + h2 * 8, pk);
           }
-        }
+        };
+        if (masked_tile) exp_store(std::false_type{});
+        else exp_store(std::true_type{});
 #undef FA_S_AT
         l_part += rs0 + rs1;
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&p_full[b]));
-        if (tracer && wg == 0) FA_TRACE(wg, tr, 4);
+        if (tracer) FA_TRACE(0, tr, 4);
         v_prev = v_pos;
         v_pos.advance(j + 1 == it.n_tiles ? 3 : 2);
         ++c;
       }
-      // ---- epilogue of this item: this thread owns output columns [64 wg, 64 wg + 64) of its row
+      // ---- epilogue of this item: this thread owns output columns [kCols wg, kCols wg + kCols) of its row
       if (!mbar_wait(smem_u32(o_full), item_cnt & 1u, wctx)) ok = false;
       tc_fence_after();
-      uint32_t o[2][32];
-      tmem_ld_32x32(t_o, o[0]);
-      tmem_ld_32x32(t_o + 32, o[1]);
+      uint32_t o[kCols / 32][32];
+#pragma unroll
+      for (int h2 = 0; h2 < kCols / 32; ++h2) tmem_ld_32x32(t_o + h2 * 32, o[h2]);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(o_empty));   // O may be overwritten by the next item from here on
       ++item_cnt;
-      // total row sum = the two halves' partial sums (same reference max)
-      float* xc = xch + (xpar * 2) * 128;
+      // total row sum = the column groups' partial sums (same reference max)
+      float* xc = xch + (xpar * kSoftmaxWGs) * 128;
       xc[wg * 128 + row] = l_part;
       softmax_bar_sync();
-      const float l_sum = l_part + xc[(wg ^ 1) * 128 + row];
+      float l_sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kSoftmaxWGs; ++w) l_sum += xc[w * 128 + row];
       xpar ^= 1u;
       if (ok && row < it.rows_valid) {
         float vds = 1.f;
         if (p.v_descale) vds = p.v_descale[it.bidb * p.vds_b + it.hk * p.vds_h];
         const bool empty = !(l_sum > 0.f);
         const float inv = empty ? 0.f : vds / l_sum;
-        uint8_t* op = out_row_ptr(p, it.coord_b, grow, it.head) + wg * 128;
-        store_o_chunk(op, 0, o[0], inv, p.out_dtype);
-        store_o_chunk(op, 1, o[1], inv, p.out_dtype);
+        uint8_t* op = out_row_ptr(p, it.coord_b, grow, it.head) + wg * (kCols * 2);
+#pragma unroll
+        for (int h2 = 0; h2 < kCols / 32; ++h2) store_o_chunk(op, h2, o[h2], inv, p.out_dtype);
         if (wg == 0 && p.lse)
           p.lse[lse_index(p, it.bidb, it.head, grow, row_in_seq)] = empty ? INFINITY : (m_ref + log2f(l_sum)) * kLn2;
       }
