@@ -60,26 +60,53 @@ def load_peaks():
 # clocks sampler
 # --------------------------------------------------------------------------------------------------
 class ClockSampler:
+    """SM clock and throttle reasons sampled DURING the timed region: NVML from a thread every 2 ms (the timed
+    regions last milliseconds, far shorter than one nvidia-smi invocation); nvidia-smi as a fallback."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index = index
-        self.samples = []
+        self.sm = []
+        self.reason_bits = 0
+        self.sm_max = None
+        self.smi_samples = []
         self._stop = threading.Event()
         self._thr = None
+        self._nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = torch.cuda.get_device_properties(index).uuid
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
 
     def _run(self):
+        nv = self._nvml
         while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                parts = [x.strip() for x in out.strip().split(",")]
-                if len(parts) >= 6:
-                    self.samples.append(parts)
-            except Exception:
-                pass
-            self._stop.wait(0.1)
+            if nv is not None:
+                try:
+                    self.sm.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                    self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                except Exception:
+                    pass
+                self._stop.wait(0.002)
+            else:
+                try:
+                    out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                    parts = [x.strip() for x in out.strip().split(",")]
+                    if len(parts) >= 6:
+                        self.smi_samples.append(parts)
+                except Exception:
+                    pass
+                self._stop.wait(0.05)
 
     def __enter__(self):
         self._thr = threading.Thread(target=self._run, daemon=True)
@@ -91,13 +118,22 @@ class ClockSampler:
         self._thr.join(timeout=10)
 
     def summary(self):
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        sm = sorted(int(float(s[0])) for s in self.samples)
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(float(self.samples[0][1])), "reasons": reasons,
-                "samples": len(sm)}
+        if self._nvml is not None and self.sm:
+            nv = self._nvml
+            bits = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                    "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                    "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                    "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+            sm = sorted(self.sm)
+            return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.sm_max,
+                    "reasons": [n for n in names if self.reason_bits & bits[n]], "samples": len(sm), "source": "nvml"}
+        if self.smi_samples:
+            sm = sorted(int(float(s[0])) for s in self.smi_samples)
+            reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.smi_samples)]
+            return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": int(float(self.smi_samples[0][1])),
+                    "reasons": reasons, "samples": len(sm), "source": "nvidia-smi"}
+        return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0, "source": "none"}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -323,8 +359,6 @@ class LongSeqWorkload:
         self.q = torch.randn(1, 1, H, D, generator=cg).to(torch.bfloat16).to(dev)
         self.bt = torch.randperm(pool, generator=torch.Generator().manual_seed(seed + 7 + rank)).to(torch.int32).view(1, pool).to(dev)
         self.sl = torch.tensor([local], dtype=torch.int32, device=dev)
-        self.gather_o = torch.empty(world, H, D, dtype=torch.float32, device=dev)
-        self.gather_l = torch.empty(world, H, dtype=torch.float32, device=dev)
         self.units = float(local * HK * D * 2 * 2 + H * D * 4 + 4 * pool)   # this rank's bytes
         self.unit_name = "bytes"
         self.h2d, self.d2h = self.q.numel() * 2, H * D * 2
@@ -335,22 +369,16 @@ class LongSeqWorkload:
                      "l2": "inputs larger than L2 (%.2f GB per GPU)" % (self.units / 1e9)}
 
     def _run(self, q):
-        o, l = self.cuda.decode_partial(q, self.kc, self.vc, self.sl, self.bt, D ** -0.5)
-        if self.world > 1:
-            import torch.distributed as dist
-            dist.all_gather_into_tensor(self.gather_o.view(-1), o.view(-1))
-            dist.all_gather_into_tensor(self.gather_l.view(-1), l.view(-1))
-        else:
-            self.gather_o.copy_(o)
-            self.gather_l.copy_(l)
-        return self.cuda.combine(self.gather_o, self.gather_l, out_dtype=torch.bfloat16, h=H)[0]
+        from flash_attn.split_kv_parallel import decode_split_across_gpus
+        out, _ = decode_split_across_gpus(q, self.kc, self.vc, self.sl, self.bt, D ** -0.5)
+        return out
 
     def step(self):
         return self._run(self.q)
 
     def step_e2e(self):
         out = self._run(self.q_host.to(self.q.device, non_blocking=True))
-        self.out_host.copy_(out, non_blocking=True)
+        self.out_host.copy_(out.view(H, D), non_blocking=True)
         return out
 
 

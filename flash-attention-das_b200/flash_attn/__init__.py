@@ -11,3 +11,4 @@ from .flash_attn_interface import (  # noqa: F401
     flash_attn_with_kvcache,
     sparse_attn_func,
 )
+from . import split_kv_parallel  # noqa: F401,E402  (multi-GPU helpers: sharding, partial all-gather + combine)

@@ -1,0 +1,74 @@
+"""Multi-GPU helpers of the attention hot path (one process per GPU, torch.distributed).
+
+The path shards without communication — decode batches by sequence, prefill by sequence (or (batch, kv head)) — so
+the only collective is the one needed when a SINGLE very long sequence is split-KV across GPUs: every rank decodes
+its own page range to an fp32 partial (O normalised by its own sum, natural-log LSE), the partials are all-gathered
+(NCCL over NVLink; 16.5 KB per rank for 32 heads) into each rank's own memory and merged there by the LSE-combine
+kernel.  No peer-memory loads are involved.
+
+The reference has no counterpart (its long-context handling is single-device split-KV only,
+csrc/flash_attn_cutlass/src/paged_attention.cu:792-826); the partial format is the one its combine kernels consume
+(src/paged_attention.h:356-445), in LSE form.
+"""
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_sequences_lpt(lengths: Sequence[int], world_size: int, power: float = 1.0) -> List[List[int]]:
+    """Greedy longest-processing-time assignment of sequences to ranks.  Cost of a sequence = length ** power
+    (1 for decode: KV bytes streamed; 2 for causal prefill: FLOPs).  Returns, per rank, the sorted indices it owns;
+    every index appears exactly once and the result is deterministic."""
+    order = sorted(range(len(lengths)), key=lambda i: (-float(lengths[i]) ** power, i))
+    loads = [0.0] * world_size
+    owned: List[List[int]] = [[] for _ in range(world_size)]
+    for i in order:
+        r = min(range(world_size), key=lambda x: (loads[x], x))
+        owned[r].append(i)
+        loads[r] += float(lengths[i]) ** power
+    return [sorted(o) for o in owned]
+
+
+def split_page_range(num_pages: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous page range [first, last) of one sequence owned by `rank` (earlier ranks take the remainder)."""
+    base, rem = divmod(num_pages, world_size)
+    first = rank * base + min(rank, rem)
+    return first, first + base + (1 if rank < rem else 0)
+
+
+def gather_partials(o_partial: torch.Tensor, lse_partial: torch.Tensor,
+                    group: Optional[dist.ProcessGroup] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All-gather per-rank partials: o_partial (rows, d) fp32 and lse_partial (rows,) fp32 ->
+    (world, rows, d) and (world, rows), rank-major, identical on every rank — the layout the combine kernel takes.
+    Works on any backend (NCCL for CUDA tensors, gloo for CPU tensors)."""
+    world = dist.get_world_size(group)
+    o_all = torch.empty((world,) + tuple(o_partial.shape), dtype=o_partial.dtype, device=o_partial.device)
+    l_all = torch.empty((world,) + tuple(lse_partial.shape), dtype=lse_partial.dtype, device=lse_partial.device)
+    if o_partial.is_cuda:
+        dist.all_gather_into_tensor(o_all.view(-1), o_partial.contiguous().view(-1), group=group)
+        dist.all_gather_into_tensor(l_all.view(-1), lse_partial.contiguous().view(-1), group=group)
+    else:  # gloo has no all_gather_into_tensor for every build: use the list form
+        dist.all_gather(list(o_all.unbind(0)), o_partial.contiguous(), group=group)
+        dist.all_gather(list(l_all.unbind(0)), lse_partial.contiguous(), group=group)
+    return o_all, l_all
+
+
+def decode_split_across_gpus(q, k_cache_local, v_cache_local, local_seqlens, local_block_table, softmax_scale=None,
+                             group: Optional[dist.ProcessGroup] = None, out_dtype=torch.bfloat16, q_descale=None,
+                             k_descale=None, v_descale=None):
+    """Decode where each rank holds a slice of every sequence's KV pages.  q: (b, 1, h, 128), identical on every
+    rank; the caches, `local_seqlens` and `local_block_table` describe this rank's slice.  Returns
+    (out (b, 1, h, 128) out_dtype, lse (b, h) fp32), identical on every rank."""
+    import flash_attn_2_cuda as cuda
+    b, _, h, d = q.shape
+    if softmax_scale is None:
+        softmax_scale = d ** -0.5
+    o_part, l_part = cuda.decode_partial(q, k_cache_local, v_cache_local, local_seqlens, local_block_table,
+                                         softmax_scale, q_descale, k_descale, v_descale)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        o_all, l_all = gather_partials(o_part.view(b * h, d), l_part.view(b * h), group)
+    else:
+        o_all, l_all = o_part.view(1, b * h, d), l_part.view(1, b * h)
+    out, lse = cuda.combine(o_all, l_all, out_dtype=out_dtype, h=h)
+    return out.view(b, 1, h, d), lse.view(b, h)

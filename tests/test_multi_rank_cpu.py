@@ -1,0 +1,90 @@
+"""CPU, world_size 2 over gloo: the host-side logic of the multi-GPU paths — sequence sharding, page-range split
+of one long sequence, and the all-gather of (O, LSE) partials whose merge must equal the unsplit attention.  The
+attention itself is evaluated by the CPU oracle here (no GPU in this test); the kernels' side of the same exchange
+is covered by the GPU tests of the combine kernel."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import attention_oracle as O
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ret):
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "flash-attention-das_b200", "flash_attn"))
+    import split_kv_parallel as P            # the module itself needs no GPU; the package import would
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(7)        # same data on every rank
+        page, h, hk, d, npages = 16, 4, 2, 128, 11
+        L = npages * page - 5
+        q = torch.randn(1, 1, h, d, generator=g)
+        k = torch.randn(1, L, hk, d, generator=g)
+        v = torch.randn(1, L, hk, d, generator=g)
+        first, last = P.split_page_range(npages, world, rank)
+        lo, hi = first * page, min(last * page, L)
+        o, l = O.attention_ref(q, k[:, lo:hi], v[:, lo:hi], out_dtype=torch.float32)   # this rank's partial
+        o_all, l_all = P.gather_partials(o.reshape(h, d).contiguous(), l.reshape(h).contiguous())
+        assert o_all.shape == (world, h, d) and l_all.shape == (world, h)
+        merged, lse = O.merge_partials_ref(o_all, l_all)
+        full, lse_full = O.attention_ref(q, k, v, out_dtype=torch.float32)
+        ok = torch.allclose(merged, full[0, 0], atol=1e-5) and torch.allclose(lse, lse_full[0, :, 0], atol=1e-5)
+        # rank-major layout: slot r of the gathered buffer is rank r's partial
+        mine_ok = torch.equal(o_all[rank], o.reshape(h, d))
+        ret[rank] = bool(ok and mine_ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_and_merge_two_ranks_gloo():
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert dict(ret) == {0: True, 1: True}
+
+
+def test_lpt_sharding_properties():
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(
+        "split_kv_parallel", os.path.join(root, "flash-attention-das_b200", "flash_attn", "split_kv_parallel.py"))
+    P = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(P)
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(1024, 32769, (64,), generator=g).tolist()
+    for world in (1, 2, 4, 8):
+        shards = P.shard_sequences_lpt(lens, world)
+        assert sorted(i for s in shards for i in s) == list(range(64))          # a partition of the batch
+        loads = [sum(lens[i] for i in s) for s in shards]
+        assert max(loads) - min(loads) <= max(lens)                             # LPT bound
+        assert shards == P.shard_sequences_lpt(lens, world)                     # deterministic
+    sq = P.shard_sequences_lpt(lens, 4, power=2.0)
+    loads2 = [sum(lens[i] ** 2 for i in s) for s in sq]
+    assert max(loads2) - min(loads2) <= max(lens) ** 2
+    # page ranges tile [0, n) exactly
+    for n, w in ((4096, 8), (11, 2), (5, 8)):
+        r = [P.split_page_range(n, w, k) for k in range(w)]
+        assert r[0][0] == 0 and r[-1][1] == n and all(r[i][1] == r[i + 1][0] for i in range(w - 1))
