@@ -40,8 +40,12 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, as a multiple of the
 # algorithmic bytes, from the ncu captures summarised under profiles/ (None = not captured yet).
-TRAFFIC_RATIO = {"decode_bf16": None, "decode_fp8": None, "prefill_bf16": None, "prefill_fp8": None,
-                 "sparse_bf16": None, "longseq": None}
+# decode: measured on a quarter of the batch (traffic grows in proportion to the tokens streamed).
+TRAFFIC_RATIO = {"decode_bf16": 1.014, "decode_fp8": 1.013, "prefill_bf16": None, "prefill_fp8": None,
+                 "sparse_bf16": None, "longseq": 1.014}
+# prefill is tensor-bound, its algorithmic unit is FLOPs; DRAM traffic is reported in bytes per token of the
+# captured case (473.7 MB for 19,679 tokens, 1.18x the compulsory q+k+v+out bytes).
+PREFILL_TRAFFIC_BYTES_PER_TOKEN = {"prefill_bf16": 473.7e6 / 19679}
 
 
 def load_peaks():
@@ -59,81 +63,76 @@ def load_peaks():
 # --------------------------------------------------------------------------------------------------
 # clocks sampler
 # --------------------------------------------------------------------------------------------------
+_NVML_POLLER = r"""
+import sys, time
+import pynvml as nv
+nv.nvmlInit()
+uuid = sys.argv[1]
+try:
+    h = nv.nvmlDeviceGetHandleByUUID(uuid.encode())
+except Exception:
+    h = nv.nvmlDeviceGetHandleByIndex(int(sys.argv[2]))
+print("max", nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM), flush=True)
+while True:
+    try:
+        print(time.monotonic_ns(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+              nv.nvmlDeviceGetCurrentClocksEventReasons(h), flush=True)
+    except Exception:
+        pass
+    time.sleep(0.001)
+"""
+
+
 class ClockSampler:
-    """SM clock and throttle reasons sampled DURING the timed region: NVML from a thread every 2 ms (the timed
-    regions last milliseconds, far shorter than one nvidia-smi invocation); nvidia-smi as a fallback."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons sampled DURING the timed region.  A child process polls NVML every
+    millisecond (a thread of this process would starve behind the launch loop, and one nvidia-smi call lasts longer
+    than a whole timed region); the samples whose monotonic timestamp falls inside the region are summarised."""
+    REASON_BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index):
         self.index = index
-        self.sm = []
-        self.reason_bits = 0
-        self.sm_max = None
-        self.smi_samples = []
-        self._stop = threading.Event()
-        self._thr = None
-        self._nvml = None
+        self.proc = None
+        self.t0 = self.t1 = 0
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            uuid = torch.cuda.get_device_properties(index).uuid
-            try:
-                self._h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
-            except Exception:
-                self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
-            self._nvml = pynvml
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+            self.proc = subprocess.Popen([sys.executable, "-c", _NVML_POLLER, uuid, str(index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            time.sleep(0.3)   # let the poller come up before the region starts
         except Exception:
-            self._nvml = None
-
-    def _run(self):
-        nv = self._nvml
-        while not self._stop.is_set():
-            if nv is not None:
-                try:
-                    self.sm.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
-                    self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
-                except Exception:
-                    pass
-                self._stop.wait(0.002)
-            else:
-                try:
-                    out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                    parts = [x.strip() for x in out.strip().split(",")]
-                    if len(parts) >= 6:
-                        self.smi_samples.append(parts)
-                except Exception:
-                    pass
-                self._stop.wait(0.05)
+            self.proc = None
 
     def __enter__(self):
-        self._thr = threading.Thread(target=self._run, daemon=True)
-        self._thr.start()
+        self.t0 = time.monotonic_ns()
         return self
 
     def __exit__(self, *a):
-        self._stop.set()
-        self._thr.join(timeout=10)
+        self.t1 = time.monotonic_ns()
 
     def summary(self):
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        if self._nvml is not None and self.sm:
-            nv = self._nvml
-            bits = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
-                    "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
-                    "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
-                    "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
-            sm = sorted(self.sm)
-            return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.sm_max,
-                    "reasons": [n for n in names if self.reason_bits & bits[n]], "samples": len(sm), "source": "nvml"}
-        if self.smi_samples:
-            sm = sorted(int(float(s[0])) for s in self.smi_samples)
-            reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.smi_samples)]
-            return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": int(float(self.smi_samples[0][1])),
-                    "reasons": reasons, "samples": len(sm), "source": "nvidia-smi"}
-        return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0, "source": "none"}
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": "none"}
+        time.sleep(0.01)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm_max, sm, bits = None, [], 0
+        for line in out.splitlines():
+            parts = line.split()
+            if len(parts) == 2 and parts[0] == "max":
+                sm_max = int(parts[1])
+            elif len(parts) == 3:
+                t, clk, r = int(parts[0]), int(parts[1]), int(parts[2])
+                if self.t0 <= t <= self.t1:
+                    sm.append(clk)
+                    bits |= r
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": sm_max, "reasons": [], "samples": 0, "source": "nvml"}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": sm_max,
+                "reasons": [n for n, b in self.REASON_BITS.items() if bits & b], "samples": len(sm), "source": "nvml"}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -466,7 +465,8 @@ def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
     import flash_attn_2_cuda
     wl = make_workload(name, dev, args.seed + 1000 * rank, rank, world, args.scale)
     metric, unit, div = METRIC[wl.unit_name]
-    with ClockSampler(dev.index) as cs:
+    sampler = ClockSampler(dev.index)
+    with sampler as cs:
         l0 = flash_attn_2_cuda.launch_count()
         ms = time_steps(wl.step, args.steps, args.warmup, world, dev)
         launches = (flash_attn_2_cuda.launch_count() - l0) // (args.steps + args.warmup) * args.steps
@@ -494,7 +494,9 @@ def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
         "gpu_launches": int(launches),
         "roofline": {"bound": bound, "achieved": round(achieved, 2), "peak": peak, "unit": punit,
                      "frac": round(achieved / peak, 4), "peak_source": peaks["source"] + (" (2x bf16 for fp8)" if "fp8" in name and bound == "tensor" else ""),
-                     "traffic": None if ratio is None else ratio * wl.units,
+                     "traffic": (ratio * wl.units if ratio is not None else
+                                 (PREFILL_TRAFFIC_BYTES_PER_TOKEN[name] * wl.desc["tokens"]
+                                  if name in PREFILL_TRAFFIC_BYTES_PER_TOKEN else None)),
                      "kernel_ms_avg": round(k_avg, 4), "kernel_ms_median": round(k_med, 4),
                      "algorithmic_per_launch": wl.units},
         "clocks": clocks,
