@@ -2,9 +2,11 @@
 //
 // A CTA owns one query tile of 128 rows of one head and walks the key tiles (128 keys each) of its sequence, or
 // the tile list of a block-sparse row block.  Two CTAs share an SM (256 TMEM columns each):
-//   warp 0      TMA producer: Q once, then K_j / V_j tiles into a two-slot shared-memory ring (128B swizzle)
-//   warp 1      MMA issuer:   S = Q K_j^T and O += P V_j with tcgen05.mma, accumulators in TMEM
-//   warps 2-5   softmax:      one thread per query row (fa_prefill_common.cuh), then the epilogue
+//   warps 0-3   softmax:      one thread per query row (fa_prefill_common.cuh), then the epilogue
+//   warp 4      TMA producer: Q once, then K_j / V_j tiles into a two-slot shared-memory ring (128B swizzle)
+//   warp 5      MMA issuer:   S = Q K_j^T and O += P V_j with tcgen05.mma, accumulators in TMEM
+//   warps 6-7   idle: they complete the second warpgroup, which hands its registers to the softmax warpgroup
+//               (setmaxnreg: 40 / 216 per thread; a row of 128 scores is live in registers at once)
 // This kernel serves block-sparse lists (per-head tile lists cannot share K/V tiles between heads) and head
 // layouts without an even GQA group; dense GQA prefill runs on the two-tile persistent kernel
 // (fa_prefill_pair.cu).  Every mbarrier wait is bounded; a CTA that gives up raises the device status word and
@@ -20,7 +22,8 @@ namespace {
 
 constexpr int kMaxSparseTiles = 512;
 constexpr int kSlots = 2;           // K/V ring
-constexpr int kThreads = 32 * 6;
+constexpr int kThreads = 32 * 8;
+constexpr int kProducerWarp = 4, kMmaWarp = 5;
 constexpr int kTmemCols = 256;      // S (128) + O (128)
 
 struct SmemLayoutInfo {
@@ -126,15 +129,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   if (n_tiles == 0) {
     // no visible key for any row of this tile
-    if (warp >= 2) {
+    if (warp < 4) {
       const int row = (warp & 3) * 32 + lane;
       if (row < rows_valid) store_empty_row(p, coord_b, bidb, head, static_cast<int64_t>(q_row0) + m0 + row, m0 + row);
     }
     return;
   }
 
-  // ---- TMEM allocation (warp 1 owns it)
-  if (warp == 1) {
+  // ---- TMEM allocation (the MMA warp owns it)
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(sm_tmem_base), kTmemCols);
     tmem_relinquish();
   }
@@ -145,7 +148,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t q_smem = smem_u32(smem + L.q_off);
   const uint32_t ring_smem = smem_u32(smem + L.ring_off);
 
-  if (warp == 0) {
+  if (warp >= 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp == kProducerWarp) {
     // ================================================================== TMA producer
     if (lane == 0) {
       const uint32_t qbar = smem_u32(q_full);
@@ -171,7 +176,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kMmaWarp) {
     // ================================================================== MMA issuer
     if (lane == 0) {
       const uint32_t t_s = tmem_base, t_o = tmem_base + 128;
@@ -203,8 +208,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
     }
     __syncwarp();
+  }
   } else {
     // ================================================================== softmax / correction / epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int lane_grp = warp & 3;
     const int row = lane_grp * 32 + lane;
     const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16);
@@ -255,7 +262,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   // ---- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }

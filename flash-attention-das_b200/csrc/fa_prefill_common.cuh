@@ -219,13 +219,14 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
 #pragma unroll
     for (int c = 0; c < 128; ++c) u[c >> 5][c & 31] = (c < lim) ? u[c >> 5][c & 31] : 0xff800000u;
   }
-  float mx0 = FA_S_AT(0), mx1 = FA_S_AT(1), mx2 = FA_S_AT(2), mx3 = FA_S_AT(3);
+  float mx0 = fmaxf(FA_S_AT(0), FA_S_AT(1)), mx1 = fmaxf(FA_S_AT(2), FA_S_AT(3));
+  float mx2 = fmaxf(FA_S_AT(4), FA_S_AT(5)), mx3 = fmaxf(FA_S_AT(6), FA_S_AT(7));
 #pragma unroll
-  for (int c = 4; c < 128; c += 4) {
-    mx0 = fmaxf(mx0, FA_S_AT(c));
-    mx1 = fmaxf(mx1, FA_S_AT(c + 1));
-    mx2 = fmaxf(mx2, FA_S_AT(c + 2));
-    mx3 = fmaxf(mx3, FA_S_AT(c + 3));
+  for (int c = 8; c < 128; c += 8) {
+    mx0 = max3(mx0, FA_S_AT(c), FA_S_AT(c + 1));
+    mx1 = max3(mx1, FA_S_AT(c + 2), FA_S_AT(c + 3));
+    mx2 = max3(mx2, FA_S_AT(c + 4), FA_S_AT(c + 5));
+    mx3 = max3(mx3, FA_S_AT(c + 6), FA_S_AT(c + 7));
   }
   const float mx_scaled = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;   // scale > 0
   if (first) {
@@ -251,18 +252,38 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
   const float m_safe = (st.m_ref == -INFINITY) ? 0.f : st.m_ref;
   float rs0 = 0.f, rs1 = 0.f;
   if constexpr (!T::kFp8) {
+    if (kPolyPattern != 0u && !need_mask) {
+      // every score of the tile is finite: a fixed share of the columns takes the polynomial path
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t pk[16];
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = fast_exp2(fmaf(FA_S_AT(c * 32 + 2 * i), scale_log2, -m_safe));
-        const float p1 = fast_exp2(fmaf(FA_S_AT(c * 32 + 2 * i + 1), scale_log2, -m_safe));
-        rs0 += p0;
-        rs1 += p1;
-        pk[i] = pack2(p0, p1, DT);
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = exp2_sel<true>(fmaf(FA_S_AT(c * 32 + 2 * i), scale_log2, -m_safe), 2 * i);
+          const float p1 = exp2_sel<true>(fmaf(FA_S_AT(c * 32 + 2 * i + 1), scale_log2, -m_safe), 2 * i + 1);
+          rs0 += p0;
+          rs1 += p1;
+          pk[i] = pack2(p0, p1, DT);
+        }
+        tmem_st_32x16(t_s + c * 16, pk);
       }
-      tmem_st_32x16(t_s + c * 16, pk);
+    } else {
+      const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_safe, -m_safe);
+      uint64_t rs2 = pack_f32x2(0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(FA_S_AT(c * 32 + 2 * i), FA_S_AT(c * 32 + 2 * i + 1)), sc2, nm2), x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          rs2 = add_f32x2(rs2, pack_f32x2(p0, p1));
+          pk[i] = pack2(p0, p1, DT);
+        }
+        tmem_st_32x16(t_s + c * 16, pk);
+      }
+      unpack_f32x2(rs2, rs0, rs1);
     }
   } else {
 #pragma unroll

@@ -316,13 +316,14 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
           for (int i = 0; i < kCols; ++i) u[i >> 5][i & 31] = (i < lim) ? u[i >> 5][i & 31] : 0xff800000u;
         }
-        float mx0 = FA_S_AT(0), mx1 = FA_S_AT(1), mx2 = FA_S_AT(2), mx3 = FA_S_AT(3);
+        float mx0 = fmaxf(FA_S_AT(0), FA_S_AT(1)), mx1 = fmaxf(FA_S_AT(2), FA_S_AT(3));
+        float mx2 = fmaxf(FA_S_AT(4), FA_S_AT(5)), mx3 = fmaxf(FA_S_AT(6), FA_S_AT(7));
 #pragma unroll
-        for (int i = 4; i < kCols; i += 4) {
-          mx0 = fmaxf(mx0, FA_S_AT(i));
-          mx1 = fmaxf(mx1, FA_S_AT(i + 1));
-          mx2 = fmaxf(mx2, FA_S_AT(i + 2));
-          mx3 = fmaxf(mx3, FA_S_AT(i + 3));
+        for (int i = 8; i < kCols; i += 8) {
+          mx0 = max3(mx0, FA_S_AT(i), FA_S_AT(i + 1));
+          mx1 = max3(mx1, FA_S_AT(i + 2), FA_S_AT(i + 3));
+          mx2 = max3(mx2, FA_S_AT(i + 4), FA_S_AT(i + 5));
+          mx3 = max3(mx3, FA_S_AT(i + 6), FA_S_AT(i + 7));
         }
         float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         // the other column groups of the row: exchange partial maxima.  After this barrier every thread of the row
@@ -370,14 +371,20 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
             for (int h2 = 0; h2 < kCols / 32; ++h2) {
               uint32_t pk[16];
+              const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_safe, -m_safe);
+              uint64_t rs2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                const float p0 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 2 * i), scale_log2, -m_safe), 2 * i);
-                const float p1 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 2 * i + 1), scale_log2, -m_safe), 2 * i + 1);
-                rs0 += p0;
-                rs1 += p1;
+                float x0, x1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(FA_S_AT(h2 * 32 + 2 * i), FA_S_AT(h2 * 32 + 2 * i + 1)), sc2, nm2), x0, x1);
+                const float p0 = exp2_sel<kPoly>(x0, 2 * i), p1 = exp2_sel<kPoly>(x1, 2 * i + 1);
+                rs2 = add_f32x2(rs2, pack_f32x2(p0, p1));
                 pk[i] = pack2(p0, p1, DT);
               }
+              float r0, r1;
+              unpack_f32x2(rs2, r0, r1);
+              rs0 += r0;
+              rs1 += r1;
               tmem_st_32x16(t_p + h2 * 16, pk);
             }
           } else {

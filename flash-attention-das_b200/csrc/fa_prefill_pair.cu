@@ -126,13 +126,13 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *sm_tmem_base;
-  // Register hand-over between warpgroups: the producer/MMA warpgroup keeps 72 registers per thread, each softmax
-  // warpgroup (128 score registers per row live at once) grows to 216.  128 * (216 + 216 + 72) <= 65536.
+  // Register hand-over between warpgroups: the producer/MMA warpgroup keeps 80 registers per thread, each softmax
+  // warpgroup (128 score registers per row live at once) grows to 208.  128 * (208 + 208 + 80) <= 65536.
   const uint32_t q_smem = smem_u32(smem + L.q_off);
   const uint32_t ring_smem = smem_u32(smem + L.ring_off);
 
   if (warp >= 8) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
   if (warp == kProducerWarp) {
     // ================================================================== TMA producer
     if (lane == 0) {
@@ -232,7 +232,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   }
   } else {
     // ================================================================== softmax / correction / epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     const int t = warp >> 2;
     const int lane_grp = warp & 3;
     const int row = lane_grp * 32 + lane;
