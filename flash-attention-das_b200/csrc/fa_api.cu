@@ -126,15 +126,17 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   if (part > 0) {
     if (part % pl.tile != 0 || (part % page != 0 && page % part != 0)) { pl.status = FA_B200_ERR_SHAPE; return pl; }
   } else {
-    // Aim for >= 16 work items per resident CTA slot (148 SMs x 2) so that ragged lengths balance, keep at least
-    // 8 tiles per partition so the pipeline fill is amortised, and at most 256 partitions per sequence so the
-    // combine stays short.
-    const int64_t bound = static_cast<int64_t>(p->b) * p->h_k * max_len;
-    const int64_t want = bound / (296 * 16);
+    // Largest power-of-two partition (>= 8 tiles, so the pipeline fill is amortised) that still yields enough CTAs:
+    // about four rounds of the 296 resident CTA slots (148 SMs x 2) for a batch, whose lengths may be ragged, and
+    // about one round for a single sequence, whose partitions are all equal.  Measured on B200: per-CTA start-up
+    // and drain cost more than a slightly ragged tail, so bigger partitions win until the grid gets this small.
     const int min_part = 8 * pl.tile;
+    const int64_t rows = static_cast<int64_t>(p->b) * p->h_k;
+    const int64_t enough = (p->b == 1) ? 237 : 1100;
     part = min_part;
-    while (part * 2 <= want) part *= 2;
-    while (static_cast<int64_t>(part) * 256 < max_len) part *= 2;
+    while (part < max_len) part *= 2;
+    while (part > min_part && rows * ((max_len + part - 1) / part) < enough) part /= 2;
+    while (static_cast<int64_t>(part) * 256 < max_len) part *= 2;   // at most 256 partitions per sequence
     if (part < unit) part = unit;
   }
   // keep the per-partition page list within the kernel's shared-memory table

@@ -79,10 +79,15 @@ def test_partition_heuristic_and_workspace(binding):
     d.d, d.dtype, d.out_dtype = 128, 1, 1
     d.b, d.h, d.h_k, d.page_size, d.max_blocks_per_seq = 64, 32, 8, 256, 128
     part = lib.fa_b200_decode_partition_tokens(ctypes.byref(d))
-    assert part % 64 == 0 and 512 <= part <= 4096
+    assert part == 8192                     # 64 x 8 rows x 4 partitions = 2048 CTAs: about four rounds of the CTA slots
     nparts = (128 * 256 + part - 1) // part
     assert lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) == nparts * 64 * 32 * 129 * 4
     d.b, d.max_blocks_per_seq = 2, 1      # one page per sequence: no split, no scratch
     assert lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) == 0
+    d.b, d.max_blocks_per_seq = 1, 4096   # one sequence of 1,048,576 tokens: equal partitions, one round of CTAs
+    assert lib.fa_b200_decode_partition_tokens(ctypes.byref(d)) == 32768
+    d.b, d.max_blocks_per_seq, d.dtype = 128, 32, 2   # e4m3, batch 128 x 8192
+    assert lib.fa_b200_decode_partition_tokens(ctypes.byref(d)) == 4096
+    d.dtype = 1
     d.partition_tokens = 100               # not a multiple of the tile
     assert lib.fa_b200_decode_partition_tokens(ctypes.byref(d)) == 0
