@@ -6,8 +6,9 @@
 //   warps 0-3     softmax + epilogue of tile 0 (one thread per query row)
 //   warps 4-7     softmax + epilogue of tile 1
 //   warp 8        TMA producer: Q_0, Q_1 per item; K_j, V_j tiles into a four-slot ring, running ahead across items
-//   warp 9        MMA issuer, order per key tile j:  O_0 += P_0 V_j,  S_0 = Q_0 K_{j+1}^T,  O_1 += P_1 V_j,  S_1 = Q_1 K_{j+1}^T
-//   warps 10-11   idle (they complete the third warpgroup so that it can hand its registers to the softmax warps)
+//   warps 9, 10   MMA issuers of tile 0 and tile 1 (one thread each), per key tile j and under a common lock:
+//                 O_t += P_t V_j,  S_t = Q_t K_{j+1}^T
+//   warp 11       idle (completes the third warpgroup so that it can hand its registers to the softmax warps)
 // TMEM (all 512 columns): S_0, S_1, O_0, O_1 of 128 fp32 columns each; P overwrites the head of S.
 // CTAs stride over the virtual item list ordered by descending query block (for causal masks: heaviest first), so
 // prologue, Q loads and epilogue of one item overlap the main loop of its neighbours.  All mbarrier phases simply
@@ -94,6 +95,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint64_t* kv_empty = kv_full + kSlots;
   uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc_off + 8);
+  int* issue_lock = reinterpret_cast<int*>(smem + L.misc_off + 12);   // held while one tile's MMA group is issued
   const WaitCtx wctx{abort_flag, p.status};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -101,6 +103,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    *issue_lock = 0;
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&q_full[t]), 1);
       mbar_init(smem_u32(&q_empty[t]), 1);
@@ -111,7 +114,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&kv_full[s]), 1);
-      mbar_init(smem_u32(&kv_empty[s]), 1);
+      mbar_init(smem_u32(&kv_empty[s]), 2);   // released by both tiles' MMA issuers
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
@@ -168,59 +171,74 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         ++item_cnt;
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ================================================================== MMA issuer
+  } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+    // ================================================================== MMA issuers: warp 9 feeds tile 0, warp 10 tile 1
+    // One thread per tile.  Issuing a product holds its thread for about as long as the product runs, and every wait
+    // or commit costs the issuing thread a few hundred cycles, so with a single issuer those are holes in the pipe.
+    // With one issuer per tile, one thread waits and commits while the other one issues.  Each thread issues its
+    // tile's group  O_t += P_t V_j ;  S_t = Q_t K_{j+1}^T  under a lock, so the groups of the two tiles never
+    // interleave: S_0 and S_1 become ready a whole group apart, which keeps the two softmaxes out of phase (one runs
+    // while the tensor pipe works for the other).  The pipe executes in issue order, so the overwrite of S_t / P_t
+    // follows the P_t V read.  Each K/V slot is released by both issuers (empty barriers count two).
     if (lane == 0) {
+      const int t = warp - kMmaWarp;
+      const uint32_t t_s = tmem_base + t * 128, t_o = tmem_base + 256 + t * 128;
+      const uint32_t q_t = q_smem + t * T::kTileBytes;
       uint32_t kv_cnt = 0, item_cnt = 0, sp_cnt = 0;
-      [[maybe_unused]] int tr = 0;
+      [[maybe_unused]] int tr = t * 500;
       bool ok = true;
+      auto lock = [&]() -> bool {
+        uint32_t it = 0;
+        while (atomicCAS(issue_lock, 0, 1) != 0) {
+          if ((++it & 1023u) == 0u && *abort_flag) return false;
+        }
+        return true;
+      };
+      auto unlock = [&]() { __threadfence_block(); atomicExch(issue_lock, 0); };
       for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
         Item it;
         if (!get_item(p, li, it) || it.n_tiles == 0) continue;
         const int n = it.n_tiles;
-        FA_TRACE(2, tr, 100 + n);
         {  // S_t(0) = Q_t K_0^T
           const uint32_t slot = kv_cnt % kSlots;
           if (!mbar_wait(smem_u32(&kv_full[slot]), (kv_cnt / kSlots) & 1u, wctx)) { ok = false; break; }
-          for (int t = 0; t < 2; ++t) {
-            if (!mbar_wait(smem_u32(&q_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
-            tc_fence_after();
-            issue_qk<DT>(q_smem + t * T::kTileBytes, ring_smem + slot * T::kTileBytes, tmem_base + t * 128);
-            tc_commit(smem_u32(&s_full[t]));
-            if (n == 1) tc_commit(smem_u32(&q_empty[t]));
-          }
-          if (!ok) break;
+          if (!mbar_wait(smem_u32(&q_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
+          tc_fence_after();
+          if (!lock()) { ok = false; break; }
+          issue_qk<DT>(q_t, ring_smem + slot * T::kTileBytes, t_s);
+          tc_commit(smem_u32(&s_full[t]));
+          unlock();
           tc_commit(smem_u32(&kv_empty[slot]));
+          if (n == 1) tc_commit(smem_u32(&q_empty[t]));
           ++kv_cnt;
         }
-        for (int j = 0; ok && j < n; ++j) {
+        for (int j = 0; j < n; ++j) {
           const uint32_t vslot = kv_cnt % kSlots;
-          if (!mbar_wait(smem_u32(&kv_full[vslot]), (kv_cnt / kSlots) & 1u, wctx)) { ok = false; break; }
+          const uint32_t kslot = (kv_cnt + 1) % kSlots;
           const bool more = (j + 1 < n);
-          const uint32_t kslot = (kv_cnt + 1) % kSlots, kph = ((kv_cnt + 1) / kSlots) & 1u;
-          for (int t = 0; t < 2; ++t) {
-            FA_TRACE(2, tr, 10 + t);
-            if (!mbar_wait(smem_u32(&p_full[t]), sp_cnt & 1u, wctx)) { ok = false; break; }
-            FA_TRACE(2, tr, 20 + t);
-            // O_t still holds the previous item's result until its epilogue has read it
-            if (j == 0 && !mbar_wait(smem_u32(&o_empty[t]), (item_cnt & 1u) ^ 1u, wctx)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv<DT>(tmem_base + t * 128, ring_smem + vslot * T::kTileBytes, tmem_base + 256 + t * 128, j == 0);
-            if (t == 1) tc_commit(smem_u32(&kv_empty[vslot]));
-            if (more) {
-              if (t == 0) {
-                if (!mbar_wait(smem_u32(&kv_full[kslot]), kph, wctx)) { ok = false; break; }
-                tc_fence_after();
-              }
-              // the tensor pipe executes in issue order: this overwrite of S_t/P_t follows the P_t V read above
-              issue_qk<DT>(q_smem + t * T::kTileBytes, ring_smem + kslot * T::kTileBytes, tmem_base + t * 128);
-              tc_commit(smem_u32(&s_full[t]));
-              if (j + 2 == n) tc_commit(smem_u32(&q_empty[t]));
-              if (t == 1) tc_commit(smem_u32(&kv_empty[kslot]));
-            } else {
-              tc_commit(smem_u32(&o_full[t]));
-            }
-            FA_TRACE(2, tr, 30 + t);
+          FA_TRACE(2, tr, 10 + t);
+          // everything this group needs, before taking the lock
+          if (!mbar_wait(smem_u32(&kv_full[vslot]), (kv_cnt / kSlots) & 1u, wctx)) { ok = false; break; }
+          if (more && !mbar_wait(smem_u32(&kv_full[kslot]), ((kv_cnt + 1) / kSlots) & 1u, wctx)) { ok = false; break; }
+          // O_t still holds the previous item's result until its epilogue has read it
+          if (j == 0 && !mbar_wait(smem_u32(&o_empty[t]), (item_cnt & 1u) ^ 1u, wctx)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&p_full[t]), sp_cnt & 1u, wctx)) { ok = false; break; }
+          tc_fence_after();
+          FA_TRACE(2, tr, 20 + t);
+          if (!lock()) { ok = false; break; }
+          issue_pv<DT>(t_s, ring_smem + vslot * T::kTileBytes, t_o, j == 0);
+          if (more) {
+            issue_qk<DT>(q_t, ring_smem + kslot * T::kTileBytes, t_s);
+            tc_commit(smem_u32(&s_full[t]));
+          } else {
+            tc_commit(smem_u32(&o_full[t]));
+          }
+          unlock();
+          FA_TRACE(2, tr, 30 + t);
+          tc_commit(smem_u32(&kv_empty[vslot]));
+          if (more) {
+            tc_commit(smem_u32(&kv_empty[kslot]));
+            if (j + 2 == n) tc_commit(smem_u32(&q_empty[t]));
           }
           ++sp_cnt;
           kv_cnt += more ? 2u : 1u;
