@@ -385,17 +385,30 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   if (p->b < 0 || p->h <= 0 || p->h_k <= 0 || p->seqlen_q < 0 || p->seqlen_k < 0) return FA_B200_ERR_SHAPE;
   if (p->h % p->h_k != 0) return FA_B200_ERR_HEADS;
   const bool varlen = p->cu_seqlens_q != nullptr;
-  if (varlen != (p->cu_seqlens_k != nullptr)) return FA_B200_ERR_NULL;
+  const bool paged = p->block_table != nullptr;
+  if (!paged && varlen != (p->cu_seqlens_k != nullptr)) return FA_B200_ERR_NULL;
+  int box_rows = 128;
+  if (paged) {
+    if (sparse) return FA_B200_ERR_UNSUPPORTED;
+    if (!p->seqused_k) return FA_B200_ERR_NULL;
+    if (p->num_blocks <= 0) return FA_B200_ERR_SHAPE;
+    const int page = p->page_size;
+    if (page >= 128 && page % 128 == 0) box_rows = 128;
+    else if (page >= 64 && page % 64 == 0) box_rows = 64;
+    else if (page == 16 || page == 32) box_rows = page;
+    else return FA_B200_ERR_PAGE;
+  }
   if (varlen && (p->total_q < 0 || p->total_k < 0)) return FA_B200_ERR_SHAPE;
   if (p->b == 0 || p->seqlen_q == 0 || (varlen && p->total_q == 0)) return FA_B200_OK;
   if (!p->q || !p->out) return FA_B200_ERR_NULL;
-  const bool has_k = varlen ? p->total_k > 0 : p->seqlen_k > 0;
+  const bool has_k = paged ? true : (varlen ? p->total_k > 0 : p->seqlen_k > 0);
   if (has_k && (!p->k || !p->v)) return FA_B200_ERR_NULL;
   const int es = elem_size(p->dtype);
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return FA_B200_ERR_ALIGN;
   if (!stride_ok(p->q_row_stride, es) || !stride_ok(p->q_head_stride, es) || !stride_ok(p->k_row_stride, es) ||
       !stride_ok(p->k_head_stride, es) || !stride_ok(p->v_row_stride, es) || !stride_ok(p->v_head_stride, es) ||
-      (!varlen && (!stride_ok(p->q_batch_stride, es) || !stride_ok(p->k_batch_stride, es) || !stride_ok(p->v_batch_stride, es))) ||
+      (!varlen && !stride_ok(p->q_batch_stride, es)) ||
+      ((!varlen || paged) && (!stride_ok(p->k_batch_stride, es) || !stride_ok(p->v_batch_stride, es))) ||
       p->o_row_stride % 8 != 0 || p->o_head_stride % 8 != 0 || (!varlen && p->o_batch_stride % 8 != 0))
     return FA_B200_ERR_STRIDE;
   if (sparse) {
@@ -411,11 +424,19 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   int st = make_tmap(&tq, p->q, p->dtype, p->h, q_rows, nb, p->q_head_stride, p->q_row_stride,
                      varlen ? p->q_row_stride * (q_rows > 0 ? q_rows : 1) : p->q_batch_stride, 128);
   if (st != FA_B200_OK) return st;
-  st = make_tmap(&tk, p->k, p->dtype, p->h_k, k_rows, nb, p->k_head_stride, p->k_row_stride,
-                 varlen ? p->k_row_stride * (k_rows > 0 ? k_rows : 1) : p->k_batch_stride, 128);
-  if (st != FA_B200_OK) return st;
-  st = make_tmap(&tv, p->v, p->dtype, p->h_k, k_rows, nb, p->v_head_stride, p->v_row_stride,
-                 varlen ? p->v_row_stride * (k_rows > 0 ? k_rows : 1) : p->v_batch_stride, 128);
+  if (paged) {
+    st = make_tmap(&tk, p->k, p->dtype, p->h_k, p->page_size, p->num_blocks, p->k_head_stride, p->k_row_stride,
+                   p->k_batch_stride, box_rows);
+    if (st != FA_B200_OK) return st;
+    st = make_tmap(&tv, p->v, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
+                   p->v_batch_stride, box_rows);
+  } else {
+    st = make_tmap(&tk, p->k, p->dtype, p->h_k, k_rows, nb, p->k_head_stride, p->k_row_stride,
+                   varlen ? p->k_row_stride * (k_rows > 0 ? k_rows : 1) : p->k_batch_stride, 128);
+    if (st != FA_B200_OK) return st;
+    st = make_tmap(&tv, p->v, p->dtype, p->h_k, k_rows, nb, p->v_head_stride, p->v_row_stride,
+                   varlen ? p->v_row_stride * (k_rows > 0 ? k_rows : 1) : p->v_batch_stride, 128);
+  }
   if (st != FA_B200_OK) return st;
 
   PrefillKernelParams k{};
@@ -439,6 +460,14 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   k.out_dtype = p->out_dtype;
   k.scale_log2 = p->softmax_scale * kLog2e;
   k.sparse = sparse ? 1 : 0;
+  k.paged = paged ? 1 : 0;
+  if (paged) {
+    k.block_table = p->block_table;
+    k.bt_stride = p->block_table_batch_stride;
+    k.seqused_k = p->seqused_k;
+    k.page_size = p->page_size;
+    k.box_rows = box_rows;
+  }
   if (sparse) {
     k.block_count = p->block_count;
     k.block_offset = p->block_offset;
@@ -455,11 +484,11 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   // double-buffered scores ("dense").  Tile lists are per head and run one tile per CTA ("single").
   // FA_B200_PREFILL_KERNEL=single|pair|dense overrides the choice where it is legal (tests, comparisons).
   const bool even_group = (p->h / p->h_k) % 2 == 0;
-  int which = sparse ? 0 : (even_group ? 1 : 2);
+  int which = (sparse || paged) ? 0 : (even_group ? 1 : 2);   // paged K/V: one-tile kernel
   if (const char* ov = getenv("FA_B200_PREFILL_KERNEL")) {
     if (!strcmp(ov, "single")) which = 0;
-    else if (!strcmp(ov, "pair") && !sparse && even_group) which = 1;
-    else if (!strcmp(ov, "dense") && !sparse) which = 2;
+    else if (!strcmp(ov, "pair") && !sparse && !paged && even_group) which = 1;
+    else if (!strcmp(ov, "dense") && !sparse && !paged) which = 2;
   }
   cudaError_t e = which == 2   ? launch_prefill_dense(p->dtype, tq, tk, tv, k, stream)
                   : which == 1 ? launch_prefill_pair(p->dtype, tq, tk, tv, k, stream)

@@ -66,6 +66,12 @@ struct PrefillKernelParams {
   const float* v_descale;
   const int32_t* block_count;
   const int32_t* block_offset;
+  // paged K/V (one-tile kernel only): k/v tensor maps are (d, h_k, row in page, page); keys of sequence b are the
+  // first seqused_k[b] rows of the pages block_table[b * bt_stride + 0..]
+  const int32_t* block_table;
+  const int32_t* seqused_k;
+  int64_t bt_stride;
+  int32_t paged, page_size, box_rows;
   int64_t o_batch_stride, o_row_stride, o_head_stride;
   int64_t qds_b, qds_h, kds_b, kds_h, vds_b, vds_h;
   int64_t total_q;

@@ -76,12 +76,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   if (p.cu_seqlens_q) {
     q_row0 = p.cu_seqlens_q[bidb];
     sq = p.cu_seqlens_q[bidb + 1] - q_row0;
-    k_row0 = p.cu_seqlens_k[bidb];
-    sk = p.cu_seqlens_k[bidb + 1] - k_row0;
+    k_row0 = p.paged ? 0 : p.cu_seqlens_k[bidb];
+    sk = p.paged ? 0 : p.cu_seqlens_k[bidb + 1] - k_row0;
     coord_b = 0;
   } else {
     q_row0 = 0; k_row0 = 0; sq = p.seqlen_q; sk = p.seqlen_k; coord_b = bidb;
   }
+  if (p.paged) sk = p.seqused_k[bidb];   // keys live in the paged cache: length from cache_seqlens
   const int block_rows = p.sparse ? p.block_m : kBlockM;   // query rows this CTA is responsible for
   const int m0 = m_block * block_rows;
   if (m0 >= sq) return;
@@ -168,11 +169,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           const uint32_t ph = (item / kSlots) & 1;
           if (!mbar_wait(smem_u32(&kv_empty[slot]), ph ^ 1u, wctx)) { ok = false; break; }
           const uint32_t bar = smem_u32(&kv_full[slot]);
-          mbar_expect_tx(bar, T::kTileBytes);
           const CUtensorMap* tm = kv ? &tmap_v : &tmap_k;
+          if (!p.paged) {
+            mbar_expect_tx(bar, T::kTileBytes);
 #pragma unroll
-          for (int hf = 0; hf < T::kHalves; ++hf)
-            tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, hk, k_row0 + start, coord_b);
+            for (int hf = 0; hf < T::kHalves; ++hf)
+              tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, hk, k_row0 + start, coord_b);
+          } else {
+            // the tile's 128 keys come from one or more pages: one box of box_rows rows per page piece; boxes that
+            // start past the end of the sequence are not fetched (their block_table slots are not valid)
+            const int nbox = min(kBlockN / p.box_rows, (sk - start + p.box_rows - 1) / p.box_rows);
+            mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * p.box_rows * 128u * T::kHalves);
+            const int32_t* bt = p.block_table + static_cast<int64_t>(bidb) * p.bt_stride;
+            for (int i = 0; i < nbox; ++i) {
+              const int tok = start + i * p.box_rows;
+              const int page = bt[tok / p.page_size], row = tok % p.page_size;
+#pragma unroll
+              for (int hf = 0; hf < T::kHalves; ++hf)
+                tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes + i * p.box_rows * 128, tm, bar, hf * 64, hk,
+                            row, page);
+            }
+          }
         }
       }
     }
@@ -236,6 +253,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       int lim = row_limit - start;
       if (half_tile) lim = min(lim, 64);
       softmax_tile<DT>(t_s, t_o, scale_log2, lim, half_tile || start + kBlockN > warp_limit, j == 0, st);
+      if (p.paged && start + kBlockN > sk) {
+        // Last tile of a paged sequence: key rows past the end were not fetched, or hold whatever the page holds
+        // there.  Their P is zero, but 0 * NaN would still poison O, so this thread clears V row `row` of the tile
+        // (after it has landed) before the P V product may start.
+        const int v_item = 2 * j + 1;
+        if (!mbar_wait(smem_u32(&kv_full[v_item % kSlots]), (v_item / kSlots) & 1, wctx)) { ok = false; break; }
+        if (row >= sk - start) {
+          const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
+#pragma unroll
+          for (int hf = 0; hf < T::kHalves; ++hf)
+#pragma unroll
+            for (int c16 = 0; c16 < 8; ++c16)
+              asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(vrow + hf * T::kHalfBytes + c16 * 16), "r"(0u) : "memory");
+        }
+        fence_proxy_async_smem();
+      }
       tc_fence_before();
       mbar_arrive(smem_u32(p_full));
     }

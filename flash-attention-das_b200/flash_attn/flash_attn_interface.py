@@ -88,10 +88,13 @@ def flash_attn_varlen_func(
 ):
     """Packed variable-length attention.  q: (total_q, nheads, 128); k, v: (total_k, nheads_k, 128);
     cu_seqlens_*: int32 (batch + 1).  FP8 e4m3 inputs take fp32 q/k/v_descale of one element or shape
-    (batch, nheads_k) and return bf16.  softmax_lse is (nheads, total_q)."""
+    (batch, nheads_k) and return bf16.  softmax_lse is (nheads, total_q).
+    With `block_table` (int32 (batch, max_blocks)) k and v are paged pools (num_blocks, page_size, nheads_k, 128) and
+    `seqused_k` (int32 (batch,)) gives each sequence's number of keys; cu_seqlens_k is not used.  The kernel reads
+    the pages directly (the reference gathers them into a contiguous copy first, flash_attn_interface.py:2350-2373)."""
     _no_backward(q, k, v)
-    if block_table is not None:
-        raise NotImplementedError("paged prefill (block_table) through flash_attn_varlen_func is not on the B200 hot path yet")
+    if block_table is not None and layout != "bshd":
+        raise NotImplementedError("paged K/V layouts other than bshd (num_blocks, page, nheads_k, d) are outside the B200 hot path")
     if q_v is not None:
         raise NotImplementedError("q_v is outside the B200 hot path of this build")
     if softmax_scale is None:

@@ -53,6 +53,8 @@ class FwdParams(ctypes.Structure):
         ("block_count", _c_vp), ("block_offset", _c_vp),
         ("num_q_blocks", _c_i32), ("nnz_s", _c_i32), ("block_m", _c_i32),
         ("profile_start_event", _c_vp), ("profile_stop_event", _c_vp),
+        ("block_table", _c_vp), ("block_table_batch_stride", _c_i64), ("seqused_k", _c_vp),
+        ("page_size", _c_i32), ("num_blocks", _c_i32),
     ]
 
 
@@ -193,6 +195,24 @@ def _descale(params, name, t: Optional[torch.Tensor], batch: int, h_k: int):
     setattr(params, name + "_head_stride", hs)
 
 
+def _set_paged(p, kcache, vcache, block_table, seqused_k, batch):
+    """K/V given as paged pools (num_blocks, page, h_k, d) + int32 block_table (batch, max_blocks) + int32
+    seqused_k (batch)."""
+    _require(block_table.dtype == torch.int32 and block_table.is_cuda, "block_table must have dtype torch.int32")
+    _require(block_table.stride(-1) == 1, "block_table must have contiguous last dimension")
+    _require(block_table.shape[0] == batch, "block_table batch mismatch")
+    _require(seqused_k is not None, "seqused_k / cache_seqlens is required with block_table")
+    _require(seqused_k.dtype == torch.int32 and seqused_k.is_contiguous() and seqused_k.numel() == batch,
+             "seqused_k must be a contiguous int32 tensor of shape (batch,)")
+    _require(kcache.dim() == 4 and kcache.shape == vcache.shape, "paged k/v must be (num_blocks, page_size, nheads_k, d)")
+    p.k, p.v = kcache.data_ptr(), vcache.data_ptr()
+    p.k_batch_stride, p.k_row_stride, p.k_head_stride = kcache.stride(0), kcache.stride(1), kcache.stride(2)
+    p.v_batch_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
+    p.block_table, p.block_table_batch_stride = block_table.data_ptr(), block_table.stride(0)
+    p.seqused_k = seqused_k.data_ptr()
+    p.page_size, p.num_blocks = kcache.shape[1], kcache.shape[0]
+
+
 def _out_dtype(q, out_):
     if out_ is not None:
         _require(out_.dtype in (torch.float16, torch.bfloat16), "Output must be fp16 or bf16")
@@ -268,23 +288,23 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
                window_size_right, softcap, return_softmax, q_descale_=None, k_descale_=None, v_descale_=None,
                gen_=None, s_aux_=None):
     _check_qkv(q, k, v)
-    _unsupported(block_table_ is not None, "paged prefill through varlen_fwd")
-    _unsupported(seqused_k is not None, "seqused_k")
+    paged = block_table_ is not None
+    _unsupported(seqused_k is not None and not paged, "seqused_k without block_table")
     _unsupported(leftpad_k_ is not None, "leftpad_k")
     _unsupported(alibi_slopes_ is not None, "alibi")
     _unsupported(p_dropout != 0.0, "dropout")
     _unsupported(softcap != 0.0, "softcap")
     _unsupported(return_softmax, "return_softmax")
     _unsupported(s_aux_ is not None, "attention sinks (s_aux)")
-    for name, t in (("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_k", cu_seqlens_k)):
+    for name, t in (("cu_seqlens_q", cu_seqlens_q),) + (() if paged else (("cu_seqlens_k", cu_seqlens_k),)):
         _require(t.dtype == torch.int32, f"{name} must have dtype int32")
         _require(t.is_cuda, f"{name} must be on CUDA device")
         _require(t.is_contiguous(), f"{name} must be contiguous")
     total_q, h, d = q.shape
-    total_k, h_k = k.shape[0], k.shape[1]
+    total_k, h_k = (0, k.shape[2]) if paged else (k.shape[0], k.shape[1])
     b = cu_seqlens_q.numel() - 1
     _require(b > 0, "batch size must be positive")
-    _require(cu_seqlens_k.numel() == b + 1, "cu_seqlens_k must have shape (batch_size + 1)")
+    _require(paged or cu_seqlens_k.numel() == b + 1, "cu_seqlens_k must have shape (batch_size + 1)")
     _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
     if window_size_left >= max_seqlen_k:
         window_size_left = -1
@@ -312,12 +332,16 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     p = FwdParams()
     p.q, p.k, p.v, p.out, p.softmax_lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
-    p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1)
-    p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1)
     p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1)
     p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = b, max_seqlen_q, max_seqlen_k, h, h_k, d
     p.total_q, p.total_k = total_q, total_k
-    p.cu_seqlens_q, p.cu_seqlens_k = cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr()
+    p.cu_seqlens_q = cu_seqlens_q.data_ptr()
+    if paged:
+        _set_paged(p, k, v, block_table_, seqused_k, b)
+    else:
+        p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1)
+        p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1)
+        p.cu_seqlens_k = cu_seqlens_k.data_ptr()
     p.softmax_scale = softmax_scale
     p.is_causal = 1 if causal else 0
     p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
@@ -386,7 +410,8 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
                 block_table_, alibi_slopes_, out_, softmax_scale, is_causal, window_size_left, window_size_right,
                 softcap, is_rotary_interleaved, num_splits, s_aux_=None, q_descale_=None, k_descale_=None,
                 v_descale_=None, max_seqlen_k=0):
-    """Paged decode.  Like the reference's mha_fwd_kvcache (flash_api.cpp:2530-2577) this path needs
+    """Attention over a paged KV cache: the decode kernel for one query token per sequence, the prefill kernel
+    reading K/V through the block table for more.  Like the reference's mha_fwd_kvcache (flash_api.cpp:2530-2577) this path needs
     ``block_table`` and ``seqlens_k`` and ignores nothing silently: the options the reference's wrapper drops
     (new k/v append, rotary, cache_batch_idx, leftpad) raise instead.  Unlike the reference, the returned
     softmax_lse is filled in."""
@@ -405,7 +430,6 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     _require(seqlens_k_.dtype == torch.int32, "seqlens_k must have dtype int32")
     _require(seqlens_k_.is_contiguous(), "seqlens_k must be contiguous")
     b, sq, h, d = q.shape
-    _unsupported(sq != 1, "more than one query token per sequence in the decode call")
     _unsupported(window_size_left >= 0 and window_size_left < kcache.shape[1] * block_table_.shape[1],
                  "sliding-window attention")
     _require(seqlens_k_.numel() == b and block_table_.shape[0] == b, "cache_seqlens / block_table batch mismatch")
@@ -420,6 +444,26 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     else:
         out = torch.empty((b, sq, h, d), dtype=odt, device=q.device)
     lse = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
+    if sq > 1:
+        # several query tokens per sequence (chunked prefill, speculative decoding) over the paged cache: the prefill
+        # kernel reads K/V through the block table; the causal mask is bottom-right aligned to each cache length
+        fp = FwdParams()
+        fp.q, fp.out, fp.softmax_lse = q.data_ptr(), out.data_ptr(), lse.data_ptr()
+        fp.q_batch_stride, fp.q_row_stride, fp.q_head_stride = q.stride(0), q.stride(1), q.stride(2)
+        fp.o_batch_stride, fp.o_row_stride, fp.o_head_stride = out.stride(0), out.stride(1), out.stride(2)
+        fp.b, fp.seqlen_q, fp.h, fp.h_k, fp.d = b, sq, h, h_k, d
+        fp.seqlen_k = kcache.shape[1] * block_table_.shape[1]
+        fp.softmax_scale = softmax_scale
+        fp.is_causal = 1 if is_causal else 0
+        fp.dtype, fp.out_dtype = _DT[q.dtype], _DT[odt]
+        _descale(fp, "q_descale", q_descale_, b, h_k)
+        _descale(fp, "k_descale", k_descale_, b, h_k)
+        _descale(fp, "v_descale", v_descale_, b, h_k)
+        _set_paged(fp, kcache, vcache, block_table_, seqlens_k_, b)
+        _apply_profile_events(fp)
+        with torch.cuda.device(q.device):
+            _check(_lib.fa_b200_fwd(ctypes.byref(fp), _stream(q)), "fwd_kvcache")
+        return [out, lse]
     p = _decode_params(q, kcache, vcache, seqlens_k_, block_table_, softmax_scale, out, lse, q_descale_, k_descale_,
                        v_descale_, 0, max_seqlen_k)
     with torch.cuda.device(q.device):

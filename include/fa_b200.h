@@ -95,6 +95,15 @@ typedef struct fa_b200_fwd_params {
    * kernel (timing of the dominant kernel alone); NULL = off. */
   void* profile_start_event;
   void* profile_stop_event;
+  /* Paged K/V (fa_b200_fwd only): when block_table is set, k and v are pools (num_blocks, page_size, h_k, d) whose
+   * block stride is k_batch_stride / v_batch_stride; int32 block_table (b, max_blocks) lists each sequence's pages and
+   * int32 seqused_k (b) its number of keys (cu_seqlens_k is not read; seqlen_k is an upper bound).  Page sizes 16, 32
+   * and multiples of 64.  Replaces the block_table branch of the reference's varlen entry
+   * (flash_attn/flash_attn_interface.py:2223-2405: pagedkv_to_contiguous + varlen_fwd) without the gather copy. */
+  const int32_t* block_table;
+  int64_t block_table_batch_stride;
+  const int32_t* seqused_k;
+  int32_t page_size, num_blocks;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch

@@ -264,3 +264,55 @@ def test_all_prefill_kernels_agree_on_gqa(fa, monkeypatch):
         _check_lse(l.cpu(), ref_lse)
         outs[kern] = o.cpu()
     assert max_err(outs["dense"], outs["pair"]) <= 2 ** -6 and max_err(outs["dense"], outs["single"]) <= 2 ** -6
+
+
+@pytest.mark.parametrize("page", [16, 64, 256])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_paged_prefill_reads_pages_directly(fa, page, dtype):
+    """flash_attn_varlen_func(block_table=...): K/V in a paged pool (NaN-poisoned unused pages and tails), packed
+    varlen q, causal mask bottom-right aligned to each sequence's key count (prefix-cache prefill)."""
+    from _util import clean_nan, make_paged
+    flash_attn, cuda = fa
+    g = gen(500 + page)
+    lens_k = [300, 130, 1000, 64, 257]
+    lens_q = [300, 2, 129, 64, 200]           # full prefill, tiny chunk, chunk of a long prefix, exact tile, ragged
+    h, h_k = 8, 2
+    kc, vc, bt, sl = make_paged(g, lens_k, h_k, page, dtype)
+    q = randn(g, sum(lens_q), h, 128, dtype=dtype)
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    out, lse = flash_attn.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cq.cuda(), None, max(lens_q), max(lens_k),
+                                                 seqused_k=sl.cuda(), causal=True, block_table=bt.cuda(),
+                                                 return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    kcc, vcc = clean_nan(kc), clean_nan(vc)
+    for i, (lq, lk) in enumerate(zip(lens_q, lens_k)):
+        qi = q[int(cq[i]):int(cq[i + 1])][None]
+        ki, vi = O.gather_paged_kv(kcc, bt[i], lk)[None], O.gather_paged_kv(vcc, bt[i], lk)[None]
+        ref32, ref_lse = O.attention_ref(qi, ki, vi, causal=True, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(qi, ki, vi, causal=True, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out[int(cq[i]):int(cq[i + 1])].cpu()[None], ref32, ref_pt, mult=2.0, eps=2 ** -8,
+                               what=f"paged prefill seq {i} page {page}")
+        _check_lse(lse[:, int(cq[i]):int(cq[i + 1])].cpu(), ref_lse[0])
+
+
+def test_kvcache_call_with_several_query_tokens(fa):
+    """flash_attn_with_kvcache with seqlen_q > 1 (speculative / chunked decoding) over the paged cache."""
+    from _util import clean_nan, make_paged
+    flash_attn, cuda = fa
+    g = gen(77)
+    lens = [9, 500, 128, 1031]
+    h, h_k, sq = 16, 4, 7
+    kc, vc, bt, sl = make_paged(g, lens, h_k, 64, torch.bfloat16)
+    q = randn(g, len(lens), sq, h, 128)
+    for causal in (True, False):
+        out, lse = flash_attn.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(),
+                                                      block_table=bt.cuda(), causal=causal, return_softmax_lse=True)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        for i, L in enumerate(lens):
+            ki, vi = O.gather_paged_kv(clean_nan(kc), bt[i], L)[None], O.gather_paged_kv(clean_nan(vc), bt[i], L)[None]
+            ref32, ref_lse = O.attention_ref(q[i:i + 1], ki, vi, causal=causal, out_dtype=torch.float32)
+            ref_pt, _ = O.attention_ref(q[i:i + 1], ki, vi, causal=causal, upcast=False, reorder_ops=True)
+            assert_close_to_oracle(out[i:i + 1].cpu(), ref32, ref_pt, mult=3.0, eps=2 ** -8, what=f"kvcache sq=7 seq {i}")
+            _check_lse(lse[i:i + 1].cpu(), ref_lse)
