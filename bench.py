@@ -155,11 +155,13 @@ class DecodeWorkload:
     """Paged-KV decode: batch of single-token queries over a paged pool; block_table is a seeded random
     permutation of the pool."""
 
-    def __init__(self, dev, seed, fp8=False, batch=None, lens=None, page=256):
+    def __init__(self, dev, seed, fp8=False, batch=None, lens=None, page=256, rank=0):
         import flash_attn
         self.fa = flash_attn
         self.fp8 = fp8
         self.name = "decode_fp8" if fp8 else "decode_bf16"
+        # the shapes (sequence lengths) are the same on every rank: per-GPU work is fixed under weak scaling;
+        # the values differ per rank
         cg = torch.Generator().manual_seed(seed)
         if lens is None:
             if fp8:
@@ -179,7 +181,7 @@ class DecodeWorkload:
         for i, n in enumerate(nblk.tolist()):
             bt[i, :n] = perm[p:p + n]
             p += n
-        dg = _cuda_gen(dev, seed + 1)
+        dg = _cuda_gen(dev, seed + 1 + 1000 * rank)
         dt = torch.bfloat16
         self.kc = torch.empty(pool, page, HK, D, dtype=dt, device=dev)
         self.vc = torch.empty(pool, page, HK, D, dtype=dt, device=dev)
@@ -228,7 +230,7 @@ class DecodeWorkload:
 class PrefillWorkload:
     """Packed varlen causal GQA prefill."""
 
-    def __init__(self, dev, seed, fp8=False, nseq=None):
+    def __init__(self, dev, seed, fp8=False, nseq=None, rank=0):
         import flash_attn
         self.fa = flash_attn
         self.fp8 = fp8
@@ -238,7 +240,7 @@ class PrefillWorkload:
         lens = torch.full((nseq,), 4096, dtype=torch.int64) if fp8 else torch.randint(512, 4097, (nseq,), generator=cg)
         self.lens = lens
         total = int(lens.sum())
-        dg = _cuda_gen(dev, seed + 1)
+        dg = _cuda_gen(dev, seed + 1 + 1000 * rank)
         mk = lambda h: torch.randn(total, h, D, generator=dg, device=dev, dtype=torch.float32).to(torch.bfloat16)
         q, k, v = mk(H), mk(HK), mk(HK)
         self.kw = {}
@@ -294,7 +296,7 @@ class SparseWorkload:
     """Block-sparse causal GQA prefill, one 32768-token sequence, 128x128 tile mask at 25 % density per head
     (diagonal tiles always kept)."""
 
-    def __init__(self, dev, seed, seqlen=32768, density=0.25):
+    def __init__(self, dev, seed, seqlen=32768, density=0.25, rank=0):
         import flash_attn
         self.fa = flash_attn
         self.name = "sparse_bf16"
@@ -305,7 +307,7 @@ class SparseWorkload:
         tm = (tm & tril) | torch.eye(n, dtype=torch.bool)
         cnt, offs = tile_mask_to_block_lists(tm)
         self.kept = int(tm.sum())
-        dg = _cuda_gen(dev, seed + 1)
+        dg = _cuda_gen(dev, seed + 1 + 1000 * rank)
         mk = lambda h: torch.randn(1, seqlen, h, D, generator=dg, device=dev, dtype=torch.float32).to(torch.bfloat16)
         self.q, self.k, self.v = mk(H), mk(HK), mk(HK)
         self.cnt, self.offs = cnt.to(dev), offs.to(dev)
@@ -383,15 +385,15 @@ class LongSeqWorkload:
 
 def make_workload(name, dev, seed, rank, world, scale=1.0):
     if name == "decode_bf16":
-        return DecodeWorkload(dev, seed, batch=max(1, int(64 * scale)))
+        return DecodeWorkload(dev, seed, batch=max(1, int(64 * scale)), rank=rank)
     if name == "decode_fp8":
-        return DecodeWorkload(dev, seed, fp8=True, batch=max(1, int(128 * scale)))
+        return DecodeWorkload(dev, seed, fp8=True, batch=max(1, int(128 * scale)), rank=rank)
     if name == "prefill_bf16":
-        return PrefillWorkload(dev, seed, nseq=max(1, int(16 * scale)))
+        return PrefillWorkload(dev, seed, nseq=max(1, int(16 * scale)), rank=rank)
     if name == "prefill_fp8":
-        return PrefillWorkload(dev, seed, fp8=True, nseq=max(1, int(8 * scale)))
+        return PrefillWorkload(dev, seed, fp8=True, nseq=max(1, int(8 * scale)), rank=rank)
     if name == "sparse_bf16":
-        return SparseWorkload(dev, seed)
+        return SparseWorkload(dev, seed, rank=rank)
     if name == "longseq":
         return LongSeqWorkload(dev, seed, rank, world)
     raise ValueError(name)
@@ -463,7 +465,7 @@ def time_kernel_alone(wl, steps, warmup):
 
 def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
     import flash_attn_2_cuda
-    wl = make_workload(name, dev, args.seed + 1000 * rank, rank, world, args.scale)
+    wl = make_workload(name, dev, args.seed, rank, world, args.scale)
     metric, unit, div = METRIC[wl.unit_name]
     sampler = ClockSampler(dev.index)
     with sampler as cs:
