@@ -180,6 +180,7 @@ const char* fa_b200_status_string(int s) {
     case FA_B200_ERR_ALIGN: return "pointer must be 16-byte aligned";
     case FA_B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
     case FA_B200_ERR_TOO_LARGE: return "size beyond a built-in limit";
+    case FA_B200_ERR_DEVICE_RANGE: return "a kernel skipped an out-of-range cache position, page id or rotary row";
   }
   return "unknown status";
 }
@@ -191,7 +192,7 @@ int fa_b200_device_status(void) {
   if (v != 0) {
     int zero = 0;
     cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
-    return FA_B200_ERR_DEVICE_TIMEOUT;
+    return (v & 0xffff) ? FA_B200_ERR_DEVICE_TIMEOUT : FA_B200_ERR_DEVICE_RANGE;
   }
   return FA_B200_OK;
 }
@@ -205,6 +206,68 @@ size_t fa_b200_decode_workspace_bytes(const fa_b200_decode_params* p) {
 int32_t fa_b200_decode_partition_tokens(const fa_b200_decode_params* p) {
   DecodePlan pl = plan_decode(p);
   return pl.status == FA_B200_OK ? pl.partition_tokens : 0;
+}
+
+int fa_b200_kv_append(const fa_b200_kv_append_params* p, void* stream) {
+  if (!p) return FA_B200_ERR_NULL;
+  if (p->d != kHeadDim) return FA_B200_ERR_HEADDIM;
+  if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) return FA_B200_ERR_DTYPE;
+  if (p->b < 0 || p->seqlen_new < 0 || p->seqlen_q < 0 || p->h <= 0 || p->h_k <= 0 || p->page_size <= 0 ||
+      p->num_blocks < 0 || p->max_blocks_per_seq < 0)
+    return FA_B200_ERR_SHAPE;
+  if (p->h % p->h_k != 0) return FA_B200_ERR_HEADS;
+  const int rd = p->rotary_dim;
+  if (rd < 0 || rd > kHeadDim || rd % 16 != 0) return FA_B200_ERR_SHAPE;
+  if (rd > 0 && p->dtype == FA_B200_E4M3) return FA_B200_ERR_UNSUPPORTED;
+  if (p->b == 0 || (p->seqlen_new == 0 && (rd == 0 || p->seqlen_q == 0) && !p->seqlens_out)) return FA_B200_OK;
+  if (!p->seqlens_k) return FA_B200_ERR_NULL;
+  if (p->seqlens_out == p->seqlens_k) return FA_B200_ERR_UNSUPPORTED;
+  const int es = elem_size(p->dtype);
+  // each lane moves four elements at once: 8-byte (4-byte for e4m3) alignment of every row start
+  auto ok_ptr = [&](const void* q) { return (reinterpret_cast<uintptr_t>(q) % (4 * es)) == 0; };
+  auto ok_str = [&](int64_t s) { return s >= 0 && s % 4 == 0; };
+  if (p->seqlen_new > 0) {
+    if (!p->k_new || !p->v_new || !p->k_cache || !p->v_cache || !p->block_table) return FA_B200_ERR_NULL;
+    if (!ok_ptr(p->k_new) || !ok_ptr(p->v_new) || !ok_ptr(p->k_cache) || !ok_ptr(p->v_cache)) return FA_B200_ERR_ALIGN;
+    if (!ok_str(p->k_new_batch_stride) || !ok_str(p->k_new_row_stride) || !ok_str(p->k_new_head_stride) ||
+        !ok_str(p->v_new_batch_stride) || !ok_str(p->v_new_row_stride) || !ok_str(p->v_new_head_stride) ||
+        !ok_str(p->k_block_stride) || !ok_str(p->k_row_stride) || !ok_str(p->k_head_stride) ||
+        !ok_str(p->v_block_stride) || !ok_str(p->v_row_stride) || !ok_str(p->v_head_stride))
+      return FA_B200_ERR_STRIDE;
+  }
+  if (rd > 0) {
+    if (!p->rotary_cos || !p->rotary_sin || p->seqlen_ro <= 0) return FA_B200_ERR_NULL;
+    if (!ok_ptr(p->rotary_cos) || !ok_ptr(p->rotary_sin)) return FA_B200_ERR_ALIGN;
+    if (p->seqlen_q > 0) {
+      if (!p->q || !p->q_out) return FA_B200_ERR_NULL;
+      if (!ok_ptr(p->q) || !ok_ptr(p->q_out)) return FA_B200_ERR_ALIGN;
+      if (!ok_str(p->q_batch_stride) || !ok_str(p->q_row_stride) || !ok_str(p->q_head_stride) ||
+          !ok_str(p->q_out_batch_stride) || !ok_str(p->q_out_row_stride) || !ok_str(p->q_out_head_stride))
+        return FA_B200_ERR_STRIDE;
+    }
+  }
+  KvAppendKernelParams k{};
+  k.status = status_ptr();
+  if (!k.status) return cuda_fail("fa_b200_kv_append", cudaGetLastError());
+  k.k_new = p->k_new; k.v_new = p->v_new; k.q = p->q; k.q_out = p->q_out;
+  k.k_cache = p->k_cache; k.v_cache = p->v_cache;
+  k.block_table = p->block_table; k.seqlens_k = p->seqlens_k; k.seqlens_out = p->seqlens_out;
+  k.cos = p->rotary_cos; k.sin = p->rotary_sin;
+  k.kn_b = p->k_new_batch_stride; k.kn_r = p->k_new_row_stride; k.kn_h = p->k_new_head_stride;
+  k.vn_b = p->v_new_batch_stride; k.vn_r = p->v_new_row_stride; k.vn_h = p->v_new_head_stride;
+  k.q_b = p->q_batch_stride; k.q_r = p->q_row_stride; k.q_h = p->q_head_stride;
+  k.qo_b = p->q_out_batch_stride; k.qo_r = p->q_out_row_stride; k.qo_h = p->q_out_head_stride;
+  k.kc_blk = p->k_block_stride; k.kc_row = p->k_row_stride; k.kc_h = p->k_head_stride;
+  k.vc_blk = p->v_block_stride; k.vc_row = p->v_row_stride; k.vc_h = p->v_head_stride;
+  k.bt_stride = p->block_table_batch_stride;
+  k.b = p->b; k.seqlen_q = p->seqlen_q; k.seqlen_new = p->seqlen_new; k.h = p->h; k.h_k = p->h_k;
+  k.page_size = p->page_size; k.num_blocks = p->num_blocks; k.max_blocks_per_seq = p->max_blocks_per_seq;
+  k.rotary_dim = rd; k.seqlen_ro = p->seqlen_ro; k.interleaved = p->is_rotary_interleaved ? 1 : 0;
+  k.q_per_token = p->rotate_q_per_token ? 1 : 0;
+  cudaError_t e = launch_kv_append(p->dtype, k, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("fa_b200_kv_append", e);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FA_B200_OK;
 }
 
 int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {

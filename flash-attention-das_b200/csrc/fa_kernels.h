@@ -93,4 +93,29 @@ cudaError_t launch_prefill_dense(int dtype, const CUtensorMap& tmap_q, const CUt
 cudaError_t launch_prefill_pair(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
                                 const CUtensorMap& tmap_v, const PrefillKernelParams& p, cudaStream_t stream);
 
+
+// KV-cache append + rotary embedding (one launch before the attention of a decode / chunked-prefill step).
+struct KvAppendKernelParams {
+  int* status;         // device status word
+  const void* k_new;
+  const void* v_new;
+  const void* q;
+  void* q_out;
+  void* k_cache;
+  void* v_cache;
+  const int32_t* block_table;
+  const int32_t* seqlens_k;
+  int32_t* seqlens_out;
+  const void* cos;
+  const void* sin;
+  int64_t kn_b, kn_r, kn_h, vn_b, vn_r, vn_h;
+  int64_t q_b, q_r, q_h, qo_b, qo_r, qo_h;
+  int64_t kc_blk, kc_row, kc_h, vc_blk, vc_row, vc_h;
+  int64_t bt_stride;
+  int32_t b, seqlen_q, seqlen_new, h, h_k;
+  int32_t page_size, num_blocks, max_blocks_per_seq;
+  int32_t rotary_dim, seqlen_ro, interleaved, q_per_token;
+};
+cudaError_t launch_kv_append(int dtype, const KvAppendKernelParams& p, cudaStream_t stream);
+
 }  // namespace fa

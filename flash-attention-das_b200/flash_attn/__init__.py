@@ -9,6 +9,10 @@ from .flash_attn_interface import (  # noqa: F401
     flash_attn_func,
     flash_attn_varlen_func,
     flash_attn_with_kvcache,
+    hg_flash_attn_varlen_func,
     sparse_attn_func,
+    varlen_fwd_unified,
+    vllm_flash_attn_varlen_func,
+    vllm_flash_attn_with_kvcache,
 )
 from . import split_kv_parallel  # noqa: F401,E402  (multi-GPU helpers: sharding, partial all-gather + combine)

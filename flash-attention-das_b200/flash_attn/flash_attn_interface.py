@@ -2,9 +2,9 @@
 flash_attn/flash_attn_interface.py (flash_attn_func :1646, flash_attn_varlen_func :2111,
 flash_attn_with_kvcache :2478, sparse_attn_func :2778).
 
-Forward only.  Options outside the hot path (dropout, alibi, softcap, sliding window, attention sinks, rotary,
-KV append, head dimensions other than 128, backward) raise NotImplementedError instead of silently taking
-another code path: there is no Triton, eager or CPU fallback.
+Forward only.  Options outside the hot path (dropout, alibi, softcap, sliding window, attention sinks, head
+dimensions other than 128, backward) raise NotImplementedError instead of silently taking another code path:
+there is no Triton, eager or CPU fallback.
 """
 from typing import List, Optional, Union
 
@@ -22,6 +22,18 @@ def maybe_contiguous(x):
 def _no_backward(*tensors):
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
         raise NotImplementedError("the B200 hot path is forward only: call under torch.no_grad() or detach inputs")
+
+
+def _paged_as_bshd(k, v, layout):
+    """A (num_blocks, page, nheads_k, d) view of paged pools given in the reference's layouts
+    (flash_attn_interface.py:2223-2237): "bshd" / 2 as is, "bhsd" / 1 = (num_blocks, nheads_k, page, d) permuted (no
+    copy: the kernels take strides).  "custom" / 0 stores V as (num_blocks, nheads_k, d, page)."""
+    if layout in ("bshd", 2):
+        return k, v
+    if layout in ("bhsd", 1):
+        return k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3)
+    raise NotImplementedError("paged layout 'custom' (V stored as (num_blocks, nheads_k, d, page)) is outside the B200 "
+                              "hot path of this build: use 'bshd' or 'bhsd'")
 
 
 def flash_attn_func(
@@ -89,12 +101,16 @@ def flash_attn_varlen_func(
     """Packed variable-length attention.  q: (total_q, nheads, 128); k, v: (total_k, nheads_k, 128);
     cu_seqlens_*: int32 (batch + 1).  FP8 e4m3 inputs take fp32 q/k/v_descale of one element or shape
     (batch, nheads_k) and return bf16.  softmax_lse is (nheads, total_q).
-    With `block_table` (int32 (batch, max_blocks)) k and v are paged pools (num_blocks, page_size, nheads_k, 128) and
-    `seqused_k` (int32 (batch,)) gives each sequence's number of keys; cu_seqlens_k is not used.  The kernel reads
-    the pages directly (the reference gathers them into a contiguous copy first, flash_attn_interface.py:2350-2373)."""
+    With `block_table` (int32 (batch, max_blocks)) k and v are paged pools, (num_blocks, page_size, nheads_k, 128)
+    for layout "bshd" or (num_blocks, nheads_k, page_size, 128) for "bhsd", and `seqused_k` (int32 (batch,)) gives
+    each sequence's number of keys; cu_seqlens_k is not used.  The kernel reads the pages directly, through strides,
+    whatever the layout (the reference gathers them into a contiguous copy first,
+    flash_attn_interface.py:2350-2373).  Layout "custom" (V stored transposed) is not supported."""
     _no_backward(q, k, v)
-    if block_table is not None and layout != "bshd":
-        raise NotImplementedError("paged K/V layouts other than bshd (num_blocks, page, nheads_k, d) are outside the B200 hot path")
+    if window_size is None:
+        window_size = (-1, -1)
+    if block_table is not None:
+        k, v = _paged_as_bshd(k, v, layout)
     if q_v is not None:
         raise NotImplementedError("q_v is outside the B200 hot path of this build")
     if softmax_scale is None:
@@ -160,6 +176,87 @@ def flash_attn_with_kvcache(
         alibi_slopes, out, softmax_scale, causal, window_size[0], window_size[1], softcap, rotary_interleaved,
         num_splits, s_aux, q_descale, k_descale, v_descale)
     return (out, softmax_lse) if return_softmax_lse else out
+
+
+def vllm_flash_attn_with_kvcache(
+    q,
+    k_cache,
+    v_cache,
+    k=None,
+    v=None,
+    rotary_cos=None,
+    rotary_sin=None,
+    cache_seqlens: Optional[Union[int, torch.Tensor]] = None,
+    cache_batch_idx: Optional[torch.Tensor] = None,
+    cache_leftpad: Optional[torch.Tensor] = None,
+    block_table: Optional[torch.Tensor] = None,
+    softmax_scale=None,
+    causal=False,
+    window_size=(-1, -1),
+    softcap=0.0,
+    rotary_interleaved=True,
+    alibi_slopes=None,
+    num_splits=0,
+    s_aux=None,
+    return_softmax_lse=False,
+    *,
+    q_scale=None,
+    k_scale=None,
+    v_scale=None,
+    kv_cache_dtype="auto",
+    out=None,
+    max_seqlen_k=0,
+    layout=0,
+):
+    """The reference's second paged-decode entry (flash_attn_interface.py:2633-2775): like flash_attn_with_kvcache
+    with fp32 q/k/v_scale (the e4m3 descales), an upper bound ``max_seqlen_k`` on cache_seqlens (0 = none) and the
+    pool layout as an integer: 2 = (num_blocks, page, nheads_k, d), 1 = (num_blocks, nheads_k, page, d); the
+    reference's default 0 (V transposed) is not supported.  Like the reference it returns only ``out`` and does
+    not append k / v."""
+    assert k_cache.stride(-1) == 1, "k_cache must have contiguous last dimension"
+    assert v_cache.stride(-1) == 1, "v_cache must have contiguous last dimension"
+    if k is not None or v is not None or rotary_cos is not None or rotary_sin is not None:
+        raise NotImplementedError("vllm_flash_attn_with_kvcache does not append k/v (as in the reference); use "
+                                  "flash_attn_with_kvcache")
+    if kv_cache_dtype not in ("auto", "") and not (kv_cache_dtype.startswith("fp8") and q.dtype == torch.float8_e4m3fn):
+        raise NotImplementedError("a KV cache dtype different from the query dtype is outside the B200 hot path")
+    if softcap is not None and softcap > 0.0:
+        raise ValueError("softcap is not supported by paged attention (vllm_flash_attn_with_kvcache)")
+    q = maybe_contiguous(q)
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    if cache_seqlens is not None and isinstance(cache_seqlens, int):
+        cache_seqlens = torch.full((q.shape[0],), cache_seqlens, dtype=torch.int32, device=k_cache.device)
+    k_cache, v_cache = _paged_as_bshd(k_cache, v_cache, layout)
+    out, _ = flash_attn_cuda.fwd_kvcache(
+        q, k_cache, v_cache, None, None, cache_seqlens, None, None, maybe_contiguous(cache_batch_idx), cache_leftpad,
+        maybe_contiguous(block_table), alibi_slopes, out, softmax_scale, causal, window_size[0], window_size[1], 0.0,
+        rotary_interleaved, num_splits, s_aux, q_scale, k_scale, v_scale, max_seqlen_k)
+    return out
+
+
+def vllm_flash_attn_varlen_func(q, k, v, max_seqlen_q, cu_seqlens_q, max_seqlen_k, cu_seqlens_k=None, seqused_k=None,
+                                q_v=None, dropout_p=0.0, softmax_scale=None, causal=False,
+                                window_size: Optional[List[int]] = None, softcap=0.0, alibi_slopes=None,
+                                deterministic=False, return_attn_probs=False, block_table=None,
+                                return_softmax_lse=False, out=None, is_prefix_cache=True, scheduler_metadata=None,
+                                q_descale=None, k_descale=None, v_descale=None, kv_cache_dtype="auto",
+                                fa_version: int = DEFAULT_FA_VERSION, s_aux=None):
+    """Argument order of the reference's vLLM entry (flash_attn_interface.py:2410-2475), which forwards to
+    flash_attn_varlen_func with layout "custom"; paged pools in that layout are not supported here, so with a
+    block_table this raises and without one it is flash_attn_varlen_func."""
+    return flash_attn_varlen_func(
+        q, k, v, max_seqlen_q=max_seqlen_q, cu_seqlens_q=cu_seqlens_q, max_seqlen_k=max_seqlen_k,
+        cu_seqlens_k=cu_seqlens_k, seqused_k=seqused_k, q_v=q_v, dropout_p=dropout_p, softmax_scale=softmax_scale,
+        causal=causal, window_size=window_size, softcap=softcap, alibi_slopes=alibi_slopes,
+        deterministic=deterministic, return_attn_probs=return_attn_probs, block_table=block_table,
+        return_softmax_lse=return_softmax_lse, out=out, layout="custom", scheduler_metadata=scheduler_metadata,
+        q_descale=q_descale, k_descale=k_descale, v_descale=v_descale, num_splits=0, fa_version=fa_version,
+        s_aux=s_aux)
+
+
+hg_flash_attn_varlen_func = flash_attn_varlen_func
+varlen_fwd_unified = flash_attn_varlen_func
 
 
 def sparse_attn_func(

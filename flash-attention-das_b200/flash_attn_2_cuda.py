@@ -91,6 +91,29 @@ class CombineParams(ctypes.Structure):
     ]
 
 
+class KvAppendParams(ctypes.Structure):
+    """struct fa_b200_kv_append_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("k_new", _c_vp), ("v_new", _c_vp),
+        ("k_new_batch_stride", _c_i64), ("k_new_row_stride", _c_i64), ("k_new_head_stride", _c_i64),
+        ("v_new_batch_stride", _c_i64), ("v_new_row_stride", _c_i64), ("v_new_head_stride", _c_i64),
+        ("k_cache", _c_vp), ("v_cache", _c_vp),
+        ("k_block_stride", _c_i64), ("k_row_stride", _c_i64), ("k_head_stride", _c_i64),
+        ("v_block_stride", _c_i64), ("v_row_stride", _c_i64), ("v_head_stride", _c_i64),
+        ("block_table", _c_vp), ("block_table_batch_stride", _c_i64),
+        ("seqlens_k", _c_vp), ("seqlens_out", _c_vp),
+        ("q", _c_vp), ("q_out", _c_vp),
+        ("q_batch_stride", _c_i64), ("q_row_stride", _c_i64), ("q_head_stride", _c_i64),
+        ("q_out_batch_stride", _c_i64), ("q_out_row_stride", _c_i64), ("q_out_head_stride", _c_i64),
+        ("rotary_cos", _c_vp), ("rotary_sin", _c_vp),
+        ("rotary_dim", _c_i32), ("seqlen_ro", _c_i32), ("is_rotary_interleaved", _c_i32),
+        ("rotate_q_per_token", _c_i32),
+        ("b", _c_i32), ("seqlen_q", _c_i32), ("seqlen_new", _c_i32), ("h", _c_i32), ("h_k", _c_i32), ("d", _c_i32),
+        ("page_size", _c_i32), ("num_blocks", _c_i32), ("max_blocks_per_seq", _c_i32),
+        ("dtype", _c_i32),
+    ]
+
+
 _lib.fa_b200_fwd.argtypes = [ctypes.POINTER(FwdParams), _c_vp]
 _lib.fa_b200_fwd.restype = ctypes.c_int
 _lib.fa_b200_fwd_sparse.argtypes = [ctypes.POINTER(FwdParams), _c_vp]
@@ -103,6 +126,8 @@ _lib.fa_b200_decode_workspace_bytes.argtypes = [ctypes.POINTER(DecodeParams)]
 _lib.fa_b200_decode_workspace_bytes.restype = ctypes.c_size_t
 _lib.fa_b200_decode_partition_tokens.argtypes = [ctypes.POINTER(DecodeParams)]
 _lib.fa_b200_decode_partition_tokens.restype = ctypes.c_int32
+_lib.fa_b200_kv_append.argtypes = [ctypes.POINTER(KvAppendParams), _c_vp]
+_lib.fa_b200_kv_append.restype = ctypes.c_int
 _lib.fa_b200_combine.argtypes = [ctypes.POINTER(CombineParams), _c_vp]
 _lib.fa_b200_combine.restype = ctypes.c_int
 _lib.fa_b200_status_string.argtypes = [ctypes.c_int]
@@ -412,12 +437,15 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
                 v_descale_=None, max_seqlen_k=0):
     """Attention over a paged KV cache: the decode kernel for one query token per sequence, the prefill kernel
     reading K/V through the block table for more.  Like the reference's mha_fwd_kvcache (flash_api.cpp:2530-2577) this path needs
-    ``block_table`` and ``seqlens_k`` and ignores nothing silently: the options the reference's wrapper drops
-    (new k/v append, rotary, cache_batch_idx, leftpad) raise instead.  Unlike the reference, the returned
-    softmax_lse is filled in."""
+    ``block_table`` and ``seqlens_k`` and ignores nothing silently.  New ``k_``/``v_`` are appended to the cache in
+    place at positions seqlens_k.. (keys rotated by ``rotary_cos_``/``rotary_sin_``, queries rotated into a copy) and
+    the attention then runs over seqlens_k + seqlen_new keys, the semantics the public signature documents
+    (flash_attn_interface.py:2503-2520) and the reference's wrapper drops; cache_batch_idx and cache_leftpad
+    (contiguous caches only) raise.  Unlike the reference, the returned softmax_lse is filled in."""
     _check_qkv(q, kcache, vcache)
-    _unsupported(k_ is not None or v_ is not None, "appending new k/v in the decode call")
-    _unsupported(rotary_cos_ is not None or rotary_sin_ is not None, "rotary embedding in the decode call")
+    _require((k_ is None) == (v_ is None), "k and v must be passed together")
+    _require(rotary_cos_ is None or k_ is not None, "rotary_cos/rotary_sin are only applicable if k and v are passed in")
+    _require((rotary_cos_ is None) == (rotary_sin_ is None), "rotary_cos and rotary_sin must be passed together")
     _unsupported(cache_batch_idx_ is not None, "cache_batch_idx")
     _unsupported(leftpad_k_ is not None, "cache_leftpad")
     _unsupported(alibi_slopes_ is not None, "alibi")
@@ -444,6 +472,9 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     else:
         out = torch.empty((b, sq, h, d), dtype=odt, device=q.device)
     lse = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
+    if k_ is not None:
+        q, seqlens_k_ = kv_append(q, kcache, vcache, k_, v_, seqlens_k_, block_table_, rotary_cos_, rotary_sin_,
+                                  is_rotary_interleaved, is_causal or window_size_left >= 0 or window_size_right >= 0)
     if sq > 1:
         # several query tokens per sequence (chunked prefill, speculative decoding) over the paged cache: the prefill
         # kernel reads K/V through the block table; the causal mask is bottom-right aligned to each cache length
@@ -472,6 +503,55 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
             p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
         _check(_lib.fa_b200_decode_paged(ctypes.byref(p), _stream(q)), "fwd_kvcache")
     return [out, lse]
+
+
+def kv_append(q, kcache, vcache, k_new, v_new, seqlens_k, block_table, rotary_cos=None, rotary_sin=None,
+              is_rotary_interleaved=True, rotate_q_per_token=True):
+    """Writes k_new / v_new (batch, seqlen_new, nheads_k, d) into the paged cache at positions
+    seqlens_k[b] .. seqlens_k[b] + seqlen_new - 1 (keys rotated when rotary_cos/sin (seqlen_ro, rotary_dim / 2) are
+    given) and returns (q or its rotated copy, seqlens_k + seqlen_new).  q is rotated at positions
+    seqlens_k[b] + s when ``rotate_q_per_token`` (causal or local attention), else at seqlens_k[b] for every s."""
+    b, sq, h, d = q.shape
+    _require(k_new.dim() == 4 and v_new.shape == k_new.shape, "k and v must be (batch, seqlen_new, nheads_k, d)")
+    _require(k_new.shape[0] == b and k_new.shape[2] == kcache.shape[2] and k_new.shape[3] == d,
+             "k and v must be (batch, seqlen_new, nheads_k, d)")
+    _require(k_new.dtype == kcache.dtype and v_new.dtype == vcache.dtype and k_new.is_cuda and v_new.is_cuda,
+             "Key and value must have the same dtype as the cache")
+    _require(k_new.stride(-1) == 1 and v_new.stride(-1) == 1, "Key and value must have contiguous last dimension")
+    p = KvAppendParams()
+    p.k_new, p.v_new = k_new.data_ptr(), v_new.data_ptr()
+    p.k_new_batch_stride, p.k_new_row_stride, p.k_new_head_stride = k_new.stride(0), k_new.stride(1), k_new.stride(2)
+    p.v_new_batch_stride, p.v_new_row_stride, p.v_new_head_stride = v_new.stride(0), v_new.stride(1), v_new.stride(2)
+    p.k_cache, p.v_cache = kcache.data_ptr(), vcache.data_ptr()
+    p.k_block_stride, p.k_row_stride, p.k_head_stride = kcache.stride(0), kcache.stride(1), kcache.stride(2)
+    p.v_block_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
+    p.block_table, p.block_table_batch_stride = block_table.data_ptr(), block_table.stride(0)
+    seqlens_out = torch.empty_like(seqlens_k)
+    p.seqlens_k, p.seqlens_out = seqlens_k.data_ptr(), seqlens_out.data_ptr()
+    q_out = q
+    if rotary_cos is not None:
+        _require(q.dtype in (torch.float16, torch.bfloat16), "rotary embedding needs fp16 or bf16 inputs")
+        _require(rotary_cos.dim() == 2 and rotary_sin.shape == rotary_cos.shape, "rotary_cos/sin must be (seqlen_ro, rotary_dim / 2)")
+        _require(rotary_cos.dtype == q.dtype and rotary_sin.dtype == q.dtype, "rotary_cos/sin must have the same dtype as query")
+        _require(rotary_cos.is_cuda and rotary_sin.is_cuda, "rotary_cos/sin must be on CUDA device")
+        rotary_dim = rotary_cos.shape[1] * 2
+        _require(rotary_dim <= d, "rotary_dim must be <= headdim")
+        _require(rotary_dim % 16 == 0, "Only rotary dimensions divisible by 16 are currently supported")
+        rotary_cos, rotary_sin = rotary_cos.contiguous(), rotary_sin.contiguous()
+        q_out = torch.empty((b, sq, h, d), dtype=q.dtype, device=q.device)
+        p.q, p.q_out = q.data_ptr(), q_out.data_ptr()
+        p.q_batch_stride, p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1), q.stride(2)
+        p.q_out_batch_stride, p.q_out_row_stride, p.q_out_head_stride = q_out.stride(0), q_out.stride(1), q_out.stride(2)
+        p.rotary_cos, p.rotary_sin = rotary_cos.data_ptr(), rotary_sin.data_ptr()
+        p.rotary_dim, p.seqlen_ro = rotary_dim, rotary_cos.shape[0]
+        p.is_rotary_interleaved = 1 if is_rotary_interleaved else 0
+        p.rotate_q_per_token = 1 if rotate_q_per_token else 0
+    p.b, p.seqlen_q, p.seqlen_new, p.h, p.h_k, p.d = b, sq, k_new.shape[1], h, kcache.shape[2], d
+    p.page_size, p.num_blocks, p.max_blocks_per_seq = kcache.shape[1], kcache.shape[0], block_table.shape[1]
+    p.dtype = _DT[kcache.dtype]
+    with torch.cuda.device(q.device):
+        _check(_lib.fa_b200_kv_append(ctypes.byref(p), _stream(q)), "kv_append")
+    return q_out, seqlens_out
 
 
 def decode_partial(q, kcache, vcache, seqlens_k, block_table, softmax_scale, q_descale=None, k_descale=None,

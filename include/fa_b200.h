@@ -45,7 +45,8 @@ enum {
   FA_B200_ERR_CUDA = 10,         /* a CUDA runtime / driver call failed; see fa_b200_last_cuda_error */
   FA_B200_ERR_ALIGN = 11,        /* base pointer not 16-byte aligned */
   FA_B200_ERR_DEVICE_TIMEOUT = 12, /* a bounded device-side wait gave up (reported by fa_b200_device_status) */
-  FA_B200_ERR_TOO_LARGE = 13     /* size beyond a fixed built-in limit */
+  FA_B200_ERR_TOO_LARGE = 13,    /* size beyond a fixed built-in limit */
+  FA_B200_ERR_DEVICE_RANGE = 14  /* a kernel skipped an out-of-range position or page id (fa_b200_device_status) */
 };
 
 /*
@@ -219,12 +220,66 @@ typedef struct fa_b200_combine_params {
 
 FA_B200_API int fa_b200_combine(const fa_b200_combine_params* p, void* stream);
 
+/*
+ * KV-cache append with optional rotary embedding, the first half of a decode call that is handed new keys and
+ * values: flash_attn_with_kvcache(q, k_cache, v_cache, k=, v=, rotary_cos=, rotary_sin=, cache_seqlens=,
+ * block_table=, rotary_interleaved=) (public signature flash_attn/flash_attn_interface.py:2478-2502, semantics
+ * in its docstring :2503-2520 and in the test oracle tests/test_flash_attn.py:3073-3122; the reference's
+ * mha_fwd_kvcache, csrc/flash_attn_cutlass/flash_api.cpp:2530-2577, accepts these arguments).
+ *
+ *   for each sequence b and new token s < seqlen_new:  pos = seqlens_k[b] + s
+ *     k_cache[page(b, pos)][pos % page_size] = rotary(k_new[b, s], cos[pos], sin[pos])
+ *     v_cache[page(b, pos)][pos % page_size] = v_new[b, s]
+ *   q_out[b, s] = rotary(q[b, s], cos[p], sin[p]),  p = seqlens_k[b] + s if rotate_q_per_token (causal or
+ *     local attention) else seqlens_k[b]
+ *   seqlens_out[b] = seqlens_k[b] + seqlen_new          (the lengths the attention that follows must use)
+ *
+ * rotary(x): the first rotary_dim elements of a head are rotated pairwise, (x[2i], x[2i+1]) if
+ * is_rotary_interleaved else (x[i], x[i + rotary_dim/2]):  o0 = x0 cos_i - x1 sin_i, o1 = x0 sin_i + x1 cos_i,
+ * in fp32 from the 16-bit inputs with one rounding to the element type (as flash_attn/ops/triton/rotary.py:69-90);
+ * the other elements are copied.  rotary_dim = 0 appends without rotation (q_out is then not written).
+ * E4M3 caches take the append only (rotary_dim must be 0).
+ * A position beyond max_blocks_per_seq * page_size, a page id outside [0, num_blocks) or a rotary row beyond
+ * seqlen_ro is skipped and reported by fa_b200_device_status() as FA_B200_ERR_DEVICE_RANGE.
+ * seqlens_out must not alias seqlens_k.  One kernel launch; nothing is allocated.
+ */
+typedef struct fa_b200_kv_append_params {
+  const void* k_new;                   /* (b, seqlen_new, h_k, d) */
+  const void* v_new;
+  int64_t k_new_batch_stride, k_new_row_stride, k_new_head_stride;   /* elements */
+  int64_t v_new_batch_stride, v_new_row_stride, v_new_head_stride;
+  void* k_cache;                       /* (num_blocks, page_size, h_k, d), written in place */
+  void* v_cache;
+  int64_t k_block_stride, k_row_stride, k_head_stride;
+  int64_t v_block_stride, v_row_stride, v_head_stride;
+  const int32_t* block_table;          /* (b, max_blocks_per_seq) */
+  int64_t block_table_batch_stride;
+  const int32_t* seqlens_k;            /* (b) lengths before the append */
+  int32_t* seqlens_out;                /* (b) lengths after the append; may be NULL */
+  const void* q;                       /* (b, seqlen_q, h, d); read only when rotary_dim > 0 */
+  void* q_out;                         /* (b, seqlen_q, h, d), same strides convention */
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t q_out_batch_stride, q_out_row_stride, q_out_head_stride;
+  const void* rotary_cos;              /* (seqlen_ro, rotary_dim / 2), element type of q, rows contiguous */
+  const void* rotary_sin;
+  int32_t rotary_dim;                  /* 0 or a multiple of 16, <= d */
+  int32_t seqlen_ro;
+  int32_t is_rotary_interleaved;
+  int32_t rotate_q_per_token;
+  int32_t b, seqlen_q, seqlen_new, h, h_k, d;
+  int32_t page_size, num_blocks, max_blocks_per_seq;
+  int32_t dtype;                       /* FA_B200_F16 / BF16 / E4M3 (append only) */
+} fa_b200_kv_append_params;
+
+FA_B200_API int fa_b200_kv_append(const fa_b200_kv_append_params* p, void* stream);
+
 /* Text for a status code. */
 FA_B200_API const char* fa_b200_status_string(int status);
 /* Last cudaError_t / CUresult text recorded by a failing call on this thread ("" if none). */
 FA_B200_API const char* fa_b200_last_cuda_error(void);
 /* Reads (with a device synchronise) and clears the device-side status word of the current device:
- * 0, or FA_B200_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up since the last call. */
+ * 0, FA_B200_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up since the last call, or
+ * FA_B200_ERR_DEVICE_RANGE if fa_b200_kv_append skipped an out-of-range position. */
 FA_B200_API int fa_b200_device_status(void);
 FA_B200_API int fa_b200_abi_version(void);
 /* Number of kernels this library has launched in this process (for launch accounting). */

@@ -272,3 +272,55 @@ def sparse_block_m(seqlen_q: int) -> int:
     """Host rule NUM_ROWS == ceil(Sq / (Sq <= 2048 ? 64 : 128))
     (csrc/flash_attn_cutlass/flash_api_sparse.cpp:127-137)."""
     return 64 if seqlen_q <= 2048 else 128
+
+
+# ----------------------------------------------------------------------------------------------
+# KV-cache append + rotary embedding
+# ----------------------------------------------------------------------------------------------
+def rotary_ref(x, cos, sin, seqlen_offsets, interleaved=False, per_token=True, out_dtype=None):
+    """Rotary embedding of x (batch, seqlen, nheads, d) at positions seqlen_offsets[b] + s (or
+    seqlen_offsets[b] for every s when ``per_token`` is False).  cos, sin: (seqlen_ro, rotary_dim / 2).
+    The pairing and the formula are those of rotate_half / apply_rotary_emb_torch
+    (flash_attn/layers/rotary.py:11-33); the arithmetic is that of the reference's kernel: fp32 from the
+    stored 16-bit values, ``o0 = x0*cos - x1*sin``, ``o1 = x0*sin + x1*cos``, one rounding to the element
+    type (flash_attn/ops/triton/rotary.py:69-90).  Returns ``out_dtype`` (default x.dtype)."""
+    b, s, h, d = x.shape
+    half = cos.shape[-1]
+    ro = 2 * half
+    assert ro <= d
+    pos = seqlen_offsets.to(torch.long).view(b, 1) + (torch.arange(s).view(1, s) if per_token else torch.zeros(1, s, dtype=torch.long))
+    c = cos.float()[pos].unsqueeze(2)   # (b, s, 1, half)
+    sn = sin.float()[pos].unsqueeze(2)
+    xf = x.float()
+    xr = xf[..., :ro]
+    if interleaved:
+        x0, x1 = xr[..., 0::2], xr[..., 1::2]
+    else:
+        x0, x1 = xr[..., :half], xr[..., half:]
+    o0 = x0 * c - x1 * sn
+    o1 = x0 * sn + x1 * c
+    if interleaved:
+        rot = torch.stack((o0, o1), dim=-1).reshape(b, s, h, ro)
+    else:
+        rot = torch.cat((o0, o1), dim=-1)
+    out = torch.cat((rot, xf[..., ro:]), dim=-1)
+    return out.to(out_dtype if out_dtype is not None else x.dtype)
+
+
+def kv_append_ref(k_cache, v_cache, block_table, cache_seqlens, k_new, v_new, cos=None, sin=None,
+                  interleaved=False):
+    """In-place append of k_new / v_new (batch, seqlen_new, nheads_k, d) to a paged cache
+    (num_blocks, page, nheads_k, d) at positions cache_seqlens[b] .. + seqlen_new - 1, keys rotated at
+    those positions when cos/sin are given; returns cache_seqlens + seqlen_new.  Follows the update the
+    reference's test applies to its cache copy (``update_mask`` / ``k_cache_ref[update_mask] = k_ro``,
+    tests/test_flash_attn.py:3073-3122) with the page addressing of paged_element_offset()."""
+    b, s_new = k_new.shape[0], k_new.shape[1]
+    page = k_cache.shape[1]
+    k_ro = rotary_ref(k_new, cos, sin, cache_seqlens, interleaved) if cos is not None else k_new
+    for bi in range(b):
+        for s in range(s_new):
+            pos = int(cache_seqlens[bi]) + s
+            blk = int(block_table[bi, pos // page])
+            k_cache[blk, pos % page] = k_ro[bi, s]
+            v_cache[blk, pos % page] = v_new[bi, s]
+    return (cache_seqlens + s_new).to(torch.int32)

@@ -15,6 +15,7 @@ nothing is copied.  For every case the script
 ``tests/test_oracle_golden.py`` replays the file on CPU without the reference tree.
 """
 import ast
+import math
 import os
 import sys
 import types
@@ -108,6 +109,12 @@ def gen_inputs(case):
         mx = torch.randn(nv, nh, parts, generator=g) * 6
         o = torch.randn(nv, nh, parts, d, generator=g)
         return es, mx, o
+    if kind == "rotary":
+        b, sq, h, d, rd, ro = (case[x] for x in ("b", "sq", "h", "d", "rotary_dim", "seqlen_ro"))
+        x = torch.randn(b, sq, h, d, generator=g).to(dt)
+        angle = torch.rand(ro, rd // 2, generator=g) * 2 * math.pi
+        off = torch.randint(0, ro - sq + 1, (b,), generator=g).to(torch.int32)
+        return x, torch.cos(angle).to(dt), torch.sin(angle).to(dt), off
     raise ValueError(kind)
 
 
@@ -124,6 +131,9 @@ CASES = [
     dict(name="fp8_e4m3_causal", kind="fp8", seed=8, dtype="float8_e4m3fn", b=1, sq=96, sk=96, h=4, hk=2, d=128, causal=True),
     dict(name="fp8_e4m3_decode", kind="fp8", seed=9, dtype="float8_e4m3fn", b=2, sq=1, sk=200, h=4, hk=1, d=128, causal=False),
     dict(name="merge_partials", kind="merge", seed=10, dtype="float32", nv=3, nh=4, parts=7, d=128),
+    dict(name="rotary_bf16_halves", kind="rotary", seed=11, dtype="bfloat16", b=2, sq=5, h=3, d=128, rotary_dim=128, seqlen_ro=64, interleaved=False),
+    dict(name="rotary_fp16_interleaved_partial", kind="rotary", seed=12, dtype="float16", b=3, sq=1, h=4, d=128, rotary_dim=32, seqlen_ro=40, interleaved=True),
+    dict(name="rotary_bf16_halves_partial", kind="rotary", seed=13, dtype="bfloat16", b=2, sq=7, h=2, d=128, rotary_dim=64, seqlen_ro=33, interleaved=False),
 ]
 
 
@@ -138,6 +148,12 @@ def main():
 
     glob = {"torch": torch, "OUT_OFF": 10_000_000, "MAX_OFF": 5_000_000, "D": 128}
     ref_merge = _function_from_source(os.path.join(REF, "tests", "welm", "test_welm_ops.py"), "merge", glob)
+
+    from einops import repeat
+    rglob = {"torch": torch, "rearrange": rearrange, "repeat": repeat}
+    rotary_py = os.path.join(REF, "flash_attn", "layers", "rotary.py")
+    _function_from_source(rotary_py, "rotate_half", rglob)
+    ref_rotary = _function_from_source(rotary_py, "apply_rotary_emb_torch", rglob)
 
     golden = {"torch_version": torch.__version__, "cases": []}
     for case in CASES:
@@ -203,6 +219,18 @@ def main():
             lse_part = (torch.log(es) + mx * 0.6931471805599453).permute(2, 0, 1)
             mine, _ = O.merge_partials_ref(o.permute(2, 0, 1, 3), lse_part)
             assert (mine - out).abs().max().item() < 2e-6, case["name"]
+            rec.update(out=out)
+        elif kind == "rotary":
+            x, cos, sin, off = gen_inputs(case)
+            sq = case["sq"]
+            # the reference's torch formula on the fp32 upcast of the stored values, one sequence at a time at its
+            # own offset (flash_attn/layers/rotary.py:20-33); the kernel's single rounding to the element type
+            # (flash_attn/ops/triton/rotary.py:69-90) is applied to this fp32 result by the checker
+            out = torch.cat([ref_rotary(x[i:i + 1].float(), cos[int(off[i]):int(off[i]) + sq].float(),
+                                        sin[int(off[i]):int(off[i]) + sq].float(), case["interleaved"])
+                             for i in range(case["b"])])
+            mine = O.rotary_ref(x, cos, sin, off, case["interleaved"], out_dtype=torch.float32)
+            assert torch.equal(mine, out), case["name"]
             rec.update(out=out)
         golden["cases"].append(rec)
         print("ok", case["name"])

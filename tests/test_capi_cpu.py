@@ -34,7 +34,8 @@ def test_struct_sizes_match_header(binding):
     # field counts guard against the ctypes mirrors drifting from the header
     hdr = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
     for struct, cls in (("fa_b200_fwd_params", binding.FwdParams), ("fa_b200_decode_params", binding.DecodeParams),
-                        ("fa_b200_combine_params", binding.CombineParams)):
+                        ("fa_b200_combine_params", binding.CombineParams),
+                        ("fa_b200_kv_append_params", binding.KvAppendParams)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), hdr, re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []
@@ -71,6 +72,16 @@ def test_host_validation_needs_no_gpu(binding):
     assert lib.fa_b200_decode_paged(ctypes.byref(d), None) == 4  # group of 32 > 16
     d.h = 8
     assert lib.fa_b200_decode_paged(ctypes.byref(d), None) == 1  # null pointers
+    a = binding.KvAppendParams()
+    assert lib.fa_b200_kv_append(None, None) == 1
+    a.d, a.dtype, a.b, a.seqlen_q, a.seqlen_new, a.h, a.h_k, a.page_size = 128, 1, 2, 1, 1, 8, 2, 64
+    a.rotary_dim = 24
+    assert lib.fa_b200_kv_append(ctypes.byref(a), None) == 6     # rotary_dim not a multiple of 16
+    a.rotary_dim, a.dtype = 32, 2
+    assert lib.fa_b200_kv_append(ctypes.byref(a), None) == 9     # no rotary on e4m3
+    a.dtype = 1
+    assert lib.fa_b200_kv_append(ctypes.byref(a), None) == 1     # null pointers
+    assert b"out-of-range" in lib.fa_b200_status_string(14)
 
 
 def test_partition_heuristic_and_workspace(binding):

@@ -61,6 +61,37 @@ def test_fp8_bit_exact(golden):
         assert torch.equal(out8, c["out_p8"]), c["name"]
 
 
+def test_rotary_bit_exact(golden):
+    for c in _cases(golden, "rotary"):
+        x, cos, sin, off = gen_inputs(c)
+        out = O.rotary_ref(x, cos, sin, off, c["interleaved"], out_dtype=torch.float32)
+        assert torch.equal(out, c["out"]), c["name"]
+
+
+def test_kv_append_ref_addresses_pages():
+    """The append writes exactly the rows paged_element_offset() names and nothing else."""
+    g = torch.Generator().manual_seed(5)
+    page, hk, d = 16, 2, 128
+    kc = torch.zeros(6, page, hk, d)
+    vc = torch.zeros(6, page, hk, d)
+    bt = torch.tensor([[4, 1, 0], [2, 5, 3]], dtype=torch.int32)
+    lens = torch.tensor([15, 30], dtype=torch.int32)
+    kn = torch.randn(2, 3, hk, d, generator=g)
+    vn = torch.randn(2, 3, hk, d, generator=g)
+    new_lens = O.kv_append_ref(kc, vc, bt, lens, kn, vn)
+    assert new_lens.tolist() == [18, 33]
+    flat_k, flat_v = kc.flatten(), vc.flatten()
+    touched = torch.zeros_like(flat_k, dtype=torch.bool)
+    for b in range(2):
+        for s in range(3):
+            for h in range(hk):
+                off = O.paged_element_offset(bt[b].tolist(), int(lens[b]) + s, h, 0, page, page * hk * d, hk * d, d)
+                assert torch.equal(flat_k[off:off + d], kn[b, s, h])
+                assert torch.equal(flat_v[off:off + d], vn[b, s, h])
+                touched[off:off + d] = True
+    assert flat_k[~touched].abs().sum() == 0 and flat_v[~touched].abs().sum() == 0
+
+
 def test_merge(golden):
     for c in _cases(golden, "merge"):
         es, mx, o = gen_inputs(c)

@@ -316,3 +316,37 @@ def test_kvcache_call_with_several_query_tokens(fa):
             ref_pt, _ = O.attention_ref(q[i:i + 1], ki, vi, causal=causal, upcast=False, reorder_ops=True)
             assert_close_to_oracle(out[i:i + 1].cpu(), ref32, ref_pt, mult=3.0, eps=2 ** -8, what=f"kvcache sq=7 seq {i}")
             _check_lse(lse[i:i + 1].cpu(), ref_lse)
+
+
+@pytest.mark.parametrize("page", [16, 128])
+def test_paged_layout_bhsd_gives_identical_bits(fa, page):
+    """layout "bhsd" pools (num_blocks, nheads_k, page, d) are read through strides: the same values as the bshd
+    pools, so prefill and decode outputs must be bit-identical to the bshd calls (reference layouts:
+    flash_attn_interface.py:2223-2237; vllm_flash_attn_with_kvcache layout 1 / 2, :2633-2775)."""
+    from _util import clean_nan, make_paged
+    flash_attn, cuda = fa
+    g = gen(900 + page)
+    lens_k, lens_q, h, h_k = [300, 130, 1000], [300, 2, 129], 8, 2
+    kc, vc, bt, sl = make_paged(g, lens_k, h_k, page, torch.bfloat16, poison=False)
+    q = randn(g, sum(lens_q), h, 128)
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32).cuda()
+    kc_d, vc_d = kc.cuda(), vc.cuda()
+    kc_t, vc_t = kc_d.permute(0, 2, 1, 3).contiguous(), vc_d.permute(0, 2, 1, 3).contiguous()   # real bhsd storage
+    args = dict(seqused_k=sl.cuda(), causal=True, block_table=bt.cuda())
+    o1 = flash_attn.flash_attn_varlen_func(q.cuda(), kc_d, vc_d, cq, None, max(lens_q), max(lens_k), **args)
+    o2 = flash_attn.flash_attn_varlen_func(q.cuda(), kc_t, vc_t, cq, None, max(lens_q), max(lens_k), layout="bhsd", **args)
+    assert torch.equal(o1, o2)
+    qd = randn(g, len(lens_k), 1, h, 128).cuda()
+    d1 = flash_attn.flash_attn_with_kvcache(qd, kc_d, vc_d, cache_seqlens=sl.cuda(), block_table=bt.cuda(), causal=True)
+    d2 = flash_attn.vllm_flash_attn_with_kvcache(qd, kc_t, vc_t, cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                                 causal=True, layout=1, max_seqlen_k=max(lens_k))
+    d3 = flash_attn.vllm_flash_attn_with_kvcache(qd, kc_d, vc_d, cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                                 causal=True, layout=2)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    assert torch.equal(d1, d2) and torch.equal(d1, d3)
+    ref32, _ = O.paged_decode_ref(qd.cpu(), kc, vc, sl, bt, out_dtype=torch.float32)
+    ref_pt, _ = O.paged_decode_ref(qd.cpu(), kc, vc, sl, bt, upcast=False, reorder_ops=True)
+    assert_close_to_oracle(d2.cpu(), ref32, ref_pt, mult=2.0, what="bhsd decode")
+    with pytest.raises(NotImplementedError):
+        flash_attn.vllm_flash_attn_with_kvcache(qd, kc_d, vc_d, cache_seqlens=sl.cuda(), block_table=bt.cuda(), layout=0)
