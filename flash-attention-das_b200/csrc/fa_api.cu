@@ -502,9 +502,16 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   }
   if (st != FA_B200_OK) return st;
 
+  // output map for whole-tile stores (strides and base are 16-byte aligned by the checks above)
+  CUtensorMap to;
+  st = make_tmap(&to, p->out, p->out_dtype, p->h, q_rows, nb, p->o_head_stride, p->o_row_stride,
+                 varlen ? p->o_row_stride * (q_rows > 0 ? q_rows : 1) : p->o_batch_stride, 128);
+  if (st != FA_B200_OK) return st;
+
   PrefillKernelParams k{};
   k.status = status_ptr();
   if (!k.status) return cuda_fail("status word", cudaGetLastError());
+  k.o_tma = 1;
   k.out = p->out;
   k.lse = p->softmax_lse;
   k.cu_seqlens_q = p->cu_seqlens_q;
@@ -554,7 +561,7 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     else if (!strcmp(ov, "dense") && !sparse && !paged) which = 2;
   }
   cudaError_t e = which == 2   ? launch_prefill_dense(p->dtype, tq, tk, tv, k, stream)
-                  : which == 1 ? launch_prefill_pair(p->dtype, tq, tk, tv, k, stream)
+                  : which == 1 ? launch_prefill_pair(p->dtype, tq, tk, tv, to, k, stream)
                                : launch_prefill_single(p->dtype, tq, tk, tv, k, stream);
   if (e != cudaSuccess) return cuda_fail("prefill launch", e);
   if (p->profile_stop_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_stop_event), stream);

@@ -81,6 +81,7 @@ struct PrefillKernelParams {
   int32_t out_dtype;
   int32_t num_q_blocks, nnz_s, block_m;  // sparse metadata geometry
   int32_t sparse;
+  int32_t o_tma;             // the output tensor map is valid: full 128-row tiles are stored through it
   float scale_log2;
 };
 // One 128-row query tile per CTA, two CTAs per SM: block-sparse lists and odd GQA groups.
@@ -90,8 +91,10 @@ cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tmap_q, const CU
 cudaError_t launch_prefill_dense(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
                                  const CUtensorMap& tmap_v, const PrefillKernelParams& p, cudaStream_t stream);
 // Persistent CTAs, two query heads of one GQA group per work item: dense / varlen prefill with an even group.
+// tmap_o: (d, h, rows, batch) map of the output with a (64 columns, 1, 128 rows, 1) box, used when p.o_tma is set.
 cudaError_t launch_prefill_pair(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
-                                const CUtensorMap& tmap_v, const PrefillKernelParams& p, cudaStream_t stream);
+                                const CUtensorMap& tmap_v, const CUtensorMap& tmap_o, const PrefillKernelParams& p,
+                                cudaStream_t stream);
 
 
 // KV-cache append + rotary embedding (one launch before the attention of a decode / chunked-prefill step).

@@ -362,10 +362,8 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
         float rs0 = 0.f, rs1 = 0.f;
-        // P = 2^(S * scale - m) in the input dtype, written over the head of the S buffer.  On tiles without masking
-        // a fixed share of the columns may take the polynomial path (exp2_poly) instead of the MUFU unit.
-        auto exp_store = [&](auto poly_tag) {
-          constexpr bool kPoly = decltype(poly_tag)::value;
+        // P = 2^(S * scale - m) in the input dtype, written over the head of the S buffer.
+        auto exp_store = [&]() {
           if constexpr (!T::kFp8) {
             const uint32_t t_p = tmem_base + lane_off + kColS + b * 128 + wg * (kCols / 2);
 #pragma unroll
@@ -377,7 +375,7 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
               for (int i = 0; i < 16; ++i) {
                 float x0, x1;
                 unpack_f32x2(fma_f32x2(pack_f32x2(FA_S_AT(h2 * 32 + 2 * i), FA_S_AT(h2 * 32 + 2 * i + 1)), sc2, nm2), x0, x1);
-                const float p0 = exp2_sel<kPoly>(x0, 2 * i), p1 = exp2_sel<kPoly>(x1, 2 * i + 1);
+                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                 rs2 = add_f32x2(rs2, pack_f32x2(p0, p1));
                 pk[i] = pack2(p0, p1, DT);
               }
@@ -394,10 +392,10 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
               uint32_t pk[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                const float p0 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 4 * i), scale_log2, -m_safe), 4 * i);
-                const float p1 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 4 * i + 1), scale_log2, -m_safe), 4 * i + 1);
-                const float p2 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 4 * i + 2), scale_log2, -m_safe), 4 * i + 2);
-                const float p3 = exp2_sel<kPoly>(fmaf(FA_S_AT(h2 * 32 + 4 * i + 3), scale_log2, -m_safe), 4 * i + 3);
+                const float p0 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i), scale_log2, -m_safe));
+                const float p1 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 1), scale_log2, -m_safe));
+                const float p2 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 2), scale_log2, -m_safe));
+                const float p3 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 3), scale_log2, -m_safe));
                 rs0 += p0 + p2;
                 rs1 += p1 + p3;
                 pk[i] = pack4_e4m3(p0, p1, p2, p3);
@@ -406,8 +404,7 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             }
           }
         };
-        if (masked_tile) exp_store(std::false_type{});
-        else exp_store(std::true_type{});
+        exp_store();
 #undef FA_S_AT
         l_part += rs0 + rs1;
         tmem_wait_st();

@@ -28,8 +28,9 @@ constexpr int kThreads = 32 * 12;
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr int kTmemCols = 512;
 
+constexpr int kStageBytes = 128 * 128;   // output staging per tile: 128 rows x 64 columns of a 16-bit type
 struct PairSmem {
-  int q_off, ring_off, bar_off, misc_off, total;
+  int q_off, ring_off, stage_off, bar_off, misc_off, total;
 };
 template <int DT>
 __host__ __device__ constexpr PairSmem pair_smem() {
@@ -37,7 +38,8 @@ __host__ __device__ constexpr PairSmem pair_smem() {
   PairSmem s{};
   s.q_off = 0;
   s.ring_off = 2 * T::kTileBytes;
-  s.bar_off = s.ring_off + kSlots * T::kTileBytes;
+  s.stage_off = s.ring_off + kSlots * T::kTileBytes;
+  s.bar_off = s.stage_off + 2 * kStageBytes;
   s.misc_off = s.bar_off + 8 * (12 + 2 * kSlots);
   s.total = s.misc_off + 32;
   return s;
@@ -79,7 +81,8 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
 template <int DT>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                    const __grid_constant__ CUtensorMap tmap_v, const PrefillKernelParams p) {
+                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                    const PrefillKernelParams p) {
   using T = TileTraits<DT>;
   constexpr PairSmem L = pair_smem<DT>();
   extern __shared__ uint8_t smem_raw[];
@@ -120,6 +123,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_o);
   }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(sm_tmem_base), kTmemCols);
@@ -133,6 +137,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // warpgroup (128 score registers per row live at once) grows to 208.  128 * (208 + 208 + 80) <= 65536.
   const uint32_t q_smem = smem_u32(smem + L.q_off);
   const uint32_t ring_smem = smem_u32(smem + L.ring_off);
+  const uint32_t stage_smem = smem_u32(smem + L.stage_off);
 
   if (warp >= 8) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
@@ -259,6 +264,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     uint32_t sp_cnt = 0, item_cnt = 0;
     [[maybe_unused]] int tr = 0;
     [[maybe_unused]] const bool tracer = (lane == 0 && lane_grp == 0);
+#ifdef FA_B200_PHASE_TRACE
+    uint32_t prof[5] = {0, 0, 0, 0, 0};
+#endif
     bool ok = true;
     for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
       Item it;
@@ -282,7 +290,13 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         tc_fence_after();
         if (tracer) FA_TRACE(t, tr, 2);
         const int start = j * kBlockN;
+#ifdef FA_B200_PHASE_TRACE
+        softmax_tile<DT>(t_s, t_o, scale_log2, row_limit - start, start + kBlockN > warp_limit, j == 0, st,
+                         tracer ? prof : nullptr);
+        if (tracer) ++prof[4];
+#else
         softmax_tile<DT>(t_s, t_o, scale_log2, row_limit - start, start + kBlockN > warp_limit, j == 0, st);
+#endif
         if (tracer) FA_TRACE(t, tr, 3);
         tc_fence_before();
         mbar_arrive(smem_u32(&p_full[t]));
@@ -294,27 +308,74 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       if (!mbar_wait(smem_u32(&o_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
       tc_fence_after();
       if (tracer) FA_TRACE(t, tr, 6);
-      uint32_t o[4][32];
-      tmem_ld_32x32(t_o + 0, o[0]);
-      tmem_ld_32x32(t_o + 32, o[1]);
-      tmem_ld_32x32(t_o + 64, o[2]);
-      tmem_ld_32x32(t_o + 96, o[3]);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&o_empty[t]));   // O_t may be overwritten by the next item from here on
-      ++item_cnt;
-      if (row < it.rows_valid) {
-        float vds = 1.f;
-        if (p.v_descale) vds = p.v_descale[it.bidb * p.vds_b + it.hk * p.vds_h];
-        const bool empty = !(st.l_sum > 0.f);
-        const float inv = empty ? 0.f : vds / st.l_sum;
-        uint8_t* op = out_row_ptr(p, it.coord_b, grow, head);
+      float vds = 1.f;
+      if (p.v_descale) vds = p.v_descale[it.bidb * p.vds_b + it.hk * p.vds_h];
+      const bool empty = !(st.l_sum > 0.f);
+      const float inv = empty ? 0.f : vds / st.l_sum;
+      if (p.o_tma && it.rows_valid == kBlockM) {
+        // Whole tile: O goes out as two 64-column halves through a 16 KB staging buffer (128-byte rows, 16-byte
+        // chunks XOR-swizzled by the row as the tensor map expects) and one tile store each: full 128-byte lines
+        // instead of one 16-byte piece per row and instruction.
+        const uint32_t stage = stage_smem + t * kStageBytes;
+        const uint32_t my_row = stage + row * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) store_o_chunk(op, c, o[c], inv, p.out_dtype);
-        if (p.lse)
-          p.lse[lse_index(p, it.bidb, head, grow, row_in_seq)] = empty ? INFINITY : (st.m_ref + log2f(st.l_sum)) * kLn2;
+        for (int hd = 0; hd < 2; ++hd) {
+          uint32_t o[2][32];
+          tmem_ld_32x32(t_o + hd * 64, o[0]);
+          tmem_ld_32x32(t_o + hd * 64 + 32, o[1]);
+          if (lane_grp == 0 && lane == 0) tma_store_wait_read();   // the previous store has left the buffer
+          tmem_wait_ld();
+          if (hd == 1) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&o_empty[t]));   // O_t may be overwritten by the next item from here on
+          }
+          if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+          else asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t* v = &o[c >> 2][(c & 3) * 8];
+            const uint32_t w0 = pack2(__uint_as_float(v[0]) * inv, __uint_as_float(v[1]) * inv, p.out_dtype);
+            const uint32_t w1 = pack2(__uint_as_float(v[2]) * inv, __uint_as_float(v[3]) * inv, p.out_dtype);
+            const uint32_t w2 = pack2(__uint_as_float(v[4]) * inv, __uint_as_float(v[5]) * inv, p.out_dtype);
+            const uint32_t w3 = pack2(__uint_as_float(v[6]) * inv, __uint_as_float(v[7]) * inv, p.out_dtype);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                         ::"r"(my_row + ((c ^ (row & 7)) << 4)), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+          }
+          fence_proxy_async_smem();
+          if (t == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+          else asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (lane_grp == 0 && lane == 0) {
+            tma_store_4d(&tmap_o, stage, hd * 64, head, it.q_row0 + it.m0, it.coord_b);
+            tma_store_commit();
+          }
+        }
+        ++item_cnt;
+      } else {
+        uint32_t o[4][32];
+        tmem_ld_32x32(t_o + 0, o[0]);
+        tmem_ld_32x32(t_o + 32, o[1]);
+        tmem_ld_32x32(t_o + 64, o[2]);
+        tmem_ld_32x32(t_o + 96, o[3]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&o_empty[t]));   // O_t may be overwritten by the next item from here on
+        ++item_cnt;
+        if (row < it.rows_valid) {
+          uint8_t* op = out_row_ptr(p, it.coord_b, grow, head);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) store_o_chunk(op, c, o[c], inv, p.out_dtype);
+        }
       }
+      if (row < it.rows_valid && p.lse)
+        p.lse[lse_index(p, it.bidb, head, grow, row_in_seq)] = empty ? INFINITY : (st.m_ref + log2f(st.l_sum)) * kLn2;
     }
+    if (lane_grp == 0 && lane == 0) tma_store_wait_all();   // shared memory must outlive the last store
+#ifdef FA_B200_PHASE_TRACE
+    if (tracer) {
+      tr = 900;   // the tail of the role's trace array holds the summed softmax phases
+      for (int i = 0; i < 5; ++i) FA_TRACE_VAL(t, tr, 100 + i, prof[i]);
+    }
+#endif
   }
 
   // ---- teardown
@@ -327,7 +388,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 }
 
 template <int DT>
-cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                           const PrefillKernelParams& p, cudaStream_t stream) {
   auto kern = prefill_pair_kernel<DT>;
   const size_t smem = 1024 + pair_smem<DT>().total;
@@ -346,7 +407,7 @@ cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   const long long total = static_cast<long long>(p.h / 2) * p.b * p.num_m_blocks;
   if (total <= 0) return cudaSuccess;
   const int grid = static_cast<int>(total < num_sms[dev] ? total : num_sms[dev]);
-  kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);
+  kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, p);
   return cudaGetLastError();
 }
 
@@ -359,11 +420,11 @@ extern "C" __attribute__((visibility("default"))) int fa_b200_debug_trace(long l
 #endif
 
 cudaError_t launch_prefill_pair(int dtype, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                                const PrefillKernelParams& p, cudaStream_t stream) {
+                                const CUtensorMap& to, const PrefillKernelParams& p, cudaStream_t stream) {
   switch (dtype) {
-    case FA_B200_F16: return launch_pair_t<FA_B200_F16>(tq, tk, tv, p, stream);
-    case FA_B200_BF16: return launch_pair_t<FA_B200_BF16>(tq, tk, tv, p, stream);
-    case FA_B200_E4M3: return launch_pair_t<FA_B200_E4M3>(tq, tk, tv, p, stream);
+    case FA_B200_F16: return launch_pair_t<FA_B200_F16>(tq, tk, tv, to, p, stream);
+    case FA_B200_BF16: return launch_pair_t<FA_B200_BF16>(tq, tk, tv, to, p, stream);
+    case FA_B200_E4M3: return launch_pair_t<FA_B200_E4M3>(tq, tk, tv, to, p, stream);
   }
   return cudaErrorInvalidValue;
 }
