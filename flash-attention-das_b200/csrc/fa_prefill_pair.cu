@@ -27,10 +27,21 @@ constexpr int kSlots = 4;
 constexpr int kThreads = 32 * 12;
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr int kTmemCols = 512;
+#ifndef FA_PAIR_SOFTMAX_REGS
+#define FA_PAIR_SOFTMAX_REGS 232
+#define FA_PAIR_OTHER_REGS 40
+#endif
+constexpr int kSoftmaxRegs = FA_PAIR_SOFTMAX_REGS, kOtherRegs = FA_PAIR_OTHER_REGS;
+// setmaxnreg.inc waits (without a limit) until the CTA's pool holds enough registers, and the pool is what the CTA got
+// at launch: 168 registers (the cap of a 384-thread CTA) for each of its threads.  A split that asks for more never
+// gets it and the kernel hangs.
+static_assert(128 * (2 * kSoftmaxRegs + kOtherRegs) <= 168 * kThreads, "register split exceeds the CTA's allocation");
 
 constexpr int kStageBytes = 128 * 128;   // output staging per tile: 128 rows x 64 columns of a 16-bit type
+constexpr int kItemSlots = 4;            // work items published by the producer for the other roles
+constexpr int kItemReaders = 10;         // eight softmax warps and the two MMA issuers take a copy of every item
 struct PairSmem {
-  int q_off, ring_off, stage_off, bar_off, misc_off, total;
+  int q_off, ring_off, stage_off, bar_off, item_off, misc_off, total;
 };
 template <int DT>
 __host__ __device__ constexpr PairSmem pair_smem() {
@@ -40,14 +51,17 @@ __host__ __device__ constexpr PairSmem pair_smem() {
   s.ring_off = 2 * T::kTileBytes;
   s.stage_off = s.ring_off + kSlots * T::kTileBytes;
   s.bar_off = s.stage_off + 2 * kStageBytes;
-  s.misc_off = s.bar_off + 8 * (12 + 2 * kSlots);
+  s.item_off = s.bar_off + 8 * (12 + 2 * kSlots + 2 * kItemSlots);
+  s.misc_off = s.item_off + kItemSlots * 64;
   s.total = s.misc_off + 32;
   return s;
 }
 
+// n_tiles < 0 marks the end of the CTA's work in the published item stream.
 struct Item {
-  int bidb, head0, hk, m0, rows_valid, q_row0, k_row0, sk, coord_b, n_tiles, causal_shift;
+  int bidb, head0, hk, m0, rows_valid, q_row0, k_row0, sk, coord_b, n_tiles, causal_shift, pad;
 };
+static_assert(sizeof(Item) == 48, "Item is copied through shared memory as three 16-byte words");
 
 // Virtual item L -> geometry.  false: the item does not exist (query block past the end of its sequence).
 __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, Item& it) {
@@ -96,6 +110,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint64_t* o_empty = o_full + 2;     // [2]
   uint64_t* kv_full = o_empty + 2;    // [kSlots]
   uint64_t* kv_empty = kv_full + kSlots;
+  uint64_t* item_full = kv_empty + kSlots;      // [kItemSlots]
+  uint64_t* item_empty = item_full + kItemSlots;
+  Item* item_ring = reinterpret_cast<Item*>(smem + L.item_off);   // 64-byte stride
   uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc_off + 8);
   int* issue_lock = reinterpret_cast<int*>(smem + L.misc_off + 12);   // held while one tile's MMA group is issued
@@ -119,6 +136,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(smem_u32(&kv_full[s]), 1);
       mbar_init(smem_u32(&kv_empty[s]), 2);   // released by both tiles' MMA issuers
     }
+    for (int s = 0; s < kItemSlots; ++s) {
+      mbar_init(smem_u32(&item_full[s]), 1);
+      mbar_init(smem_u32(&item_empty[s]), kItemReaders);
+    }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -133,22 +154,50 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *sm_tmem_base;
-  // Register hand-over between warpgroups: the producer/MMA warpgroup keeps 80 registers per thread, each softmax
-  // warpgroup (128 score registers per row live at once) grows to 208.  128 * (208 + 208 + 80) <= 65536.
+  // Register hand-over between warpgroups: the producer/MMA warpgroup keeps kOtherRegs registers per thread, each
+  // softmax warpgroup (128 score registers per row live at once) grows to kSoftmaxRegs.
   const uint32_t q_smem = smem_u32(smem + L.q_off);
   const uint32_t ring_smem = smem_u32(smem + L.ring_off);
   const uint32_t stage_smem = smem_u32(smem + L.stage_off);
 
+  // Work items: the producer works out each item's geometry once (integer divisions and cu_seqlens loads in rarely
+  // executed code: thousands of cycles when every role repeats them at every item boundary) and publishes it in a small
+  // shared-memory ring; the other roles take copies.
+  auto item_slot = [&](uint32_t idx) { return reinterpret_cast<Item*>(smem + L.item_off + (idx % kItemSlots) * 64); };
+  auto read_item = [&](uint32_t idx, Item& it) -> bool {
+    if (!mbar_wait(smem_u32(&item_full[idx % kItemSlots]), (idx / kItemSlots) & 1u, wctx)) return false;
+    const int4* src = reinterpret_cast<const int4*>(item_slot(idx));
+    const int4 a = src[0], b = src[1], c = src[2];
+    it.bidb = a.x; it.head0 = a.y; it.hk = a.z; it.m0 = a.w;
+    it.rows_valid = b.x; it.q_row0 = b.y; it.k_row0 = b.z; it.sk = b.w;
+    it.coord_b = c.x; it.n_tiles = c.y; it.causal_shift = c.z; it.pad = 0;
+    return true;
+  };
+  auto release_item = [&](uint32_t idx) { mbar_arrive(smem_u32(&item_empty[idx % kItemSlots])); };
+
   if (warp >= 8) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
   if (warp == kProducerWarp) {
     // ================================================================== TMA producer
     if (lane == 0) {
-      uint32_t kv_cnt = 0, item_cnt = 0;
+      uint32_t kv_cnt = 0, item_cnt = 0, pub = 0;
       bool ok = true;
+      auto publish = [&](const Item& it) -> bool {
+        const uint32_t slot = pub % kItemSlots;
+        if (!mbar_wait(smem_u32(&item_empty[slot]), ((pub / kItemSlots) & 1u) ^ 1u, wctx)) return false;
+        int4* dst = reinterpret_cast<int4*>(item_slot(pub));
+        dst[0] = make_int4(it.bidb, it.head0, it.hk, it.m0);
+        dst[1] = make_int4(it.rows_valid, it.q_row0, it.k_row0, it.sk);
+        dst[2] = make_int4(it.coord_b, it.n_tiles, it.causal_shift, 0);
+        mbar_arrive(smem_u32(&item_full[slot]));
+        ++pub;
+        return true;
+      };
       for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
         Item it;
-        if (!get_item(p, li, it) || it.n_tiles == 0) continue;
+        if (!get_item(p, li, it)) continue;
+        if (!publish(it)) { ok = false; break; }
+        if (it.n_tiles == 0) continue;
         for (int t = 0; t < 2; ++t) {
           if (!mbar_wait(smem_u32(&q_empty[t]), (item_cnt & 1u) ^ 1u, wctx)) { ok = false; break; }
           const uint32_t bar = smem_u32(&q_full[t]);
@@ -175,6 +224,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         ++item_cnt;
       }
+      if (ok) {
+        Item end{};
+        end.n_tiles = -1;
+        publish(end);
+      }
     }
   } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
     // ================================================================== MMA issuers: warp 9 feeds tile 0, warp 10 tile 1
@@ -200,9 +254,12 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         return true;
       };
       auto unlock = [&]() { __threadfence_block(); atomicExch(issue_lock, 0); };
-      for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
+      for (uint32_t idx = 0; ok; ++idx) {
         Item it;
-        if (!get_item(p, li, it) || it.n_tiles == 0) continue;
+        if (!read_item(idx, it)) { ok = false; break; }
+        release_item(idx);
+        if (it.n_tiles < 0) break;
+        if (it.n_tiles == 0) continue;
         const int n = it.n_tiles;
         {  // S_t(0) = Q_t K_0^T
           const uint32_t slot = kv_cnt % kSlots;
@@ -255,7 +312,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   }
   } else {
     // ================================================================== softmax / correction / epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int t = warp >> 2;
     const int lane_grp = warp & 3;
     const int row = lane_grp * 32 + lane;
@@ -268,23 +325,34 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     uint32_t prof[5] = {0, 0, 0, 0, 0};
 #endif
     bool ok = true;
-    for (int li = blockIdx.x; ok && li < total_items; li += gridDim.x) {
-      Item it;
-      if (!get_item(p, li, it)) continue;
-      const int head = it.head0 + t;
-      const int row_in_seq = it.m0 + row;
-      const int64_t grow = static_cast<int64_t>(it.q_row0) + row_in_seq;
-      if (it.n_tiles == 0) {
-        if (row < it.rows_valid) store_empty_row(p, it.coord_b, it.bidb, head, grow, row_in_seq);
+    for (uint32_t idx = 0; ok; ++idx) {
+      // The item stays in its ring slot until the epilogue is done: the main loop keeps only what it needs in
+      // registers (every register counts there) and the epilogue reads the rest again.
+      if (!mbar_wait(smem_u32(&item_full[idx % kItemSlots]), (idx / kItemSlots) & 1u, wctx)) { ok = false; break; }
+      const volatile Item* is = item_slot(idx);
+      const int n_tiles = is->n_tiles;
+      if (n_tiles < 0) break;
+      if (n_tiles == 0) {
+        Item it;
+        read_item(idx, it);
+        const int row_in_seq = it.m0 + row;
+        if (row < it.rows_valid)
+          store_empty_row(p, it.coord_b, it.bidb, it.head0 + t, static_cast<int64_t>(it.q_row0) + row_in_seq, row_in_seq);
+        __syncwarp();
+        if (lane == 0) release_item(idx);
         continue;
       }
-      const int row_limit = p.is_causal ? min(it.sk, row_in_seq + 1 + it.causal_shift) : it.sk;
-      const int warp_limit = p.is_causal ? min(it.sk, it.m0 + lane_grp * 32 + 1 + it.causal_shift) : it.sk;
+      int row_limit, warp_limit;
       float scale_log2 = p.scale_log2;
-      if (p.q_descale) scale_log2 *= p.q_descale[it.bidb * p.qds_b + it.hk * p.qds_h];
-      if (p.k_descale) scale_log2 *= p.k_descale[it.bidb * p.kds_b + it.hk * p.kds_h];
+      {
+        const int sk = is->sk, m0 = is->m0, shift = is->causal_shift;
+        row_limit = p.is_causal ? min(sk, m0 + row + 1 + shift) : sk;
+        warp_limit = p.is_causal ? min(sk, m0 + lane_grp * 32 + 1 + shift) : sk;
+        if (p.q_descale) scale_log2 *= p.q_descale[is->bidb * p.qds_b + is->hk * p.qds_h];
+        if (p.k_descale) scale_log2 *= p.k_descale[is->bidb * p.kds_b + is->hk * p.kds_h];
+      }
       RowState st{-INFINITY, 0.f};
-      for (int j = 0; j < it.n_tiles; ++j) {
+      for (int j = 0; j < n_tiles; ++j) {
         if (tracer) FA_TRACE(t, tr, 1);
         if (!mbar_wait(smem_u32(&s_full[t]), sp_cnt & 1u, wctx)) { ok = false; break; }
         tc_fence_after();
@@ -305,20 +373,28 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       if (!ok) break;
       if (tracer) FA_TRACE(t, tr, 5);
-      if (!mbar_wait(smem_u32(&o_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
-      tc_fence_after();
-      if (tracer) FA_TRACE(t, tr, 6);
+      // while the last product runs: what does not need O
+      Item it;
+      read_item(idx, it);
+      const int head = it.head0 + t;
+      const int row_in_seq = it.m0 + row;
+      const int64_t grow = static_cast<int64_t>(it.q_row0) + row_in_seq;
       float vds = 1.f;
       if (p.v_descale) vds = p.v_descale[it.bidb * p.vds_b + it.hk * p.vds_h];
       const bool empty = !(st.l_sum > 0.f);
       const float inv = empty ? 0.f : vds / st.l_sum;
+      if (row < it.rows_valid && p.lse)
+        p.lse[lse_index(p, it.bidb, head, grow, row_in_seq)] = empty ? INFINITY : (st.m_ref + log2f(st.l_sum)) * kLn2;
+      if (!mbar_wait(smem_u32(&o_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
+      tc_fence_after();
+      if (tracer) FA_TRACE(t, tr, 6);
       if (p.o_tma && it.rows_valid == kBlockM) {
         // Whole tile: O goes out as two 64-column halves through a 16 KB staging buffer (128-byte rows, 16-byte
         // chunks XOR-swizzled by the row as the tensor map expects) and one tile store each: full 128-byte lines
         // instead of one 16-byte piece per row and instruction.
         const uint32_t stage = stage_smem + t * kStageBytes;
         const uint32_t my_row = stage + row * 128;
-#pragma unroll
+#pragma unroll 1
         for (int hd = 0; hd < 2; ++hd) {
           uint32_t o[2][32];
           tmem_ld_32x32(t_o + hd * 64, o[0]);
@@ -366,8 +442,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           for (int c = 0; c < 4; ++c) store_o_chunk(op, c, o[c], inv, p.out_dtype);
         }
       }
-      if (row < it.rows_valid && p.lse)
-        p.lse[lse_index(p, it.bidb, head, grow, row_in_seq)] = empty ? INFINITY : (st.m_ref + log2f(st.l_sum)) * kLn2;
+      __syncwarp();
+      if (lane == 0) release_item(idx);
     }
     if (lane_grp == 0 && lane == 0) tma_store_wait_all();   // shared memory must outlive the last store
 #ifdef FA_B200_PHASE_TRACE
