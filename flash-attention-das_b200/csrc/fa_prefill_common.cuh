@@ -69,50 +69,6 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
   return lo | (hi << 16);
 }
 
-// 2^x on the FMA and integer pipes (no MUFU): round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic
-// minimax polynomial for 2^f on [-0.5, 0.5] (relative error 7.5e-5, far below the rounding of P to a 16-bit or
-// 8-bit type), and n added straight into the exponent field.  x is clamped at -125, so the result is never exactly
-// zero: use it only where every score is finite (tiles that need no masking).
-// The MUFU unit evaluates 16 ex2 per clock per SM, exactly what a 128x128 tile needs in the time the tensor pipe
-// needs for its two products; moving a share of the exponentials here takes the MUFU unit off the critical path.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(f, 0.0551708378f, 0.2426093519f);
-  p = fmaf(p, f, 0.6932609677f);
-  p = fmaf(p, f, 0.9999281764f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-// The same for two values at once on the packed fp32 pipe (fma.rn.f32x2 / add.rn.f32x2): per pair two clamps,
-// five packed operations and two shift-adds instead of two MUFU operations.
-__device__ __forceinline__ void exp2_poly_x2(uint64_t x2, float& p0, float& p1) {
-  float x0, x1;
-  unpack_f32x2(x2, x0, x1);
-#ifdef FA_POLY_FAKE
-  p0 = x0; p1 = x1;   // timing experiment only: no exponential at all
-#else
-  const uint64_t x = pack_f32x2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
-  const uint64_t t = add_f32x2(x, pack_f32x2(12582912.f, 12582912.f));
-  const uint64_t r = add_f32x2(t, pack_f32x2(-12582912.f, -12582912.f));
-  const uint64_t f = fma_f32x2(r, pack_f32x2(-1.f, -1.f), x);
-  uint64_t q = fma_f32x2(f, pack_f32x2(0.0551708378f, 0.0551708378f), pack_f32x2(0.2426093519f, 0.2426093519f));
-  q = fma_f32x2(q, f, pack_f32x2(0.6932609677f, 0.6932609677f));
-  q = fma_f32x2(q, f, pack_f32x2(0.9999281764f, 0.9999281764f));
-  float q0, q1, t0, t1;
-  unpack_f32x2(q, q0, q1);
-  unpack_f32x2(t, t0, t1);
-  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
-  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
-#endif
-}
-// Which column pairs of a 32-column chunk take the polynomial path (bit i: pair i of 16) in tiles that need no
-// masking; 0 = every exponential on the MUFU unit.
-#ifndef FA_POLY_MASK
-#define FA_POLY_MASK 0x0000u
-#endif
-constexpr uint32_t kPolyMask = FA_POLY_MASK;
-
 // ---- MMA issue sequences ---------------------------------------------------------------------------------------
 // One thread feeds the tensor pipe, and a 128x128x16 product takes only 64 cycles, so the issue path has to be a
 // handful of instructions per MMA: each sequence below is ONE asm block that derives the k-step descriptors with a
@@ -227,80 +183,6 @@ __device__ __forceinline__ void issue_pv(uint32_t p_tmem, uint32_t v_smem, uint3
   }
 }
 
-// ---- half-tile products (64 keys): the two-tile kernel splits every key tile in two so that the softmax of one half
-// overlaps the products of the other.
-//   S[:, 64h .. 64h+63] = Q K[64h .. 64h+63, :]^T   (N = 64; the K rows of the half start 64 * 128 bytes further)
-//   kPart: 0 = all k-steps, 1 = all but the last three (last one for e4m3), 2 = the remaining ones, so that the caller
-//   can pass the issue lock on while its last products are still queued.
-template <int DT, int kPart = 0>
-__device__ __forceinline__ void issue_qk_half(uint32_t q_smem, uint32_t k_smem, uint32_t s_tmem, int h) {
-  using T = TileTraits<DT>;
-  constexpr uint32_t idesc = make_idesc(T::kFormat, false, kBlockM, 64);
-  const uint64_t a0 = make_smem_desc_sw128(q_smem, 16, 1024), b0 = make_smem_desc_sw128(k_smem + h * 8192, 16, 1024);
-  const uint32_t d = s_tmem + h * 64;
-  if constexpr (T::kFp8) {
-    if constexpr (kPart != 2)
-      asm volatile(
-          "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b;\n\t"
-          "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
-          "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, pf;\n\t"
-          "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, pt;\n\t"
-          "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, pt;\n\t}"
-          ::"r"(d), "l"(a0), "l"(b0), "r"(idesc) : "memory");
-    if constexpr (kPart != 1)
-      asm volatile(
-          "{\n\t.reg .pred pt;\n\t.reg .b64 a, b;\n\t"
-          "setp.eq.b32 pt, 0, 0;\n\t"
-          "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, pt;\n\t}"
-          ::"r"(d), "l"(a0), "l"(b0), "r"(idesc) : "memory");
-  } else {
-    if constexpr (kPart != 2)
-      asm volatile(
-          "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b;\n\t"
-          "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
-          "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
-          "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-          "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-          "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-          "add.s64 a, %1, 1024;\n\tadd.s64 b, %2, 1024;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t}"
-          ::"r"(d), "l"(a0), "l"(b0), "r"(idesc) : "memory");
-    if constexpr (kPart != 1)
-      asm volatile(
-          "{\n\t.reg .pred pt;\n\t.reg .b64 a, b;\n\t"
-          "setp.eq.b32 pt, 0, 0;\n\t"
-          "add.s64 a, %1, 1026;\n\tadd.s64 b, %2, 1026;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-          "add.s64 a, %1, 1028;\n\tadd.s64 b, %2, 1028;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
-          "add.s64 a, %1, 1030;\n\tadd.s64 b, %2, 1030;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t}"
-          ::"r"(d), "l"(a0), "l"(b0), "r"(idesc) : "memory");
-  }
-}
-//   O (+)= P[:, 64h .. 64h+63] V[64h .. 64h+63, :]   (P of the half sits at the head of its S columns; the V rows of
-//   the half start 64 * 128 bytes further)
-template <int DT>
-__device__ __forceinline__ void issue_pv_half(uint32_t s_tmem, uint32_t v_smem, uint32_t o_tmem, int h, bool overwrite) {
-  using T = TileTraits<DT>;
-  const uint64_t b0 = make_smem_desc_sw128(v_smem + h * 8192, T::kHalfBytes, 1024);
-  const uint32_t p_tmem = s_tmem + h * 64;
-  const uint32_t acc0 = overwrite ? 0u : 1u;
-  if constexpr (T::kFp8) {
-    asm volatile(
-        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
-        "setp.ne.b32 pf, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, pf;\n\t"
-        "add.u32 a, %1, 8;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [a], b, %3, pt;\n\t}"
-        ::"r"(o_tmem), "r"(p_tmem), "l"(b0), "r"(T::kIdescPV), "r"(acc0) : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
-        "setp.ne.b32 pf, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pf;\n\t"
-        "add.u32 a, %1, 8;\n\tadd.s64 b, %2, 128;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
-        "add.u32 a, %1, 16;\n\tadd.s64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
-        "add.u32 a, %1, 24;\n\tadd.s64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t}"
-        ::"r"(o_tmem), "r"(p_tmem), "l"(b0), "r"(T::kIdescPV), "r"(acc0) : "memory");
-  }
-}
-
 // Running softmax state of one query row (one thread).
 struct RowState {
   float m_ref;   // reference max (scaled, log2 units) that the stored P and O are relative to
@@ -365,32 +247,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
   float rs0 = 0.f, rs1 = 0.f;
   FA_PROF(1, __float_as_uint(m_safe));
   if constexpr (!T::kFp8) {
-    if (kPolyMask != 0u && !need_mask) {
-      // every score of the tile is finite: a fixed share of the column pairs takes the polynomial path
-      const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_safe, -m_safe);
-      uint64_t rs2 = pack_f32x2(0.f, 0.f);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint64_t x2 = fma_f32x2(pack_f32x2(FA_S_AT(c * 32 + 2 * i), FA_S_AT(c * 32 + 2 * i + 1)), sc2, nm2);
-          float p0, p1;
-          if ((kPolyMask >> i) & 1u) {
-            exp2_poly_x2(x2, p0, p1);
-          } else {
-            float x0, x1;
-            unpack_f32x2(x2, x0, x1);
-            p0 = fast_exp2(x0);
-            p1 = fast_exp2(x1);
-          }
-          rs2 = add_f32x2(rs2, pack_f32x2(p0, p1));
-          pk[i] = pack2(p0, p1, DT);
-        }
-        tmem_st_32x16(t_s + c * 16, pk);
-      }
-      unpack_f32x2(rs2, rs0, rs1);
-    } else {
+    {
       const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_safe, -m_safe);
       uint64_t rs2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
@@ -430,101 +287,6 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
   FA_PROF(2, __float_as_uint(st.l_sum));
   tmem_wait_st();
   FA_PROF(3, 0);
-}
-
-// The same step for one 64-key half of a tile: S in 64 fp32 columns at t_s, P written over the head of those
-// columns.  `o_ready` is called (warp-uniformly) before O is rescaled: the caller makes sure there that no product
-// into O is still in flight.
-template <int DT, typename OReady>
-__device__ __forceinline__ void softmax_half(uint32_t t_s, uint32_t t_o, float scale_log2, int lim, bool need_mask,
-                                             bool first, RowState& st, OReady&& o_ready) {
-  using T = TileTraits<DT>;
-  uint32_t u[2][32];
-  tmem_ld_32x32(t_s + 0, u[0]);
-  tmem_ld_32x32(t_s + 32, u[1]);
-  tmem_wait_ld();
-#define FA_S_AT(idx) __uint_as_float(u[(idx) >> 5][(idx) & 31])
-  if (need_mask) {
-#pragma unroll
-    for (int c = 0; c < 64; ++c) u[c >> 5][c & 31] = (c < lim) ? u[c >> 5][c & 31] : 0xff800000u;
-  }
-  float mx0 = fmaxf(FA_S_AT(0), FA_S_AT(1)), mx1 = fmaxf(FA_S_AT(2), FA_S_AT(3));
-  float mx2 = fmaxf(FA_S_AT(4), FA_S_AT(5)), mx3 = fmaxf(FA_S_AT(6), FA_S_AT(7));
-#pragma unroll
-  for (int c = 8; c < 64; c += 8) {
-    mx0 = max3(mx0, FA_S_AT(c), FA_S_AT(c + 1));
-    mx1 = max3(mx1, FA_S_AT(c + 2), FA_S_AT(c + 3));
-    mx2 = max3(mx2, FA_S_AT(c + 4), FA_S_AT(c + 5));
-    mx3 = max3(mx3, FA_S_AT(c + 6), FA_S_AT(c + 7));
-  }
-  const float mx_scaled = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;   // scale > 0
-  if (first) {
-    st.m_ref = mx_scaled;
-  } else {
-    const bool grow = mx_scaled > st.m_ref + kRescaleThreshold;
-    if (__any_sync(0xffffffffu, grow)) {
-      const float m_new = grow ? mx_scaled : st.m_ref;
-      const float alpha = grow ? fast_exp2(st.m_ref - m_new) : 1.f;   // m_ref = -inf -> 0
-      st.l_sum *= alpha;
-      st.m_ref = m_new;
-      o_ready();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        tmem_ld_32x32(t_o + c * 32, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st_32x32(t_o + c * 32, o);
-      }
-    }
-  }
-  const float m_safe = (st.m_ref == -INFINITY) ? 0.f : st.m_ref;
-  float rs0 = 0.f, rs1 = 0.f;
-  if constexpr (!T::kFp8) {
-    const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_safe, -m_safe);
-    uint64_t rs2 = pack_f32x2(0.f, 0.f);
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint64_t x2 = fma_f32x2(pack_f32x2(FA_S_AT(c * 32 + 2 * i), FA_S_AT(c * 32 + 2 * i + 1)), sc2, nm2);
-        float p0, p1;
-        if (((kPolyMask >> i) & 1u) && !need_mask) {
-          exp2_poly_x2(x2, p0, p1);
-        } else {
-          float x0, x1;
-          unpack_f32x2(x2, x0, x1);
-          p0 = fast_exp2(x0);
-          p1 = fast_exp2(x1);
-        }
-        rs2 = add_f32x2(rs2, pack_f32x2(p0, p1));
-        pk[i] = pack2(p0, p1, DT);
-      }
-      tmem_st_32x16(t_s + c * 16, pk);
-    }
-    unpack_f32x2(rs2, rs0, rs1);
-  } else {
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t pk[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float p0 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i), scale_log2, -m_safe));
-        const float p1 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 1), scale_log2, -m_safe));
-        const float p2 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 2), scale_log2, -m_safe));
-        const float p3 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 3), scale_log2, -m_safe));
-        rs0 += p0 + p2;
-        rs1 += p1 + p3;
-        pk[i] = pack4_e4m3(p0, p1, p2, p3);
-      }
-      tmem_st_32x8(t_s + c * 8, pk);
-    }
-  }
-#undef FA_S_AT
-  st.l_sum += rs0 + rs1;
-  tmem_wait_st();
 }
 
 // Byte pointer of output row `grow`, head `head`.

@@ -180,7 +180,10 @@ def test_decode_rejects_what_the_path_does_not_do(fa):
     q = randn(g, 1, 1, 4, 128).cuda()
     with pytest.raises(ValueError):
         flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(), block_table=bt.cuda(), softcap=1.0)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(NotImplementedError):   # contiguous-cache options have no paged meaning
+        flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                           cache_batch_idx=torch.zeros(1, dtype=torch.int32, device="cuda"))
+    with pytest.raises(RuntimeError):          # new keys with the wrong number of kv heads
         flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), k=q, v=q, cache_seqlens=sl.cuda(), block_table=bt.cuda())
     with pytest.raises(RuntimeError):
         flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(), block_table=None)
