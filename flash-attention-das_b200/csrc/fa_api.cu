@@ -270,8 +270,15 @@ int fa_b200_kv_append(const fa_b200_kv_append_params* p, void* stream) {
   return FA_B200_OK;
 }
 
+namespace {
+bool sink_dtype_ok(const void* s_aux, int dtype) {
+  return !s_aux || dtype == FA_B200_F16 || dtype == FA_B200_BF16 || dtype == FA_B200_F32;
+}
+}  // namespace
+
 int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
   if (!p || !p->o_partial || !p->lse_partial) return FA_B200_ERR_NULL;
+  if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
   if (p->d != kHeadDim) return FA_B200_ERR_HEADDIM;
   if (p->rows < 0 || p->num_parts < 0 || p->h <= 0 || p->rows % p->h != 0) return FA_B200_ERR_SHAPE;
   if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16 && p->out_dtype >= 0) return FA_B200_ERR_DTYPE;
@@ -293,6 +300,8 @@ int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
   k.out_dtype = p->out_dtype;
   k.lse_empty_is_neg = 0;
   k.out_scale = p->out_scale;
+  k.s_aux = p->s_aux;
+  k.s_aux_dtype = p->s_aux_dtype;
   cudaError_t e = launch_combine(k, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("combine launch", e);
   if (p->rows > 0) g_launches++;
@@ -307,6 +316,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   if (!p->out && !p->o_partial_out) return FA_B200_ERR_NULL;
   if (p->o_partial_out && !p->lse_partial_out) return FA_B200_ERR_NULL;
   if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
+  if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
   const int es = elem_size(p->dtype);
   if (!aligned16(p->q) || !aligned16(p->k_cache) || !aligned16(p->v_cache) || (p->out && !aligned16(p->out)))
     return FA_B200_ERR_ALIGN;
@@ -354,6 +364,8 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.out_dtype = p->out_dtype;
   k.write_final = pl.split ? 0 : 1;
   k.scale_log2 = p->softmax_scale * kLog2e;
+  k.s_aux = p->s_aux;
+  k.s_aux_dtype = p->s_aux_dtype;
   if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
     k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * kHeadDim;
@@ -388,6 +400,8 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
       c.out_batch_stride = p->o_batch_stride;
       c.out_dtype = p->out_dtype;
       c.lse_empty_is_neg = 0;
+      c.s_aux = p->s_aux;   // partials handed to the caller stay without the sink: its final combine adds it
+      c.s_aux_dtype = p->s_aux_dtype;
     }
     e = launch_combine(c, stream);
     if (e != cudaSuccess) return cuda_fail("combine launch", e);
@@ -445,6 +459,7 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   if (p->d != kHeadDim) return FA_B200_ERR_HEADDIM;
   if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) return FA_B200_ERR_DTYPE;
   if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
+  if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
   if (p->b < 0 || p->h <= 0 || p->h_k <= 0 || p->seqlen_q < 0 || p->seqlen_k < 0) return FA_B200_ERR_SHAPE;
   if (p->h % p->h_k != 0) return FA_B200_ERR_HEADS;
   const bool varlen = p->cu_seqlens_q != nullptr;
@@ -512,6 +527,8 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   k.status = status_ptr();
   if (!k.status) return cuda_fail("status word", cudaGetLastError());
   k.o_tma = 1;
+  k.s_aux = p->s_aux;
+  k.s_aux_dtype = p->s_aux_dtype;
   k.out = p->out;
   k.lse = p->softmax_lse;
   k.cu_seqlens_q = p->cu_seqlens_q;

@@ -2,6 +2,7 @@
 // 128 output columns.  Partials are fp32, normalised by their own partition's softmax sum, with a
 // natural-log LSE (-inf or +inf marks a partition without keys).
 //   M = max_i lse_i;  w_i = e^{lse_i - M};  O = sum_i w_i O_i / sum_i w_i;  LSE = M + ln sum_i w_i
+// An attention sink (one logit per head) is one more term of the sum that carries no value.
 // Same result as the reference's combine (csrc/flash_attn_cutlass/src/paged_attention.h:356-445) and
 // its LSE-writing variant (csrc/flash_attn_hipc/src/flash_fwd_reduce.h:313-464).
 #include "fa_common.cuh"
@@ -50,6 +51,12 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   if (lane == 0) red_sum[warp] = sum;
   __syncthreads();
   sum = (red_sum[0] + red_sum[1]) + (red_sum[2] + red_sum[3]);
+  if (p.s_aux) {   // the attention sink of this head: one more term e^sink of the row's sum
+    const float sink = load_sink_log2(p.s_aux, p.s_aux_dtype, hi) * kLn2;
+    const float m2 = fmaxf(mx, sink);
+    sum = (mx == -INFINITY ? 0.f : sum * expf(mx - m2)) + expf(sink - m2);
+    mx = m2;
+  }
   const bool empty = !(sum > 0.f);
   const float lse_tot = empty ? 0.f : mx + logf(sum);
 

@@ -186,6 +186,28 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Attention sink of one query head, in log2 units (the logit times log2 e); -inf when sinks are off.
+__device__ __forceinline__ float load_sink_log2(const void* s_aux, int dtype, int head) {
+  if (!s_aux) return -INFINITY;
+  float v;
+  if (dtype == FA_B200_F32) v = static_cast<const float*>(s_aux)[head];
+  else if (dtype == FA_B200_BF16) v = __bfloat162float(static_cast<const __nv_bfloat16*>(s_aux)[head]);
+  else v = __half2float(static_cast<const __half*>(s_aux)[head]);
+  return v * kLog2e;
+}
+// A row's softmax statistics (reference max m and sum l relative to it, log2 units) with the sink as one more
+// term: returns the factor for the accumulated output (relative to m) and the natural-log LSE.  Rows without any
+// key (m = -inf, l = 0) get factor 0 and, with a sink, LSE = the sink.
+__device__ __forceinline__ void finish_row(float m, float l, float sink, float& inv, float& lse, bool& empty) {
+  const float M = fmaxf(m, sink);
+  if (M == -INFINITY) { inv = 0.f; lse = INFINITY; empty = true; return; }
+  const float fm = (m == -INFINITY) ? 0.f : fast_exp2(m - M);
+  const float tot = l * fm + ((sink == -INFINITY) ? 0.f : fast_exp2(sink - M));
+  empty = !(tot > 0.f);
+  inv = empty ? 0.f : fm / tot;
+  lse = empty ? INFINITY : (M + log2f(tot)) * kLn2;
+}
+
 // ------------------------------------------------------------------------------------------------
 // tcgen05 / TMEM (prefill path)
 // ------------------------------------------------------------------------------------------------

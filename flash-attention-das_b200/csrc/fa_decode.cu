@@ -361,10 +361,15 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         L += (mw == -INFINITY) ? 0.f : sm_l[w * 16 + row] * fast_exp2(mw - mg);
         acc += red[(w * 16 + row) * kHeadDim + tid];
       }
-      const bool empty = !(L > 0.f);
-      const float outv = empty ? 0.f : acc / L * vds;
-      const float lse = empty ? -INFINITY : (mg + log2f(L)) * kLn2;
       const int head = hk * group + row;
+      bool empty = !(L > 0.f);
+      float outv = empty ? 0.f : acc / L * vds;
+      float lse = empty ? -INFINITY : (mg + log2f(L)) * kLn2;
+      if (p.write_final && p.s_aux) {   // the sink is one more term of the row's sum
+        float inv;
+        finish_row(mg, L, load_sink_log2(p.s_aux, p.s_aux_dtype, head), inv, lse, empty);
+        outv = acc * inv * vds;
+      }
       if (p.write_final) {
         const int64_t oi = static_cast<int64_t>(b) * p.o_batch_stride + static_cast<int64_t>(head) * p.o_head_stride + tid;
         if (p.out_dtype == FA_B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(outv);

@@ -30,6 +30,8 @@ struct DecodeKernelParams {
   int32_t out_dtype;
   int32_t write_final;
   float scale_log2;
+  const void* s_aux;   // attention sinks (h), applied where the row is finalised (write_final only)
+  int32_t s_aux_dtype;
 };
 
 size_t decode_smem_bytes(int stages);
@@ -51,6 +53,8 @@ struct CombineKernelParams {
   int32_t out_dtype;         // FA_B200_F16 / BF16, or -1 for fp32
   int32_t lse_empty_is_neg;  // write -inf (partial convention) instead of +inf for rows with no keys
   float out_scale;
+  const void* s_aux;         // attention sinks (h): one more term of every row's sum
+  int32_t s_aux_dtype;
 };
 cudaError_t launch_combine(const CombineKernelParams& p, cudaStream_t stream);
 
@@ -83,6 +87,8 @@ struct PrefillKernelParams {
   int32_t sparse;
   int32_t o_tma;             // the output tensor map is valid: full 128-row tiles are stored through it
   float scale_log2;
+  const void* s_aux;         // attention sinks (h), applied in the epilogue
+  int32_t s_aux_dtype;
 };
 // One 128-row query tile per CTA, two CTAs per SM: block-sparse lists and odd GQA groups.
 cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,

@@ -276,8 +276,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       tc_fence_after();
       float vds = 1.f;
       if (p.v_descale) vds = p.v_descale[bidb * p.vds_b + hk * p.vds_h];
-      const bool empty = !(st.l_sum > 0.f);
-      const float inv = empty ? 0.f : vds / st.l_sum;
+      float inv, lse_row;
+      bool empty;
+      finish_row(st.m_ref, st.l_sum, load_sink_log2(p.s_aux, p.s_aux_dtype, head), inv, lse_row, empty);
+      inv *= vds;
       const int64_t grow = static_cast<int64_t>(q_row0) + row_in_seq;
       uint8_t* op = out_row_ptr(p, coord_b, grow, head);
 #pragma unroll
@@ -288,7 +290,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (row < rows_valid) store_o_chunk(op, c, o, inv, p.out_dtype);
       }
       if (p.lse && row < rows_valid)
-        p.lse[lse_index(p, bidb, head, grow, row_in_seq)] = empty ? INFINITY : (st.m_ref + log2f(st.l_sum)) * kLn2;
+        p.lse[lse_index(p, bidb, head, grow, row_in_seq)] = lse_row;
     }
   }
 

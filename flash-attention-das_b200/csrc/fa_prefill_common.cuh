@@ -312,14 +312,14 @@ __device__ __forceinline__ void store_o_chunk(uint8_t* op, int c, const uint32_t
   }
 }
 
-// A row that sees no key at all: out = 0, lse = +inf.
+// A row that sees no key at all: out = 0, lse = +inf (or the sink, the only term of its sum).
 __device__ __forceinline__ void store_empty_row(const PrefillKernelParams& p, int coord_b, int bidb, int head, int64_t grow,
                                                 int row_in_seq) {
   uint8_t* op = out_row_ptr(p, coord_b, grow, head);
   const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
   for (int i = 0; i < 16; ++i) reinterpret_cast<uint4*>(op)[i] = z;
-  if (p.lse) p.lse[lse_index(p, bidb, head, grow, row_in_seq)] = INFINITY;
+  if (p.lse) p.lse[lse_index(p, bidb, head, grow, row_in_seq)] = p.s_aux ? load_sink_log2(p.s_aux, p.s_aux_dtype, head) * kLn2 : INFINITY;
 }
 
 }  // namespace fa

@@ -284,7 +284,9 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
           for (int i = 0; i < kCols / 8; ++i) reinterpret_cast<uint4*>(op)[i] = z;
-          if (wg == 0 && p.lse) p.lse[lse_index(p, it.bidb, it.head, grow, row_in_seq)] = INFINITY;
+          if (wg == 0 && p.lse)
+            p.lse[lse_index(p, it.bidb, it.head, grow, row_in_seq)] =
+                p.s_aux ? load_sink_log2(p.s_aux, p.s_aux_dtype, it.head) * kLn2 : INFINITY;   // only the sink, if any
         }
         continue;
       }
@@ -438,13 +440,15 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (ok && row < it.rows_valid) {
         float vds = 1.f;
         if (p.v_descale) vds = p.v_descale[it.bidb * p.vds_b + it.hk * p.vds_h];
-        const bool empty = !(l_sum > 0.f);
-        const float inv = empty ? 0.f : vds / l_sum;
+        float inv, lse_row;
+        bool empty;
+        finish_row(m_ref, l_sum, load_sink_log2(p.s_aux, p.s_aux_dtype, it.head), inv, lse_row, empty);
+        inv *= vds;
         uint8_t* op = out_row_ptr(p, it.coord_b, grow, it.head) + wg * (kCols * 2);
 #pragma unroll
         for (int h2 = 0; h2 < kCols / 32; ++h2) store_o_chunk(op, h2, o[h2], inv, p.out_dtype);
         if (wg == 0 && p.lse)
-          p.lse[lse_index(p, it.bidb, it.head, grow, row_in_seq)] = empty ? INFINITY : (m_ref + log2f(l_sum)) * kLn2;
+          p.lse[lse_index(p, it.bidb, it.head, grow, row_in_seq)] = lse_row;
       }
     }
   }

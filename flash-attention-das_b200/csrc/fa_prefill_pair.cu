@@ -381,10 +381,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const int64_t grow = static_cast<int64_t>(it.q_row0) + row_in_seq;
       float vds = 1.f;
       if (p.v_descale) vds = p.v_descale[it.bidb * p.vds_b + it.hk * p.vds_h];
-      const bool empty = !(st.l_sum > 0.f);
-      const float inv = empty ? 0.f : vds / st.l_sum;
-      if (row < it.rows_valid && p.lse)
-        p.lse[lse_index(p, it.bidb, head, grow, row_in_seq)] = empty ? INFINITY : (st.m_ref + log2f(st.l_sum)) * kLn2;
+      float inv, lse_row;
+      bool empty;
+      finish_row(st.m_ref, st.l_sum, load_sink_log2(p.s_aux, p.s_aux_dtype, head), inv, lse_row, empty);
+      inv *= vds;
+      if (row < it.rows_valid && p.lse) p.lse[lse_index(p, it.bidb, head, grow, row_in_seq)] = lse_row;
       if (!mbar_wait(smem_u32(&o_full[t]), item_cnt & 1u, wctx)) { ok = false; break; }
       tc_fence_after();
       if (tracer) FA_TRACE(t, tr, 6);

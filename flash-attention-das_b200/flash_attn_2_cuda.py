@@ -55,6 +55,7 @@ class FwdParams(ctypes.Structure):
         ("profile_start_event", _c_vp), ("profile_stop_event", _c_vp),
         ("block_table", _c_vp), ("block_table_batch_stride", _c_i64), ("seqused_k", _c_vp),
         ("page_size", _c_i32), ("num_blocks", _c_i32),
+        ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
     ]
 
 
@@ -78,6 +79,7 @@ class DecodeParams(ctypes.Structure):
         ("workspace", _c_vp), ("workspace_bytes", ctypes.c_size_t),
         ("o_partial_out", _c_vp), ("lse_partial_out", _c_vp),
         ("profile_start_event", _c_vp), ("profile_stop_event", _c_vp),
+        ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
     ]
 
 
@@ -88,6 +90,7 @@ class CombineParams(ctypes.Structure):
         ("out_row_stride", _c_i64),
         ("num_parts", _c_i32), ("rows", _c_i32), ("d", _c_i32), ("h", _c_i32),
         ("parts_per_row", _c_vp), ("out_dtype", _c_i32), ("out_scale", _c_f32),
+        ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
     ]
 
 
@@ -238,6 +241,17 @@ def _set_paged(p, kcache, vcache, block_table, seqused_k, batch):
     p.page_size, p.num_blocks = kcache.shape[1], kcache.shape[0]
 
 
+def _set_sinks(p, s_aux: Optional[torch.Tensor], h: int):
+    """Attention sinks: one logit per query head, fp16 / bf16 (the reference asks for the dtype of q) or fp32."""
+    if s_aux is None:
+        return
+    _require(s_aux.is_cuda and s_aux.dim() == 1 and s_aux.numel() == h, "s_aux must have shape (nheads,)")
+    _require(s_aux.dtype in (torch.float16, torch.bfloat16, torch.float32), "s_aux must be fp16, bf16 or fp32")
+    _require(s_aux.is_contiguous(), "s_aux must be contiguous")
+    p.s_aux = s_aux.data_ptr()
+    p.s_aux_dtype = 3 if s_aux.dtype == torch.float32 else _DT[s_aux.dtype]
+
+
 def _out_dtype(q, out_):
     if out_ is not None:
         _require(out_.dtype in (torch.float16, torch.bfloat16), "Output must be fp16 or bf16")
@@ -258,7 +272,6 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     _unsupported(p_dropout != 0.0, "dropout")
     _unsupported(softcap != 0.0, "softcap")
     _unsupported(return_softmax, "return_softmax")
-    _unsupported(s_aux_ is not None, "attention sinks (s_aux)")
     _unsupported(skip_softmax_threshold_scale_factor != 0.0, "skip-softmax")
     b, sq, h, d = q.shape
     sk, h_k = k.shape[1], k.shape[2]
@@ -296,6 +309,7 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     p.softmax_scale = softmax_scale
     p.is_causal = 1 if causal else 0
     p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
+    _set_sinks(p, s_aux_, h)
     _apply_profile_events(p)
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "fwd")
@@ -320,7 +334,6 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     _unsupported(p_dropout != 0.0, "dropout")
     _unsupported(softcap != 0.0, "softcap")
     _unsupported(return_softmax, "return_softmax")
-    _unsupported(s_aux_ is not None, "attention sinks (s_aux)")
     for name, t in (("cu_seqlens_q", cu_seqlens_q),) + (() if paged else (("cu_seqlens_k", cu_seqlens_k),)):
         _require(t.dtype == torch.int32, f"{name} must have dtype int32")
         _require(t.is_cuda, f"{name} must be on CUDA device")
@@ -373,6 +386,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     _descale(p, "q_descale", q_descale_, b, h_k)
     _descale(p, "k_descale", k_descale_, b, h_k)
     _descale(p, "v_descale", v_descale_, b, h_k)
+    _set_sinks(p, s_aux_, h)
     _apply_profile_events(p)
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "varlen_fwd")
@@ -450,7 +464,6 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     _unsupported(leftpad_k_ is not None, "cache_leftpad")
     _unsupported(alibi_slopes_ is not None, "alibi")
     _unsupported(softcap != 0.0, "softcap")
-    _unsupported(s_aux_ is not None, "attention sinks (s_aux)")
     _require(block_table_ is not None, "block_table is required (paged KV cache)")
     _require(seqlens_k_ is not None, "cache_seqlens is required")
     _require(block_table_.dtype == torch.int32, "block_table must have dtype torch.int32")
@@ -491,12 +504,14 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
         _descale(fp, "k_descale", k_descale_, b, h_k)
         _descale(fp, "v_descale", v_descale_, b, h_k)
         _set_paged(fp, kcache, vcache, block_table_, seqlens_k_, b)
+        _set_sinks(fp, s_aux_, h)
         _apply_profile_events(fp)
         with torch.cuda.device(q.device):
             _check(_lib.fa_b200_fwd(ctypes.byref(fp), _stream(q)), "fwd_kvcache")
         return [out, lse]
     p = _decode_params(q, kcache, vcache, seqlens_k_, block_table_, softmax_scale, out, lse, q_descale_, k_descale_,
                        v_descale_, 0, max_seqlen_k)
+    _set_sinks(p, s_aux_, h)
     with torch.cuda.device(q.device):
         ws = _workspace(q.device, int(_lib.fa_b200_decode_workspace_bytes(ctypes.byref(p))))
         if ws is not None:
@@ -574,9 +589,9 @@ def decode_partial(q, kcache, vcache, seqlens_k, block_table, softmax_scale, q_d
     return o_part, lse_part
 
 
-def combine(o_partial, lse_partial, out_dtype=torch.bfloat16, h: Optional[int] = None, parts_per_row=None):
+def combine(o_partial, lse_partial, out_dtype=torch.bfloat16, h: Optional[int] = None, parts_per_row=None, s_aux=None):
     """LSE-combine: o_partial (parts, rows, 128) fp32, lse_partial (parts, rows) fp32 ->
-    (out (rows, 128) out_dtype, lse (rows) fp32)."""
+    (out (rows, 128) out_dtype, lse (rows) fp32).  rows = batch * h; ``s_aux`` (h) adds each head's attention sink."""
     _require(o_partial.dtype == torch.float32 and lse_partial.dtype == torch.float32, "partials must be fp32")
     _require(o_partial.is_contiguous() and lse_partial.is_contiguous(), "partials must be contiguous")
     parts, rows, d = o_partial.shape
@@ -589,6 +604,7 @@ def combine(o_partial, lse_partial, out_dtype=torch.bfloat16, h: Optional[int] =
     p.parts_per_row = _ptr(parts_per_row)
     p.out_dtype = -1 if out_dtype == torch.float32 else _DT[out_dtype]
     p.out_scale = 1.0
+    _set_sinks(p, s_aux, h or 1)
     with torch.cuda.device(o_partial.device):
         _check(_lib.fa_b200_combine(ctypes.byref(p), _stream(o_partial)), "combine")
     return out, lse

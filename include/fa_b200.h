@@ -28,7 +28,7 @@ extern "C" {
 #endif
 
 /* element types */
-enum { FA_B200_F16 = 0, FA_B200_BF16 = 1, FA_B200_E4M3 = 2 };
+enum { FA_B200_F16 = 0, FA_B200_BF16 = 1, FA_B200_E4M3 = 2, FA_B200_F32 = 3 /* s_aux only */ };
 
 /* status codes (host side).  fa_b200_status_string() gives the text. */
 enum {
@@ -105,6 +105,11 @@ typedef struct fa_b200_fwd_params {
   int64_t block_table_batch_stride;
   const int32_t* seqused_k;
   int32_t page_size, num_blocks;
+  /* Attention sinks (flash_attn_func(..., s_aux=), tests/test_flash_attn_saux.py:206-224): one extra logit per query
+   * head that takes part in the softmax denominator and carries no value; (h) elements of type s_aux_dtype
+   * (FA_B200_F16 / FA_B200_BF16, or FA_B200_F32), not multiplied by softmax_scale.  NULL = off. */
+  const void* s_aux;
+  int32_t s_aux_dtype;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch
@@ -162,6 +167,11 @@ typedef struct fa_b200_decode_params {
    * combine kernel runs after the stop event); NULL = off. */
   void* profile_start_event;
   void* profile_stop_event;
+  /* Attention sinks: as in fa_b200_fwd_params (the reference's decode adds the sink in its first partition,
+   * src/paged_attention.cu:333-335, 391-393; here it enters where the partitions are merged).  With
+   * o_partial_out set the sink is left to the caller's final fa_b200_combine. */
+  const void* s_aux;
+  int32_t s_aux_dtype;
 } fa_b200_decode_params;
 
 /* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)
@@ -216,6 +226,8 @@ typedef struct fa_b200_combine_params {
   const int32_t* parts_per_row;
   int32_t out_dtype;
   float out_scale;                     /* multiplies out (v_descale); 1.0 normally */
+  const void* s_aux;                   /* optional attention sinks, (h) elements of s_aux_dtype: one more term of the sum */
+  int32_t s_aux_dtype;
 } fa_b200_combine_params;
 
 FA_B200_API int fa_b200_combine(const fa_b200_combine_params* p, void* stream);

@@ -34,15 +34,19 @@ def causal_mask_bottom_right(seqlen_q: int, seqlen_k: int) -> torch.Tensor:
 
 def attention_ref(q, k, v, causal=False, upcast=True, reorder_ops=False, softmax_scale=None,
                   q_descale=None, k_descale=None, v_descale=None, intermediate_dtype=None,
-                  extra_mask=None, out_dtype=None):
+                  extra_mask=None, out_dtype=None, s_aux=None, window_size=(-1, -1)):
     """Fixed-length GQA attention.  Follows attention_ref (tests/test_flash_attn.py:220-321) and its
     FP8 sibling with ``[b, h]`` descales and P round-tripped through ``intermediate_dtype``
     (tests/test_flash_attn_varlen_fp8.py:214-320).
 
     q: (b, sq, h, d); k, v: (b, sk, hk, d).  ``extra_mask`` (broadcastable to (b, h, sq, sk), True =
     masked out) carries tile masks for the block-sparse oracle.
+    ``s_aux`` (h,): attention sinks, one extra logit per query head that joins the softmax as a last column
+    and is dropped afterwards; ``window_size`` (left, right): key j is visible to query i only if
+    i + sk - sq - left <= j <= i + sk - sq + right (-1 = unbounded).  Both follow the reference's sink oracle
+    (tests/test_flash_attn_saux.py:178-224).
     Returns (out in q.dtype (or fp32/bf16 for fp8 inputs, see below), lse fp32 (b, h, sq)).
-    Fully masked rows give out = 0 and lse = +inf.
+    Fully masked rows give out = 0 and lse = +inf (with sinks: lse = the sink).
     """
     dtype_og = q.dtype
     is_fp8 = dtype_og in (torch.float8_e4m3fn, torch.float8_e5m2)
@@ -67,14 +71,28 @@ def attention_ref(q, k, v, causal=False, upcast=True, reorder_ops=False, softmax
     masked = None
     if causal:
         masked = causal_mask_bottom_right(sq, sk)
+    if window_size[0] >= 0 or window_size[1] >= 0:
+        row = torch.arange(sq, dtype=torch.long).view(-1, 1)
+        col = torch.arange(sk, dtype=torch.long).view(1, -1)
+        wmask = torch.zeros(sq, sk, dtype=torch.bool)
+        if window_size[0] >= 0:
+            wmask |= col < row + sk - sq - window_size[0]
+        if window_size[1] >= 0:
+            wmask |= col > row + sk - sq + window_size[1]
+        masked = wmask if masked is None else (masked | wmask)
     if extra_mask is not None:
         masked = extra_mask if masked is None else (masked | extra_mask)
     if masked is not None:
         scores = scores.masked_fill(masked, float("-inf"))
+    if s_aux is not None:
+        sink = (s_aux.float() if (upcast or is_fp8) else s_aux).reshape(1, -1, 1, 1).expand(scores.shape[0], -1, sq, -1)
+        scores = torch.cat([scores, sink.to(scores.dtype)], dim=-1)
     attention = torch.softmax(scores, dim=-1)
-    if masked is not None:
+    if masked is not None and s_aux is None:
         all_masked = torch.all(masked.expand(scores.shape), dim=-1, keepdim=True)
         attention = attention.masked_fill(all_masked, 0.0)
+    if s_aux is not None:
+        attention = attention[..., :-1]
     attention = attention.to(v.dtype)
     if intermediate_dtype is not None:
         attention = attention.to(intermediate_dtype).to(attention.dtype)
@@ -88,7 +106,8 @@ def attention_ref(q, k, v, causal=False, upcast=True, reorder_ops=False, softmax
 
 def attention_varlen_ref(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, upcast=True,
                          softmax_scale=None, q_descale=None, k_descale=None, v_descale=None,
-                         intermediate_dtype=None, reorder_ops=False, out_dtype=None):
+                         intermediate_dtype=None, reorder_ops=False, out_dtype=None, s_aux=None,
+                         window_size=(-1, -1)):
     """Packed varlen attention, one sequence at a time.  Follows attention_varlen_ref
     (tests/test_flash_attn.py:432-494): LSE is (h, total_q) with -inf replaced by +inf and empty
     key ranges give zeros.  Descales are (batch, heads_k) fp32 or None."""
@@ -112,7 +131,7 @@ def attention_varlen_ref(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, upca
             q_descale=None if q_descale is None else q_descale[b:b + 1],
             k_descale=None if k_descale is None else k_descale[b:b + 1],
             v_descale=None if v_descale is None else v_descale[b:b + 1],
-            intermediate_dtype=intermediate_dtype)
+            intermediate_dtype=intermediate_dtype, s_aux=s_aux, window_size=window_size)
         outs.append(o[0])
         lses.append(l[0])
     return torch.cat(outs, dim=0), torch.cat(lses, dim=-1).float()
@@ -144,7 +163,7 @@ def gather_paged_kv(cache: torch.Tensor, block_table_row: torch.Tensor, seqlen: 
 
 def paged_decode_ref(q, k_cache, v_cache, cache_seqlens, block_table, softmax_scale=None,
                      causal=True, q_descale=None, k_descale=None, v_descale=None, upcast=True,
-                     reorder_ops=False, out_dtype=None):
+                     reorder_ops=False, out_dtype=None, s_aux=None, window_size=(-1, -1)):
     """Decode over a paged cache, one sequence at a time (a whole-batch call would need the GQA
     repeat of every sequence at once).  Follows the per-sequence loop of tests/test_pa.py:33-48,
     91-106 and the kvcache test (tests/test_flash_attn.py:3221-3236).
@@ -163,7 +182,7 @@ def paged_decode_ref(q, k_cache, v_cache, cache_seqlens, block_table, softmax_sc
             continue
         o, l = attention_ref(
             q[i:i + 1], ki, vi, causal=causal, softmax_scale=softmax_scale, upcast=upcast,
-            reorder_ops=reorder_ops, out_dtype=out_dtype,
+            reorder_ops=reorder_ops, out_dtype=out_dtype, s_aux=s_aux, window_size=window_size,
             q_descale=None if q_descale is None else q_descale[i:i + 1],
             k_descale=None if k_descale is None else k_descale[i:i + 1],
             v_descale=None if v_descale is None else v_descale[i:i + 1])

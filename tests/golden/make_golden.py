@@ -109,6 +109,13 @@ def gen_inputs(case):
         mx = torch.randn(nv, nh, parts, generator=g) * 6
         o = torch.randn(nv, nh, parts, d, generator=g)
         return es, mx, o
+    if kind == "sink":
+        b, sq, sk, h, hk, d = (case[x] for x in ("b", "sq", "sk", "h", "hk", "d"))
+        q = torch.randn(b, sq, h, d, generator=g).to(dt)
+        k = torch.randn(b, sk, hk, d, generator=g).to(dt)
+        v = torch.randn(b, sk, hk, d, generator=g).to(dt)
+        s_aux = (torch.randn(h, generator=g) * case["sink_scale"]).to(dt) if case["sink_scale"] > 0 else None
+        return q, k, v, s_aux
     if kind == "rotary":
         b, sq, h, d, rd, ro = (case[x] for x in ("b", "sq", "h", "d", "rotary_dim", "seqlen_ro"))
         x = torch.randn(b, sq, h, d, generator=g).to(dt)
@@ -131,6 +138,9 @@ CASES = [
     dict(name="fp8_e4m3_causal", kind="fp8", seed=8, dtype="float8_e4m3fn", b=1, sq=96, sk=96, h=4, hk=2, d=128, causal=True),
     dict(name="fp8_e4m3_decode", kind="fp8", seed=9, dtype="float8_e4m3fn", b=2, sq=1, sk=200, h=4, hk=1, d=128, causal=False),
     dict(name="merge_partials", kind="merge", seed=10, dtype="float32", nv=3, nh=4, parts=7, d=128),
+    dict(name="sink_bf16_causal_gqa", kind="sink", seed=14, dtype="bfloat16", b=2, sq=70, sk=131, h=6, hk=2, d=128, causal=True, window=(-1, -1), sink_scale=1.0),
+    dict(name="sink_fp16_window", kind="sink", seed=15, dtype="float16", b=1, sq=96, sk=96, h=4, hk=4, d=128, causal=True, window=(17, 0), sink_scale=0.5),
+    dict(name="window_bf16_noncausal_asym", kind="sink", seed=16, dtype="bfloat16", b=1, sq=64, sk=200, h=4, hk=1, d=128, causal=False, window=(30, 9), sink_scale=0.0),
     dict(name="rotary_bf16_halves", kind="rotary", seed=11, dtype="bfloat16", b=2, sq=5, h=3, d=128, rotary_dim=128, seqlen_ro=64, interleaved=False),
     dict(name="rotary_fp16_interleaved_partial", kind="rotary", seed=12, dtype="float16", b=3, sq=1, h=4, d=128, rotary_dim=32, seqlen_ro=40, interleaved=True),
     dict(name="rotary_bf16_halves_partial", kind="rotary", seed=13, dtype="bfloat16", b=2, sq=7, h=2, d=128, rotary_dim=64, seqlen_ro=33, interleaved=False),
@@ -144,6 +154,7 @@ def main():
     sys.path.insert(0, os.path.join(REF, "tests"))
     import test_flash_attn as T  # the reference's own oracle module
     import test_flash_attn_varlen_fp8 as T8
+    import test_flash_attn_saux as TS   # attention sinks + sliding window oracle
     from einops import rearrange
 
     glob = {"torch": torch, "OUT_OFF": 10_000_000, "MAX_OFF": 5_000_000, "D": 128}
@@ -220,6 +231,21 @@ def main():
             mine, _ = O.merge_partials_ref(o.permute(2, 0, 1, 3), lse_part)
             assert (mine - out).abs().max().item() < 2e-6, case["name"]
             rec.update(out=out)
+        elif kind == "sink":
+            q, k, v, s_aux = gen_inputs(case)
+            out, _ = TS.attention_ref(q, k, v, causal=case["causal"], s_aux=s_aux, window_size=tuple(case["window"]))
+            out_pt, _ = TS.attention_ref(q, k, v, causal=case["causal"], s_aux=s_aux, window_size=tuple(case["window"]),
+                                         upcast=False, reorder_ops=True)
+            mine, _ = O.attention_ref(q, k, v, causal=case["causal"], s_aux=s_aux, window_size=tuple(case["window"]))
+            mine_pt, _ = O.attention_ref(q, k, v, causal=case["causal"], s_aux=s_aux, window_size=tuple(case["window"]),
+                                         upcast=False, reorder_ops=True)
+            assert torch.equal(mine, out), case["name"]
+            # the same-dtype variant is only the error yardstick: its last product runs in the 16-bit type in the
+            # reference and in fp32 here, so it is compared by size, and the reference's figure is what is stored
+            err_ref = (out_pt.float() - out.float()).abs().max().item()
+            err_mine = (mine_pt.float() - out.float()).abs().max().item()
+            assert 0.5 * err_ref <= err_mine <= 2.0 * err_ref, (case["name"], err_ref, err_mine)
+            rec.update(out=out, err_pt=err_ref)
         elif kind == "rotary":
             x, cos, sin, off = gen_inputs(case)
             sq = case["sq"]

@@ -61,6 +61,21 @@ def test_fp8_bit_exact(golden):
         assert torch.equal(out8, c["out_p8"]), c["name"]
 
 
+def test_sink_and_window_bit_exact(golden):
+    for c in _cases(golden, "sink"):
+        q, k, v, s_aux = gen_inputs(c)
+        out, lse = O.attention_ref(q, k, v, causal=c["causal"], s_aux=s_aux, window_size=tuple(c["window"]))
+        assert torch.equal(out, c["out"]), c["name"]
+        # the sink only changes the normalisation: out * exp(lse_with - lse_without) is the sink-free result
+        if s_aux is not None:
+            out0, lse0 = O.attention_ref(q, k, v, causal=c["causal"], window_size=tuple(c["window"]), out_dtype=torch.float32)
+            out1, lse1 = O.attention_ref(q, k, v, causal=c["causal"], s_aux=s_aux, window_size=tuple(c["window"]),
+                                         out_dtype=torch.float32)
+            scale = torch.exp(lse1 - lse0).permute(0, 2, 1).unsqueeze(-1)
+            keep = torch.isfinite(lse0).permute(0, 2, 1).unsqueeze(-1)
+            assert torch.allclose(torch.where(keep, out1 * scale, out0), out0, atol=2e-6, rtol=1e-5), c["name"]
+
+
 def test_rotary_bit_exact(golden):
     for c in _cases(golden, "rotary"):
         x, cos, sin, off = gen_inputs(c)
