@@ -366,6 +366,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.scale_log2 = p->softmax_scale * kLog2e;
   k.s_aux = p->s_aux;
   k.s_aux_dtype = p->s_aux_dtype;
+  k.window_left = (p->has_window && p->window_left >= 0) ? p->window_left : -1;
   if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
     k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * kHeadDim;
@@ -544,6 +545,9 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   k.b = p->b; k.h = p->h; k.h_k = p->h_k;
   k.seqlen_q = p->seqlen_q; k.seqlen_k = p->seqlen_k;
   k.is_causal = p->is_causal ? 1 : 0;
+  k.window_left = (p->has_window && p->window_left >= 0) ? p->window_left : -1;
+  k.window_right = p->is_causal ? 0 : ((p->has_window && p->window_right >= 0) ? p->window_right : -1);
+  if (sparse && (k.window_left >= 0 || (k.window_right >= 0 && !p->is_causal))) return FA_B200_ERR_UNSUPPORTED;
   k.out_dtype = p->out_dtype;
   k.scale_log2 = p->softmax_scale * kLog2e;
   k.sparse = sparse ? 1 : 0;

@@ -71,11 +71,14 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int part = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int len = p.seqlens[b];
-  const int tok_begin = part * p.partition_tokens;
   // Partitions past the end of this sequence have nothing to do; partition 0 of an empty sequence
   // still runs to publish "no keys" (zero output, LSE marker).
-  if (tok_begin >= len && !(part == 0)) return;
-  const int tok_end = min(len, tok_begin + p.partition_tokens);
+  if (part * p.partition_tokens >= len && !(part == 0)) return;
+  const int tok_end = min(len, (part + 1) * p.partition_tokens);
+  // Sliding window: the query token (position len - 1) sees keys tok_lo .. len - 1.  A partition starts at the first
+  // tile that holds a visible key; partitions wholly before the window publish "no keys" like an empty sequence.
+  const int tok_lo = p.window_left >= 0 ? max(0, len - 1 - p.window_left) : 0;
+  const int tok_begin = max(part * p.partition_tokens, (tok_lo / T::kTile) * T::kTile);
   const int n_tiles = (tok_end > tok_begin) ? (tok_end - tok_begin + T::kTile - 1) / T::kTile : 0;
 
   if (threadIdx.x == 0) {
@@ -222,7 +225,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const bool ok = (tokb + nt * 8 + e) < tok_end;
+            const bool ok = (tokb + nt * 8 + e) < tok_end && (tokb + nt * 8 + e) >= tok_lo;
             sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
             sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
             mx0 = fmaxf(mx0, sc[nt][e]);

@@ -32,6 +32,7 @@ struct DecodeKernelParams {
   float scale_log2;
   const void* s_aux;   // attention sinks (h), applied where the row is finalised (write_final only)
   int32_t s_aux_dtype;
+  int32_t window_left; // the query token sees only its last window_left + 1 keys; -1 = all
 };
 
 size_t decode_smem_bytes(int stages);
@@ -82,6 +83,10 @@ struct PrefillKernelParams {
   int32_t b, h, h_k, seqlen_q, seqlen_k;
   int32_t num_m_blocks;      // ceil(max seqlen_q / 128)
   int32_t is_causal;
+  // Sliding window (bottom-right aligned like the causal mask): query row i of a sequence with sq queries and sk keys
+  // sees key j iff  i + sk - sq - window_left <= j <= i + sk - sq + window_right;  -1 = unbounded on that side.
+  // A causal mask is window_right = 0 (set by the host whenever is_causal is).
+  int32_t window_left, window_right;
   int32_t out_dtype;
   int32_t num_q_blocks, nnz_s, block_m;  // sparse metadata geometry
   int32_t sparse;

@@ -63,6 +63,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
   int* sm_ntiles = reinterpret_cast<int*>(smem + L.misc_off + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc_off + 8);
+  int* sm_tile0 = reinterpret_cast<int*>(smem + L.misc_off + 12);
   const WaitCtx wctx{abort_flag, p.status};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,8 +92,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   // ---- key tile list
   if (threadIdx.x == 0) {
-    int n = 0;
-    const int col_end = p.is_causal ? min(sk, m0 + rows_valid + causal_shift) : sk;
+    int n = 0, tile0 = 0;
+    const int col_end = row_hi(p, m0 + rows_valid - 1, sk, causal_shift);
     if (p.sparse) {
       // block_offset holds ascending K row offsets of 64-row tiles; two adjacent entries form one
       // 128-key tile, a lone entry is a half tile (upper 64 keys masked).  bit 31 marks a half tile.
@@ -108,9 +109,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         else { sm_tiles[n++] = o0 | (1 << 31); e += 1; }
       }
     } else {
-      n = col_end > 0 ? (col_end + kBlockN - 1) / kBlockN : 0;
+      key_tile_range(p, m0, rows_valid, sk, causal_shift, tile0, n);
     }
     *sm_ntiles = n;
+    *sm_tile0 = tile0;
     *abort_flag = 0;
     mbar_init(smem_u32(q_full), 1);
     mbar_init(smem_u32(s_full), 1);
@@ -127,6 +129,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   }
   __syncthreads();
   const int n_tiles = *sm_ntiles;
+  const int tile0 = *sm_tile0;   // first key tile of a dense sweep (a sliding window skips the tiles before it)
 
   if (n_tiles == 0) {
     // no visible key for any row of this tile
@@ -161,7 +164,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tma_load_4d(q_smem + hf * T::kHalfBytes, &tmap_q, qbar, hf * 64, head, q_row0 + m0, coord_b);
       bool ok = true;
       for (int j = 0; ok && j < n_tiles; ++j) {
-        const int start = p.sparse ? (sm_tiles[j] & 0x7fffffff) : j * kBlockN;
+        const int start = p.sparse ? (sm_tiles[j] & 0x7fffffff) : (tile0 + j) * kBlockN;
 #pragma unroll
         for (int kv = 0; kv < 2; ++kv) {
           const int item = 2 * j + kv;
@@ -234,9 +237,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16);
     const uint32_t t_o = t_s + 128;
     const int row_in_seq = m0 + row;
-    const int row_limit = p.is_causal ? min(sk, row_in_seq + 1 + causal_shift) : sk;
-    // smallest limit among this warp's rows: decides (warp-uniformly) whether a tile needs masking
-    const int warp_limit = p.is_causal ? min(sk, m0 + lane_grp * 32 + 1 + causal_shift) : sk;
+    // visible keys of this row [row_first, row_limit); the smallest limit and the largest first key among this warp's
+    // rows decide (warp-uniformly) whether a tile needs masking
+    const int row_limit = row_hi(p, row_in_seq, sk, causal_shift);
+    const int warp_limit = row_hi(p, m0 + lane_grp * 32, sk, causal_shift);
+    const int row_first = row_lo(p, row_in_seq, causal_shift);
+    const int warp_first = row_lo(p, m0 + lane_grp * 32 + 31, causal_shift);
 
     float scale_log2 = p.scale_log2;
     if (p.q_descale) scale_log2 *= p.q_descale[bidb * p.qds_b + hk * p.qds_h];
@@ -247,12 +253,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     for (int j = 0; j < n_tiles; ++j) {
       if (!mbar_wait(smem_u32(s_full), j & 1, wctx)) { ok = false; break; }
       tc_fence_after();
-      int start = j * kBlockN;
+      int start = (tile0 + j) * kBlockN;
       bool half_tile = false;
       if (p.sparse) { const int v = sm_tiles[j]; start = v & 0x7fffffff; half_tile = (v < 0); }
       int lim = row_limit - start;
       if (half_tile) lim = min(lim, 64);
-      softmax_tile<DT>(t_s, t_o, scale_log2, lim, half_tile || start + kBlockN > warp_limit, j == 0, st);
+      softmax_tile<DT>(t_s, t_o, scale_log2, row_first - start, lim,
+                       half_tile || start + kBlockN > warp_limit || start < warp_first, j == 0, st);
       if (p.paged && start + kBlockN > sk) {
         // Last tile of a paged sequence: key rows past the end were not fetched, or hold whatever the page holds
         // there.  Their P is zero, but 0 * NaN would still poison O, so this thread clears V row `row` of the tile

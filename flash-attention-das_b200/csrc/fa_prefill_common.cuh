@@ -183,6 +183,22 @@ __device__ __forceinline__ void issue_pv(uint32_t p_tmem, uint32_t v_smem, uint3
   }
 }
 
+// Visible key range of query row i (index inside its sequence): [row_lo, row_hi).
+__device__ __forceinline__ int row_hi(const PrefillKernelParams& p, int i, int sk, int shift) {
+  return p.window_right >= 0 ? min(sk, i + 1 + shift + p.window_right) : sk;
+}
+__device__ __forceinline__ int row_lo(const PrefillKernelParams& p, int i, int shift) {
+  return p.window_left >= 0 ? max(0, i + shift - p.window_left) : 0;
+}
+// Key tiles a block of query rows [m0, m0 + rows) touches: tiles tile0 .. tile0 + n_tiles - 1.
+__device__ __forceinline__ void key_tile_range(const PrefillKernelParams& p, int m0, int rows, int sk, int shift,
+                                               int& tile0, int& n_tiles) {
+  const int col_end = row_hi(p, m0 + rows - 1, sk, shift);
+  const int col_begin = min(row_lo(p, m0, shift), max(col_end, 0));
+  tile0 = col_begin / kBlockN;
+  n_tiles = col_end > col_begin ? (col_end + kBlockN - 1) / kBlockN - tile0 : 0;
+}
+
 // Running softmax state of one query row (one thread).
 struct RowState {
   float m_ref;   // reference max (scaled, log2 units) that the stored P and O are relative to
@@ -191,11 +207,11 @@ struct RowState {
 
 // One key tile for one row: S (TMEM, 128 fp32 columns at t_s) -> masked, scaled, exponentiated P written back
 // over the first columns of S in the input dtype; O (at t_o) rescaled when the row max grew past the threshold.
-//   lim        number of leading columns of this tile the row may see (<= 0: none; >= 128: all)
-//   need_mask  warp-uniform: some row of the warp has lim < 128
+//   lo, lim    the row sees columns lo <= c < lim of this tile (lo <= 0 and lim >= 128: all)
+//   need_mask  warp-uniform: some row of the warp has lim < 128 or lo > 0
 //   first      first tile of this row's sweep (O holds nothing yet)
 template <int DT>
-__device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float scale_log2, int lim, bool need_mask,
+__device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float scale_log2, int lo, int lim, bool need_mask,
                                              bool first, RowState& st, [[maybe_unused]] uint32_t* prof = nullptr) {
   using T = TileTraits<DT>;
 #ifdef FA_B200_PHASE_TRACE
@@ -211,7 +227,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
 #define FA_S_AT(idx) __uint_as_float(u[(idx) >> 5][(idx) & 31])
   if (need_mask) {
 #pragma unroll
-    for (int c = 0; c < 128; ++c) u[c >> 5][c & 31] = (c < lim) ? u[c >> 5][c & 31] : 0xff800000u;
+    for (int c = 0; c < 128; ++c) u[c >> 5][c & 31] = (c < lim && c >= lo) ? u[c >> 5][c & 31] : 0xff800000u;
   }
   float mx0 = fmaxf(FA_S_AT(0), FA_S_AT(1)), mx1 = fmaxf(FA_S_AT(2), FA_S_AT(3));
   float mx2 = fmaxf(FA_S_AT(4), FA_S_AT(5)), mx3 = fmaxf(FA_S_AT(6), FA_S_AT(7));

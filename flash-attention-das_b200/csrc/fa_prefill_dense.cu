@@ -67,7 +67,7 @@ struct RingPos {
 };
 
 struct Item {
-  int bidb, head, hk, m0, rows_valid, q_row0, k_row0, sk, coord_b, n_tiles, causal_shift;
+  int bidb, head, hk, m0, rows_valid, q_row0, k_row0, sk, coord_b, n_tiles, causal_shift, tile0;
 };
 
 // Virtual item L -> geometry.  false: the item does not exist (query block past the end of its sequence).
@@ -92,8 +92,7 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
   if (it.m0 >= sq) return false;
   it.rows_valid = min(kBlockM, sq - it.m0);
   it.causal_shift = it.sk - sq;
-  const int col_end = p.is_causal ? min(it.sk, it.m0 + it.rows_valid + it.causal_shift) : it.sk;
-  it.n_tiles = col_end > 0 ? (col_end + kBlockN - 1) / kBlockN : 0;
+  key_tile_range(p, it.m0, it.rows_valid, it.sk, it.causal_shift, it.tile0, it.n_tiles);
   return true;
 }
 
@@ -180,8 +179,8 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       for (int li = blockIdx.x; ok && next_work_item(p, li, total_items, it); li += gridDim.x) {
         ok = load_tile(&tmap_q, it.head, it.q_row0 + it.m0, it.coord_b);
         for (int j = 0; ok && j < it.n_tiles; ++j) {
-          ok = load_tile(&tmap_k, it.hk, it.k_row0 + j * kBlockN, it.coord_b) &&
-               load_tile(&tmap_v, it.hk, it.k_row0 + j * kBlockN, it.coord_b);
+          ok = load_tile(&tmap_k, it.hk, it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b) &&
+               load_tile(&tmap_v, it.hk, it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b);
         }
       }
     }
@@ -290,8 +289,12 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         continue;
       }
-      const int row_limit = p.is_causal ? min(it.sk, row_in_seq + 1 + it.causal_shift) : it.sk;
-      const int warp_limit = p.is_causal ? min(it.sk, it.m0 + lane_grp * 32 + 1 + it.causal_shift) : it.sk;
+      // visible keys of this row [row_first, row_limit) and the warp-uniform bounds that decide whether a tile needs
+      // masking at all
+      const int row_limit = row_hi(p, row_in_seq, it.sk, it.causal_shift);
+      const int warp_limit = row_hi(p, it.m0 + lane_grp * 32, it.sk, it.causal_shift);
+      const int row_first = row_lo(p, row_in_seq, it.causal_shift);
+      const int warp_first = row_lo(p, it.m0 + lane_grp * 32 + 31, it.causal_shift);
       float scale_log2 = p.scale_log2;
       if (p.q_descale) scale_log2 *= p.q_descale[it.bidb * p.qds_b + it.hk * p.qds_h];
       if (p.k_descale) scale_log2 *= p.k_descale[it.bidb * p.kds_b + it.hk * p.kds_h];
@@ -311,12 +314,12 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         for (int h2 = 0; h2 < kCols / 32; ++h2) tmem_ld_32x32(t_s + h2 * 32, u[h2]);
         tmem_wait_ld();
 #define FA_S_AT(idx) __uint_as_float(u[(idx) >> 5][(idx) & 31])
-        const int col0 = j * kBlockN + wg * kCols;
-        const bool masked_tile = col0 + kCols > warp_limit;   // warp-uniform
+        const int col0 = (it.tile0 + j) * kBlockN + wg * kCols;
+        const bool masked_tile = col0 + kCols > warp_limit || col0 < warp_first;   // warp-uniform
         if (masked_tile) {
-          const int lim = row_limit - col0;
+          const int lim = row_limit - col0, lo = row_first - col0;
 #pragma unroll
-          for (int i = 0; i < kCols; ++i) u[i >> 5][i & 31] = (i < lim) ? u[i >> 5][i & 31] : 0xff800000u;
+          for (int i = 0; i < kCols; ++i) u[i >> 5][i & 31] = (i < lim && i >= lo) ? u[i >> 5][i & 31] : 0xff800000u;
         }
         float mx0 = fmaxf(FA_S_AT(0), FA_S_AT(1)), mx1 = fmaxf(FA_S_AT(2), FA_S_AT(3));
         float mx2 = fmaxf(FA_S_AT(4), FA_S_AT(5)), mx3 = fmaxf(FA_S_AT(6), FA_S_AT(7));

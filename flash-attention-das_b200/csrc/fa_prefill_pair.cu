@@ -59,7 +59,7 @@ __host__ __device__ constexpr PairSmem pair_smem() {
 
 // n_tiles < 0 marks the end of the CTA's work in the published item stream.
 struct Item {
-  int bidb, head0, hk, m0, rows_valid, q_row0, k_row0, sk, coord_b, n_tiles, causal_shift, pad;
+  int bidb, head0, hk, m0, rows_valid, q_row0, k_row0, sk, coord_b, n_tiles, causal_shift, tile0;
 };
 static_assert(sizeof(Item) == 48, "Item is copied through shared memory as three 16-byte words");
 
@@ -87,12 +87,13 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
   if (it.m0 >= sq) return false;
   it.rows_valid = min(kBlockM, sq - it.m0);
   it.causal_shift = it.sk - sq;
-  const int col_end = p.is_causal ? min(it.sk, it.m0 + it.rows_valid + it.causal_shift) : it.sk;
-  it.n_tiles = col_end > 0 ? (col_end + kBlockN - 1) / kBlockN : 0;
+  key_tile_range(p, it.m0, it.rows_valid, it.sk, it.causal_shift, it.tile0, it.n_tiles);
   return true;
 }
 
-template <int DT>
+// kLeftWindow: the launch has a left sliding-window bound (kept out of the common build of the hot loop: two more live
+// values per softmax thread are enough to make it spill).
+template <int DT, bool kLeftWindow>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -170,7 +171,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int4 a = src[0], b = src[1], c = src[2];
     it.bidb = a.x; it.head0 = a.y; it.hk = a.z; it.m0 = a.w;
     it.rows_valid = b.x; it.q_row0 = b.y; it.k_row0 = b.z; it.sk = b.w;
-    it.coord_b = c.x; it.n_tiles = c.y; it.causal_shift = c.z; it.pad = 0;
+    it.coord_b = c.x; it.n_tiles = c.y; it.causal_shift = c.z; it.tile0 = c.w;
     return true;
   };
   auto release_item = [&](uint32_t idx) { mbar_arrive(smem_u32(&item_empty[idx % kItemSlots])); };
@@ -188,7 +189,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         int4* dst = reinterpret_cast<int4*>(item_slot(pub));
         dst[0] = make_int4(it.bidb, it.head0, it.hk, it.m0);
         dst[1] = make_int4(it.rows_valid, it.q_row0, it.k_row0, it.sk);
-        dst[2] = make_int4(it.coord_b, it.n_tiles, it.causal_shift, 0);
+        dst[2] = make_int4(it.coord_b, it.n_tiles, it.causal_shift, it.tile0);
         mbar_arrive(smem_u32(&item_full[slot]));
         ++pub;
         return true;
@@ -218,7 +219,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
             for (int hf = 0; hf < T::kHalves; ++hf)
               tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, it.hk,
-                          it.k_row0 + j * kBlockN, it.coord_b);
+                          it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b);
             ++kv_cnt;
           }
         }
@@ -342,12 +343,16 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (lane == 0) release_item(idx);
         continue;
       }
-      int row_limit, warp_limit;
+      // this row's visible keys [row_first, row_limit) and, for the warp-uniform decision whether a tile needs masking
+      // at all, the smallest limit and the largest first key among the warp's rows; all relative to the first tile
+      int row_first, row_limit, warp_first, warp_limit;
       float scale_log2 = p.scale_log2;
       {
-        const int sk = is->sk, m0 = is->m0, shift = is->causal_shift;
-        row_limit = p.is_causal ? min(sk, m0 + row + 1 + shift) : sk;
-        warp_limit = p.is_causal ? min(sk, m0 + lane_grp * 32 + 1 + shift) : sk;
+        const int sk = is->sk, m0 = is->m0, shift = is->causal_shift, base = is->tile0 * kBlockN;
+        row_limit = row_hi(p, m0 + row, sk, shift) - base;
+        warp_limit = row_hi(p, m0 + lane_grp * 32, sk, shift) - base;
+        row_first = kLeftWindow ? row_lo(p, m0 + row, shift) - base : 0;
+        warp_first = kLeftWindow ? row_lo(p, m0 + lane_grp * 32 + 31, shift) - base : 0;
         if (p.q_descale) scale_log2 *= p.q_descale[is->bidb * p.qds_b + is->hk * p.qds_h];
         if (p.k_descale) scale_log2 *= p.k_descale[is->bidb * p.kds_b + is->hk * p.kds_h];
       }
@@ -359,11 +364,13 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (tracer) FA_TRACE(t, tr, 2);
         const int start = j * kBlockN;
 #ifdef FA_B200_PHASE_TRACE
-        softmax_tile<DT>(t_s, t_o, scale_log2, row_limit - start, start + kBlockN > warp_limit, j == 0, st,
+        softmax_tile<DT>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, row_limit - start,
+                         start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st,
                          tracer ? prof : nullptr);
         if (tracer) ++prof[4];
 #else
-        softmax_tile<DT>(t_s, t_o, scale_log2, row_limit - start, start + kBlockN > warp_limit, j == 0, st);
+        softmax_tile<DT>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, row_limit - start,
+                         start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st);
 #endif
         if (tracer) FA_TRACE(t, tr, 3);
         tc_fence_before();
@@ -467,19 +474,20 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 template <int DT>
 cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                           const PrefillKernelParams& p, cudaStream_t stream) {
-  auto kern = prefill_pair_kernel<DT>;
+  const bool win = p.window_left >= 0;
+  auto kern = win ? prefill_pair_kernel<DT, true> : prefill_pair_kernel<DT, false>;
   const size_t smem = 1024 + pair_smem<DT>().total;
-  static bool attr_done[64] = {};
+  static bool attr_done[2][64] = {};
   static int num_sms[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (!attr_done[dev]) {
+  if (!attr_done[win][dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     e = cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
-    attr_done[dev] = true;
+    attr_done[win][dev] = true;
   }
   const long long total = static_cast<long long>(p.h / 2) * p.b * p.num_m_blocks;
   if (total <= 0) return cudaSuccess;

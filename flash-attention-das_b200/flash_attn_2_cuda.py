@@ -56,6 +56,7 @@ class FwdParams(ctypes.Structure):
         ("block_table", _c_vp), ("block_table_batch_stride", _c_i64), ("seqused_k", _c_vp),
         ("page_size", _c_i32), ("num_blocks", _c_i32),
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
+        ("has_window", _c_i32), ("window_left", _c_i32), ("window_right", _c_i32),
     ]
 
 
@@ -80,6 +81,7 @@ class DecodeParams(ctypes.Structure):
         ("o_partial_out", _c_vp), ("lse_partial_out", _c_vp),
         ("profile_start_event", _c_vp), ("profile_stop_event", _c_vp),
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
+        ("has_window", _c_i32), ("window_left", _c_i32),
     ]
 
 
@@ -252,6 +254,15 @@ def _set_sinks(p, s_aux: Optional[torch.Tensor], h: int):
     p.s_aux_dtype = 3 if s_aux.dtype == torch.float32 else _DT[s_aux.dtype]
 
 
+def _set_window(p, left: int, right: int):
+    """Sliding window (left, right), -1 = open side; the right side is dropped for the decode struct."""
+    if left >= 0 or right >= 0:
+        p.has_window = 1
+        p.window_left = left
+        if hasattr(p, "window_right"):
+            p.window_right = right
+
+
 def _out_dtype(q, out_):
     if out_ is not None:
         _require(out_.dtype in (torch.float16, torch.bfloat16), "Output must be fp16 or bf16")
@@ -287,8 +298,7 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
         is_causal = False
     if is_causal:
         window_size_right = 0
-    causal = window_size_left < 0 and window_size_right == 0
-    _unsupported(not causal and (window_size_left >= 0 or window_size_right >= 0), "sliding-window attention")
+    causal = window_size_right == 0   # a zero right window is the bottom-right causal mask (plus a left window, if any)
     if q.data_ptr() == k.data_ptr():
         q = q.clone()
     odt = _out_dtype(q, out_)
@@ -310,6 +320,7 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     p.is_causal = 1 if causal else 0
     p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
     _set_sinks(p, s_aux_, h)
+    _set_window(p, window_size_left, window_size_right)
     _apply_profile_events(p)
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "fwd")
@@ -352,8 +363,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
         is_causal = False
     if is_causal:
         window_size_right = 0
-    causal = window_size_left < 0 and window_size_right == 0
-    _unsupported(not causal and (window_size_left >= 0 or window_size_right >= 0), "sliding-window attention")
+    causal = window_size_right == 0
     if q.data_ptr() == k.data_ptr():
         q = q.clone()
     odt = _out_dtype(q, out_)
@@ -387,6 +397,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     _descale(p, "k_descale", k_descale_, b, h_k)
     _descale(p, "v_descale", v_descale_, b, h_k)
     _set_sinks(p, s_aux_, h)
+    _set_window(p, window_size_left, window_size_right)
     _apply_profile_events(p)
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "varlen_fwd")
@@ -471,8 +482,6 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     _require(seqlens_k_.dtype == torch.int32, "seqlens_k must have dtype int32")
     _require(seqlens_k_.is_contiguous(), "seqlens_k must be contiguous")
     b, sq, h, d = q.shape
-    _unsupported(window_size_left >= 0 and window_size_left < kcache.shape[1] * block_table_.shape[1],
-                 "sliding-window attention")
     _require(seqlens_k_.numel() == b and block_table_.shape[0] == b, "cache_seqlens / block_table batch mismatch")
     _require(kcache.shape == vcache.shape, "k_cache and v_cache must have the same shape")
     h_k = kcache.shape[2]
@@ -505,6 +514,7 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
         _descale(fp, "v_descale", v_descale_, b, h_k)
         _set_paged(fp, kcache, vcache, block_table_, seqlens_k_, b)
         _set_sinks(fp, s_aux_, h)
+        _set_window(fp, window_size_left, 0 if is_causal else window_size_right)
         _apply_profile_events(fp)
         with torch.cuda.device(q.device):
             _check(_lib.fa_b200_fwd(ctypes.byref(fp), _stream(q)), "fwd_kvcache")
@@ -512,6 +522,7 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     p = _decode_params(q, kcache, vcache, seqlens_k_, block_table_, softmax_scale, out, lse, q_descale_, k_descale_,
                        v_descale_, 0, max_seqlen_k)
     _set_sinks(p, s_aux_, h)
+    _set_window(p, window_size_left, -1)   # one query token at the end of its sequence: only the left side matters
     with torch.cuda.device(q.device):
         ws = _workspace(q.device, int(_lib.fa_b200_decode_workspace_bytes(ctypes.byref(p))))
         if ws is not None:

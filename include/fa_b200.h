@@ -110,6 +110,11 @@ typedef struct fa_b200_fwd_params {
    * (FA_B200_F16 / FA_B200_BF16, or FA_B200_F32), not multiplied by softmax_scale.  NULL = off. */
   const void* s_aux;
   int32_t s_aux_dtype;
+  /* Sliding window (flash_attn_func(..., window_size=(left, right)), construct_local_mask in
+   * tests/test_flash_attn.py:185-217): with has_window != 0, query i of a sequence with sq queries and sk keys sees key
+   * j iff  i + sk - sq - window_left <= j <= i + sk - sq + window_right;  a negative value leaves that side open.
+   * is_causal forces window_right = 0.  Not available with tile lists (fa_b200_fwd_sparse). */
+  int32_t has_window, window_left, window_right;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch
@@ -172,6 +177,10 @@ typedef struct fa_b200_decode_params {
    * o_partial_out set the sink is left to the caller's final fa_b200_combine. */
   const void* s_aux;
   int32_t s_aux_dtype;
+  /* Sliding window: with has_window != 0 and window_left >= 0 the query token sees only the last window_left + 1
+   * keys of its sequence (the reference's decode takes window_size_left the same way,
+   * src/paged_attention_window.h:47-109). */
+  int32_t has_window, window_left;
 } fa_b200_decode_params;
 
 /* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)

@@ -237,7 +237,7 @@ def test_prefill_rejects_what_the_path_does_not_do(fa):
     with pytest.raises(NotImplementedError):
         flash_attn.flash_attn_func(q, q, q, dropout_p=0.1)
     with pytest.raises(NotImplementedError):
-        flash_attn.flash_attn_func(q, q, q, window_size=(4, 0))
+        flash_attn.flash_attn_func(q, q, q, softcap=30.0)
     with pytest.raises(RuntimeError):
         flash_attn.flash_attn_func(q[..., :64], q[..., :64], q[..., :64])
     with pytest.raises(RuntimeError):
