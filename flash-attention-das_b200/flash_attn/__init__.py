@@ -15,4 +15,5 @@ from .flash_attn_interface import (  # noqa: F401
     vllm_flash_attn_varlen_func,
     vllm_flash_attn_with_kvcache,
 )
+from . import torch_ops  # noqa: F401,E402  (registers flash_attn::_flash_attn_forward, flash_attn2_c_op::varlen_fwd / fwd_kvcache)
 from . import split_kv_parallel  # noqa: F401,E402  (multi-GPU helpers: sharding, partial all-gather + combine)

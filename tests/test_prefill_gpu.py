@@ -350,3 +350,29 @@ def test_paged_layout_bhsd_gives_identical_bits(fa, page):
     assert_close_to_oracle(d2.cpu(), ref32, ref_pt, mult=2.0, what="bhsd decode")
     with pytest.raises(NotImplementedError):
         flash_attn.vllm_flash_attn_with_kvcache(qd, kc_d, vc_d, cache_seqlens=sl.cuda(), block_table=bt.cuda(), layout=0)
+
+
+def test_torch_ops_reach_the_same_kernels(fa):
+    """flash_attn::_flash_attn_forward and flash_attn2_c_op::varlen_fwd / fwd_kvcache (the names the reference registers)
+    give the same bits as the Python API."""
+    from _util import make_paged
+    flash_attn, cuda = fa
+    g = gen(321)
+    q, k, v = randn(g, 2, 200, 8, 128).cuda(), randn(g, 2, 200, 2, 128).cuda(), randn(g, 2, 200, 2, 128).cuda()
+    scale = 128 ** -0.5
+    o1 = flash_attn.flash_attn_func(q, k, v, causal=True)
+    o2, lse, _, _ = torch.ops.flash_attn._flash_attn_forward(q, k, v, 0.0, scale, True, -1, -1, 0.0, None, False)
+    assert torch.equal(o1, o2) and lse.shape == (2, 8, 200)
+    cu = torch.tensor([0, 150, 400], dtype=torch.int32, device="cuda")
+    qv, kv, vv = q.reshape(400, 8, 128), k.reshape(400, 2, 128), v.reshape(400, 2, 128)
+    o3 = flash_attn.flash_attn_varlen_func(qv, kv, vv, cu, cu, 250, 250, causal=True)
+    o4, _, _, _ = torch.ops.flash_attn2_c_op.varlen_fwd(qv, kv, vv, None, cu, cu, None, None, None, None, 250, 250, 0.0,
+                                                         scale, False, True, -1, -1, 0.0, False)
+    assert torch.equal(o3, o4)
+    kc, vc, bt, sl = make_paged(g, [70, 300], 2, 64, torch.bfloat16, poison=False)
+    qd = randn(g, 2, 1, 8, 128).cuda()
+    o5 = flash_attn.flash_attn_with_kvcache(qd, kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(), block_table=bt.cuda(), causal=True)
+    o6, _ = torch.ops.flash_attn2_c_op.fwd_kvcache(qd, kc.cuda(), vc.cuda(), None, None, sl.cuda(), None, None, None, None,
+                                                   bt.cuda(), None, None, scale, True, -1, -1, 0.0, True, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(o5, o6)
