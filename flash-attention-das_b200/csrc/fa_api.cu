@@ -85,6 +85,30 @@ int make_tmap(CUtensorMap* out, const void* base, int dtype, int64_t heads, int6
   return FA_B200_OK;
 }
 
+// 4-D tile descriptor over a transposed V pool (tokens of a page, d, heads, blocks): tokens contiguous, a
+// 128-byte-swizzled box of (64 tokens, 128 d rows, 1, 1) of a 16-bit type.  Strides in elements.
+int make_tmap_vt(CUtensorMap* out, const void* base, int dtype, int64_t page, int64_t heads, int64_t blocks,
+                 int64_t d_stride, int64_t head_stride, int64_t block_stride) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) { set_error("cuTensorMapEncodeTiled", "driver entry point not found"); return FA_B200_ERR_CUDA; }
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(page), static_cast<cuuint64_t>(kHeadDim),
+                        static_cast<cuuint64_t>(heads > 0 ? heads : 1), static_cast<cuuint64_t>(blocks > 0 ? blocks : 1)};
+  auto fix = [&](int64_t s) { return static_cast<cuuint64_t>((s > 0 ? s : page) * 2); };
+  cuuint64_t strides[3] = {fix(d_stride), fix(head_stride), fix(block_stride)};
+  cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(kHeadDim), 1u, 1u};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, dtype == FA_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_error("cuTensorMapEncodeTiled", buf);
+    return FA_B200_ERR_CUDA;
+  }
+  return FA_B200_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 bool stride_ok(int64_t s, int es) { return s >= 0 && (s * es) % 16 == 0; }
 
@@ -333,8 +357,15 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   int st = make_tmap(&tk, p->k_cache, p->dtype, p->h_k, p->page_size, p->num_blocks, p->k_head_stride, p->k_row_stride,
                      p->k_block_stride, pl.box_tok);
   if (st != FA_B200_OK) return st;
-  st = make_tmap(&tv, p->v_cache, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
-                 p->v_block_stride, pl.box_tok);
+  if (p->v_transposed) {
+    if (p->dtype == FA_B200_E4M3) return FA_B200_ERR_UNSUPPORTED;
+    if (p->page_size % 64 != 0) return FA_B200_ERR_PAGE;
+    st = make_tmap_vt(&tv, p->v_cache, p->dtype, p->page_size, p->h_k, p->num_blocks, p->v_row_stride,
+                      p->v_head_stride, p->v_block_stride);
+  } else {
+    st = make_tmap(&tv, p->v_cache, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
+                   p->v_block_stride, pl.box_tok);
+  }
   if (st != FA_B200_OK) return st;
 
   DecodeKernelParams k{};
@@ -367,6 +398,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.s_aux = p->s_aux;
   k.s_aux_dtype = p->s_aux_dtype;
   k.window_left = (p->has_window && p->window_left >= 0) ? p->window_left : -1;
+  k.v_transposed = p->v_transposed ? 1 : 0;
   if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
     k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * kHeadDim;

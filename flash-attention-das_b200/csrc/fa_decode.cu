@@ -51,7 +51,10 @@ __device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
   else return pack_f16(lo, hi);
 }
 
-template <int DT, int STAGES>
+// VT: the V pool is stored transposed, (num_blocks, h_k, d, page) with tokens contiguous (the reference's paged layout
+// 0, flash_attn_interface.py:2223-2227): a V tile then lands in shared memory as 128 d rows of 64 tokens and feeds the
+// P V product through plain (non-transposing) ldmatrix, exactly as K feeds Q K^T.  16-bit types, pages of 64 * n.
+template <int DT, int STAGES, bool VT>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
 decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                     const DecodeKernelParams p) {
@@ -143,8 +146,9 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 #pragma unroll
           for (int hf = 0; hf < T::kHalves; ++hf) {
             tma_load_4d(kdst + hf * (T::kTile * 128) + off, &tmap_k, fb, hf * 64, hk, row, page);
-            tma_load_4d(vdst + hf * (T::kTile * 128) + off, &tmap_v, fb, hf * 64, hk, row, page);
+            if constexpr (!VT) tma_load_4d(vdst + hf * (T::kTile * 128) + off, &tmap_v, fb, hf * 64, hk, row, page);
           }
+          if constexpr (VT) tma_load_4d(vdst, &tmap_v, fb, row, 0, hk, page);   // one box: 64 tokens x 128 d rows
         }
       }
     }
@@ -185,7 +189,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       const int wrow0 = cw * T::kRowsPerWarp;
       // Rows at or past the end of the sequence were not loaded (or hold other tokens): their V must
       // be zero so that 0 * garbage cannot poison the PV product; their scores are masked by index.
-      if (tok0 + wrow0 + T::kRowsPerWarp > tok_end) {
+      if (!VT && tok0 + wrow0 + T::kRowsPerWarp > tok_end) {
         const int first_bad = max(tok_end - tok0, wrow0);
         const int nchunk = T::kHalves * 8;
         for (int r = first_bad; r < wrow0 + T::kRowsPerWarp; ++r) {
@@ -268,6 +272,25 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         pa[3] = pack_p<DT>(sc[1][2], sc[1][3]);
         {
           const int mi = lane >> 3;
+          if constexpr (VT) {
+            // tokens at or past the end of the sequence were loaded with whatever the page holds there: their P is
+            // zero, and the fragment halves that hold them are cleared so that 0 * NaN cannot reach O
+            const int lim = tok_end - tok0 - r0;   // valid tokens of this 16-token sub-block
+            const int t_lo = 2 * qd;
+            const uint32_t keep_lo = (t_lo < lim ? 0x0000ffffu : 0u) | (t_lo + 1 < lim ? 0xffff0000u : 0u);
+            const uint32_t keep_hi = (t_lo + 8 < lim ? 0x0000ffffu : 0u) | (t_lo + 9 < lim ? 0xffff0000u : 0u);
+#pragma unroll
+            for (int nd = 0; nd < 16; nd += 2) {
+              const int drow = (nd + (mi >> 1)) * 8 + (lane & 7);
+              const int chunk = (r0 >> 3) + (mi & 1);   // 16-byte piece (8 tokens) of the d row
+              const uint32_t addr = vbase + drow * 128 + ((chunk ^ (drow & 7)) << 4);
+              uint32_t v0, v1, v2, v3;
+              ldsm_x4(addr, v0, v1, v2, v3);
+              mma_pv<DT>(o[nd], pa, v0 & keep_lo, v1 & keep_hi);
+              mma_pv<DT>(o[nd + 1], pa, v2 & keep_lo, v3 & keep_hi);
+            }
+          } else {
+          const int mi = lane >> 3;
           const int row = r0 + ((mi & 1) << 3) + (lane & 7);
           const uint32_t rbase = vbase + row * 128;
           const int rsw = row & 7;
@@ -299,6 +322,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
               mma_pv<DT>(o[2 * cc + 2], pa, cvt_e4m3x2_to_f16x2(t2), cvt_e4m3x2_to_f16x2(t3));
               mma_pv<DT>(o[2 * cc + 3], pa, cvt_e4m3x2_to_f16x2(t2 >> 16), cvt_e4m3x2_to_f16x2(t3 >> 16));
             }
+          }
           }
         }
       }
@@ -395,11 +419,11 @@ size_t decode_smem_bytes(int stages) {
 }
 int decode_max_pages_per_partition() { return kMaxPagesPerPartition; }
 
-template <int DT>
+template <int DT, bool VT>
 static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
                                     cudaStream_t stream) {
   constexpr int STAGES = 3;
-  auto kern = decode_paged_kernel<DT, STAGES>;
+  auto kern = decode_paged_kernel<DT, STAGES, VT>;
   const size_t smem = decode_smem_bytes(STAGES);
   static bool attr_done[64] = {};
   int dev = 0;
@@ -416,10 +440,15 @@ static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv
 
 cudaError_t launch_decode(int dtype, const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
                           cudaStream_t stream) {
+  if (p.v_transposed) {
+    if (dtype == FA_B200_F16) return launch_decode_dt<FA_B200_F16, true>(tk, tv, p, stream);
+    if (dtype == FA_B200_BF16) return launch_decode_dt<FA_B200_BF16, true>(tk, tv, p, stream);
+    return cudaErrorInvalidValue;
+  }
   switch (dtype) {
-    case FA_B200_F16: return launch_decode_dt<FA_B200_F16>(tk, tv, p, stream);
-    case FA_B200_BF16: return launch_decode_dt<FA_B200_BF16>(tk, tv, p, stream);
-    case FA_B200_E4M3: return launch_decode_dt<FA_B200_E4M3>(tk, tv, p, stream);
+    case FA_B200_F16: return launch_decode_dt<FA_B200_F16, false>(tk, tv, p, stream);
+    case FA_B200_BF16: return launch_decode_dt<FA_B200_BF16, false>(tk, tv, p, stream);
+    case FA_B200_E4M3: return launch_decode_dt<FA_B200_E4M3, false>(tk, tv, p, stream);
   }
   return cudaErrorInvalidValue;
 }

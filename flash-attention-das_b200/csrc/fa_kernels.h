@@ -33,6 +33,7 @@ struct DecodeKernelParams {
   const void* s_aux;   // attention sinks (h), applied where the row is finalised (write_final only)
   int32_t s_aux_dtype;
   int32_t window_left; // the query token sees only its last window_left + 1 keys; -1 = all
+  int32_t v_transposed; // tmap_v describes (page tokens, d, h_k, block) with a (64, 128, 1, 1) box
 };
 
 size_t decode_smem_bytes(int stages);

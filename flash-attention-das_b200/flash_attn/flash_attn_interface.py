@@ -26,14 +26,17 @@ def _no_backward(*tensors):
 
 def _paged_as_bshd(k, v, layout):
     """A (num_blocks, page, nheads_k, d) view of paged pools given in the reference's layouts
-    (flash_attn_interface.py:2223-2237): "bshd" / 2 as is, "bhsd" / 1 = (num_blocks, nheads_k, page, d) permuted (no
-    copy: the kernels take strides).  "custom" / 0 stores V as (num_blocks, nheads_k, d, page)."""
+    (flash_attn_interface.py:2223-2237): "bshd" / 2 as is, "bhsd" / 1 = (num_blocks, nheads_k, page, d) permuted,
+    "custom" / 0 = K as bhsd and V stored as (num_blocks, nheads_k, d, page).  No copies: the kernels take strides."""
     if layout in ("bshd", 2):
         return k, v
     if layout in ("bhsd", 1):
         return k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3)
-    raise NotImplementedError("paged layout 'custom' (V stored as (num_blocks, nheads_k, d, page)) is outside the B200 "
-                              "hot path of this build: use 'bshd' or 'bhsd'")
+    if layout in ("custom", 0):
+        # V is (num_blocks, nheads_k, d, page): the view keeps the tokens as its contiguous axis, which the binding
+        # module recognises (one-token decode only; the prefill kernels do not take this layout)
+        return k.permute(0, 2, 1, 3), v.permute(0, 3, 1, 2)
+    raise ValueError(f"unknown paged layout {layout!r}")
 
 
 def flash_attn_func(
@@ -105,12 +108,28 @@ def flash_attn_varlen_func(
     for layout "bshd" or (num_blocks, nheads_k, page_size, 128) for "bhsd", and `seqused_k` (int32 (batch,)) gives
     each sequence's number of keys; cu_seqlens_k is not used.  The kernel reads the pages directly, through strides,
     whatever the layout (the reference gathers them into a contiguous copy first,
-    flash_attn_interface.py:2350-2373).  Layout "custom" (V stored transposed) is not supported."""
+    flash_attn_interface.py:2350-2373).  Layout "custom" (V stored transposed, (num_blocks, nheads_k, 128, page_size)) is
+    taken for one query token per sequence (the decode kernel), as the reference sends that case to its decode
+    kernel too (flash_attn_interface.py:2316-2348)."""
     _no_backward(q, k, v)
     if window_size is None:
         window_size = (-1, -1)
     if block_table is not None:
         k, v = _paged_as_bshd(k, v, layout)
+        if layout in ("custom", 0):
+            if max_seqlen_q != 1 or q.shape[0] != block_table.shape[0]:
+                raise NotImplementedError("paged layout 'custom' (V transposed) is taken for one query token per sequence "
+                                          "only: use 'bshd' or 'bhsd' for prefill over a paged cache")
+            if softmax_scale is None:
+                softmax_scale = q.shape[-1] ** (-0.5)
+            o, lse = flash_attn_cuda.fwd_kvcache(
+                q.unsqueeze(1), k, v, None, None, seqused_k, None, None, None, None, block_table, alibi_slopes,
+                None if out is None else out.unsqueeze(1), softmax_scale, causal, window_size[0], window_size[1], softcap,
+                True, num_splits, s_aux, q_descale, k_descale, v_descale, max_seqlen_k)
+            o, lse = o.squeeze(1), lse.squeeze(-1).transpose(0, 1)
+            if return_attn_probs:
+                return o, lse, None
+            return (o, lse) if return_softmax_lse else o
     if q_v is not None:
         raise NotImplementedError("q_v is outside the B200 hot path of this build")
     if softmax_scale is None:
@@ -210,9 +229,9 @@ def vllm_flash_attn_with_kvcache(
 ):
     """The reference's second paged-decode entry (flash_attn_interface.py:2633-2775): like flash_attn_with_kvcache
     with fp32 q/k/v_scale (the e4m3 descales), an upper bound ``max_seqlen_k`` on cache_seqlens (0 = none) and the
-    pool layout as an integer: 2 = (num_blocks, page, nheads_k, d), 1 = (num_blocks, nheads_k, page, d); the
-    reference's default 0 (V transposed) is not supported.  Like the reference it returns only ``out`` and does
-    not append k / v."""
+    pool layout as an integer: 2 = (num_blocks, page, nheads_k, d), 1 = (num_blocks, nheads_k, page, d), 0 (the
+    reference's default) = K as 1 and V as (num_blocks, nheads_k, d, page), which is taken for one query token per
+    sequence in fp16 / bf16 with pages of 64 * n.  Like the reference it returns only ``out`` and does not append k / v."""
     assert k_cache.stride(-1) == 1, "k_cache must have contiguous last dimension"
     assert v_cache.stride(-1) == 1, "v_cache must have contiguous last dimension"
     if k is not None or v is not None or rotary_cos is not None or rotary_sin is not None:

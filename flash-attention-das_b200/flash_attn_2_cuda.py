@@ -82,6 +82,7 @@ class DecodeParams(ctypes.Structure):
         ("profile_start_event", _c_vp), ("profile_stop_event", _c_vp),
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
         ("has_window", _c_i32), ("window_left", _c_i32),
+        ("v_transposed", _c_i32),
     ]
 
 
@@ -198,12 +199,12 @@ def _unsupported(cond: bool, what: str):
         raise NotImplementedError(f"{what} is outside the B200 hot path of this build")
 
 
-def _check_qkv(q, k, v):
+def _check_qkv(q, k, v, v_transposed=False):
     _require(q.dtype in _DT, "FlashAttention only support fp16, bf16 and fp8 e4m3 data type")
     _require(k.dtype == q.dtype, "query and key must have the same dtype")
     _require(v.dtype == q.dtype, "query and value must have the same dtype")
     _require(q.is_cuda and k.is_cuda and v.is_cuda, "Input tensor must be on CUDA device")
-    for t in (q, k, v):
+    for t in (q, k) if v_transposed else (q, k, v):
         _require(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
     _require(q.shape[-1] == 128 and v.shape[-1] == 128,
              "this build implements head dimension 128 only (the hot path named by the B200 port)")
@@ -428,6 +429,11 @@ def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
     return ws
 
 
+def _is_transposed_v(vcache) -> bool:
+    """A (num_blocks, page, h_k, d) view whose contiguous axis is the page's tokens (the reference's layout 0)."""
+    return vcache.dim() == 4 and vcache.stride(-1) != 1 and vcache.stride(1) == 1
+
+
 def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out, lse, q_descale=None,
                    k_descale=None, v_descale=None, partition_tokens=0, max_seqlen_k=0):
     b, sq, h, d = q.shape
@@ -439,7 +445,12 @@ def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out
     if out is not None:
         p.o_batch_stride, p.o_head_stride = out.stride(0), out.stride(2)
     p.k_block_stride, p.k_row_stride, p.k_head_stride = kcache.stride(0), kcache.stride(1), kcache.stride(2)
-    p.v_block_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
+    if _is_transposed_v(vcache):
+        # (num_blocks, page, h_k, d) view of a pool stored as (num_blocks, h_k, d, page): the tokens are the contiguous axis
+        p.v_transposed = 1
+        p.v_block_stride, p.v_head_stride, p.v_row_stride = vcache.stride(0), vcache.stride(2), vcache.stride(3)
+    else:
+        p.v_block_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
     p.block_table, p.block_table_batch_stride = block_table.data_ptr(), block_table.stride(0)
     p.cache_seqlens = seqlens_k.data_ptr()
     p.b, p.h, p.h_k, p.d = b, h, h_k, d
@@ -467,7 +478,10 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     the attention then runs over seqlens_k + seqlen_new keys, the semantics the public signature documents
     (flash_attn_interface.py:2503-2520) and the reference's wrapper drops; cache_batch_idx and cache_leftpad
     (contiguous caches only) raise.  Unlike the reference, the returned softmax_lse is filled in."""
-    _check_qkv(q, kcache, vcache)
+    v_t = _is_transposed_v(vcache)
+    _check_qkv(q, kcache, vcache, v_t)
+    _unsupported(v_t and (q.shape[1] != 1 or k_ is not None or q.dtype == torch.float8_e4m3fn),
+                 "a transposed V pool (layout 0) outside one-token bf16/fp16 decode without append")
     _require((k_ is None) == (v_ is None), "k and v must be passed together")
     _require(rotary_cos_ is None or k_ is not None, "rotary_cos/rotary_sin are only applicable if k and v are passed in")
     _require((rotary_cos_ is None) == (rotary_sin_ is None), "rotary_cos and rotary_sin must be passed together")

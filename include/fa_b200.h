@@ -181,6 +181,11 @@ typedef struct fa_b200_decode_params {
    * keys of its sequence (the reference's decode takes window_size_left the same way,
    * src/paged_attention_window.h:47-109). */
   int32_t has_window, window_left;
+  /* V stored transposed, (num_blocks, h_k, d, page_size) with the tokens of a page contiguous (the reference's paged
+   * layout 0 / "custom", flash_attn_interface.py:2223-2227; K is then (num_blocks, h_k, page_size, d), which the
+   * K strides already express).  With v_transposed != 0, v_row_stride is the stride between consecutive d rows.
+   * F16 / BF16 only, page_size a multiple of 64. */
+  int32_t v_transposed;
 } fa_b200_decode_params;
 
 /* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)

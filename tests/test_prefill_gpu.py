@@ -348,8 +348,23 @@ def test_paged_layout_bhsd_gives_identical_bits(fa, page):
     ref32, _ = O.paged_decode_ref(qd.cpu(), kc, vc, sl, bt, out_dtype=torch.float32)
     ref_pt, _ = O.paged_decode_ref(qd.cpu(), kc, vc, sl, bt, upcast=False, reorder_ops=True)
     assert_close_to_oracle(d2.cpu(), ref32, ref_pt, mult=2.0, what="bhsd decode")
-    with pytest.raises(NotImplementedError):
-        flash_attn.vllm_flash_attn_with_kvcache(qd, kc_d, vc_d, cache_seqlens=sl.cuda(), block_table=bt.cuda(), layout=0)
+    if page % 64 == 0:
+        # layout 0: K as bhsd, V stored transposed (num_blocks, nheads_k, d, page); the decode kernel reads it as it is
+        vc_tt = vc_d.permute(0, 2, 3, 1).contiguous()
+        d4 = flash_attn.vllm_flash_attn_with_kvcache(qd, kc_t, vc_tt, cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                                     causal=True)          # layout 0 is the reference's default
+        cq1 = torch.arange(len(lens_k) + 1, dtype=torch.int32, device="cuda")
+        d5 = flash_attn.flash_attn_varlen_func(qd[:, 0], kc_t, vc_tt, cq1, None, 1, max(lens_k), seqused_k=sl.cuda(),
+                                               causal=True, block_table=bt.cuda(), layout="custom")
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        assert torch.equal(d1, d4) and torch.equal(d1[:, 0], d5)
+        with pytest.raises(NotImplementedError):   # prefill over a transposed V pool is not taken
+            flash_attn.flash_attn_varlen_func(q.cuda(), kc_t, vc_tt, cq, None, max(lens_q), max(lens_k), layout="custom", **args)
+    else:
+        with pytest.raises(RuntimeError):          # layout 0 needs pages of 64 * n
+            flash_attn.vllm_flash_attn_with_kvcache(qd, kc_t, vc_d.permute(0, 2, 3, 1).contiguous(), cache_seqlens=sl.cuda(),
+                                                    block_table=bt.cuda(), causal=True)
 
 
 def test_torch_ops_reach_the_same_kernels(fa):
