@@ -545,6 +545,30 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     return [out, lse]
 
 
+def paged_attention(out, query, key_cache, value_cache, scale, block_tables, seq_lens, alibi_slopes=None, kv_cache_dtype="auto",
+                    q_scale=None, k_scale=None, v_scale=None, max_seq_len=0, s_aux_=None, layout=0, window_size_left=-1,
+                    window_size_right=-1, is_causal=False):
+    """The reference's second decode binding (csrc/flash_attn_cutlass/flash_api.cpp:2496-2515): attention of
+    query (num_seqs, seqlen_q, num_heads, 128) over paged pools into the caller's ``out``.  layout 0: key_cache
+    (num_blocks, h_k, page, d) and value_cache (num_blocks, h_k, d, page); 1: both (num_blocks, h_k, page, d); 2: both
+    (num_blocks, page, h_k, d).  q/k/v_scale are the e4m3 descales."""
+    _unsupported(kv_cache_dtype not in ("auto", "") and not (str(kv_cache_dtype).startswith("fp8") and
+                                                             query.dtype == torch.float8_e4m3fn),
+                 "a KV cache dtype different from the query dtype")
+    if layout == 2:
+        kc, vc = key_cache, value_cache
+    elif layout == 1:
+        kc, vc = key_cache.permute(0, 2, 1, 3), value_cache.permute(0, 2, 1, 3)
+    elif layout == 0:
+        kc, vc = key_cache.permute(0, 2, 1, 3), value_cache.permute(0, 3, 1, 2)
+    else:
+        raise RuntimeError(f"unknown paged layout {layout}")
+    q4 = query if query.dim() == 4 else query.unsqueeze(1)
+    o4 = out if out.dim() == 4 else out.unsqueeze(1)
+    fwd_kvcache(q4, kc, vc, None, None, seq_lens, None, None, None, None, block_tables, alibi_slopes, o4, float(scale),
+                is_causal, window_size_left, window_size_right, 0.0, True, 0, s_aux_, q_scale, k_scale, v_scale, max_seq_len)
+
+
 def kv_append(q, kcache, vcache, k_new, v_new, seqlens_k, block_table, rotary_cos=None, rotary_sin=None,
               is_rotary_interleaved=True, rotate_q_per_token=True):
     """Writes k_new / v_new (batch, seqlen_new, nheads_k, d) into the paged cache at positions

@@ -190,3 +190,25 @@ def test_decode_rejects_what_the_path_does_not_do(fa):
     with pytest.raises(RuntimeError):
         flash_attn.flash_attn_with_kvcache(q[..., :64].contiguous(), kc.cuda()[..., :64].contiguous(),
                                            vc.cuda()[..., :64].contiguous(), cache_seqlens=sl.cuda(), block_table=bt.cuda())
+
+
+def test_paged_attention_binding_layouts(fa):
+    """flash_attn_2_cuda.paged_attention (the reference's second decode binding, flash_api.cpp:2496-2515) writes into the
+    caller's out for the three pool layouts, bit-identical to flash_attn_with_kvcache."""
+    flash_attn, cuda = fa
+    g = gen(99)
+    lens, h, hk = [1, 200, 64, 513], 8, 2
+    kc, vc, bt, sl = make_paged(g, lens, hk, 64, torch.bfloat16, poison=False)
+    q = randn(g, len(lens), 1, h, 128).cuda()
+    kc_d, vc_d = kc.cuda(), vc.cuda()
+    want = flash_attn.flash_attn_with_kvcache(q, kc_d, vc_d, cache_seqlens=sl.cuda(), block_table=bt.cuda(), causal=True)
+    pools = {2: (kc_d, vc_d),
+             1: (kc_d.permute(0, 2, 1, 3).contiguous(), vc_d.permute(0, 2, 1, 3).contiguous()),
+             0: (kc_d.permute(0, 2, 1, 3).contiguous(), vc_d.permute(0, 2, 3, 1).contiguous())}
+    for layout, (kp, vp) in pools.items():
+        out = torch.full_like(want, float("nan"))
+        cuda.paged_attention(out, q, kp, vp, 128 ** -0.5, bt.cuda(), sl.cuda(), None, "auto", None, None, None, max(lens),
+                             None, layout, -1, -1, True)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        assert torch.equal(out, want), layout
