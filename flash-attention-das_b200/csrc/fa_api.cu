@@ -294,6 +294,53 @@ int fa_b200_kv_append(const fa_b200_kv_append_params* p, void* stream) {
   return FA_B200_OK;
 }
 
+int fa_b200_unpad_plan(const void* mask, int32_t elem, int32_t b, int32_t s, int64_t row_stride, int32_t* seqlens,
+                       int32_t* cu_seqlens, int64_t* indices, int32_t* stats, void* stream) {
+  if (elem != 1 && elem != 4 && elem != 8) return FA_B200_ERR_DTYPE;
+  if (b < 0 || s < 0 || row_stride < 0) return FA_B200_ERR_SHAPE;
+  if (!cu_seqlens || !stats || (b > 0 && (!mask || !seqlens || (s > 0 && !indices)))) return FA_B200_ERR_NULL;
+  if (b == 0) {
+    cudaError_t e = cudaMemsetAsync(cu_seqlens, 0, sizeof(int32_t), static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaMemsetAsync(stats, 0, 2 * sizeof(int32_t), static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? FA_B200_OK : cuda_fail("fa_b200_unpad_plan", e);
+  }
+  cudaError_t e = launch_unpad_plan(mask, elem, b, s, row_stride, seqlens, cu_seqlens, indices, stats,
+                                    static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("fa_b200_unpad_plan", e);
+  g_launches += 3;
+  return FA_B200_OK;
+}
+
+static int move_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows, int64_t row_bytes,
+                     int64_t limit_rows, bool scatter, void* stream) {
+  if (n_rows < 0 || row_bytes < 0 || limit_rows < 0) return FA_B200_ERR_SHAPE;
+  if (n_rows == 0 || row_bytes == 0) return FA_B200_OK;
+  if (!src || !dst || !indices) return FA_B200_ERR_NULL;
+  cudaError_t e = launch_move_rows(src, indices, dst, n_rows, row_bytes, limit_rows, scatter, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(scatter ? "fa_b200_scatter_rows" : "fa_b200_gather_rows", e);
+  g_launches++;
+  return FA_B200_OK;
+}
+int fa_b200_gather_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows, int64_t row_bytes,
+                        int64_t limit_rows, void* stream) {
+  return move_rows(src, indices, dst, n_rows, row_bytes, limit_rows, false, stream);
+}
+int fa_b200_scatter_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows, int64_t row_bytes,
+                         int64_t limit_rows, void* stream) {
+  return move_rows(src, indices, dst, n_rows, row_bytes, limit_rows, true, stream);
+}
+
+int fa_b200_block_map_to_offset(const uint8_t* block_map, int32_t* block_offset, int32_t* block_count, int64_t rows, int32_t k,
+                                int32_t scale, int32_t fill, void* stream) {
+  if (rows < 0 || k < 0) return FA_B200_ERR_SHAPE;
+  if (rows == 0) return FA_B200_OK;
+  if (!block_count || (k > 0 && (!block_map || !block_offset))) return FA_B200_ERR_NULL;
+  cudaError_t e = launch_block_map(block_map, block_offset, block_count, rows, k, scale, fill, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("fa_b200_block_map_to_offset", e);
+  g_launches++;
+  return FA_B200_OK;
+}
+
 namespace {
 bool sink_dtype_ok(const void* s_aux, int dtype) {
   return !s_aux || dtype == FA_B200_F16 || dtype == FA_B200_BF16 || dtype == FA_B200_F32;

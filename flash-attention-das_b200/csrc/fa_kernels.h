@@ -133,4 +133,13 @@ struct KvAppendKernelParams {
 };
 cudaError_t launch_kv_append(int dtype, const KvAppendKernelParams& p, cudaStream_t stream);
 
+
+// Callers' glue (fa_glue.cu): padding removal and block-map conversion.
+cudaError_t launch_unpad_plan(const void* mask, int elem, int b, int s, int64_t row_stride, int32_t* seqlens,
+                              int32_t* cu_seqlens, int64_t* indices, int32_t* stats, cudaStream_t stream);
+cudaError_t launch_move_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows, int64_t row_bytes,
+                             int64_t limit_rows, bool scatter, cudaStream_t stream);
+cudaError_t launch_block_map(const uint8_t* map, int32_t* offset, int32_t* count, int64_t rows, int k, int scale, int fill,
+                             cudaStream_t stream);
+
 }  // namespace fa

@@ -136,6 +136,14 @@ _lib.fa_b200_kv_append.argtypes = [ctypes.POINTER(KvAppendParams), _c_vp]
 _lib.fa_b200_kv_append.restype = ctypes.c_int
 _lib.fa_b200_combine.argtypes = [ctypes.POINTER(CombineParams), _c_vp]
 _lib.fa_b200_combine.restype = ctypes.c_int
+_lib.fa_b200_unpad_plan.argtypes = [_c_vp, _c_i32, _c_i32, _c_i32, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]
+_lib.fa_b200_unpad_plan.restype = ctypes.c_int
+_lib.fa_b200_gather_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_i64, _c_i64, _c_i64, _c_vp]
+_lib.fa_b200_gather_rows.restype = ctypes.c_int
+_lib.fa_b200_scatter_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_i64, _c_i64, _c_i64, _c_vp]
+_lib.fa_b200_scatter_rows.restype = ctypes.c_int
+_lib.fa_b200_block_map_to_offset.argtypes = [_c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_vp]
+_lib.fa_b200_block_map_to_offset.restype = ctypes.c_int
 _lib.fa_b200_status_string.argtypes = [ctypes.c_int]
 _lib.fa_b200_status_string.restype = ctypes.c_char_p
 _lib.fa_b200_last_cuda_error.restype = ctypes.c_char_p
@@ -707,3 +715,69 @@ def fwd_sparse(q, k, v, block_count, block_offset, column_count, column_index, o
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd_sparse(ctypes.byref(p), _stream(q)), "fwd_sparse")
     return [out, lse]
+
+
+# ------------------------------------------------------------------------------------------------
+# callers' glue: padding removal and block-map conversion
+# ------------------------------------------------------------------------------------------------
+def unpad_plan(attention_mask):
+    """attention_mask (batch, seqlen) bool / int -> (seqlens int32 (batch), cu_seqlens int32 (batch + 1), indices int64
+    (total), max_seqlen int).  Reads the two totals back (one host synchronisation, as the reference's .item())."""
+    _require(attention_mask.is_cuda and attention_mask.dim() == 2, "attention_mask must be a CUDA tensor of shape (batch, seqlen)")
+    _require(attention_mask.element_size() in (1, 4, 8) and attention_mask.stride(1) == 1,
+             "attention_mask must be bool / uint8 / int32 / int64 with contiguous rows")
+    b, s = attention_mask.shape
+    dev = attention_mask.device
+    seqlens = torch.empty((b,), dtype=torch.int32, device=dev)
+    cu = torch.empty((b + 1,), dtype=torch.int32, device=dev)
+    indices = torch.empty((b * s,), dtype=torch.int64, device=dev)
+    stats = torch.empty((2,), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.fa_b200_unpad_plan(attention_mask.data_ptr(), attention_mask.element_size(), b, s, attention_mask.stride(0),
+                                       seqlens.data_ptr(), cu.data_ptr(), indices.data_ptr(), stats.data_ptr(),
+                                       _stream(attention_mask)), "unpad_plan")
+    mx, total = stats.tolist()
+    return seqlens, cu, indices[:total], mx
+
+
+def _move_rows(fn, what, src2d, indices, dst2d):
+    _require(src2d.is_cuda and dst2d.is_cuda and indices.is_cuda, "tensors must be on a CUDA device")
+    _require(indices.dtype == torch.int64 and indices.is_contiguous(), "indices must be a contiguous int64 tensor")
+    _require(src2d.is_contiguous() and dst2d.is_contiguous() and src2d.dtype == dst2d.dtype, "rows must be contiguous and of one dtype")
+    row_bytes = src2d.shape[1] * src2d.element_size()
+    limit = dst2d.shape[0] if fn is _lib.fa_b200_scatter_rows else src2d.shape[0]
+    with torch.cuda.device(src2d.device):
+        _check(fn(src2d.data_ptr(), indices.data_ptr(), dst2d.data_ptr(), indices.numel(), row_bytes, limit, _stream(src2d)), what)
+
+
+def gather_rows(src, indices):
+    """src (n, ...) -> src[indices] (index_first_axis of the reference's bert_padding.py)."""
+    src2d = src.reshape(src.shape[0], -1)
+    src2d = src2d if src2d.is_contiguous() else src2d.contiguous()
+    out = torch.empty((indices.numel(), src2d.shape[1]), dtype=src.dtype, device=src.device)
+    _move_rows(_lib.fa_b200_gather_rows, "gather_rows", src2d, indices, out)
+    return out.reshape(indices.numel(), *src.shape[1:])
+
+
+def scatter_rows(values, indices, first_axis_dim):
+    """zeros (first_axis_dim, ...) with rows `indices` set to `values` (index_put_first_axis)."""
+    v2d = values.reshape(values.shape[0], -1)
+    v2d = v2d if v2d.is_contiguous() else v2d.contiguous()
+    out = torch.zeros((first_axis_dim, v2d.shape[1]), dtype=values.dtype, device=values.device)
+    _move_rows(_lib.fa_b200_scatter_rows, "scatter_rows", v2d, indices, out)
+    return out.reshape(first_axis_dim, *values.shape[1:])
+
+
+def block_map_to_offset(block_map, scale=1, fill=10000000):
+    """block_map (..., k) bool -> (block_offset (..., k) int32: ascending set positions times ``scale`` then ``fill``,
+    block_count (...) int32)."""
+    _require(block_map.is_cuda and block_map.dtype in (torch.bool, torch.uint8), "block_map must be a CUDA bool / uint8 tensor")
+    bm = block_map if block_map.is_contiguous() else block_map.contiguous()
+    k = bm.shape[-1]
+    rows = bm.numel() // k if k else 0
+    off = torch.empty(bm.shape, dtype=torch.int32, device=bm.device)
+    cnt = torch.empty(bm.shape[:-1], dtype=torch.int32, device=bm.device)
+    with torch.cuda.device(bm.device):
+        _check(_lib.fa_b200_block_map_to_offset(bm.data_ptr(), off.data_ptr(), cnt.data_ptr(), rows, k, scale, fill, _stream(bm)),
+               "block_map_to_offset")
+    return off, cnt

@@ -299,6 +299,29 @@ typedef struct fa_b200_kv_append_params {
 
 FA_B200_API int fa_b200_kv_append(const fa_b200_kv_append_params* p, void* stream);
 
+/*
+ * Callers' glue around the attention call (forward only).
+ *
+ * fa_b200_unpad_plan: from an attention mask (b, s) (element size 1, 4 or 8 bytes, nonzero = keep; mask_row_stride in
+ * elements) the per-sequence lengths seqlens (b), cu_seqlens (b + 1), the flat indices row * s + column of the kept
+ * tokens in order (indices, capacity b * s, int64) and stats = {max length, total kept}.  What unpad_input computes with
+ * sum / nonzero / cumsum (flash_attn/bert_padding.py:98-122).  Three launches.
+ * fa_b200_gather_rows: dst[r] = src[indices[r]] for r < n_rows (index_first_axis, bert_padding.py:8-37);
+ * fa_b200_scatter_rows: dst[indices[r]] = src[r] (index_put_first_axis / pad_input, :40-67, :199-214; the caller zeroes
+ * dst first).  Rows are row_bytes bytes, contiguous; indices outside [0, limit_rows) are skipped.
+ * fa_b200_block_map_to_offset: a boolean tile map (rows, k) -> per row the ascending indices of its set entries times
+ * `scale` (1 = block indices as flash_attn/utils/sparse_utils.py:526-566 returns them, 64 = the key-row offsets
+ * fa_b200_fwd_sparse takes), padded with `fill` (the reference pads with 10000000), and their count.
+ */
+FA_B200_API int fa_b200_unpad_plan(const void* mask, int32_t mask_elem_size, int32_t b, int32_t s, int64_t mask_row_stride,
+                                   int32_t* seqlens, int32_t* cu_seqlens, int64_t* indices, int32_t* stats, void* stream);
+FA_B200_API int fa_b200_gather_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows, int64_t row_bytes,
+                                    int64_t limit_rows, void* stream);
+FA_B200_API int fa_b200_scatter_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows, int64_t row_bytes,
+                                     int64_t limit_rows, void* stream);
+FA_B200_API int fa_b200_block_map_to_offset(const uint8_t* block_map, int32_t* block_offset, int32_t* block_count,
+                                            int64_t rows, int32_t k, int32_t scale, int32_t fill, void* stream);
+
 /* Text for a status code. */
 FA_B200_API const char* fa_b200_status_string(int status);
 /* Last cudaError_t / CUresult text recorded by a failing call on this thread ("" if none). */

@@ -26,6 +26,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 from oracle import attention_oracle as O  # noqa: E402
+from oracle import padding_oracle as PO  # noqa: E402
 
 REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FA_REFERENCE_ROOT", "")
 
@@ -116,6 +117,13 @@ def gen_inputs(case):
         v = torch.randn(b, sk, hk, d, generator=g).to(dt)
         s_aux = (torch.randn(h, generator=g) * case["sink_scale"]).to(dt) if case["sink_scale"] > 0 else None
         return q, k, v, s_aux
+    if kind == "unpad":
+        b, s = case["b"], case["s"]
+        x = torch.randn(b, s, *case["feat"], generator=g).to(dt)
+        mask = torch.rand(b, s, generator=g) < case["p_keep"]
+        mask[1] = False                      # a sequence with no valid token
+        mask[0, 0] = True
+        return x, mask.to(getattr(torch, case["mask_dtype"]))
     if kind == "rotary":
         b, sq, h, d, rd, ro = (case[x] for x in ("b", "sq", "h", "d", "rotary_dim", "seqlen_ro"))
         x = torch.randn(b, sq, h, d, generator=g).to(dt)
@@ -141,6 +149,8 @@ CASES = [
     dict(name="sink_bf16_causal_gqa", kind="sink", seed=14, dtype="bfloat16", b=2, sq=70, sk=131, h=6, hk=2, d=128, causal=True, window=(-1, -1), sink_scale=1.0),
     dict(name="sink_fp16_window", kind="sink", seed=15, dtype="float16", b=1, sq=96, sk=96, h=4, hk=4, d=128, causal=True, window=(17, 0), sink_scale=0.5),
     dict(name="window_bf16_noncausal_asym", kind="sink", seed=16, dtype="bfloat16", b=1, sq=64, sk=200, h=4, hk=1, d=128, causal=False, window=(30, 9), sink_scale=0.0),
+    dict(name="unpad_bool_ragged", kind="unpad", seed=17, dtype="bfloat16", b=5, s=37, feat=(3, 8), mask_dtype="bool", p_keep=0.6),
+    dict(name="unpad_int64_with_empty_row", kind="unpad", seed=18, dtype="float16", b=4, s=300, feat=(16,), mask_dtype="int64", p_keep=0.3),
     dict(name="rotary_bf16_halves", kind="rotary", seed=11, dtype="bfloat16", b=2, sq=5, h=3, d=128, rotary_dim=128, seqlen_ro=64, interleaved=False),
     dict(name="rotary_fp16_interleaved_partial", kind="rotary", seed=12, dtype="float16", b=3, sq=1, h=4, d=128, rotary_dim=32, seqlen_ro=40, interleaved=True),
     dict(name="rotary_bf16_halves_partial", kind="rotary", seed=13, dtype="bfloat16", b=2, sq=7, h=2, d=128, rotary_dim=64, seqlen_ro=33, interleaved=False),
@@ -160,6 +170,10 @@ def main():
     glob = {"torch": torch, "OUT_OFF": 10_000_000, "MAX_OFF": 5_000_000, "D": 128}
     ref_merge = _function_from_source(os.path.join(REF, "tests", "welm", "test_welm_ops.py"), "merge", glob)
 
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ref_bert_padding", os.path.join(REF, "flash_attn", "bert_padding.py"))
+    BP = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(BP)             # the reference's padding helpers: plain PyTorch, run as they are
     from einops import repeat
     rglob = {"torch": torch, "rearrange": rearrange, "repeat": repeat}
     rotary_py = os.path.join(REF, "flash_attn", "layers", "rotary.py")
@@ -246,6 +260,14 @@ def main():
             err_mine = (mine_pt.float() - out.float()).abs().max().item()
             assert 0.5 * err_ref <= err_mine <= 2.0 * err_ref, (case["name"], err_ref, err_mine)
             rec.update(out=out, err_pt=err_ref)
+        elif kind == "unpad":
+            x, mask = gen_inputs(case)
+            xs, idx, cu, mx = BP.unpad_input(x, mask)
+            back = BP.pad_input(xs, idx, case["b"], case["s"])
+            m_xs, m_idx, m_cu, m_mx = PO.unpad_input_ref(x, mask)
+            assert torch.equal(m_xs, xs) and torch.equal(m_idx, idx) and torch.equal(m_cu, cu) and m_mx == mx, case["name"]
+            assert torch.equal(PO.pad_input_ref(xs, idx, case["b"], case["s"]), back), case["name"]
+            rec.update(indices=idx, cu_seqlens=cu, max_seqlen=mx, unpadded=xs, repadded=back)
         elif kind == "rotary":
             x, cos, sin, off = gen_inputs(case)
             sq = case["sq"]

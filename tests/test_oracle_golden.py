@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from oracle import attention_oracle as O
+from oracle import padding_oracle as PO
 
 _spec = importlib.util.spec_from_file_location(
     "make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
@@ -74,6 +75,23 @@ def test_sink_and_window_bit_exact(golden):
             scale = torch.exp(lse1 - lse0).permute(0, 2, 1).unsqueeze(-1)
             keep = torch.isfinite(lse0).permute(0, 2, 1).unsqueeze(-1)
             assert torch.allclose(torch.where(keep, out1 * scale, out0), out0, atol=2e-6, rtol=1e-5), c["name"]
+
+
+def test_unpad_bit_exact(golden):
+    for c in _cases(golden, "unpad"):
+        x, mask = gen_inputs(c)
+        xs, idx, cu, mx = PO.unpad_input_ref(x, mask)
+        assert torch.equal(idx, c["indices"]) and torch.equal(cu, c["cu_seqlens"]) and mx == c["max_seqlen"], c["name"]
+        assert torch.equal(xs, c["unpadded"]), c["name"]
+        assert torch.equal(PO.pad_input_ref(xs, idx, c["b"], c["s"]), c["repadded"]), c["name"]
+
+
+def test_block_map_known_answer():
+    """The worked example of the reference's docstring (flash_attn/utils/sparse_utils.py:537-541)."""
+    bm = torch.tensor([[[[0, 0, 1, 0, 0, 1, 0, 1, 0, 1]]]], dtype=torch.bool)
+    off, cnt = PO.block_map_to_block_offset_ref(bm)
+    assert off[0, 0, 0, :4].tolist() == [2, 5, 7, 9] and torch.all(off[0, 0, 0, 4:] == 10000000)
+    assert cnt.tolist() == [[[4]]]
 
 
 def test_rotary_bit_exact(golden):
