@@ -37,6 +37,22 @@ def split_page_range(num_pages: int, world_size: int, rank: int) -> Tuple[int, i
     return first, first + base + (1 if rank < rem else 0)
 
 
+def window_for_slice(seqlen_total: int, slice_first: int, slice_len: int, window_left: int) -> Tuple[int, int]:
+    """Sliding window of a decode step seen from one rank's slice [slice_first, slice_first + slice_len) of the
+    sequence's keys.  The query token (position seqlen_total - 1) sees keys lo .. seqlen_total - 1 with
+    lo = max(0, seqlen_total - 1 - window_left) (window_left < 0: all).  Returns (local length, local window_left) to
+    hand to the decode call on the slice: length 0 if the slice lies wholly before the window, window -1 if it lies
+    wholly inside."""
+    if window_left < 0:
+        return slice_len, -1
+    lo = max(0, seqlen_total - 1 - window_left)
+    if lo >= slice_first + slice_len:
+        return 0, -1
+    if lo <= slice_first:
+        return slice_len, -1
+    return slice_len, slice_len - 1 - (lo - slice_first)
+
+
 def gather_partials(o_partial: torch.Tensor, lse_partial: torch.Tensor,
                     group: Optional[dist.ProcessGroup] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """All-gather per-rank partials: o_partial (rows, d) fp32 and lse_partial (rows,) fp32 ->
@@ -56,19 +72,20 @@ def gather_partials(o_partial: torch.Tensor, lse_partial: torch.Tensor,
 
 def decode_split_across_gpus(q, k_cache_local, v_cache_local, local_seqlens, local_block_table, softmax_scale=None,
                              group: Optional[dist.ProcessGroup] = None, out_dtype=torch.bfloat16, q_descale=None,
-                             k_descale=None, v_descale=None):
+                             k_descale=None, v_descale=None, s_aux=None, local_window_left: int = -1):
     """Decode where each rank holds a slice of every sequence's KV pages.  q: (b, 1, h, 128), identical on every
-    rank; the caches, `local_seqlens` and `local_block_table` describe this rank's slice.  Returns
-    (out (b, 1, h, 128) out_dtype, lse (b, h) fp32), identical on every rank."""
+    rank; the caches, `local_seqlens` and `local_block_table` describe this rank's slice.  Attention sinks
+    (``s_aux``, (h)) enter once, in the final combine; a sliding window is given per slice (``window_for_slice``).
+    Returns (out (b, 1, h, 128) out_dtype, lse (b, h) fp32), identical on every rank."""
     import flash_attn_2_cuda as cuda
     b, _, h, d = q.shape
     if softmax_scale is None:
         softmax_scale = d ** -0.5
     o_part, l_part = cuda.decode_partial(q, k_cache_local, v_cache_local, local_seqlens, local_block_table,
-                                         softmax_scale, q_descale, k_descale, v_descale)
+                                         softmax_scale, q_descale, k_descale, v_descale, window_left=local_window_left)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         o_all, l_all = gather_partials(o_part.view(b * h, d), l_part.view(b * h), group)
     else:
         o_all, l_all = o_part.view(1, b * h, d), l_part.view(1, b * h)
-    out, lse = cuda.combine(o_all, l_all, out_dtype=out_dtype, h=h)
+    out, lse = cuda.combine(o_all, l_all, out_dtype=out_dtype, h=h, s_aux=s_aux)
     return out.view(b, 1, h, d), lse.view(b, h)

@@ -627,9 +627,10 @@ def kv_append(q, kcache, vcache, k_new, v_new, seqlens_k, block_table, rotary_co
 
 
 def decode_partial(q, kcache, vcache, seqlens_k, block_table, softmax_scale, q_descale=None, k_descale=None,
-                   v_descale=None, max_seqlen_k=0):
+                   v_descale=None, max_seqlen_k=0, window_left=-1):
     """Decode over a LOCAL slice of each sequence's pages and return the unnormalised-merge inputs
-    (o_partial fp32 (b, h, d), lse fp32 (b, h)) for a cross-GPU combine (one sequence split-KV across GPUs)."""
+    (o_partial fp32 (b, h, d), lse fp32 (b, h)) for a cross-GPU combine (one sequence split-KV across GPUs).
+    ``window_left`` >= 0: only the last window_left + 1 keys of the slice are visible."""
     _check_qkv(q, kcache, vcache)
     b, sq, h, d = q.shape
     _require(sq == 1, "decode_partial takes one query token per sequence")
@@ -638,6 +639,7 @@ def decode_partial(q, kcache, vcache, seqlens_k, block_table, softmax_scale, q_d
     p = _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, None, None, q_descale, k_descale,
                        v_descale, 0, max_seqlen_k)
     p.o_partial_out, p.lse_partial_out = o_part.data_ptr(), lse_part.data_ptr()
+    _set_window(p, window_left, -1)
     with torch.cuda.device(q.device):
         ws = _workspace(q.device, int(_lib.fa_b200_decode_workspace_bytes(ctypes.byref(p))))
         if ws is not None:

@@ -46,7 +46,25 @@ def _worker(rank, world, port, ret):
         ok = torch.allclose(merged, full[0, 0], atol=1e-5) and torch.allclose(lse, lse_full[0, :, 0], atol=1e-5)
         # rank-major layout: slot r of the gathered buffer is rank r's partial
         mine_ok = torch.equal(o_all[rank], o.reshape(h, d))
-        ret[rank] = bool(ok and mine_ok)
+        # the same exchange under a sliding window with attention sinks: each rank applies the window its slice sees
+        # (window_for_slice), the sink enters once, after the merge
+        win_ok = True
+        s_aux = torch.randn(h, generator=g)
+        for wl in (0, 3, 40, 90, 1000):
+            n_loc, wl_loc = P.window_for_slice(L, lo, hi - lo, wl)
+            if n_loc == 0:
+                o_w, l_w = torch.zeros(h, d), torch.full((h,), float("-inf"))
+            else:
+                o_w, l_w = O.attention_ref(q, k[:, lo:lo + n_loc], v[:, lo:lo + n_loc], out_dtype=torch.float32,
+                                           window_size=(wl_loc, -1))
+                o_w, l_w = o_w.reshape(h, d), l_w.reshape(h)
+            ow_all, lw_all = P.gather_partials(o_w.contiguous(), l_w.contiguous())
+            merged_w, lse_w = O.merge_partials_ref(ow_all, lw_all)
+            tot = torch.logaddexp(lse_w, s_aux)
+            merged_w = merged_w * torch.exp(lse_w - tot).unsqueeze(-1)
+            full_w, _ = O.attention_ref(q, k, v, out_dtype=torch.float32, window_size=(wl, -1), s_aux=s_aux)
+            win_ok = win_ok and torch.allclose(merged_w, full_w[0, 0], atol=1e-5)
+        ret[rank] = bool(ok and mine_ok and win_ok)
     finally:
         dist.destroy_process_group()
 
