@@ -205,6 +205,7 @@ const char* fa_b200_status_string(int s) {
     case FA_B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
     case FA_B200_ERR_TOO_LARGE: return "size beyond a built-in limit";
     case FA_B200_ERR_DEVICE_RANGE: return "a kernel skipped an out-of-range cache position, page id or rotary row";
+    case FA_B200_ERR_DEVICE_UNSUPPORTED: return "a kernel met device-resident input it does not take (vertical sparsity)";
   }
   return "unknown status";
 }
@@ -216,7 +217,7 @@ int fa_b200_device_status(void) {
   if (v != 0) {
     int zero = 0;
     cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
-    return (v & 0xffff) ? FA_B200_ERR_DEVICE_TIMEOUT : FA_B200_ERR_DEVICE_RANGE;
+    return (v & 0xffff) ? FA_B200_ERR_DEVICE_TIMEOUT : ((v & 0x10000) ? FA_B200_ERR_DEVICE_RANGE : FA_B200_ERR_DEVICE_UNSUPPORTED);
   }
   return FA_B200_OK;
 }
@@ -641,6 +642,7 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   if (sparse) {
     k.block_count = p->block_count;
     k.block_offset = p->block_offset;
+    k.column_count = p->column_count;
     k.num_q_blocks = p->num_q_blocks;
     k.nnz_s = p->nnz_s;
     k.block_m = p->block_m;

@@ -72,6 +72,7 @@ struct PrefillKernelParams {
   const float* v_descale;
   const int32_t* block_count;
   const int32_t* block_offset;
+  const int32_t* column_count;   // sparse lists: must be zero everywhere (a non-zero entry raises a status bit)
   // paged K/V (one-tile kernel only): k/v tensor maps are (d, h_k, row in page, page); keys of sequence b are the
   // first seqused_k[b] rows of the pages block_table[b * bt_stride + 0..]
   const int32_t* block_table;

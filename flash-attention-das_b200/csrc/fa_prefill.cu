@@ -98,6 +98,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       // block_offset holds ascending K row offsets of 64-row tiles; two adjacent entries form one
       // 128-key tile, a lone entry is a half tile (upper 64 keys masked).  bit 31 marks a half tile.
       const int64_t lrow = (static_cast<int64_t>(bidb) * p.h + head) * p.num_q_blocks + m_block;
+      if (p.column_count && p.column_count[lrow] != 0) atomicOr(p.status, 0x20000);   // vertical sparsity: not taken
       int cnt = p.block_count[lrow];
       cnt = max(0, min(cnt, p.nnz_s));
       const int32_t* offs = p.block_offset + lrow * p.nnz_s;

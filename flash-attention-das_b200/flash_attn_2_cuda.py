@@ -57,6 +57,7 @@ class FwdParams(ctypes.Structure):
         ("page_size", _c_i32), ("num_blocks", _c_i32),
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
         ("has_window", _c_i32), ("window_left", _c_i32), ("window_right", _c_i32),
+        ("column_count", _c_vp),
     ]
 
 
@@ -688,8 +689,10 @@ def fwd_sparse(q, k, v, block_count, block_offset, column_count, column_index, o
     for name, t in (("block_count", block_count), ("block_offset", block_offset)):
         _require(t.dtype == torch.int32 and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous int32 CUDA tensor")
     if column_count is not None:
-        _require(column_count.dtype == torch.int32, "column_count must have dtype int32")
-        _unsupported(bool((column_count != 0).any().item()), "vertical (column_index) sparsity")
+        # the vertical part of the pattern is not taken; the kernel checks the counts where it reads its lists (no host
+        # synchronisation here) and a non-zero one shows up in device_status()
+        _require(column_count.dtype == torch.int32 and column_count.is_cuda and column_count.is_contiguous(),
+                 "column_count must be a contiguous int32 CUDA tensor")
     # host rule of the reference: NUM_ROWS == ceil(Sq / (Sq <= 2048 ? 64 : 128)) (flash_api_sparse.cpp:127-137)
     block_m = 64 if sq <= 2048 else 128
     num_rows = (sq + block_m - 1) // block_m
@@ -713,6 +716,9 @@ def fwd_sparse(q, k, v, block_count, block_offset, column_count, column_index, o
     p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
     p.block_count, p.block_offset = block_count.data_ptr(), block_offset.data_ptr()
     p.num_q_blocks, p.nnz_s, p.block_m = num_rows, block_offset.shape[3], block_m
+    if column_count is not None:
+        _require(tuple(column_count.shape) == (b, h, num_rows), "column_count must have shape (batch, nheads, NUM_ROWS)")
+        p.column_count = column_count.data_ptr()
     _apply_profile_events(p)
     with torch.cuda.device(q.device):
         _check(_lib.fa_b200_fwd_sparse(ctypes.byref(p), _stream(q)), "fwd_sparse")

@@ -46,7 +46,8 @@ enum {
   FA_B200_ERR_ALIGN = 11,        /* base pointer not 16-byte aligned */
   FA_B200_ERR_DEVICE_TIMEOUT = 12, /* a bounded device-side wait gave up (reported by fa_b200_device_status) */
   FA_B200_ERR_TOO_LARGE = 13,    /* size beyond a fixed built-in limit */
-  FA_B200_ERR_DEVICE_RANGE = 14  /* a kernel skipped an out-of-range position or page id (fa_b200_device_status) */
+  FA_B200_ERR_DEVICE_RANGE = 14, /* a kernel skipped an out-of-range position or page id (fa_b200_device_status) */
+  FA_B200_ERR_DEVICE_UNSUPPORTED = 15 /* a kernel met device-resident input it does not take (fa_b200_device_status) */
 };
 
 /*
@@ -115,6 +116,11 @@ typedef struct fa_b200_fwd_params {
    * j iff  i + sk - sq - window_left <= j <= i + sk - sq + window_right;  a negative value leaves that side open.
    * is_causal forces window_right = 0.  Not available with tile lists (fa_b200_fwd_sparse). */
   int32_t has_window, window_left, window_right;
+  /* fa_b200_fwd_sparse only: the reference's vertical part of the sparsity pattern (column_count / column_index,
+   * flash_attn_interface.py:2778-2855) is not built; pass column_count (b, h, num_q_blocks) here and a row whose count
+   * is not zero is reported by fa_b200_device_status() as FA_B200_ERR_DEVICE_UNSUPPORTED (checked on the device: no host
+   * synchronisation).  NULL = not checked. */
+  const int32_t* column_count;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch
@@ -327,8 +333,9 @@ FA_B200_API const char* fa_b200_status_string(int status);
 /* Last cudaError_t / CUresult text recorded by a failing call on this thread ("" if none). */
 FA_B200_API const char* fa_b200_last_cuda_error(void);
 /* Reads (with a device synchronise) and clears the device-side status word of the current device:
- * 0, FA_B200_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up since the last call, or
- * FA_B200_ERR_DEVICE_RANGE if fa_b200_kv_append skipped an out-of-range position. */
+ * 0, FA_B200_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up since the last call,
+ * FA_B200_ERR_DEVICE_RANGE if fa_b200_kv_append skipped an out-of-range position, or
+ * FA_B200_ERR_DEVICE_UNSUPPORTED if fa_b200_fwd_sparse met a non-zero column_count. */
 FA_B200_API int fa_b200_device_status(void);
 FA_B200_API int fa_b200_abi_version(void);
 /* Number of kernels this library has launched in this process (for launch accounting). */

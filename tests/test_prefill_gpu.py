@@ -229,6 +229,13 @@ def test_sparse_manual_two_block_selection(fa):
     ref32, _ = O.attention_ref(q, ks, vs, out_dtype=torch.float32)
     ref_pt, _ = O.attention_ref(q, ks, vs, upcast=False, reorder_ops=True)
     assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what="sparse manual")
+    # the vertical part of the pattern is not taken: a non-zero column_count is caught on the device (the call itself
+    # does not synchronise) and reported by the status word
+    cc[1, 0, 2] = 3
+    flash_attn.sparse_attn_func(q.cuda(), k.cuda(), v.cuda(), cnt.cuda(), offs.cuda(), cc.cuda(), ci.cuda(), causal=False)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 15      # FA_B200_ERR_DEVICE_UNSUPPORTED, cleared by the read
+    assert cuda.device_status() == 0
 
 
 def test_prefill_rejects_what_the_path_does_not_do(fa):
