@@ -44,7 +44,8 @@ __host__ __device__ constexpr SmemLayoutInfo smem_layout() {
   return s;
 }
 
-template <int DT>
+// kLeftWindow: the launch has a left sliding-window bound (kept out of the common build of the softmax loop).
+template <int DT, bool kLeftWindow>
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const PrefillKernelParams p) {
@@ -242,8 +243,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     // rows decide (warp-uniformly) whether a tile needs masking
     const int row_limit = row_hi(p, row_in_seq, sk, causal_shift);
     const int warp_limit = row_hi(p, m0 + lane_grp * 32, sk, causal_shift);
-    const int row_first = row_lo(p, row_in_seq, causal_shift);
-    const int warp_first = row_lo(p, m0 + lane_grp * 32 + 31, causal_shift);
+    const int row_first = kLeftWindow ? row_lo(p, row_in_seq, causal_shift) : 0;
+    const int warp_first = kLeftWindow ? row_lo(p, m0 + lane_grp * 32 + 31, causal_shift) : 0;
 
     float scale_log2 = p.scale_log2;
     if (p.q_descale) scale_log2 *= p.q_descale[bidb * p.qds_b + hk * p.qds_h];
@@ -259,8 +260,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (p.sparse) { const int v = sm_tiles[j]; start = v & 0x7fffffff; half_tile = (v < 0); }
       int lim = row_limit - start;
       if (half_tile) lim = min(lim, 64);
-      softmax_tile<DT>(t_s, t_o, scale_log2, row_first - start, lim,
-                       half_tile || start + kBlockN > warp_limit || start < warp_first, j == 0, st);
+      softmax_tile<DT>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, lim,
+                       half_tile || start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st);
       if (p.paged && start + kBlockN > sk) {
         // Last tile of a paged sequence: key rows past the end were not fetched, or hold whatever the page holds
         // there.  Their P is zero, but 0 * NaN would still poison O, so this thread clears V row `row` of the tile
@@ -314,15 +315,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 template <int DT>
 cudaError_t launch_single_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const PrefillKernelParams& p, cudaStream_t stream) {
-  auto kern = prefill_kernel<DT>;
+  const bool win = p.window_left >= 0;
+  auto kern = win ? prefill_kernel<DT, true> : prefill_kernel<DT, false>;
   const size_t smem = 1024 + smem_layout<DT>().total;
-  static bool attr_done[64] = {};
+  static bool attr_done[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && !attr_done[dev]) {
+  if (dev < 64 && !attr_done[win][dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    attr_done[dev] = true;
+    attr_done[win][dev] = true;
   }
   dim3 grid(p.h, p.num_m_blocks, p.b);
   kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);
