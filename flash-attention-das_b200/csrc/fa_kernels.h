@@ -96,6 +96,7 @@ struct PrefillKernelParams {
   float scale_log2;
   const void* s_aux;         // attention sinks (h), applied in the epilogue
   int32_t s_aux_dtype;
+  int* work_counter;         // persistent kernels: zeroed before the launch; CTAs claim work items past their first from it
 };
 // One 128-row query tile per CTA, two CTAs per SM: block-sparse lists and odd GQA groups.
 cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
