@@ -15,6 +15,11 @@ namespace {
 // Device-side status word (one per device that loads the library).
 __device__ int g_device_status = 0;
 
+// Work counters of the persistent prefill launches in flight: a launch takes the next slot of the pool and zeroes it on
+// its stream; the CTAs claim their work items from it.  64 slots: as many launches may overlap on one device.
+constexpr int kCounterSlots = 64;
+__device__ int g_work_counters[kCounterSlots];
+
 std::atomic<uint64_t> g_launches{0};
 thread_local char g_last_error[256] = "";
 
@@ -52,6 +57,21 @@ int* status_ptr() {
     ptrs[dev] = static_cast<int*>(ptr);
   }
   return ptrs[dev];
+}
+
+int* next_work_counter(cudaStream_t stream) {
+  static int* base[64] = {};
+  static std::atomic<unsigned> next_slot{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_work_counters) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<int*>(ptr);
+  }
+  int* c = base[dev] + (next_slot.fetch_add(1, std::memory_order_relaxed) % kCounterSlots);
+  if (cudaMemsetAsync(c, 0, sizeof(int), stream) != cudaSuccess) return nullptr;
+  return c;
 }
 
 int elem_size(int dtype) { return dtype == FA_B200_E4M3 ? 1 : 2; }
@@ -650,7 +670,6 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   } else {
     k.num_m_blocks = (p->seqlen_q + 127) / 128;
   }
-  if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
   // Kernel choice.  Dense / varlen prefill with an even GQA group: persistent CTAs that work on two heads of the
   // group at once and share every K/V tile ("pair").  Other head layouts (MHA, odd groups): persistent CTAs with
   // double-buffered scores ("dense").  Tile lists are per head and run one tile per CTA ("single").
@@ -662,6 +681,11 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     else if (!strcmp(ov, "pair") && !sparse && !paged && even_group) which = 1;
     else if (!strcmp(ov, "dense") && !sparse && !paged) which = 2;
   }
+  if (which != 0) {   // the persistent kernels claim their work items from a counter
+    k.work_counter = next_work_counter(stream);
+    if (!k.work_counter) return cuda_fail("work counter", cudaGetLastError());
+  }
+  if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
   cudaError_t e = which == 2   ? launch_prefill_dense(p->dtype, tq, tk, tv, k, stream)
                   : which == 1 ? launch_prefill_pair(p->dtype, tq, tk, tv, to, k, stream)
                                : launch_prefill_single(p->dtype, tq, tk, tv, k, stream);

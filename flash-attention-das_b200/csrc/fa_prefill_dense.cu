@@ -35,6 +35,8 @@ namespace {
 constexpr int kSlots = 6;         // ring of 32 KB (16 KB e4m3) tiles: Q, K_0, V_0, K_1, V_1, ... of item after item
 constexpr int kSoftmaxWGs = 2;                    // warpgroups sharing a tile's key columns
 constexpr int kCols = kBlockN / kSoftmaxWGs;      // key (and output) columns per softmax thread
+constexpr int kIdSlots = 4;       // claimed work item indices handed from the producer to the other roles
+constexpr int kIdReaders = 2 + 4 * kSoftmaxWGs;   // the two MMA issuers and every softmax warp read each index
 constexpr int kSoftmaxWarps = 4 * kSoftmaxWGs;
 constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;   // kMmaWarp + 1: second MMA issuer
 constexpr int kThreads = 32 * (kSoftmaxWarps + 4);
@@ -51,7 +53,7 @@ __host__ __device__ constexpr DenseSmem dense_smem() {
   s.ring_off = 0;
   s.bar_off = s.ring_off + kSlots * T::kTileBytes;
   // s_full[2] p_full[2] o_full o_empty ring_full[kSlots] ring_empty[kSlots]
-  s.xch_off = s.bar_off + 8 * (6 + 2 * kSlots);
+  s.xch_off = s.bar_off + 8 * (6 + 2 * kSlots + 2 * kIdSlots);
   s.misc_off = s.xch_off + 4 * 2 * kSoftmaxWGs * 128;
   s.total = s.misc_off + 32;
   return s;
@@ -96,13 +98,6 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
   return true;
 }
 
-// Next item of this CTA at or after virtual index li that has key tiles (the ones that use the pipeline).
-__device__ __forceinline__ bool next_work_item(const PrefillKernelParams& p, int& li, int total, Item& it) {
-  for (; li < total; li += gridDim.x) {
-    if (get_item(p, li, it) && it.n_tiles > 0) return true;
-  }
-  return false;
-}
 
 __device__ __forceinline__ void softmax_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(32 * kSoftmaxWarps) : "memory");
@@ -124,6 +119,9 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* ring_full = o_empty + 1;    // [kSlots] tile landed                       (TMA transaction bytes)
   uint64_t* ring_empty = ring_full + kSlots;  // [kSlots] tile consumed: Q after its copy to TMEM and V after its P V
                                         //      (tcgen05.commit), K after its scores are complete (a softmax thread)
+  uint64_t* id_full = ring_empty + kSlots;    // [kIdSlots] a claimed item index is published     (the producer)
+  uint64_t* id_empty = id_full + kIdSlots;    // [kIdSlots] every reader has taken it
+  int* id_ring = reinterpret_cast<int*>(smem + L.misc_off + 12);   // [kIdSlots]
   float* xch = reinterpret_cast<float*>(smem + L.xch_off);   // [2 parity][kSoftmaxWGs column groups][128 rows]
   uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc_off + 8);
@@ -144,6 +142,10 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_init(smem_u32(&ring_full[s]), 1);
       mbar_init(smem_u32(&ring_empty[s]), 1);
     }
+    for (int s = 0; s < kIdSlots; ++s) {
+      mbar_init(smem_u32(&id_full[s]), 1);
+      mbar_init(smem_u32(&id_empty[s]), kIdReaders);
+    }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -158,6 +160,17 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *sm_tmem_base;
   const uint32_t ring_smem = smem_u32(smem + L.ring_off);
+
+  // Work items are claimed in order from a global counter by the producer (a fixed stride over the item grid leaves the
+  // CTAs of a varlen batch unevenly loaded) and their indices handed to the other roles through a small ring; -1 ends
+  // the stream.  `take` returns the idx-th index of the stream (-2 if the wait gave up); one thread per reader releases.
+  auto take = [&](uint32_t idx, bool release) -> int {
+    const uint32_t slot = idx % kIdSlots;
+    if (!mbar_wait(smem_u32(&id_full[slot]), (idx / kIdSlots) & 1u, wctx)) return -2;
+    const int v = *reinterpret_cast<volatile int*>(&id_ring[slot]);
+    if (release) mbar_arrive(smem_u32(&id_empty[slot]));
+    return v;
+  };
 
   if (warp == kProducerWarp) {
     // ================================================================== TMA producer
@@ -175,14 +188,29 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         pos.advance(1);
         return true;
       };
+      uint32_t pub = 0;
+      auto publish = [&](int v) -> bool {
+        const uint32_t slot = pub % kIdSlots;
+        if (!mbar_wait(smem_u32(&id_empty[slot]), ((pub / kIdSlots) & 1u) ^ 1u, wctx)) return false;
+        id_ring[slot] = v;
+        mbar_arrive(smem_u32(&id_full[slot]));
+        ++pub;
+        return true;
+      };
       Item it;
-      for (int li = blockIdx.x; ok && next_work_item(p, li, total_items, it); li += gridDim.x) {
+      int li = blockIdx.x;
+      int li_next = static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);   // claimed one item ahead
+      for (; ok && li < total_items; li = li_next, li_next = static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1)) {
+        if (!get_item(p, li, it)) continue;
+        if (!publish(li)) { ok = false; break; }
+        if (it.n_tiles == 0) continue;
         ok = load_tile(&tmap_q, it.head, it.q_row0 + it.m0, it.coord_b);
         for (int j = 0; ok && j < it.n_tiles; ++j) {
           ok = load_tile(&tmap_k, it.hk, it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b) &&
                load_tile(&tmap_v, it.hk, it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b);
         }
       }
+      if (ok) publish(-1);
     }
   } else if (warp == kMmaWarp) {
     // ================================================================== MMA issuer 1: Q staging and S = Q K^T
@@ -196,7 +224,11 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       [[maybe_unused]] int tr = 0;
       bool ok = true;
       Item it;
-      for (int li = blockIdx.x; ok && next_work_item(p, li, total_items, it); li += gridDim.x) {
+      for (uint32_t idx = 0; ok; ++idx) {
+        const int li = take(idx, true);
+        if (li < 0) { ok = (li == -1); break; }
+        get_item(p, li, it);
+        if (it.n_tiles == 0) continue;
         // item's Q: ring -> TMEM.  The copy runs in issue order with this thread's MMAs, so it cannot overtake the
         // Q K^T products of the item before last, which read the same TMEM columns.
         const uint32_t q_tmem = tmem_base + kColQ + (item_cnt & 1u) * 64;
@@ -234,7 +266,11 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       [[maybe_unused]] int tr = 600;
       bool ok = true;
       Item it;
-      for (int li = blockIdx.x; ok && next_work_item(p, li, total_items, it); li += gridDim.x) {
+      for (uint32_t idx = 0; ok; ++idx) {
+        const int li = take(idx, true);
+        if (li < 0) { ok = (li == -1); break; }
+        get_item(p, li, it);
+        if (it.n_tiles == 0) continue;
         const int n = it.n_tiles;
         for (int j = 0; j < n; ++j) {
           FA_TRACE(2, tr, 10);
@@ -272,9 +308,13 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     bool ok = true;
     // A wait that gives up sets ok = false but the loops keep their shape (the named barriers below are not
     // bounded, so every softmax thread must reach each of them); results are discarded.
-    for (int li = blockIdx.x; li < total_items; li += gridDim.x) {
+    for (uint32_t idx = 0;; ++idx) {
+      const int li = take(idx, false);
+      __syncwarp();
+      if (lane == 0 && li != -2) mbar_arrive(smem_u32(&id_empty[idx % kIdSlots]));
+      if (li < 0) break;
       Item it;
-      if (!get_item(p, li, it)) continue;
+      get_item(p, li, it);
       const int row_in_seq = it.m0 + row;
       const int64_t grow = static_cast<int64_t>(it.q_row0) + row_in_seq;
       if (it.n_tiles == 0) {
@@ -485,6 +525,7 @@ cudaError_t launch_dense_t(const CUtensorMap& tq, const CUtensorMap& tk, const C
   const long long total = static_cast<long long>(p.h) * p.b * p.num_m_blocks;
   if (total <= 0) return cudaSuccess;
   const int grid = static_cast<int>(total < num_sms[dev] ? total : num_sms[dev]);
+  if (!p.work_counter) return cudaErrorInvalidValue;
   kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);
   return cudaGetLastError();
 }

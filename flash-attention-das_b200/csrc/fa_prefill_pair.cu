@@ -18,8 +18,6 @@
 // Same math as the reference's dense forward (csrc/flash_attn_cutlass/src/flash_fwd_kernel.h:2818-3328, FP8
 // 3330-3778; softmax.h:592-640,932-964); the heaviest-first order plays the role of the reference's reversed
 // m_block launch order (flash_fwd_kernel.h:8684).
-#include <atomic>
-
 #include "fa_prefill_common.cuh"
 
 namespace fa {
@@ -480,10 +478,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   }
 }
 
-// Work counters of the launches in flight: a launch takes the next slot of the pool and zeroes it on its stream.
-constexpr int kCounterSlots = 64;
-__device__ int g_work_counters[kCounterSlots];
-
 template <int DT>
 cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                           const PrefillKernelParams& p, cudaStream_t stream) {
@@ -505,19 +499,8 @@ cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   const long long total = static_cast<long long>(p.h / 2) * p.b * p.num_m_blocks;
   if (total <= 0) return cudaSuccess;
   const int grid = static_cast<int>(total < num_sms[dev] ? total : num_sms[dev]);
-  static int* counters[64] = {};
-  static std::atomic<unsigned> next_slot{0};
-  if (!counters[dev]) {
-    void* ptr = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&ptr, g_work_counters);
-    if (e != cudaSuccess) return e;
-    counters[dev] = static_cast<int*>(ptr);
-  }
-  PrefillKernelParams pk = p;
-  pk.work_counter = counters[dev] + (next_slot.fetch_add(1, std::memory_order_relaxed) % kCounterSlots);
-  cudaError_t e = cudaMemsetAsync(pk.work_counter, 0, sizeof(int), stream);
-  if (e != cudaSuccess) return e;
-  kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, pk);
+  if (!p.work_counter) return cudaErrorInvalidValue;
+  kern<<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, p);
   return cudaGetLastError();
 }
 
