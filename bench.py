@@ -8,7 +8,8 @@ paged-KV bf16 decode configuration (batch 64, context 1024..32768, page 256, 32/
 `value` is whole-job HBM GB/s of ALGORITHMIC bytes (KV bytes read once + q/out + block table) with the cache
 resident in HBM; `e2e` is the same metric through the public Python API with the step's inputs (q,
 cache_seqlens, block_table) coming from pinned host memory and the output read back to the host inside the
-timed region.  The varlen causal bf16 prefill configuration is timed in the same run and reported under
+timed region, every step; the decode and prefill workloads run those steps as a serving loop would, on three
+streams with two sets of device buffers, so that one step's copies overlap its neighbours' attention.  The varlen causal bf16 prefill configuration is timed in the same run and reported under
 `also` (TFLOP/s, reference FLOP convention 4*S^2*H*D/2 per sequence).
 
 Multi-GPU (torchrun, one rank per GPU): every rank runs the same per-GPU workload on its own seeded data with
@@ -151,6 +152,51 @@ def _randn_into(t, g, chunk=1 << 26):
         flat[i:i + n] = torch.randn(n, generator=g, device=t.device, dtype=torch.float32).to(t.dtype)
 
 
+class E2EPipeline:
+    """End-to-end steps as a serving loop would run them: three streams (host->device copies, the attention call,
+    device->host copy of the result) and two sets of device buffers, so that the copies of one step overlap the
+    attention of its neighbours.  Every step still moves its own inputs from pinned host memory and its own result
+    back; ``begin`` / ``end`` tie the three streams to the stream the timing events are recorded on."""
+
+    def __init__(self, dev):
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]
+        self.ev_run = [torch.cuda.Event() for _ in range(2)]
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]
+        self.i = 0
+
+    def begin(self):
+        cur = torch.cuda.current_stream()
+        for st in (self.s_in, self.s_run, self.s_out):
+            st.wait_stream(cur)
+
+    def end(self):
+        cur = torch.cuda.current_stream()
+        for st in (self.s_in, self.s_run, self.s_out):
+            cur.wait_stream(st)
+
+    def step(self, copy_in, run, copy_out):
+        """copy_in(buf), run(buf), copy_out(buf) are issued on their streams for buffer set buf = step parity."""
+        buf = self.i & 1
+        first_use = self.i < 2
+        self.i += 1
+        with torch.cuda.stream(self.s_in):
+            if not first_use:
+                self.s_in.wait_event(self.ev_run[buf])     # the attention that read these inputs two steps ago
+            copy_in(buf)
+            self.ev_in[buf].record(self.s_in)
+        with torch.cuda.stream(self.s_run):
+            self.s_run.wait_event(self.ev_in[buf])
+            if not first_use:
+                self.s_run.wait_event(self.ev_out[buf])    # the result buffer has been read back
+            run(buf)
+            self.ev_run[buf].record(self.s_run)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_run[buf])
+            copy_out(buf)
+            self.ev_out[buf].record(self.s_out)
+
+
 class DecodeWorkload:
     """Paged-KV decode: batch of single-token queries over a paged pool; block_table is a seeded random
     permutation of the pool."""
@@ -218,13 +264,29 @@ class DecodeWorkload:
         return self.fa.flash_attn_with_kvcache(self.q, self.kc, self.vc, cache_seqlens=self.sl, block_table=self.bt,
                                                causal=True, **self.kw)
 
+    def e2e_setup(self):
+        dev = self.q.device
+        self.pipe = E2EPipeline(dev)
+        self.d_q = [torch.empty_like(self.q) for _ in range(2)]
+        self.d_bt = [torch.empty_like(self.bt) for _ in range(2)]
+        self.d_sl = [torch.empty_like(self.sl) for _ in range(2)]
+        self.d_out = [torch.empty(self.batch, 1, H, D, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.out_hosts = [self.out_host, torch.empty_like(self.out_host).pin_memory()]
+
     def step_e2e(self):
-        q = self.q_host.to(self.q.device, non_blocking=True)
-        bt = self.bt_host.to(self.q.device, non_blocking=True)
-        sl = self.sl_host.to(self.q.device, non_blocking=True)
-        out = self.fa.flash_attn_with_kvcache(q, self.kc, self.vc, cache_seqlens=sl, block_table=bt, causal=True, **self.kw)
-        self.out_host.copy_(out, non_blocking=True)
-        return out
+        def copy_in(b):
+            self.d_q[b].copy_(self.q_host, non_blocking=True)
+            self.d_bt[b].copy_(self.bt_host, non_blocking=True)
+            self.d_sl[b].copy_(self.sl_host, non_blocking=True)
+
+        def run(b):
+            self.fa.flash_attn_with_kvcache(self.d_q[b], self.kc, self.vc, cache_seqlens=self.d_sl[b], block_table=self.d_bt[b],
+                                            causal=True, out=self.d_out[b], **self.kw)
+
+        def copy_out(b):
+            self.out_hosts[b].copy_(self.d_out[b], non_blocking=True)
+
+        self.pipe.step(copy_in, run, copy_out)
 
 
 class PrefillWorkload:
@@ -269,13 +331,29 @@ class PrefillWorkload:
         return self.fa.flash_attn_varlen_func(self.q, self.k, self.v, self.cu, self.cu, self.maxlen, self.maxlen,
                                               causal=True, **self.kw)
 
-    def step_e2e(self):
+    def e2e_setup(self):
         dev = self.q.device
-        q, k, v = [t.to(dev, non_blocking=True) for t in (self.q_host, self.k_host, self.v_host)]
-        cu = self.cu_host.to(dev, non_blocking=True)
-        out = self.fa.flash_attn_varlen_func(q, k, v, cu, cu, self.maxlen, self.maxlen, causal=True, **self.kw)
-        self.out_host.copy_(out, non_blocking=True)
-        return out
+        self.pipe = E2EPipeline(dev)
+        self.d_qkv = [[torch.empty_like(t) for t in (self.q, self.k, self.v)] for _ in range(2)]
+        self.d_cu = [torch.empty_like(self.cu) for _ in range(2)]
+        self.d_out = [torch.empty(self.q.shape[0], H, D, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.out_hosts = [self.out_host, torch.empty_like(self.out_host).pin_memory()]
+
+    def step_e2e(self):
+        def copy_in(b):
+            for dst, src in zip(self.d_qkv[b], (self.q_host, self.k_host, self.v_host)):
+                dst.copy_(src, non_blocking=True)
+            self.d_cu[b].copy_(self.cu_host, non_blocking=True)
+
+        def run(b):
+            q, k, v = self.d_qkv[b]
+            self.fa.flash_attn_varlen_func(q, k, v, self.d_cu[b], self.d_cu[b], self.maxlen, self.maxlen, causal=True,
+                                           out=self.d_out[b], **self.kw)
+
+        def copy_out(b):
+            self.out_hosts[b].copy_(self.d_out[b], non_blocking=True)
+
+        self.pipe.step(copy_in, run, copy_out)
 
 
 def tile_mask_to_block_lists(tile_mask):
@@ -430,14 +508,22 @@ def sum_over_ranks(x, world, dev):
     return float(t.item())
 
 
-def time_steps(fn, steps, warmup, world, dev):
+def time_steps(fn, steps, warmup, world, dev, pipe=None):
+    """Average device time of `steps` calls after `warmup`, max over ranks.  With a pipeline (side streams), the side
+    streams start behind the first event and the second event waits for all of them."""
     for _ in range(warmup):
         fn()
+    if pipe is not None:
+        pipe.end()
     barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    if pipe is not None:
+        pipe.begin()
     for _ in range(steps):
         fn()
+    if pipe is not None:
+        pipe.end()
     e1.record()
     barrier(world)
     return max_over_ranks(e0.elapsed_time(e1), world, dev) / steps
@@ -472,7 +558,9 @@ def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
         l0 = flash_attn_2_cuda.launch_count()
         ms = time_steps(wl.step, args.steps, args.warmup, world, dev)
         launches = (flash_attn_2_cuda.launch_count() - l0) // (args.steps + args.warmup) * args.steps
-        ms_e2e = time_steps(wl.step_e2e, args.steps, args.warmup, world, dev)
+        if hasattr(wl, "e2e_setup"):
+            wl.e2e_setup()
+        ms_e2e = time_steps(wl.step_e2e, args.steps, args.warmup, world, dev, getattr(wl, "pipe", None))
     clocks = cs.summary()
     total_units = sum_over_ranks(wl.units, world, dev)
     value = total_units / (ms * 1e-3) / div
