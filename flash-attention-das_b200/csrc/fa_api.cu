@@ -394,6 +394,9 @@ int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
   k.out_scale = p->out_scale;
   k.s_aux = p->s_aux;
   k.s_aux_dtype = p->s_aux_dtype;
+  k.o_part_stride = p->o_part_stride > 0 ? p->o_part_stride : static_cast<int64_t>(p->rows) * kHeadDim;
+  k.lse_part_stride = p->lse_part_stride > 0 ? p->lse_part_stride : p->rows;
+  if (k.o_part_stride % 4 != 0) return FA_B200_ERR_STRIDE;
   cudaError_t e = launch_combine(k, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("combine launch", e);
   if (p->rows > 0) g_launches++;
@@ -487,6 +490,8 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
     c.h = p->h;
     c.partition_tokens = pl.partition_tokens;
     c.out_scale = 1.f;
+    c.o_part_stride = static_cast<int64_t>(c.rows) * kHeadDim;
+    c.lse_part_stride = c.rows;
     if (p->o_partial_out) {
       c.out = p->o_partial_out;
       c.lse = p->lse_partial_out;

@@ -26,10 +26,9 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   if (p.parts_per_row) nparts = min(nparts, p.parts_per_row[bi]);
   else if (p.seqlens) nparts = min(nparts, (p.seqlens[bi] + p.partition_tokens - 1) / p.partition_tokens);
 
-  const int64_t rows = p.rows;
   float mx = -INFINITY;
   for (int i = threadIdx.x; i < nparts; i += kCombineWarps * 32) {
-    float l = p.lse_partial[i * rows + row];
+    float l = p.lse_partial[i * p.lse_part_stride + row];
     if (l == INFINITY) l = -INFINITY;
     mx = fmaxf(mx, l);
   }
@@ -41,7 +40,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   float sum = 0.f;
   if (mx != -INFINITY) {
     for (int i = threadIdx.x; i < nparts; i += kCombineWarps * 32) {
-      float l = p.lse_partial[i * rows + row];
+      float l = p.lse_partial[i * p.lse_part_stride + row];
       if (l == INFINITY) l = -INFINITY;
       sum += expf(l - mx);
     }
@@ -69,8 +68,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
       float4 v[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        l[j] = p.lse_partial[(i + j * kCombineWarps) * rows + row];
-        v[j] = op[((i + j * kCombineWarps) * rows + row) * (kHeadDim / 4)];
+        l[j] = p.lse_partial[(i + j * kCombineWarps) * p.lse_part_stride + row];
+        v[j] = op[((i + j * kCombineWarps) * p.o_part_stride + row * kHeadDim) / 4];
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -80,8 +79,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
       }
     }
     for (; i < nparts; i += kCombineWarps) {
-      const float l = p.lse_partial[i * rows + row];
-      const float4 v = op[(i * rows + row) * (kHeadDim / 4)];
+      const float l = p.lse_partial[i * p.lse_part_stride + row];
+      const float4 v = op[(i * p.o_part_stride + row * kHeadDim) / 4];
       const float w = (l == INFINITY || l == -INFINITY) ? 0.f : expf(l - lse_tot);
       if (w != 0.f) { acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w; }
     }

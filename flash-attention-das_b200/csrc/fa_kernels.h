@@ -42,8 +42,9 @@ cudaError_t launch_decode(int dtype, const CUtensorMap& tmap_k, const CUtensorMa
                           const DecodeKernelParams& p, cudaStream_t stream);
 
 struct CombineKernelParams {
-  const float* o_partial;    // [num_parts][rows][128]
-  const float* lse_partial;  // [num_parts][rows]
+  const float* o_partial;    // [num_parts][rows][128], partitions o_part_stride floats apart
+  const float* lse_partial;  // [num_parts][rows], partitions lse_part_stride floats apart
+  int64_t o_part_stride, lse_part_stride;
   void* out;
   float* lse;
   const int32_t* seqlens;    // optional: row r uses ceil(seqlens[r / h] / partition_tokens) parts

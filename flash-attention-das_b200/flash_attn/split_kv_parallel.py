@@ -84,7 +84,18 @@ def decode_split_across_gpus(q, k_cache_local, v_cache_local, local_seqlens, loc
     o_part, l_part = cuda.decode_partial(q, k_cache_local, v_cache_local, local_seqlens, local_block_table,
                                          softmax_scale, q_descale, k_descale, v_descale, window_left=local_window_left)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
-        o_all, l_all = gather_partials(o_part.view(b * h, d), l_part.view(b * h), group)
+        rows = b * h
+        if (o_part.is_cuda and (rows * (d + 1)) % 4 == 0 and
+                o_part.untyped_storage().data_ptr() == l_part.untyped_storage().data_ptr()):
+            # decode_partial returns [O | LSE] in one buffer: one all-gather moves both
+            world = dist.get_world_size(group)
+            packed = torch.empty((world, rows * (d + 1)), dtype=torch.float32, device=o_part.device)
+            mine = torch.as_strided(o_part, (rows * (d + 1),), (1,), o_part.storage_offset())
+            dist.all_gather_into_tensor(packed.view(-1), mine, group=group)
+            o_all = packed[:, :rows * d].unflatten(1, (rows, d))
+            l_all = packed[:, rows * d:]
+        else:
+            o_all, l_all = gather_partials(o_part.view(rows, d), l_part.view(rows), group)
     else:
         o_all, l_all = o_part.view(1, b * h, d), l_part.view(1, b * h)
     out, lse = cuda.combine(o_all, l_all, out_dtype=out_dtype, h=h, s_aux=s_aux)

@@ -95,6 +95,7 @@ class CombineParams(ctypes.Structure):
         ("num_parts", _c_i32), ("rows", _c_i32), ("d", _c_i32), ("h", _c_i32),
         ("parts_per_row", _c_vp), ("out_dtype", _c_i32), ("out_scale", _c_f32),
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
+        ("o_part_stride", _c_i64), ("lse_part_stride", _c_i64),
     ]
 
 
@@ -635,8 +636,9 @@ def decode_partial(q, kcache, vcache, seqlens_k, block_table, softmax_scale, q_d
     _check_qkv(q, kcache, vcache)
     b, sq, h, d = q.shape
     _require(sq == 1, "decode_partial takes one query token per sequence")
-    o_part = torch.empty((b, h, d), dtype=torch.float32, device=q.device)
-    lse_part = torch.empty((b, h), dtype=torch.float32, device=q.device)
+    # one buffer, [O | LSE] back to back: a cross-GPU exchange moves it with a single all-gather
+    packed = torch.empty((b * h * (d + 1),), dtype=torch.float32, device=q.device)
+    o_part, lse_part = packed[:b * h * d].view(b, h, d), packed[b * h * d:].view(b, h)
     p = _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, None, None, q_descale, k_descale,
                        v_descale, 0, max_seqlen_k)
     p.o_partial_out, p.lse_partial_out = o_part.data_ptr(), lse_part.data_ptr()
@@ -653,7 +655,9 @@ def combine(o_partial, lse_partial, out_dtype=torch.bfloat16, h: Optional[int] =
     """LSE-combine: o_partial (parts, rows, 128) fp32, lse_partial (parts, rows) fp32 ->
     (out (rows, 128) out_dtype, lse (rows) fp32).  rows = batch * h; ``s_aux`` (h) adds each head's attention sink."""
     _require(o_partial.dtype == torch.float32 and lse_partial.dtype == torch.float32, "partials must be fp32")
-    _require(o_partial.is_contiguous() and lse_partial.is_contiguous(), "partials must be contiguous")
+    # partitions may be strided (partials gathered as one [O | LSE] buffer per rank); rows and columns are packed
+    _require(o_partial.dim() == 3 and o_partial.stride(2) == 1 and o_partial.stride(1) == o_partial.shape[2] and
+             lse_partial.dim() == 2 and lse_partial.stride(1) == 1, "partials must be packed within a partition")
     parts, rows, d = o_partial.shape
     out = torch.empty((rows, d), dtype=out_dtype, device=o_partial.device)
     lse = torch.empty((rows,), dtype=torch.float32, device=o_partial.device)
@@ -664,6 +668,7 @@ def combine(o_partial, lse_partial, out_dtype=torch.bfloat16, h: Optional[int] =
     p.parts_per_row = _ptr(parts_per_row)
     p.out_dtype = -1 if out_dtype == torch.float32 else _DT[out_dtype]
     p.out_scale = 1.0
+    p.o_part_stride, p.lse_part_stride = o_partial.stride(0), lse_partial.stride(0)
     _set_sinks(p, s_aux, h or 1)
     with torch.cuda.device(o_partial.device):
         _check(_lib.fa_b200_combine(ctypes.byref(p), _stream(o_partial)), "combine")

@@ -248,6 +248,9 @@ typedef struct fa_b200_combine_params {
   float out_scale;                     /* multiplies out (v_descale); 1.0 normally */
   const void* s_aux;                   /* optional attention sinks, (h) elements of s_aux_dtype: one more term of the sum */
   int32_t s_aux_dtype;
+  /* Floats between consecutive partitions of o_partial / lse_partial; 0 = packed (rows * d and rows).  Lets partials
+   * that were gathered as one buffer per rank ([O | LSE] back to back) be combined in place; multiples of 4. */
+  int64_t o_part_stride, lse_part_stride;
 } fa_b200_combine_params;
 
 FA_B200_API int fa_b200_combine(const fa_b200_combine_params* p, void* stream);

@@ -212,3 +212,26 @@ def test_paged_attention_binding_layouts(fa):
         torch.cuda.synchronize()
         assert cuda.device_status() == 0
         assert torch.equal(out, want), layout
+
+
+def test_combine_takes_strided_partitions(fa):
+    """Partials laid out as one [O | LSE] buffer per partition (what a single all-gather of decode_partial's output
+    produces) are combined in place, bit-identical to the packed layout."""
+    _, cuda = fa
+    g = gen(17)
+    parts, rows, d = 6, 32, 128
+    o = torch.randn(parts, rows, d, generator=g)
+    lse = torch.randn(parts, rows, generator=g) * 3
+    packed = torch.cat([o.reshape(parts, rows * d), lse], dim=1).cuda()          # (parts, rows * (d + 1))
+    o_v = packed[:, :rows * d].unflatten(1, (rows, d))
+    l_v = packed[:, rows * d:]
+    out1, l1 = cuda.combine(o_v, l_v, out_dtype=torch.float32, h=8)
+    out2, l2 = cuda.combine(o.cuda(), lse.cuda(), out_dtype=torch.float32, h=8)
+    assert torch.equal(out1, out2) and torch.equal(l1, l2)
+    # decode_partial hands back exactly that layout
+    kc, vc, bt, sl = make_paged(g, [300, 77], 2, 64, torch.bfloat16, poison=False)
+    q = randn(g, 2, 1, 8, 128).cuda()
+    op, lp = cuda.decode_partial(q, kc.cuda(), vc.cuda(), sl.cuda(), bt.cuda(), 128 ** -0.5)
+    assert op.untyped_storage().data_ptr() == lp.untyped_storage().data_ptr()
+    ref, ref_l = O.paged_decode_ref(q.cpu(), kc, vc, sl, bt, out_dtype=torch.float32)
+    assert max_err(op.cpu(), ref[:, 0]) < 2e-2 and max_err(lp.cpu(), ref_l[:, :, 0]) < 1e-3
