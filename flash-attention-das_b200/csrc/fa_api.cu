@@ -152,6 +152,7 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   if (p->b < 0 || p->h <= 0 || p->h_k <= 0 || p->max_blocks_per_seq < 0 || p->num_blocks < 0) { pl.status = FA_B200_ERR_SHAPE; return pl; }
   if (p->h % p->h_k != 0 || p->h / p->h_k > 16) { pl.status = FA_B200_ERR_HEADS; return pl; }
   pl.group = p->h / p->h_k;
+  if (p->seqlen_q < 0 || (p->seqlen_q > 1 && p->seqlen_q * pl.group > 16)) { pl.status = FA_B200_ERR_HEADS; return pl; }
   pl.tile = p->dtype == FA_B200_E4M3 ? 128 : 64;
   const int page = p->page_size;
   if (page >= 64) {
@@ -194,7 +195,8 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
 
 size_t decode_ws_bytes(const fa_b200_decode_params* p, const DecodePlan& pl) {
   if (!pl.split) return 0;
-  return static_cast<size_t>(pl.num_partitions) * p->b * p->h * (kHeadDim + 1) * sizeof(float);
+  const size_t sq = p->seqlen_q > 1 ? p->seqlen_q : 1;
+  return static_cast<size_t>(pl.num_partitions) * p->b * p->h * sq * (kHeadDim + 1) * sizeof(float);
 }
 
 }  // namespace
@@ -385,6 +387,8 @@ int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
   k.parts_per_row = p->parts_per_row;
   k.out_row_stride = p->out_row_stride;
   k.out_batch_stride = p->out_row_stride * p->h;
+  k.out_tok_stride = 0;
+  k.sq = 1;
   k.num_parts = p->num_parts;
   k.rows = p->rows;
   k.h = p->h;
@@ -470,9 +474,13 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.s_aux_dtype = p->s_aux_dtype;
   k.window_left = (p->has_window && p->window_left >= 0) ? p->window_left : -1;
   k.v_transposed = p->v_transposed ? 1 : 0;
+  k.sq = p->seqlen_q > 1 ? p->seqlen_q : 1;
+  k.causal = p->is_causal ? 1 : 0;
+  k.q_row_stride = p->q_row_stride;
+  k.o_row_stride = p->o_row_stride;
   if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
-    k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * kHeadDim;
+    k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * k.sq * kHeadDim;
   }
   if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
   cudaError_t e = launch_decode(p->dtype, tk, tv, k, stream);
@@ -486,8 +494,9 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
     c.seqlens = p->cache_seqlens;
     c.parts_per_row = nullptr;
     c.num_parts = pl.num_partitions;
-    c.rows = p->b * p->h;
+    c.rows = p->b * p->h * k.sq;
     c.h = p->h;
+    c.sq = k.sq;
     c.partition_tokens = pl.partition_tokens;
     c.out_scale = 1.f;
     c.o_part_stride = static_cast<int64_t>(c.rows) * kHeadDim;
@@ -495,8 +504,9 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
     if (p->o_partial_out) {
       c.out = p->o_partial_out;
       c.lse = p->lse_partial_out;
-      c.out_row_stride = kHeadDim;
-      c.out_batch_stride = static_cast<int64_t>(p->h) * kHeadDim;
+      c.out_row_stride = static_cast<int64_t>(k.sq) * kHeadDim;          // partial rows are (b, h, tok)
+      c.out_batch_stride = static_cast<int64_t>(p->h) * k.sq * kHeadDim;
+      c.out_tok_stride = kHeadDim;
       c.out_dtype = -1;
       c.lse_empty_is_neg = 1;
     } else {
@@ -504,6 +514,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
       c.lse = p->softmax_lse;
       c.out_row_stride = p->o_head_stride;
       c.out_batch_stride = p->o_batch_stride;
+      c.out_tok_stride = p->o_row_stride;
       c.out_dtype = p->out_dtype;
       c.lse_empty_is_neg = 0;
       c.s_aux = p->s_aux;   // partials handed to the caller stay without the sink: its final combine adds it

@@ -21,7 +21,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   __shared__ float4 red_acc[kCombineWarps][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
-  const int bi = row / p.h, hi = row - bi * p.h;
+  const int sq = p.sq > 0 ? p.sq : 1;
+  const int bi = row / (p.h * sq), hi = (row / sq) % p.h, ti = row % sq;
   int nparts = p.num_parts;
   if (p.parts_per_row) nparts = min(nparts, p.parts_per_row[bi]);
   else if (p.seqlens) nparts = min(nparts, (p.seqlens[bi] + p.partition_tokens - 1) / p.partition_tokens);
@@ -97,7 +98,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   }
   acc.x *= p.out_scale; acc.y *= p.out_scale; acc.z *= p.out_scale; acc.w *= p.out_scale;
   if (p.out) {
-    const int64_t off = static_cast<int64_t>(bi) * p.out_batch_stride + static_cast<int64_t>(hi) * p.out_row_stride + lane * 4;
+    const int64_t off = static_cast<int64_t>(bi) * p.out_batch_stride + static_cast<int64_t>(hi) * p.out_row_stride +
+                        static_cast<int64_t>(ti) * p.out_tok_stride + lane * 4;
     if (p.out_dtype == FA_B200_BF16) {
       __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), c = __floats2bfloat162_rn(acc.z, acc.w);
       uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));

@@ -80,7 +80,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int tok_end = min(len, (part + 1) * p.partition_tokens);
   // Sliding window: the query token (position len - 1) sees keys tok_lo .. len - 1.  A partition starts at the first
   // tile that holds a visible key; partitions wholly before the window publish "no keys" like an empty sequence.
-  const int tok_lo = p.window_left >= 0 ? max(0, len - 1 - p.window_left) : 0;
+  const int tok_lo = p.window_left >= 0 ? max(0, len - p.sq - p.window_left) : 0;   // of the first query token
   const int tok_begin = max(part * p.partition_tokens, (tok_lo / T::kTile) * T::kTile);
   const int n_tiles = (tok_end > tok_begin) ? (tok_end - tok_begin + T::kTile - 1) / T::kTile : 0;
 
@@ -158,21 +158,38 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     const int g = lane >> 2, qd = lane & 3;
     const int head0 = hk * group;
 
-    // Query fragments (A operand, rows = heads of the group, zero beyond the group).
+    // Query fragments (A operand).  Row r of the 16-row tile is query token r / group and head r % group of the kv
+    // head's group (one token per sequence: the rows are the heads); rows past sq * group are zero.
+    const int rows = p.sq * group;
     uint32_t qf[T::kQSteps][4];
     {
       const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) +
                           (static_cast<int64_t>(b) * p.q_batch_stride + static_cast<int64_t>(head0) * p.q_head_stride) * T::kElem;
-      const int64_t hs = p.q_head_stride * T::kElem;
+      const int64_t off0 = ((g / group) * p.q_row_stride + (g % group) * p.q_head_stride) * T::kElem;
+      const int64_t off1 = (((g + 8) / group) * p.q_row_stride + ((g + 8) % group) * p.q_head_stride) * T::kElem;
 #pragma unroll
       for (int ks = 0; ks < T::kQSteps; ++ks) {
         // bytes of the two 4-byte groups this thread holds per row in k-step ks
         const int c0 = T::kFp8 ? (ks * 32 + 4 * qd) : (ks * 32 + 4 * qd);
         const int c1 = c0 + 16;
-        qf[ks][0] = (g < group) ? __ldg(reinterpret_cast<const uint32_t*>(qb + g * hs + c0)) : 0u;
-        qf[ks][1] = (g + 8 < group) ? __ldg(reinterpret_cast<const uint32_t*>(qb + (g + 8) * hs + c0)) : 0u;
-        qf[ks][2] = (g < group) ? __ldg(reinterpret_cast<const uint32_t*>(qb + g * hs + c1)) : 0u;
-        qf[ks][3] = (g + 8 < group) ? __ldg(reinterpret_cast<const uint32_t*>(qb + (g + 8) * hs + c1)) : 0u;
+        qf[ks][0] = (g < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off0 + c0)) : 0u;
+        qf[ks][1] = (g + 8 < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off1 + c0)) : 0u;
+        qf[ks][2] = (g < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off0 + c1)) : 0u;
+        qf[ks][3] = (g + 8 < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off1 + c1)) : 0u;
+      }
+    }
+    // Keys visible to this thread's two rows: query token s of sq sits at position len - sq + s, so it sees keys below
+    // len - (sq - 1 - s) when the mask is causal, and not before its own window start.
+    int hi0 = tok_end, hi1 = tok_end, lo0 = tok_lo, lo1 = tok_lo;
+    if (p.sq > 1) {
+      const int s0 = min(g / group, p.sq - 1), s1 = min((g + 8) / group, p.sq - 1);
+      if (p.causal) {
+        hi0 = min(tok_end, len - (p.sq - 1 - s0));
+        hi1 = min(tok_end, len - (p.sq - 1 - s1));
+      }
+      if (p.window_left >= 0) {
+        lo0 = max(0, len - (p.sq - 1 - s0) - 1 - p.window_left);
+        lo1 = max(0, len - (p.sq - 1 - s1) - 1 - p.window_left);
       }
     }
     float scale_log2 = p.scale_log2;
@@ -229,9 +246,9 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const bool ok = (tokb + nt * 8 + e) < tok_end && (tokb + nt * 8 + e) >= tok_lo;
-            sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
-            sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+            const int tk = tokb + nt * 8 + e;
+            sc[nt][e] = (tk < hi0 && tk >= lo0) ? sc[nt][e] * scale_log2 : -INFINITY;
+            sc[nt][2 + e] = (tk < hi1 && tk >= lo1) ? sc[nt][2 + e] * scale_log2 : -INFINITY;
             mx0 = fmaxf(mx0, sc[nt][e]);
             mx1 = fmaxf(mx1, sc[nt][2 + e]);
           }
@@ -350,7 +367,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
       const int row = g + rr * 8;
-      if (row < group) {
+      if (row < p.sq * group) {
         float mg = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) mg = fmaxf(mg, sm_m[w * 16 + row]);
@@ -377,7 +394,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     const int tid = threadIdx.x - 32;  // 0..127 = d
     float vds = 1.f;
     if (p.v_descale) vds = p.v_descale[b * p.vds_b + hk * p.vds_h];
-    for (int row = 0; row < group; ++row) {
+    for (int row = 0; row < p.sq * group; ++row) {
       float mg = -INFINITY;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) mg = fmaxf(mg, sm_m[w * 16 + row]);
@@ -388,7 +405,8 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         L += (mw == -INFINITY) ? 0.f : sm_l[w * 16 + row] * fast_exp2(mw - mg);
         acc += red[(w * 16 + row) * kHeadDim + tid];
       }
-      const int head = hk * group + row;
+      const int tok = row / group;                 // query token of this row
+      const int head = hk * group + row % group;
       bool empty = !(L > 0.f);
       float outv = empty ? 0.f : acc / L * vds;
       float lse = empty ? -INFINITY : (mg + log2f(L)) * kLn2;
@@ -398,12 +416,14 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         outv = acc * inv * vds;
       }
       if (p.write_final) {
-        const int64_t oi = static_cast<int64_t>(b) * p.o_batch_stride + static_cast<int64_t>(head) * p.o_head_stride + tid;
+        const int64_t oi = static_cast<int64_t>(b) * p.o_batch_stride + static_cast<int64_t>(tok) * p.o_row_stride +
+                           static_cast<int64_t>(head) * p.o_head_stride + tid;
         if (p.out_dtype == FA_B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(outv);
         else reinterpret_cast<__half*>(p.out)[oi] = __float2half_rn(outv);
-        if (tid == 0 && p.lse_out) p.lse_out[b * p.h + head] = empty ? INFINITY : lse;
+        if (tid == 0 && p.lse_out) p.lse_out[(static_cast<int64_t>(b) * p.h + head) * p.sq + tok] = empty ? INFINITY : lse;
       } else {
-        const int64_t slot = (static_cast<int64_t>(part) * p.b + b) * p.h + head;
+        // partial rows are (sequence, head, token): the layout of the (b, h, sq) LSE
+        const int64_t slot = ((static_cast<int64_t>(part) * p.b + b) * p.h + head) * p.sq + tok;
         p.o_partial[slot * kHeadDim + tid] = outv;
         if (tid == 0) p.lse_partial[slot] = lse;
       }

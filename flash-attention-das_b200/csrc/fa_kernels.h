@@ -20,8 +20,8 @@ struct DecodeKernelParams {
   const float* v_descale;
   float* o_partial;    // [partition][b][h][128] fp32
   float* lse_partial;  // [partition][b][h] fp32, natural log, -inf = no keys
-  int64_t q_batch_stride, q_head_stride;
-  int64_t o_batch_stride, o_head_stride;
+  int64_t q_batch_stride, q_head_stride, q_row_stride;
+  int64_t o_batch_stride, o_head_stride, o_row_stride;
   int64_t bt_stride;
   int64_t qds_b, qds_h, kds_b, kds_h, vds_b, vds_h;
   int32_t b, h, h_k, group;
@@ -34,6 +34,8 @@ struct DecodeKernelParams {
   int32_t s_aux_dtype;
   int32_t window_left; // the query token sees only its last window_left + 1 keys; -1 = all
   int32_t v_transposed; // tmap_v describes (page tokens, d, h_k, block) with a (64, 128, 1, 1) box
+  int32_t sq;           // query tokens per sequence, the last sq positions of it; sq * group <= 16 rows of the MMA tile
+  int32_t causal;       // sq > 1: token s sees the keys up to its own position
 };
 
 size_t decode_smem_bytes(int stages);
@@ -49,8 +51,10 @@ struct CombineKernelParams {
   float* lse;
   const int32_t* seqlens;    // optional: row r uses ceil(seqlens[r / h] / partition_tokens) parts
   const int32_t* parts_per_row;  // optional explicit count per batch entry
-  int64_t out_row_stride;    // rows are (b, h): element offset = (r / h) * out_batch_stride + (r % h) * out_row_stride
+  int64_t out_row_stride;    // rows are (b, h, tok): element offset = b * out_batch_stride + h * out_row_stride + tok * out_tok_stride
   int64_t out_batch_stride;
+  int64_t out_tok_stride;
+  int32_t sq;                // query tokens per (sequence, head); rows = b * h * sq
   int32_t num_parts, rows, h;
   int32_t partition_tokens;
   int32_t out_dtype;         // FA_B200_F16 / BF16, or -1 for fp32

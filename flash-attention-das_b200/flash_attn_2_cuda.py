@@ -84,6 +84,8 @@ class DecodeParams(ctypes.Structure):
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
         ("has_window", _c_i32), ("window_left", _c_i32),
         ("v_transposed", _c_i32),
+        ("seqlen_q", _c_i32), ("is_causal", _c_i32),
+        ("q_row_stride", _c_i64), ("o_row_stride", _c_i64),
     ]
 
 
@@ -451,9 +453,10 @@ def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out
     p = DecodeParams()
     p.q, p.k_cache, p.v_cache = q.data_ptr(), kcache.data_ptr(), vcache.data_ptr()
     p.out, p.softmax_lse = _ptr(out), _ptr(lse)
-    p.q_batch_stride, p.q_head_stride = q.stride(0), q.stride(2)
+    p.q_batch_stride, p.q_head_stride, p.q_row_stride = q.stride(0), q.stride(2), q.stride(1)
+    p.seqlen_q = sq
     if out is not None:
-        p.o_batch_stride, p.o_head_stride = out.stride(0), out.stride(2)
+        p.o_batch_stride, p.o_head_stride, p.o_row_stride = out.stride(0), out.stride(2), out.stride(1)
     p.k_block_stride, p.k_row_stride, p.k_head_stride = kcache.stride(0), kcache.stride(1), kcache.stride(2)
     if _is_transposed_v(vcache):
         # (num_blocks, page, h_k, d) view of a pool stored as (num_blocks, h_k, d, page): the tokens are the contiguous axis
@@ -490,8 +493,9 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     (contiguous caches only) raise.  Unlike the reference, the returned softmax_lse is filled in."""
     v_t = _is_transposed_v(vcache)
     _check_qkv(q, kcache, vcache, v_t)
-    _unsupported(v_t and (q.shape[1] != 1 or k_ is not None or q.dtype == torch.float8_e4m3fn),
-                 "a transposed V pool (layout 0) outside one-token bf16/fp16 decode without append")
+    _unsupported(v_t and (q.shape[1] * (q.shape[2] // max(kcache.shape[2], 1)) > 16 or k_ is not None or
+                          q.dtype == torch.float8_e4m3fn),
+                 "a transposed V pool (layout 0) outside bf16/fp16 decode of a few tokens without append")
     _require((k_ is None) == (v_ is None), "k and v must be passed together")
     _require(rotary_cos_ is None or k_ is not None, "rotary_cos/rotary_sin are only applicable if k and v are passed in")
     _require((rotary_cos_ is None) == (rotary_sin_ is None), "rotary_cos and rotary_sin must be passed together")
@@ -521,9 +525,11 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     if k_ is not None:
         q, seqlens_k_ = kv_append(q, kcache, vcache, k_, v_, seqlens_k_, block_table_, rotary_cos_, rotary_sin_,
                                   is_rotary_interleaved, is_causal or window_size_left >= 0 or window_size_right >= 0)
-    if sq > 1:
-        # several query tokens per sequence (chunked prefill, speculative decoding) over the paged cache: the prefill
-        # kernel reads K/V through the block table; the causal mask is bottom-right aligned to each cache length
+    if sq > 1 and (sq * (h // h_k) > 16 or v_t):
+        # several query tokens per sequence (chunked prefill) over the paged cache: the prefill kernel reads K/V through
+        # the block table; the causal mask is bottom-right aligned to each cache length.  A few tokens (speculative
+        # decoding: tokens x heads per kv head <= 16) stay on the decode kernel below, which packs them into the rows of
+        # its tile and streams the cache once.
         fp = FwdParams()
         fp.q, fp.out, fp.softmax_lse = q.data_ptr(), out.data_ptr(), lse.data_ptr()
         fp.q_batch_stride, fp.q_row_stride, fp.q_head_stride = q.stride(0), q.stride(1), q.stride(2)
@@ -545,8 +551,10 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
         return [out, lse]
     p = _decode_params(q, kcache, vcache, seqlens_k_, block_table_, softmax_scale, out, lse, q_descale_, k_descale_,
                        v_descale_, 0, max_seqlen_k)
+    p.is_causal = 1 if is_causal else 0
+    _unsupported(sq > 1 and not is_causal and window_size_right >= 0, "a right window bound with several decode tokens")
     _set_sinks(p, s_aux_, h)
-    _set_window(p, window_size_left, -1)   # one query token at the end of its sequence: only the left side matters
+    _set_window(p, window_size_left, -1)   # query tokens at the end of their sequence: only the left side matters
     with torch.cuda.device(q.device):
         ws = _workspace(q.device, int(_lib.fa_b200_decode_workspace_bytes(ctypes.byref(p))))
         if ws is not None:

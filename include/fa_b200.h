@@ -192,6 +192,13 @@ typedef struct fa_b200_decode_params {
    * K strides already express).  With v_transposed != 0, v_row_stride is the stride between consecutive d rows.
    * F16 / BF16 only, page_size a multiple of 64. */
   int32_t v_transposed;
+  /* Several query tokens per sequence (speculative decoding, multi-token prediction): q and out are
+   * (b, seqlen_q, h, d) with q_row_stride / o_row_stride between tokens, softmax_lse (b, h, seqlen_q); the tokens are the
+   * last seqlen_q positions of their sequence (cache_seqlens counts them) and with is_causal each sees the keys up to its
+   * own position.  seqlen_q * (h / h_k) must fit the 16 rows of the kernel's tile (the reference sends this case to its
+   * decode kernel under the same kind of bound, flash_attn_interface.py:2256).  0 or 1 = one token. */
+  int32_t seqlen_q, is_causal;
+  int64_t q_row_stride, o_row_stride;
 } fa_b200_decode_params;
 
 /* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)

@@ -235,3 +235,54 @@ def test_combine_takes_strided_partitions(fa):
     assert op.untyped_storage().data_ptr() == lp.untyped_storage().data_ptr()
     ref, ref_l = O.paged_decode_ref(q.cpu(), kc, vc, sl, bt, out_dtype=torch.float32)
     assert max_err(op.cpu(), ref[:, 0]) < 2e-2 and max_err(lp.cpu(), ref_l[:, :, 0]) < 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float8_e4m3fn])
+@pytest.mark.parametrize("sq,h,hk", [(2, 8, 2), (4, 8, 2), (3, 4, 4), (8, 4, 2), (2, 8, 1), (16, 2, 2)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_few_query_tokens_stay_on_the_decode_kernel(fa, dtype, sq, h, hk, causal):
+    """Speculative decoding / multi-token prediction: seqlen_q * group <= 16 query rows are packed into the decode
+    kernel's tile (one pass over the cache for all of them), with and without a KV split, against the oracle."""
+    flash_attn, cuda = fa
+    g = gen(700 + sq * 31 + h)
+    lens = [sq, sq + 1, 64, 65, 300, 1031]
+    fp8 = dtype == torch.float8_e4m3fn
+    kc, vc, bt, sl = make_paged(g, lens, hk, 64, torch.bfloat16, poison=not fp8)
+    q = randn(g, len(lens), sq, h, 128)
+    kw, okw = {}, {}
+    if fp8:
+        q8, qd = O.quantize_e4m3_per_tensor(q)
+        k8, kd = O.quantize_e4m3_per_tensor(kc)
+        v8, vd = O.quantize_e4m3_per_tensor(vc)
+        q, kc, vc = q8, k8, v8
+        kw = dict(q_descale=qd.cuda(), k_descale=kd.cuda(), v_descale=vd.cuda())
+    else:
+        q, kc, vc = q.to(dtype), kc.to(dtype), vc.to(dtype)
+    launches = cuda.launch_count()
+    outs = {}
+    for part in (None, 128 if fp8 else 64):      # without and with a KV split (the e4m3 tile is 128 tokens)
+        if part is not None:
+            os.environ["FA_B200_DECODE_PARTITION"] = str(part)
+        try:
+            out, lse = flash_attn.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(),
+                                                          block_table=bt.cuda(), causal=causal, return_softmax_lse=True, **kw)
+            torch.cuda.synchronize()
+        finally:
+            os.environ.pop("FA_B200_DECODE_PARTITION", None)
+        assert cuda.device_status() == 0
+        outs[part] = (out.cpu(), lse.cpu())
+    assert cuda.launch_count() - launches <= 4          # decode (+ combine) per call: not the prefill kernel's path
+    for i, L in enumerate(lens):
+        ki = O.gather_paged_kv(clean_nan(kc) if not fp8 else kc, bt[i], L)[None]
+        vi = O.gather_paged_kv(clean_nan(vc) if not fp8 else vc, bt[i], L)[None]
+        if fp8:
+            okw = dict(q_descale=qd.view(1, 1).expand(1, hk), k_descale=kd.view(1, 1).expand(1, hk), v_descale=vd.view(1, 1).expand(1, hk))
+        ref32, ref_lse = O.attention_ref(q[i:i + 1], ki, vi, causal=causal, out_dtype=torch.float32, **okw)
+        for part, (out, lse) in outs.items():
+            if fp8:
+                assert max_err(out[i:i + 1], ref32) < 7e-2, (i, part)
+            else:
+                ref_pt, _ = O.attention_ref(q[i:i + 1], ki, vi, causal=causal, upcast=False, reorder_ops=True)
+                assert_close_to_oracle(out[i:i + 1], ref32, ref_pt, mult=3.0, eps=2 ** -8, what=f"few tokens seq {i} part {part}")
+            ok = torch.isfinite(ref_lse[0])
+            assert max_err(lse[i][ok], ref_lse[0][ok]) < 2e-3

@@ -175,11 +175,13 @@ def test_decode_window(fa, window_left, partition):
     assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=3.0, eps=2 ** -8, what=f"decode window {window_left}")
 
 
-def test_paged_chunk_with_window_and_sinks(fa):
-    """Several query tokens over a paged cache (the prefill kernel through the block table) with a window and sinks."""
+@pytest.mark.parametrize("sq", [3, 7])
+def test_paged_chunk_with_window_and_sinks(fa, sq):
+    """Several query tokens over a paged cache with a window and sinks: 7 tokens x 4 heads per kv head go through the
+    prefill kernel and the block table, 3 x 4 = 12 rows stay on the decode kernel."""
     flash_attn, cuda = fa
     g = gen(4242)
-    dtype, lens, h, hk, sq = torch.float16, [9, 500, 128, 1031], 8, 2, 7
+    dtype, lens, h, hk = torch.float16, [9, 500, 128, 1031], 8, 2
     kc, vc, bt, sl = make_paged(g, lens, hk, 64, dtype)
     q = randn(g, len(lens), sq, h, 128, dtype=dtype)
     s_aux = (torch.randn(h, generator=g)).to(dtype)
