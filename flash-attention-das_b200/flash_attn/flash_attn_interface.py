@@ -116,17 +116,27 @@ def flash_attn_varlen_func(
         window_size = (-1, -1)
     if block_table is not None:
         k, v = _paged_as_bshd(k, v, layout)
-        if layout in ("custom", 0):
-            if max_seqlen_q != 1 or q.shape[0] != block_table.shape[0]:
-                raise NotImplementedError("paged layout 'custom' (V transposed) is taken for one query token per sequence "
-                                          "only: use 'bshd' or 'bhsd' for prefill over a paged cache")
+        # One or a few query tokens per sequence, the same number for all (decode, speculative decoding): the decode
+        # kernel, as in the reference (its direct paged path, flash_attn_interface.py:2256, 2305-2348).  Rows of the
+        # kernel's tile: tokens x heads per kv head <= 16.
+        bs = block_table.shape[0]
+        group = q.shape[1] // k.shape[2]
+        few_tokens = max_seqlen_q >= 1 and max_seqlen_q * bs == q.shape[0] and max_seqlen_q * group <= 16
+        if layout in ("custom", 0) and not few_tokens:
+            raise NotImplementedError("paged layout 'custom' (V transposed) is taken for a few query tokens per sequence "
+                                      "only: use 'bshd' or 'bhsd' for prefill over a paged cache")
+        if few_tokens and (max_seqlen_q > 1 or layout in ("custom", 0)) and q_v is None and dropout_p == 0.0:
             if softmax_scale is None:
                 softmax_scale = q.shape[-1] ** (-0.5)
+            q = maybe_contiguous(q)
+            sq = max_seqlen_q
             o, lse = flash_attn_cuda.fwd_kvcache(
-                q.unsqueeze(1), k, v, None, None, seqused_k, None, None, None, None, block_table, alibi_slopes,
-                None if out is None else out.unsqueeze(1), softmax_scale, causal, window_size[0], window_size[1], softcap,
-                True, num_splits, s_aux, q_descale, k_descale, v_descale, max_seqlen_k)
-            o, lse = o.squeeze(1), lse.squeeze(-1).transpose(0, 1)
+                q.view(bs, sq, q.shape[1], q.shape[2]), k, v, None, None, seqused_k, None, None, None, None, block_table,
+                alibi_slopes, None if out is None else out.view(bs, sq, q.shape[1], q.shape[2]), softmax_scale, causal,
+                window_size[0], window_size[1], softcap, True, num_splits, s_aux, q_descale, k_descale, v_descale,
+                max_seqlen_k)
+            o = o.view(bs * sq, q.shape[1], q.shape[2])
+            lse = lse.permute(1, 0, 2).reshape(q.shape[1], bs * sq)      # (b, h, sq) -> (h, total_q)
             if return_attn_probs:
                 return o, lse, None
             return (o, lse) if return_softmax_lse else o

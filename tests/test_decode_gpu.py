@@ -286,3 +286,24 @@ def test_few_query_tokens_stay_on_the_decode_kernel(fa, dtype, sq, h, hk, causal
                 assert_close_to_oracle(out[i:i + 1], ref32, ref_pt, mult=3.0, eps=2 ** -8, what=f"few tokens seq {i} part {part}")
             ok = torch.isfinite(ref_lse[0])
             assert max_err(lse[i][ok], ref_lse[0][ok]) < 2e-3
+
+
+def test_varlen_entry_with_few_tokens_uses_the_decode_kernel(fa):
+    """flash_attn_varlen_func(block_table=...) with the same small number of query tokens for every sequence (the form
+    vLLM-style callers use for speculative decoding) gives the bits of flash_attn_with_kvcache on the same inputs."""
+    flash_attn, cuda = fa
+    g = gen(55)
+    lens, h, hk, sq = [40, 300, 64, 1000], 8, 2, 4
+    kc, vc, bt, sl = make_paged(g, lens, hk, 64, torch.bfloat16, poison=False)
+    q = randn(g, len(lens), sq, h, 128).cuda()
+    want, want_lse = flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                                        causal=True, return_softmax_lse=True)
+    cu = torch.arange(0, (len(lens) + 1) * sq, sq, dtype=torch.int32, device="cuda")
+    n0 = cuda.launch_count()
+    got, got_lse = flash_attn.flash_attn_varlen_func(q.view(-1, h, 128), kc.cuda(), vc.cuda(), cu, None, sq, max(lens),
+                                                     seqused_k=sl.cuda(), causal=True, block_table=bt.cuda(),
+                                                     return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.launch_count() - n0 <= 2
+    assert torch.equal(got.view(len(lens), sq, h, 128), want)
+    assert torch.equal(got_lse.view(h, len(lens), sq).permute(1, 0, 2), want_lse)
