@@ -42,11 +42,11 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, as a multiple of the
 # algorithmic bytes, from the ncu captures summarised under profiles/ (None = not captured yet).
 # decode: measured on a quarter of the batch (traffic grows in proportion to the tokens streamed).
-TRAFFIC_RATIO = {"decode_bf16": 1.014, "decode_fp8": 1.013, "prefill_bf16": None, "prefill_fp8": None,
-                 "sparse_bf16": None, "longseq": 1.014}
+TRAFFIC_RATIO = {"decode_bf16": 1.007, "decode_fp8": 1.013, "prefill_bf16": None, "prefill_fp8": None,
+                 "sparse_bf16": None, "longseq": 1.007}
 # prefill is tensor-bound, its algorithmic unit is FLOPs; DRAM traffic is reported in bytes per token of the
-# captured case (473.7 MB for 19,679 tokens, 1.18x the compulsory q+k+v+out bytes).
-PREFILL_TRAFFIC_BYTES_PER_TOKEN = {"prefill_bf16": 473.7e6 / 19679}
+# captured case (521.5 MB for 19,679 tokens, 1.29x the compulsory q+k+v+out bytes).
+PREFILL_TRAFFIC_BYTES_PER_TOKEN = {"prefill_bf16": 521.5e6 / 19679}
 
 
 def load_peaks():
