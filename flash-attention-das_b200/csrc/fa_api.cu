@@ -153,7 +153,8 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   if (p->h % p->h_k != 0 || p->h / p->h_k > 16) { pl.status = FA_B200_ERR_HEADS; return pl; }
   pl.group = p->h / p->h_k;
   if (p->seqlen_q < 0 || (p->seqlen_q > 1 && p->seqlen_q * pl.group > 16)) { pl.status = FA_B200_ERR_HEADS; return pl; }
-  pl.tile = p->dtype == FA_B200_E4M3 ? 128 : 64;
+  if (p->kv_e4m3 && p->dtype == FA_B200_E4M3) { pl.status = FA_B200_ERR_DTYPE; return pl; }   // the flag is for 16-bit queries
+  pl.tile = (p->dtype == FA_B200_E4M3 || p->kv_e4m3) ? 128 : 64;
   const int page = p->page_size;
   if (page >= 64) {
     if (page % 64 != 0) { pl.status = FA_B200_ERR_PAGE; return pl; }
@@ -416,29 +417,32 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   if (p->o_partial_out && !p->lse_partial_out) return FA_B200_ERR_NULL;
   if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
   if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
-  const int es = elem_size(p->dtype);
+  const int kv_dtype = p->kv_e4m3 ? FA_B200_E4M3 : p->dtype;   // element type of the caches
+  const int es = elem_size(kv_dtype), qes = elem_size(p->dtype);
   if (!aligned16(p->q) || !aligned16(p->k_cache) || !aligned16(p->v_cache) || (p->out && !aligned16(p->out)))
     return FA_B200_ERR_ALIGN;
+  // the kernel reads q in 4-byte pieces (8-byte pieces for 16-bit queries over an e4m3 cache)
+  const int q_piece = p->kv_e4m3 ? 8 : 4;
   if (!stride_ok(p->k_block_stride, es) || !stride_ok(p->k_row_stride, es) || !stride_ok(p->k_head_stride, es) ||
       !stride_ok(p->v_block_stride, es) || !stride_ok(p->v_row_stride, es) || !stride_ok(p->v_head_stride, es) ||
-      (p->q_batch_stride * es) % 4 != 0 || (p->q_head_stride * es) % 4 != 0 || p->o_batch_stride % 8 != 0 ||
-      p->o_head_stride % 8 != 0)
+      (p->q_batch_stride * qes) % q_piece != 0 || (p->q_head_stride * qes) % q_piece != 0 ||
+      (p->q_row_stride * qes) % q_piece != 0 || p->o_batch_stride % 8 != 0 || p->o_head_stride % 8 != 0)
     return FA_B200_ERR_STRIDE;
   if (p->b == 0) return FA_B200_OK;
   const size_t need = decode_ws_bytes(p, pl);
   if (need > 0 && (!p->workspace || p->workspace_bytes < need || !aligned16(p->workspace))) return FA_B200_ERR_WORKSPACE;
 
   CUtensorMap tk, tv;
-  int st = make_tmap(&tk, p->k_cache, p->dtype, p->h_k, p->page_size, p->num_blocks, p->k_head_stride, p->k_row_stride,
+  int st = make_tmap(&tk, p->k_cache, kv_dtype, p->h_k, p->page_size, p->num_blocks, p->k_head_stride, p->k_row_stride,
                      p->k_block_stride, pl.box_tok);
   if (st != FA_B200_OK) return st;
   if (p->v_transposed) {
-    if (p->dtype == FA_B200_E4M3) return FA_B200_ERR_UNSUPPORTED;
+    if (kv_dtype == FA_B200_E4M3) return FA_B200_ERR_UNSUPPORTED;
     if (p->page_size % 64 != 0) return FA_B200_ERR_PAGE;
     st = make_tmap_vt(&tv, p->v_cache, p->dtype, p->page_size, p->h_k, p->num_blocks, p->v_row_stride,
                       p->v_head_stride, p->v_block_stride);
   } else {
-    st = make_tmap(&tv, p->v_cache, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
+    st = make_tmap(&tv, p->v_cache, kv_dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
                    p->v_block_stride, pl.box_tok);
   }
   if (st != FA_B200_OK) return st;
@@ -476,6 +480,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.v_transposed = p->v_transposed ? 1 : 0;
   k.sq = p->seqlen_q > 1 ? p->seqlen_q : 1;
   k.causal = p->is_causal ? 1 : 0;
+  k.kv_e4m3 = p->kv_e4m3 ? 1 : 0;
   k.q_row_stride = p->q_row_stride;
   k.o_row_stride = p->o_row_stride;
   if (pl.split) {

@@ -54,11 +54,18 @@ __device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
 // VT: the V pool is stored transposed, (num_blocks, h_k, d, page) with tokens contiguous (the reference's paged layout
 // 0, flash_attn_interface.py:2223-2227): a V tile then lands in shared memory as 128 d rows of 64 tokens and feeds the
 // P V product through plain (non-transposing) ldmatrix, exactly as K feeds Q K^T.  16-bit types, pages of 64 * n.
-template <int DT, int STAGES, bool VT>
+// QT: element type of the queries.  Normally QT == DT; QT = F16 / BF16 with DT = E4M3 is the "fp8 KV cache" mode: the
+// cache is e4m3, the queries (and the output) are 16-bit.  K is then converted to f16 in registers on its way into the
+// Q K^T product (f16 MMA; bf16 queries are converted to f16 once per CTA), V as in the all-e4m3 mode.
+template <int DT, int STAGES, bool VT, int QT = DT>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
 decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                     const DecodeKernelParams p) {
   using T = DecodeTraits<DT>;
+  constexpr bool kMixed = (QT != DT);
+  static_assert(!kMixed || (DT == FA_B200_E4M3 && !VT), "mixed mode: 16-bit queries over an e4m3 cache");
+  constexpr int kQElem = kMixed ? 2 : T::kElem;
+  constexpr int kQRegSteps = kMixed ? 8 : T::kQSteps;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -161,21 +168,43 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     // Query fragments (A operand).  Row r of the 16-row tile is query token r / group and head r % group of the kv
     // head's group (one token per sequence: the rows are the heads); rows past sq * group are zero.
     const int rows = p.sq * group;
-    uint32_t qf[T::kQSteps][4];
+    uint32_t qf[kQRegSteps][4];
     {
       const uint8_t* qb = reinterpret_cast<const uint8_t*>(p.q) +
-                          (static_cast<int64_t>(b) * p.q_batch_stride + static_cast<int64_t>(head0) * p.q_head_stride) * T::kElem;
-      const int64_t off0 = ((g / group) * p.q_row_stride + (g % group) * p.q_head_stride) * T::kElem;
-      const int64_t off1 = (((g + 8) / group) * p.q_row_stride + ((g + 8) % group) * p.q_head_stride) * T::kElem;
+                          (static_cast<int64_t>(b) * p.q_batch_stride + static_cast<int64_t>(head0) * p.q_head_stride) * kQElem;
+      const int64_t off0 = ((g / group) * p.q_row_stride + (g % group) * p.q_head_stride) * kQElem;
+      const int64_t off1 = (((g + 8) / group) * p.q_row_stride + ((g + 8) % group) * p.q_head_stride) * kQElem;
+      if constexpr (kMixed) {
+        // f16 product over an e4m3 K: per 16-wide k-step the thread holds the FOUR consecutive d values 4 * qd .. + 3
+        // of its rows (first pair in registers 0/1, second in 2/3), the order in which the K bytes come out of
+        // ldmatrix below; the sum over k does not care about the order as long as both operands use the same one.
+        auto to_f16x2 = [](uint32_t v) -> uint32_t {
+          if (QT == FA_B200_F16) return v;
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+          return pack_f16(f.x, f.y);
+        };
 #pragma unroll
-      for (int ks = 0; ks < T::kQSteps; ++ks) {
-        // bytes of the two 4-byte groups this thread holds per row in k-step ks
-        const int c0 = T::kFp8 ? (ks * 32 + 4 * qd) : (ks * 32 + 4 * qd);
-        const int c1 = c0 + 16;
-        qf[ks][0] = (g < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off0 + c0)) : 0u;
-        qf[ks][1] = (g + 8 < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off1 + c0)) : 0u;
-        qf[ks][2] = (g < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off0 + c1)) : 0u;
-        qf[ks][3] = (g + 8 < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off1 + c1)) : 0u;
+        for (int j = 0; j < 8; ++j) {
+          const int c = (16 * j + 4 * qd) * 2;
+          const uint2 z = make_uint2(0u, 0u);
+          const uint2 r0v = (g < rows) ? __ldg(reinterpret_cast<const uint2*>(qb + off0 + c)) : z;
+          const uint2 r1v = (g + 8 < rows) ? __ldg(reinterpret_cast<const uint2*>(qb + off1 + c)) : z;
+          qf[j][0] = to_f16x2(r0v.x);
+          qf[j][1] = to_f16x2(r1v.x);
+          qf[j][2] = to_f16x2(r0v.y);
+          qf[j][3] = to_f16x2(r1v.y);
+        }
+      } else {
+#pragma unroll
+        for (int ks = 0; ks < T::kQSteps; ++ks) {
+          // bytes of the two 4-byte groups this thread holds per row in k-step ks
+          const int c0 = ks * 32 + 4 * qd;
+          const int c1 = c0 + 16;
+          qf[ks][0] = (g < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off0 + c0)) : 0u;
+          qf[ks][1] = (g + 8 < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off1 + c0)) : 0u;
+          qf[ks][2] = (g < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off0 + c1)) : 0u;
+          qf[ks][3] = (g + 8 < rows) ? __ldg(reinterpret_cast<const uint32_t*>(qb + off1 + c1)) : 0u;
+        }
       }
     }
     // Keys visible to this thread's two rows: query token s of sq sits at position len - sq + s, so it sees keys below
@@ -235,8 +264,16 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const uint32_t addr = rbase + (chunk >> 3) * (T::kTile * 128) + (((chunk & 7) ^ rsw) << 4);
             uint32_t b00, b01, b10, b11;
             ldsm_x4(addr, b00, b01, b10, b11);
-            mma_qk<DT>(sc[0], qf[ks], b00, b01);
-            mma_qk<DT>(sc[1], qf[ks], b10, b11);
+            if constexpr (kMixed) {
+              // each register holds four consecutive e4m3 d values of one token: two f16 pairs, one 16-wide k-step
+              mma_f16_16816(sc[0], qf[2 * ks], cvt_e4m3x2_to_f16x2(b00), cvt_e4m3x2_to_f16x2(b00 >> 16));
+              mma_f16_16816(sc[0], qf[2 * ks + 1], cvt_e4m3x2_to_f16x2(b01), cvt_e4m3x2_to_f16x2(b01 >> 16));
+              mma_f16_16816(sc[1], qf[2 * ks], cvt_e4m3x2_to_f16x2(b10), cvt_e4m3x2_to_f16x2(b10 >> 16));
+              mma_f16_16816(sc[1], qf[2 * ks + 1], cvt_e4m3x2_to_f16x2(b11), cvt_e4m3x2_to_f16x2(b11 >> 16));
+            } else {
+              mma_qk<DT>(sc[0], qf[ks], b00, b01);
+              mma_qk<DT>(sc[1], qf[ks], b10, b11);
+            }
           }
         }
         // ---- online softmax (base-2 domain), rows g and g+8
@@ -439,11 +476,11 @@ size_t decode_smem_bytes(int stages) {
 }
 int decode_max_pages_per_partition() { return kMaxPagesPerPartition; }
 
-template <int DT, bool VT>
+template <int DT, bool VT, int QT = DT>
 static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
                                     cudaStream_t stream) {
   constexpr int STAGES = 3;
-  auto kern = decode_paged_kernel<DT, STAGES, VT>;
+  auto kern = decode_paged_kernel<DT, STAGES, VT, QT>;
   const size_t smem = decode_smem_bytes(STAGES);
   static bool attr_done[64] = {};
   int dev = 0;
@@ -460,6 +497,12 @@ static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv
 
 cudaError_t launch_decode(int dtype, const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
                           cudaStream_t stream) {
+  if (p.kv_e4m3) {   // 16-bit queries over an e4m3 cache
+    if (p.v_transposed) return cudaErrorInvalidValue;
+    if (dtype == FA_B200_F16) return launch_decode_dt<FA_B200_E4M3, false, FA_B200_F16>(tk, tv, p, stream);
+    if (dtype == FA_B200_BF16) return launch_decode_dt<FA_B200_E4M3, false, FA_B200_BF16>(tk, tv, p, stream);
+    return cudaErrorInvalidValue;
+  }
   if (p.v_transposed) {
     if (dtype == FA_B200_F16) return launch_decode_dt<FA_B200_F16, true>(tk, tv, p, stream);
     if (dtype == FA_B200_BF16) return launch_decode_dt<FA_B200_BF16, true>(tk, tv, p, stream);

@@ -36,6 +36,7 @@ struct DecodeKernelParams {
   int32_t v_transposed; // tmap_v describes (page tokens, d, h_k, block) with a (64, 128, 1, 1) box
   int32_t sq;           // query tokens per sequence, the last sq positions of it; sq * group <= 16 rows of the MMA tile
   int32_t causal;       // sq > 1: token s sees the keys up to its own position
+  int32_t kv_e4m3;      // the cache is e4m3 while the queries are 16-bit (launch_decode's dtype is then the query type)
 };
 
 size_t decode_smem_bytes(int stages);

@@ -247,8 +247,14 @@ def vllm_flash_attn_with_kvcache(
     if k is not None or v is not None or rotary_cos is not None or rotary_sin is not None:
         raise NotImplementedError("vllm_flash_attn_with_kvcache does not append k/v (as in the reference); use "
                                   "flash_attn_with_kvcache")
-    if kv_cache_dtype not in ("auto", "") and not (kv_cache_dtype.startswith("fp8") and q.dtype == torch.float8_e4m3fn):
-        raise NotImplementedError("a KV cache dtype different from the query dtype is outside the B200 hot path")
+    if str(kv_cache_dtype).startswith("fp8"):
+        # an e4m3 cache under 16-bit (or e4m3) queries; k_scale / v_scale are its descales.  Raw-byte caches are viewed.
+        if "e5m2" in str(kv_cache_dtype):
+            raise NotImplementedError("an e5m2 KV cache is outside the B200 hot path")
+        if k_cache.dtype == torch.uint8:
+            k_cache, v_cache = k_cache.view(torch.float8_e4m3fn), v_cache.view(torch.float8_e4m3fn)
+    elif kv_cache_dtype not in ("auto", ""):
+        raise NotImplementedError(f"kv_cache_dtype {kv_cache_dtype!r} is outside the B200 hot path")
     if softcap is not None and softcap > 0.0:
         raise ValueError("softcap is not supported by paged attention (vllm_flash_attn_with_kvcache)")
     q = maybe_contiguous(q)
@@ -260,7 +266,8 @@ def vllm_flash_attn_with_kvcache(
     out, _ = flash_attn_cuda.fwd_kvcache(
         q, k_cache, v_cache, None, None, cache_seqlens, None, None, maybe_contiguous(cache_batch_idx), cache_leftpad,
         maybe_contiguous(block_table), alibi_slopes, out, softmax_scale, causal, window_size[0], window_size[1], 0.0,
-        rotary_interleaved, num_splits, s_aux, q_scale, k_scale, v_scale, max_seqlen_k)
+        rotary_interleaved, num_splits, s_aux, q_scale if q.dtype == torch.float8_e4m3fn else None, k_scale, v_scale,
+        max_seqlen_k)
     return out
 
 

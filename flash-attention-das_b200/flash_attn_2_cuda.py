@@ -86,6 +86,7 @@ class DecodeParams(ctypes.Structure):
         ("v_transposed", _c_i32),
         ("seqlen_q", _c_i32), ("is_causal", _c_i32),
         ("q_row_stride", _c_i64), ("o_row_stride", _c_i64),
+        ("kv_e4m3", _c_i32),
     ]
 
 
@@ -211,10 +212,16 @@ def _unsupported(cond: bool, what: str):
         raise NotImplementedError(f"{what} is outside the B200 hot path of this build")
 
 
-def _check_qkv(q, k, v, v_transposed=False):
+def _is_fp8_kv(q, k) -> bool:
+    """16-bit queries over an e4m3 cache (the reference's kv_cache_dtype = "fp8" mode)."""
+    return q.dtype in (torch.float16, torch.bfloat16) and k.dtype == torch.float8_e4m3fn
+
+
+def _check_qkv(q, k, v, v_transposed=False, allow_fp8_kv=False):
     _require(q.dtype in _DT, "FlashAttention only support fp16, bf16 and fp8 e4m3 data type")
-    _require(k.dtype == q.dtype, "query and key must have the same dtype")
-    _require(v.dtype == q.dtype, "query and value must have the same dtype")
+    if not (allow_fp8_kv and _is_fp8_kv(q, k)):
+        _require(k.dtype == q.dtype, "query and key must have the same dtype")
+    _require(v.dtype == k.dtype, "key and value must have the same dtype")
     _require(q.is_cuda and k.is_cuda and v.is_cuda, "Input tensor must be on CUDA device")
     for t in (q, k) if v_transposed else (q, k, v):
         _require(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
@@ -470,6 +477,7 @@ def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out
     p.num_blocks, p.page_size, p.max_blocks_per_seq = num_blocks, page, block_table.shape[1]
     p.softmax_scale = softmax_scale
     p.dtype = _DT[q.dtype]
+    p.kv_e4m3 = 1 if _is_fp8_kv(q, kcache) else 0
     p.out_dtype = _DT[out.dtype] if out is not None else BF16
     _descale(p, "q_descale", q_descale, b, h_k)
     _descale(p, "k_descale", k_descale, b, h_k)
@@ -492,7 +500,11 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     (flash_attn_interface.py:2503-2520) and the reference's wrapper drops; cache_batch_idx and cache_leftpad
     (contiguous caches only) raise.  Unlike the reference, the returned softmax_lse is filled in."""
     v_t = _is_transposed_v(vcache)
-    _check_qkv(q, kcache, vcache, v_t)
+    fp8_kv = _is_fp8_kv(q, kcache)
+    _check_qkv(q, kcache, vcache, v_t, allow_fp8_kv=True)
+    _unsupported(fp8_kv and (v_t or k_ is not None or q_descale_ is not None or
+                             q.shape[1] * (q.shape[2] // max(kcache.shape[2], 1)) > 16),
+                 "an e4m3 KV cache under 16-bit queries outside the decode of a few tokens (no append, no q_descale)")
     _unsupported(v_t and (q.shape[1] * (q.shape[2] // max(kcache.shape[2], 1)) > 16 or k_ is not None or
                           q.dtype == torch.float8_e4m3fn),
                  "a transposed V pool (layout 0) outside bf16/fp16 decode of a few tokens without append")
@@ -570,9 +582,12 @@ def paged_attention(out, query, key_cache, value_cache, scale, block_tables, seq
     query (num_seqs, seqlen_q, num_heads, 128) over paged pools into the caller's ``out``.  layout 0: key_cache
     (num_blocks, h_k, page, d) and value_cache (num_blocks, h_k, d, page); 1: both (num_blocks, h_k, page, d); 2: both
     (num_blocks, page, h_k, d).  q/k/v_scale are the e4m3 descales."""
-    _unsupported(kv_cache_dtype not in ("auto", "") and not (str(kv_cache_dtype).startswith("fp8") and
-                                                             query.dtype == torch.float8_e4m3fn),
-                 "a KV cache dtype different from the query dtype")
+    if str(kv_cache_dtype).startswith("fp8"):
+        _unsupported("e5m2" in str(kv_cache_dtype), "an e5m2 KV cache")
+        if key_cache.dtype == torch.uint8:      # caches kept as raw bytes
+            key_cache, value_cache = key_cache.view(torch.float8_e4m3fn), value_cache.view(torch.float8_e4m3fn)
+    else:
+        _unsupported(kv_cache_dtype not in ("auto", ""), f"kv_cache_dtype {kv_cache_dtype!r}")
     if layout == 2:
         kc, vc = key_cache, value_cache
     elif layout == 1:

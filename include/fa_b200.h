@@ -199,6 +199,10 @@ typedef struct fa_b200_decode_params {
    * decode kernel under the same kind of bound, flash_attn_interface.py:2256).  0 or 1 = one token. */
   int32_t seqlen_q, is_causal;
   int64_t q_row_stride, o_row_stride;
+  /* "fp8 KV cache": with kv_e4m3 != 0 the caches are E4M3 while q (and out) are of `dtype` F16 / BF16 (the reference's
+   * paged_attention with kv_cache_dtype = "fp8" and k_scale / v_scale, flash_api.cpp:2496-2515).  k_descale / v_descale
+   * carry the cache scales; q_descale is not used.  Not with v_transposed. */
+  int32_t kv_e4m3;
 } fa_b200_decode_params;
 
 /* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)

@@ -307,3 +307,43 @@ def test_varlen_entry_with_few_tokens_uses_the_decode_kernel(fa):
     assert cuda.launch_count() - n0 <= 2
     assert torch.equal(got.view(len(lens), sq, h, 128), want)
     assert torch.equal(got_lse.view(h, len(lens), sq).permute(1, 0, 2), want_lse)
+
+
+@pytest.mark.parametrize("qdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("sq", [1, 3])
+def test_fp8_kv_cache_under_16bit_queries(fa, qdtype, sq):
+    """The reference's kv_cache_dtype = "fp8" mode (flash_api.cpp:2496-2515): e4m3 K/V pools with per-tensor scales, 16-bit
+    queries and output.  Checked against the oracle on the dequantised cache, through flash_attn_with_kvcache and the
+    vLLM-named entry (raw uint8 pools, layout 1)."""
+    flash_attn, cuda = fa
+    g = gen(808 + sq)
+    lens, h, hk = [sq, 100, 128, 129, 1000, 2049], 8, 2
+    kc, vc, bt, sl = make_paged(g, lens, hk, 64, torch.bfloat16, poison=False)
+    k8, kd = O.quantize_e4m3_per_tensor(kc)
+    v8, vd = O.quantize_e4m3_per_tensor(vc)
+    q = randn(g, len(lens), sq, h, 128, dtype=qdtype)
+    k_deq, v_deq = k8.float() * kd, v8.float() * vd
+    ref32, ref_lse = O.paged_decode_ref(q, k_deq, v_deq, sl, bt, out_dtype=torch.float32)
+    ref_pt, _ = O.paged_decode_ref(q, k_deq.to(qdtype), v_deq.to(qdtype), sl, bt, upcast=False, reorder_ops=True)
+    for part in (None, 128):
+        if part is not None:
+            os.environ["FA_B200_DECODE_PARTITION"] = str(part)
+        try:
+            out, lse = flash_attn.flash_attn_with_kvcache(q.cuda(), k8.cuda(), v8.cuda(), cache_seqlens=sl.cuda(),
+                                                          block_table=bt.cuda(), causal=True, return_softmax_lse=True,
+                                                          k_descale=kd.cuda(), v_descale=vd.cuda())
+            torch.cuda.synchronize()
+        finally:
+            os.environ.pop("FA_B200_DECODE_PARTITION", None)
+        assert cuda.device_status() == 0
+        assert out.dtype == qdtype
+        assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=3.0, eps=2 ** -8, what=f"fp8 kv cache part {part}")
+        assert max_err(lse.cpu(), ref_lse) < 2e-3
+    if sq == 1:
+        k_raw = k8.cuda().permute(0, 2, 1, 3).contiguous().view(torch.uint8)       # (blocks, h_k, page, d) bytes
+        v_raw = v8.cuda().permute(0, 2, 1, 3).contiguous().view(torch.uint8)
+        o2 = flash_attn.vllm_flash_attn_with_kvcache(q.cuda(), k_raw, v_raw, cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                                     causal=True, k_scale=kd.cuda(), v_scale=vd.cuda(), kv_cache_dtype="fp8",
+                                                     layout=1)
+        torch.cuda.synchronize()
+        assert_close_to_oracle(o2.cpu(), ref32, ref_pt, mult=3.0, eps=2 ** -8, what="fp8 kv cache, vllm entry")
