@@ -79,15 +79,15 @@ int elem_size(int dtype) { return dtype == FA_B200_E4M3 ? 1 : 2; }
 // 4-D tile descriptor over (d, heads, rows, batch) with a 128-byte-swizzled box of (128 bytes, 1, box_rows, 1).
 // Strides are in elements.  Out-of-range rows read as zero.
 int make_tmap(CUtensorMap* out, const void* base, int dtype, int64_t heads, int64_t rows, int64_t batch,
-              int64_t head_stride, int64_t row_stride, int64_t batch_stride, int box_rows) {
+              int64_t head_stride, int64_t row_stride, int64_t batch_stride, int box_rows, int d = kHeadDim) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) { set_error("cuTensorMapEncodeTiled", "driver entry point not found"); return FA_B200_ERR_CUDA; }
   const int es = elem_size(dtype);
   static const uint8_t dummy[64] __attribute__((aligned(64))) = {};
   void* addr = const_cast<void*>(base ? base : static_cast<const void*>(dummy));
-  cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(heads > 0 ? heads : 1),
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(heads > 0 ? heads : 1),
                         static_cast<cuuint64_t>(rows > 0 ? rows : 1), static_cast<cuuint64_t>(batch > 0 ? batch : 1)};
-  auto fix = [&](int64_t s) { return static_cast<cuuint64_t>((s > 0 ? s : kHeadDim) * es); };
+  auto fix = [&](int64_t s) { return static_cast<cuuint64_t>((s > 0 ? s : d) * es); };
   cuuint64_t strides[3] = {fix(head_stride), fix(row_stride), fix(batch_stride)};
   cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / es), 1u, static_cast<cuuint32_t>(box_rows), 1u};
   cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -137,6 +137,10 @@ int env_int(const char* name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 
+// 128 everywhere; 64, 192 and 256 for 16-bit tensors in the plain layouts (`only128`: the call uses a variant that is
+// built for 128 alone).
+bool head_dim_ok(int d, bool only128) { return d == kHeadDim || (!only128 && (d == 64 || d == 192 || d == 256)); }
+
 struct DecodePlan {
   int status;
   int group, tile, box_tok, partition_tokens, num_partitions, max_len;
@@ -147,7 +151,7 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   DecodePlan pl{};
   pl.status = FA_B200_OK;
   if (!p) { pl.status = FA_B200_ERR_NULL; return pl; }
-  if (p->d != kHeadDim) { pl.status = FA_B200_ERR_HEADDIM; return pl; }
+  if (!head_dim_ok(p->d, p->dtype == FA_B200_E4M3 || p->kv_e4m3 || p->v_transposed)) { pl.status = FA_B200_ERR_HEADDIM; return pl; }
   if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) { pl.status = FA_B200_ERR_DTYPE; return pl; }
   if (p->b < 0 || p->h <= 0 || p->h_k <= 0 || p->max_blocks_per_seq < 0 || p->num_blocks < 0) { pl.status = FA_B200_ERR_SHAPE; return pl; }
   if (p->h % p->h_k != 0 || p->h / p->h_k > 16) { pl.status = FA_B200_ERR_HEADS; return pl; }
@@ -197,7 +201,7 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
 size_t decode_ws_bytes(const fa_b200_decode_params* p, const DecodePlan& pl) {
   if (!pl.split) return 0;
   const size_t sq = p->seqlen_q > 1 ? p->seqlen_q : 1;
-  return static_cast<size_t>(pl.num_partitions) * p->b * p->h * sq * (kHeadDim + 1) * sizeof(float);
+  return static_cast<size_t>(pl.num_partitions) * p->b * p->h * sq * (p->d + 1) * sizeof(float);
 }
 
 }  // namespace
@@ -216,7 +220,7 @@ const char* fa_b200_status_string(int s) {
     case FA_B200_OK: return "ok";
     case FA_B200_ERR_NULL: return "a required pointer is null";
     case FA_B200_ERR_DTYPE: return "unsupported element type";
-    case FA_B200_ERR_HEADDIM: return "head dimension must be 128";
+    case FA_B200_ERR_HEADDIM: return "head dimension must be 128 (or 64, 192, 256 with fp16 / bf16 tensors in the plain layouts)";
     case FA_B200_ERR_HEADS: return "Number of heads in key/value must divide number of heads in query (group <= 16 for decode)";
     case FA_B200_ERR_STRIDE: return "Input tensor must have contiguous last dimension and 16-byte aligned strides";
     case FA_B200_ERR_SHAPE: return "inconsistent or negative sizes";
@@ -374,7 +378,7 @@ bool sink_dtype_ok(const void* s_aux, int dtype) {
 int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
   if (!p || !p->o_partial || !p->lse_partial) return FA_B200_ERR_NULL;
   if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
-  if (p->d != kHeadDim) return FA_B200_ERR_HEADDIM;
+  if (!head_dim_ok(p->d, false)) return FA_B200_ERR_HEADDIM;
   if (p->rows < 0 || p->num_parts < 0 || p->h <= 0 || p->rows % p->h != 0) return FA_B200_ERR_SHAPE;
   if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16 && p->out_dtype >= 0) return FA_B200_ERR_DTYPE;
   if (!aligned16(p->o_partial) || (p->out && !aligned16(p->out))) return FA_B200_ERR_ALIGN;
@@ -399,7 +403,8 @@ int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
   k.out_scale = p->out_scale;
   k.s_aux = p->s_aux;
   k.s_aux_dtype = p->s_aux_dtype;
-  k.o_part_stride = p->o_part_stride > 0 ? p->o_part_stride : static_cast<int64_t>(p->rows) * kHeadDim;
+  k.d = p->d;
+  k.o_part_stride = p->o_part_stride > 0 ? p->o_part_stride : static_cast<int64_t>(p->rows) * p->d;
   k.lse_part_stride = p->lse_part_stride > 0 ? p->lse_part_stride : p->rows;
   if (k.o_part_stride % 4 != 0) return FA_B200_ERR_STRIDE;
   cudaError_t e = launch_combine(k, static_cast<cudaStream_t>(stream));
@@ -434,7 +439,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
 
   CUtensorMap tk, tv;
   int st = make_tmap(&tk, p->k_cache, kv_dtype, p->h_k, p->page_size, p->num_blocks, p->k_head_stride, p->k_row_stride,
-                     p->k_block_stride, pl.box_tok);
+                     p->k_block_stride, pl.box_tok, p->d);
   if (st != FA_B200_OK) return st;
   if (p->v_transposed) {
     if (kv_dtype == FA_B200_E4M3) return FA_B200_ERR_UNSUPPORTED;
@@ -443,7 +448,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
                       p->v_head_stride, p->v_block_stride);
   } else {
     st = make_tmap(&tv, p->v_cache, kv_dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
-                   p->v_block_stride, pl.box_tok);
+                   p->v_block_stride, pl.box_tok, p->d);
   }
   if (st != FA_B200_OK) return st;
 
@@ -481,11 +486,12 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.sq = p->seqlen_q > 1 ? p->seqlen_q : 1;
   k.causal = p->is_causal ? 1 : 0;
   k.kv_e4m3 = p->kv_e4m3 ? 1 : 0;
+  k.d = p->d;
   k.q_row_stride = p->q_row_stride;
   k.o_row_stride = p->o_row_stride;
   if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
-    k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * k.sq * kHeadDim;
+    k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * k.sq * p->d;
   }
   if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
   cudaError_t e = launch_decode(p->dtype, tk, tv, k, stream);
@@ -504,14 +510,15 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
     c.sq = k.sq;
     c.partition_tokens = pl.partition_tokens;
     c.out_scale = 1.f;
-    c.o_part_stride = static_cast<int64_t>(c.rows) * kHeadDim;
+    c.d = p->d;
+    c.o_part_stride = static_cast<int64_t>(c.rows) * p->d;
     c.lse_part_stride = c.rows;
     if (p->o_partial_out) {
       c.out = p->o_partial_out;
       c.lse = p->lse_partial_out;
-      c.out_row_stride = static_cast<int64_t>(k.sq) * kHeadDim;          // partial rows are (b, h, tok)
-      c.out_batch_stride = static_cast<int64_t>(p->h) * k.sq * kHeadDim;
-      c.out_tok_stride = kHeadDim;
+      c.out_row_stride = static_cast<int64_t>(k.sq) * p->d;          // partial rows are (b, h, tok)
+      c.out_batch_stride = static_cast<int64_t>(p->h) * k.sq * p->d;
+      c.out_tok_stride = p->d;
       c.out_dtype = -1;
       c.lse_empty_is_neg = 1;
     } else {
@@ -578,7 +585,7 @@ int fa_b200_decode_paged_static(const fa_b200_decode_params* p, void* stream) {
 static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!p) return FA_B200_ERR_NULL;
-  if (p->d != kHeadDim) return FA_B200_ERR_HEADDIM;
+  if (!head_dim_ok(p->d, p->dtype == FA_B200_E4M3)) return FA_B200_ERR_HEADDIM;
   if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) return FA_B200_ERR_DTYPE;
   if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
   if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
@@ -622,33 +629,34 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   const int64_t q_rows = varlen ? p->total_q : p->seqlen_q, k_rows = varlen ? p->total_k : p->seqlen_k;
   const int64_t nb = varlen ? 1 : p->b;
   int st = make_tmap(&tq, p->q, p->dtype, p->h, q_rows, nb, p->q_head_stride, p->q_row_stride,
-                     varlen ? p->q_row_stride * (q_rows > 0 ? q_rows : 1) : p->q_batch_stride, 128);
+                     varlen ? p->q_row_stride * (q_rows > 0 ? q_rows : 1) : p->q_batch_stride, 128, p->d);
   if (st != FA_B200_OK) return st;
   if (paged) {
     st = make_tmap(&tk, p->k, p->dtype, p->h_k, p->page_size, p->num_blocks, p->k_head_stride, p->k_row_stride,
-                   p->k_batch_stride, box_rows);
+                   p->k_batch_stride, box_rows, p->d);
     if (st != FA_B200_OK) return st;
     st = make_tmap(&tv, p->v, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
-                   p->v_batch_stride, box_rows);
+                   p->v_batch_stride, box_rows, p->d);
   } else {
     st = make_tmap(&tk, p->k, p->dtype, p->h_k, k_rows, nb, p->k_head_stride, p->k_row_stride,
-                   varlen ? p->k_row_stride * (k_rows > 0 ? k_rows : 1) : p->k_batch_stride, 128);
+                   varlen ? p->k_row_stride * (k_rows > 0 ? k_rows : 1) : p->k_batch_stride, 128, p->d);
     if (st != FA_B200_OK) return st;
     st = make_tmap(&tv, p->v, p->dtype, p->h_k, k_rows, nb, p->v_head_stride, p->v_row_stride,
-                   varlen ? p->v_row_stride * (k_rows > 0 ? k_rows : 1) : p->v_batch_stride, 128);
+                   varlen ? p->v_row_stride * (k_rows > 0 ? k_rows : 1) : p->v_batch_stride, 128, p->d);
   }
   if (st != FA_B200_OK) return st;
 
   // output map for whole-tile stores (strides and base are 16-byte aligned by the checks above)
   CUtensorMap to;
   st = make_tmap(&to, p->out, p->out_dtype, p->h, q_rows, nb, p->o_head_stride, p->o_row_stride,
-                 varlen ? p->o_row_stride * (q_rows > 0 ? q_rows : 1) : p->o_batch_stride, 128);
+                 varlen ? p->o_row_stride * (q_rows > 0 ? q_rows : 1) : p->o_batch_stride, 128, p->d);
   if (st != FA_B200_OK) return st;
 
   PrefillKernelParams k{};
   k.status = status_ptr();
   if (!k.status) return cuda_fail("status word", cudaGetLastError());
   k.o_tma = 1;
+  k.d = p->d;
   k.s_aux = p->s_aux;
   k.s_aux_dtype = p->s_aux_dtype;
   k.out = p->out;
@@ -696,11 +704,12 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   // double-buffered scores ("dense").  Tile lists are per head and run one tile per CTA ("single").
   // FA_B200_PREFILL_KERNEL=single|pair|dense overrides the choice where it is legal (tests, comparisons).
   const bool even_group = (p->h / p->h_k) % 2 == 0;
-  int which = (sparse || paged) ? 0 : (even_group ? 1 : 2);   // paged K/V: one-tile kernel
+  const bool one_tile_only = sparse || paged || p->d != kHeadDim;   // paged K/V, other head dimensions: one-tile kernel
+  int which = one_tile_only ? 0 : (even_group ? 1 : 2);
   if (const char* ov = getenv("FA_B200_PREFILL_KERNEL")) {
     if (!strcmp(ov, "single")) which = 0;
-    else if (!strcmp(ov, "pair") && !sparse && !paged && even_group) which = 1;
-    else if (!strcmp(ov, "dense") && !sparse && !paged) which = 2;
+    else if (!strcmp(ov, "pair") && !one_tile_only && even_group) which = 1;
+    else if (!strcmp(ov, "dense") && !one_tile_only) which = 2;
   }
   if (which != 0) {   // the persistent kernels claim their work items from a counter
     k.work_counter = next_work_counter(stream);
@@ -718,5 +727,87 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
 
 int fa_b200_fwd(const fa_b200_fwd_params* p, void* stream) { return fwd_common(p, stream, false); }
 int fa_b200_fwd_sparse(const fa_b200_fwd_params* p, void* stream) { return fwd_common(p, stream, true); }
+
+namespace {
+// The decode parameters of the raw-pointer entry (sizes only for the workspace query).
+fa_b200_decode_params raw_decode_params(int32_t num_query, int32_t num_q_head, int32_t num_kv_head, int32_t num_dim,
+                                        int32_t num_pages, int32_t page_size, int32_t max_seqlen_k, int32_t dtype) {
+  fa_b200_decode_params d{};
+  d.b = num_query; d.h = num_q_head; d.h_k = num_kv_head; d.d = num_dim;
+  d.num_blocks = num_pages; d.page_size = page_size;
+  d.max_blocks_per_seq = page_size > 0 ? (max_seqlen_k - 1) / page_size + 1 : 0;
+  d.max_seqlen_k = max_seqlen_k;
+  d.dtype = dtype; d.out_dtype = dtype;
+  return d;
+}
+}  // namespace
+
+size_t fa_b200_kv_cache_attention_workspace_bytes(int32_t num_query, int32_t num_q_head, int32_t num_kv_head,
+                                                  int32_t num_dim, int32_t page_size, int32_t max_seqlen_k) {
+  // the pool size and the 16-bit element type do not enter the partition plan
+  fa_b200_decode_params d = raw_decode_params(num_query, num_q_head, num_kv_head, num_dim, 1, page_size, max_seqlen_k,
+                                              FA_B200_BF16);
+  return fa_b200_decode_workspace_bytes(&d);
+}
+
+int fa_b200_kv_cache_attention(const void* q, const int32_t* seq_offsets, int32_t max_seqlen_q, int32_t max_seqlen_k,
+                               const void* k_caches, const void* v_caches, const int32_t* page_tables,
+                               const int32_t* cache_lens, void* out, int32_t num_query, int32_t num_tokens,
+                               int32_t num_q_head, int32_t num_kv_head, int32_t num_dim, int32_t num_pages,
+                               int32_t page_size, int32_t dtype, int32_t layout, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  if (dtype != FA_B200_F16 && dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
+  if (layout < 0 || layout > 2) return FA_B200_ERR_UNSUPPORTED;
+  if (num_query < 0 || num_tokens < num_query || num_q_head <= 0 || num_kv_head <= 0 || num_pages <= 0 || page_size <= 0 ||
+      max_seqlen_k <= 0)
+    return FA_B200_ERR_SHAPE;
+  if (!head_dim_ok(num_dim, layout == 0)) return FA_B200_ERR_HEADDIM;
+  if (num_query == 0) return FA_B200_OK;
+  const int64_t d = num_dim, hk = num_kv_head, ps = page_size;
+  const int64_t block_stride = hk * ps * d;
+  const int64_t row_stride = layout == 2 ? hk * d : d, head_stride = layout == 2 ? d : ps * d;
+  const int32_t max_pages = (max_seqlen_k - 1) / page_size + 1;
+  const float scale = 1.0f / sqrtf(static_cast<float>(num_dim));
+  if (num_query == num_tokens) {
+    fa_b200_decode_params p = raw_decode_params(num_query, num_q_head, num_kv_head, num_dim, num_pages, page_size,
+                                                max_seqlen_k, dtype);
+    p.q = q; p.k_cache = k_caches; p.v_cache = v_caches; p.out = out;
+    p.q_batch_stride = p.o_batch_stride = static_cast<int64_t>(num_q_head) * d;
+    p.q_head_stride = p.o_head_stride = d;
+    p.k_block_stride = p.v_block_stride = block_stride;
+    p.k_row_stride = row_stride; p.k_head_stride = head_stride;
+    if (layout == 0) {   // V (pages, kv heads, d, page): "row" = one d row of page_size tokens
+      p.v_transposed = 1; p.v_row_stride = ps; p.v_head_stride = d * ps;
+      p.k_row_stride = d; p.k_head_stride = ps * d;
+    } else {
+      p.v_row_stride = row_stride; p.v_head_stride = head_stride;
+    }
+    p.block_table = page_tables; p.block_table_batch_stride = max_pages;
+    p.cache_seqlens = cache_lens;
+    p.softmax_scale = scale;
+    p.workspace = workspace; p.workspace_bytes = workspace_bytes;
+    return fa_b200_decode_paged(&p, stream);
+  }
+  if (layout == 0) return FA_B200_ERR_UNSUPPORTED;
+  if (!seq_offsets) return FA_B200_ERR_NULL;
+  fa_b200_fwd_params p{};
+  p.q = q; p.k = k_caches; p.v = v_caches; p.out = out;
+  p.q_row_stride = p.o_row_stride = static_cast<int64_t>(num_q_head) * d;
+  p.q_head_stride = p.o_head_stride = d;
+  p.k_batch_stride = p.v_batch_stride = block_stride;
+  p.k_row_stride = p.v_row_stride = row_stride;
+  p.k_head_stride = p.v_head_stride = head_stride;
+  p.b = num_query; p.seqlen_q = max_seqlen_q; p.seqlen_k = max_seqlen_k;
+  p.h = num_q_head; p.h_k = num_kv_head; p.d = num_dim;
+  p.total_q = num_tokens; p.total_k = 0;
+  p.cu_seqlens_q = seq_offsets;
+  p.softmax_scale = scale;
+  p.is_causal = 1;
+  p.dtype = dtype; p.out_dtype = dtype;
+  p.block_table = page_tables; p.block_table_batch_stride = max_pages;
+  p.seqused_k = cache_lens;
+  p.page_size = page_size; p.num_blocks = num_pages;
+  return fa_b200_fwd(&p, stream);
+}
 
 }  // extern "C"

@@ -1,5 +1,5 @@
-// LSE-combine of split-KV partials: one CTA of four warps per (sequence, head) row, each lane owns four of the
-// 128 output columns.  Partials are fp32, normalised by their own partition's softmax sum, with a
+// LSE-combine of split-KV partials: one CTA of four warps per (sequence, head) row, each lane owns four of every
+// 128 output columns (head dimension 128: one group of four; 256: two; 64: the first sixteen lanes).  Partials are fp32, normalised by their own partition's softmax sum, with a
 // natural-log LSE (-inf or +inf marks a partition without keys).
 //   M = max_i lse_i;  w_i = e^{lse_i - M};  O = sum_i w_i O_i / sum_i w_i;  LSE = M + ln sum_i w_i
 // An attention sink (one logit per head) is one more term of the sum that carries no value.
@@ -16,9 +16,11 @@ constexpr int kCombineWarps = 4;
 // One CTA per (sequence, head) row.  The four warps share the partitions of the row (warp w takes partitions
 // w, w + 4, ...), each lane owns four of the 128 output columns, and the warps' partial sums meet in shared memory,
 // so a row with hundreds of partitions (one very long sequence) is not walked by a single warp.
+// NV: groups of 128 columns (ceil(d / 128)).
+template <int NV>
 __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineKernelParams p) {
   __shared__ float red_max[kCombineWarps], red_sum[kCombineWarps];
-  __shared__ float4 red_acc[kCombineWarps][32];
+  __shared__ float4 red_acc[kCombineWarps][NV][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
   const int sq = p.sq > 0 ? p.sq : 1;
@@ -60,56 +62,80 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   const bool empty = !(sum > 0.f);
   const float lse_tot = empty ? 0.f : mx + logf(sum);
 
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  // columns of this lane: 4 * lane + 128 * v, v < NV, those below d
+  bool live[NV];
+  float4 acc[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    live[v] = 4 * lane + 128 * v < p.d;
+    acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   if (!empty) {
     const float4* op = reinterpret_cast<const float4*>(p.o_partial) + lane;
+    const int64_t row_off = static_cast<int64_t>(row) * p.d;
     int i = warp;
     for (; i + 3 * kCombineWarps < nparts; i += 4 * kCombineWarps) {
       float l[4];
-      float4 v[4];
+      float4 v[4][NV];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         l[j] = p.lse_partial[(i + j * kCombineWarps) * p.lse_part_stride + row];
-        v[j] = op[((i + j * kCombineWarps) * p.o_part_stride + row * kHeadDim) / 4];
+#pragma unroll
+        for (int g = 0; g < NV; ++g)
+          if (live[g]) v[j][g] = op[((i + j * kCombineWarps) * p.o_part_stride + row_off) / 4 + 32 * g];
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float w = (l[j] == INFINITY || l[j] == -INFINITY) ? 0.f : expf(l[j] - lse_tot);
         // a weight of exactly zero must not pick up NaN/Inf from an unused partial
-        if (w != 0.f) { acc.x += w * v[j].x; acc.y += w * v[j].y; acc.z += w * v[j].z; acc.w += w * v[j].w; }
+        if (w != 0.f) {
+#pragma unroll
+          for (int g = 0; g < NV; ++g)
+            if (live[g]) { acc[g].x += w * v[j][g].x; acc[g].y += w * v[j][g].y; acc[g].z += w * v[j][g].z; acc[g].w += w * v[j][g].w; }
+        }
       }
     }
     for (; i < nparts; i += kCombineWarps) {
       const float l = p.lse_partial[i * p.lse_part_stride + row];
-      const float4 v = op[(i * p.o_part_stride + row * kHeadDim) / 4];
       const float w = (l == INFINITY || l == -INFINITY) ? 0.f : expf(l - lse_tot);
-      if (w != 0.f) { acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w; }
+      if (w != 0.f) {
+#pragma unroll
+        for (int g = 0; g < NV; ++g)
+          if (live[g]) {
+            const float4 v = op[(i * p.o_part_stride + row_off) / 4 + 32 * g];
+            acc[g].x += w * v.x; acc[g].y += w * v.y; acc[g].z += w * v.z; acc[g].w += w * v.w;
+          }
+      }
     }
   }
-  red_acc[warp][lane] = acc;
+#pragma unroll
+  for (int g = 0; g < NV; ++g) red_acc[warp][g][lane] = acc[g];
   __syncthreads();
   if (warp != 0) return;
-  // fixed summation order: the result does not depend on scheduling
-  acc = red_acc[0][lane];
 #pragma unroll
-  for (int w = 1; w < kCombineWarps; ++w) {
-    const float4 t = red_acc[w][lane];
-    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-  }
-  acc.x *= p.out_scale; acc.y *= p.out_scale; acc.z *= p.out_scale; acc.w *= p.out_scale;
-  if (p.out) {
-    const int64_t off = static_cast<int64_t>(bi) * p.out_batch_stride + static_cast<int64_t>(hi) * p.out_row_stride +
-                        static_cast<int64_t>(ti) * p.out_tok_stride + lane * 4;
-    if (p.out_dtype == FA_B200_BF16) {
-      __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), c = __floats2bfloat162_rn(acc.z, acc.w);
-      uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));
-      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = u;
-    } else if (p.out_dtype == FA_B200_F16) {
-      __half2 a = __floats2half2_rn(acc.x, acc.y), c = __floats2half2_rn(acc.z, acc.w);
-      uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));
-      *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + off) = u;
-    } else {
-      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off) = acc;
+  for (int g = 0; g < NV; ++g) {
+    // fixed summation order: the result does not depend on scheduling
+    float4 a = red_acc[0][g][lane];
+#pragma unroll
+    for (int w = 1; w < kCombineWarps; ++w) {
+      const float4 t = red_acc[w][g][lane];
+      a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+    }
+    a.x *= p.out_scale; a.y *= p.out_scale; a.z *= p.out_scale; a.w *= p.out_scale;
+    if (p.out && live[g]) {
+      const int64_t off = static_cast<int64_t>(bi) * p.out_batch_stride + static_cast<int64_t>(hi) * p.out_row_stride +
+                          static_cast<int64_t>(ti) * p.out_tok_stride + lane * 4 + 128 * g;
+      if (p.out_dtype == FA_B200_BF16) {
+        __nv_bfloat162 x = __floats2bfloat162_rn(a.x, a.y), c = __floats2bfloat162_rn(a.z, a.w);
+        uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&c));
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = u;
+      } else if (p.out_dtype == FA_B200_F16) {
+        __half2 x = __floats2half2_rn(a.x, a.y), c = __floats2half2_rn(a.z, a.w);
+        uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&c));
+        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + off) = u;
+      } else {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off) = a;
+      }
     }
   }
   if (p.lse && lane == 0) p.lse[row] = empty ? (p.lse_empty_is_neg ? -INFINITY : INFINITY) : lse_tot;
@@ -120,7 +146,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
 cudaError_t launch_combine(const CombineKernelParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return cudaSuccess;
   const int grid = p.rows;
-  combine_kernel<<<grid, kCombineWarps * 32, 0, stream>>>(p);
+  if (p.d > 128) combine_kernel<2><<<grid, kCombineWarps * 32, 0, stream>>>(p);
+  else combine_kernel<1><<<grid, kCombineWarps * 32, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

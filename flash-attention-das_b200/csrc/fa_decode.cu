@@ -20,18 +20,21 @@ namespace {
 
 constexpr int kConsumerWarps = 4;
 constexpr int kDecodeThreads = 32 * (1 + kConsumerWarps);
-constexpr int kStageBytes = 32768;      // K tile 16 KB + V tile 16 KB
 constexpr int kMaxPagesPerPartition = 512;
 
-template <int DT>
+// HD: head dimension, 128 for every element type and 64 / 192 / 256 for the 16-bit ones.
+template <int DT, int HD = 128>
 struct DecodeTraits {
   static constexpr bool kFp8 = (DT == FA_B200_E4M3);
   static constexpr int kElem = kFp8 ? 1 : 2;
   static constexpr int kTile = kFp8 ? 128 : 64;            // tokens per stage
   static constexpr int kRowsPerWarp = kTile / kConsumerWarps;
   static constexpr int kSub = kRowsPerWarp / 16;            // 16-token sub-blocks per warp per tile
-  static constexpr int kHalves = kFp8 ? 1 : 2;             // 128-byte column groups per K/V row
-  static constexpr int kQSteps = kFp8 ? 4 : 8;             // MMA k-steps over d = 128
+  static constexpr int kHalves = HD * kElem / 128;         // 128-byte column groups per K/V row
+  static constexpr int kQSteps = HD * kElem / 32;          // MMA k-steps over d
+  static constexpr int kNT = HD / 8;                        // 8-column accumulator tiles of O
+  static constexpr int kStageBytes = 2 * kTile * HD * kElem;   // one K tile + one V tile
+  static_assert(HD == 128 || (!kFp8 && (HD == 64 || HD == 192 || HD == 256)), "head dimension");
 };
 
 template <int DT>
@@ -57,13 +60,15 @@ __device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
 // QT: element type of the queries.  Normally QT == DT; QT = F16 / BF16 with DT = E4M3 is the "fp8 KV cache" mode: the
 // cache is e4m3, the queries (and the output) are 16-bit.  K is then converted to f16 in registers on its way into the
 // Q K^T product (f16 MMA; bf16 queries are converted to f16 once per CTA), V as in the all-e4m3 mode.
-template <int DT, int STAGES, bool VT, int QT = DT>
-__global__ void __launch_bounds__(kDecodeThreads, 2)
+template <int DT, int STAGES, bool VT, int QT = DT, int HD = 128>
+__global__ void __launch_bounds__(kDecodeThreads, HD > 128 ? 1 : 2)
 decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                     const DecodeKernelParams p) {
-  using T = DecodeTraits<DT>;
+  using T = DecodeTraits<DT, HD>;
   constexpr bool kMixed = (QT != DT);
+  constexpr int kStageBytes = T::kStageBytes;
   static_assert(!kMixed || (DT == FA_B200_E4M3 && !VT), "mixed mode: 16-bit queries over an e4m3 cache");
+  static_assert(HD == 128 || (!kMixed && !VT), "other head dimensions: plain 16-bit pools only");
   constexpr int kQElem = kMixed ? 2 : T::kElem;
   constexpr int kQRegSteps = kMixed ? 8 : T::kQSteps;
   extern __shared__ uint8_t smem_raw[];
@@ -123,9 +128,9 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int group = p.group;  // query heads per kv head (rows of the packed query tile), <= 16
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
-  float o[16][4];
+  float o[T::kNT][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  for (int i = 0; i < T::kNT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -314,7 +319,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         l_run[1] = l_run[1] * al1 + ps1;
         if (__any_sync(0xffffffffu, (al0 != 1.f) || (al1 != 1.f))) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < T::kNT; ++i) {
             o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1;
           }
         }
@@ -350,7 +355,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           const int rsw = row & 7;
           if constexpr (!T::kFp8) {
 #pragma unroll
-            for (int nd = 0; nd < 16; nd += 2) {
+            for (int nd = 0; nd < T::kNT; nd += 2) {
               const int chunk = nd + (mi >> 1);
               const uint32_t addr = rbase + (chunk >> 3) * (T::kTile * 128) + (((chunk & 7) ^ rsw) << 4);
               uint32_t v0, v1, v2, v3;
@@ -397,7 +402,8 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   }
   __syncthreads();  // every tile consumed: the ring is free to be reused as the cross-warp reduce buffer
   const bool aborted = (*abort_flag != 0);
-  float* red = reinterpret_cast<float*>(stages);  // [4 warps][16 rows][128]
+  float* red = reinterpret_cast<float*>(stages);  // [4 warps][16 rows][HD]
+  static_assert(kConsumerWarps * 16 * HD * 4 <= STAGES * kStageBytes, "the reduce buffer reuses the ring");
   if (warp > 0 && !aborted) {
     const int cw = warp - 1;
     const int g = lane >> 2, qd = lane & 3;
@@ -409,9 +415,9 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) mg = fmaxf(mg, sm_m[w * 16 + row]);
         const float f = (mg == -INFINITY) ? 0.f : fast_exp2(m_run[rr] - mg);
-        float* dst = red + (cw * 16 + row) * kHeadDim;
+        float* dst = red + (cw * 16 + row) * HD;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < T::kNT; ++j) {
           int d0, d1;
           if constexpr (T::kFp8) {
             d0 = (j >> 1) * 16 + 4 * qd + (j & 1);
@@ -428,41 +434,49 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   }
   __syncthreads();
   if (warp > 0 && !aborted) {
-    const int tid = threadIdx.x - 32;  // 0..127 = d
+    const int tid = threadIdx.x - 32;  // 0..127: column d = tid, tid + 128, ...
     float vds = 1.f;
     if (p.v_descale) vds = p.v_descale[b * p.vds_b + hk * p.vds_h];
     for (int row = 0; row < p.sq * group; ++row) {
       float mg = -INFINITY;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) mg = fmaxf(mg, sm_m[w * 16 + row]);
-      float L = 0.f, acc = 0.f;
+      float L = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) {
         const float mw = sm_m[w * 16 + row];
         L += (mw == -INFINITY) ? 0.f : sm_l[w * 16 + row] * fast_exp2(mw - mg);
-        acc += red[(w * 16 + row) * kHeadDim + tid];
       }
       const int tok = row / group;                 // query token of this row
       const int head = hk * group + row % group;
       bool empty = !(L > 0.f);
-      float outv = empty ? 0.f : acc / L * vds;
+      float inv = empty ? 0.f : 1.f / L;
       float lse = empty ? -INFINITY : (mg + log2f(L)) * kLn2;
-      if (p.write_final && p.s_aux) {   // the sink is one more term of the row's sum
-        float inv;
-        finish_row(mg, L, load_sink_log2(p.s_aux, p.s_aux_dtype, head), inv, lse, empty);
-        outv = acc * inv * vds;
+      const bool sink = p.write_final && p.s_aux;   // the sink is one more term of the row's sum
+      if (sink) finish_row(mg, L, load_sink_log2(p.s_aux, p.s_aux_dtype, head), inv, lse, empty);
+      const int64_t slot = ((static_cast<int64_t>(part) * p.b + b) * p.h + head) * p.sq + tok;
+#pragma unroll
+      for (int dd = tid; dd < HD; dd += 128) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) acc += red[(w * 16 + row) * HD + dd];
+        const float outv = sink ? acc * inv * vds : (empty ? 0.f : acc / L * vds);
+        if (p.write_final) {
+          const int64_t oi = static_cast<int64_t>(b) * p.o_batch_stride + static_cast<int64_t>(tok) * p.o_row_stride +
+                             static_cast<int64_t>(head) * p.o_head_stride + dd;
+          if (p.out_dtype == FA_B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(outv);
+          else reinterpret_cast<__half*>(p.out)[oi] = __float2half_rn(outv);
+        } else {
+          // partial rows are (sequence, head, token): the layout of the (b, h, sq) LSE
+          p.o_partial[slot * HD + dd] = outv;
+        }
       }
-      if (p.write_final) {
-        const int64_t oi = static_cast<int64_t>(b) * p.o_batch_stride + static_cast<int64_t>(tok) * p.o_row_stride +
-                           static_cast<int64_t>(head) * p.o_head_stride + tid;
-        if (p.out_dtype == FA_B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(outv);
-        else reinterpret_cast<__half*>(p.out)[oi] = __float2half_rn(outv);
-        if (tid == 0 && p.lse_out) p.lse_out[(static_cast<int64_t>(b) * p.h + head) * p.sq + tok] = empty ? INFINITY : lse;
-      } else {
-        // partial rows are (sequence, head, token): the layout of the (b, h, sq) LSE
-        const int64_t slot = ((static_cast<int64_t>(part) * p.b + b) * p.h + head) * p.sq + tok;
-        p.o_partial[slot * kHeadDim + tid] = outv;
-        if (tid == 0) p.lse_partial[slot] = lse;
+      if (tid == 0) {
+        if (p.write_final) {
+          if (p.lse_out) p.lse_out[(static_cast<int64_t>(b) * p.h + head) * p.sq + tok] = empty ? INFINITY : lse;
+        } else {
+          p.lse_partial[slot] = lse;
+        }
       }
     }
   }
@@ -470,18 +484,19 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 
 }  // namespace
 
-size_t decode_smem_bytes(int stages) {
-  return 1024 + static_cast<size_t>(stages) * kStageBytes + 2 * stages * 8 + 2 * kConsumerWarps * 16 * 4 +
+static size_t decode_smem_bytes(int stages, int stage_bytes) {
+  return 1024 + static_cast<size_t>(stages) * stage_bytes + 2 * stages * 8 + 2 * kConsumerWarps * 16 * 4 +
          kMaxPagesPerPartition * 4 + 16;
 }
 int decode_max_pages_per_partition() { return kMaxPagesPerPartition; }
 
-template <int DT, bool VT, int QT = DT>
+template <int DT, bool VT, int QT = DT, int HD = 128>
 static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
                                     cudaStream_t stream) {
-  constexpr int STAGES = 3;
-  auto kern = decode_paged_kernel<DT, STAGES, VT, QT>;
-  const size_t smem = decode_smem_bytes(STAGES);
+  // about 96 KB of tiles in flight per CTA at two CTAs per SM; one CTA per SM above d = 128
+  constexpr int STAGES = HD == 64 ? 6 : (HD == 192 ? 4 : 3);
+  auto kern = decode_paged_kernel<DT, STAGES, VT, QT, HD>;
+  const size_t smem = decode_smem_bytes(STAGES, DecodeTraits<DT, HD>::kStageBytes);
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -497,6 +512,19 @@ static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv
 
 cudaError_t launch_decode(int dtype, const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
                           cudaStream_t stream) {
+  if (p.d != 128) {   // other head dimensions: plain 16-bit pools
+    if (p.kv_e4m3 || p.v_transposed || dtype == FA_B200_E4M3) return cudaErrorInvalidValue;
+    const bool bf = dtype == FA_B200_BF16;
+    switch (p.d) {
+      case 64: return bf ? launch_decode_dt<FA_B200_BF16, false, FA_B200_BF16, 64>(tk, tv, p, stream)
+                         : launch_decode_dt<FA_B200_F16, false, FA_B200_F16, 64>(tk, tv, p, stream);
+      case 192: return bf ? launch_decode_dt<FA_B200_BF16, false, FA_B200_BF16, 192>(tk, tv, p, stream)
+                          : launch_decode_dt<FA_B200_F16, false, FA_B200_F16, 192>(tk, tv, p, stream);
+      case 256: return bf ? launch_decode_dt<FA_B200_BF16, false, FA_B200_BF16, 256>(tk, tv, p, stream)
+                          : launch_decode_dt<FA_B200_F16, false, FA_B200_F16, 256>(tk, tv, p, stream);
+    }
+    return cudaErrorInvalidValue;
+  }
   if (p.kv_e4m3) {   // 16-bit queries over an e4m3 cache
     if (p.v_transposed) return cudaErrorInvalidValue;
     if (dtype == FA_B200_F16) return launch_decode_dt<FA_B200_E4M3, false, FA_B200_F16>(tk, tv, p, stream);

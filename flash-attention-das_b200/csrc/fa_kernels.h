@@ -37,15 +37,15 @@ struct DecodeKernelParams {
   int32_t sq;           // query tokens per sequence, the last sq positions of it; sq * group <= 16 rows of the MMA tile
   int32_t causal;       // sq > 1: token s sees the keys up to its own position
   int32_t kv_e4m3;      // the cache is e4m3 while the queries are 16-bit (launch_decode's dtype is then the query type)
+  int32_t d;            // head dimension: 128, or 64 / 192 / 256 with 16-bit pools
 };
 
-size_t decode_smem_bytes(int stages);
 int decode_max_pages_per_partition();
 cudaError_t launch_decode(int dtype, const CUtensorMap& tmap_k, const CUtensorMap& tmap_v,
                           const DecodeKernelParams& p, cudaStream_t stream);
 
 struct CombineKernelParams {
-  const float* o_partial;    // [num_parts][rows][128], partitions o_part_stride floats apart
+  const float* o_partial;    // [num_parts][rows][d], partitions o_part_stride floats apart
   const float* lse_partial;  // [num_parts][rows], partitions lse_part_stride floats apart
   int64_t o_part_stride, lse_part_stride;
   void* out;
@@ -57,6 +57,7 @@ struct CombineKernelParams {
   int64_t out_tok_stride;
   int32_t sq;                // query tokens per (sequence, head); rows = b * h * sq
   int32_t num_parts, rows, h;
+  int32_t d;                 // head dimension (64, 128, 192 or 256)
   int32_t partition_tokens;
   int32_t out_dtype;         // FA_B200_F16 / BF16, or -1 for fp32
   int32_t lse_empty_is_neg;  // write -inf (partial convention) instead of +inf for rows with no keys
@@ -103,6 +104,7 @@ struct PrefillKernelParams {
   const void* s_aux;         // attention sinks (h), applied in the epilogue
   int32_t s_aux_dtype;
   int* work_counter;         // persistent kernels: zeroed before the launch; CTAs claim work items past their first from it
+  int32_t d;              // head dimension: 128, or 64 / 192 / 256 (16-bit types, one-tile kernel)
 };
 // One 128-row query tile per CTA, two CTAs per SM: block-sparse lists and odd GQA groups.
 cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,

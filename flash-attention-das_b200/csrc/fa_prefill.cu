@@ -24,15 +24,16 @@ constexpr int kMaxSparseTiles = 512;
 constexpr int kSlots = 2;           // K/V ring
 constexpr int kThreads = 32 * 8;
 constexpr int kProducerWarp = 4, kMmaWarp = 5;
-constexpr int kTmemCols = 256;      // S (128) + O (128)
+// TMEM columns: S (128) + O (head dimension), rounded up to a power of two
+__host__ __device__ constexpr int tmem_cols(int hd) { return 128 + hd <= 256 ? 256 : 512; }
 
 struct SmemLayoutInfo {
   int q_off, ring_off, bar_off, tiles_off, misc_off, total;
 };
 
-template <int DT>
+template <int DT, int HD>
 __host__ __device__ constexpr SmemLayoutInfo smem_layout() {
-  using T = TileTraits<DT>;
+  using T = TileTraits<DT, HD>;
   SmemLayoutInfo s{};
   s.q_off = 0;
   s.ring_off = s.q_off + T::kTileBytes;
@@ -45,12 +46,14 @@ __host__ __device__ constexpr SmemLayoutInfo smem_layout() {
 }
 
 // kLeftWindow: the launch has a left sliding-window bound (kept out of the common build of the softmax loop).
-template <int DT, bool kLeftWindow>
-__global__ void __launch_bounds__(kThreads, 2)
+// HD: head dimension (128; 64, 192, 256 for the 16-bit types — one CTA per SM above 128: shared memory and TMEM).
+template <int DT, bool kLeftWindow, int HD>
+__global__ void __launch_bounds__(kThreads, HD > 128 ? 1 : 2)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const PrefillKernelParams p) {
-  using T = TileTraits<DT>;
-  constexpr SmemLayoutInfo L = smem_layout<DT>();
+  using T = TileTraits<DT, HD>;
+  constexpr SmemLayoutInfo L = smem_layout<DT, HD>();
+  constexpr int kTmemCols = tmem_cols(HD);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bar_off);
@@ -137,7 +140,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     // no visible key for any row of this tile
     if (warp < 4) {
       const int row = (warp & 3) * 32 + lane;
-      if (row < rows_valid) store_empty_row(p, coord_b, bidb, head, static_cast<int64_t>(q_row0) + m0 + row, m0 + row);
+      if (row < rows_valid) store_empty_row<HD>(p, coord_b, bidb, head, static_cast<int64_t>(q_row0) + m0 + row, m0 + row);
     }
     return;
   }
@@ -205,7 +208,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       bool ok = mbar_wait(smem_u32(&kv_full[0]), 0, wctx) && mbar_wait(smem_u32(q_full), 0, wctx);
       if (ok) {
         tc_fence_after();
-        issue_qk<DT>(q_smem, ring_smem, t_s);
+        issue_qk<DT, HD>(q_smem, ring_smem, t_s);
         tc_commit(smem_u32(s_full));
         tc_commit(smem_u32(&kv_empty[0]));   // K_0 is free once S(0) has completed
       }
@@ -215,13 +218,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!mbar_wait(smem_u32(&kv_full[v_slot]), (v_item / kSlots) & 1, wctx)) { ok = false; break; }
         if (!mbar_wait(smem_u32(p_full), j & 1, wctx)) { ok = false; break; }
         tc_fence_after();
-        issue_pv<DT>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
+        issue_pv<DT, HD>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
         tc_commit(smem_u32(&kv_empty[v_slot]));
         if (j + 1 < n_tiles) {
           if (!mbar_wait(smem_u32(&kv_full[k_slot]), (k_item / kSlots) & 1, wctx)) { ok = false; break; }
           tc_fence_after();
           // the tensor pipe executes in issue order: this overwrite of S/P follows the P V read above
-          issue_qk<DT>(q_smem, ring_smem + k_slot * T::kTileBytes, t_s);
+          issue_qk<DT, HD>(q_smem, ring_smem + k_slot * T::kTileBytes, t_s);
           tc_commit(smem_u32(s_full));
           tc_commit(smem_u32(&kv_empty[k_slot]));
         } else {
@@ -260,7 +263,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (p.sparse) { const int v = sm_tiles[j]; start = v & 0x7fffffff; half_tile = (v < 0); }
       int lim = row_limit - start;
       if (half_tile) lim = min(lim, 64);
-      softmax_tile<DT>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, lim,
+      softmax_tile<DT, HD>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, lim,
                        half_tile || start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st);
       if (p.paged && start + kBlockN > sk) {
         // Last tile of a paged sequence: key rows past the end were not fetched, or hold whatever the page holds
@@ -292,7 +295,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const int64_t grow = static_cast<int64_t>(q_row0) + row_in_seq;
       uint8_t* op = out_row_ptr(p, coord_b, grow, head);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < T::kOChunks; ++c) {
         uint32_t o[32];
         tmem_ld_32x32(t_o + c * 32, o);
         tmem_wait_ld();
@@ -312,12 +315,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   }
 }
 
-template <int DT>
+template <int DT, int HD = kHeadDim>
 cudaError_t launch_single_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const PrefillKernelParams& p, cudaStream_t stream) {
   const bool win = p.window_left >= 0;
-  auto kern = win ? prefill_kernel<DT, true> : prefill_kernel<DT, false>;
-  const size_t smem = 1024 + smem_layout<DT>().total;
+  auto kern = win ? prefill_kernel<DT, true, HD> : prefill_kernel<DT, false, HD>;
+  const size_t smem = 1024 + smem_layout<DT, HD>().total;
   static bool attr_done[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -335,6 +338,16 @@ cudaError_t launch_single_t(const CUtensorMap& tq, const CUtensorMap& tk, const 
 
 cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                                   const PrefillKernelParams& p, cudaStream_t stream) {
+  if (p.d != kHeadDim) {   // other head dimensions: 16-bit types
+    const bool bf = dtype == FA_B200_BF16;
+    if (dtype != FA_B200_BF16 && dtype != FA_B200_F16) return cudaErrorInvalidValue;
+    switch (p.d) {
+      case 64: return bf ? launch_single_t<FA_B200_BF16, 64>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 64>(tq, tk, tv, p, stream);
+      case 192: return bf ? launch_single_t<FA_B200_BF16, 192>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 192>(tq, tk, tv, p, stream);
+      case 256: return bf ? launch_single_t<FA_B200_BF16, 256>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 256>(tq, tk, tv, p, stream);
+    }
+    return cudaErrorInvalidValue;
+  }
   switch (dtype) {
     case FA_B200_F16: return launch_single_t<FA_B200_F16>(tq, tk, tv, p, stream);
     case FA_B200_BF16: return launch_single_t<FA_B200_BF16>(tq, tk, tv, p, stream);

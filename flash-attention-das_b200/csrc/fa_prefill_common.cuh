@@ -43,19 +43,22 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: O in TMEM is rescaled only when the max grew by more
 
-template <int DT>
+// HD: head dimension, 128 for every element type and 64 / 192 / 256 for the 16-bit ones (one-tile kernel only).
+template <int DT, int HD = kHeadDim>
 struct TileTraits {
   static constexpr bool kFp8 = (DT == FA_B200_E4M3);
   static constexpr int kElem = kFp8 ? 1 : 2;
-  static constexpr int kTileBytes = kBlockN * kHeadDim * kElem;   // one Q, K or V tile
-  static constexpr int kHalves = kFp8 ? 1 : 2;                    // 128-byte column groups per row
-  static constexpr int kHalfBytes = kTileBytes / kHalves;
+  static constexpr int kTileBytes = kBlockN * HD * kElem;         // one Q, K or V tile
+  static constexpr int kHalves = HD * kElem / 128;                // 128-byte column groups per row
+  static constexpr int kHalfBytes = kTileBytes / kHalves;         // 128 rows x 128 bytes
   static constexpr int kUmmaK = kFp8 ? 32 : 16;
-  static constexpr int kKSteps = kHeadDim / kUmmaK;               // k-steps of Q K^T
+  static constexpr int kKSteps = HD / kUmmaK;                     // k-steps of Q K^T
   static constexpr int kPVSteps = kBlockN / kUmmaK;               // k-steps of P V
+  static constexpr int kOChunks = HD / 32;                        // 32-column pieces of an O row
   static constexpr uint32_t kFormat = kFp8 ? 0u : (DT == FA_B200_BF16 ? 1u : 0u);
   static constexpr uint32_t kIdescQK = make_idesc(kFormat, false, kBlockM, kBlockN);
-  static constexpr uint32_t kIdescPV = make_idesc(kFormat, true, kBlockM, kHeadDim);
+  static constexpr uint32_t kIdescPV = make_idesc(kFormat, true, kBlockM, HD);
+  static_assert(HD == kHeadDim || (!kFp8 && (HD == 64 || HD == 192 || HD == 256)), "head dimension");
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, int dt) {
@@ -80,11 +83,18 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
 //   TMEM operand (Q, P):    k-step ks starts 8 columns further.
 
 // S[tmem] = Q[smem] K^T[smem]
-template <int DT>
+template <int DT, int HD = kHeadDim>
 __device__ __forceinline__ void issue_qk(uint32_t q_smem, uint32_t k_smem, uint32_t s_tmem) {
-  using T = TileTraits<DT>;
+  using T = TileTraits<DT, HD>;
   const uint64_t a0 = make_smem_desc_sw128(q_smem, 16, 1024), b0 = make_smem_desc_sw128(k_smem, 16, 1024);
-  if constexpr (T::kFp8) {
+  if constexpr (HD != kHeadDim) {
+    // other head dimensions (16-bit): one instruction per k-step, four steps per 128-byte column group
+#pragma unroll
+    for (int ks = 0; ks < T::kKSteps; ++ks) {
+      const uint64_t off = static_cast<uint64_t>((ks >> 2) * (T::kHalfBytes >> 4) + (ks & 3) * 2);
+      tc_mma_ss(s_tmem, a0 + off, b0 + off, T::kIdescQK, ks > 0 ? 1u : 0u, false);
+    }
+  } else if constexpr (T::kFp8) {
     asm volatile(
         "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b;\n\t"
         "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
@@ -153,12 +163,17 @@ __device__ __forceinline__ void issue_qk_ts(uint32_t q_tmem, uint32_t k_smem, ui
 }
 // O[tmem] (+)= P[tmem] V[smem]: V is MN-major (d contiguous); the two 64-column groups of a 16-bit tile are
 // kHalfBytes apart (leading-dimension offset).  `overwrite`: the first k-step replaces O instead of accumulating.
-template <int DT>
+template <int DT, int HD = kHeadDim>
 __device__ __forceinline__ void issue_pv(uint32_t p_tmem, uint32_t v_smem, uint32_t o_tmem, bool overwrite) {
-  using T = TileTraits<DT>;
+  using T = TileTraits<DT, HD>;
   const uint64_t b0 = make_smem_desc_sw128(v_smem, T::kHalfBytes, 1024);
   const uint32_t acc0 = overwrite ? 0u : 1u;
-  if constexpr (T::kFp8) {
+  if constexpr (HD != kHeadDim) {
+    // other head dimensions (16-bit): N = HD columns per instruction, 16 key rows (2048 bytes) per k-step
+#pragma unroll
+    for (int ks = 0; ks < T::kPVSteps; ++ks)
+      tc_mma_ts(o_tmem, p_tmem + ks * 8, b0 + static_cast<uint64_t>(ks * 128), T::kIdescPV, ks > 0 ? 1u : acc0, false);
+  } else if constexpr (T::kFp8) {
     asm volatile(
         "{\n\t.reg .pred pf, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
         "setp.ne.b32 pf, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
@@ -210,10 +225,10 @@ struct RowState {
 //   lo, lim    the row sees columns lo <= c < lim of this tile (lo <= 0 and lim >= 128: all)
 //   need_mask  warp-uniform: some row of the warp has lim < 128 or lo > 0
 //   first      first tile of this row's sweep (O holds nothing yet)
-template <int DT>
+template <int DT, int HD = kHeadDim>
 __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float scale_log2, int lo, int lim, bool need_mask,
                                              bool first, RowState& st, [[maybe_unused]] uint32_t* prof = nullptr) {
-  using T = TileTraits<DT>;
+  using T = TileTraits<DT, HD>;
 #ifdef FA_B200_PHASE_TRACE
   uint32_t prof_t = prof ? clock_after(0) : 0u;
 #endif
@@ -249,7 +264,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
       st.l_sum *= alpha;
       st.m_ref = m_new;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < T::kOChunks; ++c) {
         uint32_t o[32];
         tmem_ld_32x32(t_o + c * 32, o);
         tmem_wait_ld();
@@ -329,12 +344,13 @@ __device__ __forceinline__ void store_o_chunk(uint8_t* op, int c, const uint32_t
 }
 
 // A row that sees no key at all: out = 0, lse = +inf (or the sink, the only term of its sum).
+template <int HD = kHeadDim>
 __device__ __forceinline__ void store_empty_row(const PrefillKernelParams& p, int coord_b, int bidb, int head, int64_t grow,
                                                 int row_in_seq) {
   uint8_t* op = out_row_ptr(p, coord_b, grow, head);
   const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) reinterpret_cast<uint4*>(op)[i] = z;
+  for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4*>(op)[i] = z;
   if (p.lse) p.lse[lse_index(p, bidb, head, grow, row_in_seq)] = p.s_aux ? load_sink_log2(p.s_aux, p.s_aux_dtype, head) * kLn2 : INFINITY;
 }
 

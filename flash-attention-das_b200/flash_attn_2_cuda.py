@@ -149,6 +149,11 @@ _lib.fa_b200_scatter_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_i64, _c_i64, _c_i6
 _lib.fa_b200_scatter_rows.restype = ctypes.c_int
 _lib.fa_b200_block_map_to_offset.argtypes = [_c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_vp]
 _lib.fa_b200_block_map_to_offset.restype = ctypes.c_int
+_lib.fa_b200_kv_cache_attention.argtypes = ([_c_vp, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp] + [_c_i32] * 9 +
+                                            [_c_vp, ctypes.c_size_t, _c_vp])
+_lib.fa_b200_kv_cache_attention.restype = ctypes.c_int
+_lib.fa_b200_kv_cache_attention_workspace_bytes.argtypes = [_c_i32] * 6
+_lib.fa_b200_kv_cache_attention_workspace_bytes.restype = ctypes.c_size_t
 _lib.fa_b200_status_string.argtypes = [ctypes.c_int]
 _lib.fa_b200_status_string.restype = ctypes.c_char_p
 _lib.fa_b200_last_cuda_error.restype = ctypes.c_char_p
@@ -225,8 +230,8 @@ def _check_qkv(q, k, v, v_transposed=False, allow_fp8_kv=False):
     _require(q.is_cuda and k.is_cuda and v.is_cuda, "Input tensor must be on CUDA device")
     for t in (q, k) if v_transposed else (q, k, v):
         _require(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
-    _require(q.shape[-1] == 128 and v.shape[-1] == 128,
-             "this build implements head dimension 128 only (the hot path named by the B200 port)")
+    _require(q.shape[-1] in (64, 128, 192, 256) and v.shape[-1] == q.shape[-1] and k.shape[-1] == q.shape[-1],
+             "head dimension must be 128 (or 64, 192, 256 with fp16 / bf16 tensors in the plain layouts)")
 
 
 def _descale(params, name, t: Optional[torch.Tensor], batch: int, h_k: int):
@@ -600,6 +605,42 @@ def paged_attention(out, query, key_cache, value_cache, scale, block_tables, seq
     o4 = out if out.dim() == 4 else out.unsqueeze(1)
     fwd_kvcache(q4, kc, vc, None, None, seq_lens, None, None, None, None, block_tables, alibi_slopes, o4, float(scale),
                 is_causal, window_size_left, window_size_right, 0.0, True, 0, s_aux_, q_scale, k_scale, v_scale, max_seq_len)
+
+
+def kv_cache_attention(q, seq_offsets, max_seqlen_q, max_seqlen_k, k_caches, v_caches, page_tables, cache_lens, out,
+                       num_query, num_tokens, num_q_head, num_kv_head, num_dim, num_pages, page_size, dtype="bf16",
+                       layout=1):
+    """The reference's raw-pointer entry (extern "C" kv_cache_attention, csrc/flash_attn_cutlass/flash_api.cpp:2589-2624)
+    with the same argument list; the tensors stand for its device pointers.  One token per request
+    (num_query == num_tokens) decodes over all keys; otherwise the requests' tokens attend causally to their pages.
+    layout 1: caches (num_pages, num_kv_head, page_size, num_dim); 2: (num_pages, page_size, num_kv_head, num_dim);
+    0 (one token per request only): V (num_pages, num_kv_head, num_dim, page_size).  Writes ``out``."""
+    for t in (q, k_caches, v_caches, page_tables, cache_lens, out):
+        _require(t.is_cuda and t.is_contiguous(), "kv_cache_attention takes contiguous CUDA tensors")
+    _require(page_tables.dtype == torch.int32 and cache_lens.dtype == torch.int32, "page_tables and cache_lens must be int32")
+    offs = 0
+    if num_query != num_tokens:
+        _require(seq_offsets is not None and seq_offsets.dtype == torch.int32 and seq_offsets.is_cuda,
+                 "seq_offsets must be an int32 CUDA tensor")
+        offs = seq_offsets.data_ptr()
+    code = F16 if dtype == "fp16" else BF16      # the reference: "fp16", anything else is bf16
+    _require(q.dtype == (torch.float16 if code == F16 else torch.bfloat16), "q does not have the dtype named")
+    with torch.cuda.device(q.device):
+        nbytes = int(_lib.fa_b200_kv_cache_attention_workspace_bytes(num_query, num_q_head, num_kv_head, num_dim,
+                                                                     page_size, max_seqlen_k)) if num_query == num_tokens else 0
+        ws = _workspace(q.device, nbytes)
+        _check(_lib.fa_b200_kv_cache_attention(
+            q.data_ptr(), offs, max_seqlen_q, max_seqlen_k, k_caches.data_ptr(), v_caches.data_ptr(),
+            page_tables.data_ptr(), cache_lens.data_ptr(), out.data_ptr(), num_query, num_tokens, num_q_head,
+            num_kv_head, num_dim, num_pages, page_size, code, layout, ws.data_ptr() if ws is not None else None,
+            nbytes, _stream(q)), "kv_cache_attention")
+
+
+def cal_paged_attention(q, seq_offsets, max_seqlen_q, max_seqlen_k, k_caches, v_caches, page_tables, cache_lens, out,
+                        num_query, num_tokens, num_q_head, num_kv_head, num_dim, num_pages, page_size, dtype="bf16"):
+    """kv_cache_attention with layout 1 (flash_api.cpp:2625-2631)."""
+    kv_cache_attention(q, seq_offsets, max_seqlen_q, max_seqlen_k, k_caches, v_caches, page_tables, cache_lens, out,
+                       num_query, num_tokens, num_q_head, num_kv_head, num_dim, num_pages, page_size, dtype, 1)
 
 
 def kv_append(q, kcache, vcache, k_new, v_new, seqlens_k, block_table, rotary_cos=None, rotary_sin=None,

@@ -35,7 +35,7 @@ enum {
   FA_B200_OK = 0,
   FA_B200_ERR_NULL = 1,          /* a required pointer is null */
   FA_B200_ERR_DTYPE = 2,         /* unsupported element type combination */
-  FA_B200_ERR_HEADDIM = 3,       /* head dimension other than 128 */
+  FA_B200_ERR_HEADDIM = 3,       /* head dimension not 128 (64, 192, 256: fp16 / bf16 in the plain layouts only) */
   FA_B200_ERR_HEADS = 4,         /* h not a multiple of h_k, or group too large for the decode tile */
   FA_B200_ERR_STRIDE = 5,        /* last dim not contiguous / stride not 16-byte aligned */
   FA_B200_ERR_SHAPE = 6,         /* negative or inconsistent sizes */
@@ -265,6 +265,41 @@ typedef struct fa_b200_combine_params {
 } fa_b200_combine_params;
 
 FA_B200_API int fa_b200_combine(const fa_b200_combine_params* p, void* stream);
+
+/*
+ * Raw-pointer paged attention over a whole batch of requests, with the argument list of the reference's
+ * extern "C" kv_cache_attention(q, seq_offsets, max_seqlen_q, max_seqlen_k, k_caches, v_caches, page_tables, cache_lens,
+ * out, num_query, num_tokens, num_q_head, num_kv_head, num_dim, num_pages, page_size, dtype, layout)
+ * (csrc/flash_attn_cutlass/flash_api.cpp:2589-2624; cal_paged_attention, :2625-2631, is the same call with layout 1).
+ * Differences forced by a C ABI that never allocates: the element type is an enum (the reference takes a std::string,
+ * "fp16" or anything else for bf16), and the scratch memory and the stream are arguments.
+ *
+ *   q, out        (num_tokens, num_q_head, num_dim), packed
+ *   seq_offsets   int32 (num_query + 1): first token of each request in q
+ *   k_caches / v_caches   layout 1: (num_pages, num_kv_head, page_size, num_dim)
+ *                         layout 2: (num_pages, page_size, num_kv_head, num_dim)
+ *                         layout 0: K as layout 1, V (num_pages, num_kv_head, num_dim, page_size); one token per request only
+ *   page_tables   int32 (num_query, (max_seqlen_k - 1) / page_size + 1)
+ *   cache_lens    int32 (num_query): keys of each request, the new tokens included
+ *
+ * num_query == num_tokens: one query token per request, every key visible (the reference's paged_attention branch).
+ * Otherwise: each request's tokens are the last ones of its sequence and attend causally (bottom-right aligned) to its
+ * pages (the reference's hg_prefix_prefill_varlen_fwd branch; layouts 1 and 2).  softmax scale = 1 / sqrt(num_dim).
+ * workspace: fa_b200_kv_cache_attention_workspace_bytes(num_query, num_q_head, num_kv_head, num_dim, page_size,
+ * max_seqlen_k)
+ * bytes, 16-byte aligned
+ * (only the one-token branch uses it).
+ */
+FA_B200_API int fa_b200_kv_cache_attention(const void* q, const int32_t* seq_offsets, int32_t max_seqlen_q,
+                                           int32_t max_seqlen_k, const void* k_caches, const void* v_caches,
+                                           const int32_t* page_tables, const int32_t* cache_lens, void* out,
+                                           int32_t num_query, int32_t num_tokens, int32_t num_q_head,
+                                           int32_t num_kv_head, int32_t num_dim, int32_t num_pages, int32_t page_size,
+                                           int32_t dtype, int32_t layout, void* workspace, size_t workspace_bytes,
+                                           void* stream);
+FA_B200_API size_t fa_b200_kv_cache_attention_workspace_bytes(int32_t num_query, int32_t num_q_head,
+                                                              int32_t num_kv_head, int32_t num_dim, int32_t page_size,
+                                                              int32_t max_seqlen_k);
 
 /*
  * KV-cache append with optional rotary embedding, the first half of a decode call that is handed new keys and

@@ -58,8 +58,10 @@ def test_host_validation_needs_no_gpu(binding):
     lib = binding.lib()
     assert lib.fa_b200_fwd(None, None) == 1
     p = binding.FwdParams()
-    p.d = 64
+    p.d = 96
     assert lib.fa_b200_fwd(ctypes.byref(p), None) == 3          # head dim
+    p.d, p.dtype = 64, 2
+    assert lib.fa_b200_fwd(ctypes.byref(p), None) == 3          # 64 / 192 / 256 are for the 16-bit types
     p.d, p.dtype, p.out_dtype = 128, 7, 1
     assert lib.fa_b200_fwd(ctypes.byref(p), None) == 2          # dtype
     p.dtype, p.b, p.h, p.h_k, p.seqlen_q, p.seqlen_k = 1, 1, 6, 4, 8, 8
@@ -102,3 +104,27 @@ def test_partition_heuristic_and_workspace(binding):
     d.dtype = 1
     d.partition_tokens = 100               # not a multiple of the tile
     assert lib.fa_b200_decode_partition_tokens(ctypes.byref(d)) == 0
+
+
+def test_raw_pointer_entry_validates_before_touching_anything(binding):
+    """fa_b200_kv_cache_attention (the reference's extern "C" kv_cache_attention argument list): argument errors come back
+    as status codes without a GPU, and its workspace query agrees with the decode call's."""
+    lib = binding.lib()
+
+    def call(dtype=1, layout=1, num_query=4, num_tokens=4, hq=8, hk=2, d=128, pages=16, page=64, max_k=512):
+        return lib.fa_b200_kv_cache_attention(None, None, 1, max_k, None, None, None, None, None, num_query, num_tokens, hq,
+                                              hk, d, pages, page, dtype, layout, None, 0, None)
+    assert call(dtype=2) == 2            # e4m3 is not taken by this entry
+    assert call(layout=3) == 9
+    assert call(d=96) == 3
+    assert call(num_tokens=3) == 6       # fewer tokens than requests
+    assert call(num_query=0, num_tokens=0) == 0
+    assert call(hq=6, hk=4) == 4         # reaches the decode call's own checks
+    assert call() == 1                   # null pointers
+    assert call(num_tokens=9, layout=0) == 9   # several tokens per request over a transposed V pool
+    assert call(num_tokens=9) == 1       # seq_offsets missing
+    d = binding.DecodeParams()
+    d.d, d.dtype, d.out_dtype = 128, 1, 1
+    d.b, d.h, d.h_k, d.page_size, d.max_blocks_per_seq, d.max_seqlen_k = 64, 32, 8, 256, 128, 32768
+    assert (lib.fa_b200_kv_cache_attention_workspace_bytes(64, 32, 8, 128, 256, 32768) ==
+            lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) > 0)

@@ -188,8 +188,8 @@ def test_decode_rejects_what_the_path_does_not_do(fa):
     with pytest.raises(RuntimeError):
         flash_attn.flash_attn_with_kvcache(q, kc.cuda(), vc.cuda(), cache_seqlens=sl.cuda(), block_table=None)
     with pytest.raises(RuntimeError):
-        flash_attn.flash_attn_with_kvcache(q[..., :64].contiguous(), kc.cuda()[..., :64].contiguous(),
-                                           vc.cuda()[..., :64].contiguous(), cache_seqlens=sl.cuda(), block_table=bt.cuda())
+        flash_attn.flash_attn_with_kvcache(q[..., :96].contiguous(), kc.cuda()[..., :96].contiguous(),
+                                           vc.cuda()[..., :96].contiguous(), cache_seqlens=sl.cuda(), block_table=bt.cuda())
 
 
 def test_paged_attention_binding_layouts(fa):
@@ -347,3 +347,58 @@ def test_fp8_kv_cache_under_16bit_queries(fa, qdtype, sq):
                                                      layout=1)
         torch.cuda.synchronize()
         assert_close_to_oracle(o2.cpu(), ref32, ref_pt, mult=3.0, eps=2 ** -8, what="fp8 kv cache, vllm entry")
+
+
+@pytest.mark.gpu
+def test_raw_pointer_entry_matches_the_tensor_entries(fa):
+    """kv_cache_attention / cal_paged_attention (the reference's extern "C" raw-pointer entry, flash_api.cpp:2589-2631):
+    one token per request gives the bits of flash_attn_with_kvcache for the three layouts; several tokens per request give
+    the bits of the paged varlen entry (causal, bottom-right aligned) and agree with the oracle."""
+    flash_attn, cuda = fa
+    g = gen(123)
+    lens, h, hk, page = [1, 200, 64, 513, 300], 8, 2, 64
+    kc, vc, bt, sl = make_paged(g, lens, hk, page, torch.bfloat16)
+    n, pool = len(lens), kc.shape[0]
+    kc_d, vc_d, bt_d, sl_d = kc.cuda(), vc.cuda(), bt.cuda().contiguous(), sl.cuda()
+    assert bt.shape[1] == (max(lens) - 1) // page + 1
+    pools = {2: (kc_d, vc_d),
+             1: (kc_d.permute(0, 2, 1, 3).contiguous(), vc_d.permute(0, 2, 1, 3).contiguous()),
+             0: (kc_d.permute(0, 2, 1, 3).contiguous(), vc_d.permute(0, 2, 3, 1).contiguous())}
+    # one token per request
+    q = randn(g, n, h, 128).cuda()
+    want = flash_attn.flash_attn_with_kvcache(q.unsqueeze(1), kc_d, vc_d, cache_seqlens=sl_d, block_table=bt_d).squeeze(1)
+    for layout, (kp, vp) in pools.items():
+        out = torch.full_like(q, float("nan"))
+        cuda.kv_cache_attention(q, None, 1, max(lens), kp, vp, bt_d, sl_d, out, n, n, h, hk, 128, pool, page, "bf16", layout)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        assert torch.equal(out, want), layout
+    out = torch.full_like(q, float("nan"))
+    cuda.cal_paged_attention(q, None, 1, max(lens), pools[1][0], pools[1][1], bt_d, sl_d, out, n, n, h, hk, 128, pool, page)
+    assert torch.equal(out, want)
+    # several tokens per request: the last q_lens[i] positions of each sequence
+    q_lens = [1, 37, 64, 130, 300]
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    total = int(cu[-1])
+    qv = randn(g, total, h, 128)
+    qv_d, cu_d = qv.cuda(), cu.cuda()
+    want = flash_attn.flash_attn_varlen_func(qv_d, kc_d, vc_d, cu_d, None, max(q_lens), max(lens), causal=True,
+                                             block_table=bt_d, seqused_k=sl_d)
+    for layout in (1, 2):
+        out = torch.full_like(qv_d, float("nan"))
+        cuda.kv_cache_attention(qv_d, cu_d, max(q_lens), max(lens), pools[layout][0], pools[layout][1], bt_d, sl_d, out, n,
+                                total, h, hk, 128, pool, page, "bf16", layout)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        assert torch.equal(out, want), layout
+    kcc, vcc = clean_nan(kc), clean_nan(vc)
+    for i, (lq, lk) in enumerate(zip(q_lens, lens)):
+        q_i = qv[int(cu[i]):int(cu[i + 1])][None]
+        k_i, v_i = O.gather_paged_kv(kcc, bt[i], lk)[None], O.gather_paged_kv(vcc, bt[i], lk)[None]
+        ref32, _ = O.attention_ref(q_i, k_i, v_i, causal=True, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(q_i, k_i, v_i, causal=True, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out[int(cu[i]):int(cu[i + 1])].cpu()[None], ref32, ref_pt, mult=2.0, eps=2 ** -8,
+                               what=f"request {i}")
+    with pytest.raises(RuntimeError):    # several tokens per request over a transposed V pool: not built
+        cuda.kv_cache_attention(qv_d, cu_d, max(q_lens), max(lens), pools[0][0], pools[0][1], bt_d, sl_d, out, n, total, h,
+                                hk, 128, pool, page, "bf16", 0)

@@ -246,7 +246,7 @@ def test_prefill_rejects_what_the_path_does_not_do(fa):
     with pytest.raises(NotImplementedError):
         flash_attn.flash_attn_func(q, q, q, softcap=30.0)
     with pytest.raises(RuntimeError):
-        flash_attn.flash_attn_func(q[..., :64], q[..., :64], q[..., :64])
+        flash_attn.flash_attn_func(q[..., :96], q[..., :96], q[..., :96])
     with pytest.raises(RuntimeError):
         flash_attn.flash_attn_func(q, q[:, :, :1].expand(1, 16, 3, 128), q)
 
