@@ -586,6 +586,8 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!p) return FA_B200_ERR_NULL;
   if (!head_dim_ok(p->d, p->dtype == FA_B200_E4M3)) return FA_B200_ERR_HEADDIM;
+  const int dv = p->d_v > 0 ? p->d_v : p->d;
+  if (dv != p->d && !(p->d == 192 && dv == 128)) return FA_B200_ERR_HEADDIM;
   if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) return FA_B200_ERR_DTYPE;
   if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
   if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
@@ -636,20 +638,20 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
                    p->k_batch_stride, box_rows, p->d);
     if (st != FA_B200_OK) return st;
     st = make_tmap(&tv, p->v, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
-                   p->v_batch_stride, box_rows, p->d);
+                   p->v_batch_stride, box_rows, dv);
   } else {
     st = make_tmap(&tk, p->k, p->dtype, p->h_k, k_rows, nb, p->k_head_stride, p->k_row_stride,
                    varlen ? p->k_row_stride * (k_rows > 0 ? k_rows : 1) : p->k_batch_stride, 128, p->d);
     if (st != FA_B200_OK) return st;
     st = make_tmap(&tv, p->v, p->dtype, p->h_k, k_rows, nb, p->v_head_stride, p->v_row_stride,
-                   varlen ? p->v_row_stride * (k_rows > 0 ? k_rows : 1) : p->v_batch_stride, 128, p->d);
+                   varlen ? p->v_row_stride * (k_rows > 0 ? k_rows : 1) : p->v_batch_stride, 128, dv);
   }
   if (st != FA_B200_OK) return st;
 
   // output map for whole-tile stores (strides and base are 16-byte aligned by the checks above)
   CUtensorMap to;
   st = make_tmap(&to, p->out, p->out_dtype, p->h, q_rows, nb, p->o_head_stride, p->o_row_stride,
-                 varlen ? p->o_row_stride * (q_rows > 0 ? q_rows : 1) : p->o_batch_stride, 128, p->d);
+                 varlen ? p->o_row_stride * (q_rows > 0 ? q_rows : 1) : p->o_batch_stride, 128, dv);
   if (st != FA_B200_OK) return st;
 
   PrefillKernelParams k{};
@@ -657,6 +659,7 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   if (!k.status) return cuda_fail("status word", cudaGetLastError());
   k.o_tma = 1;
   k.d = p->d;
+  k.d_v = dv;
   k.s_aux = p->s_aux;
   k.s_aux_dtype = p->s_aux_dtype;
   k.out = p->out;

@@ -105,6 +105,7 @@ struct PrefillKernelParams {
   int32_t s_aux_dtype;
   int* work_counter;         // persistent kernels: zeroed before the launch; CTAs claim work items past their first from it
   int32_t d;              // head dimension: 128, or 64 / 192 / 256 (16-bit types, one-tile kernel)
+  int32_t d_v;            // head dimension of v and out (= d, or 128 with d = 192)
 };
 // One 128-row query tile per CTA, two CTAs per SM: block-sparse lists and odd GQA groups.
 cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,

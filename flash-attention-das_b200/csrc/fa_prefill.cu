@@ -31,6 +31,7 @@ struct SmemLayoutInfo {
   int q_off, ring_off, bar_off, tiles_off, misc_off, total;
 };
 
+// Ring slots are sized for a K tile; a V tile of a smaller head dimension uses the head of its slot.
 template <int DT, int HD>
 __host__ __device__ constexpr SmemLayoutInfo smem_layout() {
   using T = TileTraits<DT, HD>;
@@ -46,14 +47,17 @@ __host__ __device__ constexpr SmemLayoutInfo smem_layout() {
 }
 
 // kLeftWindow: the launch has a left sliding-window bound (kept out of the common build of the softmax loop).
-// HD: head dimension (128; 64, 192, 256 for the 16-bit types — one CTA per SM above 128: shared memory and TMEM).
-template <int DT, bool kLeftWindow, int HD>
+// HD: head dimension of q and k (128; 64, 192, 256 for the 16-bit types — one CTA per SM above 128: shared memory and
+// TMEM).  HDV: head dimension of v and out (= HD, or 128 with HD = 192).
+template <int DT, bool kLeftWindow, int HD, int HDV = HD>
 __global__ void __launch_bounds__(kThreads, HD > 128 ? 1 : 2)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const PrefillKernelParams p) {
   using T = TileTraits<DT, HD>;
+  using TV = TileTraits<DT, HDV>;
+  static_assert(HDV <= HD, "a V tile must fit a ring slot");
   constexpr SmemLayoutInfo L = smem_layout<DT, HD>();
-  constexpr int kTmemCols = tmem_cols(HD);
+  constexpr int kTmemCols = tmem_cols(HDV);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bar_off);
@@ -140,7 +144,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     // no visible key for any row of this tile
     if (warp < 4) {
       const int row = (warp & 3) * 32 + lane;
-      if (row < rows_valid) store_empty_row<HD>(p, coord_b, bidb, head, static_cast<int64_t>(q_row0) + m0 + row, m0 + row);
+      if (row < rows_valid) store_empty_row<HDV>(p, coord_b, bidb, head, static_cast<int64_t>(q_row0) + m0 + row, m0 + row);
     }
     return;
   }
@@ -178,22 +182,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           if (!mbar_wait(smem_u32(&kv_empty[slot]), ph ^ 1u, wctx)) { ok = false; break; }
           const uint32_t bar = smem_u32(&kv_full[slot]);
           const CUtensorMap* tm = kv ? &tmap_v : &tmap_k;
+          const int halves = kv ? TV::kHalves : T::kHalves;   // 128-byte column groups of this tile
           if (!p.paged) {
-            mbar_expect_tx(bar, T::kTileBytes);
-#pragma unroll
-            for (int hf = 0; hf < T::kHalves; ++hf)
+            mbar_expect_tx(bar, kv ? TV::kTileBytes : T::kTileBytes);
+            for (int hf = 0; hf < halves; ++hf)
               tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, hk, k_row0 + start, coord_b);
           } else {
             // the tile's 128 keys come from one or more pages: one box of box_rows rows per page piece; boxes that
             // start past the end of the sequence are not fetched (their block_table slots are not valid)
             const int nbox = min(kBlockN / p.box_rows, (sk - start + p.box_rows - 1) / p.box_rows);
-            mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * p.box_rows * 128u * T::kHalves);
+            mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * p.box_rows * 128u * halves);
             const int32_t* bt = p.block_table + static_cast<int64_t>(bidb) * p.bt_stride;
             for (int i = 0; i < nbox; ++i) {
               const int tok = start + i * p.box_rows;
               const int page = bt[tok / p.page_size], row = tok % p.page_size;
-#pragma unroll
-              for (int hf = 0; hf < T::kHalves; ++hf)
+              for (int hf = 0; hf < halves; ++hf)
                 tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes + i * p.box_rows * 128, tm, bar, hf * 64, hk,
                             row, page);
             }
@@ -218,7 +221,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!mbar_wait(smem_u32(&kv_full[v_slot]), (v_item / kSlots) & 1, wctx)) { ok = false; break; }
         if (!mbar_wait(smem_u32(p_full), j & 1, wctx)) { ok = false; break; }
         tc_fence_after();
-        issue_pv<DT, HD>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
+        issue_pv<DT, HDV>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
         tc_commit(smem_u32(&kv_empty[v_slot]));
         if (j + 1 < n_tiles) {
           if (!mbar_wait(smem_u32(&kv_full[k_slot]), (k_item / kSlots) & 1, wctx)) { ok = false; break; }
@@ -263,7 +266,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (p.sparse) { const int v = sm_tiles[j]; start = v & 0x7fffffff; half_tile = (v < 0); }
       int lim = row_limit - start;
       if (half_tile) lim = min(lim, 64);
-      softmax_tile<DT, HD>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, lim,
+      softmax_tile<DT, HDV>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, lim,
                        half_tile || start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st);
       if (p.paged && start + kBlockN > sk) {
         // Last tile of a paged sequence: key rows past the end were not fetched, or hold whatever the page holds
@@ -274,7 +277,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (row >= sk - start) {
           const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
 #pragma unroll
-          for (int hf = 0; hf < T::kHalves; ++hf)
+          for (int hf = 0; hf < TV::kHalves; ++hf)
 #pragma unroll
             for (int c16 = 0; c16 < 8; ++c16)
               asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(vrow + hf * T::kHalfBytes + c16 * 16), "r"(0u) : "memory");
@@ -295,7 +298,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const int64_t grow = static_cast<int64_t>(q_row0) + row_in_seq;
       uint8_t* op = out_row_ptr(p, coord_b, grow, head);
 #pragma unroll
-      for (int c = 0; c < T::kOChunks; ++c) {
+      for (int c = 0; c < TV::kOChunks; ++c) {
         uint32_t o[32];
         tmem_ld_32x32(t_o + c * 32, o);
         tmem_wait_ld();
@@ -315,11 +318,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   }
 }
 
-template <int DT, int HD = kHeadDim>
+template <int DT, int HD = kHeadDim, int HDV = HD>
 cudaError_t launch_single_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const PrefillKernelParams& p, cudaStream_t stream) {
   const bool win = p.window_left >= 0;
-  auto kern = win ? prefill_kernel<DT, true, HD> : prefill_kernel<DT, false, HD>;
+  auto kern = win ? prefill_kernel<DT, true, HD, HDV> : prefill_kernel<DT, false, HD, HDV>;
   const size_t smem = 1024 + smem_layout<DT, HD>().total;
   static bool attr_done[2][64] = {};
   int dev = 0;
@@ -343,7 +346,10 @@ cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tq, const CUtens
     if (dtype != FA_B200_BF16 && dtype != FA_B200_F16) return cudaErrorInvalidValue;
     switch (p.d) {
       case 64: return bf ? launch_single_t<FA_B200_BF16, 64>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 64>(tq, tk, tv, p, stream);
-      case 192: return bf ? launch_single_t<FA_B200_BF16, 192>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 192>(tq, tk, tv, p, stream);
+      case 192:
+        if (p.d_v == 128)
+          return bf ? launch_single_t<FA_B200_BF16, 192, 128>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 192, 128>(tq, tk, tv, p, stream);
+        return bf ? launch_single_t<FA_B200_BF16, 192>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 192>(tq, tk, tv, p, stream);
       case 256: return bf ? launch_single_t<FA_B200_BF16, 256>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 256>(tq, tk, tv, p, stream);
     }
     return cudaErrorInvalidValue;

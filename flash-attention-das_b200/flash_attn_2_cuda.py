@@ -57,7 +57,7 @@ class FwdParams(ctypes.Structure):
         ("page_size", _c_i32), ("num_blocks", _c_i32),
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
         ("has_window", _c_i32), ("window_left", _c_i32), ("window_right", _c_i32),
-        ("column_count", _c_vp),
+        ("column_count", _c_vp), ("d_v", _c_i32),
     ]
 
 
@@ -222,7 +222,7 @@ def _is_fp8_kv(q, k) -> bool:
     return q.dtype in (torch.float16, torch.bfloat16) and k.dtype == torch.float8_e4m3fn
 
 
-def _check_qkv(q, k, v, v_transposed=False, allow_fp8_kv=False):
+def _check_qkv(q, k, v, v_transposed=False, allow_fp8_kv=False, allow_dv=False):
     _require(q.dtype in _DT, "FlashAttention only support fp16, bf16 and fp8 e4m3 data type")
     if not (allow_fp8_kv and _is_fp8_kv(q, k)):
         _require(k.dtype == q.dtype, "query and key must have the same dtype")
@@ -230,8 +230,10 @@ def _check_qkv(q, k, v, v_transposed=False, allow_fp8_kv=False):
     _require(q.is_cuda and k.is_cuda and v.is_cuda, "Input tensor must be on CUDA device")
     for t in (q, k) if v_transposed else (q, k, v):
         _require(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
-    _require(q.shape[-1] in (64, 128, 192, 256) and v.shape[-1] == q.shape[-1] and k.shape[-1] == q.shape[-1],
-             "head dimension must be 128 (or 64, 192, 256 with fp16 / bf16 tensors in the plain layouts)")
+    _require(q.shape[-1] in (64, 128, 192, 256) and k.shape[-1] == q.shape[-1] and
+             (v.shape[-1] == q.shape[-1] or (allow_dv and q.shape[-1] == 192 and v.shape[-1] == 128)),
+             "head dimension must be 128 (or 64, 192, 256, or 192 with 128 for v, with fp16 / bf16 tensors in the plain "
+             "layouts)")
 
 
 def _descale(params, name, t: Optional[torch.Tensor], batch: int, h_k: int):
@@ -259,7 +261,7 @@ def _set_paged(p, kcache, vcache, block_table, seqused_k, batch):
     _require(seqused_k is not None, "seqused_k / cache_seqlens is required with block_table")
     _require(seqused_k.dtype == torch.int32 and seqused_k.is_contiguous() and seqused_k.numel() == batch,
              "seqused_k must be a contiguous int32 tensor of shape (batch,)")
-    _require(kcache.dim() == 4 and kcache.shape == vcache.shape, "paged k/v must be (num_blocks, page_size, nheads_k, d)")
+    _require(kcache.dim() == 4 and kcache.shape[:3] == vcache.shape[:3], "paged k/v must be (num_blocks, page_size, nheads_k, d)")
     p.k, p.v = kcache.data_ptr(), vcache.data_ptr()
     p.k_batch_stride, p.k_row_stride, p.k_head_stride = kcache.stride(0), kcache.stride(1), kcache.stride(2)
     p.v_batch_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
@@ -302,7 +304,7 @@ def _out_dtype(q, out_):
 # ------------------------------------------------------------------------------------------------
 def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, window_size_left, window_size_right,
         softcap, return_softmax, gen_, is_bhsd=False, s_aux_=None, skip_softmax_threshold_scale_factor=0.0):
-    _check_qkv(q, k, v)
+    _check_qkv(q, k, v, allow_dv=True)
     _unsupported(is_bhsd, "bhsd layout")
     _unsupported(alibi_slopes_ is not None, "alibi")
     _unsupported(p_dropout != 0.0, "dropout")
@@ -310,10 +312,10 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     _unsupported(return_softmax, "return_softmax")
     _unsupported(skip_softmax_threshold_scale_factor != 0.0, "skip-softmax")
     b, sq, h, d = q.shape
-    sk, h_k = k.shape[1], k.shape[2]
+    sk, h_k, dv = k.shape[1], k.shape[2], v.shape[3]
     _require(b > 0, "batch size must be positive")
     _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
-    _require(tuple(k.shape) == (b, sk, h_k, d) and tuple(v.shape) == (b, sk, h_k, d), "k/v shape mismatch")
+    _require(tuple(k.shape) == (b, sk, h_k, d) and tuple(v.shape) == (b, sk, h_k, dv), "k/v shape mismatch")
     # window normalisation as in mha_fwd (flash_api.cpp:1055-1060)
     if window_size_left >= sk:
         window_size_left = -1
@@ -328,11 +330,11 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
         q = q.clone()
     odt = _out_dtype(q, out_)
     if out_ is not None:
-        _require(tuple(out_.shape) == (b, sq, h, d), "out has wrong shape")
+        _require(tuple(out_.shape) == (b, sq, h, dv), "out has wrong shape")
         _require(out_.stride(-1) == 1, "Output tensor must have contiguous last dimension")
         out = out_
     else:
-        out = torch.empty((b, sq, h, d), dtype=odt, device=q.device)
+        out = torch.empty((b, sq, h, dv), dtype=odt, device=q.device)
     lse = torch.empty((b, h, sq), dtype=torch.float32, device=q.device)
     p = FwdParams()
     p.q, p.k, p.v, p.out, p.softmax_lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
@@ -340,7 +342,7 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     p.k_batch_stride, p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1), k.stride(2)
     p.v_batch_stride, p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1), v.stride(2)
     p.o_batch_stride, p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1), out.stride(2)
-    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = b, sq, sk, h, h_k, d
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d, p.d_v = b, sq, sk, h, h_k, d, dv
     p.softmax_scale = softmax_scale
     p.is_causal = 1 if causal else 0
     p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
@@ -362,7 +364,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
                max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
                window_size_right, softcap, return_softmax, q_descale_=None, k_descale_=None, v_descale_=None,
                gen_=None, s_aux_=None):
-    _check_qkv(q, k, v)
+    _check_qkv(q, k, v, allow_dv=True)
     paged = block_table_ is not None
     _unsupported(seqused_k is not None and not paged, "seqused_k without block_table")
     _unsupported(leftpad_k_ is not None, "leftpad_k")
@@ -375,6 +377,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
         _require(t.is_cuda, f"{name} must be on CUDA device")
         _require(t.is_contiguous(), f"{name} must be contiguous")
     total_q, h, d = q.shape
+    dv = v.shape[-1]
     total_k, h_k = (0, k.shape[2]) if paged else (k.shape[0], k.shape[1])
     b = cu_seqlens_q.numel() - 1
     _require(b > 0, "batch size must be positive")
@@ -393,11 +396,11 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
         q = q.clone()
     odt = _out_dtype(q, out_)
     if out_ is not None:
-        _require(tuple(out_.shape) == (total_q, h, d), "out has wrong shape")
+        _require(tuple(out_.shape) == (total_q, h, dv), "out has wrong shape")
         _require(out_.stride(-1) == 1, "Output tensor must have contiguous last dimension")
         out = out_
     else:
-        out = torch.empty((total_q, h, d), dtype=odt, device=q.device)
+        out = torch.empty((total_q, h, dv), dtype=odt, device=q.device)
     lse = torch.empty((h, total_q), dtype=torch.float32, device=q.device)
     if zero_tensors:
         out.zero_()
@@ -406,7 +409,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     p.q, p.k, p.v, p.out, p.softmax_lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
     p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1)
-    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = b, max_seqlen_q, max_seqlen_k, h, h_k, d
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d, p.d_v = b, max_seqlen_q, max_seqlen_k, h, h_k, d, dv
     p.total_q, p.total_k = total_q, total_k
     p.cu_seqlens_q = cu_seqlens_q.data_ptr()
     if paged:

@@ -121,6 +121,10 @@ typedef struct fa_b200_fwd_params {
    * is not zero is reported by fa_b200_device_status() as FA_B200_ERR_DEVICE_UNSUPPORTED (checked on the device: no host
    * synchronisation).  NULL = not checked. */
   const int32_t* column_count;
+  /* Head dimension of v and out when it differs from d (q and k): the pair d = 192, d_v = 128 (fp16 / bf16), the
+   * multi-head latent attention prefill shape the reference takes in its bshd paths (flash_attn_interface.py:2241-2242).
+   * 0 = same as d. */
+  int32_t d_v;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch

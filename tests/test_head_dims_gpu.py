@@ -179,3 +179,78 @@ def test_other_head_dims_are_for_16bit_plain_layouts(fa):
     q = torch.zeros(1, 128, 2, 96, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
         flash_attn.flash_attn_func(q, q, q)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_qk_192_v_128(fa, dtype):
+    """q / k with head dimension 192 and v / out with 128 (the multi-head latent attention prefill shape): fixed length,
+    packed varlen and paged K/V."""
+    flash_attn, cuda = fa
+    g = gen(192128)
+    h, h_k = 8, 2
+    q, k, v = randn(g, 2, 300, h, 192, dtype=dtype), randn(g, 2, 450, h_k, 192, dtype=dtype), randn(g, 2, 450, h_k, 128, dtype=dtype)
+    out, lse, _ = flash_attn.flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=True, return_attn_probs=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0 and out.shape == (2, 300, h, 128)
+    ref32, ref_lse = O.attention_ref(q, k, v, causal=True, out_dtype=torch.float32)
+    ref_pt, _ = O.attention_ref(q, k, v, causal=True, upcast=False, reorder_ops=True)
+    assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what="192/128 fixed")
+    _check_lse(lse.cpu(), ref_lse)
+    lens = [1, 127, 129, 700, 33]
+    total = sum(lens)
+    q, k, v = randn(g, total, h, 192, dtype=dtype), randn(g, total, h_k, 192, dtype=dtype), randn(g, total, h_k, 128, dtype=dtype)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    out, lse = flash_attn.flash_attn_varlen_func(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens),
+                                                 causal=True, return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0 and out.shape == (total, h, 128)
+    ref32, ref_lse = O.attention_varlen_ref(q, k, v, cu, cu, causal=True, out_dtype=torch.float32)
+    ref_pt, _ = O.attention_varlen_ref(q, k, v, cu, cu, causal=True, upcast=False, reorder_ops=True)
+    assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what="192/128 varlen")
+    _check_lse(lse.cpu(), ref_lse)
+    # paged K (d 192) and V (d 128) pools sharing one block table
+    lens_k, lens_q, page = [300, 130, 1000], [300, 2, 129], 64
+    kc, _, bt, sl = make_paged(g, lens_k, h_k, page, dtype, d=192)
+    vc = randn(g, kc.shape[0], page, h_k, 128, dtype=dtype)
+    q = randn(g, sum(lens_q), h, 192, dtype=dtype)
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    out = flash_attn.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cq.cuda(), None, max(lens_q), max(lens_k),
+                                            seqused_k=sl.cuda(), causal=True, block_table=bt.cuda())
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    kcc = clean_nan(kc)
+    for i, (lq, lk) in enumerate(zip(lens_q, lens_k)):
+        qi = q[int(cq[i]):int(cq[i + 1])][None]
+        ki, vi = O.gather_paged_kv(kcc, bt[i], lk)[None], O.gather_paged_kv(vc, bt[i], lk)[None]
+        ref32, _ = O.attention_ref(qi, ki, vi, causal=True, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(qi, ki, vi, causal=True, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out[int(cq[i]):int(cq[i + 1])].cpu()[None], ref32, ref_pt, mult=2.0, eps=2 ** -8,
+                               what=f"192/128 paged seq {i}")
+
+
+@pytest.mark.parametrize("d", DIMS)
+def test_tile_lists_other_head_dims(fa, d):
+    """Block-sparse tile lists (sparse_attn_func) with another head dimension."""
+    flash_attn, cuda = fa
+    g = gen(7 + d)
+    b, s, h, h_k = 1, 640, 4, 2
+    block_m = O.sparse_block_m(s)
+    nq, nk = (s + block_m - 1) // block_m, (s + 127) // 128
+    tm = torch.rand(b, h, nq, nk, generator=g) < 0.4
+    qi = torch.arange(nq).view(-1, 1) * block_m
+    ki = torch.arange(nk).view(1, -1) * 128
+    tm &= (ki <= qi + block_m - 1)
+    tm |= (ki <= qi) & (qi < ki + 128)        # always keep the diagonal tile
+    cnt, offs = O.tile_mask_to_block_lists(tm, block_m=block_m, block_n=64, tile_n=128)
+    q, k, v = randn(g, b, s, h, d), randn(g, b, s, h_k, d), randn(g, b, s, h_k, d)
+    cc = torch.zeros(b, h, nq, dtype=torch.int32)
+    ci = torch.zeros(b, h, nq, 1, dtype=torch.int32)
+    out, lse = flash_attn.sparse_attn_func(q.cuda(), k.cuda(), v.cuda(), cnt.cuda(), offs.cuda(), cc.cuda(), ci.cuda(),
+                                           causal=True, return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    mask = O.block_lists_to_dense_mask(cnt, offs, s, s, block_m)
+    ref32, ref_lse = O.attention_ref(q, k, v, causal=True, out_dtype=torch.float32, extra_mask=mask)
+    ref_pt, _ = O.attention_ref(q, k, v, causal=True, upcast=False, reorder_ops=True, extra_mask=mask)
+    assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"tile lists d={d}")
+    _check_lse(lse.cpu(), ref_lse)
