@@ -2,9 +2,9 @@
 flash_attn/flash_attn_interface.py (flash_attn_func :1646, flash_attn_varlen_func :2111,
 flash_attn_with_kvcache :2478, sparse_attn_func :2778).
 
-Forward only.  Options outside the hot path (dropout, alibi, softcap, sliding window, attention sinks, head
-dimensions other than 128, backward) raise NotImplementedError instead of silently taking another code path:
-there is no Triton, eager or CPU fallback.
+Forward only, head dimension 128 (fp16 / bf16 also 64, 192, 256, and 192 with 128 for v).  Options outside the hot
+path (dropout, alibi, softcap, backward) raise NotImplementedError instead of silently taking another code path: there
+is no Triton, eager or CPU fallback.
 """
 from typing import List, Optional, Union
 
