@@ -607,6 +607,11 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     else if (page == 16 || page == 32) box_rows = page;
     else return FA_B200_ERR_PAGE;
   }
+  if (p->v_transposed) {
+    if (!paged || p->dtype == FA_B200_E4M3) return FA_B200_ERR_UNSUPPORTED;
+    if (p->d != kHeadDim || dv != kHeadDim) return FA_B200_ERR_HEADDIM;
+    if (p->page_size % 64 != 0) return FA_B200_ERR_PAGE;
+  }
   if (varlen && (p->total_q < 0 || p->total_k < 0)) return FA_B200_ERR_SHAPE;
   if (p->b == 0 || p->seqlen_q == 0 || (varlen && p->total_q == 0)) return FA_B200_OK;
   if (!p->q || !p->out) return FA_B200_ERR_NULL;
@@ -637,8 +642,12 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     st = make_tmap(&tk, p->k, p->dtype, p->h_k, p->page_size, p->num_blocks, p->k_head_stride, p->k_row_stride,
                    p->k_batch_stride, box_rows, p->d);
     if (st != FA_B200_OK) return st;
-    st = make_tmap(&tv, p->v, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
-                   p->v_batch_stride, box_rows, dv);
+    if (p->v_transposed)
+      st = make_tmap_vt(&tv, p->v, p->dtype, p->page_size, p->h_k, p->num_blocks, p->v_row_stride, p->v_head_stride,
+                        p->v_batch_stride);
+    else
+      st = make_tmap(&tv, p->v, p->dtype, p->h_k, p->page_size, p->num_blocks, p->v_head_stride, p->v_row_stride,
+                     p->v_batch_stride, box_rows, dv);
   } else {
     st = make_tmap(&tk, p->k, p->dtype, p->h_k, k_rows, nb, p->k_head_stride, p->k_row_stride,
                    varlen ? p->k_row_stride * (k_rows > 0 ? k_rows : 1) : p->k_batch_stride, 128, p->d);
@@ -660,6 +669,7 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   k.o_tma = 1;
   k.d = p->d;
   k.d_v = dv;
+  k.v_transposed = p->v_transposed ? 1 : 0;
   k.s_aux = p->s_aux;
   k.s_aux_dtype = p->s_aux_dtype;
   k.out = p->out;
@@ -791,7 +801,6 @@ int fa_b200_kv_cache_attention(const void* q, const int32_t* seq_offsets, int32_
     p.workspace = workspace; p.workspace_bytes = workspace_bytes;
     return fa_b200_decode_paged(&p, stream);
   }
-  if (layout == 0) return FA_B200_ERR_UNSUPPORTED;
   if (!seq_offsets) return FA_B200_ERR_NULL;
   fa_b200_fwd_params p{};
   p.q = q; p.k = k_caches; p.v = v_caches; p.out = out;
@@ -800,6 +809,9 @@ int fa_b200_kv_cache_attention(const void* q, const int32_t* seq_offsets, int32_
   p.k_batch_stride = p.v_batch_stride = block_stride;
   p.k_row_stride = p.v_row_stride = row_stride;
   p.k_head_stride = p.v_head_stride = head_stride;
+  if (layout == 0) {   // V (pages, kv heads, d, page)
+    p.v_transposed = 1; p.v_row_stride = ps; p.v_head_stride = d * ps;
+  }
   p.b = num_query; p.seqlen_q = max_seqlen_q; p.seqlen_k = max_seqlen_k;
   p.h = num_q_head; p.h_k = num_kv_head; p.d = num_dim;
   p.total_q = num_tokens; p.total_k = 0;

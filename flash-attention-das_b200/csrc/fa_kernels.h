@@ -106,6 +106,7 @@ struct PrefillKernelParams {
   int* work_counter;         // persistent kernels: zeroed before the launch; CTAs claim work items past their first from it
   int32_t d;              // head dimension: 128, or 64 / 192 / 256 (16-bit types, one-tile kernel)
   int32_t d_v;            // head dimension of v and out (= d, or 128 with d = 192)
+  int32_t v_transposed;   // paged V pool with the tokens contiguous: tmap_v describes (page tokens, d, h_k, block), box (64, 128, 1, 1)
 };
 // One 128-row query tile per CTA, two CTAs per SM: block-sparse lists and odd GQA groups.
 cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,

@@ -49,13 +49,15 @@ __host__ __device__ constexpr SmemLayoutInfo smem_layout() {
 // kLeftWindow: the launch has a left sliding-window bound (kept out of the common build of the softmax loop).
 // HD: head dimension of q and k (128; 64, 192, 256 for the 16-bit types — one CTA per SM above 128: shared memory and
 // TMEM).  HDV: head dimension of v and out (= HD, or 128 with HD = 192).
-template <int DT, bool kLeftWindow, int HD, int HDV = HD>
+// VT: the paged V pool is stored transposed (tokens contiguous): a V tile lands as 128 d rows x 128 keys.
+template <int DT, bool kLeftWindow, int HD, int HDV = HD, bool VT = false>
 __global__ void __launch_bounds__(kThreads, HD > 128 ? 1 : 2)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const PrefillKernelParams p) {
   using T = TileTraits<DT, HD>;
   using TV = TileTraits<DT, HDV>;
   static_assert(HDV <= HD, "a V tile must fit a ring slot");
+  static_assert(!VT || (HD == kHeadDim && HDV == kHeadDim && !T::kFp8), "transposed V: 16-bit types, d = 128");
   constexpr SmemLayoutInfo L = smem_layout<DT, HD>();
   constexpr int kTmemCols = tmem_cols(HDV);
   extern __shared__ uint8_t smem_raw[];
@@ -187,6 +189,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             mbar_expect_tx(bar, kv ? TV::kTileBytes : T::kTileBytes);
             for (int hf = 0; hf < halves; ++hf)
               tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, hk, k_row0 + start, coord_b);
+          } else if (VT && kv) {
+            // transposed V pool: one box of 64 keys x 128 d rows per column group; groups that start past the end of
+            // the sequence are not fetched
+            const int nbox = min(kBlockN / 64, (sk - start + 63) / 64);
+            mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * T::kHalfBytes);
+            const int32_t* bt = p.block_table + static_cast<int64_t>(bidb) * p.bt_stride;
+            for (int i = 0; i < nbox; ++i) {
+              const int tok = start + i * 64;
+              tma_load_4d(ring_smem + slot * T::kTileBytes + i * T::kHalfBytes, tm, bar, tok % p.page_size, 0, hk,
+                          bt[tok / p.page_size]);
+            }
           } else {
             // the tile's 128 keys come from one or more pages: one box of box_rows rows per page piece; boxes that
             // start past the end of the sequence are not fetched (their block_table slots are not valid)
@@ -221,7 +234,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!mbar_wait(smem_u32(&kv_full[v_slot]), (v_item / kSlots) & 1, wctx)) { ok = false; break; }
         if (!mbar_wait(smem_u32(p_full), j & 1, wctx)) { ok = false; break; }
         tc_fence_after();
-        issue_pv<DT, HDV>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
+        if constexpr (VT) issue_pv_vt<DT>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
+        else issue_pv<DT, HDV>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
         tc_commit(smem_u32(&kv_empty[v_slot]));
         if (j + 1 < n_tiles) {
           if (!mbar_wait(smem_u32(&kv_full[k_slot]), (k_item / kSlots) & 1, wctx)) { ok = false; break; }
@@ -274,7 +288,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         // (after it has landed) before the P V product may start.
         const int v_item = 2 * j + 1;
         if (!mbar_wait(smem_u32(&kv_full[v_item % kSlots]), (v_item / kSlots) & 1, wctx)) { ok = false; break; }
-        if (row >= sk - start) {
+        if constexpr (VT) {
+          // this thread owns d row `row` of the transposed tile: keys at or past the end are cleared, whole 16-byte
+          // pieces (8 keys) where possible, element by element in the piece the end falls into
+          const int lim_k = sk - start;
+          const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const int k0 = c * 8;
+            if (k0 + 8 <= lim_k) continue;
+            const uint32_t addr = vrow + (c >> 3) * T::kHalfBytes + (((c & 7) ^ (row & 7)) << 4);
+            uint32_t w[4] = {0u, 0u, 0u, 0u};
+            if (k0 < lim_k) {
+              asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int ka = k0 + 2 * e;
+                w[e] = (ka < lim_k ? (w[e] & 0x0000ffffu) : 0u) | (ka + 1 < lim_k ? (w[e] & 0xffff0000u) : 0u);
+              }
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+          }
+        } else if (row >= sk - start) {
           const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
 #pragma unroll
           for (int hf = 0; hf < TV::kHalves; ++hf)
@@ -318,11 +353,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   }
 }
 
-template <int DT, int HD = kHeadDim, int HDV = HD>
+template <int DT, int HD = kHeadDim, int HDV = HD, bool VT = false>
 cudaError_t launch_single_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                             const PrefillKernelParams& p, cudaStream_t stream) {
   const bool win = p.window_left >= 0;
-  auto kern = win ? prefill_kernel<DT, true, HD, HDV> : prefill_kernel<DT, false, HD, HDV>;
+  auto kern = win ? prefill_kernel<DT, true, HD, HDV, VT> : prefill_kernel<DT, false, HD, HDV, VT>;
   const size_t smem = 1024 + smem_layout<DT, HD>().total;
   static bool attr_done[2][64] = {};
   int dev = 0;
@@ -352,6 +387,11 @@ cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tq, const CUtens
         return bf ? launch_single_t<FA_B200_BF16, 192>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 192>(tq, tk, tv, p, stream);
       case 256: return bf ? launch_single_t<FA_B200_BF16, 256>(tq, tk, tv, p, stream) : launch_single_t<FA_B200_F16, 256>(tq, tk, tv, p, stream);
     }
+    return cudaErrorInvalidValue;
+  }
+  if (p.v_transposed) {
+    if (dtype == FA_B200_BF16) return launch_single_t<FA_B200_BF16, kHeadDim, kHeadDim, true>(tq, tk, tv, p, stream);
+    if (dtype == FA_B200_F16) return launch_single_t<FA_B200_F16, kHeadDim, kHeadDim, true>(tq, tk, tv, p, stream);
     return cudaErrorInvalidValue;
   }
   switch (dtype) {

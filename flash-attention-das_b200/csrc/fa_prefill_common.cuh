@@ -198,6 +198,21 @@ __device__ __forceinline__ void issue_pv(uint32_t p_tmem, uint32_t v_smem, uint3
   }
 }
 
+// O[tmem] (+)= P[tmem] V[smem] with V given transposed: the tile is 128 d rows of 128 keys (two 128-byte column groups
+// of 64 keys, 16 KB apart), i.e. a K-major B operand laid out exactly like a K tile in Q K^T.  16-bit types.
+template <int DT>
+__device__ __forceinline__ void issue_pv_vt(uint32_t p_tmem, uint32_t vt_smem, uint32_t o_tmem, bool overwrite) {
+  using T = TileTraits<DT>;
+  static_assert(!T::kFp8, "transposed V: 16-bit types");
+  constexpr uint32_t idesc = make_idesc(T::kFormat, false, kBlockM, kHeadDim);
+  const uint64_t b0 = make_smem_desc_sw128(vt_smem, 16, 1024);
+#pragma unroll
+  for (int ks = 0; ks < T::kPVSteps; ++ks) {
+    const uint64_t off = static_cast<uint64_t>((ks >> 2) * (T::kHalfBytes >> 4) + (ks & 3) * 2);
+    tc_mma_ts(o_tmem, p_tmem + ks * 8, b0 + off, idesc, ks > 0 ? 1u : (overwrite ? 0u : 1u), false);
+  }
+}
+
 // Visible key range of query row i (index inside its sequence): [row_lo, row_hi).
 __device__ __forceinline__ int row_hi(const PrefillKernelParams& p, int i, int sk, int shift) {
   return p.window_right >= 0 ? min(sk, i + 1 + shift + p.window_right) : sk;

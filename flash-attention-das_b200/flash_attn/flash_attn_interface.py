@@ -108,9 +108,9 @@ def flash_attn_varlen_func(
     for layout "bshd" or (num_blocks, nheads_k, page_size, 128) for "bhsd", and `seqused_k` (int32 (batch,)) gives
     each sequence's number of keys; cu_seqlens_k is not used.  The kernel reads the pages directly, through strides,
     whatever the layout (the reference gathers them into a contiguous copy first,
-    flash_attn_interface.py:2350-2373).  Layout "custom" (V stored transposed, (num_blocks, nheads_k, 128, page_size)) is
-    taken for one query token per sequence (the decode kernel), as the reference sends that case to its decode
-    kernel too (flash_attn_interface.py:2316-2348)."""
+    flash_attn_interface.py:2350-2373).  Layout "custom": K as "bhsd" and V stored transposed,
+    (num_blocks, nheads_k, 128, page_size), fp16 / bf16 with pages of a multiple of 64 tokens; a V tile is then fed to
+    the P V product as the K-major operand."""
     _no_backward(q, k, v)
     if window_size is None:
         window_size = (-1, -1)
@@ -122,9 +122,6 @@ def flash_attn_varlen_func(
         bs = block_table.shape[0]
         group = q.shape[1] // k.shape[2]
         few_tokens = max_seqlen_q >= 1 and max_seqlen_q * bs == q.shape[0] and max_seqlen_q * group <= 16
-        if layout in ("custom", 0) and not few_tokens:
-            raise NotImplementedError("paged layout 'custom' (V transposed) is taken for a few query tokens per sequence "
-                                      "only: use 'bshd' or 'bhsd' for prefill over a paged cache")
         if few_tokens and (max_seqlen_q > 1 or layout in ("custom", 0)) and q_v is None and dropout_p == 0.0:
             if softmax_scale is None:
                 softmax_scale = q.shape[-1] ** (-0.5)
@@ -279,8 +276,7 @@ def vllm_flash_attn_varlen_func(q, k, v, max_seqlen_q, cu_seqlens_q, max_seqlen_
                                 q_descale=None, k_descale=None, v_descale=None, kv_cache_dtype="auto",
                                 fa_version: int = DEFAULT_FA_VERSION, s_aux=None):
     """Argument order of the reference's vLLM entry (flash_attn_interface.py:2410-2475), which forwards to
-    flash_attn_varlen_func with layout "custom"; paged pools in that layout are not supported here, so with a
-    block_table this raises and without one it is flash_attn_varlen_func."""
+    flash_attn_varlen_func with layout "custom" (K (num_blocks, nheads_k, page, d), V (num_blocks, nheads_k, d, page))."""
     return flash_attn_varlen_func(
         q, k, v, max_seqlen_q=max_seqlen_q, cu_seqlens_q=cu_seqlens_q, max_seqlen_k=max_seqlen_k,
         cu_seqlens_k=cu_seqlens_k, seqused_k=seqused_k, q_v=q_v, dropout_p=dropout_p, softmax_scale=softmax_scale,

@@ -57,7 +57,7 @@ class FwdParams(ctypes.Structure):
         ("page_size", _c_i32), ("num_blocks", _c_i32),
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
         ("has_window", _c_i32), ("window_left", _c_i32), ("window_right", _c_i32),
-        ("column_count", _c_vp), ("d_v", _c_i32),
+        ("column_count", _c_vp), ("d_v", _c_i32), ("v_transposed", _c_i32),
     ]
 
 
@@ -264,7 +264,12 @@ def _set_paged(p, kcache, vcache, block_table, seqused_k, batch):
     _require(kcache.dim() == 4 and kcache.shape[:3] == vcache.shape[:3], "paged k/v must be (num_blocks, page_size, nheads_k, d)")
     p.k, p.v = kcache.data_ptr(), vcache.data_ptr()
     p.k_batch_stride, p.k_row_stride, p.k_head_stride = kcache.stride(0), kcache.stride(1), kcache.stride(2)
-    p.v_batch_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
+    if _is_transposed_v(vcache):
+        # (num_blocks, page, h_k, d) view of a pool stored as (num_blocks, h_k, d, page): the tokens are the contiguous axis
+        p.v_transposed = 1
+        p.v_batch_stride, p.v_head_stride, p.v_row_stride = vcache.stride(0), vcache.stride(2), vcache.stride(3)
+    else:
+        p.v_batch_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
     p.block_table, p.block_table_batch_stride = block_table.data_ptr(), block_table.stride(0)
     p.seqused_k = seqused_k.data_ptr()
     p.page_size, p.num_blocks = kcache.shape[1], kcache.shape[0]
@@ -364,8 +369,8 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
                max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
                window_size_right, softcap, return_softmax, q_descale_=None, k_descale_=None, v_descale_=None,
                gen_=None, s_aux_=None):
-    _check_qkv(q, k, v, allow_dv=True)
     paged = block_table_ is not None
+    _check_qkv(q, k, v, paged and _is_transposed_v(v), allow_dv=True)
     _unsupported(seqused_k is not None and not paged, "seqused_k without block_table")
     _unsupported(leftpad_k_ is not None, "leftpad_k")
     _unsupported(alibi_slopes_ is not None, "alibi")
@@ -513,9 +518,8 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     _unsupported(fp8_kv and (v_t or k_ is not None or q_descale_ is not None or
                              q.shape[1] * (q.shape[2] // max(kcache.shape[2], 1)) > 16),
                  "an e4m3 KV cache under 16-bit queries outside the decode of a few tokens (no append, no q_descale)")
-    _unsupported(v_t and (q.shape[1] * (q.shape[2] // max(kcache.shape[2], 1)) > 16 or k_ is not None or
-                          q.dtype == torch.float8_e4m3fn),
-                 "a transposed V pool (layout 0) outside bf16/fp16 decode of a few tokens without append")
+    _unsupported(v_t and (k_ is not None or q.dtype == torch.float8_e4m3fn),
+                 "a transposed V pool (layout 0) with e4m3 tensors or with new keys to append")
     _require((k_ is None) == (v_ is None), "k and v must be passed together")
     _require(rotary_cos_ is None or k_ is not None, "rotary_cos/rotary_sin are only applicable if k and v are passed in")
     _require((rotary_cos_ is None) == (rotary_sin_ is None), "rotary_cos and rotary_sin must be passed together")
@@ -545,7 +549,7 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     if k_ is not None:
         q, seqlens_k_ = kv_append(q, kcache, vcache, k_, v_, seqlens_k_, block_table_, rotary_cos_, rotary_sin_,
                                   is_rotary_interleaved, is_causal or window_size_left >= 0 or window_size_right >= 0)
-    if sq > 1 and (sq * (h // h_k) > 16 or v_t):
+    if sq > 1 and sq * (h // h_k) > 16:
         # several query tokens per sequence (chunked prefill) over the paged cache: the prefill kernel reads K/V through
         # the block table; the causal mask is bottom-right aligned to each cache length.  A few tokens (speculative
         # decoding: tokens x heads per kv head <= 16) stay on the decode kernel below, which packs them into the rows of

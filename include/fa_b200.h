@@ -125,6 +125,11 @@ typedef struct fa_b200_fwd_params {
    * multi-head latent attention prefill shape the reference takes in its bshd paths (flash_attn_interface.py:2241-2242).
    * 0 = same as d. */
   int32_t d_v;
+  /* Paged V stored transposed, (num_blocks, h_k, d, page_size) with the tokens of a page contiguous (the reference's
+   * paged layout 0 / "custom", flash_attn/flash_attn_interface.py:2223-2227; K is then (num_blocks, h_k, page_size, d),
+   * which the K strides express).  With v_transposed != 0, v_row_stride is the stride between consecutive d rows.
+   * Needs block_table; F16 / BF16, d = 128, page_size a multiple of 64. */
+  int32_t v_transposed;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch
@@ -282,13 +287,13 @@ FA_B200_API int fa_b200_combine(const fa_b200_combine_params* p, void* stream);
  *   seq_offsets   int32 (num_query + 1): first token of each request in q
  *   k_caches / v_caches   layout 1: (num_pages, num_kv_head, page_size, num_dim)
  *                         layout 2: (num_pages, page_size, num_kv_head, num_dim)
- *                         layout 0: K as layout 1, V (num_pages, num_kv_head, num_dim, page_size); one token per request only
+ *                         layout 0: K as layout 1, V (num_pages, num_kv_head, num_dim, page_size)
  *   page_tables   int32 (num_query, (max_seqlen_k - 1) / page_size + 1)
  *   cache_lens    int32 (num_query): keys of each request, the new tokens included
  *
  * num_query == num_tokens: one query token per request, every key visible (the reference's paged_attention branch).
  * Otherwise: each request's tokens are the last ones of its sequence and attend causally (bottom-right aligned) to its
- * pages (the reference's hg_prefix_prefill_varlen_fwd branch; layouts 1 and 2).  softmax scale = 1 / sqrt(num_dim).
+ * pages (the reference's hg_prefix_prefill_varlen_fwd branch, which takes layouts 1 and 2).  softmax scale = 1 / sqrt(num_dim).
  * workspace: fa_b200_kv_cache_attention_workspace_bytes(num_query, num_q_head, num_kv_head, num_dim, page_size,
  * max_seqlen_k)
  * bytes, 16-byte aligned

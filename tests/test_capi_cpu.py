@@ -121,7 +121,7 @@ def test_raw_pointer_entry_validates_before_touching_anything(binding):
     assert call(num_query=0, num_tokens=0) == 0
     assert call(hq=6, hk=4) == 4         # reaches the decode call's own checks
     assert call() == 1                   # null pointers
-    assert call(num_tokens=9, layout=0) == 9   # several tokens per request over a transposed V pool
+    assert call(num_tokens=9, layout=0, d=64) == 3   # a transposed V pool: head dimension 128 only
     assert call(num_tokens=9) == 1       # seq_offsets missing
     d = binding.DecodeParams()
     d.d, d.dtype, d.out_dtype = 128, 1, 1

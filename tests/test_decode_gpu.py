@@ -353,7 +353,8 @@ def test_fp8_kv_cache_under_16bit_queries(fa, qdtype, sq):
 def test_raw_pointer_entry_matches_the_tensor_entries(fa):
     """kv_cache_attention / cal_paged_attention (the reference's extern "C" raw-pointer entry, flash_api.cpp:2589-2631):
     one token per request gives the bits of flash_attn_with_kvcache for the three layouts; several tokens per request give
-    the bits of the paged varlen entry (causal, bottom-right aligned) and agree with the oracle."""
+    the bits of the paged varlen entry (causal, bottom-right aligned; layout 0 the same values through another operand
+    layout) and agree with the oracle."""
     flash_attn, cuda = fa
     g = gen(123)
     lens, h, hk, page = [1, 200, 64, 513, 300], 8, 2, 64
@@ -384,13 +385,13 @@ def test_raw_pointer_entry_matches_the_tensor_entries(fa):
     qv_d, cu_d = qv.cuda(), cu.cuda()
     want = flash_attn.flash_attn_varlen_func(qv_d, kc_d, vc_d, cu_d, None, max(q_lens), max(lens), causal=True,
                                              block_table=bt_d, seqused_k=sl_d)
-    for layout in (1, 2):
+    for layout in (0, 1, 2):
         out = torch.full_like(qv_d, float("nan"))
         cuda.kv_cache_attention(qv_d, cu_d, max(q_lens), max(lens), pools[layout][0], pools[layout][1], bt_d, sl_d, out, n,
                                 total, h, hk, 128, pool, page, "bf16", layout)
         torch.cuda.synchronize()
         assert cuda.device_status() == 0
-        assert torch.equal(out, want), layout
+        assert torch.equal(out, want) if layout else max_err(out, want) <= 2 ** -6, layout
     kcc, vcc = clean_nan(kc), clean_nan(vc)
     for i, (lq, lk) in enumerate(zip(q_lens, lens)):
         q_i = qv[int(cu[i]):int(cu[i + 1])][None]
@@ -399,6 +400,3 @@ def test_raw_pointer_entry_matches_the_tensor_entries(fa):
         ref_pt, _ = O.attention_ref(q_i, k_i, v_i, causal=True, upcast=False, reorder_ops=True)
         assert_close_to_oracle(out[int(cu[i]):int(cu[i + 1])].cpu()[None], ref32, ref_pt, mult=2.0, eps=2 ** -8,
                                what=f"request {i}")
-    with pytest.raises(RuntimeError):    # several tokens per request over a transposed V pool: not built
-        cuda.kv_cache_attention(qv_d, cu_d, max(q_lens), max(lens), pools[0][0], pools[0][1], bt_d, sl_d, out, n, total, h,
-                                hk, 128, pool, page, "bf16", 0)

@@ -366,8 +366,11 @@ def test_paged_layout_bhsd_gives_identical_bits(fa, page):
         torch.cuda.synchronize()
         assert cuda.device_status() == 0
         assert torch.equal(d1, d4) and torch.equal(d1[:, 0], d5)
-        with pytest.raises(NotImplementedError):   # prefill over a transposed V pool is not taken
-            flash_attn.flash_attn_varlen_func(q.cuda(), kc_t, vc_tt, cq, None, max(lens_q), max(lens_k), layout="custom", **args)
+        # prefill over the transposed V pool: the same values reach the tensor cores through a K-major operand
+        o3 = flash_attn.flash_attn_varlen_func(q.cuda(), kc_t, vc_tt, cq, None, max(lens_q), max(lens_k), layout="custom", **args)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        assert max_err(o3, o1) <= 2 ** -6
     else:
         with pytest.raises(RuntimeError):          # layout 0 needs pages of 64 * n
             flash_attn.vllm_flash_attn_with_kvcache(qd, kc_t, vc_d.permute(0, 2, 3, 1).contiguous(), cache_seqlens=sl.cuda(),
@@ -398,3 +401,48 @@ def test_torch_ops_reach_the_same_kernels(fa):
                                                    bt.cuda(), None, None, scale, True, -1, -1, 0.0, True, 0)
     torch.cuda.synchronize()
     assert torch.equal(o5, o6)
+
+
+@pytest.mark.parametrize("page", [64, 256])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_paged_prefill_over_transposed_v_pool(fa, page, dtype):
+    """Layout "custom" (the reference's paged layout 0, flash_attn_interface.py:2223-2227): K (num_blocks, h_k, page, d),
+    V (num_blocks, h_k, d, page).  Unused pages and the rows / columns past each sequence's end are NaN: nothing past
+    the end may reach the output.  Also through flash_attn_with_kvcache with many query tokens."""
+    from _util import clean_nan, make_paged
+    flash_attn, cuda = fa
+    g = gen(777 + page)
+    lens_k = [300, 130, 1000, 64, 257, 960]
+    lens_q = [300, 2, 129, 64, 200, 17]
+    h, h_k = 8, 2
+    kc, vc, bt, sl = make_paged(g, lens_k, h_k, page, dtype)
+    q = randn(g, sum(lens_q), h, 128, dtype=dtype)
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    kc_t = kc.cuda().permute(0, 2, 1, 3).contiguous()
+    vc_tt = vc.cuda().permute(0, 2, 3, 1).contiguous()
+    out, lse = flash_attn.flash_attn_varlen_func(q.cuda(), kc_t, vc_tt, cq.cuda(), None, max(lens_q), max(lens_k),
+                                                 seqused_k=sl.cuda(), causal=True, block_table=bt.cuda(), layout="custom",
+                                                 return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    kcc, vcc = clean_nan(kc), clean_nan(vc)
+    for i, (lq, lk) in enumerate(zip(lens_q, lens_k)):
+        qi = q[int(cq[i]):int(cq[i + 1])][None]
+        ki, vi = O.gather_paged_kv(kcc, bt[i], lk)[None], O.gather_paged_kv(vcc, bt[i], lk)[None]
+        ref32, ref_lse = O.attention_ref(qi, ki, vi, causal=True, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(qi, ki, vi, causal=True, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out[int(cq[i]):int(cq[i + 1])].cpu()[None], ref32, ref_pt, mult=2.0, eps=2 ** -8,
+                               what=f"transposed V pool seq {i} page {page}")
+        _check_lse(lse[:, int(cq[i]):int(cq[i + 1])].cpu(), ref_lse[0])
+    # the kvcache entry with 40 query tokens per sequence (40 x 4 rows: beyond the decode tile) takes the same kernel
+    lens2 = [300, 130, 1000, 64]
+    qd = randn(g, len(lens2), 40, h, 128, dtype=dtype)
+    o2 = flash_attn.vllm_flash_attn_with_kvcache(qd.cuda(), kc_t, vc_tt, cache_seqlens=sl[:4].cuda(), block_table=bt[:4].cuda(),
+                                                 causal=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    for i, lk in enumerate(lens2):
+        ki, vi = O.gather_paged_kv(kcc, bt[i], lk)[None], O.gather_paged_kv(vcc, bt[i], lk)[None]
+        ref32, _ = O.attention_ref(qd[i][None], ki, vi, causal=True, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(qd[i][None], ki, vi, causal=True, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(o2[i].cpu()[None], ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"kvcache transposed V seq {i}")
