@@ -486,6 +486,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.sq = p->seqlen_q > 1 ? p->seqlen_q : 1;
   k.causal = p->is_causal ? 1 : 0;
   k.kv_e4m3 = p->kv_e4m3 ? 1 : 0;
+  k.kv_e5m2 = (p->kv_e4m3 && p->kv_e5m2) ? 1 : 0;
   k.d = p->d;
   k.q_row_stride = p->q_row_stride;
   k.o_row_stride = p->o_row_stride;

@@ -157,6 +157,12 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint32_t x) {
 }
 // Packed fp32 pairs (sm_100 executes fma / add on two floats per instruction) and the three-input max: the
 // softmax threads are bound by the number of instructions they issue, not by any one pipe.
+// Two fp8 bytes (low 16 bits of x) -> f16x2.  E5: the bytes are e5m2, i.e. the high bytes of the two f16 values.
+template <bool E5>
+__device__ __forceinline__ uint32_t cvt_fp8x2_to_f16x2(uint32_t x) {
+  if constexpr (E5) return __byte_perm(x, 0u, 0x1404);
+  else return cvt_e4m3x2_to_f16x2(x);
+}
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));

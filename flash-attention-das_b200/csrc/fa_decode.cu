@@ -60,7 +60,8 @@ __device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
 // QT: element type of the queries.  Normally QT == DT; QT = F16 / BF16 with DT = E4M3 is the "fp8 KV cache" mode: the
 // cache is e4m3, the queries (and the output) are 16-bit.  K is then converted to f16 in registers on its way into the
 // Q K^T product (f16 MMA; bf16 queries are converted to f16 once per CTA), V as in the all-e4m3 mode.
-template <int DT, int STAGES, bool VT, int QT = DT, int HD = 128>
+// E5 (mixed mode only): the cache bytes are e5m2.
+template <int DT, int STAGES, bool VT, int QT = DT, int HD = 128, bool E5 = false>
 __global__ void __launch_bounds__(kDecodeThreads, HD > 128 ? 1 : 2)
 decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                     const DecodeKernelParams p) {
@@ -69,6 +70,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   constexpr int kStageBytes = T::kStageBytes;
   static_assert(!kMixed || (DT == FA_B200_E4M3 && !VT), "mixed mode: 16-bit queries over an e4m3 cache");
   static_assert(HD == 128 || (!kMixed && !VT), "other head dimensions: plain 16-bit pools only");
+  static_assert(!E5 || kMixed, "e5m2 bytes: cache under 16-bit queries only");
   constexpr int kQElem = kMixed ? 2 : T::kElem;
   constexpr int kQRegSteps = kMixed ? 8 : T::kQSteps;
   extern __shared__ uint8_t smem_raw[];
@@ -271,10 +273,10 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             ldsm_x4(addr, b00, b01, b10, b11);
             if constexpr (kMixed) {
               // each register holds four consecutive e4m3 d values of one token: two f16 pairs, one 16-wide k-step
-              mma_f16_16816(sc[0], qf[2 * ks], cvt_e4m3x2_to_f16x2(b00), cvt_e4m3x2_to_f16x2(b00 >> 16));
-              mma_f16_16816(sc[0], qf[2 * ks + 1], cvt_e4m3x2_to_f16x2(b01), cvt_e4m3x2_to_f16x2(b01 >> 16));
-              mma_f16_16816(sc[1], qf[2 * ks], cvt_e4m3x2_to_f16x2(b10), cvt_e4m3x2_to_f16x2(b10 >> 16));
-              mma_f16_16816(sc[1], qf[2 * ks + 1], cvt_e4m3x2_to_f16x2(b11), cvt_e4m3x2_to_f16x2(b11 >> 16));
+              mma_f16_16816(sc[0], qf[2 * ks], cvt_fp8x2_to_f16x2<E5>(b00), cvt_fp8x2_to_f16x2<E5>(b00 >> 16));
+              mma_f16_16816(sc[0], qf[2 * ks + 1], cvt_fp8x2_to_f16x2<E5>(b01), cvt_fp8x2_to_f16x2<E5>(b01 >> 16));
+              mma_f16_16816(sc[1], qf[2 * ks], cvt_fp8x2_to_f16x2<E5>(b10), cvt_fp8x2_to_f16x2<E5>(b10 >> 16));
+              mma_f16_16816(sc[1], qf[2 * ks + 1], cvt_fp8x2_to_f16x2<E5>(b11), cvt_fp8x2_to_f16x2<E5>(b11 >> 16));
             } else {
               mma_qk<DT>(sc[0], qf[ks], b00, b01);
               mma_qk<DT>(sc[1], qf[ks], b10, b11);
@@ -376,10 +378,10 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
               ldsm_x4_trans(addr, w0, w1, w2, w3);
               const uint32_t t0 = __byte_perm(w0, 0u, 0x3120), t1 = __byte_perm(w1, 0u, 0x3120);
               const uint32_t t2 = __byte_perm(w2, 0u, 0x3120), t3 = __byte_perm(w3, 0u, 0x3120);
-              mma_pv<DT>(o[2 * cc], pa, cvt_e4m3x2_to_f16x2(t0), cvt_e4m3x2_to_f16x2(t1));
-              mma_pv<DT>(o[2 * cc + 1], pa, cvt_e4m3x2_to_f16x2(t0 >> 16), cvt_e4m3x2_to_f16x2(t1 >> 16));
-              mma_pv<DT>(o[2 * cc + 2], pa, cvt_e4m3x2_to_f16x2(t2), cvt_e4m3x2_to_f16x2(t3));
-              mma_pv<DT>(o[2 * cc + 3], pa, cvt_e4m3x2_to_f16x2(t2 >> 16), cvt_e4m3x2_to_f16x2(t3 >> 16));
+              mma_pv<DT>(o[2 * cc], pa, cvt_fp8x2_to_f16x2<E5>(t0), cvt_fp8x2_to_f16x2<E5>(t1));
+              mma_pv<DT>(o[2 * cc + 1], pa, cvt_fp8x2_to_f16x2<E5>(t0 >> 16), cvt_fp8x2_to_f16x2<E5>(t1 >> 16));
+              mma_pv<DT>(o[2 * cc + 2], pa, cvt_fp8x2_to_f16x2<E5>(t2), cvt_fp8x2_to_f16x2<E5>(t3));
+              mma_pv<DT>(o[2 * cc + 3], pa, cvt_fp8x2_to_f16x2<E5>(t2 >> 16), cvt_fp8x2_to_f16x2<E5>(t3 >> 16));
             }
           }
           }
@@ -490,12 +492,12 @@ static size_t decode_smem_bytes(int stages, int stage_bytes) {
 }
 int decode_max_pages_per_partition() { return kMaxPagesPerPartition; }
 
-template <int DT, bool VT, int QT = DT, int HD = 128>
+template <int DT, bool VT, int QT = DT, int HD = 128, bool E5 = false>
 static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,
                                     cudaStream_t stream) {
   // about 96 KB of tiles in flight per CTA at two CTAs per SM; one CTA per SM above d = 128
   constexpr int STAGES = HD == 64 ? 6 : (HD == 192 ? 4 : 3);
-  auto kern = decode_paged_kernel<DT, STAGES, VT, QT, HD>;
+  auto kern = decode_paged_kernel<DT, STAGES, VT, QT, HD, E5>;
   const size_t smem = decode_smem_bytes(STAGES, DecodeTraits<DT, HD>::kStageBytes);
   static bool attr_done[64] = {};
   int dev = 0;
@@ -527,6 +529,11 @@ cudaError_t launch_decode(int dtype, const CUtensorMap& tk, const CUtensorMap& t
   }
   if (p.kv_e4m3) {   // 16-bit queries over an e4m3 cache
     if (p.v_transposed) return cudaErrorInvalidValue;
+    if (p.kv_e5m2) {
+      if (dtype == FA_B200_F16) return launch_decode_dt<FA_B200_E4M3, false, FA_B200_F16, 128, true>(tk, tv, p, stream);
+      if (dtype == FA_B200_BF16) return launch_decode_dt<FA_B200_E4M3, false, FA_B200_BF16, 128, true>(tk, tv, p, stream);
+      return cudaErrorInvalidValue;
+    }
     if (dtype == FA_B200_F16) return launch_decode_dt<FA_B200_E4M3, false, FA_B200_F16>(tk, tv, p, stream);
     if (dtype == FA_B200_BF16) return launch_decode_dt<FA_B200_E4M3, false, FA_B200_BF16>(tk, tv, p, stream);
     return cudaErrorInvalidValue;

@@ -38,6 +38,7 @@ struct DecodeKernelParams {
   int32_t causal;       // sq > 1: token s sees the keys up to its own position
   int32_t kv_e4m3;      // the cache is e4m3 while the queries are 16-bit (launch_decode's dtype is then the query type)
   int32_t d;            // head dimension: 128, or 64 / 192 / 256 with 16-bit pools
+  int32_t kv_e5m2;      // with kv_e4m3: the cache bytes are e5m2
 };
 
 int decode_max_pages_per_partition();

@@ -245,11 +245,11 @@ def vllm_flash_attn_with_kvcache(
         raise NotImplementedError("vllm_flash_attn_with_kvcache does not append k/v (as in the reference); use "
                                   "flash_attn_with_kvcache")
     if str(kv_cache_dtype).startswith("fp8"):
-        # an e4m3 cache under 16-bit (or e4m3) queries; k_scale / v_scale are its descales.  Raw-byte caches are viewed.
-        if "e5m2" in str(kv_cache_dtype):
-            raise NotImplementedError("an e5m2 KV cache is outside the B200 hot path")
+        # an e4m3 cache under 16-bit (or e4m3) queries, or an e5m2 cache ("fp8_e5m2") under 16-bit queries; k_scale /
+        # v_scale are its descales.  Raw-byte caches are viewed.
         if k_cache.dtype == torch.uint8:
-            k_cache, v_cache = k_cache.view(torch.float8_e4m3fn), v_cache.view(torch.float8_e4m3fn)
+            f8 = torch.float8_e5m2 if "e5m2" in str(kv_cache_dtype) else torch.float8_e4m3fn
+            k_cache, v_cache = k_cache.view(f8), v_cache.view(f8)
     elif kv_cache_dtype not in ("auto", ""):
         raise NotImplementedError(f"kv_cache_dtype {kv_cache_dtype!r} is outside the B200 hot path")
     if softcap is not None and softcap > 0.0:

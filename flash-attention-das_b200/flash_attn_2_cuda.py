@@ -86,7 +86,7 @@ class DecodeParams(ctypes.Structure):
         ("v_transposed", _c_i32),
         ("seqlen_q", _c_i32), ("is_causal", _c_i32),
         ("q_row_stride", _c_i64), ("o_row_stride", _c_i64),
-        ("kv_e4m3", _c_i32),
+        ("kv_e4m3", _c_i32), ("kv_e5m2", _c_i32),
     ]
 
 
@@ -218,8 +218,8 @@ def _unsupported(cond: bool, what: str):
 
 
 def _is_fp8_kv(q, k) -> bool:
-    """16-bit queries over an e4m3 cache (the reference's kv_cache_dtype = "fp8" mode)."""
-    return q.dtype in (torch.float16, torch.bfloat16) and k.dtype == torch.float8_e4m3fn
+    """16-bit queries over an e4m3 or e5m2 cache (the reference's kv_cache_dtype = "fp8" / "fp8_e5m2" modes)."""
+    return q.dtype in (torch.float16, torch.bfloat16) and k.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
 
 
 def _check_qkv(q, k, v, v_transposed=False, allow_fp8_kv=False, allow_dv=False):
@@ -491,6 +491,7 @@ def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out
     p.softmax_scale = softmax_scale
     p.dtype = _DT[q.dtype]
     p.kv_e4m3 = 1 if _is_fp8_kv(q, kcache) else 0
+    p.kv_e5m2 = 1 if p.kv_e4m3 and kcache.dtype == torch.float8_e5m2 else 0
     p.out_dtype = _DT[out.dtype] if out is not None else BF16
     _descale(p, "q_descale", q_descale, b, h_k)
     _descale(p, "k_descale", k_descale, b, h_k)
@@ -595,9 +596,9 @@ def paged_attention(out, query, key_cache, value_cache, scale, block_tables, seq
     (num_blocks, h_k, page, d) and value_cache (num_blocks, h_k, d, page); 1: both (num_blocks, h_k, page, d); 2: both
     (num_blocks, page, h_k, d).  q/k/v_scale are the e4m3 descales."""
     if str(kv_cache_dtype).startswith("fp8"):
-        _unsupported("e5m2" in str(kv_cache_dtype), "an e5m2 KV cache")
         if key_cache.dtype == torch.uint8:      # caches kept as raw bytes
-            key_cache, value_cache = key_cache.view(torch.float8_e4m3fn), value_cache.view(torch.float8_e4m3fn)
+            f8 = torch.float8_e5m2 if "e5m2" in str(kv_cache_dtype) else torch.float8_e4m3fn
+            key_cache, value_cache = key_cache.view(f8), value_cache.view(f8)
     else:
         _unsupported(kv_cache_dtype not in ("auto", ""), f"kv_cache_dtype {kv_cache_dtype!r}")
     if layout == 2:

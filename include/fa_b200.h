@@ -212,6 +212,10 @@ typedef struct fa_b200_decode_params {
    * paged_attention with kv_cache_dtype = "fp8" and k_scale / v_scale, flash_api.cpp:2496-2515).  k_descale / v_descale
    * carry the cache scales; q_descale is not used.  Not with v_transposed. */
   int32_t kv_e4m3;
+  /* With kv_e4m3 != 0 and kv_e5m2 != 0 the cache bytes are E5M2 instead (kv_cache_dtype = "fp8_e5m2",
+   * src/paged_attention.cu:747-1149 takes both fp8 formats): an e5m2 value is the high byte of an f16, so the
+   * conversion on the way into the products is a byte move. */
+  int32_t kv_e5m2;
 } fa_b200_decode_params;
 
 /* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)

@@ -309,18 +309,24 @@ def test_varlen_entry_with_few_tokens_uses_the_decode_kernel(fa):
     assert torch.equal(got_lse.view(h, len(lens), sq).permute(1, 0, 2), want_lse)
 
 
+@pytest.mark.parametrize("f8", [torch.float8_e4m3fn, torch.float8_e5m2])
 @pytest.mark.parametrize("qdtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("sq", [1, 3])
-def test_fp8_kv_cache_under_16bit_queries(fa, qdtype, sq):
-    """The reference's kv_cache_dtype = "fp8" mode (flash_api.cpp:2496-2515): e4m3 K/V pools with per-tensor scales, 16-bit
-    queries and output.  Checked against the oracle on the dequantised cache, through flash_attn_with_kvcache and the
+def test_fp8_kv_cache_under_16bit_queries(fa, qdtype, sq, f8):
+    """The reference's kv_cache_dtype = "fp8" / "fp8_e5m2" modes (flash_api.cpp:2496-2515): e4m3 or e5m2 K/V pools with
+    per-tensor scales, 16-bit queries and output.  Checked against the oracle on the dequantised cache, through flash_attn_with_kvcache and the
     vLLM-named entry (raw uint8 pools, layout 1)."""
     flash_attn, cuda = fa
     g = gen(808 + sq)
     lens, h, hk = [sq, 100, 128, 129, 1000, 2049], 8, 2
     kc, vc, bt, sl = make_paged(g, lens, hk, 64, torch.bfloat16, poison=False)
-    k8, kd = O.quantize_e4m3_per_tensor(kc)
-    v8, vd = O.quantize_e4m3_per_tensor(vc)
+    if f8 == torch.float8_e4m3fn:
+        k8, kd = O.quantize_e4m3_per_tensor(kc)
+        v8, vd = O.quantize_e4m3_per_tensor(vc)
+    else:   # e5m2: same per-tensor scheme, scaled into a range well inside the format's
+        kd, vd = kc.float().abs().max() / 448.0, vc.float().abs().max() / 448.0
+        k8, v8 = (kc.float() / kd).to(f8), (vc.float() / vd).to(f8)
+        kd, vd = kd.reshape(1), vd.reshape(1)
     q = randn(g, len(lens), sq, h, 128, dtype=qdtype)
     k_deq, v_deq = k8.float() * kd, v8.float() * vd
     ref32, ref_lse = O.paged_decode_ref(q, k_deq, v_deq, sl, bt, out_dtype=torch.float32)
@@ -343,7 +349,8 @@ def test_fp8_kv_cache_under_16bit_queries(fa, qdtype, sq):
         k_raw = k8.cuda().permute(0, 2, 1, 3).contiguous().view(torch.uint8)       # (blocks, h_k, page, d) bytes
         v_raw = v8.cuda().permute(0, 2, 1, 3).contiguous().view(torch.uint8)
         o2 = flash_attn.vllm_flash_attn_with_kvcache(q.cuda(), k_raw, v_raw, cache_seqlens=sl.cuda(), block_table=bt.cuda(),
-                                                     causal=True, k_scale=kd.cuda(), v_scale=vd.cuda(), kv_cache_dtype="fp8",
+                                                     causal=True, k_scale=kd.cuda(), v_scale=vd.cuda(),
+                                                     kv_cache_dtype="fp8" if f8 == torch.float8_e4m3fn else "fp8_e5m2",
                                                      layout=1)
         torch.cuda.synchronize()
         assert_close_to_oracle(o2.cpu(), ref32, ref_pt, mult=3.0, eps=2 ** -8, what="fp8 kv cache, vllm entry")
