@@ -726,7 +726,12 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     else if (!strcmp(ov, "dense") && !one_tile_only) which = 2;
   }
   if (which != 0) {   // the persistent kernels claim their work items from a counter
-    k.work_counter = next_work_counter(stream);
+    if (p->work_counter) {   // the caller's own counter
+      if (cudaMemsetAsync(p->work_counter, 0, sizeof(int), stream) != cudaSuccess) return cuda_fail("work counter", cudaGetLastError());
+      k.work_counter = p->work_counter;
+    } else {
+      k.work_counter = next_work_counter(stream);
+    }
     if (!k.work_counter) return cuda_fail("work counter", cudaGetLastError());
   }
   if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);

@@ -57,7 +57,7 @@ class FwdParams(ctypes.Structure):
         ("page_size", _c_i32), ("num_blocks", _c_i32),
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
         ("has_window", _c_i32), ("window_left", _c_i32), ("window_right", _c_i32),
-        ("column_count", _c_vp), ("d_v", _c_i32), ("v_transposed", _c_i32),
+        ("column_count", _c_vp), ("d_v", _c_i32), ("v_transposed", _c_i32), ("work_counter", _c_vp),
     ]
 
 
@@ -175,6 +175,16 @@ def set_profile_events(start: Optional["torch.cuda.Event"], stop: Optional["torc
     right before and right after its main kernel, so the dominant kernel can be timed alone."""
     global _profile_events
     _profile_events = None if start is None else (start, stop)
+
+
+def _own_work_counter(p, device):
+    """Under stream capture every captured prefill call gets a work counter of its own (graph-private memory), so that a
+    replay cannot meet another launch on the library's shared counters; kept alive by the returned tensor."""
+    if torch.cuda.is_current_stream_capturing():
+        c = torch.empty(1, dtype=torch.int32, device=device)
+        p.work_counter = c.data_ptr()
+        return c
+    return None
 
 
 def _apply_profile_events(p):
@@ -355,6 +365,7 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     _set_window(p, window_size_left, window_size_right)
     _apply_profile_events(p)
     with torch.cuda.device(q.device):
+        _counter = _own_work_counter(p, q.device)
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "fwd")
     rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
     s_dmask = torch.empty((0,), dtype=q.dtype, device=q.device)
@@ -433,6 +444,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     _set_window(p, window_size_left, window_size_right)
     _apply_profile_events(p)
     with torch.cuda.device(q.device):
+        _counter = _own_work_counter(p, q.device)
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "varlen_fwd")
     rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
     s_dmask = torch.empty((0,), dtype=q.dtype, device=q.device)

@@ -130,6 +130,11 @@ typedef struct fa_b200_fwd_params {
    * which the K strides express).  With v_transposed != 0, v_row_stride is the stride between consecutive d rows.
    * Needs block_table; F16 / BF16, d = 128, page_size a multiple of 64. */
   int32_t v_transposed;
+  /* Optional int32 in device memory, owned by the caller for the duration of the kernel: the persistent prefill kernels
+   * hand out their work items from it (the call zeroes it on the stream first).  NULL = one of 64 counters inside the
+   * library, taken in turn: safe for launches that are ordered on one stream or fewer than 64 in flight.  A caller that
+   * replays a captured launch while other launches run on other streams should give each captured call its own counter. */
+  int32_t* work_counter;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch
