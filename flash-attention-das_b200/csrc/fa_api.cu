@@ -747,6 +747,55 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
 int fa_b200_fwd(const fa_b200_fwd_params* p, void* stream) { return fwd_common(p, stream, false); }
 int fa_b200_fwd_sparse(const fa_b200_fwd_params* p, void* stream) { return fwd_common(p, stream, true); }
 
+int fa_b200_block_pool(const void* x, int32_t dtype, int64_t batch_stride, int64_t head_stride, int64_t row_stride,
+                       int32_t b, int32_t h, int32_t n, int32_t d, int32_t block_rows, const float* sim_threshold,
+                       void* pooled, uint8_t* sim, void* stream) {
+  if (dtype != FA_B200_F16 && dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
+  if (d != 64 && d != 128 && d != 256) return FA_B200_ERR_HEADDIM;
+  if (b < 0 || h <= 0 || n < 0 || block_rows <= 0 || block_rows > 128) return FA_B200_ERR_SHAPE;
+  if (b == 0 || n == 0) return FA_B200_OK;
+  if (!x || !sim_threshold || !pooled || !sim) return FA_B200_ERR_NULL;
+  const int piece = d / 32 * 2;   // bytes one lane loads
+  if (reinterpret_cast<uintptr_t>(x) % piece != 0 || (batch_stride * 2) % piece != 0 || (head_stride * 2) % piece != 0 ||
+      (row_stride * 2) % piece != 0)
+    return FA_B200_ERR_STRIDE;
+  BlockPoolParams k{};
+  k.x = x; k.batch_stride = batch_stride; k.head_stride = head_stride; k.row_stride = row_stride;
+  k.b = b; k.h = h; k.n = n; k.d = d; k.dtype = dtype;
+  k.block_rows = block_rows; k.num_blocks = (n + block_rows - 1) / block_rows;
+  k.sim_threshold = sim_threshold; k.pooled = pooled; k.sim = sim;
+  cudaError_t e = launch_block_pool(k, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("block pool launch", e);
+  g_launches++;
+  return FA_B200_OK;
+}
+
+int fa_b200_block_select(const void* pooled_q, const void* pooled_k, const uint8_t* sim_q, const uint8_t* sim_k,
+                         int32_t dtype, int32_t b, int32_t h, int32_t nq, int32_t nk, int32_t d, int32_t block_q,
+                         int32_t block_k, float scale, const float* cdf_threshold, const float* topk, int32_t is_causal,
+                         int32_t attention_sink, uint8_t* block_map, void* stream) {
+  if (dtype != FA_B200_F16 && dtype != FA_B200_BF16) return FA_B200_ERR_DTYPE;
+  if (d <= 0 || d > 256) return FA_B200_ERR_HEADDIM;
+  if (b < 0 || h <= 0 || nq < 0 || nk < 0 || block_q <= 0 || block_k <= 0) return FA_B200_ERR_SHAPE;
+  if (nk > block_select_max_key_blocks()) return FA_B200_ERR_TOO_LARGE;
+  if ((cdf_threshold == nullptr) == (topk == nullptr)) return FA_B200_ERR_UNSUPPORTED;   // exactly one of the two
+  if (b == 0 || nq == 0 || nk == 0) return FA_B200_OK;
+  if (!pooled_q || !pooled_k || !sim_q || !sim_k || !block_map) return FA_B200_ERR_NULL;
+  BlockSelectParams k{};
+  k.pooled_q = pooled_q; k.pooled_k = pooled_k; k.sim_q = sim_q; k.sim_k = sim_k;
+  k.dtype = dtype; k.b = b; k.h = h; k.nq = nq; k.nk = nk; k.d = d;
+  k.nk_pow2 = 2;
+  while (k.nk_pow2 < nk) k.nk_pow2 *= 2;
+  k.block_q = block_q; k.block_k = block_k; k.scale = scale;
+  k.cdf_threshold = cdf_threshold; k.topk = topk;
+  k.is_causal = is_causal ? 1 : 0; k.attention_sink = attention_sink ? 1 : 0;
+  k.block_map = block_map;
+  cudaError_t e = launch_block_select(k, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("block select launch", e);
+  g_launches++;
+  return FA_B200_OK;
+}
+
 namespace {
 // The decode parameters of the raw-pointer entry (sizes only for the workspace query).
 fa_b200_decode_params raw_decode_params(int32_t num_query, int32_t num_q_head, int32_t num_kv_head, int32_t num_dim,

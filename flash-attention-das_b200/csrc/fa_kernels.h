@@ -155,4 +155,31 @@ cudaError_t launch_move_rows(const void* src, const int64_t* indices, void* dst,
 cudaError_t launch_block_map(const uint8_t* map, int32_t* offset, int32_t* count, int64_t rows, int k, int scale, int fill,
                              cudaStream_t stream);
 
+// Mean-similarity choice of key tiles (fa_block_select.cu).
+struct BlockPoolParams {
+  const void* x;             // (b, h, n, d) 16-bit, strides in elements, last dim contiguous
+  int64_t batch_stride, head_stride, row_stride;
+  int32_t b, h, n, d, dtype;
+  int32_t block_rows, num_blocks;
+  const float* sim_threshold;   // (h)
+  void* pooled;              // (b, h, num_blocks, d), element type of x
+  uint8_t* sim;              // (b, h, num_blocks)
+};
+struct BlockSelectParams {
+  const void* pooled_q;      // (b, h, nq, d)
+  const void* pooled_k;      // (b, h, nk, d)
+  const uint8_t* sim_q;      // (b, h, nq)
+  const uint8_t* sim_k;      // (b, h, nk)
+  int32_t dtype, b, h, nq, nk, nk_pow2, d;
+  int32_t block_q, block_k;  // rows per query / key block (causal mask between blocks)
+  float scale;
+  const float* cdf_threshold;   // (h), or
+  const float* topk;            // (h): fraction of the key blocks to keep
+  int32_t is_causal, attention_sink;
+  uint8_t* block_map;        // (b, h, nq, nk)
+};
+int block_select_max_key_blocks();
+cudaError_t launch_block_pool(const BlockPoolParams& p, cudaStream_t stream);
+cudaError_t launch_block_select(const BlockSelectParams& p, cudaStream_t stream);
+
 }  // namespace fa

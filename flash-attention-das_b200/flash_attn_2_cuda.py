@@ -149,6 +149,10 @@ _lib.fa_b200_scatter_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_i64, _c_i64, _c_i6
 _lib.fa_b200_scatter_rows.restype = ctypes.c_int
 _lib.fa_b200_block_map_to_offset.argtypes = [_c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_vp]
 _lib.fa_b200_block_map_to_offset.restype = ctypes.c_int
+_lib.fa_b200_block_pool.argtypes = [_c_vp, _c_i32, _c_i64, _c_i64, _c_i64] + [_c_i32] * 5 + [_c_vp, _c_vp, _c_vp, _c_vp]
+_lib.fa_b200_block_pool.restype = ctypes.c_int
+_lib.fa_b200_block_select.argtypes = ([_c_vp] * 4 + [_c_i32] * 8 + [_c_f32, _c_vp, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp])
+_lib.fa_b200_block_select.restype = ctypes.c_int
 _lib.fa_b200_kv_cache_attention.argtypes = ([_c_vp, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp] + [_c_i32] * 9 +
                                             [_c_vp, ctypes.c_size_t, _c_vp])
 _lib.fa_b200_kv_cache_attention.restype = ctypes.c_int
@@ -878,3 +882,41 @@ def block_map_to_offset(block_map, scale=1, fill=10000000):
         _check(_lib.fa_b200_block_map_to_offset(bm.data_ptr(), off.data_ptr(), cnt.data_ptr(), rows, k, scale, fill, _stream(bm)),
                "block_map_to_offset")
     return off, cnt
+
+
+def block_pool(x, block_rows, sim_threshold):
+    """x (B, H, N, D) fp16 / bf16 (last dim contiguous) -> (pooled (B, H, nb, D) of x's dtype: the mean row of every
+    block of ``block_rows`` rows; sim (B, H, nb) bool: the block's rows are similar to one another, mean pairwise cosine
+    similarity > sim_threshold[head]).  sim_threshold: fp32 (H) on the device."""
+    _require(x.is_cuda and x.dim() == 4 and x.dtype in (torch.float16, torch.bfloat16) and x.stride(-1) == 1,
+             "x must be a (B, H, N, D) fp16 / bf16 CUDA tensor with contiguous last dimension")
+    _require(sim_threshold.is_cuda and sim_threshold.dtype == torch.float32 and sim_threshold.numel() == x.shape[1],
+             "sim_threshold must be a float32 CUDA tensor with one element per head")
+    B, H, N, D = x.shape
+    nb = (N + block_rows - 1) // block_rows
+    pooled = torch.empty((B, H, nb, D), dtype=x.dtype, device=x.device)
+    sim = torch.empty((B, H, nb), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(_lib.fa_b200_block_pool(x.data_ptr(), _DT[x.dtype], x.stride(0), x.stride(1), x.stride(2), B, H, N, D,
+                                       block_rows, sim_threshold.data_ptr(), pooled.data_ptr(), sim.data_ptr(), _stream(x)),
+               "block_pool")
+    return pooled, sim.view(torch.bool)
+
+
+def block_select(pooled_q, pooled_k, sim_q, sim_k, block_q, block_k, scale, cdf_threshold=None, topk=None,
+                 is_causal=False, attention_sink=False):
+    """The key blocks every query block keeps: (B, H, nq, nk) bool.  cdf_threshold or topk: fp32 (H) on the device."""
+    _require((cdf_threshold is None) != (topk is None), "Only one of cdfthreshd and topk can be set.")
+    B, H, nq, D = pooled_q.shape
+    nk = pooled_k.shape[2]
+    for t in (pooled_q, pooled_k, sim_q, sim_k):
+        _require(t.is_cuda and t.is_contiguous(), "block_select takes contiguous CUDA tensors")
+    hyper = cdf_threshold if cdf_threshold is not None else topk
+    _require(hyper.is_cuda and hyper.dtype == torch.float32 and hyper.numel() == H, "one float32 threshold per head")
+    block_map = torch.empty((B, H, nq, nk), dtype=torch.uint8, device=pooled_q.device)
+    with torch.cuda.device(pooled_q.device):
+        _check(_lib.fa_b200_block_select(
+            pooled_q.data_ptr(), pooled_k.data_ptr(), sim_q.data_ptr(), sim_k.data_ptr(), _DT[pooled_q.dtype], B, H, nq, nk,
+            D, block_q, block_k, float(scale), _ptr(cdf_threshold), _ptr(topk), 1 if is_causal else 0,
+            1 if attention_sink else 0, block_map.data_ptr(), _stream(pooled_q)), "block_select")
+    return block_map.view(torch.bool)

@@ -408,6 +408,31 @@ FA_B200_API int fa_b200_abi_version(void);
 /* Number of kernels this library has launched in this process (for launch accounting). */
 FA_B200_API uint64_t fa_b200_launch_count(void);
 
+/*
+ * Choice of the key tiles for fa_b200_fwd_sparse from the queries and keys themselves (the reference's
+ * get_block_map_meansim, flash_attn/utils/sparse_utils.py:376-441), two launches:
+ *
+ * fa_b200_block_pool: x (b, h, n, d) F16 / BF16 (strides in elements, last dim contiguous, d = 64, 128 or 256) in blocks
+ * of block_rows (<= 128) rows -> pooled (b, h, nb, d), the mean row of every block in the type of x, and sim (b, h, nb),
+ * 1 where the mean cosine similarity over all pairs of rows of the block exceeds sim_threshold[head] (fp32 (h));
+ * nb = ceil(n / block_rows); a block cut short by the end of the sequence is 0 (sparse_utils.py:281-299).
+ *
+ * fa_b200_block_select: block_map (b, h, nq, nk) uint8.  Per query block: softmax over the key blocks of
+ * pooled_q . pooled_k * scale (key blocks with sim_k = 0 and, if is_causal, blocks that start at or after row
+ * (qi + 1) * block_q: excluded), sorted descending; kept are the first #{cumulative sum <= cdf_threshold[head]} blocks
+ * (or topk[head] * nk of them if topk is given; at least one), every key block with sim_k = 0, all of them where
+ * sim_q = 0; then the causal mask again and, with attention_sink, key block 0.  fp32 arithmetic throughout.
+ * nk <= 4096.  fa_b200_block_map_to_offset turns the map into the lists of fa_b200_fwd_sparse.
+ */
+FA_B200_API int fa_b200_block_pool(const void* x, int32_t dtype, int64_t batch_stride, int64_t head_stride,
+                                   int64_t row_stride, int32_t b, int32_t h, int32_t n, int32_t d, int32_t block_rows,
+                                   const float* sim_threshold, void* pooled, uint8_t* sim, void* stream);
+FA_B200_API int fa_b200_block_select(const void* pooled_q, const void* pooled_k, const uint8_t* sim_q,
+                                     const uint8_t* sim_k, int32_t dtype, int32_t b, int32_t h, int32_t nq, int32_t nk,
+                                     int32_t d, int32_t block_q, int32_t block_k, float scale,
+                                     const float* cdf_threshold, const float* topk, int32_t is_causal,
+                                     int32_t attention_sink, uint8_t* block_map, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,6 +27,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 from oracle import attention_oracle as O  # noqa: E402
 from oracle import padding_oracle as PO  # noqa: E402
+from oracle import block_select_oracle as BS  # noqa: E402
 
 REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FA_REFERENCE_ROOT", "")
 
@@ -130,7 +131,43 @@ def gen_inputs(case):
         angle = torch.rand(ro, rd // 2, generator=g) * 2 * math.pi
         off = torch.randint(0, ro - sq + 1, (b,), generator=g).to(torch.int32)
         return x, torch.cos(angle).to(dt), torch.sin(angle).to(dt), off
+    if kind == "block_select":
+        # q, k (B, H, N, D) fp32: noise around one direction per head, so that most blocks are self-similar
+        shape = (case["b"], case["h"], case["n"], case["d"])
+        q = torch.randn(*shape, generator=g) * case["noise"] + torch.randn(case["b"], case["h"], 1, case["d"], generator=g)
+        k = torch.randn(*shape, generator=g) * case["noise"] + torch.randn(case["b"], case["h"], 1, case["d"], generator=g)
+        return q, k
     raise ValueError(kind)
+
+
+def _reference_block_selection(ref_root):
+    """The reference's get_block_map_meansim (flash_attn/utils/sparse_utils.py:376-441) made runnable on the CPU: the
+    module is loaded by path and its three Triton launches are replaced by torch statements of the same kernels
+    (pooling / self-similarity :281-299 -> oracle.pool_sim_ref; map fill :336-347; causal block mask :359-366).  The
+    torch chain between them (scores, masking, softmax, sort, cumsum, searchsorted, final map) is the reference's own."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ref_sparse_utils", os.path.join(ref_root, "flash_attn", "utils", "sparse_utils.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    def pool(x, bs, th):
+        pooled, sim, _ = BS.pool_sim_ref(x, bs, th.float())
+        return pooled, sim
+
+    def fill(final_map, num_to_select, sorted_indices):
+        n = torch.where(num_to_select == 0, num_to_select + 1, num_to_select)
+        sel = torch.arange(final_map.shape[-1]).view(1, 1, 1, -1) < n.unsqueeze(-1)
+        final_map.scatter_(-1, sorted_indices, final_map.gather(-1, sorted_indices) | sel)
+        return final_map
+
+    def causal(mask, ratio):
+        qi = torch.arange(mask.shape[0]).view(-1, 1)
+        kj = torch.arange(mask.shape[1]).view(1, -1)
+        mask.copy_(~(kj >= (qi + 1) * ratio))
+        return mask
+
+    mod.get_pool_sim_triton_simmean, mod.fill_block_map_triton, mod.fill_causal_mask_triton = pool, fill, causal
+    return mod.get_block_map_meansim
 
 
 CASES = [
@@ -151,6 +188,10 @@ CASES = [
     dict(name="window_bf16_noncausal_asym", kind="sink", seed=16, dtype="bfloat16", b=1, sq=64, sk=200, h=4, hk=1, d=128, causal=False, window=(30, 9), sink_scale=0.0),
     dict(name="unpad_bool_ragged", kind="unpad", seed=17, dtype="bfloat16", b=5, s=37, feat=(3, 8), mask_dtype="bool", p_keep=0.6),
     dict(name="unpad_int64_with_empty_row", kind="unpad", seed=18, dtype="float16", b=4, s=300, feat=(16,), mask_dtype="int64", p_keep=0.3),
+    dict(name="block_select_cdf", kind="block_select", dtype="float32", seed=19, b=2, h=3, n=900, d=128, noise=0.3, causal=False, args=dict(cdfthreshd=0.9)),
+    dict(name="block_select_cdf_causal_sink", kind="block_select", dtype="float32", seed=20, b=1, h=4, n=1100, d=128, noise=0.3, causal=True, args=dict(cdfthreshd=0.5, attention_sink=True)),
+    dict(name="block_select_topk_causal", kind="block_select", dtype="float32", seed=21, b=1, h=2, n=1024, d=64, noise=0.5, causal=True, args=dict(cdfthreshd=None, topk=0.3)),
+    dict(name="block_select_dissimilar_blocks", kind="block_select", dtype="float32", seed=24, b=1, h=2, n=640, d=128, noise=1.0, causal=False, args=dict(cdfthreshd=0.7, simthreshd1=torch.tensor([0.505, 0.1]))),
     dict(name="rotary_bf16_halves", kind="rotary", seed=11, dtype="bfloat16", b=2, sq=5, h=3, d=128, rotary_dim=128, seqlen_ro=64, interleaved=False),
     dict(name="rotary_fp16_interleaved_partial", kind="rotary", seed=12, dtype="float16", b=3, sq=1, h=4, d=128, rotary_dim=32, seqlen_ro=40, interleaved=True),
     dict(name="rotary_bf16_halves_partial", kind="rotary", seed=13, dtype="bfloat16", b=2, sq=7, h=2, d=128, rotary_dim=64, seqlen_ro=33, interleaved=False),
@@ -179,6 +220,7 @@ def main():
     rotary_py = os.path.join(REF, "flash_attn", "layers", "rotary.py")
     _function_from_source(rotary_py, "rotate_half", rglob)
     ref_rotary = _function_from_source(rotary_py, "apply_rotary_emb_torch", rglob)
+    ref_block_select = _reference_block_selection(REF)
 
     golden = {"torch_version": torch.__version__, "cases": []}
     for case in CASES:
@@ -268,6 +310,12 @@ def main():
             assert torch.equal(m_xs, xs) and torch.equal(m_idx, idx) and torch.equal(m_cu, cu) and m_mx == mx, case["name"]
             assert torch.equal(PO.pad_input_ref(xs, idx, case["b"], case["s"]), back), case["name"]
             rec.update(indices=idx, cu_seqlens=cu, max_seqlen=mx, unpadded=xs, repadded=back)
+        elif kind == "block_select":
+            q, k = gen_inputs(case)
+            final = ref_block_select(q, k, is_causal=case["causal"], **case["args"]).bool()
+            mine, margin = BS.block_map_meansim_ref(q, k, is_causal=case["causal"], **case["args"])
+            assert torch.equal(mine, final), case["name"]
+            rec.update(block_map=final, min_margin=float(margin.min()))
         elif kind == "rotary":
             x, cos, sin, off = gen_inputs(case)
             sq = case["sq"]

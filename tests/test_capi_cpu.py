@@ -128,3 +128,17 @@ def test_raw_pointer_entry_validates_before_touching_anything(binding):
     d.b, d.h, d.h_k, d.page_size, d.max_blocks_per_seq, d.max_seqlen_k = 64, 32, 8, 256, 128, 32768
     assert (lib.fa_b200_kv_cache_attention_workspace_bytes(64, 32, 8, 128, 256, 32768) ==
             lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) > 0)
+
+
+def test_block_selection_entries_validate(binding):
+    lib = binding.lib()
+    assert lib.fa_b200_block_pool(None, 2, 0, 0, 0, 1, 1, 128, 128, 64, None, None, None, None) == 2      # e4m3
+    assert lib.fa_b200_block_pool(None, 1, 0, 0, 0, 1, 1, 128, 96, 64, None, None, None, None) == 3       # head dim
+    assert lib.fa_b200_block_pool(None, 1, 0, 0, 0, 1, 1, 128, 128, 256, None, None, None, None) == 6     # block too tall
+    assert lib.fa_b200_block_pool(None, 1, 0, 0, 0, 0, 1, 128, 128, 64, None, None, None, None) == 0      # empty batch
+    assert lib.fa_b200_block_pool(None, 1, 0, 0, 0, 1, 1, 128, 128, 64, None, None, None, None) == 1      # null pointers
+    sel = lambda nk=8, cdf=None, topk=None: lib.fa_b200_block_select(None, None, None, None, 1, 1, 1, 4, nk, 128, 128, 64,
+                                                                      ctypes.c_float(0.1), cdf, topk, 0, 0, None, None)
+    assert sel() == 9                      # neither a cdf threshold nor a top-k fraction
+    assert sel(nk=5000, cdf=1) == 13       # more key blocks than the in-kernel sort takes
+    assert sel(cdf=1) == 1                 # null pointers

@@ -86,6 +86,19 @@ def test_unpad_bit_exact(golden):
         assert torch.equal(PO.pad_input_ref(xs, idx, c["b"], c["s"]), c["repadded"]), c["name"]
 
 
+def test_block_selection_matches_the_reference_chain(golden):
+    """oracle.block_map_meansim_ref against maps made by the reference's own get_block_map_meansim (its torch chain run
+    on the CPU in fp32, its three Triton launches replaced by torch statements; tests/golden/make_golden.py)."""
+    from oracle import block_select_oracle as BS
+    cases = _cases(golden, "block_select")
+    assert len(cases) >= 4
+    for c in cases:
+        q, k = gen_inputs(c)
+        mine, margin = BS.block_map_meansim_ref(q, k, is_causal=c["causal"], **c["args"])
+        assert torch.equal(mine, c["block_map"]), c["name"]
+        assert 0.05 < mine.float().mean() < 0.98, c["name"]     # neither empty nor dense: the choice is exercised
+
+
 def test_block_map_known_answer():
     """The worked example of the reference's docstring (flash_attn/utils/sparse_utils.py:537-541)."""
     bm = torch.tensor([[[[0, 0, 1, 0, 0, 1, 0, 1, 0, 1]]]], dtype=torch.bool)
