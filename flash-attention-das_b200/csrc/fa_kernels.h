@@ -18,8 +18,8 @@ struct DecodeKernelParams {
   const float* q_descale;
   const float* k_descale;
   const float* v_descale;
-  float* o_partial;    // [partition][b][h][128] fp32
-  float* lse_partial;  // [partition][b][h] fp32, natural log, -inf = no keys
+  float* o_partial;    // [partition][b][h][sq][d] fp32
+  float* lse_partial;  // [partition][b][h][sq] fp32, natural log, -inf = no keys
   int64_t q_batch_stride, q_head_stride, q_row_stride;
   int64_t o_batch_stride, o_head_stride, o_row_stride;
   int64_t bt_stride;

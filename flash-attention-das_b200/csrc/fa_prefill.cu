@@ -7,9 +7,11 @@
 //   warp 5      MMA issuer:   S = Q K_j^T and O += P V_j with tcgen05.mma, accumulators in TMEM
 //   warps 6-7   idle: they complete the second warpgroup, which hands its registers to the softmax warpgroup
 //               (setmaxnreg: 40 / 216 per thread; a row of 128 scores is live in registers at once)
-// This kernel serves block-sparse lists (per-head tile lists cannot share K/V tiles between heads) and head
-// layouts without an even GQA group; dense GQA prefill runs on the two-tile persistent kernel
-// (fa_prefill_pair.cu).  Every mbarrier wait is bounded; a CTA that gives up raises the device status word and
+// This kernel serves block-sparse lists (per-head tile lists cannot share K/V tiles between heads), K/V read through
+// a block table (pages in the bshd / bhsd layouts, or with V stored transposed), and the head dimensions other than
+// 128 (64, 192, 256, and 192 with 128 for v: fp16 / bf16; above 128 one CTA per SM, 512 TMEM columns); dense GQA
+// prefill at d = 128 runs on the two-tile persistent kernel (fa_prefill_pair.cu), other head layouts on
+// fa_prefill_dense.cu.  Every mbarrier wait is bounded; a CTA that gives up raises the device status word and
 // leaves through the common teardown, so TMEM is always released.
 //
 // Computes what the reference's dense forward computes

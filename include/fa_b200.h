@@ -55,6 +55,7 @@ enum {
  * Mirrors the fields of Flash_fwd_params that the forward path reads
  * (csrc/flash_attn_cutlass/src/flash.h:52-206): pointers, batch/row/head strides in ELEMENTS,
  * b, h, h_k, seqlen_q/k, d, total_q, cu_seqlens, scale, descale pointers and strides, is_causal.
+ * d = 128 for every element type; 64, 192 and 256 for F16 / BF16 (see also d_v).
  *
  * Fixed length: cu_seqlens_q == cu_seqlens_k == NULL; q is (b, seqlen_q, h, d), k/v (b, seqlen_k, h_k, d);
  *               softmax_lse is (b, h, seqlen_q) fp32.
@@ -148,8 +149,9 @@ FA_B200_API int fa_b200_fwd(const fa_b200_fwd_params* p, void* stream);
 FA_B200_API int fa_b200_fwd_sparse(const fa_b200_fwd_params* p, void* stream);
 
 /*
- * Paged-KV decode (one query token per sequence, GQA group packed into one query tile), split-KV
- * over fixed-size token partitions plus an LSE-combine kernel.
+ * Paged-KV decode (one query token per sequence, or a few: seqlen_q; GQA group packed into one query tile), split-KV
+ * over fixed-size token partitions plus an LSE-combine kernel.  d = 128; 64, 192 and 256 for F16 / BF16 caches in the
+ * plain layout.
  * k_cache / v_cache: (num_blocks, page_size, h_k, d); block_table: int32 (b, max_blocks_per_seq);
  * cache_seqlens: int32 (b).  Physical page of token t of sequence s is
  * block_table[s * block_table_batch_stride + t / page_size], row t % page_size
