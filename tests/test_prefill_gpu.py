@@ -446,3 +446,30 @@ def test_paged_prefill_over_transposed_v_pool(fa, page, dtype):
         ref32, _ = O.attention_ref(qd[i][None], ki, vi, causal=True, out_dtype=torch.float32)
         ref_pt, _ = O.attention_ref(qd[i][None], ki, vi, causal=True, upcast=False, reorder_ops=True)
         assert_close_to_oracle(o2[i].cpu()[None], ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"kvcache transposed V seq {i}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kernel", ["pair", "dense", "single"])
+def test_scores_that_outgrow_the_running_maximum(fa, monkeypatch, dtype, kernel):
+    """Keys whose scores grow by hundreds of log2 units from one key tile to the next (and rows whose first tiles are
+    fully masked by a window): every tile forces the rescale of O and of the row sum, down to a factor of zero."""
+    flash_attn, cuda = fa
+    monkeypatch.setenv("FA_B200_PREFILL_KERNEL", kernel)
+    g = gen(60)
+    b, s, h, h_k = 1, 1024, 4, 2
+    q = randn(g, b, s, h, 128, dtype=dtype)
+    k = randn(g, b, s, h_k, 128, dtype=dtype)
+    v = randn(g, b, s, h_k, 128, dtype=dtype)
+    # key tile t is scaled by 4^t / 16: the largest scores of successive tiles are hundreds of log2 units apart
+    ramp = (4.0 ** (torch.arange(s) // 128).float() / 16).view(1, s, 1, 1)
+    k = (k.float() * ramp).to(dtype)
+    for causal, window in ((False, (-1, -1)), (True, (-1, -1)), (False, (200, 300))):
+        out, lse, _ = flash_attn.flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=causal, window_size=window,
+                                                 return_attn_probs=True)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        ref32, ref_lse = O.attention_ref(q, k, v, causal=causal, window_size=window, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(q, k, v, causal=causal, window_size=window, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"{kernel} causal={causal} window={window}")
+        fin = torch.isfinite(ref_lse)
+        assert (lse.cpu()[fin] - ref_lse[fin]).abs().max() < 1e-3 * max(1.0, ref_lse[fin].abs().max().item())
