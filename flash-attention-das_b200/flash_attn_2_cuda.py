@@ -335,10 +335,12 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     _require(b > 0, "batch size must be positive")
     _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
     _require(tuple(k.shape) == (b, sk, h_k, d) and tuple(v.shape) == (b, sk, h_k, dv), "k/v shape mismatch")
-    # window normalisation as in mha_fwd (flash_api.cpp:1055-1060)
+    # window normalisation as in mha_fwd (flash_api.cpp:1055-1060), except that a right bound is dropped only where it
+    # cannot hide a key: with more queries than keys, bottom-right alignment puts the first rows' windows before key 0
+    # (construct_local_mask, tests/test_flash_attn.py:185-217), however wide the bound
     if window_size_left >= sk:
         window_size_left = -1
-    if window_size_right >= sk:
+    if window_size_right >= max(sk, sq):
         window_size_right = -1
     if sq == 1 and alibi_slopes_ is None:
         is_causal = False
@@ -405,7 +407,7 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
     if window_size_left >= max_seqlen_k:
         window_size_left = -1
-    if window_size_right >= max_seqlen_k:
+    if window_size_right >= max(max_seqlen_k, max_seqlen_q):   # see fwd: a right bound can matter when sq > sk
         window_size_right = -1
     if max_seqlen_q == 1 and alibi_slopes_ is None:
         is_causal = False
