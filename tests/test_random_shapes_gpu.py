@@ -167,3 +167,127 @@ def test_random_paged(fa, seed):
         ref_pt, _ = O.attention_ref(qs[i][None], ki, vi, causal=eff_causal, window_size=win, s_aux=s_aux, upcast=False,
                                     reorder_ops=True)
         assert_close_to_oracle(outs[i][None], ref32, ref_pt, mult=3.0, eps=1e-5 + 2 ** -8, what=f"{what0} seq {i}")
+
+
+def _quant(x, per_head, b, h_k, rng):
+    """e4m3 tensor + descale: one element, or (batch, kv heads) filled with one value (a per-tensor scale in the
+    (b, h_k) form the reference passes, src/flash.h:105-113)."""
+    x8, ds = O.quantize_e4m3_per_tensor(x)
+    return x8, (ds.expand(b, h_k).contiguous() if per_head else ds)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_fp8(fa, seed):
+    """e4m3 q / k / v with fp32 descales: varlen prefill, paged decode and the e4m3 / e5m2 cache under 16-bit queries.
+    Rule: error <= 2 x the error of the same math with P round-tripped through e4m3, cosine difference < 1e-3
+    (tests/test_flash_attn_varlen_fp8.py:477-484, 521-694)."""
+    from _util import cos_diff
+    flash_attn, cuda = fa
+    rng = random.Random(3000 + seed)
+    g = gen(3000 + seed)
+    h, h_k = _heads(rng, max_group=8)
+    per_head = rng.random() < 0.5
+    mode = seed % 3
+    if mode == 0:
+        n = rng.randint(1, 4)
+        lens = [max(1, _len(rng, 700)) for _ in range(n)]
+        total = sum(lens)
+        causal = rng.random() < 0.6
+        q8, qd = _quant(randn(g, total, h, 128), per_head, n, h_k, rng)
+        k8, kd = _quant(randn(g, total, h_k, 128), per_head, n, h_k, rng)
+        v8, vd = _quant(randn(g, total, h_k, 128), per_head, n, h_k, rng)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+        out = flash_attn.flash_attn_varlen_func(q8.cuda(), k8.cuda(), v8.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens),
+                                                causal=causal, q_descale=qd.cuda(), k_descale=kd.cuda(), v_descale=vd.cuda())
+        torch.cuda.synchronize()
+        kw = dict(q_descale=qd.expand(n, h_k), k_descale=kd.expand(n, h_k), v_descale=vd.expand(n, h_k))
+        ref32, _ = O.attention_varlen_ref(q8, k8, v8, cu, cu, causal=causal, out_dtype=torch.float32, **kw)
+        ref_p8, _ = O.attention_varlen_ref(q8, k8, v8, cu, cu, causal=causal, out_dtype=torch.float32,
+                                           intermediate_dtype=torch.float8_e4m3fn, **kw)
+        what = f"fp8 varlen {lens} h{h}/{h_k} causal={causal}"
+    else:
+        n = rng.randint(1, 4)
+        page = rng.choice([16, 64, 256])
+        lens = [max(1, _len(rng, 3000)) for _ in range(n)]
+        kc, vc, bt, sl = make_paged(g, lens, h_k, page, torch.bfloat16, poison=False)
+        q16 = randn(g, n, 1, h, 128)
+        f8 = torch.float8_e4m3fn if (mode == 1 or rng.random() < 0.5) else torch.float8_e5m2
+        if f8 == torch.float8_e4m3fn:
+            k8, kd = _quant(kc, per_head, n, h_k, rng)
+            v8, vd = _quant(vc, per_head, n, h_k, rng)
+        else:
+            kd, vd = (kc.float().abs().max() / 448.0).reshape(1), (vc.float().abs().max() / 448.0).reshape(1)
+            k8, v8 = (kc.float() / kd).to(f8), (vc.float() / vd).to(f8)
+        if mode == 1:      # everything e4m3
+            q8, qd = _quant(q16, per_head, n, h_k, rng)
+            out = flash_attn.flash_attn_with_kvcache(q8.cuda(), k8.cuda(), v8.cuda(), cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                                     q_descale=qd.cuda(), k_descale=kd.cuda(), v_descale=vd.cuda())
+            torch.cuda.synchronize()
+            kw = dict(q_descale=qd.expand(n, h_k), k_descale=kd.expand(n, h_k), v_descale=vd.expand(n, h_k))
+            ref32, _ = O.paged_decode_ref(q8, k8, v8, sl, bt, out_dtype=torch.float32, **kw)
+            what = f"fp8 decode {lens} page{page} h{h}/{h_k}"
+        else:              # 16-bit queries over an fp8 cache
+            out = flash_attn.flash_attn_with_kvcache(q16.cuda(), k8.cuda(), v8.cuda(), cache_seqlens=sl.cuda(), block_table=bt.cuda(),
+                                                     k_descale=kd.cuda(), v_descale=vd.cuda())
+            torch.cuda.synchronize()
+            k_deq = k8.float() * (kd.view(-1)[0])
+            v_deq = v8.float() * (vd.view(-1)[0])
+            ref32, _ = O.paged_decode_ref(q16, k_deq, v_deq, sl, bt, out_dtype=torch.float32)
+            what = f"{f8} cache under bf16 queries {lens} page{page} h{h}/{h_k}"
+        ref_p8 = None
+    assert cuda.device_status() == 0, what
+    e = max_err(out.cpu(), ref32)
+    if ref_p8 is not None:
+        assert e <= 2 * max_err(ref_p8, ref32) + 2 ** -7, what
+    else:
+        assert e < 2e-2, (what, e)        # decode keeps P in f16: far inside the stated atol of 7e-2 (tests/test_pa.py:108-117)
+    assert cos_diff(out.cpu(), ref32) < 1e-3, what
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_append_rotary_layouts(fa, seed):
+    """New keys / values appended to the paged cache with rotary embedding, in the bshd or bhsd pool layout, then the
+    attention over the updated cache: cache contents bit-exact, outputs by the reference's rule."""
+    import math
+    flash_attn, cuda = fa
+    rng = random.Random(4000 + seed)
+    g = gen(4000 + seed)
+    dtype = rng.choice([torch.bfloat16, torch.float16])
+    h, h_k = _heads(rng, max_group=4)
+    page = rng.choice([16, 32, 64, 256])
+    n = rng.randint(1, 4)
+    s_new = rng.choice([1, 1, 2, 5, 33])
+    lens = [_len(rng, 900) for _ in range(n)]
+    kc, vc, bt, _ = make_paged(g, [L + s_new for L in lens], h_k, page, dtype, poison=False)
+    sl = torch.tensor(lens, dtype=torch.int32)
+    q, kn, vn = randn(g, n, s_new, h, 128, dtype=dtype), randn(g, n, s_new, h_k, 128, dtype=dtype), randn(g, n, s_new, h_k, 128, dtype=dtype)
+    rotary_dim = rng.choice([0, 32, 64, 128])
+    interleaved = rng.random() < 0.5
+    cos = sin = None
+    if rotary_dim:
+        angle = torch.rand(max(lens) + s_new + 3, rotary_dim // 2, generator=g) * 2 * math.pi
+        cos, sin = torch.cos(angle).to(dtype), torch.sin(angle).to(dtype)
+    causal = rng.random() < 0.7
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    new_lens = O.kv_append_ref(kc_ref, vc_ref, bt, sl, kn, vn, cos, sin, interleaved)
+    q_ro = O.rotary_ref(q, cos, sin, sl, interleaved, per_token=causal) if rotary_dim else q
+    bhsd = rng.random() < 0.5
+    kc_d, vc_d = kc.cuda(), vc.cuda()
+    if bhsd:       # pools stored (num_blocks, h_k, page, d), handed over as strided (num_blocks, page, h_k, d) views
+        kc_d = kc_d.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+        vc_d = vc_d.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    out = flash_attn.flash_attn_with_kvcache(q.cuda(), kc_d, vc_d, k=kn.cuda(), v=vn.cuda(),
+                                             rotary_cos=None if cos is None else cos.cuda(),
+                                             rotary_sin=None if sin is None else sin.cuda(), cache_seqlens=sl.cuda(),
+                                             block_table=bt.cuda(), causal=causal, rotary_interleaved=interleaved)
+    torch.cuda.synchronize()
+    what = f"append {lens}+{s_new} page{page} h{h}/{h_k} rot{rotary_dim} il{interleaved} causal{causal} bhsd{bhsd}"
+    assert cuda.device_status() == 0, what
+    assert torch.equal(kc_d.cpu(), kc_ref) and torch.equal(vc_d.cpu(), vc_ref), what
+    for i in range(n):
+        lk = int(new_lens[i])
+        ki, vi = O.gather_paged_kv(kc_ref, bt[i], lk)[None], O.gather_paged_kv(vc_ref, bt[i], lk)[None]
+        eff = causal and s_new > 1
+        ref32, _ = O.attention_ref(q_ro[i][None], ki, vi, causal=eff, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(q_ro[i][None], ki, vi, causal=eff, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out[i].cpu()[None], ref32, ref_pt, mult=3.0, eps=1e-5 + 2 ** -8, what=f"{what} seq {i}")
