@@ -291,3 +291,41 @@ def test_random_append_rotary_layouts(fa, seed):
         ref32, _ = O.attention_ref(q_ro[i][None], ki, vi, causal=eff, out_dtype=torch.float32)
         ref_pt, _ = O.attention_ref(q_ro[i][None], ki, vi, causal=eff, upcast=False, reorder_ops=True)
         assert_close_to_oracle(out[i].cpu()[None], ref32, ref_pt, mult=3.0, eps=1e-5 + 2 ** -8, what=f"{what} seq {i}")
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_tile_lists(fa, seed):
+    """Tile lists at the granularity of the reference's metadata (64-row K tiles, any subset, rows with no tile at all),
+    sequence lengths that are not multiples of the tile sizes, both query block heights (64 up to 2048 rows, 128 above)."""
+    flash_attn, cuda = fa
+    rng = random.Random(5000 + seed)
+    g = gen(5000 + seed)
+    dtype = rng.choice([torch.bfloat16, torch.float16])
+    h, h_k = _heads(rng, max_group=4)
+    s = rng.choice([64, 100, 640, 1000, 2048, 2100, 2500])
+    b = rng.randint(1, 2)
+    causal = rng.random() < 0.6
+    block_m = O.sparse_block_m(s)
+    nq, nk = (s + block_m - 1) // block_m, (s + 63) // 64
+    keep = torch.rand(b, h, nq, nk, generator=g) < rng.choice([0.1, 0.4, 0.8])
+    if causal:          # keep the tile holding each block's diagonal, as every real selection does
+        for i in range(nq):
+            keep[:, :, i, min(nk - 1, (i * block_m) // 64)] = True
+    keep[:, :, rng.randrange(nq)] = False                 # one query block with an empty list
+    cnt, offs = O.tile_mask_to_block_lists(keep, block_m=block_m, block_n=64, tile_n=64)
+    q, k, v = randn(g, b, s, h, 128, dtype=dtype), randn(g, b, s, h_k, 128, dtype=dtype), randn(g, b, s, h_k, 128, dtype=dtype)
+    cc = torch.zeros(b, h, nq, dtype=torch.int32)
+    ci = torch.zeros(b, h, nq, 1, dtype=torch.int32)
+    out, lse = flash_attn.sparse_attn_func(q.cuda(), k.cuda(), v.cuda(), cnt.cuda(), offs.cuda(), cc.cuda(), ci.cuda(),
+                                           causal=causal, return_softmax_lse=True)
+    torch.cuda.synchronize()
+    what = f"tile lists s{s} b{b} h{h}/{h_k} causal{causal} block_m{block_m}"
+    assert cuda.device_status() == 0, what
+    mask = O.block_lists_to_dense_mask(cnt, offs, s, s, block_m)
+    ref32, ref_lse = O.attention_ref(q, k, v, causal=causal, out_dtype=torch.float32, extra_mask=mask)
+    ref_pt, _ = O.attention_ref(q, k, v, causal=causal, upcast=False, reorder_ops=True, extra_mask=mask)
+    assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=what)
+    fin = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse.cpu()), fin), what
+    if fin.any():
+        assert max_err(lse.cpu()[fin], ref_lse[fin]) < 1e-3, what
