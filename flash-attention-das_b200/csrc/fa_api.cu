@@ -718,12 +718,14 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   // double-buffered scores ("dense").  Tile lists are per head and run one tile per CTA ("single").
   // FA_B200_PREFILL_KERNEL=single|pair|dense overrides the choice where it is legal (tests, comparisons).
   const bool even_group = (p->h / p->h_k) % 2 == 0;
-  const bool one_tile_only = sparse || paged || p->d != kHeadDim;   // paged K/V, other head dimensions: one-tile kernel
+  // Tile lists, other head dimensions and transposed V pools: the one-tile kernel.  Paged K/V in the plain layouts:
+  // the two-tile kernel where the GQA group is even, else the one-tile kernel.
+  const bool one_tile_only = sparse || p->d != kHeadDim || p->v_transposed || (paged && !even_group);
   int which = one_tile_only ? 0 : (even_group ? 1 : 2);
   if (const char* ov = getenv("FA_B200_PREFILL_KERNEL")) {
     if (!strcmp(ov, "single")) which = 0;
     else if (!strcmp(ov, "pair") && !one_tile_only && even_group) which = 1;
-    else if (!strcmp(ov, "dense") && !one_tile_only) which = 2;
+    else if (!strcmp(ov, "dense") && !one_tile_only && !paged) which = 2;
   }
   if (which != 0) {   // the persistent kernels claim their work items from a counter
     if (p->work_counter) {   // the caller's own counter

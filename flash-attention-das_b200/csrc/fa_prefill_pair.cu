@@ -10,8 +10,10 @@
 //                 O_t += P_t V_j,  S_t = Q_t K_{j+1}^T
 //   warp 11       idle (completes the third warpgroup so that it can hand its registers to the softmax warps)
 // TMEM (all 512 columns): S_0, S_1, O_0, O_1 of 128 fp32 columns each; P overwrites the head of S.
-// CTAs stride over the virtual item list ordered by descending query block (for causal masks: heaviest first), so
-// prologue, Q loads and epilogue of one item overlap the main loop of its neighbours.  All mbarrier phases simply
+// CTAs claim their items from the virtual item list ordered by descending query block (for causal masks: heaviest
+// first), so prologue, Q loads and epilogue of one item overlap the main loop of its neighbours.  K/V may live in a
+// paged pool (kPaged build): the producer then fetches every key tile page piece by page piece through the block
+// table, and the softmax warpgroups clear the V rows past the end of the sequence in its last tile.  All mbarrier phases simply
 // keep counting across items.  Every wait is bounded; a CTA that gives up raises the device status word and leaves
 // through the common teardown (TMEM is always released).
 //
@@ -77,11 +79,15 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
   if (p.cu_seqlens_q) {
     it.q_row0 = p.cu_seqlens_q[it.bidb];
     sq = p.cu_seqlens_q[it.bidb + 1] - it.q_row0;
-    it.k_row0 = p.cu_seqlens_k[it.bidb];
-    it.sk = p.cu_seqlens_k[it.bidb + 1] - it.k_row0;
+    it.k_row0 = p.paged ? 0 : p.cu_seqlens_k[it.bidb];
+    it.sk = p.paged ? 0 : p.cu_seqlens_k[it.bidb + 1] - it.k_row0;
     it.coord_b = 0;
   } else {
     it.q_row0 = 0; it.k_row0 = 0; sq = p.seqlen_q; it.sk = p.seqlen_k; it.coord_b = it.bidb;
+  }
+  if (p.paged) {   // keys in a paged pool: their number comes with the block table, rows are addressed page by page
+    it.k_row0 = 0;
+    it.sk = p.seqused_k[it.bidb];
   }
   it.m0 = m_block * kBlockM;
   if (it.m0 >= sq) return false;
@@ -93,7 +99,8 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
 
 // kLeftWindow: the launch has a left sliding-window bound (kept out of the common build of the hot loop: two more live
 // values per softmax thread are enough to make it spill).
-template <int DT, bool kLeftWindow>
+// kPaged: K/V are read through a block table (its own build, so that the common one carries none of its state).
+template <int DT, bool kLeftWindow, bool kPaged>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -221,12 +228,29 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             const uint32_t slot = kv_cnt % kSlots, ph = (kv_cnt / kSlots) & 1u;
             if (!mbar_wait(smem_u32(&kv_empty[slot]), ph ^ 1u, wctx)) { ok = false; break; }
             const uint32_t bar = smem_u32(&kv_full[slot]);
-            mbar_expect_tx(bar, T::kTileBytes);
             const CUtensorMap* tm = kv ? &tmap_v : &tmap_k;
+            if constexpr (!kPaged) {
+              mbar_expect_tx(bar, T::kTileBytes);
 #pragma unroll
-            for (int hf = 0; hf < T::kHalves; ++hf)
-              tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, it.hk,
-                          it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b);
+              for (int hf = 0; hf < T::kHalves; ++hf)
+                tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, it.hk,
+                            it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b);
+            } else {
+              // the tile's 128 keys come from one or more pages: one box of box_rows rows per page piece; boxes that
+              // start past the end of the sequence are not fetched (their block_table slots are not valid)
+              const int start = (it.tile0 + j) * kBlockN;
+              const int nbox = min(kBlockN / p.box_rows, (it.sk - start + p.box_rows - 1) / p.box_rows);
+              mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * p.box_rows * 128u * T::kHalves);
+              const int32_t* bt = p.block_table + static_cast<int64_t>(it.bidb) * p.bt_stride;
+              for (int i = 0; i < nbox; ++i) {
+                const int tok = start + i * p.box_rows;
+                const int page = bt[tok / p.page_size], prow = tok % p.page_size;
+#pragma unroll
+                for (int hf = 0; hf < T::kHalves; ++hf)
+                  tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes + i * p.box_rows * 128, tm, bar, hf * 64,
+                              it.hk, prow, page);
+              }
+            }
             ++kv_cnt;
           }
         }
@@ -327,6 +351,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + t * 128;
     const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + 256 + t * 128;
     uint32_t sp_cnt = 0, item_cnt = 0;
+    [[maybe_unused]] uint32_t kv_tiles = 0;   // kPaged: key tiles this CTA has consumed so far (tile n's V is ring item 2 n + 1)
     [[maybe_unused]] int tr = 0;
     [[maybe_unused]] const bool tracer = (lane == 0 && lane_grp == 0);
 #ifdef FA_B200_PHASE_TRACE
@@ -353,9 +378,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // this row's visible keys [row_first, row_limit) and, for the warp-uniform decision whether a tile needs masking
       // at all, the smallest limit and the largest first key among the warp's rows; all relative to the first tile
       int row_first, row_limit, warp_first, warp_limit;
+      [[maybe_unused]] int sk_rel = 0;
       float scale_log2 = p.scale_log2;
       {
         const int sk = is->sk, m0 = is->m0, shift = is->causal_shift, base = is->tile0 * kBlockN;
+        if constexpr (kPaged) sk_rel = sk - base;
         row_limit = row_hi(p, m0 + row, sk, shift) - base;
         warp_limit = row_hi(p, m0 + lane_grp * 32, sk, shift) - base;
         row_first = kLeftWindow ? row_lo(p, m0 + row, shift) - base : 0;
@@ -380,6 +407,26 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                          start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st);
 #endif
         if (tracer) FA_TRACE(t, tr, 3);
+        if constexpr (kPaged) {
+        if (start + kBlockN > sk_rel) {
+          // Last tile of a paged sequence: key rows past the end were not fetched, or hold whatever the page holds
+          // there.  Their P is zero, but 0 * NaN would still poison O, so this thread clears V row `row` of the tile
+          // (after it has landed) before this tile's P V product may start.  Both softmax warpgroups do it (the two
+          // products read the same V tile; writing zeros twice is harmless).
+          const uint32_t v_item = 2 * kv_tiles + 1;
+          if (!mbar_wait(smem_u32(&kv_full[v_item % kSlots]), (v_item / kSlots) & 1u, wctx)) { ok = false; break; }
+          if (row >= sk_rel - start) {
+            const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
+#pragma unroll
+            for (int hf = 0; hf < T::kHalves; ++hf)
+#pragma unroll
+              for (int c16 = 0; c16 < 8; ++c16)
+                asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(vrow + hf * T::kHalfBytes + c16 * 16), "r"(0u) : "memory");
+          }
+          fence_proxy_async_smem();
+        }
+        ++kv_tiles;
+        }
         tc_fence_before();
         mbar_arrive(smem_u32(&p_full[t]));
         if (tracer) FA_TRACE(t, tr, 4);
@@ -482,19 +529,21 @@ template <int DT>
 cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                           const PrefillKernelParams& p, cudaStream_t stream) {
   const bool win = p.window_left >= 0;
-  auto kern = win ? prefill_pair_kernel<DT, true> : prefill_pair_kernel<DT, false>;
+  const bool paged = p.paged != 0;
+  auto kern = paged ? (win ? prefill_pair_kernel<DT, true, true> : prefill_pair_kernel<DT, false, true>)
+                    : (win ? prefill_pair_kernel<DT, true, false> : prefill_pair_kernel<DT, false, false>);
   const size_t smem = 1024 + pair_smem<DT>().total;
-  static bool attr_done[2][64] = {};
+  static bool attr_done[4][64] = {};
   static int num_sms[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (!attr_done[win][dev]) {
+  if (!attr_done[win + 2 * paged][dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     e = cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
-    attr_done[win][dev] = true;
+    attr_done[win + 2 * paged][dev] = true;
   }
   const long long total = static_cast<long long>(p.h / 2) * p.b * p.num_m_blocks;
   if (total <= 0) return cudaSuccess;
