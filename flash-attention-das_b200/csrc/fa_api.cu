@@ -718,9 +718,9 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   // double-buffered scores ("dense").  Tile lists are per head and run one tile per CTA ("single").
   // FA_B200_PREFILL_KERNEL=single|pair|dense overrides the choice where it is legal (tests, comparisons).
   const bool even_group = (p->h / p->h_k) % 2 == 0;
-  // Tile lists, other head dimensions and transposed V pools: the one-tile kernel.  Paged K/V in the plain layouts:
-  // the two-tile kernel where the GQA group is even, else the one-tile kernel.
-  const bool one_tile_only = sparse || p->d != kHeadDim || p->v_transposed || (paged && !even_group);
+  // Tile lists and other head dimensions: the one-tile kernel.  Paged K/V (any pool layout): the two-tile kernel where
+  // the GQA group is even, else the one-tile kernel.
+  const bool one_tile_only = sparse || p->d != kHeadDim || (paged && !even_group);
   int which = one_tile_only ? 0 : (even_group ? 1 : 2);
   if (const char* ov = getenv("FA_B200_PREFILL_KERNEL")) {
     if (!strcmp(ov, "single")) which = 0;

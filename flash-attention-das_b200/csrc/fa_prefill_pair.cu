@@ -100,12 +100,15 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
 // kLeftWindow: the launch has a left sliding-window bound (kept out of the common build of the hot loop: two more live
 // values per softmax thread are enough to make it spill).
 // kPaged: K/V are read through a block table (its own build, so that the common one carries none of its state).
-template <int DT, bool kLeftWindow, bool kPaged>
+// kVT (with kPaged, 16-bit types): the V pool is stored transposed, tokens contiguous: a V tile lands as 128 d rows of
+// 128 keys and enters the P V product as a K-major operand (issue_pv_vt).
+template <int DT, bool kLeftWindow, bool kPaged, bool kVT = false>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
                     const PrefillKernelParams p) {
   using T = TileTraits<DT>;
+  static_assert(!kVT || (kPaged && !T::kFp8), "transposed V: paged pools of a 16-bit type");
   constexpr PairSmem L = pair_smem<DT>();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -235,6 +238,18 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
               for (int hf = 0; hf < T::kHalves; ++hf)
                 tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, it.hk,
                             it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b);
+            } else if (kVT && kv) {
+              // transposed V pool: one box of 64 keys x 128 d rows per column group; groups that start past the end of
+              // the sequence are not fetched
+              const int start = (it.tile0 + j) * kBlockN;
+              const int nbox = min(kBlockN / 64, (it.sk - start + 63) / 64);
+              mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * T::kHalfBytes);
+              const int32_t* bt = p.block_table + static_cast<int64_t>(it.bidb) * p.bt_stride;
+              for (int i = 0; i < nbox; ++i) {
+                const int tok = start + i * 64;
+                tma_load_4d(ring_smem + slot * T::kTileBytes + i * T::kHalfBytes, tm, bar, tok % p.page_size, 0, it.hk,
+                            bt[tok / p.page_size]);
+              }
             } else {
               // the tile's 128 keys come from one or more pages: one box of box_rows rows per page piece; boxes that
               // start past the end of the sequence are not fetched (their block_table slots are not valid)
@@ -320,7 +335,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           tc_fence_after();
           FA_TRACE(2, tr, 20 + t);
           if (!lock()) { ok = false; break; }
-          issue_pv<DT>(t_s, ring_smem + vslot * T::kTileBytes, t_o, j == 0);
+          if constexpr (kVT) issue_pv_vt<DT>(t_s, ring_smem + vslot * T::kTileBytes, t_o, j == 0);
+          else issue_pv<DT>(t_s, ring_smem + vslot * T::kTileBytes, t_o, j == 0);
           if (more) {
             issue_qk<DT>(q_t, ring_smem + kslot * T::kTileBytes, t_s);
             tc_commit(smem_u32(&s_full[t]));
@@ -415,7 +431,28 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           // products read the same V tile; writing zeros twice is harmless).
           const uint32_t v_item = 2 * kv_tiles + 1;
           if (!mbar_wait(smem_u32(&kv_full[v_item % kSlots]), (v_item / kSlots) & 1u, wctx)) { ok = false; break; }
-          if (row >= sk_rel - start) {
+          if constexpr (kVT) {
+            // this thread owns d row `row` of the transposed tile: keys at or past the end are cleared, whole 16-byte
+            // pieces (8 keys) where possible, element by element in the piece the end falls into
+            const int lim_k = sk_rel - start;
+            const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int k0 = c * 8;
+              if (k0 + 8 <= lim_k) continue;
+              const uint32_t addr = vrow + (c >> 3) * T::kHalfBytes + (((c & 7) ^ (row & 7)) << 4);
+              uint32_t w[4] = {0u, 0u, 0u, 0u};
+              if (k0 < lim_k) {
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int ka = k0 + 2 * e;
+                  w[e] = (ka < lim_k ? (w[e] & 0x0000ffffu) : 0u) | (ka + 1 < lim_k ? (w[e] & 0xffff0000u) : 0u);
+                }
+              }
+              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+          } else if (row >= sk_rel - start) {
             const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
 #pragma unroll
             for (int hf = 0; hf < T::kHalves; ++hf)
@@ -530,20 +567,29 @@ cudaError_t launch_pair_t(const CUtensorMap& tq, const CUtensorMap& tk, const CU
                           const PrefillKernelParams& p, cudaStream_t stream) {
   const bool win = p.window_left >= 0;
   const bool paged = p.paged != 0;
+  const bool vt = p.v_transposed != 0;
   auto kern = paged ? (win ? prefill_pair_kernel<DT, true, true> : prefill_pair_kernel<DT, false, true>)
                     : (win ? prefill_pair_kernel<DT, true, false> : prefill_pair_kernel<DT, false, false>);
+  if (vt) {
+    if constexpr (DT == FA_B200_E4M3) {
+      return cudaErrorInvalidValue;
+    } else {
+      if (!paged) return cudaErrorInvalidValue;
+      kern = win ? prefill_pair_kernel<DT, true, true, true> : prefill_pair_kernel<DT, false, true, true>;
+    }
+  }
   const size_t smem = 1024 + pair_smem<DT>().total;
-  static bool attr_done[4][64] = {};
+  static bool attr_done[6][64] = {};
   static int num_sms[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (!attr_done[win + 2 * paged][dev]) {
+  if (!attr_done[win + 2 * paged + 2 * vt][dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     e = cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
-    attr_done[win + 2 * paged][dev] = true;
+    attr_done[win + 2 * paged + 2 * vt][dev] = true;
   }
   const long long total = static_cast<long long>(p.h / 2) * p.b * p.num_m_blocks;
   if (total <= 0) return cudaSuccess;
