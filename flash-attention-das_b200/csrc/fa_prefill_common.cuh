@@ -204,13 +204,21 @@ template <int DT>
 __device__ __forceinline__ void issue_pv_vt(uint32_t p_tmem, uint32_t vt_smem, uint32_t o_tmem, bool overwrite) {
   using T = TileTraits<DT>;
   static_assert(!T::kFp8, "transposed V: 16-bit types");
-  constexpr uint32_t idesc = make_idesc(T::kFormat, false, kBlockM, kHeadDim);
+  // same operand walk as Q K^T with Q in TMEM (issue_qk_ts): the instruction descriptor is the K-major 128 x 128 one
   const uint64_t b0 = make_smem_desc_sw128(vt_smem, 16, 1024);
-#pragma unroll
-  for (int ks = 0; ks < T::kPVSteps; ++ks) {
-    const uint64_t off = static_cast<uint64_t>((ks >> 2) * (T::kHalfBytes >> 4) + (ks & 3) * 2);
-    tc_mma_ts(o_tmem, p_tmem + ks * 8, b0 + off, idesc, ks > 0 ? 1u : (overwrite ? 0u : 1u), false);
-  }
+  const uint32_t acc0 = overwrite ? 0u : 1u;
+  asm volatile(
+      "{\n\t.reg .pred pf, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+      "setp.ne.b32 pf, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pf;\n\t"
+      "add.u32 a, %1, 8;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 16;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 24;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 32;\n\tadd.s64 b, %2, 1024;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 40;\n\tadd.s64 b, %2, 1026;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 48;\n\tadd.s64 b, %2, 1028;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 56;\n\tadd.s64 b, %2, 1030;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t}"
+      ::"r"(o_tmem), "r"(p_tmem), "l"(b0), "r"(T::kIdescQK), "r"(acc0) : "memory");
 }
 
 // Visible key range of query row i (index inside its sequence): [row_lo, row_hi).
