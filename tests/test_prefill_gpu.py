@@ -473,3 +473,50 @@ def test_scores_that_outgrow_the_running_maximum(fa, monkeypatch, dtype, kernel)
         assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"{kernel} causal={causal} window={window}")
         fin = torch.isfinite(ref_lse)
         assert (lse.cpu()[fin] - ref_lse[fin]).abs().max() < 1e-3 * max(1.0, ref_lse[fin].abs().max().item())
+
+
+@pytest.mark.parametrize("h,h_k", [(8, 2), (6, 2)])      # even group: two-tile kernel; odd group: one-tile kernel
+@pytest.mark.parametrize("page", [16, 64, 256])
+def test_fp8_paged_prefill(fa, page, h, h_k):
+    """e4m3 queries over an e4m3 paged cache with several query tokens per sequence (chunked prefill in FP8), the
+    unused pages and tails poisoned with the e4m3 NaN pattern.  Rule of the reference's FP8 tests: error <= 2 x the error
+    of the same math with P round-tripped through e4m3, cosine difference < 1e-3."""
+    from _util import make_paged
+    flash_attn, cuda = fa
+    g = gen(8800 + page + h)
+    lens_k = [300, 130, 1000, 64, 257]
+    lens_q = [300, 2, 129, 64, 200]
+    n = len(lens_k)
+    kc16, vc16, bt, sl = make_paged(g, lens_k, h_k, page, torch.bfloat16, poison=False)
+    q16 = randn(g, sum(lens_q), h, 128)
+    q8, qd = O.quantize_e4m3_per_tensor(q16)
+    k8, kd = O.quantize_e4m3_per_tensor(kc16)
+    v8, vd = O.quantize_e4m3_per_tensor(vc16)
+    # poison what no sequence owns: spare pages and the rows past each sequence's end (0x7f = e4m3 NaN)
+    k_dev, v_dev = k8.clone().view(torch.uint8), v8.clone().view(torch.uint8)
+    used = torch.zeros(k8.shape[0], dtype=torch.bool)
+    for i, L in enumerate(lens_k):
+        nb = (L + page - 1) // page
+        used[bt[i, :nb].long()] = True
+        if L % page:
+            last = int(bt[i, nb - 1])
+            k_dev[last, L % page:] = 0x7f
+            v_dev[last, L % page:] = 0x7f
+    k_dev[~used] = 0x7f
+    v_dev[~used] = 0x7f
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    out = flash_attn.flash_attn_varlen_func(q8.cuda(), k_dev.view(torch.float8_e4m3fn).cuda(), v_dev.view(torch.float8_e4m3fn).cuda(),
+                                            cq.cuda(), None, max(lens_q), max(lens_k), seqused_k=sl.cuda(), causal=True,
+                                            block_table=bt.cuda(), q_descale=qd.cuda(), k_descale=kd.cuda(), v_descale=vd.cuda())
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    assert out.dtype == torch.bfloat16 and not torch.isnan(out.float()).any()
+    kw = dict(q_descale=qd.expand(1, h_k), k_descale=kd.expand(1, h_k), v_descale=vd.expand(1, h_k))
+    for i, (lq, lk) in enumerate(zip(lens_q, lens_k)):
+        qi = q8[int(cq[i]):int(cq[i + 1])][None]
+        ki, vi = O.gather_paged_kv(k8, bt[i], lk)[None], O.gather_paged_kv(v8, bt[i], lk)[None]
+        ref32, _ = O.attention_ref(qi, ki, vi, causal=True, out_dtype=torch.float32, **kw)
+        ref_p8, _ = O.attention_ref(qi, ki, vi, causal=True, out_dtype=torch.float32, intermediate_dtype=torch.float8_e4m3fn, **kw)
+        got = out[int(cq[i]):int(cq[i + 1])].cpu()[None]
+        assert max_err(got, ref32) <= 2 * max_err(ref_p8, ref32) + 2 ** -7, (i, page)
+        assert cos_diff(got, ref32) < 1e-3, (i, page)
