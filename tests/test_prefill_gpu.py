@@ -520,3 +520,38 @@ def test_fp8_paged_prefill(fa, page, h, h_k):
         got = out[int(cq[i]):int(cq[i + 1])].cpu()[None]
         assert max_err(got, ref32) <= 2 * max_err(ref_p8, ref32) + 2 ** -7, (i, page)
         assert cos_diff(got, ref32) < 1e-3, (i, page)
+
+
+@pytest.mark.parametrize("h,h_k", [(8, 2), (3, 1)])      # two-tile and one-tile kernel
+def test_paged_prefill_empty_and_short_caches(fa, h, h_k):
+    """Paged prefill where a sequence has no keys at all, or fewer keys than queries (the first rows then see nothing:
+    zero output, LSE = +inf), next to ordinary sequences."""
+    from _util import clean_nan, make_paged
+    flash_attn, cuda = fa
+    g = gen(4711 + h)
+    page = 64
+    lens_k = [0, 40, 700, 1, 129]
+    lens_q = [17, 100, 300, 64, 129]
+    kc, vc, bt, sl = make_paged(g, [max(l, 1) for l in lens_k], h_k, page, torch.bfloat16)
+    sl = torch.tensor(lens_k, dtype=torch.int32)
+    q = randn(g, sum(lens_q), h, 128)
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    out, lse = flash_attn.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cq.cuda(), None, max(lens_q), max(lens_k),
+                                                 seqused_k=sl.cuda(), causal=True, block_table=bt.cuda(), return_softmax_lse=True)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    assert not torch.isnan(out.float()).any()
+    kcc, vcc = clean_nan(kc), clean_nan(vc)
+    for i, (lq, lk) in enumerate(zip(lens_q, lens_k)):
+        o_i, l_i = out[int(cq[i]):int(cq[i + 1])].cpu(), lse[:, int(cq[i]):int(cq[i + 1])].cpu()
+        if lk == 0:
+            assert torch.all(o_i == 0) and torch.all(l_i == float("inf"))
+            continue
+        qi = q[int(cq[i]):int(cq[i + 1])][None]
+        ki, vi = O.gather_paged_kv(kcc, bt[i], lk)[None], O.gather_paged_kv(vcc, bt[i], lk)[None]
+        ref32, ref_lse = O.attention_ref(qi, ki, vi, causal=True, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(qi, ki, vi, causal=True, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(o_i[None], ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"seq {i}")
+        _check_lse(l_i, ref_lse[0])
+        if lq > lk:
+            assert torch.all(o_i[:lq - lk] == 0)
