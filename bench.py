@@ -46,7 +46,8 @@ TRAFFIC_RATIO = {"decode_bf16": 1.007, "decode_fp8": 1.013, "prefill_bf16": None
                  "sparse_bf16": None, "longseq": 1.007}
 # prefill is tensor-bound, its algorithmic unit is FLOPs; DRAM traffic is reported in bytes per token of the
 # captured case (521.5 MB for 19,679 tokens, 1.29x the compulsory q+k+v+out bytes).
-PREFILL_TRAFFIC_BYTES_PER_TOKEN = {"prefill_bf16": 521.5e6 / 19679}
+# block-sparse: the full configuration was captured (3.251 GB read + 0.237 GB written for its 32,768 tokens).
+PREFILL_TRAFFIC_BYTES_PER_TOKEN = {"prefill_bf16": 521.5e6 / 19679, "sparse_bf16": 3.4879e9 / 32768}
 
 
 def load_peaks():
