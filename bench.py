@@ -401,7 +401,7 @@ class SparseWorkload:
         self.h2d = (self.q.numel() + 2 * self.k.numel()) * 2 + (cnt.numel() + offs.numel()) * 4
         self.d2h = self.out_host.numel() * 2
         self.desc = {"workload": "block-sparse causal GQA prefill bf16: 1 x %d, 128x128 tiles at %.0f%% density" %
-                     (seqlen, density * 100), "kept_tiles": self.kept, "nheads": H, "nheads_kv": HK, "headdim": D,
+                     (seqlen, density * 100), "kept_tiles": self.kept, "tokens": seqlen, "nheads": H, "nheads_kv": HK, "headdim": D,
                      "l2": "inputs larger than L2 is NOT true here (q+k+v %.0f MB): L2 flushed between steps" %
                      ((self.q.numel() + 2 * self.k.numel()) * 2 / 1e6)}
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
