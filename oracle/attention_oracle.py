@@ -110,7 +110,7 @@ def attention_varlen_ref(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, upca
                          window_size=(-1, -1)):
     """Packed varlen attention, one sequence at a time.  Follows attention_varlen_ref
     (tests/test_flash_attn.py:432-494): LSE is (h, total_q) with -inf replaced by +inf and empty
-    key ranges give zeros.  Descales are (batch, heads_k) fp32 or None."""
+    key ranges give zeros (LSE = the sink where sinks are given).  Descales are (batch, heads_k) fp32 or None."""
     nb = cu_seqlens_q.numel() - 1
     outs, lses = [], []
     cq = cu_seqlens_q.tolist()
@@ -123,7 +123,10 @@ def attention_varlen_ref(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, upca
             is_fp8 = q.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
             outs.append(torch.zeros(qi.shape[1], q.shape[1], v.shape[-1],
                                     dtype=out_dtype or (torch.bfloat16 if is_fp8 else q.dtype)))
-            lses.append(torch.full((q.shape[1], qi.shape[1]), float("inf")))
+            if s_aux is None:
+                lses.append(torch.full((q.shape[1], qi.shape[1]), float("inf")))
+            else:   # the sink is the only term of such a row's sum, as for fully masked rows in attention_ref
+                lses.append(s_aux.float().reshape(-1, 1).expand(q.shape[1], qi.shape[1]).clone())
             continue
         o, l = attention_ref(
             qi, ki, vi, causal=causal, upcast=upcast, softmax_scale=softmax_scale,
