@@ -108,3 +108,39 @@ def test_selected_blocks_drive_the_sparse_kernel(fa):
     ref_pt, _ = O.attention_ref(qs, ks, vs, causal=True, upcast=False, reorder_ops=True, extra_mask=mask)
     assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what="selected blocks")
     assert 0.05 < bmap.float().mean() < 0.6
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_selection_configurations(fa, seed):
+    """Random lengths (cut blocks included), head dimensions, thresholds per head, top-k or cumulative selection,
+    causal / sink flags: maps equal to the oracle's on every row the oracle calls decided."""
+    import os
+    import random
+    _, cuda, su = fa
+    off = int(os.environ.get("FA_TEST_SEED_OFFSET", "0"))
+    rng = random.Random(7000 + seed + off)
+    g = gen(7000 + seed + off)
+    dtype = rng.choice([torch.bfloat16, torch.float16])
+    b, h, d = rng.randint(1, 2), rng.randint(1, 4), rng.choice([64, 128, 256])
+    n = rng.choice([64, 129, 500, 1024, 1500, 3000])
+    noise = rng.choice([0.2, 0.4, 0.8])
+    q, k = _qk(g, b, h, n, d, noise, dtype)
+    causal, sink = rng.random() < 0.5, rng.random() < 0.3
+    if rng.random() < 0.5:
+        args = dict(cdfthreshd=torch.tensor([rng.choice([0.3, 0.6, 0.9, 0.98]) for _ in range(h)]))
+    else:
+        args = dict(cdfthreshd=None, topk=rng.choice([0.1, 0.25, 0.5]))
+    got = su.get_block_map_meansim(q.cuda(), k.cuda(), is_causal=causal, attention_sink=sink, **args)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    ref, margin = BS.block_map_meansim_ref(q, k, is_causal=causal, attention_sink=sink, **args)
+    th1 = torch.full((h,), 0.1)
+    _, _, vq = BS.pool_sim_ref(q, 128, th1)
+    _, _, vk = BS.pool_sim_ref(k, 64, th1)
+    near = ((vq - 0.1).abs() < 1e-3).any() or ((vk - 0.1).abs() < 1e-3).any()
+    if near:
+        pytest.skip("a self-similarity value lies within 1e-3 of its threshold")
+    decided = margin > 1e-5
+    what = f"n{n} d{d} b{b} h{h} causal{causal} sink{sink} {args}"
+    assert torch.equal(got.cpu()[decided], ref[decided]), what
+    assert (got.cpu() != ref).sum(dim=-1).max() <= 2, what
