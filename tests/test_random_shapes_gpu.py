@@ -149,9 +149,17 @@ def test_random_paged(fa, seed):
         lens_q = [max(1, min(_len(rng, 300), lk)) for lk in lens_k]
         cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
         q = randn(g, int(cq[-1]), h, d, dtype=dtype)
-        out = flash_attn.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cq.cuda(), None, max(lens_q), max(lens_k),
+        # the pool in one of the reference's three layouts (flash_attn_interface.py:2223-2237)
+        layouts = ["bshd", "bhsd"] + (["custom"] if page % 64 == 0 and d == 128 else [])
+        layout = rng.choice(layouts)
+        k_arg, v_arg = kc.cuda(), vc.cuda()
+        if layout != "bshd":
+            k_arg = k_arg.permute(0, 2, 1, 3).contiguous()
+            v_arg = v_arg.permute(0, 2, 1, 3).contiguous() if layout == "bhsd" else v_arg.permute(0, 2, 3, 1).contiguous()
+        out = flash_attn.flash_attn_varlen_func(q.cuda(), k_arg, v_arg, cq.cuda(), None, max(lens_q), max(lens_k),
                                                 seqused_k=sl.cuda(), causal=True, window_size=(window[0], -1 if window[0] < 0 else 0),
-                                                block_table=bt.cuda(), s_aux=None if s_aux is None else s_aux.cuda())
+                                                block_table=bt.cuda(), s_aux=None if s_aux is None else s_aux.cuda(),
+                                                layout=layout)
         torch.cuda.synchronize()
         qs = [q[int(cq[i]):int(cq[i + 1])] for i in range(n)]
         outs = [out[int(cq[i]):int(cq[i + 1])].cpu() for i in range(n)]
