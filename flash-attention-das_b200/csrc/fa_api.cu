@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "fa_common.cuh"
 #include "fa_kernels.h"
@@ -15,13 +16,18 @@ namespace {
 // Device-side status word (one per device that loads the library).
 __device__ int g_device_status = 0;
 
-// Work counters of the persistent prefill launches in flight: a launch takes the next slot of the pool and zeroes it on
-// its stream; the CTAs claim their work items from it.  64 slots: as many launches may overlap on one device.
-constexpr int kCounterSlots = 64;
-__device__ int g_work_counters[kCounterSlots];
+// Per-stream scratch inside the library.  A (device, stream) pair owns one slot: a work counter for the persistent
+// prefill kernels (zeroed on the stream before each launch) and a block of split-KV tickets for the decode kernel
+// (zero whenever no decode launch of that stream is in flight: the kernel puts them back).  Launches of one stream
+// are ordered by the stream and so may share a slot; different streams get different slots.
+constexpr int kStreamSlots = 64;
+constexpr int kTicketsPerSlot = 4096;   // (sequence, kv head) pairs of one decode launch that can merge in the kernel
+__device__ int g_work_counters[kStreamSlots];
+__device__ int g_tickets[kStreamSlots * kTicketsPerSlot];
 
 std::atomic<uint64_t> g_launches{0};
 thread_local char g_last_error[256] = "";
+thread_local char g_launch_info[320] = "";
 
 void set_error(const char* what, const char* detail) {
   snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, detail ? detail : "");
@@ -48,30 +54,77 @@ EncodeTiledFn get_encode_fn() {
 }
 
 int* status_ptr() {
-  static int* ptrs[64] = {};
+  static std::atomic<int*> ptrs[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!ptrs[dev]) {
+  int* cached = ptrs[dev].load(std::memory_order_acquire);
+  if (!cached) {
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
-    ptrs[dev] = static_cast<int*>(ptr);
+    cached = static_cast<int*>(ptr);
+    ptrs[dev].store(cached, std::memory_order_release);
   }
-  return ptrs[dev];
+  return cached;
+}
+
+// Slot of (current device, stream); the least recently used slot is taken over when all are in use, which is safe as
+// long as no more than kStreamSlots streams have launches of this library in flight at once.
+int stream_slot(int dev, cudaStream_t stream) {
+  struct Entry { int dev; cudaStream_t stream; uint64_t stamp; };
+  static std::mutex mu;
+  static Entry entries[kStreamSlots];
+  static int used = 0;
+  static uint64_t clock = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  ++clock;
+  int lru = 0;
+  for (int i = 0; i < used; ++i) {
+    if (entries[i].dev == dev && entries[i].stream == stream) { entries[i].stamp = clock; return i; }
+    if (entries[i].stamp < entries[lru].stamp) lru = i;
+  }
+  const int slot = used < kStreamSlots ? used++ : lru;
+  entries[slot] = Entry{dev, stream, clock};
+  return slot;
+}
+
+// Device addresses of the per-stream scratch arrays on the current device, looked up once per device.
+struct SlotBases { std::atomic<int*> counters{nullptr}; std::atomic<int*> tickets{nullptr}; };
+SlotBases* slot_bases(int* dev_out) {
+  static SlotBases bases[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  SlotBases& b = bases[dev];
+  if (!b.counters.load(std::memory_order_acquire)) {
+    void *c = nullptr, *t = nullptr;
+    if (cudaGetSymbolAddress(&c, g_work_counters) != cudaSuccess) return nullptr;
+    if (cudaGetSymbolAddress(&t, g_tickets) != cudaSuccess) return nullptr;
+    b.tickets.store(static_cast<int*>(t), std::memory_order_release);
+    b.counters.store(static_cast<int*>(c), std::memory_order_release);
+  }
+  *dev_out = dev;
+  return &b;
 }
 
 int* next_work_counter(cudaStream_t stream) {
-  static int* base[64] = {};
-  static std::atomic<unsigned> next_slot{0};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!base[dev]) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_work_counters) != cudaSuccess) return nullptr;
-    base[dev] = static_cast<int*>(ptr);
-  }
-  int* c = base[dev] + (next_slot.fetch_add(1, std::memory_order_relaxed) % kCounterSlots);
+  SlotBases* b = slot_bases(&dev);
+  if (!b) return nullptr;
+  int* c = b->counters.load(std::memory_order_acquire) + stream_slot(dev, stream);
   if (cudaMemsetAsync(c, 0, sizeof(int), stream) != cudaSuccess) return nullptr;
   return c;
+}
+
+// Tickets for `count` (sequence, kv head) pairs of a decode launch on `stream`, or nullptr when the launch has to use
+// the separate combine kernel: too many pairs, or the stream is being captured into a graph (a replay could overlap
+// launches of the stream that owns the slot).
+int* stream_tickets(cudaStream_t stream, int64_t count) {
+  if (count > kTicketsPerSlot) return nullptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+  int dev = 0;
+  SlotBases* b = slot_bases(&dev);
+  if (!b) return nullptr;
+  return b->tickets.load(std::memory_order_acquire) + static_cast<size_t>(stream_slot(dev, stream)) * kTicketsPerSlot;
 }
 
 int elem_size(int dtype) { return dtype == FA_B200_E4M3 ? 1 : 2; }
@@ -132,9 +185,33 @@ int make_tmap_vt(CUtensorMap* out, const void* base, int dtype, int64_t page, in
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 bool stride_ok(int64_t s, int es) { return s >= 0 && (s * es) % 16 == 0; }
 
-int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return (v && *v) ? atoi(v) : dflt;
+// Environment switches, read once when the library is loaded (as the reference reads its own,
+// csrc/flash_attn_cutlass/src/flash.h:20-25):
+//   FA_B200_DECODE_PARTITION=<tokens>        partition size of the split-KV decode (0 / unset: heuristic)
+//   FA_B200_PREFILL_KERNEL=single|pair|dense prefill kernel, where that kernel can take the call
+//   FA_B200_PRINT_PARAM=1                    one line on stderr per attention call: kernel, grid, tiling
+//                                            (the reference: FLASH_ATTENTION_PRINT_PARAM, flash_api.cpp:219-222;
+//                                            PA_PRINT_PARAM, src/paged_attention.cu:40)
+// Callers that want to switch per call use the struct fields partition_tokens / kernel_choice instead.
+struct EnvConfig {
+  int decode_partition = 0;
+  int prefill_kernel = 0;   // 0 auto, 1 single, 2 pair, 3 dense
+  int print_param = 0;
+  EnvConfig() {
+    if (const char* v = getenv("FA_B200_DECODE_PARTITION")) decode_partition = atoi(v);
+    if (const char* v = getenv("FA_B200_PREFILL_KERNEL")) {
+      if (!strcmp(v, "single")) prefill_kernel = 1;
+      else if (!strcmp(v, "pair")) prefill_kernel = 2;
+      else if (!strcmp(v, "dense")) prefill_kernel = 3;
+    }
+    if (const char* v = getenv("FA_B200_PRINT_PARAM")) print_param = atoi(v);
+  }
+};
+const EnvConfig g_env;
+std::atomic<int> g_print_param{-1};   // -1: follow the environment; 0 / 1: set by fa_b200_set_print_param
+bool print_param() {
+  const int v = g_print_param.load(std::memory_order_relaxed);
+  return v < 0 ? g_env.print_param != 0 : v != 0;
 }
 
 // 128 everywhere; 64, 192 and 256 for 16-bit tensors in the plain layouts (`only128`: the call uses a variant that is
@@ -151,6 +228,7 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   DecodePlan pl{};
   pl.status = FA_B200_OK;
   if (!p) { pl.status = FA_B200_ERR_NULL; return pl; }
+  if (p->struct_size != sizeof(fa_b200_decode_params)) { pl.status = FA_B200_ERR_ABI; return pl; }
   if (!head_dim_ok(p->d, p->dtype == FA_B200_E4M3 || p->kv_e4m3 || p->v_transposed)) { pl.status = FA_B200_ERR_HEADDIM; return pl; }
   if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) { pl.status = FA_B200_ERR_DTYPE; return pl; }
   if (p->b < 0 || p->h <= 0 || p->h_k <= 0 || p->max_blocks_per_seq < 0 || p->num_blocks < 0) { pl.status = FA_B200_ERR_SHAPE; return pl; }
@@ -172,7 +250,7 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   if (max_len > (1ll << 30)) { pl.status = FA_B200_ERR_TOO_LARGE; return pl; }
   pl.max_len = static_cast<int>(max_len);
   const int unit = pl.tile > page ? (pl.tile % page == 0 ? pl.tile : pl.tile * page) : (page % pl.tile == 0 ? page : pl.tile * page);
-  int part = p->partition_tokens > 0 ? p->partition_tokens : env_int("FA_B200_DECODE_PARTITION", 0);
+  int part = p->partition_tokens > 0 ? p->partition_tokens : g_env.decode_partition;
   if (part > 0) {
     if (part % pl.tile != 0 || (part % page != 0 && page % part != 0)) { pl.status = FA_B200_ERR_SHAPE; return pl; }
   } else {
@@ -212,6 +290,8 @@ using namespace fa;
 extern "C" {
 
 int fa_b200_abi_version(void) { return FA_B200_ABI_VERSION; }
+void fa_b200_set_print_param(int on) { g_print_param.store(on < 0 ? -1 : (on ? 1 : 0)); }
+const char* fa_b200_last_launch_info(void) { return g_launch_info; }
 uint64_t fa_b200_launch_count(void) { return g_launches.load(); }
 const char* fa_b200_last_cuda_error(void) { return g_last_error; }
 
@@ -233,6 +313,7 @@ const char* fa_b200_status_string(int s) {
     case FA_B200_ERR_TOO_LARGE: return "size beyond a built-in limit";
     case FA_B200_ERR_DEVICE_RANGE: return "a kernel skipped an out-of-range cache position, page id or rotary row";
     case FA_B200_ERR_DEVICE_UNSUPPORTED: return "a kernel met device-resident input it does not take (vertical sparsity)";
+    case FA_B200_ERR_ABI: return "struct_size does not match this library: caller and library were built from different headers";
   }
   return "unknown status";
 }
@@ -262,6 +343,7 @@ int32_t fa_b200_decode_partition_tokens(const fa_b200_decode_params* p) {
 
 int fa_b200_kv_append(const fa_b200_kv_append_params* p, void* stream) {
   if (!p) return FA_B200_ERR_NULL;
+  if (p->struct_size != sizeof(fa_b200_kv_append_params)) return FA_B200_ERR_ABI;
   if (p->d != kHeadDim) return FA_B200_ERR_HEADDIM;
   if (p->dtype != FA_B200_F16 && p->dtype != FA_B200_BF16 && p->dtype != FA_B200_E4M3) return FA_B200_ERR_DTYPE;
   if (p->b < 0 || p->seqlen_new < 0 || p->seqlen_q < 0 || p->h <= 0 || p->h_k <= 0 || p->page_size <= 0 ||
@@ -376,7 +458,9 @@ bool sink_dtype_ok(const void* s_aux, int dtype) {
 }  // namespace
 
 int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
-  if (!p || !p->o_partial || !p->lse_partial) return FA_B200_ERR_NULL;
+  if (!p) return FA_B200_ERR_NULL;
+  if (p->struct_size != sizeof(fa_b200_combine_params)) return FA_B200_ERR_ABI;
+  if (!p->o_partial || !p->lse_partial) return FA_B200_ERR_NULL;
   if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
   if (!head_dim_ok(p->d, false)) return FA_B200_ERR_HEADDIM;
   if (p->rows < 0 || p->num_parts < 0 || p->h <= 0 || p->rows % p->h != 0) return FA_B200_ERR_SHAPE;
@@ -490,16 +574,44 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.d = p->d;
   k.q_row_stride = p->q_row_stride;
   k.o_row_stride = p->o_row_stride;
+  k.max_len = pl.max_len;
+  bool merge_in_kernel = false;
   if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
     k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * k.sq * p->d;
+    // The last CTA of each (sequence, kv head) merges the partials itself when there are tickets to count on.
+    if (pl.num_partitions <= 256) k.tickets = p->tickets ? p->tickets : stream_tickets(stream, static_cast<int64_t>(p->b) * p->h_k);
+    merge_in_kernel = k.tickets != nullptr;
+    if (merge_in_kernel) {
+      if (p->o_partial_out) {   // fp32 rows (b, h, tok) for a cross-GPU combine; the sink is left to that combine
+        k.out = p->o_partial_out;
+        k.lse_out = p->lse_partial_out;
+        k.o_batch_stride = static_cast<int64_t>(p->h) * k.sq * p->d;
+        k.o_head_stride = static_cast<int64_t>(k.sq) * p->d;
+        k.o_row_stride = p->d;
+        k.out_dtype = -1;
+        k.merge_lse_empty_is_neg = 1;
+      } else {
+        k.merge_sink = 1;
+      }
+    }
+  }
+  {
+    const char* dt = p->dtype == FA_B200_E4M3 ? "e4m3" : (p->dtype == FA_B200_BF16 ? "bf16" : "f16");
+    snprintf(g_launch_info, sizeof(g_launch_info),
+             "fa_b200 decode: kernel=decode_paged dtype=%s%s d=%d b=%d h=%d h_k=%d seqlen_q=%d page=%d partition_tokens=%d "
+             "partitions=%d grid=(%d,%d,%d) threads=160 merge=%s",
+             dt, p->kv_e4m3 ? (p->kv_e5m2 ? "+e5m2 cache" : "+e4m3 cache") : "", p->d, p->b, p->h, p->h_k, k.sq, p->page_size,
+             pl.partition_tokens, pl.num_partitions, pl.num_partitions, p->h_k, p->b,
+             !pl.split ? "none (one partition)" : (merge_in_kernel ? "in-kernel (last CTA per sequence and kv head)" : "combine kernel"));
+    if (print_param()) fprintf(stderr, "%s\n", g_launch_info);
   }
   if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
   cudaError_t e = launch_decode(p->dtype, tk, tv, k, stream);
   if (e != cudaSuccess) return cuda_fail("decode launch", e);
   if (p->profile_stop_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_stop_event), stream);
   g_launches++;
-  if (pl.split) {
+  if (pl.split && !merge_in_kernel) {
     CombineKernelParams c{};
     c.o_partial = k.o_partial;
     c.lse_partial = k.lse_partial;
@@ -548,18 +660,18 @@ static __device__ __align__(256) unsigned char g_static_scratch[FA_B200_STATIC_S
 // handle for the runtime, not an address a kernel could use: the address comes from
 // cudaGetSymbolAddress, asked once per device with that device current.
 static void* static_scratch_ptr(cudaError_t* err) {
-  static void* ptrs[64] = {};
+  static std::atomic<void*> ptrs[64];
   int dev = 0;
   *err = cudaGetDevice(&dev);
   if (*err != cudaSuccess) return nullptr;
   if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
-  if (!ptrs[dev]) {
-    void* ptr = nullptr;
-    *err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+  void* cached = ptrs[dev].load(std::memory_order_acquire);
+  if (!cached) {
+    *err = cudaGetSymbolAddress(&cached, g_static_scratch);
     if (*err != cudaSuccess) return nullptr;
-    ptrs[dev] = ptr;
+    ptrs[dev].store(cached, std::memory_order_release);
   }
-  return ptrs[dev];
+  return cached;
 }
 
 int fa_b200_decode_paged_static(const fa_b200_decode_params* p, void* stream) {
@@ -586,6 +698,7 @@ int fa_b200_decode_paged_static(const fa_b200_decode_params* p, void* stream) {
 static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!p) return FA_B200_ERR_NULL;
+  if (p->struct_size != sizeof(fa_b200_fwd_params)) return FA_B200_ERR_ABI;
   if (!head_dim_ok(p->d, p->dtype == FA_B200_E4M3)) return FA_B200_ERR_HEADDIM;
   const int dv = p->d_v > 0 ? p->d_v : p->d;
   if (dv != p->d && !(p->d == 192 && dv == 128)) return FA_B200_ERR_HEADDIM;
@@ -701,6 +814,7 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     k.seqused_k = p->seqused_k;
     k.page_size = p->page_size;
     k.box_rows = box_rows;
+    k.max_keys = p->max_blocks_per_seq > 0 ? static_cast<int64_t>(p->max_blocks_per_seq) * p->page_size : 0;
   }
   if (sparse) {
     k.block_count = p->block_count;
@@ -716,17 +830,16 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   // Kernel choice.  Dense / varlen prefill with an even GQA group: persistent CTAs that work on two heads of the
   // group at once and share every K/V tile ("pair").  Other head layouts (MHA, odd groups): persistent CTAs with
   // double-buffered scores ("dense").  Tile lists are per head and run one tile per CTA ("single").
-  // FA_B200_PREFILL_KERNEL=single|pair|dense overrides the choice where it is legal (tests, comparisons).
+  // kernel_choice / FA_B200_PREFILL_KERNEL override the choice where the chosen kernel can take the call.
   const bool even_group = (p->h / p->h_k) % 2 == 0;
   // Tile lists and other head dimensions: the one-tile kernel.  Paged K/V (any pool layout): the two-tile kernel where
   // the GQA group is even, else the one-tile kernel.
   const bool one_tile_only = sparse || p->d != kHeadDim || (paged && !even_group);
   int which = one_tile_only ? 0 : (even_group ? 1 : 2);
-  if (const char* ov = getenv("FA_B200_PREFILL_KERNEL")) {
-    if (!strcmp(ov, "single")) which = 0;
-    else if (!strcmp(ov, "pair") && !one_tile_only && even_group) which = 1;
-    else if (!strcmp(ov, "dense") && !one_tile_only && !paged) which = 2;
-  }
+  const int choice = p->kernel_choice > 0 ? p->kernel_choice : g_env.prefill_kernel;
+  if (choice == 1) which = 0;
+  else if (choice == 2 && !one_tile_only && even_group) which = 1;
+  else if (choice == 3 && !one_tile_only && !paged) which = 2;
   if (which != 0) {   // the persistent kernels claim their work items from a counter
     if (p->work_counter) {   // the caller's own counter
       if (cudaMemsetAsync(p->work_counter, 0, sizeof(int), stream) != cudaSuccess) return cuda_fail("work counter", cudaGetLastError());
@@ -735,6 +848,18 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
       k.work_counter = next_work_counter(stream);
     }
     if (!k.work_counter) return cuda_fail("work counter", cudaGetLastError());
+  }
+  {
+    static const char* const names[3] = {"prefill_single (one query tile per CTA, two CTAs per SM)",
+                                         "prefill_pair (persistent, two heads of a GQA group per item)",
+                                         "prefill_dense (persistent, double-buffered scores)"};
+    const char* dt = p->dtype == FA_B200_E4M3 ? "e4m3" : (p->dtype == FA_B200_BF16 ? "bf16" : "f16");
+    snprintf(g_launch_info, sizeof(g_launch_info),
+             "fa_b200 prefill: kernel=%s dtype=%s d=%d d_v=%d b=%d h=%d h_k=%d seqlen_q=%d seqlen_k=%d varlen=%d paged=%d "
+             "tile_lists=%d causal=%d window=(%d,%d) q_blocks=%d",
+             names[which], dt, p->d, dv, p->b, p->h, p->h_k, p->seqlen_q, p->seqlen_k, varlen ? 1 : 0, paged ? 1 : 0,
+             sparse ? 1 : 0, k.is_causal, k.window_left, k.window_right, k.num_m_blocks);
+    if (print_param()) fprintf(stderr, "%s\n", g_launch_info);
   }
   if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
   cudaError_t e = which == 2   ? launch_prefill_dense(p->dtype, tq, tk, tv, k, stream)
@@ -803,6 +928,7 @@ namespace {
 fa_b200_decode_params raw_decode_params(int32_t num_query, int32_t num_q_head, int32_t num_kv_head, int32_t num_dim,
                                         int32_t num_pages, int32_t page_size, int32_t max_seqlen_k, int32_t dtype) {
   fa_b200_decode_params d{};
+  d.struct_size = sizeof(d);
   d.b = num_query; d.h = num_q_head; d.h_k = num_kv_head; d.d = num_dim;
   d.num_blocks = num_pages; d.page_size = page_size;
   d.max_blocks_per_seq = page_size > 0 ? (max_seqlen_k - 1) / page_size + 1 : 0;
@@ -860,6 +986,7 @@ int fa_b200_kv_cache_attention(const void* q, const int32_t* seq_offsets, int32_
   }
   if (!seq_offsets) return FA_B200_ERR_NULL;
   fa_b200_fwd_params p{};
+  p.struct_size = sizeof(p);
   p.q = q; p.k = k_caches; p.v = v_caches; p.out = out;
   p.q_row_stride = p.o_row_stride = static_cast<int64_t>(num_q_head) * d;
   p.q_head_stride = p.o_head_stride = d;
@@ -879,6 +1006,7 @@ int fa_b200_kv_cache_attention(const void* q, const int32_t* seq_offsets, int32_
   p.block_table = page_tables; p.block_table_batch_stride = max_pages;
   p.seqused_k = cache_lens;
   p.page_size = page_size; p.num_blocks = num_pages;
+  p.max_blocks_per_seq = max_pages;
   return fa_b200_fwd(&p, stream);
 }
 

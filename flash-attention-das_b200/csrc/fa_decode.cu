@@ -54,6 +54,136 @@ __device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
   else return pack_f16(lo, hi);
 }
 
+// Merge of one (sequence, kv head)'s split-KV partials by the CTA that finished last (see DecodeKernelParams::tickets):
+// the LSE-combine of fa_combine.cu for the rows of one GQA group, run by the four consumer warps inside the decode
+// kernel so that a split decode is one launch.  Row r of the group is query token r / group, head r % group.
+//   phase A  warp w, rows w, w + 4, ..: row maximum and sum over the partitions' LSEs (the sink as one more term),
+//            the merged LSE, and every partition's weight e^{lse_i - LSE} into shared memory
+//   phase B  every warp walks its share of the partitions (w, w + 4, ..) for every row, eight loads in flight
+//   phase C  the four warps' sums are added in a fixed order and stored
+// smem: at least (16 * 256 + 4 * 16 * HD) floats.  Partials were written by other CTAs: read past L1.
+template <int HD>
+__device__ __forceinline__ void merge_group_partials(const DecodeKernelParams& p, float* smem, int b, int hk, int nparts) {
+  constexpr int NV = (HD + 127) / 128;
+  constexpr int kMaxParts = 256;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cw = warp - 1;   // consumer warp index; the producer warp only takes part in the barriers
+  const int group = p.group, rows = p.sq * group;
+  float* sm_w = smem;                               // [rows][nparts]
+  float* red = smem + 16 * kMaxParts;               // [4][rows][HD]
+  const int64_t part_stride = static_cast<int64_t>(p.b) * p.h * p.sq;   // slots between consecutive partitions
+  if (cw >= 0) {
+    for (int r = cw; r < rows; r += kConsumerWarps) {
+      const int head = hk * group + r % group, tok = r / group;
+      const int64_t slot0 = (static_cast<int64_t>(b) * p.h + head) * p.sq + tok;
+      float mx = -INFINITY;
+      for (int i = lane; i < nparts; i += 32) {
+        float l = __ldcg(p.lse_partial + i * part_stride + slot0);
+        if (l == INFINITY) l = -INFINITY;
+        mx = fmaxf(mx, l);
+      }
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+      float sum = 0.f;
+      if (mx != -INFINITY) {
+        for (int i = lane; i < nparts; i += 32) {
+          float l = __ldcg(p.lse_partial + i * part_stride + slot0);
+          if (l == INFINITY) l = -INFINITY;
+          sum += expf(l - mx);
+        }
+      }
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+      if (p.merge_sink && p.s_aux) {
+        const float sink = load_sink_log2(p.s_aux, p.s_aux_dtype, head) * kLn2;
+        const float m2 = fmaxf(mx, sink);
+        sum = (mx == -INFINITY ? 0.f : sum * expf(mx - m2)) + expf(sink - m2);
+        mx = m2;
+      }
+      const bool empty = !(sum > 0.f);
+      const float lse_tot = empty ? 0.f : mx + logf(sum);
+      for (int i = lane; i < nparts; i += 32) {
+        const float l = __ldcg(p.lse_partial + i * part_stride + slot0);
+        sm_w[r * nparts + i] = (empty || l == INFINITY || l == -INFINITY) ? 0.f : expf(l - lse_tot);
+      }
+      if (lane == 0 && p.lse_out)
+        p.lse_out[slot0] = empty ? (p.merge_lse_empty_is_neg ? -INFINITY : INFINITY) : lse_tot;
+    }
+  }
+  __syncthreads();
+  if (cw >= 0) {
+    for (int r = 0; r < rows; ++r) {
+      const int head = hk * group + r % group, tok = r / group;
+      const int64_t slot0 = (static_cast<int64_t>(b) * p.h + head) * p.sq + tok;
+      const float* wrow = sm_w + r * nparts;
+      float4 acc[NV];
+#pragma unroll
+      for (int g = 0; g < NV; ++g) acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+      constexpr int U = 8 / NV;
+      for (int i0 = cw; i0 < nparts; i0 += U * kConsumerWarps) {
+        float4 v[U][NV];
+        float w[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+          const int i = i0 + j * kConsumerWarps;
+          w[j] = (i < nparts) ? wrow[i] : 0.f;
+          // a weight of exactly zero must not pick up NaN / Inf from a partial that was never written
+          if (w[j] != 0.f) {
+            const float4* src = reinterpret_cast<const float4*>(p.o_partial + (i * part_stride + slot0) * HD) + lane;
+#pragma unroll
+            for (int g = 0; g < NV; ++g)
+              if (4 * lane + 128 * g < HD) v[j][g] = __ldcg(src + 32 * g);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+          if (w[j] != 0.f) {
+#pragma unroll
+            for (int g = 0; g < NV; ++g)
+              if (4 * lane + 128 * g < HD) {
+                acc[g].x += w[j] * v[j][g].x; acc[g].y += w[j] * v[j][g].y;
+                acc[g].z += w[j] * v[j][g].z; acc[g].w += w[j] * v[j][g].w;
+              }
+          }
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < NV; ++g)
+        if (4 * lane + 128 * g < HD)
+          *reinterpret_cast<float4*>(red + (static_cast<int64_t>(cw) * rows + r) * HD + 4 * lane + 128 * g) = acc[g];
+    }
+  }
+  __syncthreads();
+  if (cw >= 0) {
+    for (int r = cw; r < rows; r += kConsumerWarps) {
+      const int head = hk * group + r % group, tok = r / group;
+#pragma unroll
+      for (int g = 0; g < NV; ++g) {
+        if (4 * lane + 128 * g >= HD) continue;
+        float4 a = *reinterpret_cast<const float4*>(red + static_cast<int64_t>(r) * HD + 4 * lane + 128 * g);
+#pragma unroll
+        for (int w = 1; w < kConsumerWarps; ++w) {
+          const float4 t = *reinterpret_cast<const float4*>(red + (static_cast<int64_t>(w) * rows + r) * HD + 4 * lane + 128 * g);
+          a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+        }
+        const int64_t off = static_cast<int64_t>(b) * p.o_batch_stride + static_cast<int64_t>(tok) * p.o_row_stride +
+                            static_cast<int64_t>(head) * p.o_head_stride + 4 * lane + 128 * g;
+        if (p.out_dtype == FA_B200_BF16) {
+          __nv_bfloat162 x = __floats2bfloat162_rn(a.x, a.y), c = __floats2bfloat162_rn(a.z, a.w);
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) =
+              make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&c));
+        } else if (p.out_dtype == FA_B200_F16) {
+          __half2 x = __floats2half2_rn(a.x, a.y), c = __floats2half2_rn(a.z, a.w);
+          *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + off) =
+              make_uint2(*reinterpret_cast<uint32_t*>(&x), *reinterpret_cast<uint32_t*>(&c));
+        } else {
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off) = a;
+        }
+      }
+    }
+  }
+}
+
 // VT: the V pool is stored transposed, (num_blocks, h_k, d, page) with tokens contiguous (the reference's paged layout
 // 0, flash_attn_interface.py:2223-2227): a V tile then lands in shared memory as 128 d rows of 64 tokens and feeds the
 // P V product through plain (non-transposing) ldmatrix, exactly as K feeds Q K^T.  16-bit types, pages of 64 * n.
@@ -87,7 +217,12 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 
   const int part = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int len = p.seqlens[b];
+  // A length beyond what the block table covers would walk past the table row: cut it and report it.
+  int len = p.seqlens[b];
+  if (len > p.max_len) {
+    len = p.max_len;
+    if (threadIdx.x == 0 && part == 0) atomicOr(p.status, 0x10000);
+  }
   // Partitions past the end of this sequence have nothing to do; partition 0 of an empty sequence
   // still runs to publish "no keys" (zero output, LSE marker).
   if (part * p.partition_tokens >= len && !(part == 0)) return;
@@ -481,6 +616,27 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         }
       }
     }
+  }
+  if (p.tickets != nullptr) {
+    // Split mode, merge in this kernel.  Every CTA that got here takes a ticket of its (sequence, kv head) once its
+    // partial is visible device-wide (a CTA that gave up on a wait takes one too, so the count always comes back to
+    // zero); the CTA that takes the last one merges.
+    __threadfence();
+    __syncthreads();
+    int* s_last = const_cast<int*>(abort_flag) + 1;
+    if (threadIdx.x == 0) {
+      const int expected = max(1, min(p.num_partitions, (len + p.partition_tokens - 1) / p.partition_tokens));
+      int* tk = p.tickets + b * p.h_k + hk;
+      const int last = (atomicAdd(tk, 1) == expected - 1) ? 1 : 0;
+      if (last) *tk = 0;   // nobody else of this launch touches it again: zero for the next launch
+      *s_last = last ? expected : 0;
+    }
+    __syncthreads();
+    const int nparts = *s_last;
+    if (nparts == 0) return;
+    __threadfence();
+    static_assert((16 * 256 + kConsumerWarps * 16 * HD) * 4 <= STAGES * kStageBytes, "the merge buffers reuse the ring");
+    merge_group_partials<HD>(p, reinterpret_cast<float*>(stages), b, hk, nparts);
   }
 }
 

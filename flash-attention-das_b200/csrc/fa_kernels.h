@@ -39,6 +39,15 @@ struct DecodeKernelParams {
   int32_t kv_e4m3;      // the cache is e4m3 while the queries are 16-bit (launch_decode's dtype is then the query type)
   int32_t d;            // head dimension: 128, or 64 / 192 / 256 with 16-bit pools
   int32_t kv_e5m2;      // with kv_e4m3: the cache bytes are e5m2
+  int32_t max_len;      // tokens the block table (and the partition grid) covers: longer cache_seqlens entries are cut
+                        // to it and reported through the status word
+  // Split mode with the merge inside this kernel: one int per (sequence, kv head), zero before the launch.  Every CTA
+  // that wrote a partial takes a ticket; the one that takes the last ticket of its (sequence, kv head) merges that
+  // pair's partials into out / lse_out (out_dtype -1: fp32) and puts the ticket back to zero.  nullptr: the partials
+  // are left for the combine kernel.
+  int* tickets;
+  int32_t merge_lse_empty_is_neg;   // merged rows without keys: LSE -inf (partial convention) instead of +inf
+  int32_t merge_sink;               // the merge adds the sink (s_aux) to the row sums
 };
 
 int decode_max_pages_per_partition();
@@ -87,6 +96,7 @@ struct PrefillKernelParams {
   const int32_t* seqused_k;
   int64_t bt_stride;
   int32_t paged, page_size, box_rows;
+  int64_t max_keys;        // paged: keys the block table covers (0 = unknown); longer seqused_k entries are cut and reported
   int64_t o_batch_stride, o_row_stride, o_head_stride;
   int64_t qds_b, qds_h, kds_b, kds_h, vds_b, vds_h;
   int64_t total_q;

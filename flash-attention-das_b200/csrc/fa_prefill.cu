@@ -95,7 +95,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   } else {
     q_row0 = 0; k_row0 = 0; sq = p.seqlen_q; sk = p.seqlen_k; coord_b = bidb;
   }
-  if (p.paged) sk = p.seqused_k[bidb];   // keys live in the paged cache: length from cache_seqlens
+  if (p.paged) {   // keys live in the paged cache: length from cache_seqlens
+    sk = p.seqused_k[bidb];
+    if (p.max_keys > 0 && sk > p.max_keys) {   // longer than the block table row: cut and report
+      sk = static_cast<int>(p.max_keys);
+      if (threadIdx.x == 0) atomicOr(p.status, 0x10000);
+    }
+  }
   const int block_rows = p.sparse ? p.block_m : kBlockM;   // query rows this CTA is responsible for
   const int m0 = m_block * block_rows;
   if (m0 >= sq) return;
@@ -284,16 +290,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (half_tile) lim = min(lim, 64);
       softmax_tile<DT, HDV>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, lim,
                        half_tile || start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st);
-      if (p.paged && start + kBlockN > sk) {
-        // Last tile of a paged sequence: key rows past the end were not fetched, or hold whatever the page holds
-        // there.  Their P is zero, but 0 * NaN would still poison O, so this thread clears V row `row` of the tile
-        // (after it has landed) before the P V product may start.
+      // Key rows of this tile that exist and are selected: the sequence may end inside the tile, and a half tile of a
+      // tile list uses its first 64 keys only.  The other rows hold whatever lies there (the next sequence of a packed
+      // batch, the rest of a page, keys the list left out, or nothing that was fetched).  Their P is zero, but
+      // 0 * NaN would still poison O, so this thread clears V row `row` of the tile (after it has landed) before the
+      // P V product may start, as the reference zero-fills out-of-range rows on load
+      // (csrc/flash_attn_cutlass/src/flash_fwd_kernel.h:319).
+      const int v_rows = min(sk - start, half_tile ? 64 : kBlockN);
+      if (v_rows < kBlockN) {
         const int v_item = 2 * j + 1;
         if (!mbar_wait(smem_u32(&kv_full[v_item % kSlots]), (v_item / kSlots) & 1, wctx)) { ok = false; break; }
         if constexpr (VT) {
           // this thread owns d row `row` of the transposed tile: keys at or past the end are cleared, whole 16-byte
           // pieces (8 keys) where possible, element by element in the piece the end falls into
-          const int lim_k = sk - start;
+          const int lim_k = v_rows;
           const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
@@ -311,7 +321,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             }
             asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
           }
-        } else if (row >= sk - start) {
+        } else if (row >= v_rows) {
           const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
 #pragma unroll
           for (int hf = 0; hf < TV::kHalves; ++hf)

@@ -452,6 +452,26 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         exp_store();
 #undef FA_S_AT
         l_part += rs0 + rs1;
+        if (j + 1 == it.n_tiles) {
+          // Last tile of the sweep: if the sequence ends inside it, the key rows past the end hold the next sequence of
+          // a packed batch (or nothing).  Their P is zero, but 0 * NaN would still poison O: the first column group's
+          // thread of each row clears V row `row` of the tile (after it has landed) before this tile's P V product may
+          // start (every softmax warp arrives on p_full below), as the reference zero-fills out-of-range rows on load
+          // (csrc/flash_attn_cutlass/src/flash_fwd_kernel.h:319).
+          const int lim_k = it.sk - (it.tile0 + j) * kBlockN;
+          if (lim_k < kBlockN && wg == 0) {
+            if (!mbar_wait(smem_u32(&ring_full[v_pos.slot]), v_pos.phase, wctx)) ok = false;
+            if (ok && row >= lim_k) {
+              const uint32_t vrow = ring_smem + v_pos.slot * T::kTileBytes + row * 128;
+#pragma unroll
+              for (int hf = 0; hf < T::kHalves; ++hf)
+#pragma unroll
+                for (int c16 = 0; c16 < 8; ++c16)
+                  asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(vrow + hf * T::kHalfBytes + c16 * 16), "r"(0u) : "memory");
+            }
+            fence_proxy_async_smem();
+          }
+        }
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();

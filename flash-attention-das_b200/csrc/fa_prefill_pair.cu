@@ -13,7 +13,8 @@
 // CTAs claim their items from the virtual item list ordered by descending query block (for causal masks: heaviest
 // first), so prologue, Q loads and epilogue of one item overlap the main loop of its neighbours.  K/V may live in a
 // paged pool (kPaged build): the producer then fetches every key tile page piece by page piece through the block
-// table, and the softmax warpgroups clear the V rows past the end of the sequence in its last tile.  All mbarrier phases simply
+// table.  In every build the softmax warpgroups clear the V rows past the end of the sequence in its last tile, so that
+// what lies behind a sequence (the next one of a packed batch, the rest of a page) cannot reach the output.  All mbarrier phases simply
 // keep counting across items.  Every wait is bounded; a CTA that gives up raises the device status word and leaves
 // through the common teardown (TMEM is always released).
 //
@@ -88,6 +89,10 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
   if (p.paged) {   // keys in a paged pool: their number comes with the block table, rows are addressed page by page
     it.k_row0 = 0;
     it.sk = p.seqused_k[it.bidb];
+    if (p.max_keys > 0 && it.sk > p.max_keys) {   // longer than the block table row: cut and report
+      it.sk = static_cast<int>(p.max_keys);
+      atomicOr(p.status, 0x10000);
+    }
   }
   it.m0 = m_block * kBlockM;
   if (it.m0 >= sq) return false;
@@ -123,7 +128,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint64_t* kv_empty = kv_full + kSlots;
   uint64_t* item_full = kv_empty + kSlots;      // [kItemSlots]
   uint64_t* item_empty = item_full + kItemSlots;
-  Item* item_ring = reinterpret_cast<Item*>(smem + L.item_off);   // 64-byte stride
   uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc_off + 8);
   int* issue_lock = reinterpret_cast<int*>(smem + L.misc_off + 12);   // held while one tile's MMA group is issued
@@ -367,7 +371,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + t * 128;
     const uint32_t t_o = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16) + 256 + t * 128;
     uint32_t sp_cnt = 0, item_cnt = 0;
-    [[maybe_unused]] uint32_t kv_tiles = 0;   // kPaged: key tiles this CTA has consumed so far (tile n's V is ring item 2 n + 1)
     [[maybe_unused]] int tr = 0;
     [[maybe_unused]] const bool tracer = (lane == 0 && lane_grp == 0);
 #ifdef FA_B200_PHASE_TRACE
@@ -394,11 +397,9 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // this row's visible keys [row_first, row_limit) and, for the warp-uniform decision whether a tile needs masking
       // at all, the smallest limit and the largest first key among the warp's rows; all relative to the first tile
       int row_first, row_limit, warp_first, warp_limit;
-      [[maybe_unused]] int sk_rel = 0;
       float scale_log2 = p.scale_log2;
       {
         const int sk = is->sk, m0 = is->m0, shift = is->causal_shift, base = is->tile0 * kBlockN;
-        if constexpr (kPaged) sk_rel = sk - base;
         row_limit = row_hi(p, m0 + row, sk, shift) - base;
         warp_limit = row_hi(p, m0 + lane_grp * 32, sk, shift) - base;
         row_first = kLeftWindow ? row_lo(p, m0 + row, shift) - base : 0;
@@ -423,46 +424,47 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                          start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st);
 #endif
         if (tracer) FA_TRACE(t, tr, 3);
-        if constexpr (kPaged) {
-        if (start + kBlockN > sk_rel) {
-          // Last tile of a paged sequence: key rows past the end were not fetched, or hold whatever the page holds
-          // there.  Their P is zero, but 0 * NaN would still poison O, so this thread clears V row `row` of the tile
-          // (after it has landed) before this tile's P V product may start.  Both softmax warpgroups do it (the two
-          // products read the same V tile; writing zeros twice is harmless).
-          const uint32_t v_item = 2 * kv_tiles + 1;
-          if (!mbar_wait(smem_u32(&kv_full[v_item % kSlots]), (v_item / kSlots) & 1u, wctx)) { ok = false; break; }
-          if constexpr (kVT) {
-            // this thread owns d row `row` of the transposed tile: keys at or past the end are cleared, whole 16-byte
-            // pieces (8 keys) where possible, element by element in the piece the end falls into
-            const int lim_k = sk_rel - start;
-            const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
+        if (j == n_tiles - 1) {
+          // Last tile of the sweep: if the sequence ends inside it, the key rows past the end hold whatever lies there
+          // (the next sequence of a packed batch, the rest of a page, or nothing that was fetched).  Their P is zero,
+          // but 0 * NaN would still poison O, so this thread clears V row `row` of the tile (after it has landed)
+          // before this tile's P V product may start, as the reference zero-fills out-of-range rows on load
+          // (csrc/flash_attn_cutlass/src/flash_fwd_kernel.h:319).  Both softmax warpgroups do it (the two products read
+          // the same V tile; writing zeros twice is harmless).  Key tile n of this CTA has its V in ring item 2 n + 1.
+          const int lim_k = is->sk - (is->tile0 + j) * kBlockN;   // keys of this tile that exist
+          if (lim_k < kBlockN) {
+            const uint32_t v_item = 2 * sp_cnt + 1;
+            if (!mbar_wait(smem_u32(&kv_full[v_item % kSlots]), (v_item / kSlots) & 1u, wctx)) { ok = false; break; }
+            if constexpr (kVT) {
+              // this thread owns d row `row` of the transposed tile: keys at or past the end are cleared, whole 16-byte
+              // pieces (8 keys) where possible, element by element in the piece the end falls into
+              const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const int k0 = c * 8;
-              if (k0 + 8 <= lim_k) continue;
-              const uint32_t addr = vrow + (c >> 3) * T::kHalfBytes + (((c & 7) ^ (row & 7)) << 4);
-              uint32_t w[4] = {0u, 0u, 0u, 0u};
-              if (k0 < lim_k) {
-                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+              for (int c = 0; c < 16; ++c) {
+                const int k0 = c * 8;
+                if (k0 + 8 <= lim_k) continue;
+                const uint32_t addr = vrow + (c >> 3) * T::kHalfBytes + (((c & 7) ^ (row & 7)) << 4);
+                uint32_t w[4] = {0u, 0u, 0u, 0u};
+                if (k0 < lim_k) {
+                  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int ka = k0 + 2 * e;
-                  w[e] = (ka < lim_k ? (w[e] & 0x0000ffffu) : 0u) | (ka + 1 < lim_k ? (w[e] & 0xffff0000u) : 0u);
+                  for (int e = 0; e < 4; ++e) {
+                    const int ka = k0 + 2 * e;
+                    w[e] = (ka < lim_k ? (w[e] & 0x0000ffffu) : 0u) | (ka + 1 < lim_k ? (w[e] & 0xffff0000u) : 0u);
+                  }
                 }
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
               }
-              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            } else if (row >= lim_k) {
+              const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
+#pragma unroll
+              for (int hf = 0; hf < T::kHalves; ++hf)
+#pragma unroll
+                for (int c16 = 0; c16 < 8; ++c16)
+                  asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(vrow + hf * T::kHalfBytes + c16 * 16), "r"(0u) : "memory");
             }
-          } else if (row >= sk_rel - start) {
-            const uint32_t vrow = ring_smem + (v_item % kSlots) * T::kTileBytes + row * 128;
-#pragma unroll
-            for (int hf = 0; hf < T::kHalves; ++hf)
-#pragma unroll
-              for (int c16 = 0; c16 < 8; ++c16)
-                asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(vrow + hf * T::kHalfBytes + c16 * 16), "r"(0u) : "memory");
+            fence_proxy_async_smem();
           }
-          fence_proxy_async_smem();
-        }
-        ++kv_tiles;
         }
         tc_fence_before();
         mbar_arrive(smem_u32(&p_full[t]));

@@ -34,9 +34,18 @@ _DT = {torch.float16: F16, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3}
 _c_i64, _c_i32, _c_f32, _c_vp = ctypes.c_int64, ctypes.c_int32, ctypes.c_float, ctypes.c_void_p
 
 
-class FwdParams(ctypes.Structure):
+class _SizedStruct(ctypes.Structure):
+    """Parameter structs start with ``struct_size``: the library refuses a struct whose size is not its own."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.struct_size = ctypes.sizeof(self)
+
+
+class FwdParams(_SizedStruct):
     """struct fa_b200_fwd_params (include/fa_b200.h)."""
     _fields_ = [
+        ("struct_size", ctypes.c_uint32),
         ("q", _c_vp), ("k", _c_vp), ("v", _c_vp), ("out", _c_vp), ("softmax_lse", _c_vp),
         ("q_batch_stride", _c_i64), ("q_row_stride", _c_i64), ("q_head_stride", _c_i64),
         ("k_batch_stride", _c_i64), ("k_row_stride", _c_i64), ("k_head_stride", _c_i64),
@@ -58,12 +67,14 @@ class FwdParams(ctypes.Structure):
         ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
         ("has_window", _c_i32), ("window_left", _c_i32), ("window_right", _c_i32),
         ("column_count", _c_vp), ("d_v", _c_i32), ("v_transposed", _c_i32), ("work_counter", _c_vp),
+        ("kernel_choice", _c_i32), ("max_blocks_per_seq", _c_i32),
     ]
 
 
-class DecodeParams(ctypes.Structure):
+class DecodeParams(_SizedStruct):
     """struct fa_b200_decode_params (include/fa_b200.h)."""
     _fields_ = [
+        ("struct_size", ctypes.c_uint32),
         ("q", _c_vp), ("k_cache", _c_vp), ("v_cache", _c_vp), ("out", _c_vp), ("softmax_lse", _c_vp),
         ("q_batch_stride", _c_i64), ("q_head_stride", _c_i64),
         ("o_batch_stride", _c_i64), ("o_head_stride", _c_i64),
@@ -87,12 +98,14 @@ class DecodeParams(ctypes.Structure):
         ("seqlen_q", _c_i32), ("is_causal", _c_i32),
         ("q_row_stride", _c_i64), ("o_row_stride", _c_i64),
         ("kv_e4m3", _c_i32), ("kv_e5m2", _c_i32),
+        ("tickets", _c_vp),
     ]
 
 
-class CombineParams(ctypes.Structure):
+class CombineParams(_SizedStruct):
     """struct fa_b200_combine_params (include/fa_b200.h)."""
     _fields_ = [
+        ("struct_size", ctypes.c_uint32),
         ("o_partial", _c_vp), ("lse_partial", _c_vp), ("out", _c_vp), ("lse", _c_vp),
         ("out_row_stride", _c_i64),
         ("num_parts", _c_i32), ("rows", _c_i32), ("d", _c_i32), ("h", _c_i32),
@@ -102,9 +115,10 @@ class CombineParams(ctypes.Structure):
     ]
 
 
-class KvAppendParams(ctypes.Structure):
+class KvAppendParams(_SizedStruct):
     """struct fa_b200_kv_append_params (include/fa_b200.h)."""
     _fields_ = [
+        ("struct_size", ctypes.c_uint32),
         ("k_new", _c_vp), ("v_new", _c_vp),
         ("k_new_batch_stride", _c_i64), ("k_new_row_stride", _c_i64), ("k_new_head_stride", _c_i64),
         ("v_new_batch_stride", _c_i64), ("v_new_row_stride", _c_i64), ("v_new_head_stride", _c_i64),
@@ -164,6 +178,9 @@ _lib.fa_b200_last_cuda_error.restype = ctypes.c_char_p
 _lib.fa_b200_device_status.restype = ctypes.c_int
 _lib.fa_b200_abi_version.restype = ctypes.c_int
 _lib.fa_b200_launch_count.restype = ctypes.c_uint64
+_lib.fa_b200_set_print_param.argtypes = [ctypes.c_int]
+_lib.fa_b200_set_print_param.restype = None
+_lib.fa_b200_last_launch_info.restype = ctypes.c_char_p
 
 
 def lib():
@@ -191,6 +208,17 @@ def _own_work_counter(p, device):
     return None
 
 
+def _own_tickets(p, device, pairs: int):
+    """Under stream capture a split decode call gets ticket counters of its own (graph-private memory, zeroed by a
+    memset node of the graph), so that the captured call is a single launch too and a replay cannot meet another launch
+    on the library's per-stream counters; kept alive by the returned tensor."""
+    if torch.cuda.is_current_stream_capturing():
+        t = torch.zeros(pairs, dtype=torch.int32, device=device)
+        p.tickets = t.data_ptr()
+        return t
+    return None
+
+
 def _apply_profile_events(p):
     if _profile_events is not None:
         p.profile_start_event = _profile_events[0].cuda_event
@@ -199,6 +227,31 @@ def _apply_profile_events(p):
 
 def launch_count() -> int:
     return int(_lib.fa_b200_launch_count())
+
+
+def set_print_param(on: Optional[bool]):
+    """Print one line per attention call with the kernel, grid and tiling the library picked (None: back to the
+    FA_B200_PRINT_PARAM environment variable, which the library reads once when it is loaded)."""
+    _lib.fa_b200_set_print_param(-1 if on is None else int(bool(on)))
+
+
+def last_launch_info() -> str:
+    """The line describing this thread's last attention call (kernel, grid, tiling), whether or not printing is on."""
+    return _lib.fa_b200_last_launch_info().decode()
+
+
+# The library reads its environment switches once, when it is loaded.  This module looks at the same two variables on
+# every call and passes them through the struct fields, so that a process may change them while it runs.
+_KERNEL_CHOICE = {"single": 1, "pair": 2, "dense": 3}
+
+
+def _env_partition() -> int:
+    v = os.environ.get("FA_B200_DECODE_PARTITION")
+    return int(v) if v else 0
+
+
+def _env_kernel() -> int:
+    return _KERNEL_CHOICE.get(os.environ.get("FA_B200_PREFILL_KERNEL", ""), 0)
 
 
 def device_status() -> int:
@@ -217,8 +270,39 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _stream_handle(device) -> int:
+    """The current stream of `device` as an integer handle (without building a torch.cuda.Stream object per call)."""
+    if _raw_stream is not None:
+        return _raw_stream(device.index if device.index is not None else torch.cuda.current_device())
+    return torch.cuda.current_stream(device).cuda_stream
+
+
 def _stream(t: torch.Tensor):
-    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    return ctypes.c_void_p(_stream_handle(t.device))
+
+
+class _on_device:
+    """``with _on_device(dev):`` makes `dev` the current CUDA device for the call; costs nothing when it already is."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = device.index
+
+    def __enter__(self):
+        self.prev = -1
+        if self.idx is not None:
+            cur = torch.cuda.current_device()
+            if cur != self.idx:
+                self.prev = cur
+                torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def _require(cond: bool, msg: str):
@@ -287,6 +371,7 @@ def _set_paged(p, kcache, vcache, block_table, seqused_k, batch):
     p.block_table, p.block_table_batch_stride = block_table.data_ptr(), block_table.stride(0)
     p.seqused_k = seqused_k.data_ptr()
     p.page_size, p.num_blocks = kcache.shape[1], kcache.shape[0]
+    p.max_blocks_per_seq = block_table.shape[1]
 
 
 def _set_sinks(p, s_aux: Optional[torch.Tensor], h: int):
@@ -370,7 +455,8 @@ def fwd(q, k, v, out_, alibi_slopes_, p_dropout, softmax_scale, is_causal, windo
     _set_sinks(p, s_aux_, h)
     _set_window(p, window_size_left, window_size_right)
     _apply_profile_events(p)
-    with torch.cuda.device(q.device):
+    p.kernel_choice = _env_kernel()
+    with _on_device(q.device):
         _counter = _own_work_counter(p, q.device)
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "fwd")
     rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
@@ -449,7 +535,8 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_,
     _set_sinks(p, s_aux_, h)
     _set_window(p, window_size_left, window_size_right)
     _apply_profile_events(p)
-    with torch.cuda.device(q.device):
+    p.kernel_choice = _env_kernel()
+    with _on_device(q.device):
         _counter = _own_work_counter(p, q.device)
         _check(_lib.fa_b200_fwd(ctypes.byref(p), _stream(q)), "varlen_fwd")
     rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
@@ -471,7 +558,7 @@ def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
         return None
     if torch.cuda.is_current_stream_capturing():
         return torch.empty(nbytes, dtype=torch.uint8, device=device)
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, _stream_handle(device))
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -514,7 +601,7 @@ def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out
     _descale(p, "q_descale", q_descale, b, h_k)
     _descale(p, "k_descale", k_descale, b, h_k)
     _descale(p, "v_descale", v_descale, b, h_k)
-    p.partition_tokens = partition_tokens
+    p.partition_tokens = partition_tokens or _env_partition()
     p.max_seqlen_k = max_seqlen_k
     _apply_profile_events(p)
     return p
@@ -579,6 +666,8 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
         fp.o_batch_stride, fp.o_row_stride, fp.o_head_stride = out.stride(0), out.stride(1), out.stride(2)
         fp.b, fp.seqlen_q, fp.h, fp.h_k, fp.d = b, sq, h, h_k, d
         fp.seqlen_k = kcache.shape[1] * block_table_.shape[1]
+        if max_seqlen_k > 0:   # the caller's bound on the cache lengths
+            fp.seqlen_k = min(fp.seqlen_k, max_seqlen_k)
         fp.softmax_scale = softmax_scale
         fp.is_causal = 1 if is_causal else 0
         fp.dtype, fp.out_dtype = _DT[q.dtype], _DT[odt]
@@ -589,7 +678,9 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
         _set_sinks(fp, s_aux_, h)
         _set_window(fp, window_size_left, 0 if is_causal else window_size_right)
         _apply_profile_events(fp)
-        with torch.cuda.device(q.device):
+        fp.kernel_choice = _env_kernel()
+        with _on_device(q.device):
+            _counter = _own_work_counter(fp, q.device)
             _check(_lib.fa_b200_fwd(ctypes.byref(fp), _stream(q)), "fwd_kvcache")
         return [out, lse]
     p = _decode_params(q, kcache, vcache, seqlens_k_, block_table_, softmax_scale, out, lse, q_descale_, k_descale_,
@@ -598,10 +689,11 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     _unsupported(sq > 1 and not is_causal and window_size_right >= 0, "a right window bound with several decode tokens")
     _set_sinks(p, s_aux_, h)
     _set_window(p, window_size_left, -1)   # query tokens at the end of their sequence: only the left side matters
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         ws = _workspace(q.device, int(_lib.fa_b200_decode_workspace_bytes(ctypes.byref(p))))
         if ws is not None:
             p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+            _tickets = _own_tickets(p, q.device, b * h_k)
         _check(_lib.fa_b200_decode_paged(ctypes.byref(p), _stream(q)), "fwd_kvcache")
     return [out, lse]
 
@@ -651,7 +743,7 @@ def kv_cache_attention(q, seq_offsets, max_seqlen_q, max_seqlen_k, k_caches, v_c
         offs = seq_offsets.data_ptr()
     code = F16 if dtype == "fp16" else BF16      # the reference: "fp16", anything else is bf16
     _require(q.dtype == (torch.float16 if code == F16 else torch.bfloat16), "q does not have the dtype named")
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         nbytes = int(_lib.fa_b200_kv_cache_attention_workspace_bytes(num_query, num_q_head, num_kv_head, num_dim,
                                                                      page_size, max_seqlen_k)) if num_query == num_tokens else 0
         ws = _workspace(q.device, nbytes)
@@ -713,7 +805,7 @@ def kv_append(q, kcache, vcache, k_new, v_new, seqlens_k, block_table, rotary_co
     p.b, p.seqlen_q, p.seqlen_new, p.h, p.h_k, p.d = b, sq, k_new.shape[1], h, kcache.shape[2], d
     p.page_size, p.num_blocks, p.max_blocks_per_seq = kcache.shape[1], kcache.shape[0], block_table.shape[1]
     p.dtype = _DT[kcache.dtype]
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         _check(_lib.fa_b200_kv_append(ctypes.byref(p), _stream(q)), "kv_append")
     return q_out, seqlens_out
 
@@ -733,10 +825,11 @@ def decode_partial(q, kcache, vcache, seqlens_k, block_table, softmax_scale, q_d
                        v_descale, 0, max_seqlen_k)
     p.o_partial_out, p.lse_partial_out = o_part.data_ptr(), lse_part.data_ptr()
     _set_window(p, window_left, -1)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         ws = _workspace(q.device, int(_lib.fa_b200_decode_workspace_bytes(ctypes.byref(p))))
         if ws is not None:
             p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+            _tickets = _own_tickets(p, q.device, b * kcache.shape[2])
         _check(_lib.fa_b200_decode_paged(ctypes.byref(p), _stream(q)), "decode_partial")
     return o_part, lse_part
 
@@ -760,7 +853,7 @@ def combine(o_partial, lse_partial, out_dtype=torch.bfloat16, h: Optional[int] =
     p.out_scale = 1.0
     p.o_part_stride, p.lse_part_stride = o_partial.stride(0), lse_partial.stride(0)
     _set_sinks(p, s_aux, h or 1)
-    with torch.cuda.device(o_partial.device):
+    with _on_device(o_partial.device):
         _check(_lib.fa_b200_combine(ctypes.byref(p), _stream(o_partial)), "combine")
     return out, lse
 
@@ -815,7 +908,8 @@ def fwd_sparse(q, k, v, block_count, block_offset, column_count, column_index, o
         _require(tuple(column_count.shape) == (b, h, num_rows), "column_count must have shape (batch, nheads, NUM_ROWS)")
         p.column_count = column_count.data_ptr()
     _apply_profile_events(p)
-    with torch.cuda.device(q.device):
+    p.kernel_choice = _env_kernel()
+    with _on_device(q.device):
         _check(_lib.fa_b200_fwd_sparse(ctypes.byref(p), _stream(q)), "fwd_sparse")
     return [out, lse]
 
@@ -835,7 +929,7 @@ def unpad_plan(attention_mask):
     cu = torch.empty((b + 1,), dtype=torch.int32, device=dev)
     indices = torch.empty((b * s,), dtype=torch.int64, device=dev)
     stats = torch.empty((2,), dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         _check(_lib.fa_b200_unpad_plan(attention_mask.data_ptr(), attention_mask.element_size(), b, s, attention_mask.stride(0),
                                        seqlens.data_ptr(), cu.data_ptr(), indices.data_ptr(), stats.data_ptr(),
                                        _stream(attention_mask)), "unpad_plan")
@@ -849,7 +943,7 @@ def _move_rows(fn, what, src2d, indices, dst2d):
     _require(src2d.is_contiguous() and dst2d.is_contiguous() and src2d.dtype == dst2d.dtype, "rows must be contiguous and of one dtype")
     row_bytes = src2d.shape[1] * src2d.element_size()
     limit = dst2d.shape[0] if fn is _lib.fa_b200_scatter_rows else src2d.shape[0]
-    with torch.cuda.device(src2d.device):
+    with _on_device(src2d.device):
         _check(fn(src2d.data_ptr(), indices.data_ptr(), dst2d.data_ptr(), indices.numel(), row_bytes, limit, _stream(src2d)), what)
 
 
@@ -880,7 +974,7 @@ def block_map_to_offset(block_map, scale=1, fill=10000000):
     rows = bm.numel() // k if k else 0
     off = torch.empty(bm.shape, dtype=torch.int32, device=bm.device)
     cnt = torch.empty(bm.shape[:-1], dtype=torch.int32, device=bm.device)
-    with torch.cuda.device(bm.device):
+    with _on_device(bm.device):
         _check(_lib.fa_b200_block_map_to_offset(bm.data_ptr(), off.data_ptr(), cnt.data_ptr(), rows, k, scale, fill, _stream(bm)),
                "block_map_to_offset")
     return off, cnt
@@ -898,7 +992,7 @@ def block_pool(x, block_rows, sim_threshold):
     nb = (N + block_rows - 1) // block_rows
     pooled = torch.empty((B, H, nb, D), dtype=x.dtype, device=x.device)
     sim = torch.empty((B, H, nb), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         _check(_lib.fa_b200_block_pool(x.data_ptr(), _DT[x.dtype], x.stride(0), x.stride(1), x.stride(2), B, H, N, D,
                                        block_rows, sim_threshold.data_ptr(), pooled.data_ptr(), sim.data_ptr(), _stream(x)),
                "block_pool")
@@ -916,7 +1010,7 @@ def block_select(pooled_q, pooled_k, sim_q, sim_k, block_q, block_k, scale, cdf_
     hyper = cdf_threshold if cdf_threshold is not None else topk
     _require(hyper.is_cuda and hyper.dtype == torch.float32 and hyper.numel() == H, "one float32 threshold per head")
     block_map = torch.empty((B, H, nq, nk), dtype=torch.uint8, device=pooled_q.device)
-    with torch.cuda.device(pooled_q.device):
+    with _on_device(pooled_q.device):
         _check(_lib.fa_b200_block_select(
             pooled_q.data_ptr(), pooled_k.data_ptr(), sim_q.data_ptr(), sim_k.data_ptr(), _DT[pooled_q.dtype], B, H, nq, nk,
             D, block_q, block_k, float(scale), _ptr(cdf_threshold), _ptr(topk), 1 if is_causal else 0,

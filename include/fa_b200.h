@@ -19,7 +19,10 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 1
+/* Version 2: every parameter struct starts with struct_size (callers set it to sizeof of the struct they compiled
+ * against; a call whose struct_size differs from the library's own is refused with FA_B200_ERR_ABI before any other
+ * field is read), the decode struct gained `tickets`, the forward struct `kernel_choice` and `max_blocks_per_seq`. */
+#define FA_B200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define FA_B200_API __attribute__((visibility("default")))
@@ -47,7 +50,8 @@ enum {
   FA_B200_ERR_DEVICE_TIMEOUT = 12, /* a bounded device-side wait gave up (reported by fa_b200_device_status) */
   FA_B200_ERR_TOO_LARGE = 13,    /* size beyond a fixed built-in limit */
   FA_B200_ERR_DEVICE_RANGE = 14, /* a kernel skipped an out-of-range position or page id (fa_b200_device_status) */
-  FA_B200_ERR_DEVICE_UNSUPPORTED = 15 /* a kernel met device-resident input it does not take (fa_b200_device_status) */
+  FA_B200_ERR_DEVICE_UNSUPPORTED = 15, /* a kernel met device-resident input it does not take (fa_b200_device_status) */
+  FA_B200_ERR_ABI = 16           /* struct_size is not the size of this library's struct: header / library mismatch */
 };
 
 /*
@@ -64,6 +68,7 @@ enum {
  * Fully masked rows give out = 0 and lse = +inf.  The causal mask is bottom-right aligned.
  */
 typedef struct fa_b200_fwd_params {
+  uint32_t struct_size;                /* sizeof(fa_b200_fwd_params) */
   const void* q;
   const void* k;
   const void* v;
@@ -132,10 +137,20 @@ typedef struct fa_b200_fwd_params {
    * Needs block_table; F16 / BF16, d = 128, page_size a multiple of 64. */
   int32_t v_transposed;
   /* Optional int32 in device memory, owned by the caller for the duration of the kernel: the persistent prefill kernels
-   * hand out their work items from it (the call zeroes it on the stream first).  NULL = one of 64 counters inside the
-   * library, taken in turn: safe for launches that are ordered on one stream or fewer than 64 in flight.  A caller that
-   * replays a captured launch while other launches run on other streams should give each captured call its own counter. */
+   * hand out their work items from it (the call zeroes it on the stream first).  NULL = a counter inside the library
+   * that belongs to the (device, stream) pair of the call: launches of one stream follow each other and share it,
+   * different streams use different ones (up to 64 streams with launches in flight).  A caller that replays a captured
+   * launch on another stream than it was captured on, while launches run on the capture stream, should give each
+   * captured call its own counter. */
   int32_t* work_counter;
+  /* Kernel choice for this call: 0 = the library decides (or FA_B200_PREFILL_KERNEL, read when the library is loaded),
+   * 1 = one query tile per CTA, 2 = persistent two-heads-per-item kernel, 3 = persistent double-buffered kernel.  A
+   * choice the call cannot take (tile lists, other head dimensions, odd GQA groups for 2 ...) falls back to the
+   * library's own. */
+  int32_t kernel_choice;
+  /* Paged K/V: columns of block_table that hold page ids.  A seqused_k entry beyond max_blocks_per_seq * page_size is
+   * cut to that and reported by fa_b200_device_status() as FA_B200_ERR_DEVICE_RANGE.  0 = not given, not checked. */
+  int32_t max_blocks_per_seq;
 } fa_b200_fwd_params;
 
 /* Replaces mha_fwd / mha_varlen_fwd -> run_mha_fwd -> flash_fwd_kernel_16x64_prefetch
@@ -156,8 +171,12 @@ FA_B200_API int fa_b200_fwd_sparse(const fa_b200_fwd_params* p, void* stream);
  * cache_seqlens: int32 (b).  Physical page of token t of sequence s is
  * block_table[s * block_table_batch_stride + t / page_size], row t % page_size
  * (same addressing as src/paged_attention.cu:146,209 and paged_attention_decode_arch.h:3992-3998).
+ * A cache_seqlens entry beyond what the call covers (max_blocks_per_seq * page_size, or max_seqlen_k if that is
+ * smaller) is cut to it and reported by fa_b200_device_status() as FA_B200_ERR_DEVICE_RANGE: the kernel never reads
+ * past a block_table row.
  */
 typedef struct fa_b200_decode_params {
+  uint32_t struct_size;                /* sizeof(fa_b200_decode_params) */
   const void* q;                       /* (b, 1, h, d) */
   const void* k_cache;
   const void* v_cache;
@@ -190,8 +209,8 @@ typedef struct fa_b200_decode_params {
    * combine; out may then be NULL. */
   float* o_partial_out;
   float* lse_partial_out;
-  /* Optional cudaEvent_t handles recorded right before and right after the partition kernel (the
-   * combine kernel runs after the stop event); NULL = off. */
+  /* Optional cudaEvent_t handles recorded right before and right after the partition kernel (a
+   * separate combine kernel, when one is needed, runs after the stop event); NULL = off. */
   void* profile_start_event;
   void* profile_stop_event;
   /* Attention sinks: as in fa_b200_fwd_params (the reference's decode adds the sink in its first partition,
@@ -223,6 +242,14 @@ typedef struct fa_b200_decode_params {
    * src/paged_attention.cu:747-1149 takes both fp8 formats): an e5m2 value is the high byte of an f16, so the
    * conversion on the way into the products is a byte move. */
   int32_t kv_e5m2;
+  /* Split-KV merge inside the decode kernel.  When a call is split into partitions, the CTA that finishes last for a
+   * (sequence, kv head) merges that pair's partials itself, so the call is one launch.  The CTAs count themselves on one
+   * int32 per pair.  NULL = the library's own counters, one block per (device, stream) for up to 64 streams with
+   * launches in flight and 4096 pairs per launch; beyond that, and on a stream that is being captured into a CUDA
+   * graph, the call falls back to a second launch (the LSE-combine kernel).  A caller that wants the single launch
+   * under capture, or more pairs, passes b * h_k int32 of its own here: zero before the first use (the kernel leaves
+   * them zero), not shared by launches that can overlap on the GPU. */
+  int32_t* tickets;
 } fa_b200_decode_params;
 
 /* Replaces mha_fwd_kvcache -> paged_attention(layout=2) -> paged_attention_kernel (+ combine)
@@ -247,6 +274,9 @@ FA_B200_API int fa_b200_decode_paged(const fa_b200_decode_params* p, void* strea
  *  - All calls on a device share the one array, and it keeps whatever the previous call left there (every
  *    slot a call reads is written by that call first, so nothing needs clearing).  Two calls whose kernels can
  *    overlap on the GPU (different streams, no ordering between them) race on it: serialise them.
+ *  - If fa_b200_device_status() reports FA_B200_ERR_DEVICE_TIMEOUT after a call, throw that call's output away: a
+ *    CTA that gave up on a wait wrote no partial, so the merge read what an earlier call had left in its slot, and
+ *    the result can look plausible while being wrong.
  */
 #define FA_B200_STATIC_SCRATCH_BYTES (32u << 20)
 FA_B200_API int fa_b200_decode_paged_static(const fa_b200_decode_params* p, void* stream);
@@ -268,6 +298,7 @@ FA_B200_API int32_t fa_b200_decode_partition_tokens(const fa_b200_decode_params*
  * flash_fwd_splitkv_reduce_varlen_kernel (csrc/flash_attn_hipc/src/flash_fwd_reduce.h:313-464).
  */
 typedef struct fa_b200_combine_params {
+  uint32_t struct_size;                /* sizeof(fa_b200_combine_params) */
   const float* o_partial;
   const float* lse_partial;
   void* out;
@@ -345,6 +376,7 @@ FA_B200_API size_t fa_b200_kv_cache_attention_workspace_bytes(int32_t num_query,
  * seqlens_out must not alias seqlens_k.  One kernel launch; nothing is allocated.
  */
 typedef struct fa_b200_kv_append_params {
+  uint32_t struct_size;                /* sizeof(fa_b200_kv_append_params) */
   const void* k_new;                   /* (b, seqlen_new, h_k, d) */
   const void* v_new;
   int64_t k_new_batch_stride, k_new_row_stride, k_new_head_stride;   /* elements */
@@ -407,6 +439,13 @@ FA_B200_API const char* fa_b200_last_cuda_error(void);
  * FA_B200_ERR_DEVICE_UNSUPPORTED if fa_b200_fwd_sparse met a non-zero column_count. */
 FA_B200_API int fa_b200_device_status(void);
 FA_B200_API int fa_b200_abi_version(void);
+/* One line on stderr per attention call with the kernel, grid and tiling the library picked (what the reference prints
+ * under FLASH_ATTENTION_PRINT_PARAM, csrc/flash_attn_cutlass/flash_api.cpp:219-222, and PA_PRINT_PARAM,
+ * src/paged_attention.cu:40).  on = 1 / 0 switches it for the process; -1 goes back to the environment variable
+ * FA_B200_PRINT_PARAM, which the library reads once when it is loaded.  fa_b200_last_launch_info() returns the line of
+ * the calling thread's last attention call whether or not printing is on ("" before the first call). */
+FA_B200_API void fa_b200_set_print_param(int on);
+FA_B200_API const char* fa_b200_last_launch_info(void);
 /* Number of kernels this library has launched in this process (for launch accounting). */
 FA_B200_API uint64_t fa_b200_launch_count(void);
 

@@ -10,6 +10,10 @@ re-checked by ``tests/test_oracle_golden.py`` on CPU.
 
 Each function cites the reference code it follows (paths relative to the reference project).
 All math is fp32 on the CPU ("upcast=True" in the reference's vocabulary) unless stated.
+
+The attention functions follow their inputs' device, so the GPU tests can also evaluate the same statements in
+fp32 on the device over whole configurations (TF32 off); such a device-side evaluation is tied back to the pinned
+CPU evaluation on a subset by the tests that use it.
 """
 from __future__ import annotations
 
@@ -24,11 +28,11 @@ E4M3_MAX = 448.0
 # ----------------------------------------------------------------------------------------------
 # dense / fixed-length
 # ----------------------------------------------------------------------------------------------
-def causal_mask_bottom_right(seqlen_q: int, seqlen_k: int) -> torch.Tensor:
+def causal_mask_bottom_right(seqlen_q: int, seqlen_k: int, device=None) -> torch.Tensor:
     """True where the score is masked OUT.  Follows construct_local_mask with window (-1, 0):
     ``col > row + seqlen_k - seqlen_q`` (tests/test_flash_attn.py:185-217)."""
-    row = torch.arange(seqlen_q, dtype=torch.long).view(-1, 1)
-    col = torch.arange(seqlen_k, dtype=torch.long)
+    row = torch.arange(seqlen_q, dtype=torch.long, device=device).view(-1, 1)
+    col = torch.arange(seqlen_k, dtype=torch.long, device=device)
     return col > row + seqlen_k - seqlen_q
 
 
@@ -70,11 +74,11 @@ def attention_ref(q, k, v, causal=False, upcast=True, reorder_ops=False, softmax
     scores = torch.einsum("bthd,bshd->bhts", qs, ks)
     masked = None
     if causal:
-        masked = causal_mask_bottom_right(sq, sk)
+        masked = causal_mask_bottom_right(sq, sk, q.device)
     if window_size[0] >= 0 or window_size[1] >= 0:
-        row = torch.arange(sq, dtype=torch.long).view(-1, 1)
-        col = torch.arange(sk, dtype=torch.long).view(1, -1)
-        wmask = torch.zeros(sq, sk, dtype=torch.bool)
+        row = torch.arange(sq, dtype=torch.long, device=q.device).view(-1, 1)
+        col = torch.arange(sk, dtype=torch.long, device=q.device).view(1, -1)
+        wmask = torch.zeros(sq, sk, dtype=torch.bool, device=q.device)
         if window_size[0] >= 0:
             wmask |= col < row + sk - sq - window_size[0]
         if window_size[1] >= 0:
@@ -121,10 +125,10 @@ def attention_varlen_ref(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, upca
         vi = v[ck[b]:ck[b + 1]][None]
         if ki.shape[1] == 0:
             is_fp8 = q.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
-            outs.append(torch.zeros(qi.shape[1], q.shape[1], v.shape[-1],
+            outs.append(torch.zeros(qi.shape[1], q.shape[1], v.shape[-1], device=q.device,
                                     dtype=out_dtype or (torch.bfloat16 if is_fp8 else q.dtype)))
             if s_aux is None:
-                lses.append(torch.full((q.shape[1], qi.shape[1]), float("inf")))
+                lses.append(torch.full((q.shape[1], qi.shape[1]), float("inf"), device=q.device))
             else:   # the sink is the only term of such a row's sum, as for fully masked rows in attention_ref
                 lses.append(s_aux.float().reshape(-1, 1).expand(q.shape[1], qi.shape[1]).clone())
             continue
@@ -179,9 +183,9 @@ def paged_decode_ref(q, k_cache, v_cache, cache_seqlens, block_table, softmax_sc
         vi = gather_paged_kv(v_cache, block_table[i], L)[None]
         if L == 0:
             is_fp8 = q.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
-            outs.append(torch.zeros(1, q.shape[1], q.shape[2], q.shape[3],
+            outs.append(torch.zeros(1, q.shape[1], q.shape[2], q.shape[3], device=q.device,
                                     dtype=out_dtype or (torch.bfloat16 if is_fp8 else q.dtype)))
-            lses.append(torch.full((1, q.shape[2], q.shape[1]), float("inf")))
+            lses.append(torch.full((1, q.shape[2], q.shape[1]), float("inf"), device=q.device))
             continue
         o, l = attention_ref(
             q[i:i + 1], ki, vi, causal=causal, softmax_scale=softmax_scale, upcast=upcast,

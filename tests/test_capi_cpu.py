@@ -27,7 +27,7 @@ def test_every_declared_symbol_is_exported(binding):
     lib = binding.lib()
     for n in names:
         assert hasattr(lib, n), n
-    assert lib.fa_b200_abi_version() == 1
+    assert lib.fa_b200_abi_version() == 2
 
 
 def test_struct_sizes_match_header(binding):
@@ -45,6 +45,32 @@ def test_struct_sizes_match_header(binding):
                 continue
             fields += [re.findall(r"(\w+)\s*$", x.strip())[0] for x in stmt.split(",")]
         assert fields == [f[0] for f in cls._fields_], struct
+
+
+def test_a_struct_of_another_size_is_refused(binding):
+    """Every parameter struct starts with its own size: a caller built against another header version (a shorter or a
+    longer struct) is told so before any other field is read."""
+    lib = binding.lib()
+    calls = ((binding.FwdParams, lib.fa_b200_fwd), (binding.FwdParams, lib.fa_b200_fwd_sparse),
+             (binding.DecodeParams, lib.fa_b200_decode_paged), (binding.DecodeParams, lib.fa_b200_decode_paged_static),
+             (binding.CombineParams, lib.fa_b200_combine), (binding.KvAppendParams, lib.fa_b200_kv_append))
+    for cls, fn in calls:
+        p = cls()
+        assert p.struct_size == ctypes.sizeof(cls)
+        for wrong in (0, p.struct_size - 8, p.struct_size + 8):
+            p.struct_size = wrong
+            assert fn(ctypes.byref(p), None) == 16, (cls.__name__, wrong)
+    d = binding.DecodeParams()
+    d.struct_size = 8
+    assert lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) == 0
+    assert lib.fa_b200_decode_partition_tokens(ctypes.byref(d)) == 0
+    assert b"struct_size" in lib.fa_b200_status_string(16)
+
+
+def test_launch_description_is_empty_before_any_call(binding):
+    assert binding.last_launch_info() == "" or binding.last_launch_info().startswith("fa_b200 ")
+    binding.set_print_param(False)
+    binding.set_print_param(None)
 
 
 def test_status_strings(binding):
