@@ -3,19 +3,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-One "step" is one pass of the hot path over one batch of seeded synthetic input.  The default workload is the
-paged-KV bf16 decode configuration (batch 64, context 1024..32768, page 256, 32/8 heads, d 128): the
-`value` is whole-job HBM GB/s of ALGORITHMIC bytes (KV bytes read once + q/out + block table) with the cache
-resident in HBM; `e2e` is the same metric through the public Python API with the step's inputs (q,
-cache_seqlens, block_table) coming from pinned host memory and the output read back to the host inside the
-timed region, every step; the decode and prefill workloads run those steps as a serving loop would, on three
-streams with two sets of device buffers, so that one step's copies overlap its neighbours' attention.  The varlen causal bf16 prefill configuration is timed in the same run and reported under
-`also` (TFLOP/s, reference FLOP convention 4*S^2*H*D/2 per sequence).
+One "step" is one pass of the hot path over one batch of seeded synthetic input.  The headline workload is the
+paged-KV bf16 decode configuration (batch 64, context 1024..32768, page 256, 32/8 heads, d 128): `value` is whole-job
+HBM GB/s of ALGORITHMIC bytes (KV bytes read once + q/out + block table) with the cache resident in HBM; `e2e` is the
+same metric through the public Python API with the step's inputs (q, cache_seqlens, block_table) coming from pinned
+host memory and the output read back to the host inside the timed region, every step; the decode and prefill
+workloads run those steps as a serving loop would, on three streams with two sets of device buffers, so that one
+step's copies overlap its neighbours' attention.  The other configurations are timed in the same run and reported under
+`also`: varlen causal prefill bf16 (TFLOP/s, reference FLOP convention 4*S^2*H*D/2 per sequence), e4m3 decode and
+prefill, block-sparse prefill and the single 1,048,576-token decode.  Every entry carries a `check`: the maximum
+absolute error of the timed call's output against the fp32 oracle on a stated subset, computed outside the timed region.
 
-Multi-GPU (torchrun, one rank per GPU): every rank runs the same per-GPU workload on its own seeded data with
-no data-path collective ("weak" scaling); the time is the max over ranks of the CUDA-event time between two
-barriers.  `--workload longseq` is the one case with an exchange step: a single 1,048,576-token sequence is
-split-KV across the ranks and the partial (O, LSE) are all-gathered with NCCL before the combine kernel.
+Multi-GPU (torchrun, one rank per GPU): the SAME configurations, sharded over the ranks with no data-path collective
+("strong" scaling: the total work is fixed, value = total algorithmic bytes or FLOPs / the slowest rank's step time
+between two barriers): decode batches by sequence (longest-processing-time on the lengths), prefill over a
+(sequence group, kv-head group) grid, block-sparse prefill by kv head; each rank builds only its own shard.  The one
+case with an exchange step is the single 1,048,576-token sequence, split-KV across the ranks by page range: the partial
+(O, LSE) are all-gathered with NCCL before the combine kernel (its three phases are also timed one by one).  The
+whole-batch-per-rank figure ("weak" scaling) is kept under `also` as `decode_bf16_replica`.
+`--shard-of W [--shard-rank R]` runs rank R's share of a W-way job on one GPU without any collective (sizing a shard
+without the machine that would run it).
 
 `--impl reference` times the CPU oracle (the reference's PyTorch attention restated in oracle/) on the host
 cores over a bounded sample of the same workload; under torchrun only rank 0 runs it.
@@ -42,8 +49,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, as a multiple of the
 # algorithmic bytes, from the ncu captures summarised under profiles/ (None = not captured yet).
 # decode: measured on a quarter of the batch (traffic grows in proportion to the tokens streamed).
-TRAFFIC_RATIO = {"decode_bf16": 1.007, "decode_fp8": 1.013, "prefill_bf16": None, "prefill_fp8": None,
-                 "sparse_bf16": None, "longseq": 1.007}
+TRAFFIC_RATIO = {"decode_bf16": 1.007, "decode_bf16_replica": 1.007, "decode_fp8": 1.013, "prefill_bf16": None,
+                 "prefill_fp8": None, "sparse_bf16": None, "longseq": 1.007}
 # prefill is tensor-bound, its algorithmic unit is FLOPs; DRAM traffic is reported in bytes per token of the
 # captured case (521.5 MB for 19,679 tokens, 1.29x the compulsory q+k+v+out bytes).
 # block-sparse: the full configuration was captured (3.251 GB read + 0.237 GB written for its 32,768 tokens).
@@ -198,25 +205,52 @@ class E2EPipeline:
             self.ev_out[buf].record(self.s_out)
 
 
+def _shard_helpers():
+    from flash_attn import split_kv_parallel
+    return split_kv_parallel
+
+
+def _err(a, b):
+    return float((a.float() - b.float()).abs().max().item())
+
+
+def decode_config(cg, fp8, batch, page, shard):
+    """Lengths of this rank's sequences and the `config` object of a decode workload (no device needed: the reference
+    arm describes the same configuration)."""
+    if fp8:
+        batch = batch or 128
+        all_lens = torch.full((batch,), 8192, dtype=torch.int64)
+    else:
+        batch = batch or 64
+        all_lens = torch.randint(1024, 32769, (batch,), generator=cg)
+    rank, world = shard
+    owned = _shard_helpers().shard_sequences_lpt(all_lens.tolist(), world)[rank]
+    lens = all_lens[owned]
+    pool = int(((lens + page - 1) // page).sum())
+    es = 1 if fp8 else 2
+    # algorithmic bytes: every K and V byte once + q + out + the used block-table entries
+    units = float(int(lens.sum()) * HK * D * 2 * es + len(lens) * H * D * (es + 2) + 4 * pool)
+    desc = {"workload": ("paged-KV decode e4m3: batch %d x context 8192" % batch) if fp8 else
+            "paged-KV decode bf16: batch %d, context uniform[1024,32768]" % batch,
+            "page_block_size": page, "nheads": H, "nheads_kv": HK, "headdim": D,
+            "sharding": "by sequence, longest-processing-time on the lengths: %d of %d sequences on rank %d of %d" %
+                        (len(lens), batch, rank, world),
+            "tokens": int(lens.sum()), "l2": "inputs larger than L2 (KV pool of this rank %.2f GB)" % (units / 1e9)}
+    return lens, units, desc
+
+
 class DecodeWorkload:
     """Paged-KV decode: batch of single-token queries over a paged pool; block_table is a seeded random
-    permutation of the pool."""
+    permutation of the pool.  `shard` = (rank, world): this rank's sequences of the batch (LPT on the lengths)."""
 
-    def __init__(self, dev, seed, fp8=False, batch=None, lens=None, page=256, rank=0):
+    def __init__(self, dev, seed, fp8=False, batch=None, page=256, shard=(0, 1), data_rank=0, name=None):
         import flash_attn
         self.fa = flash_attn
         self.fp8 = fp8
-        self.name = "decode_fp8" if fp8 else "decode_bf16"
-        # the shapes (sequence lengths) are the same on every rank: per-GPU work is fixed under weak scaling;
-        # the values differ per rank
+        self.name = name or ("decode_fp8" if fp8 else "decode_bf16")
         cg = torch.Generator().manual_seed(seed)
-        if lens is None:
-            if fp8:
-                batch = batch or 128
-                lens = torch.full((batch,), 8192, dtype=torch.int64)
-            else:
-                batch = batch or 64
-                lens = torch.randint(1024, 32769, (batch,), generator=cg)
+        rank, world = shard
+        lens, self.units, self.desc = decode_config(cg, fp8, batch, page, shard)
         self.lens = lens
         self.batch = len(lens)
         self.page = page
@@ -228,7 +262,7 @@ class DecodeWorkload:
         for i, n in enumerate(nblk.tolist()):
             bt[i, :n] = perm[p:p + n]
             p += n
-        dg = _cuda_gen(dev, seed + 1 + 1000 * rank)
+        dg = _cuda_gen(dev, seed + 1 + 1000 * (rank + data_rank))
         dt = torch.bfloat16
         self.kc = torch.empty(pool, page, HK, D, dtype=dt, device=dev)
         self.vc = torch.empty(pool, page, HK, D, dtype=dt, device=dev)
@@ -251,19 +285,31 @@ class DecodeWorkload:
         self.sl = self.sl_host.to(dev)
         self.out_host = torch.empty(self.batch, 1, H, D, dtype=torch.bfloat16).pin_memory()
         es = 1 if fp8 else 2
-        # algorithmic bytes: every K and V byte once + q + out + the used block-table entries
-        self.units = float(int(lens.sum()) * HK * D * 2 * es + self.batch * H * D * (es + 2) + 4 * pool)
         self.unit_name = "bytes"
         self.h2d = self.q_host.numel() * es + self.bt_host.numel() * 4 + self.sl_host.numel() * 4
         self.d2h = self.out_host.numel() * 2
-        self.desc = {"workload": ("paged-KV decode e4m3: batch %d x context 8192" % self.batch) if fp8 else
-                     "paged-KV decode bf16: batch %d, context uniform[1024,32768]" % self.batch,
-                     "page_block_size": page, "nheads": H, "nheads_kv": HK, "headdim": D,
-                     "tokens": int(lens.sum()), "l2": "inputs larger than L2 (KV pool %.2f GB)" % (self.units / 1e9)}
 
     def step(self):
         return self.fa.flash_attn_with_kvcache(self.q, self.kc, self.vc, cache_seqlens=self.sl, block_table=self.bt,
                                                causal=True, **self.kw)
+
+    def check(self):
+        """Timed call's output against the fp32 oracle evaluated on the device for the shortest, the longest and the
+        middle sequence of this rank's shard."""
+        from oracle import attention_oracle as O
+        out = self.step()
+        order = torch.argsort(self.lens)
+        picks = sorted({int(order[0]), int(order[-1]), int(order[len(order) // 2])})
+        worst = 0.0
+        for b in picks:
+            kw = {k: v.reshape(1, 1).expand(1, HK) for k, v in self.kw.items()}
+            ref, _ = O.paged_decode_ref(self.q[b:b + 1], self.kc, self.vc, self.sl[b:b + 1], self.bt[b:b + 1],
+                                        out_dtype=torch.float32, **kw)
+            worst = max(worst, _err(out[b:b + 1], ref))
+        tol = 7e-2 if self.fp8 else 1e-2
+        return {"max_abs_err": worst, "tolerance": tol, "ok": worst <= tol,
+                "subset": "%d of this rank's %d sequences (shortest, middle, longest), all heads; oracle in fp32 on the device" %
+                          (len(picks), self.batch)}
 
     def e2e_setup(self):
         dev = self.q.device
@@ -291,21 +337,26 @@ class DecodeWorkload:
 
 
 class PrefillWorkload:
-    """Packed varlen causal GQA prefill."""
+    """Packed varlen causal GQA prefill.  `shard` = (rank, world): this rank's cell of the (sequence group, kv-head
+    group) grid."""
 
-    def __init__(self, dev, seed, fp8=False, nseq=None, rank=0):
+    def __init__(self, dev, seed, fp8=False, nseq=None, shard=(0, 1)):
         import flash_attn
         self.fa = flash_attn
         self.fp8 = fp8
         self.name = "prefill_fp8" if fp8 else "prefill_bf16"
         cg = torch.Generator().manual_seed(seed)
         nseq = nseq or (8 if fp8 else 16)
-        lens = torch.full((nseq,), 4096, dtype=torch.int64) if fp8 else torch.randint(512, 4097, (nseq,), generator=cg)
+        all_lens = torch.full((nseq,), 4096, dtype=torch.int64) if fp8 else torch.randint(512, 4097, (nseq,), generator=cg)
+        rank, world = shard
+        sg, hg, owned = _shard_helpers().shard_prefill_grid(all_lens.tolist(), HK, world)
+        lens = all_lens[owned[rank // hg]]
+        self.h, self.hk = H // hg, HK // hg
         self.lens = lens
         total = int(lens.sum())
         dg = _cuda_gen(dev, seed + 1 + 1000 * rank)
         mk = lambda h: torch.randn(total, h, D, generator=dg, device=dev, dtype=torch.float32).to(torch.bfloat16)
-        q, k, v = mk(H), mk(HK), mk(HK)
+        q, k, v = mk(self.h), mk(self.hk), mk(self.hk)
         self.kw = {}
         if fp8:
             qd, kd, vd = [(t.abs().max().float() / 448.0).reshape(1) for t in (q, k, v)]
@@ -316,28 +367,57 @@ class PrefillWorkload:
         self.cu = self.cu_host.to(dev)
         self.maxlen = int(lens.max())
         self.q_host, self.k_host, self.v_host = [t.cpu().pin_memory() for t in (q, k, v)]
-        self.out_host = torch.empty(total, H, D, dtype=torch.bfloat16).pin_memory()
+        self.out_host = torch.empty(total, self.h, D, dtype=torch.bfloat16).pin_memory()
         # reference FLOP convention: 4 * S^2 * H * D / 2 per causal sequence (benchmarks/benchmark_attnmask.py:24-30)
-        self.units = float((4 * lens.double() ** 2 * H * D / 2).sum())
+        self.units = float((4 * lens.double() ** 2 * self.h * D / 2).sum())
         self.unit_name = "flops"
         es = 1 if fp8 else 2
         self.h2d = (q.numel() + k.numel() + v.numel()) * es + self.cu_host.numel() * 4
         self.d2h = self.out_host.numel() * 2
         self.desc = {"workload": ("varlen causal prefill e4m3: %d x 4096" % nseq if fp8 else
                                   "varlen causal GQA prefill bf16: %d sequences, length uniform[512,4096]" % nseq),
-                     "nheads": H, "nheads_kv": HK, "headdim": D, "tokens": total,
-                     "l2": "inputs larger than L2 (q+k+v %.0f MB)" % ((q.numel() + 2 * k.numel()) * es / 1e6)}
+                     "nheads": H, "nheads_kv": HK, "headdim": D,
+                     "sharding": "%d sequence group(s) (LPT on length^2) x %d kv-head group(s): rank %d of %d has %d sequences, "
+                                 "%d query / %d kv heads" % (sg, hg, rank, world, len(lens), self.h, self.hk),
+                     "tokens": total,
+                     "l2": "inputs larger than L2 (q+k+v of this rank %.0f MB)" % ((q.numel() + 2 * k.numel()) * es / 1e6)}
 
     def step(self):
         return self.fa.flash_attn_varlen_func(self.q, self.k, self.v, self.cu, self.cu, self.maxlen, self.maxlen,
                                               causal=True, **self.kw)
+
+    def check(self):
+        """The shortest and the longest sequence of this rank, all of its heads, against the fp32 oracle on the device."""
+        from oracle import attention_oracle as O
+        out = self.step()
+        picks = sorted({int(self.lens.argmin()), int(self.lens.argmax())})
+        worst, worst_ref = 0.0, 0.0
+        for i in picks:
+            lo, hi = int(self.cu_host[i]), int(self.cu_host[i + 1])
+            kw = {k: v.reshape(1, 1).expand(1, self.hk) for k, v in self.kw.items()}
+            ref, _ = O.attention_ref(self.q[lo:hi][None], self.k[lo:hi][None], self.v[lo:hi][None], causal=True,
+                                     out_dtype=torch.float32, **kw)
+            worst = max(worst, _err(out[lo:hi][None], ref))
+            # the tolerance is relative to what the same math gives with P rounded to the input type
+            if self.fp8:
+                ref_p, _ = O.attention_ref(self.q[lo:hi][None], self.k[lo:hi][None], self.v[lo:hi][None], causal=True,
+                                           out_dtype=torch.float32, intermediate_dtype=torch.float8_e4m3fn, **kw)
+            else:
+                ref_p, _ = O.attention_ref(self.q[lo:hi][None], self.k[lo:hi][None], self.v[lo:hi][None], causal=True,
+                                           upcast=False, reorder_ops=True)
+            worst_ref = max(worst_ref, _err(ref_p, ref))
+            del ref, ref_p
+        tol = 2 * worst_ref + (2 ** -7 if self.fp8 else 2 ** -8)
+        return {"max_abs_err": worst, "tolerance": tol, "ok": worst <= tol,
+                "subset": "%d of this rank's %d sequences (shortest, longest), all of its heads; oracle in fp32 on the device; "
+                          "tolerance = 2 x the error of the same math with P in the input type" % (len(picks), len(self.lens))}
 
     def e2e_setup(self):
         dev = self.q.device
         self.pipe = E2EPipeline(dev)
         self.d_qkv = [[torch.empty_like(t) for t in (self.q, self.k, self.v)] for _ in range(2)]
         self.d_cu = [torch.empty_like(self.cu) for _ in range(2)]
-        self.d_out = [torch.empty(self.q.shape[0], H, D, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.d_out = [torch.empty(self.q.shape[0], self.h, D, dtype=torch.bfloat16, device=dev) for _ in range(2)]
         self.out_hosts = [self.out_host, torch.empty_like(self.out_host).pin_memory()]
 
     def step_e2e(self):
@@ -373,28 +453,34 @@ def tile_mask_to_block_lists(tile_mask):
 
 class SparseWorkload:
     """Block-sparse causal GQA prefill, one 32768-token sequence, 128x128 tile mask at 25 % density per head
-    (diagonal tiles always kept)."""
+    (diagonal tiles always kept).  `shard` = (rank, world): this rank's kv heads and their query heads."""
 
-    def __init__(self, dev, seed, seqlen=32768, density=0.25, rank=0):
+    def __init__(self, dev, seed, seqlen=32768, density=0.25, shard=(0, 1)):
         import flash_attn
         self.fa = flash_attn
         self.name = "sparse_bf16"
+        rank, world = shard
+        if HK % world:
+            raise SystemExit("block-sparse prefill shards by kv head: the rank count must divide %d" % HK)
+        self.h, self.hk = H // world, HK // world
         cg = torch.Generator().manual_seed(seed)
         n = seqlen // 128
         tm = torch.rand(1, H, n, n, generator=cg) < density
         tril = torch.tril(torch.ones(n, n, dtype=torch.bool))
         tm = (tm & tril) | torch.eye(n, dtype=torch.bool)
+        tm = tm[:, rank * self.h:(rank + 1) * self.h].contiguous()
+        self.tm = tm
         cnt, offs = tile_mask_to_block_lists(tm)
         self.kept = int(tm.sum())
         dg = _cuda_gen(dev, seed + 1 + 1000 * rank)
         mk = lambda h: torch.randn(1, seqlen, h, D, generator=dg, device=dev, dtype=torch.float32).to(torch.bfloat16)
-        self.q, self.k, self.v = mk(H), mk(HK), mk(HK)
+        self.q, self.k, self.v = mk(self.h), mk(self.hk), mk(self.hk)
         self.cnt, self.offs = cnt.to(dev), offs.to(dev)
-        self.cc = torch.zeros(1, H, n, dtype=torch.int32, device=dev)
-        self.ci = torch.zeros(1, H, n, 1, dtype=torch.int32, device=dev)
+        self.cc = torch.zeros(1, self.h, n, dtype=torch.int32, device=dev)
+        self.ci = torch.zeros(1, self.h, n, 1, dtype=torch.int32, device=dev)
         self.q_host, self.k_host, self.v_host = [t.cpu().pin_memory() for t in (self.q, self.k, self.v)]
         self.cnt_host, self.offs_host = cnt.pin_memory(), offs.pin_memory()
-        self.out_host = torch.empty(1, seqlen, H, D, dtype=torch.bfloat16).pin_memory()
+        self.out_host = torch.empty(1, seqlen, self.h, D, dtype=torch.bfloat16).pin_memory()
         # kept tiles x 4*128*128*128 FLOPs, diagonal tiles counted as full tiles
         self.units = float(self.kept) * 4 * 128 * 128 * 128
         self.unit_name = "flops"
@@ -402,13 +488,43 @@ class SparseWorkload:
         self.d2h = self.out_host.numel() * 2
         self.desc = {"workload": "block-sparse causal GQA prefill bf16: 1 x %d, 128x128 tiles at %.0f%% density" %
                      (seqlen, density * 100), "kept_tiles": self.kept, "tokens": seqlen, "nheads": H, "nheads_kv": HK, "headdim": D,
-                     "l2": "inputs larger than L2 is NOT true here (q+k+v %.0f MB): L2 flushed between steps" %
+                     "sharding": "by kv head: rank %d of %d has %d query / %d kv heads" % (rank, world, self.h, self.hk),
+                     "l2": "inputs are NOT larger than L2 here (q+k+v of this rank %.0f MB): L2 flushed between steps" %
                      ((self.q.numel() + 2 * self.k.numel()) * 2 / 1e6)}
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def step(self):
         self.flush.zero_()
         return self.fa.sparse_attn_func(self.q, self.k, self.v, self.cnt, self.offs, self.cc, self.ci, causal=True)
+
+    def check(self):
+        """Whole query tiles (head, q-block) against the fp32 oracle on the device: only the kept key tiles are gathered,
+        the causal mask acts inside the diagonal tile (the last kept one)."""
+        from oracle import attention_oracle as O
+        out = self.step()
+        n = self.tm.shape[-1]
+        cg = torch.Generator().manual_seed(11)
+        pairs = {(0, 0), (self.h - 1, n - 1)}
+        while len(pairs) < 12:
+            pairs.add((int(torch.randint(0, self.h, (1,), generator=cg)), int(torch.randint(0, n, (1,), generator=cg))))
+        worst, worst_ref = 0.0, 0.0
+        for head, m in sorted(pairs):
+            kept = torch.nonzero(self.tm[0, head, m]).flatten().tolist()
+            rows = slice(m * 128, m * 128 + 128)
+            hk = head // (self.h // self.hk)
+            ks = torch.cat([self.k[0, j * 128:(j + 1) * 128, hk] for j in kept])[None, :, None]
+            vs = torch.cat([self.v[0, j * 128:(j + 1) * 128, hk] for j in kept])[None, :, None]
+            qs = self.q[0, rows, head][None, :, None]
+            mask = torch.zeros(128, len(kept) * 128, dtype=torch.bool, device=qs.device)
+            if kept[-1] == m:
+                mask[:, -128:] = torch.triu(torch.ones(128, 128, dtype=torch.bool, device=qs.device), diagonal=1)
+            ref, _ = O.attention_ref(qs, ks, vs, out_dtype=torch.float32, extra_mask=mask)
+            ref_p, _ = O.attention_ref(qs, ks, vs, upcast=False, reorder_ops=True, extra_mask=mask)
+            worst = max(worst, _err(out[0, rows, head], ref[0, :, 0]))
+            worst_ref = max(worst_ref, _err(ref_p, ref))
+        tol = 2 * worst_ref + 2 ** -8
+        return {"max_abs_err": worst, "tolerance": tol, "ok": worst <= tol,
+                "subset": "%d (head, query block) tiles of this rank, whole tiles; oracle in fp32 on the device" % len(pairs)}
 
     def step_e2e(self):
         dev = self.q.device
@@ -423,13 +539,16 @@ class LongSeqWorkload:
     """One sequence of 1,048,576 tokens, split-KV across the ranks by page range; each rank decodes its slice to
     an fp32 partial (O, LSE); the partials are all-gathered (NCCL) and combined on every rank."""
 
-    def __init__(self, dev, seed, rank, world, total_tokens=1 << 20, page=256):
+    def __init__(self, dev, seed, shard, real_world, total_tokens=1 << 20, page=256):
         import flash_attn_2_cuda
         self.cuda = flash_attn_2_cuda
         self.name = "longseq"
-        self.world = world
-        local = total_tokens // world
-        pool = local // page
+        rank, world = shard
+        self.world, self.real_world = world, real_world
+        npages = total_tokens // page
+        first, last = _shard_helpers().split_page_range(npages, world, rank)
+        pool = last - first
+        local = pool * page
         cg = torch.Generator().manual_seed(seed)  # same q on every rank
         dg = _cuda_gen(dev, seed + 1 + rank)
         self.kc = torch.empty(pool, page, HK, D, dtype=torch.bfloat16, device=dev)
@@ -446,15 +565,54 @@ class LongSeqWorkload:
         self.out_host = torch.empty(H, D, dtype=torch.bfloat16).pin_memory()
         self.desc = {"workload": "single-sequence %d-token bf16 decode, split-KV across %d GPU(s), NCCL allgather of (O, LSE)" %
                      (total_tokens, world), "page_block_size": page, "nheads": H, "nheads_kv": HK, "headdim": D,
-                     "l2": "inputs larger than L2 (%.2f GB per GPU)" % (self.units / 1e9)}
+                     "sharding": "by page range: rank %d of %d holds pages [%d, %d)" % (rank, world, first, last),
+                     "l2": "inputs larger than L2 (%.2f GB on this rank)" % (self.units / 1e9)}
 
-    def _run(self, q):
+    def _run(self, q, events=None):
         from flash_attn.split_kv_parallel import decode_split_across_gpus
-        out, _ = decode_split_across_gpus(q, self.kc, self.vc, self.sl, self.bt, D ** -0.5)
+        out, _ = decode_split_across_gpus(q, self.kc, self.vc, self.sl, self.bt, D ** -0.5, phase_events=events)
         return out
 
     def step(self):
         return self._run(self.q)
+
+    def check(self):
+        """Every rank evaluates the fp32 oracle on kv head 2 (query heads 8..11) of its own slice on the device; the
+        partials are all-gathered and merged by the oracle's merge; the kernel path's output (partition kernel, NCCL
+        all-gather of the packed [O | LSE], combine kernel) is compared with that."""
+        from oracle import attention_oracle as O
+        from flash_attn.split_kv_parallel import gather_partials
+        import torch.distributed as dist
+        out = self.step()
+        hk, g = 2, H // HK
+        pages = self.bt[0].long()
+        kk = self.kc[pages, :, hk].reshape(-1, D)[None, :, None]
+        vv = self.vc[pages, :, hk].reshape(-1, D)[None, :, None]
+        o, l = O.attention_ref(self.q[:, :, hk * g:(hk + 1) * g], kk, vv, out_dtype=torch.float32)
+        o, l = o.reshape(g, D).contiguous(), l.reshape(g).contiguous()
+        if self.real_world > 1 and dist.is_initialized():
+            o_all, l_all = gather_partials(o, l)
+        else:
+            o_all, l_all = o[None], l[None]
+        ref, _ = O.merge_partials_ref(o_all, l_all)
+        e = _err(out.view(H, D)[hk * g:(hk + 1) * g], ref)
+        return {"max_abs_err": e, "tolerance": 1e-2, "ok": e <= 1e-2,
+                "subset": "kv head 2 (query heads 8..11) over the whole sequence: each rank's slice by the fp32 oracle on the "
+                          "device, partials gathered and merged by the oracle's merge"}
+
+    def phases(self, steps):
+        """Average device time of the three phases of a step, from CUDA events on the launching stream."""
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+        for _ in range(3):
+            self._run(self.q)
+        torch.cuda.synchronize()
+        for e in ev:
+            self._run(self.q, e)
+        torch.cuda.synchronize()
+        avg = lambda i: sum(e[i].elapsed_time(e[i + 1]) for e in ev) / steps * 1e3
+        return {"partition_kernel_with_local_merge_us": round(avg(0), 2), "all_gather_us": round(avg(1), 2),
+                "final_combine_us": round(avg(2), 2), "note": "measured one step at a time with events between the phases; "
+                "the all-gather is an NCCL call on the same stream (no call at one rank)"}
 
     def step_e2e(self):
         out = self._run(self.q_host.to(self.q.device, non_blocking=True))
@@ -462,19 +620,21 @@ class LongSeqWorkload:
         return out
 
 
-def make_workload(name, dev, seed, rank, world, scale=1.0):
+def make_workload(name, dev, seed, shard, real_world, scale=1.0):
     if name == "decode_bf16":
-        return DecodeWorkload(dev, seed, batch=max(1, int(64 * scale)), rank=rank)
+        return DecodeWorkload(dev, seed, batch=max(1, int(64 * scale)), shard=shard)
+    if name == "decode_bf16_replica":   # the whole batch on every rank, other values per rank ("weak" scaling)
+        return DecodeWorkload(dev, seed, batch=max(1, int(64 * scale)), shard=(0, 1), data_rank=shard[0], name=name)
     if name == "decode_fp8":
-        return DecodeWorkload(dev, seed, fp8=True, batch=max(1, int(128 * scale)), rank=rank)
+        return DecodeWorkload(dev, seed, fp8=True, batch=max(1, int(128 * scale)), shard=shard)
     if name == "prefill_bf16":
-        return PrefillWorkload(dev, seed, nseq=max(1, int(16 * scale)), rank=rank)
+        return PrefillWorkload(dev, seed, nseq=max(1, int(16 * scale)), shard=shard)
     if name == "prefill_fp8":
-        return PrefillWorkload(dev, seed, fp8=True, nseq=max(1, int(8 * scale)), rank=rank)
+        return PrefillWorkload(dev, seed, fp8=True, nseq=max(1, int(8 * scale)), shard=shard)
     if name == "sparse_bf16":
-        return SparseWorkload(dev, seed, rank=rank)
+        return SparseWorkload(dev, seed, shard=shard)
     if name == "longseq":
-        return LongSeqWorkload(dev, seed, rank, world)
+        return LongSeqWorkload(dev, seed, shard, real_world)
     raise ValueError(name)
 
 
@@ -550,9 +710,24 @@ def time_kernel_alone(wl, steps, warmup):
     return sum(ts) / len(ts), ts[len(ts) // 2]
 
 
-def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
+def host_us_per_call(wl, calls=200):
+    """Wall time the host spends inside one public API call when the stream is idle (median), in microseconds."""
+    for _ in range(10):
+        wl.step()
+    ts = []
+    for _ in range(calls):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        wl.step()
+        ts.append(time.perf_counter() - t0)
+    torch.cuda.synchronize()
+    ts.sort()
+    return round(ts[len(ts) // 2] * 1e6, 1)
+
+
+def run_workload(name, args, dev, rank, world, shard, peaks, cpu_budget):
     import flash_attn_2_cuda
-    wl = make_workload(name, dev, args.seed, rank, world, args.scale)
+    wl = make_workload(name, dev, args.seed, shard, world, args.scale)
     metric, unit, div = METRIC[wl.unit_name]
     sampler = ClockSampler(dev.index)
     with sampler as cs:
@@ -563,6 +738,7 @@ def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
             wl.e2e_setup()
         ms_e2e = time_steps(wl.step_e2e, args.steps, args.warmup, world, dev, getattr(wl, "pipe", None))
     clocks = cs.summary()
+    launch_info = flash_attn_2_cuda.last_launch_info()
     total_units = sum_over_ranks(wl.units, world, dev)
     value = total_units / (ms * 1e-3) / div
     e2e = total_units / (ms_e2e * 1e-3) / div
@@ -575,9 +751,17 @@ def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
         peak = peaks["bf16_tflops"] * (2.0 if "fp8" in name else 1.0)
         bound, punit = "tensor", "TFLOP/s"
     ratio = TRAFFIC_RATIO.get(name)
+    # correctness of what was timed, outside the timed region; every rank checks its own shard, the worst is reported
+    check = wl.check()
+    check["max_abs_err"] = round(max_over_ranks(check["max_abs_err"], world, dev), 6)
+    check["tolerance"] = round(max_over_ranks(check["tolerance"], world, dev), 6)
+    check["ok"] = bool(max_over_ranks(0.0 if check["ok"] else 1.0, world, dev) == 0.0)
+    check["device_status"] = int(max_over_ranks(float(flash_attn_2_cuda.device_status()), world, dev))
+    replica = name.endswith("_replica")
     res = {
-        "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "name": name, "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak" if replica else "strong",
         "vs_baseline": None, "dtype": "e4m3" if "fp8" in name else "bf16", "data": "synthetic (seeded)",
         "config": wl.desc,
         "e2e": {"value": round(e2e, 2), "unit": unit, "h2d_bytes_per_step": int(wl.h2d), "d2h_bytes_per_step": int(wl.d2h),
@@ -588,12 +772,22 @@ def run_workload(name, args, dev, rank, world, peaks, with_cpu_baseline):
                      "traffic": (ratio * wl.units if ratio is not None else
                                  (PREFILL_TRAFFIC_BYTES_PER_TOKEN[name] * wl.desc["tokens"]
                                   if name in PREFILL_TRAFFIC_BYTES_PER_TOKEN else None)),
+                     "traffic_source": "ncu capture of a smaller case (profiles/), scaled by the units processed",
                      "kernel_ms_avg": round(k_avg, 4), "kernel_ms_median": round(k_med, 4),
-                     "algorithmic_per_launch": wl.units},
+                     "algorithmic_per_launch": wl.units, "rank": rank},
+        "check": check,
         "clocks": clocks,
+        "kernel": launch_info,
     }
-    if with_cpu_baseline and rank == 0:
-        res["cpu_baseline"] = cpu_baseline(name, args.seed, budget_s=args.cpu_budget)
+    if shard[1] != world:
+        res["config"]["emulated"] = "rank %d of a %d-way job on one GPU, no collective" % shard
+    if "decode" in name:
+        res["host_us_per_call"] = host_us_per_call(wl)
+    if name == "longseq":
+        res["phases"] = wl.phases(max(args.steps, 10))
+        res["host_us_per_call"] = host_us_per_call(wl, 100)
+    if cpu_budget > 0 and rank == 0:
+        res["cpu_baseline"] = cpu_baseline(name, args.seed, budget_s=cpu_budget)
     del wl
     torch.cuda.empty_cache()
     return res
@@ -648,25 +842,33 @@ def cpu_baseline(name, seed, budget_s=15.0):
 
 
 def run_reference(args, rank, world):
-    """--impl reference: the CPU restatement of the reference's PyTorch attention on the host cores."""
+    """--impl reference: the CPU restatement of the reference's PyTorch attention on the host cores, W warm-up and K
+    timed steps, each step a bounded sample of the configuration our own arm is quoted on."""
     if rank != 0:
         return
-    name = "decode_bf16" if args.workload in ("default", "all") else args.workload
+    name = "decode_bf16" if args.workload in ("default", "all", "decode_bf16_replica") else args.workload
     metric, unit, _ = METRIC["bytes" if ("decode" in name or name == "longseq") else "flops"]
+    n_all = args.steps + args.warmup
+    per_step = max(0.5, min(args.cpu_budget / 2, 150.0 / n_all))   # the whole run ends within a few minutes
+    for i in range(args.warmup):
+        cpu_baseline(name, args.seed + 1000 + i, budget_s=per_step)
     vals = []
-    for _ in range(args.warmup if args.warmup < 2 else 1):
-        cpu_baseline(name, args.seed, budget_s=2.0)
     t0 = time.perf_counter()
-    for i in range(max(1, min(args.steps, 5))):
-        vals.append(cpu_baseline(name, args.seed + i, budget_s=args.cpu_budget / 2))
+    for i in range(args.steps):
+        vals.append(cpu_baseline(name, args.seed + i, budget_s=per_step))
     dt = time.perf_counter() - t0
     v = sum(x["value"] for x in vals) / len(vals)
     cb = dict(vals[-1])
     cb["value"] = round(v, 4)
+    cb["sample"] = "each of the %d steps: %s" % (len(vals), cb["sample"])
+    if name == "decode_bf16":   # the headline: the same `config` object as our own arm prints
+        _, _, config = decode_config(torch.Generator().manual_seed(args.seed), False, max(1, int(64 * args.scale)), 256, (0, world))
+    else:
+        config = {"workload": name}
     line = {"impl": "reference", "metric": metric, "value": round(v, 4), "unit": unit, "n_gpus": world,
-            "steps": len(vals), "warmup": 1, "ms_per_step": round(dt / len(vals) * 1e3, 2), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
-            "config": {"workload": name + " (bounded CPU sample: " + cb["sample"] + ")"},
+            "steps": len(vals), "warmup": args.warmup, "ms_per_step": round(dt / len(vals) * 1e3, 2), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+            "config": config,
             "cpu_baseline": cb,
             "e2e": {"value": round(v, 4), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -680,12 +882,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="default",
-                    choices=["default", "all", "decode_bf16", "prefill_bf16", "decode_fp8", "prefill_fp8", "sparse_bf16", "longseq"])
+                    choices=["default", "all", "decode_bf16", "decode_bf16_replica", "prefill_bf16", "decode_fp8",
+                             "prefill_fp8", "sparse_bf16", "longseq"])
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample")
+    ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for each cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scale", type=float, default=1.0,
                     help="shrink the batch / sequence count (profiler captures on a small case); 1.0 = the baseline configuration")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="one GPU only: run one rank's share of a job sharded this many ways (no collective)")
+    ap.add_argument("--shard-rank", type=int, default=0, help="with --shard-of: which rank's share")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -701,22 +907,28 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    shard = (rank, world)
+    if args.shard_of > 0:
+        if world != 1:
+            raise SystemExit("--shard-of is for a single process")
+        shard = (args.shard_rank, args.shard_of)
     peaks = load_peaks()
-    if args.workload == "default":
-        names = ["decode_bf16", "prefill_bf16"]
-    elif args.workload == "all":
-        names = ["decode_bf16", "prefill_bf16", "decode_fp8", "prefill_fp8", "sparse_bf16", "longseq"]
+    if args.workload in ("default", "all"):
+        names = ["decode_bf16"] + (["decode_bf16_replica"] if world > 1 else []) + \
+                ["prefill_bf16", "decode_fp8", "prefill_fp8", "sparse_bf16", "longseq"]
     else:
         names = [args.workload]
     results = []
     for i, n in enumerate(names):
-        results.append(run_workload(n, args, dev, rank, world, peaks,
-                                    with_cpu_baseline=(world == 1 and not args.no_cpu_baseline)))
+        # the CPU port is timed beside the two headline metrics (decode bytes, prefill FLOPs) on rank 0 of a one-GPU run
+        cpu = args.cpu_budget if (world == 1 and not args.no_cpu_baseline and n in ("decode_bf16", "prefill_bf16")) else 0.0
+        results.append(run_workload(n, args, dev, rank, world, shard, peaks, cpu))
     if rank == 0:
         line = results[0]
         if len(results) > 1:
-            line["also"] = [{k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "config", "e2e",
-                                                 "gpu_launches", "roofline", "cpu_baseline") if k in r}
+            line["also"] = [{k: r[k] for k in ("name", "metric", "value", "unit", "ms_per_step", "scaling", "dtype", "config",
+                                                 "e2e", "gpu_launches", "roofline", "check", "clocks", "kernel", "phases",
+                                                 "host_us_per_call", "cpu_baseline") if k in r}
                             for r in results[1:]]
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -26,6 +26,9 @@ __device__ int g_work_counters[kStreamSlots];
 __device__ int g_tickets[kStreamSlots * kTicketsPerSlot];
 
 std::atomic<uint64_t> g_launches{0};
+#ifdef FA_B200_TEST_HOOKS
+std::atomic<int> g_test_withhold{0};   // the next decode / two-tile prefill launch withholds one tile load
+#endif
 thread_local char g_last_error[256] = "";
 thread_local char g_launch_info[320] = "";
 
@@ -288,6 +291,12 @@ size_t decode_ws_bytes(const fa_b200_decode_params* p, const DecodePlan& pl) {
 using namespace fa;
 
 extern "C" {
+
+#ifdef FA_B200_TEST_HOOKS
+// Test library only (not declared in the public header): the next decode or two-tile prefill launch of this process
+// announces one tile load and never issues it, so that a bounded device-side wait runs out.
+__attribute__((visibility("default"))) void fa_b200_test_withhold_load(int on) { g_test_withhold.store(on ? 1 : 0); }
+#endif
 
 int fa_b200_abi_version(void) { return FA_B200_ABI_VERSION; }
 void fa_b200_set_print_param(int on) { g_print_param.store(on < 0 ? -1 : (on ? 1 : 0)); }
@@ -575,6 +584,9 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.q_row_stride = p->q_row_stride;
   k.o_row_stride = p->o_row_stride;
   k.max_len = pl.max_len;
+#ifdef FA_B200_TEST_HOOKS
+  k.test_withhold = g_test_withhold.exchange(0);
+#endif
   bool merge_in_kernel = false;
   if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
@@ -840,6 +852,9 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
   if (choice == 1) which = 0;
   else if (choice == 2 && !one_tile_only && even_group) which = 1;
   else if (choice == 3 && !one_tile_only && !paged) which = 2;
+#ifdef FA_B200_TEST_HOOKS
+  if (which == 1) k.test_withhold = g_test_withhold.exchange(0);
+#endif
   if (which != 0) {   // the persistent kernels claim their work items from a counter
     if (p->work_counter) {   // the caller's own counter
       if (cudaMemsetAsync(p->work_counter, 0, sizeof(int), stream) != cudaSuccess) return cuda_fail("work counter", cudaGetLastError());

@@ -17,7 +17,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 // A wait on an mbarrier gives up after this many SM clock cycles (about two seconds).
+// FA_B200_TEST_HOOKS builds a second library for the failure-detection tests only: its waits give up after about a
+// millisecond, and a launch can be told to withhold one tile load so that a wait does run out (fa_b200_test_withhold_load).
+#ifdef FA_B200_TEST_HOOKS
+constexpr long long kWaitLimitCycles = 2000000ll;
+#else
 constexpr long long kWaitLimitCycles = 4000000000ll;
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -285,6 +285,10 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         for (int j = 0; j < boxes_per_tile; ++j) nvalid += (tok0 + j * box_tok < tok_end) ? 1 : 0;
         const uint32_t fb = smem_u32(&full_bar[s]);
         mbar_expect_tx(fb, 2u * T::kHalves * nvalid * box_bytes);
+#ifdef FA_B200_TEST_HOOKS
+        // failure-detection test: the bytes announced above never arrive, the consumers' wait runs out
+        if (p.test_withhold && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) continue;
+#endif
         const uint32_t kdst = smem_u32(stages + s * kStageBytes);
         const uint32_t vdst = kdst + kStageBytes / 2;
         for (int j = 0; j < nvalid; ++j) {

@@ -48,6 +48,7 @@ struct DecodeKernelParams {
   int* tickets;
   int32_t merge_lse_empty_is_neg;   // merged rows without keys: LSE -inf (partial convention) instead of +inf
   int32_t merge_sink;               // the merge adds the sink (s_aux) to the row sums
+  int32_t test_withhold;            // FA_B200_TEST_HOOKS builds only: CTA (0, 0, 0) announces its first tile and never loads it
 };
 
 int decode_max_pages_per_partition();
@@ -118,6 +119,7 @@ struct PrefillKernelParams {
   int32_t d;              // head dimension: 128, or 64 / 192 / 256 (16-bit types, one-tile kernel)
   int32_t d_v;            // head dimension of v and out (= d, or 128 with d = 192)
   int32_t v_transposed;   // paged V pool with the tokens contiguous: tmap_v describes (page tokens, d, h_k, block), box (64, 128, 1, 1)
+  int32_t test_withhold;  // FA_B200_TEST_HOOKS builds only: CTA 0 announces the first K tile of its first item and never loads it
 };
 // One 128-row query tile per CTA, two CTAs per SM: block-sparse lists and odd GQA groups.
 cudaError_t launch_prefill_single(int dtype, const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,

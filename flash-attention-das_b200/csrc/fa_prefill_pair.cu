@@ -238,6 +238,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             const CUtensorMap* tm = kv ? &tmap_v : &tmap_k;
             if constexpr (!kPaged) {
               mbar_expect_tx(bar, T::kTileBytes);
+#ifdef FA_B200_TEST_HOOKS
+              // failure-detection test: the bytes announced above never arrive, the MMA issuers' wait runs out
+              if (p.test_withhold && kv_cnt == 0 && blockIdx.x == 0) { ++kv_cnt; continue; }
+#endif
 #pragma unroll
               for (int hf = 0; hf < T::kHalves; ++hf)
                 tma_load_4d(ring_smem + slot * T::kTileBytes + hf * T::kHalfBytes, tm, bar, hf * 64, it.hk,

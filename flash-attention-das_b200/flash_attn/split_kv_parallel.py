@@ -30,6 +30,29 @@ def shard_sequences_lpt(lengths: Sequence[int], world_size: int, power: float = 
     return [sorted(o) for o in owned]
 
 
+def shard_prefill_grid(lengths: Sequence[int], h_k: int, world_size: int) -> Tuple[int, int, List[List[int]]]:
+    """Two-axis split of a prefill batch: ``world_size = seq_groups * head_groups`` with ``head_groups`` dividing the kv
+    heads.  Sequences go to the sequence groups by LPT on length squared (causal FLOPs); every rank of a sequence group
+    takes the same sequences and one contiguous slice of the kv heads (and of the query heads that belong to them), so
+    each rank still makes ONE varlen call and nothing is exchanged.  Of the admissible factorisations the one with the
+    smallest largest load is taken (ties: fewer head groups, i.e. wider K/V sharing inside a rank) — a few long sequences
+    go to the head axis, many sequences to the sequence axis.
+    Returns (seq_groups, head_groups, owned) with owned[g] = sorted sequence indices of sequence group g; rank r works on
+    sequence group r // head_groups and kv heads [hg * h_k / head_groups, (hg + 1) * h_k / head_groups), hg = r % head_groups."""
+    best = None
+    for hg in range(1, min(h_k, world_size) + 1):
+        if h_k % hg or world_size % hg:
+            continue
+        sg = world_size // hg
+        owned = shard_sequences_lpt(lengths, sg, power=2.0)
+        load = max(sum(float(lengths[i]) ** 2 for i in o) for o in owned) / hg
+        if best is None or load < best[0] * (1 - 1e-9):
+            best = (load, sg, hg, owned)
+    if best is None:
+        raise ValueError("world_size must be a product of a sequence split and a divisor of the kv heads")
+    return best[1], best[2], best[3]
+
+
 def split_page_range(num_pages: int, world_size: int, rank: int) -> Tuple[int, int]:
     """Contiguous page range [first, last) of one sequence owned by `rank` (earlier ranks take the remainder)."""
     base, rem = divmod(num_pages, world_size)
@@ -72,17 +95,24 @@ def gather_partials(o_partial: torch.Tensor, lse_partial: torch.Tensor,
 
 def decode_split_across_gpus(q, k_cache_local, v_cache_local, local_seqlens, local_block_table, softmax_scale=None,
                              group: Optional[dist.ProcessGroup] = None, out_dtype=torch.bfloat16, q_descale=None,
-                             k_descale=None, v_descale=None, s_aux=None, local_window_left: int = -1):
+                             k_descale=None, v_descale=None, s_aux=None, local_window_left: int = -1,
+                             phase_events: Optional[Sequence["torch.cuda.Event"]] = None):
     """Decode where each rank holds a slice of every sequence's KV pages.  q: (b, 1, h, 128), identical on every
     rank; the caches, `local_seqlens` and `local_block_table` describe this rank's slice.  Attention sinks
     (``s_aux``, (h)) enter once, in the final combine; a sliding window is given per slice (``window_for_slice``).
-    Returns (out (b, 1, h, 128) out_dtype, lse (b, h) fp32), identical on every rank."""
+    Returns (out (b, 1, h, 128) out_dtype, lse (b, h) fp32), identical on every rank.
+    ``phase_events``: four CUDA events recorded on the current stream before the local decode, after it (partition
+    kernel with its in-kernel merge), after the all-gather and after the final combine (timing of the three phases)."""
     import flash_attn_2_cuda as cuda
     b, _, h, d = q.shape
     if softmax_scale is None:
         softmax_scale = d ** -0.5
+    if phase_events is not None:
+        phase_events[0].record()
     o_part, l_part = cuda.decode_partial(q, k_cache_local, v_cache_local, local_seqlens, local_block_table,
                                          softmax_scale, q_descale, k_descale, v_descale, window_left=local_window_left)
+    if phase_events is not None:
+        phase_events[1].record()
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         rows = b * h
         if (o_part.is_cuda and (rows * (d + 1)) % 4 == 0 and
@@ -98,5 +128,9 @@ def decode_split_across_gpus(q, k_cache_local, v_cache_local, local_seqlens, loc
             o_all, l_all = gather_partials(o_part.view(rows, d), l_part.view(rows), group)
     else:
         o_all, l_all = o_part.view(1, b * h, d), l_part.view(1, b * h)
+    if phase_events is not None:
+        phase_events[2].record()
     out, lse = cuda.combine(o_all, l_all, out_dtype=out_dtype, h=h, s_aux=s_aux)
+    if phase_events is not None:
+        phase_events[3].record()
     return out.view(b, 1, h, d), lse.view(b, h)

@@ -106,3 +106,31 @@ def test_lpt_sharding_properties():
     for n, w in ((4096, 8), (11, 2), (5, 8)):
         r = [P.split_page_range(n, w, k) for k in range(w)]
         assert r[0][0] == 0 and r[-1][1] == n and all(r[i][1] == r[i + 1][0] for i in range(w - 1))
+
+
+def test_prefill_grid_sharding():
+    """The (sequence group, kv-head group) grid of a prefill batch: a partition of the work, balanced, deterministic."""
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(
+        "split_kv_parallel", os.path.join(root, "flash-attention-das_b200", "flash_attn", "split_kv_parallel.py"))
+    P = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(P)
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(512, 4097, (16,), generator=g).tolist()
+    total = sum(l * l for l in lens)
+    for world in (1, 2, 4, 8):
+        sg, hg, owned = P.shard_prefill_grid(lens, 8, world)
+        assert sg * hg == world and 8 % hg == 0 and len(owned) == sg
+        assert sorted(i for o in owned for i in o) == list(range(16))
+        worst = max(sum(lens[i] ** 2 for i in o) for o in owned) / hg
+        assert worst <= total / world * 1.0001          # few ragged sequences: the head axis balances exactly
+        assert (sg, hg, owned) == P.shard_prefill_grid(lens, 8, world)
+    # many equal sequences: the sequence axis is enough, K/V sharing inside a rank stays as wide as possible
+    assert P.shard_prefill_grid([4096] * 8, 8, 8)[:2] == (8, 1)
+    assert P.shard_prefill_grid([4096] * 8, 8, 4)[:2] == (4, 1)
+    # sixteen ranks over eight kv heads and three sequences: both axes
+    sg, hg, owned = P.shard_prefill_grid([1000, 3000, 2000], 8, 16)
+    assert sg * hg == 16 and 8 % hg == 0
+    with pytest.raises(ValueError):
+        P.shard_prefill_grid([100], 2, 0)   # no rank, no factorisation

@@ -1,8 +1,8 @@
 """GPU: fa_b200_decode_paged_static, the decode entry point for callers that cannot allocate or pass scratch
 (a plugin inside a server that forbids allocation after start-up, or code that does not own a buffer to hand
 over): its split-KV partials live in a fixed array inside the library.  Called straight through the C ABI, it
-must give what fa_b200_decode_paged gives with a caller workspace, on two calls in a row (the array is shared
-and keeps the previous call's contents), and must refuse sizes beyond the array.
+must give what fa_b200_decode_paged gives with a caller workspace (and what the oracle gives), on two calls in a row
+(the array is shared and keeps the previous call's contents), and must refuse sizes beyond the array.
 
 Collected last on purpose, so that a run that stops at the first failure has already run every other test.
 """
@@ -11,7 +11,8 @@ import ctypes
 import pytest
 import torch
 
-from _util import gen, make_paged, randn
+from oracle import attention_oracle as O
+from _util import clean_nan, gen, make_paged, max_err, randn
 
 pytestmark = pytest.mark.gpu
 
@@ -38,6 +39,7 @@ def test_static_scratch_matches_workspace_entry_point_twice(lens, partition):
         g = gen(1234 + round_)
         kc, vc, bt, sl = make_paged(g, lens, h_k, 64, torch.bfloat16)
         q = randn(g, len(lens), 1, h, 128).cuda()
+        ref32, ref_lse = O.paged_decode_ref(q.cpu(), clean_nan(kc), clean_nan(vc), sl, bt, out_dtype=torch.float32)
         kc, vc, bt, sl = kc.cuda(), vc.cuda(), bt.cuda(), sl.cuda()
         out_a = torch.empty(len(lens), 1, h, 128, dtype=torch.bfloat16, device="cuda")
         lse_a = torch.empty(len(lens), h, 1, dtype=torch.float32, device="cuda")
@@ -54,6 +56,10 @@ def test_static_scratch_matches_workspace_entry_point_twice(lens, partition):
         # same kernels, same partition plan: the tests' tolerance (atol 1e-2) is met with room to spare
         assert torch.allclose(out_b.float(), out_a.float(), atol=1e-2, rtol=1e-2)
         assert torch.equal(out_b, out_a) and torch.equal(lse_b, lse_a)
+        # and against the oracle itself, not only against its sibling (the reference's decode tolerance)
+        assert torch.allclose(out_b.cpu().float(), ref32, atol=1e-2, rtol=1e-2)
+        fin = torch.isfinite(ref_lse)
+        assert max_err(lse_b.cpu()[fin], ref_lse[fin]) < 1e-3
 
 
 def test_static_scratch_refuses_sizes_beyond_the_array():
