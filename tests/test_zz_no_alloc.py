@@ -30,7 +30,7 @@ def _call(cuda, fn, p, q):
     return st
 
 
-@pytest.mark.parametrize("lens,partition", [([3000, 130, 1, 2049], 512), ([700, 5000, 0], 1024)])
+@pytest.mark.parametrize("lens,partition", [([3000, 130, 1, 2049], 512), ([700, 5000, 0], 1024), ([3000, 130, 1, 2049, 0], 0)])
 def test_static_scratch_matches_workspace_entry_point_twice(lens, partition):
     import flash_attn_2_cuda as cuda
     lib = cuda.lib()
