@@ -192,7 +192,6 @@ bool stride_ok(int64_t s, int es) { return s >= 0 && (s * es) % 16 == 0; }
 // csrc/flash_attn_cutlass/src/flash.h:20-25):
 //   FA_B200_DECODE_PARTITION=<tokens>        partition size of the split-KV decode (0 / unset: heuristic)
 //   FA_B200_PREFILL_KERNEL=single|pair|dense prefill kernel, where that kernel can take the call
-//   FA_B200_DECODE_CTAS=<n>                  CTAs of the balanced decode kernel (default: two per SM, one above d = 128)
 //   FA_B200_PRINT_PARAM=1                    one line on stderr per attention call: kernel, grid, tiling
 //                                            (the reference: FLASH_ATTENTION_PRINT_PARAM, flash_api.cpp:219-222;
 //                                            PA_PRINT_PARAM, src/paged_attention.cu:40)
@@ -201,9 +200,7 @@ struct EnvConfig {
   int decode_partition = 0;
   int prefill_kernel = 0;   // 0 auto, 1 single, 2 pair, 3 dense
   int print_param = 0;
-  int decode_ctas = 0;
   EnvConfig() {
-    if (const char* v = getenv("FA_B200_DECODE_CTAS")) decode_ctas = atoi(v);
     if (const char* v = getenv("FA_B200_DECODE_PARTITION")) decode_partition = atoi(v);
     if (const char* v = getenv("FA_B200_PREFILL_KERNEL")) {
       if (!strcmp(v, "single")) prefill_kernel = 1;
@@ -228,11 +225,7 @@ struct DecodePlan {
   int status;
   int group, tile, box_tok, partition_tokens, num_partitions, max_len;
   bool split;
-  bool balanced;   // the default: equal shares of the tile list per CTA (fa_decode_balanced.cu)
 };
-
-// The balanced kernel's grid never exceeds this many CTAs (two per SM on a B200 are 296); its scratch is sized for it.
-constexpr int kBalancedMaxCtas = 320;
 
 DecodePlan plan_decode(const fa_b200_decode_params* p) {
   DecodePlan pl{};
@@ -261,7 +254,6 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   pl.max_len = static_cast<int>(max_len);
   const int unit = pl.tile > page ? (pl.tile % page == 0 ? pl.tile : pl.tile * page) : (page % pl.tile == 0 ? page : pl.tile * page);
   int part = p->partition_tokens > 0 ? p->partition_tokens : g_env.decode_partition;
-  const bool forced_partition = part > 0;
   if (part > 0) {
     if (part % pl.tile != 0 || (part % page != 0 && page % part != 0)) { pl.status = FA_B200_ERR_SHAPE; return pl; }
   } else {
@@ -284,23 +276,11 @@ DecodePlan plan_decode(const fa_b200_decode_params* p) {
   pl.partition_tokens = part;
   pl.num_partitions = max_len > 0 ? static_cast<int>((max_len + part - 1) / part) : 1;
   pl.split = pl.num_partitions > 1 || p->o_partial_out != nullptr;
-  // Whatever would be split runs on the balanced kernel unless the caller (or the environment) fixed a partition size
-  // or the batch is larger than its in-kernel prefix sum takes.  Short caches (one partition per sequence) keep the
-  // direct path, which needs no scratch at all.
-  pl.balanced = pl.split && !forced_partition && p->b <= decode_balanced_max_batch() && p->h_k <= 64 &&
-                static_cast<int64_t>(p->b) * ((max_len + pl.tile - 1) / pl.tile + 1) < (1ll << 31);
   return pl;
 }
 
 size_t decode_ws_bytes(const fa_b200_decode_params* p, const DecodePlan& pl) {
   if (!pl.split) return 0;
-  if (pl.balanced) {
-    // two partial slots of 16 rows per CTA, and room for the tickets of every (sequence, kv head) in case neither the
-    // caller nor the library's per-stream block can provide them (a stream under capture)
-    const size_t partials = static_cast<size_t>(2 * kBalancedMaxCtas) * 16 * (p->d + 1) * sizeof(float);
-    const size_t tickets = (static_cast<size_t>(p->b) * p->h_k * sizeof(int) + 15) & ~static_cast<size_t>(15);
-    return partials + tickets;
-  }
   const size_t sq = p->seqlen_q > 1 ? p->seqlen_q : 1;
   return static_cast<size_t>(pl.num_partitions) * p->b * p->h * sq * (p->d + 1) * sizeof(float);
 }
@@ -623,19 +603,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
       k.merge_sink = 1;
     }
   };
-  if (pl.balanced) {
-    k.o_partial = static_cast<float*>(p->workspace);
-    k.lse_partial = k.o_partial + static_cast<size_t>(2 * kBalancedMaxCtas) * 16 * p->d;
-    k.min_tiles_per_cta = 8;
-    const int64_t pairs = static_cast<int64_t>(p->b) * p->h_k;
-    k.tickets = p->tickets ? p->tickets : stream_tickets(stream, pairs);
-    if (!k.tickets) {   // a stream under capture, or more pairs than the library's block holds: tickets in the scratch
-      k.tickets = reinterpret_cast<int*>(k.lse_partial + static_cast<size_t>(2 * kBalancedMaxCtas) * 16);
-      if (cudaMemsetAsync(k.tickets, 0, pairs * sizeof(int), stream) != cudaSuccess) return cuda_fail("tickets", cudaGetLastError());
-    }
-    merge_in_kernel = true;
-    final_rows_to_caller();
-  } else if (pl.split) {
+  if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
     k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * k.sq * p->d;
     // The last CTA of each (sequence, kv head) merges the partials itself when there are tickets to count on.
@@ -646,25 +614,16 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   {
     const char* dt = p->dtype == FA_B200_E4M3 ? "e4m3" : (p->dtype == FA_B200_BF16 ? "bf16" : "f16");
     const char* cache = p->kv_e4m3 ? (p->kv_e5m2 ? "+e5m2 cache" : "+e4m3 cache") : "";
-    if (pl.balanced)
-      snprintf(g_launch_info, sizeof(g_launch_info),
-               "fa_b200 decode: kernel=decode_balanced dtype=%s%s d=%d b=%d h=%d h_k=%d seqlen_q=%d page=%d tile=%d tokens "
-               "grid=two CTAs per SM (one above d=128), at most %d, equal shares of the tile list (>= %d tiles) threads=160 "
-               "merge=in-kernel (last CTA per sequence and kv head)",
-               dt, cache, p->d, p->b, p->h, p->h_k, k.sq, p->page_size, pl.tile, kBalancedMaxCtas, k.min_tiles_per_cta);
-    else
-      snprintf(g_launch_info, sizeof(g_launch_info),
-               "fa_b200 decode: kernel=decode_paged dtype=%s%s d=%d b=%d h=%d h_k=%d seqlen_q=%d page=%d partition_tokens=%d "
-               "partitions=%d grid=(%d,%d,%d) threads=160 merge=%s",
-               dt, cache, p->d, p->b, p->h, p->h_k, k.sq, p->page_size, pl.partition_tokens, pl.num_partitions,
-               pl.num_partitions, p->h_k, p->b,
-               !pl.split ? "none (one partition)" : (merge_in_kernel ? "in-kernel (last CTA per sequence and kv head)" : "combine kernel"));
+    snprintf(g_launch_info, sizeof(g_launch_info),
+             "fa_b200 decode: kernel=decode_paged dtype=%s%s d=%d b=%d h=%d h_k=%d seqlen_q=%d page=%d partition_tokens=%d "
+             "partitions=%d grid=(%d,%d,%d) threads=160 merge=%s",
+             dt, cache, p->d, p->b, p->h, p->h_k, k.sq, p->page_size, pl.partition_tokens, pl.num_partitions,
+             pl.num_partitions, p->h_k, p->b,
+             !pl.split ? "none (one partition)" : (merge_in_kernel ? "in-kernel (last CTA per sequence and kv head)" : "combine kernel"));
     if (print_param()) fprintf(stderr, "%s\n", g_launch_info);
   }
   if (p->profile_start_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_start_event), stream);
-  const int max_ctas = (g_env.decode_ctas > 0 && g_env.decode_ctas < kBalancedMaxCtas) ? g_env.decode_ctas : kBalancedMaxCtas;
-  cudaError_t e = pl.balanced ? launch_decode_balanced(p->dtype, tk, tv, k, max_ctas, stream)
-                              : launch_decode(p->dtype, tk, tv, k, stream);
+  cudaError_t e = launch_decode(p->dtype, tk, tv, k, stream);
   if (e != cudaSuccess) return cuda_fail("decode launch", e);
   if (p->profile_stop_event) cudaEventRecord(static_cast<cudaEvent_t>(p->profile_stop_event), stream);
   g_launches++;

@@ -1,7 +1,6 @@
-// Pieces shared by the two paged-decode kernels (fa_decode.cu: one CTA per token partition; fa_decode_balanced.cu:
-// an equal share of the whole batch's tiles per CTA): tile traits, the producer's tile loads, the query fragments, one
-// K/V tile's worth of S = Q K^T, online softmax and O += P V for one consumer warp, the write of a finished row and the
-// merge of split-KV partials.
+// Building blocks of the paged-decode kernel (fa_decode.cu): tile traits, the producer's tile loads, the query
+// fragments, one K/V tile's worth of S = Q K^T, online softmax and O += P V for one consumer warp, and the merge of
+// split-KV partials.
 //
 // Data flow as in the reference's partitioned paged attention (csrc/flash_attn_cutlass/src/paged_attention.cu:61-558),
 // with exact softmax (no epsilon) and fp32 partials, as the reference's PyTorch oracle defines the result.
@@ -382,20 +381,6 @@ __device__ __forceinline__ MergeArgs merge_args(const DecodeKernelParams& p) {
   a.merge_sink = p.merge_sink; a.merge_lse_empty_is_neg = p.merge_lse_empty_is_neg;
   return a;
 }
-// Barrier of the four consumer warps on an mbarrier with a bounded wait (a warp that gives up raises the CTA's abort
-// flag, which the caller looks at afterwards).  `phase` counts the meetings so far.
-struct ConsumerSync {
-  uint32_t bar, phase;
-  WaitCtx wctx;
-  int lane;
-  __device__ __forceinline__ bool operator()() {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar);
-    const bool r = mbar_wait(bar, phase & 1u, wctx);
-    ++phase;
-    return r;
-  }
-};
 struct BlockSync {
   __device__ __forceinline__ bool operator()() { __syncthreads(); return true; }
 };

@@ -49,19 +49,12 @@ struct DecodeKernelParams {
   int32_t merge_lse_empty_is_neg;   // merged rows without keys: LSE -inf (partial convention) instead of +inf
   int32_t merge_sink;               // the merge adds the sink (s_aux) to the row sums
   int32_t test_withhold;            // FA_B200_TEST_HOOKS builds only: CTA (0, 0, 0) announces its first tile and never loads it
-  int32_t min_tiles_per_cta;        // balanced kernel: a CTA's share of the tile list is at least this long
 };
 
 int decode_max_pages_per_partition();
 // One CTA per (token partition, kv head, sequence): partials in o_partial / lse_partial as documented above.
 cudaError_t launch_decode(int dtype, const CUtensorMap& tmap_k, const CUtensorMap& tmap_v,
                           const DecodeKernelParams& p, cudaStream_t stream);
-// Equal shares of the launch's tile list per CTA (fa_decode_balanced.cu), at most max_ctas CTAs.  Needs p.tickets
-// (b * h_k ints, zero) and partials for 2 * max_ctas slots: o_partial [2 * max_ctas][16][d], lse_partial
-// [2 * max_ctas][16].  p.b <= decode_balanced_max_batch().  The final rows go to p.out / p.lse_out.
-cudaError_t launch_decode_balanced(int dtype, const CUtensorMap& tmap_k, const CUtensorMap& tmap_v,
-                                   const DecodeKernelParams& p, int max_ctas, cudaStream_t stream);
-int decode_balanced_max_batch();
 
 struct CombineKernelParams {
   const float* o_partial;    // [num_parts][rows][d], partitions o_part_stride floats apart

@@ -245,10 +245,10 @@ typedef struct fa_b200_decode_params {
   /* Split-KV merge inside the decode kernel.  When a call is split into partitions, the CTA that finishes last for a
    * (sequence, kv head) merges that pair's partials itself, so the call is one launch.  The CTAs count themselves on one
    * int32 per pair.  NULL = the library's own counters, one block per (device, stream) for up to 64 streams with
-   * launches in flight and 4096 pairs per launch; beyond that, and on a stream that is being captured into a CUDA
-   * graph, the call falls back to a second launch (the LSE-combine kernel).  A caller that wants the single launch
-   * under capture, or more pairs, passes b * h_k int32 of its own here: zero before the first use (the kernel leaves
-   * them zero), not shared by launches that can overlap on the GPU. */
+   * launches in flight and 4096 pairs per launch; beyond that (or with more than 256 partitions per sequence), and on a
+   * stream that is being captured into a CUDA graph, the call falls back to a second launch (the LSE-combine kernel).
+   * A caller that wants the single launch under capture, or more pairs, passes b * h_k int32 of its own here: zero
+   * before the first use (the kernel leaves them zero), not shared by launches that can overlap on the GPU. */
   int32_t* tickets;
 } fa_b200_decode_params;
 

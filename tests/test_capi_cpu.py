@@ -119,14 +119,8 @@ def test_partition_heuristic_and_workspace(binding):
     d.b, d.h, d.h_k, d.page_size, d.max_blocks_per_seq = 64, 32, 8, 256, 128
     part = lib.fa_b200_decode_partition_tokens(ctypes.byref(d))
     assert part == 8192                     # 64 x 8 rows x 4 partitions = 2048 CTAs: about four rounds of the CTA slots
-    # default: the balanced kernel — two partial slots of 16 rows for each of at most 320 CTAs, plus tickets per
-    # (sequence, kv head); independent of the lengths
-    assert lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) == 2 * 320 * 16 * 129 * 4 + 64 * 8 * 4
-    # a partition size fixed by the caller: the partition-grid kernel, one partial per partition
-    d.partition_tokens = part
     nparts = (128 * 256 + part - 1) // part
     assert lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) == nparts * 64 * 32 * 129 * 4
-    d.partition_tokens = 0
     d.b, d.max_blocks_per_seq = 2, 1      # one page per sequence: no split, no scratch
     assert lib.fa_b200_decode_workspace_bytes(ctypes.byref(d)) == 0
     d.b, d.max_blocks_per_seq = 1, 4096   # one sequence of 1,048,576 tokens: equal partitions, one round of CTAs
