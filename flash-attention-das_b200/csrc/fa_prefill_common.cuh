@@ -64,14 +64,48 @@ struct TileTraits {
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, int dt) {
   return dt == FA_B200_BF16 ? pack_bf16(lo, hi) : pack_f16(lo, hi);
 }
-// four floats -> four e4m3 bytes (byte i = value i)
+// four floats -> four e4m3 bytes (byte i = value i): two conversions and one register pack
 __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
-  uint32_t lo, hi;
-  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(lo) : "f"(a), "f"(b));
-  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(hi) : "f"(c), "f"(d));
-  return lo | (hi << 16);
+  uint32_t r;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
 }
 
+// ---- exponentials of the e4m3 softmax ----------------------------------------------------------------------------
+// An e4m3 tile has half the tensor work of a 16-bit one (about 515 cycles per 128 x 128 tile) but the same 16,384
+// exponentials (1,024 cycles of the MUFU unit per tile).  P is rounded to 3 mantissa bits right after, so a share of
+// the exponentials can go to the FMA pipe in a cheap form: round-to-nearest range reduction with the magic-number add, a
+// degree-2 polynomial of 2^f on [-0.5, 0.5] (relative error 1.7e-3), the integer part added to the exponent field; packed
+// f32x2 arithmetic.  The row sum uses the same values, so P and its normaliser stay consistent.  Measured on 8 x 4096
+// tokens (two-tile kernel): 0 / 1 / 2 / 3 / 4 / 6 of every 8 groups of four columns on the FMA pipe give 1312 / 1375 /
+// 1415 / 1391 / 1246 / 1103 TFLOP/s — the softmax threads are bound by the instructions they issue as much as by the
+// exponential unit, so the cheap form pays only for a quarter of the columns.  (Two exponentials per MUFU instruction
+// in half precision, ex2.approx.f16x2 with the f16 pair converted straight to e4m3, measured 1112.)
+constexpr int kFp8PolyGroups = 2;
+// 2^x for two values on the FMA pipe; x = s * scale - m, clamped below (-inf for masked columns) so that the exponent
+// arithmetic cannot wrap.
+__device__ __forceinline__ void exp2_poly_x2(float s0, float s1, uint64_t sc2, uint64_t nm2, float& p0, float& p1) {
+  float x0, x1;
+  unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), sc2, nm2), x0, x1);
+  x0 = fmaxf(x0, -120.f);
+  x1 = fmaxf(x1, -120.f);
+  const uint64_t x2 = pack_f32x2(x0, x1);
+  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);              // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
+  const uint64_t t2 = add_f32x2(x2, magic);
+  const uint64_t r2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));   // round(x)
+  const uint64_t f2 = fma_f32x2(r2, pack_f32x2(-1.f, -1.f), x2);             // x - round(x) in [-0.5, 0.5]
+  uint64_t q2 = fma_f32x2(f2, pack_f32x2(0.23842697f, 0.23842697f), pack_f32x2(0.7034453f, 0.7034453f));
+  q2 = fma_f32x2(q2, f2, pack_f32x2(1.00044307f, 1.00044307f));
+  float q0, q1, t0, t1;
+  unpack_f32x2(q2, q0, q1);
+  unpack_f32x2(t2, t0, t1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
 // ---- MMA issue sequences ---------------------------------------------------------------------------------------
 // One thread feeds the tensor pipe, and a 128x128x16 product takes only 64 cycles, so the issue path has to be a
 // handful of instructions per MMA: each sequence below is ONE asm block that derives the k-step descriptors with a
@@ -320,21 +354,34 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
       unpack_f32x2(rs2, rs0, rs1);
     }
   } else {
+    // packed f32x2 arithmetic for the scaling and the row sum: the softmax threads are bound by the instructions they issue
+    const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_safe, -m_safe);
+    uint64_t rs2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t pk[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float p0 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i), scale_log2, -m_safe));
-        const float p1 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 1), scale_log2, -m_safe));
-        const float p2 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 2), scale_log2, -m_safe));
-        const float p3 = fast_exp2(fmaf(FA_S_AT(c * 32 + 4 * i + 3), scale_log2, -m_safe));
-        rs0 += p0 + p2;
-        rs1 += p1 + p3;
+        float p0, p1, p2, p3;
+        // kFp8PolyGroups of every 8 groups go to the FMA pipe, spread evenly so that both pipes always have work
+        if (((i + 1) * kFp8PolyGroups) / 8 > (i * kFp8PolyGroups) / 8) {
+          exp2_poly_x2(FA_S_AT(c * 32 + 4 * i), FA_S_AT(c * 32 + 4 * i + 1), sc2, nm2, p0, p1);
+          exp2_poly_x2(FA_S_AT(c * 32 + 4 * i + 2), FA_S_AT(c * 32 + 4 * i + 3), sc2, nm2, p2, p3);
+        } else {
+          float x0, x1, x2, x3;
+          unpack_f32x2(fma_f32x2(pack_f32x2(FA_S_AT(c * 32 + 4 * i), FA_S_AT(c * 32 + 4 * i + 1)), sc2, nm2), x0, x1);
+          unpack_f32x2(fma_f32x2(pack_f32x2(FA_S_AT(c * 32 + 4 * i + 2), FA_S_AT(c * 32 + 4 * i + 3)), sc2, nm2), x2, x3);
+          p0 = fast_exp2(x0);
+          p1 = fast_exp2(x1);
+          p2 = fast_exp2(x2);
+          p3 = fast_exp2(x3);
+        }
+        rs2 = add_f32x2(rs2, add_f32x2(pack_f32x2(p0, p1), pack_f32x2(p2, p3)));
         pk[i] = pack4_e4m3(p0, p1, p2, p3);
       }
       tmem_st_32x8(t_s + c * 8, pk);
     }
+    unpack_f32x2(rs2, rs0, rs1);
   }
 #undef FA_S_AT
   st.l_sum += rs0 + rs1;

@@ -432,21 +432,36 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             }
           } else {
             const uint32_t t_p = tmem_base + lane_off + kColS + b * 128 + wg * (kCols / 4);
+            // as softmax_tile: packed arithmetic, a quarter of the exponentials on the FMA pipe
+            const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(-m_safe, -m_safe);
+            uint64_t rs2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
             for (int h2 = 0; h2 < kCols / 32; ++h2) {
               uint32_t pk[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                const float p0 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i), scale_log2, -m_safe));
-                const float p1 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 1), scale_log2, -m_safe));
-                const float p2 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 2), scale_log2, -m_safe));
-                const float p3 = fast_exp2(fmaf(FA_S_AT(h2 * 32 + 4 * i + 3), scale_log2, -m_safe));
-                rs0 += p0 + p2;
-                rs1 += p1 + p3;
+                float p0, p1, p2, p3;
+                if (((i + 1) * kFp8PolyGroups) / 8 > (i * kFp8PolyGroups) / 8) {
+                  exp2_poly_x2(FA_S_AT(h2 * 32 + 4 * i), FA_S_AT(h2 * 32 + 4 * i + 1), sc2, nm2, p0, p1);
+                  exp2_poly_x2(FA_S_AT(h2 * 32 + 4 * i + 2), FA_S_AT(h2 * 32 + 4 * i + 3), sc2, nm2, p2, p3);
+                } else {
+                  float x0, x1, x2, x3;
+                  unpack_f32x2(fma_f32x2(pack_f32x2(FA_S_AT(h2 * 32 + 4 * i), FA_S_AT(h2 * 32 + 4 * i + 1)), sc2, nm2), x0, x1);
+                  unpack_f32x2(fma_f32x2(pack_f32x2(FA_S_AT(h2 * 32 + 4 * i + 2), FA_S_AT(h2 * 32 + 4 * i + 3)), sc2, nm2), x2, x3);
+                  p0 = fast_exp2(x0);
+                  p1 = fast_exp2(x1);
+                  p2 = fast_exp2(x2);
+                  p3 = fast_exp2(x3);
+                }
+                rs2 = add_f32x2(rs2, add_f32x2(pack_f32x2(p0, p1), pack_f32x2(p2, p3)));
                 pk[i] = pack4_e4m3(p0, p1, p2, p3);
               }
               tmem_st_32x8(t_p + h2 * 8, pk);
             }
+            float r0, r1;
+            unpack_f32x2(rs2, r0, r1);
+            rs0 += r0;
+            rs1 += r1;
           }
         };
         exp_store();

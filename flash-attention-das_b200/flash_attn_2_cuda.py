@@ -1016,3 +1016,62 @@ def block_select(pooled_q, pooled_k, sim_q, sim_k, block_q, block_k, scale, cdf_
             D, block_q, block_k, float(scale), _ptr(cdf_threshold), _ptr(topk), 1 if is_causal else 0,
             1 if attention_sink else 0, block_map.data_ptr(), _stream(pooled_q)), "block_select")
     return block_map.view(torch.bool)
+
+
+# ------------------------------------------------------------------------------------------------
+# torch.library ops the reference's compiled extension defines on import
+# ------------------------------------------------------------------------------------------------
+# flash_attn2_c_op::varlen_fwd and ::fwd_kvcache are C++ schemas in the reference (csrc/flash_attn_cutlass/
+# flash_api.cpp:2796-2816, TORCH_LIBRARY + TORCH_LIBRARY_IMPL); its Python interface only adds fake implementations
+# (flash_attn/flash_attn_interface.py:203-278) and calls them through torch.ops.  Defining them here, with the same
+# schemas character for character, lets that interface run unchanged over this module.
+VARLEN_FWD_SCHEMA = (
+    "(Tensor q, Tensor k, Tensor v, Tensor? out, "
+    "Tensor cu_seqlens_q, Tensor cu_seqlens_k, Tensor? seqused_k, "
+    "Tensor? leftpad_k_, Tensor? block_table_, Tensor? alibi_slopes_, "
+    "int max_seqlen_q, int max_seqlen_k, float p_dropout, "
+    "float softmax_scale, bool zero_tensors, bool is_causal, "
+    "int window_size_left, int window_size_right, float softcap, "
+    "bool return_softmax) -> (Tensor, Tensor, Tensor, Tensor)")
+
+FWD_KVCACHE_SCHEMA = (
+    "(Tensor q, Tensor kcache, Tensor vcache, "
+    "Tensor? k_, Tensor? v_, Tensor? seqlens_k_, "
+    "Tensor? rotary_cos_, Tensor? rotary_sin_, "
+    "Tensor? cache_batch_idx_, Tensor? leftpad_k_, "
+    "Tensor? block_table_, Tensor? alibi_slopes_, Tensor? out_, "
+    "float softmax_scale, bool is_causal, "
+    "int window_size_left, int window_size_right, "
+    "float softcap, bool is_rotary_interleaved, int num_splits) "
+    "-> (Tensor, Tensor)")
+
+
+def _varlen_fwd_op(q, k, v, out, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_, block_table_, alibi_slopes_,
+                   max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
+                   window_size_right, softcap, return_softmax):
+    res = varlen_fwd(q, k, v, out, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k_, block_table_, alibi_slopes_,
+                     max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
+                     window_size_right, softcap, return_softmax)
+    return res[0], res[5], res[6], res[7]   # out, softmax_lse, S_dmask, rng_state (flash_api.cpp TORCH_LIBRARY_IMPL)
+
+
+def _fwd_kvcache_op(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_, cache_batch_idx_, leftpad_k_,
+                    block_table_, alibi_slopes_, out_, softmax_scale, is_causal, window_size_left, window_size_right,
+                    softcap, is_rotary_interleaved, num_splits):
+    out, lse = fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_, cache_batch_idx_, leftpad_k_,
+                           block_table_, alibi_slopes_, out_, softmax_scale, is_causal, window_size_left,
+                           window_size_right, softcap, is_rotary_interleaved, num_splits)
+    return out, lse
+
+
+def _define_c_ops():
+    try:
+        torch.library.define("flash_attn2_c_op::varlen_fwd", VARLEN_FWD_SCHEMA)
+        torch.library.define("flash_attn2_c_op::fwd_kvcache", FWD_KVCACHE_SCHEMA)
+    except RuntimeError:      # already defined in this process (the module was loaded under a second name)
+        return
+    torch.library.impl("flash_attn2_c_op::varlen_fwd", "CUDA")(_varlen_fwd_op)
+    torch.library.impl("flash_attn2_c_op::fwd_kvcache", "CUDA")(_fwd_kvcache_op)
+
+
+_define_c_ops()
