@@ -108,30 +108,49 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const int rows_valid = min(block_rows, sq - m0);
   const int causal_shift = sk - sq;                        // bottom-right alignment
 
-  // ---- key tile list
-  if (threadIdx.x == 0) {
+  // ---- key tile list (warp 0) and barrier set-up (warp 1), side by side
+  if (warp == 0) {
     int n = 0, tile0 = 0;
     const int col_end = row_hi(p, m0 + rows_valid - 1, sk, causal_shift);
     if (p.sparse) {
-      // block_offset holds ascending K row offsets of 64-row tiles; two adjacent entries form one
-      // 128-key tile, a lone entry is a half tile (upper 64 keys masked).  bit 31 marks a half tile.
+      // block_offset holds ascending K row offsets of 64-row tiles.  Walking the list in order, an entry that sees a key
+      // (0 <= offset < col_end) starts a tile; if the entry after it lies exactly 64 rows further the two form one
+      // 128-key tile, else it is a half tile (upper 64 keys masked; bit 31 marks it).  The walk is a recurrence
+      // (an entry is swallowed iff its predecessor started a tile and links to it), so inside a run of linked entries
+      // the starts alternate: the whole warp resolves 32 entries at a time from the distance to the run's first entry.
       const int64_t lrow = (static_cast<int64_t>(bidb) * p.h + head) * p.num_q_blocks + m_block;
-      if (p.column_count && p.column_count[lrow] != 0) atomicOr(p.status, 0x20000);   // vertical sparsity: not taken
-      int cnt = p.block_count[lrow];
-      cnt = max(0, min(cnt, p.nnz_s));
+      if (lane == 0 && p.column_count && p.column_count[lrow] != 0) atomicOr(p.status, 0x20000);   // vertical sparsity: not taken
+      const int cnt = max(0, min(p.block_count[lrow], p.nnz_s));
       const int32_t* offs = p.block_offset + lrow * p.nnz_s;
-      int e = 0;
-      while (e < cnt && n < kMaxSparseTiles) {
-        const int o0 = offs[e];
-        if (o0 < 0 || o0 >= col_end) { ++e; continue; }     // nothing visible in this tile
-        if (e + 1 < cnt && offs[e + 1] == o0 + 64) { sm_tiles[n++] = o0; e += 2; }
-        else { sm_tiles[n++] = o0 | (1 << 31); e += 1; }
+      int carry_k = -1;   // distance of the previous chunk's last entry to its run's first entry
+      for (int e0 = 0; e0 < cnt; e0 += 32) {
+        const int e = e0 + lane;
+        const bool in = e < cnt;
+        const int o = in ? offs[e] : 0;
+        const int o_prev = (in && e > 0) ? offs[e - 1] : 0;
+        const int o_next = (in && e + 1 < cnt) ? offs[e + 1] : 0;
+        const bool valid = in && o >= 0 && o < col_end;
+        // this entry can be swallowed by its predecessor: the predecessor sees a key and links to it
+        const bool chained = in && e > 0 && o_prev >= 0 && o_prev < col_end && o == o_prev + 64;
+        const bool link = in && e + 1 < cnt && o_next == o + 64;
+        const uint32_t heads = __ballot_sync(0xffffffffu, !chained);             // entries that begin a run
+        const uint32_t upto = heads & (0xffffffffu >> (31 - lane));              // those at or before this lane
+        const int k = upto ? lane - (31 - __clz(upto)) : carry_k + 1 + lane;     // distance to the run's first entry
+        const bool start = valid && (k & 1) == 0;
+        const uint32_t starts = __ballot_sync(0xffffffffu, start);
+        const int idx = n + __popc(starts & ((1u << lane) - 1u));
+        if (start && idx < kMaxSparseTiles) sm_tiles[idx] = link ? o : (o | (1 << 31));
+        n = min(n + __popc(starts), kMaxSparseTiles);
+        carry_k = __shfl_sync(0xffffffffu, k, 31);
       }
     } else {
       key_tile_range(p, m0, rows_valid, sk, causal_shift, tile0, n);
     }
-    *sm_ntiles = n;
-    *sm_tile0 = tile0;
+    if (lane == 0) {
+      *sm_ntiles = n;
+      *sm_tile0 = tile0;
+    }
+  } else if (threadIdx.x == 32) {
     *abort_flag = 0;
     mbar_init(smem_u32(q_full), 1);
     mbar_init(smem_u32(s_full), 1);

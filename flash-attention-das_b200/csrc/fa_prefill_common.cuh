@@ -290,13 +290,13 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
   uint32_t prof_t = prof ? clock_after(0) : 0u;
 #endif
   uint32_t u[4][32];
+#define FA_S_AT(idx) __uint_as_float(u[(idx) >> 5][(idx) & 31])
   tmem_ld_32x32(t_s + 0, u[0]);
   tmem_ld_32x32(t_s + 32, u[1]);
   tmem_ld_32x32(t_s + 64, u[2]);
   tmem_ld_32x32(t_s + 96, u[3]);
   tmem_wait_ld();
   FA_PROF(0, u[3][31]);
-#define FA_S_AT(idx) __uint_as_float(u[(idx) >> 5][(idx) & 31])
   if (need_mask) {
 #pragma unroll
     for (int c = 0; c < 128; ++c) u[c >> 5][c & 31] = (c < lim && c >= lo) ? u[c >> 5][c & 31] : 0xff800000u;

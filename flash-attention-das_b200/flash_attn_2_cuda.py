@@ -914,6 +914,70 @@ def fwd_sparse(q, k, v, block_count, block_offset, column_count, column_index, o
     return [out, lse]
 
 
+def varlen_fwd_sparse(q, k, v, block_count, block_offset, column_count, column_index, out_, cu_seqlens_q, cu_seqlens_k,
+                      seqused_k, alibi_slopes_, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors,
+                      is_causal, softcap, return_softmax, gen_=None, pv_threshold=50.0, enable_dynamic_skip=False):
+    """Block-list attention over packed sequences, the reference binding's ``varlen_fwd_sparse``
+    (csrc/flash_attn_cutlass/flash_api_sparse.cpp:339-558, bound at flash_api.cpp:3018): q (total_q, h, 128), k / v
+    (total_k, h_k, 128), int32 cu_seqlens; block_count (b, h, NUM_ROWS), block_offset (b, h, NUM_ROWS, NNZ_S) with
+    NUM_ROWS = ceil(max_seqlen_q / (64 if max_seqlen_q <= 2048 else 128)) and key row offsets relative to each
+    sequence's first key.  Returns [out, softmax_lse (h, total_q)]."""
+    _check_qkv(q, k, v)
+    _require(q.dtype in (torch.float16, torch.bfloat16), "FlashAttention only support fp16 and bf16 data type")
+    _unsupported(seqused_k is not None, "seqused_k")
+    _unsupported(alibi_slopes_ is not None, "alibi")
+    _unsupported(p_dropout != 0.0, "dropout")
+    _unsupported(softcap != 0.0, "softcap")
+    _unsupported(return_softmax, "return_softmax")
+    _unsupported(enable_dynamic_skip, "dynamic PV skip")
+    for name, t in (("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_k", cu_seqlens_k)):
+        _require(t.dtype == torch.int32, f"{name} must have dtype int32")
+        _require(t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous CUDA tensor")
+    total_q, h, d = q.shape
+    total_k, h_k = k.shape[0], k.shape[1]
+    b = cu_seqlens_q.numel() - 1
+    _require(b > 0, "batch size must be positive")
+    _require(cu_seqlens_k.numel() == b + 1, "cu_seqlens_k must have shape (batch_size + 1)")
+    _require(h % h_k == 0, "Number of heads in key/value must divide number of heads in query")
+    for name, t in (("block_count", block_count), ("block_offset", block_offset)):
+        _require(t.dtype == torch.int32 and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous int32 CUDA tensor")
+    block_m = 64 if max_seqlen_q <= 2048 else 128
+    num_rows = (max_seqlen_q + block_m - 1) // block_m
+    _require(tuple(block_count.shape) == (b, h, num_rows), "block_count must have shape (batch, nheads, NUM_ROWS)")
+    _require(block_offset.dim() == 4 and tuple(block_offset.shape[:3]) == (b, h, num_rows),
+             "block_offset must have shape (batch, nheads, NUM_ROWS, NNZ_S)")
+    if max_seqlen_q == 1:
+        is_causal = False
+    odt = _out_dtype(q, out_)
+    out = out_ if out_ is not None else torch.empty((total_q, h, d), dtype=odt, device=q.device)
+    lse = torch.empty((h, total_q), dtype=torch.float32, device=q.device)
+    if zero_tensors:
+        out.zero_()
+        lse.fill_(float("-inf"))
+    p = FwdParams()
+    p.q, p.k, p.v, p.out, p.softmax_lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
+    p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1)
+    p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1)
+    p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1)
+    p.b, p.seqlen_q, p.seqlen_k, p.h, p.h_k, p.d = b, max_seqlen_q, max_seqlen_k, h, h_k, d
+    p.total_q, p.total_k = total_q, total_k
+    p.cu_seqlens_q, p.cu_seqlens_k = cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr()
+    p.softmax_scale = softmax_scale
+    p.is_causal = 1 if is_causal else 0
+    p.dtype, p.out_dtype = _DT[q.dtype], _DT[odt]
+    p.block_count, p.block_offset = block_count.data_ptr(), block_offset.data_ptr()
+    p.num_q_blocks, p.nnz_s, p.block_m = num_rows, block_offset.shape[3], block_m
+    if column_count is not None:
+        _require(column_count.dtype == torch.int32 and column_count.is_cuda and column_count.is_contiguous() and
+                 tuple(column_count.shape) == (b, h, num_rows), "column_count must be a contiguous int32 (batch, nheads, NUM_ROWS) CUDA tensor")
+        p.column_count = column_count.data_ptr()
+    _apply_profile_events(p)
+    with _on_device(q.device):
+        _check(_lib.fa_b200_fwd_sparse(ctypes.byref(p), _stream(q)), "varlen_fwd_sparse")
+    return [out, lse]
+
+
 # ------------------------------------------------------------------------------------------------
 # callers' glue: padding removal and block-map conversion
 # ------------------------------------------------------------------------------------------------

@@ -158,9 +158,11 @@ typedef struct fa_b200_fwd_params {
  *  src/flash_fwd_kernel.h:2818-3328, FP8: 3330-3778). */
 FA_B200_API int fa_b200_fwd(const fa_b200_fwd_params* p, void* stream);
 
-/* Replaces mha_fwd_sparse -> run_mha_fwd_sparse -> sparse_attn_1rowblock
- * (csrc/flash_attn_cutlass/flash_api_sparse.cpp:170-338, 140-149;
- *  src/flash_fwd_sparse_kernel.h:36-775), block-list path only. */
+/* Replaces mha_fwd_sparse and mha_varlen_fwd_sparse -> run_mha_fwd_sparse -> sparse_attn_1rowblock
+ * (csrc/flash_attn_cutlass/flash_api_sparse.cpp:170-338, 339-558, 140-149;
+ *  src/flash_fwd_sparse_kernel.h:36-775), block-list path only.  With cu_seqlens (packed sequences) the lists are
+ * (b, h, num_q_blocks, nnz_s) with num_q_blocks = ceil(seqlen_q / block_m) counted on the longest sequence, and the
+ * key row offsets are relative to each sequence's first key. */
 FA_B200_API int fa_b200_fwd_sparse(const fa_b200_fwd_params* p, void* stream);
 
 /*

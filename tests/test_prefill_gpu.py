@@ -207,6 +207,45 @@ def test_sparse_matches_oracle(fa, s, causal):
     assert cs > 0.9999                                     # tests/test_spas_fa2_attn.py:64-110 asks > 0.99
 
 
+@pytest.mark.parametrize("max_len,causal", [(700, True), (700, False), (2300, True)])
+def test_varlen_sparse_matches_oracle(fa, max_len, causal):
+    """Tile lists over packed sequences (the reference binding's varlen_fwd_sparse, flash_api_sparse.cpp:339-558): lists
+    of shape (batch, heads, NUM_ROWS of the longest sequence, NNZ_S), key offsets relative to each sequence."""
+    _, cuda = fa
+    g = gen(7000 + max_len)
+    lens = [max_len, 130, 64, max_len // 2 + 3]
+    b, h, h_k = len(lens), 4, 2
+    block_m = O.sparse_block_m(max_len)
+    nq, nk = (max_len + block_m - 1) // block_m, (max_len + 127) // 128
+    tm = torch.rand(b, h, nq, nk, generator=g) < 0.5
+    if causal:
+        qi = torch.arange(nq).view(-1, 1) * block_m
+        ki = torch.arange(nk).view(1, -1) * 128
+        tm &= (ki <= qi + block_m - 1)
+        tm |= (ki <= qi) & (qi < ki + 128)
+    tm[..., 0] = True
+    cnt, offs = O.tile_mask_to_block_lists(tm, block_m=block_m, block_n=64, tile_n=128)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    total = sum(lens)
+    q, k, v = randn(g, total, h, 128), randn(g, total, h_k, 128), randn(g, total, h_k, 128)
+    cc = torch.zeros(b, h, nq, dtype=torch.int32)
+    ci = torch.zeros(b, h, nq, 1, dtype=torch.int32)
+    out, lse = cuda.varlen_fwd_sparse(q.cuda(), k.cuda(), v.cuda(), cnt.cuda(), offs.cuda(), cc.cuda(), ci.cuda(), None,
+                                      cu.cuda(), cu.cuda(), None, None, max_len, max_len, 0.0, 128 ** -0.5, False, causal,
+                                      0.0, False, None)
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    assert lse.shape == (h, total)
+    for i, L in enumerate(lens):
+        lo, hi = int(cu[i]), int(cu[i + 1])
+        qi_, ki_, vi_ = q[lo:hi][None], k[lo:hi][None], v[lo:hi][None]
+        mask = O.block_lists_to_dense_mask(cnt[i:i + 1], offs[i:i + 1], L, L, block_m)
+        ref32, ref_lse = O.attention_ref(qi_, ki_, vi_, causal=causal, out_dtype=torch.float32, extra_mask=mask)
+        ref_pt, _ = O.attention_ref(qi_, ki_, vi_, causal=causal, upcast=False, reorder_ops=True, extra_mask=mask)
+        assert_close_to_oracle(out[lo:hi][None].cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"varlen sparse seq {i}")
+        _check_lse(lse[:, lo:hi].cpu(), ref_lse[0])
+
+
 def test_sparse_manual_two_block_selection(fa):
     """The reference's own sparse test case (tests/test_spas_fa2_attn.py:64-110): every q block attends K rows
     [0, 64) and [128, 192) only."""
