@@ -52,9 +52,11 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 TRAFFIC_RATIO = {"decode_bf16": 1.007, "decode_bf16_replica": 1.007, "decode_fp8": 1.013, "prefill_bf16": None,
                  "prefill_fp8": None, "sparse_bf16": None, "longseq": 1.007}
 # prefill is tensor-bound, its algorithmic unit is FLOPs; DRAM traffic is reported in bytes per token of the
-# captured case (521.5 MB for 19,679 tokens, 1.29x the compulsory q+k+v+out bytes).
-# block-sparse: the full configuration was captured (3.251 GB read + 0.237 GB written for its 32,768 tokens).
-PREFILL_TRAFFIC_BYTES_PER_TOKEN = {"prefill_bf16": 521.5e6 / 19679, "sparse_bf16": 3.4879e9 / 32768}
+# captured case: bf16 526.2 MB for 19,679 tokens (1.31x the compulsory q+k+v+out bytes), e4m3 188.7 MB for
+# 4 x 4096 tokens (0.80x: a third of the 134 MB bf16 output is still in L2 when the launch ends),
+# block-sparse 3.090 GB read + 0.237 GB written for the full configuration's 32,768 tokens.
+PREFILL_TRAFFIC_BYTES_PER_TOKEN = {"prefill_bf16": 526.2e6 / 19679, "prefill_fp8": 188.7e6 / 16384,
+                                   "sparse_bf16": 3.3273e9 / 32768}
 
 
 def load_peaks():
