@@ -192,6 +192,8 @@ bool stride_ok(int64_t s, int es) { return s >= 0 && (s * es) % 16 == 0; }
 // csrc/flash_attn_cutlass/src/flash.h:20-25):
 //   FA_B200_DECODE_PARTITION=<tokens>        partition size of the split-KV decode (0 / unset: heuristic)
 //   FA_B200_PREFILL_KERNEL=single|pair|dense prefill kernel, where that kernel can take the call
+//   FA_B200_DECODE_MERGE=combine|kernel      split decode calls merge their partitions with the separate combine launch /
+//                                            in the decode kernel (unset: by grid size, see fa_b200_decode_paged)
 //   FA_B200_PRINT_PARAM=1                    one line on stderr per attention call: kernel, grid, tiling
 //                                            (the reference: FLASH_ATTENTION_PRINT_PARAM, flash_api.cpp:219-222;
 //                                            PA_PRINT_PARAM, src/paged_attention.cu:40)
@@ -200,7 +202,9 @@ struct EnvConfig {
   int decode_partition = 0;
   int prefill_kernel = 0;   // 0 auto, 1 single, 2 pair, 3 dense
   int print_param = 0;
+  int decode_merge = 0;   // 0 auto, 1 always the separate combine launch, 2 in the decode kernel wherever it can
   EnvConfig() {
+    if (const char* v = getenv("FA_B200_DECODE_MERGE")) decode_merge = !strcmp(v, "combine") ? 1 : (!strcmp(v, "kernel") ? 2 : 0);
     if (const char* v = getenv("FA_B200_DECODE_PARTITION")) decode_partition = atoi(v);
     if (const char* v = getenv("FA_B200_PREFILL_KERNEL")) {
       if (!strcmp(v, "single")) prefill_kernel = 1;
@@ -616,8 +620,16 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   if (pl.split) {
     k.o_partial = static_cast<float*>(p->workspace);
     k.lse_partial = k.o_partial + static_cast<size_t>(pl.num_partitions) * p->b * p->h * k.sq * p->d;
-    // The last CTA of each (sequence, kv head) merges the partials itself when there are tickets to count on.
-    if (pl.num_partitions <= 256) k.tickets = p->tickets ? p->tickets : stream_tickets(stream, static_cast<int64_t>(p->b) * p->h_k);
+    // The last CTA of each (sequence, kv head) merges the partials itself when there are tickets to count on and the
+    // grid is at most two rounds of the 296 resident CTA slots.  The merge saves a launch (about 5 us per step, which
+    // is what counts for a small batch), but every CTA pays for it at its end: a fence and a ticket, and for the last
+    // one of a group the dependent reads of the merge, 2 to 5 us in which its half of the SM streams nothing.  In a grid
+    // of many rounds that adds up: 128 sequences x 8192 tokens of e4m3 (7 rounds of 58 us CTAs) measured 0.424 ms
+    // with the merge in the kernel against 0.389 ms with the combine launch; bf16 CTAs are longer and HBM-bound, and
+    // measured the same both ways.
+    const int64_t ctas = static_cast<int64_t>(pl.num_partitions) * p->h_k * p->b;
+    const bool want = g_env.decode_merge == 2 || (g_env.decode_merge == 0 && ctas <= 2 * 296);
+    if (pl.num_partitions <= 256 && want) k.tickets = p->tickets ? p->tickets : stream_tickets(stream, static_cast<int64_t>(p->b) * p->h_k);
     merge_in_kernel = k.tickets != nullptr;
     if (merge_in_kernel) final_rows_to_caller();
   }

@@ -30,11 +30,7 @@ constexpr int kSlots = 4;
 constexpr int kThreads = 32 * 12;
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr int kTmemCols = 512;
-#ifndef FA_PAIR_SOFTMAX_REGS
-#define FA_PAIR_SOFTMAX_REGS 232
-#define FA_PAIR_OTHER_REGS 40
-#endif
-constexpr int kSoftmaxRegs = FA_PAIR_SOFTMAX_REGS, kOtherRegs = FA_PAIR_OTHER_REGS;
+constexpr int kSoftmaxRegs = 232, kOtherRegs = 40;
 // setmaxnreg.inc waits (without a limit) until the CTA's pool holds enough registers, and the pool is what the CTA got
 // at launch: 168 registers (the cap of a 384-thread CTA) for each of its threads.  A split that asks for more never
 // gets it and the kernel hangs.

@@ -244,9 +244,10 @@ typedef struct fa_b200_decode_params {
    * src/paged_attention.cu:747-1149 takes both fp8 formats): an e5m2 value is the high byte of an f16, so the
    * conversion on the way into the products is a byte move. */
   int32_t kv_e5m2;
-  /* Split-KV merge inside the decode kernel.  When a call is split into partitions, the CTA that finishes last for a
-   * (sequence, kv head) merges that pair's partials itself, so the call is one launch.  The CTAs count themselves on one
-   * int32 per pair.  NULL = the library's own counters, one block per (device, stream) for up to 64 streams with
+  /* Split-KV merge inside the decode kernel.  When a call is split into partitions and its grid is small (at most two
+   * rounds of the GPU's resident CTAs: that is where a saved launch counts; in larger grids the second launch is the
+   * cheaper way and is used whatever this field holds), the CTA that finishes last for a (sequence, kv head) merges
+   * that pair's partials itself, so the call is one launch.  The CTAs count themselves on one int32 per pair.  NULL = the library's own counters, one block per (device, stream) for up to 64 streams with
    * launches in flight and 4096 pairs per launch; beyond that (or with more than 256 partitions per sequence), and on a
    * stream that is being captured into a CUDA graph, the call falls back to a second launch (the LSE-combine kernel).
    * A caller that wants the single launch under capture, or more pairs, passes b * h_k int32 of its own here: zero

@@ -107,3 +107,58 @@ def test_varlen_prefill_replayed_with_other_lengths(fa):
         ref32, _ = O.attention_varlen_ref(q[:n], k[:n], v[:n], cu, cu, causal=True, out_dtype=torch.float32)
         ref_pt, _ = O.attention_varlen_ref(q[:n], k[:n], v[:n], cu, cu, causal=True, upcast=False, reorder_ops=True)
         assert_close_to_oracle(out_s[:n].cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"graph prefill {lens}")
+
+
+def test_chunks_of_new_tokens_over_the_paged_cache_replayed_concurrently(fa):
+    """flash_attn_with_kvcache with a chunk of query tokens per sequence (more than the decode tile holds) runs the
+    persistent paged prefill kernel.  Two such calls captured into two graphs get a work counter each, so their replays
+    may overlap on two streams; each replay reads the lengths of the moment and is checked against the oracle."""
+    from _util import make_paged
+    flash_attn, cuda = fa
+    g = gen(4343)
+    h, hk, page, sq = 8, 2, 64, 48
+    cap = [1500, 700, 2048]
+    pools = [make_paged(g, cap, hk, page, torch.bfloat16, poison=False) for _ in range(2)]
+    q_s = [torch.zeros(len(cap), sq, h, 128, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    out_s = [torch.zeros_like(x) for x in q_s]
+    dev = [(kc.cuda(), vc.cuda(), bt.cuda(), sl.cuda()) for kc, vc, bt, sl in pools]
+
+    def call(i):
+        kc_d, vc_d, bt_d, sl_d = dev[i]
+        flash_attn.flash_attn_with_kvcache(q_s[i], kc_d, vc_d, cache_seqlens=sl_d, block_table=bt_d, causal=True, out=out_s[i])
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call(0)
+        assert "prefill" in cuda.last_launch_info()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graphs = []
+    for i in range(2):
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            call(i)
+        graphs.append(gr)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for lens in ([1500, 700, 2048], [48, 64, 1000], [777, 49, 130]):
+        qs = [randn(g, len(cap), sq, h, 128) for _ in range(2)]
+        for i in range(2):
+            q_s[i].copy_(qs[i].cuda())
+            dev[i][3].copy_(torch.tensor(lens, dtype=torch.int32).cuda())
+            out_s[i].fill_(float("nan"))
+        torch.cuda.synchronize()
+        for rep in range(3):                                    # overlapping replays of the two graphs
+            for i in range(2):
+                with torch.cuda.stream(streams[i]):
+                    graphs[i].replay()
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        for i in range(2):
+            kc, vc, bt, _ = pools[i]
+            for s, L in enumerate(lens):
+                ki, vi = O.gather_paged_kv(kc, bt[s], L)[None], O.gather_paged_kv(vc, bt[s], L)[None]
+                ref32, _ = O.attention_ref(qs[i][s:s + 1], ki, vi, causal=True, out_dtype=torch.float32)
+                ref_pt, _ = O.attention_ref(qs[i][s:s + 1], ki, vi, causal=True, upcast=False, reorder_ops=True)
+                assert_close_to_oracle(out_s[i][s:s + 1].cpu(), ref32, ref_pt, mult=3.0, eps=2 ** -8,
+                                       what=f"graph chunk {i} lens {lens} seq {s}")

@@ -407,3 +407,37 @@ def test_raw_pointer_entry_matches_the_tensor_entries(fa):
         ref_pt, _ = O.attention_ref(q_i, k_i, v_i, causal=True, upcast=False, reorder_ops=True)
         assert_close_to_oracle(out[int(cu[i]):int(cu[i + 1])].cpu()[None], ref32, ref_pt, mult=2.0, eps=2 ** -8,
                                what=f"request {i}")
+
+
+@pytest.mark.parametrize("partition", [None, 256])
+def test_lengths_beyond_the_block_table_are_clamped_and_reported(fa, partition):
+    """A cache_seqlens entry larger than what the sequence's row of the block table covers must not send the kernel past
+    the row: the length is clamped to the covered tokens (the result is attention over exactly those) and the launch
+    reports FA_B200_ERR_DEVICE_RANGE through fa_b200_device_status()."""
+    flash_attn, cuda = fa
+    g = gen(911)
+    lens, h, hk, page = [300, 1024, 77], 8, 2, 64
+    kc, vc, bt, sl = make_paged(g, lens, hk, page, torch.bfloat16, poison=False)
+    covered = bt.shape[1] * page                                  # 1024 tokens per row of the table
+    assert covered == 1024
+    bt = bt.clone()
+    bt[0, :] = bt[1, :]                                           # sequence 0 may read all 16 pages once it is clamped
+    bad = sl.clone()
+    bad[0] = covered + 1000                                       # 2024 tokens claimed, 1024 covered
+    q = randn(g, len(lens), 1, h, 128)
+    if partition is not None:
+        os.environ["FA_B200_DECODE_PARTITION"] = str(partition)
+    try:
+        out = flash_attn.flash_attn_with_kvcache(q.cuda(), kc.cuda(), vc.cuda(), cache_seqlens=bad.cuda(),
+                                                 block_table=bt.cuda(), causal=True)
+        torch.cuda.synchronize()
+    finally:
+        os.environ.pop("FA_B200_DECODE_PARTITION", None)
+    RANGE = 14
+    assert cuda.device_status() == RANGE
+    assert cuda.device_status() == 0                              # cleared by the read
+    clamped = bad.clone()
+    clamped[0] = covered
+    ref32, _ = O.paged_decode_ref(q, kc, vc, clamped, bt, out_dtype=torch.float32)
+    ref_pt, _ = O.paged_decode_ref(q, kc, vc, clamped, bt, upcast=False, reorder_ops=True)
+    assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=3.0, eps=1e-5 + 2 ** -8, what="clamped lengths")
