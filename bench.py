@@ -381,10 +381,19 @@ class PrefillWorkload:
                      "nheads": H, "nheads_kv": HK, "headdim": D,
                      "sharding": "%d sequence group(s) (LPT on length^2) x %d kv-head group(s): rank %d of %d has %d sequences, "
                                  "%d query / %d kv heads" % (sg, hg, rank, world, len(lens), self.h, self.hk),
-                     "tokens": total,
-                     "l2": "inputs larger than L2 (q+k+v of this rank %.0f MB)" % ((q.numel() + 2 * k.numel()) * es / 1e6)}
+                     "tokens": total}
+        in_mb = (q.numel() + 2 * k.numel()) * es / 1e6
+        if in_mb > 126:   # the L2 of a B200 holds 126 MB
+            self.flush = None
+            self.desc["l2"] = "inputs larger than L2 (q+k+v of this rank %.0f MB)" % in_mb
+        else:   # a shard of the configuration on one of several GPUs
+            self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+            self.desc["l2"] = ("inputs are NOT larger than L2 here (q+k+v of this rank %.0f MB): L2 flushed between steps, "
+                               "inside the timed region" % in_mb)
 
     def step(self):
+        if self.flush is not None:
+            self.flush.zero_()
         return self.fa.flash_attn_varlen_func(self.q, self.k, self.v, self.cu, self.cu, self.maxlen, self.maxlen,
                                               causal=True, **self.kw)
 
@@ -491,12 +500,19 @@ class SparseWorkload:
         self.desc = {"workload": "block-sparse causal GQA prefill bf16: 1 x %d, 128x128 tiles at %.0f%% density" %
                      (seqlen, density * 100), "kept_tiles": self.kept, "tokens": seqlen, "nheads": H, "nheads_kv": HK, "headdim": D,
                      "sharding": "by kv head: rank %d of %d has %d query / %d kv heads" % (rank, world, self.h, self.hk),
-                     "l2": "inputs are NOT larger than L2 here (q+k+v of this rank %.0f MB): L2 flushed between steps" %
-                     ((self.q.numel() + 2 * self.k.numel()) * 2 / 1e6)}
-        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+                     }
+        in_mb = (self.q.numel() + 2 * self.k.numel()) * 2 / 1e6
+        if in_mb > 126:   # the L2 of a B200 holds 126 MB
+            self.flush = None
+            self.desc["l2"] = "inputs larger than L2 (q+k+v of this rank %.0f MB)" % in_mb
+        else:
+            self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+            self.desc["l2"] = ("inputs are NOT larger than L2 here (q+k+v of this rank %.0f MB): L2 flushed between steps, "
+                               "inside the timed region" % in_mb)
 
     def step(self):
-        self.flush.zero_()
+        if self.flush is not None:
+            self.flush.zero_()
         return self.fa.sparse_attn_func(self.q, self.k, self.v, self.cnt, self.offs, self.cc, self.ci, causal=True)
 
     def check(self):
@@ -712,6 +728,32 @@ def time_kernel_alone(wl, steps, warmup):
     return sum(ts) / len(ts), ts[len(ts) // 2]
 
 
+_READ_PEAK = {}
+
+
+def read_stream_gbs(dev):
+    """Bandwidth of a read-only pass over 2 GiB of this GPU's memory (the library's fa_b200_read_stream kernel, median of
+    10 timed passes after 3 warm-up ones).  The roofline's `peak` is the driver-measured COPY bandwidth (read + write);
+    the decode kernels only read, so their fraction of that peak can exceed 1: this figure is reported beside it."""
+    if dev.index in _READ_PEAK:
+        return _READ_PEAK[dev.index]
+    import flash_attn_2_cuda
+    buf = torch.empty(2 << 30, dtype=torch.uint8, device=dev)
+    sink = torch.zeros(1, dtype=torch.int32, device=dev)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+    for _ in range(3):
+        flash_attn_2_cuda.read_stream(buf, sink)
+    for a, b in ev:
+        a.record()
+        flash_attn_2_cuda.read_stream(buf, sink)
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in ev)
+    _READ_PEAK[dev.index] = buf.numel() / (ts[len(ts) // 2] * 1e-3) / 1e9
+    del buf
+    return _READ_PEAK[dev.index]
+
+
 def host_us_per_call(wl, calls=200):
     """Wall time the host spends inside one public API call when the stream is idle (median), in microseconds."""
     for _ in range(10):
@@ -781,6 +823,13 @@ def run_workload(name, args, dev, rank, world, shard, peaks, cpu_budget):
         "clocks": clocks,
         "kernel": launch_info,
     }
+    if bound == "hbm":
+        rp = read_stream_gbs(dev)
+        res["roofline"]["read_stream_gbs"] = round(rp, 1)
+        res["roofline"]["frac_of_read_stream"] = round(achieved / rp, 4)
+        res["roofline"]["note"] = ("peak is the measured device-to-device COPY bandwidth (reads and writes); this kernel only "
+                                   "reads, so frac can pass 1: read_stream_gbs is a read-only pass over 2 GiB measured in "
+                                   "this run on this GPU")
     if shard[1] != world:
         res["config"]["emulated"] = "rank %d of a %d-way job on one GPU, no collective" % shard
     if "decode" in name:

@@ -427,6 +427,14 @@ int fa_b200_kv_append(const fa_b200_kv_append_params* p, void* stream) {
   return FA_B200_OK;
 }
 
+int fa_b200_read_stream(const void* src, int64_t bytes, uint32_t* sink, void* stream) {
+  if (!src || !sink) return FA_B200_ERR_NULL;
+  if (bytes < 0) return FA_B200_ERR_SHAPE;
+  if (!aligned16(src)) return FA_B200_ERR_ALIGN;
+  cudaError_t e = launch_read_stream(src, bytes, sink, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FA_B200_OK : cuda_fail("fa_b200_read_stream", e);
+}
+
 int fa_b200_unpad_plan(const void* mask, int32_t elem, int32_t b, int32_t s, int64_t row_stride, int32_t* seqlens,
                        int32_t* cu_seqlens, int64_t* indices, int32_t* stats, void* stream) {
   if (elem != 1 && elem != 4 && elem != 8) return FA_B200_ERR_DTYPE;

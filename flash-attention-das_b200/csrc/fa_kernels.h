@@ -161,6 +161,7 @@ cudaError_t launch_kv_append(int dtype, const KvAppendKernelParams& p, cudaStrea
 
 
 // Callers' glue (fa_glue.cu): padding removal and block-map conversion.
+cudaError_t launch_read_stream(const void* src, int64_t bytes, uint32_t* sink, cudaStream_t stream);
 cudaError_t launch_unpad_plan(const void* mask, int elem, int b, int s, int64_t row_stride, int32_t* seqlens,
                               int32_t* cu_seqlens, int64_t* indices, int32_t* stats, cudaStream_t stream);
 cudaError_t launch_move_rows(const void* src, const int64_t* indices, void* dst, int64_t n_rows, int64_t row_bytes,

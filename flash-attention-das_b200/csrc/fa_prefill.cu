@@ -80,9 +80,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bidb = blockIdx.z;
-  const int m_block = p.is_causal ? (p.num_m_blocks - 1 - static_cast<int>(blockIdx.y)) : static_cast<int>(blockIdx.y);
-  const int head = blockIdx.x;
-  const int hk = head / (p.h / p.h_k);
+  // CTAs are dispatched in the order of their linear index (x fastest).  That order walks one kv head at a time, inside
+  // it the query blocks (for causal masks: heaviest first) and for each block the query heads of the group: the CTAs
+  // that are resident together then read the K/V of one or two kv heads, which stay in L2, instead of all of them
+  // (32k tokens x 8 kv heads of K and V are 134 MB, more than L2: in head-fastest order every tile came back from
+  // DRAM about five times).
+  const int group = p.h / p.h_k;
+  const int lin = static_cast<int>(blockIdx.y) * p.h + static_cast<int>(blockIdx.x);
+  const int per_hk = group * p.num_m_blocks;
+  const int hk = lin / per_hk;
+  const int in_hk = lin - hk * per_hk;
+  const int mrev = in_hk / group;
+  const int head = hk * group + (in_hk - mrev * group);
+  const int m_block = p.is_causal ? (p.num_m_blocks - 1 - mrev) : mrev;
 
   // ---- sequence geometry
   int q_row0, k_row0, sq, sk, coord_b;

@@ -178,6 +178,8 @@ _lib.fa_b200_last_cuda_error.restype = ctypes.c_char_p
 _lib.fa_b200_device_status.restype = ctypes.c_int
 _lib.fa_b200_abi_version.restype = ctypes.c_int
 _lib.fa_b200_launch_count.restype = ctypes.c_uint64
+_lib.fa_b200_read_stream.argtypes = [_c_vp, _c_i64, _c_vp, _c_vp]
+_lib.fa_b200_read_stream.restype = ctypes.c_int
 _lib.fa_b200_set_print_param.argtypes = [ctypes.c_int]
 _lib.fa_b200_set_print_param.restype = None
 _lib.fa_b200_last_launch_info.restype = ctypes.c_char_p
@@ -227,6 +229,15 @@ def _apply_profile_events(p):
 
 def launch_count() -> int:
     return int(_lib.fa_b200_launch_count())
+
+
+def read_stream(buf: torch.Tensor, sink: torch.Tensor) -> None:
+    """One read-only pass over ``buf`` on the current stream (fa_b200_read_stream): a measurement aid that gives, timed
+    with events, the bandwidth of a pure read stream on this GPU.  ``sink``: one int32 / uint32 element on the device."""
+    _require(buf.is_cuda and buf.is_contiguous() and sink.is_cuda and sink.numel() >= 1, "read_stream: contiguous CUDA tensors")
+    with _on_device(buf.device):
+        _check(_lib.fa_b200_read_stream(buf.data_ptr(), buf.numel() * buf.element_size(), sink.data_ptr(), _stream(buf)),
+               "read_stream")
 
 
 def set_print_param(on: Optional[bool]):

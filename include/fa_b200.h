@@ -449,6 +449,11 @@ FA_B200_API int fa_b200_abi_version(void);
  * the calling thread's last attention call whether or not printing is on ("" before the first call). */
 FA_B200_API void fa_b200_set_print_param(int on);
 FA_B200_API const char* fa_b200_last_launch_info(void);
+/* Measurement aid: one read-only pass over `bytes` bytes at `src` (16-byte aligned device memory) on `stream`, folded
+ * into *sink (one uint32 in device memory).  Timed with events around it, it gives the bandwidth of a pure read
+ * stream on this GPU, the yardstick for the decode kernels (a device-to-device copy, the usual figure, reads and
+ * writes).  Not part of the attention path. */
+FA_B200_API int fa_b200_read_stream(const void* src, int64_t bytes, uint32_t* sink, void* stream);
 /* Number of kernels this library has launched in this process (for launch accounting). */
 FA_B200_API uint64_t fa_b200_launch_count(void);
 
