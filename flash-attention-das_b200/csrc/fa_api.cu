@@ -194,6 +194,7 @@ bool stride_ok(int64_t s, int es) { return s >= 0 && (s * es) % 16 == 0; }
 //   FA_B200_PREFILL_KERNEL=single|pair|dense prefill kernel, where that kernel can take the call
 //   FA_B200_DECODE_MERGE=combine|kernel      split decode calls merge their partitions with the separate combine launch /
 //                                            in the decode kernel (unset: by grid size, see fa_b200_decode_paged)
+//   FA_B200_DEPENDENT_LAUNCH=0               decode kernels are launched without programmatic stream serialisation
 //   FA_B200_PRINT_PARAM=1                    one line on stderr per attention call: kernel, grid, tiling
 //                                            (the reference: FLASH_ATTENTION_PRINT_PARAM, flash_api.cpp:219-222;
 //                                            PA_PRINT_PARAM, src/paged_attention.cu:40)
@@ -202,8 +203,10 @@ struct EnvConfig {
   int decode_partition = 0;
   int prefill_kernel = 0;   // 0 auto, 1 single, 2 pair, 3 dense
   int print_param = 0;
+  int dependent_launch = 1;   // decode launches may start during the tail of the kernel before them
   int decode_merge = 0;   // 0 auto, 1 always the separate combine launch, 2 in the decode kernel wherever it can
   EnvConfig() {
+    if (const char* v = getenv("FA_B200_DEPENDENT_LAUNCH")) dependent_launch = atoi(v) != 0;
     if (const char* v = getenv("FA_B200_DECODE_MERGE")) decode_merge = !strcmp(v, "combine") ? 1 : (!strcmp(v, "kernel") ? 2 : 0);
     if (const char* v = getenv("FA_B200_DECODE_PARTITION")) decode_partition = atoi(v);
     if (const char* v = getenv("FA_B200_PREFILL_KERNEL")) {
@@ -606,6 +609,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   k.q_row_stride = p->q_row_stride;
   k.o_row_stride = p->o_row_stride;
   k.max_len = pl.max_len;
+  k.dependent_launch = g_env.dependent_launch;
 #ifdef FA_B200_TEST_HOOKS
   k.test_withhold = g_test_withhold.exchange(0);
 #endif

@@ -85,6 +85,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 }
 
 // ------------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the stream-serialisation attribute may start while the
+// kernel before it in the stream is still running; griddep_wait() returns once that kernel has completed and its
+// writes are visible (at once when the launch carried no such attribute), and griddep_launch_dependents() lets the
+// kernel after this one start as soon as every CTA of this grid has got here or exited.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------------
 // TMA (tile mode, no multicast): global -> shared, completion on an mbarrier
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {

@@ -50,6 +50,21 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 
   const int part = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), kConsumerWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  // Up to here the CTA has touched its own shared memory and its parameters only.  With programmatic dependent launch
+  // it may have started during the tail of the kernel before it in the stream; everything below reads what earlier
+  // kernels wrote (lengths, page table, q, the cache, the scratch and ticket words of the previous decode call).
+  griddep_wait();
+  griddep_launch_dependents();
   // A length beyond what the block table covers would walk past the table row: cut it and report it.
   int len = p.seqlens[b];
   if (len > p.max_len) {
@@ -66,16 +81,6 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int tok_begin = max(part * p.partition_tokens, (tok_lo / T::kTile) * T::kTile);
   const int n_tiles = (tok_end > tok_begin) ? (tok_end - tok_begin + T::kTile - 1) / T::kTile : 0;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), kConsumerWarps);
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&tmap_k);
-    tma_prefetch_desc(&tmap_v);
-  }
   if (warp == 0) {
     // This partition's slice of the block table -> shared memory
     const int first_page = tok_begin / p.page_size;
@@ -264,9 +269,17 @@ static cudaError_t launch_decode_dt(const CUtensorMap& tk, const CUtensorMap& tv
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  dim3 grid(p.num_partitions, p.h_k, p.b);
-  kern<<<grid, kDecodeThreads, smem, stream>>>(tk, tv, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.num_partitions, p.h_k, p.b);
+  cfg.blockDim = dim3(kDecodeThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.dependent_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, tk, tv, p);
 }
 
 cudaError_t launch_decode(int dtype, const CUtensorMap& tk, const CUtensorMap& tv, const DecodeKernelParams& p,

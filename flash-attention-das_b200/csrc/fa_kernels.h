@@ -48,6 +48,7 @@ struct DecodeKernelParams {
   int* tickets;
   int32_t merge_lse_empty_is_neg;   // merged rows without keys: LSE -inf (partial convention) instead of +inf
   int32_t merge_sink;               // the merge adds the sink (s_aux) to the row sums
+  int32_t dependent_launch;         // launch with programmatic stream serialisation (the kernel waits by itself)
   int32_t test_withhold;            // FA_B200_TEST_HOOKS builds only: CTA (0, 0, 0) announces its first tile and never loads it
 };
 
