@@ -594,9 +594,21 @@ class LongSeqWorkload:
                      "sharding": "by page range: rank %d of %d holds pages [%d, %d)" % (rank, world, first, last),
                      "l2": "inputs larger than L2 (%.2f GB on this rank)" % (self.units / 1e9)}
 
-    def _run(self, q, events=None):
+    def _exchange(self):
+        """At more than one rank the partials cross NVLink inside the library's exchange + combine kernel (peer stores
+        over CUDA IPC mappings), set up once; FA_B200_BENCH_LONGSEQ=nccl keeps the all-gather + combine pair."""
+        if not hasattr(self, "_ex"):
+            self._ex = None
+            import torch.distributed as dist
+            if self.real_world > 1 and dist.is_initialized() and os.environ.get("FA_B200_BENCH_LONGSEQ", "") != "nccl":
+                from flash_attn.split_kv_parallel import PartialExchange
+                self._ex = PartialExchange(H, D, self.q.device)
+        return self._ex
+
+    def _run(self, q, events=None, nccl=False):
         from flash_attn.split_kv_parallel import decode_split_across_gpus
-        out, _ = decode_split_across_gpus(q, self.kc, self.vc, self.sl, self.bt, D ** -0.5, phase_events=events)
+        out, _ = decode_split_across_gpus(q, self.kc, self.vc, self.sl, self.bt, D ** -0.5, phase_events=events,
+                                          exchange=None if nccl else self._exchange())
         return out
 
     def step(self):
@@ -604,8 +616,8 @@ class LongSeqWorkload:
 
     def check(self):
         """Every rank evaluates the fp32 oracle on kv head 2 (query heads 8..11) of its own slice on the device; the
-        partials are all-gathered and merged by the oracle's merge; the kernel path's output (partition kernel, NCCL
-        all-gather of the packed [O | LSE], combine kernel) is compared with that."""
+        partials are all-gathered and merged by the oracle's merge; the kernel path's output (partition kernel, then the
+        exchange + combine kernel over peer memory, or NCCL all-gather + combine kernel) is compared with that."""
         from oracle import attention_oracle as O
         from flash_attn.split_kv_parallel import gather_partials
         import torch.distributed as dist
@@ -636,9 +648,23 @@ class LongSeqWorkload:
             self._run(self.q, e)
         torch.cuda.synchronize()
         avg = lambda i: sum(e[i].elapsed_time(e[i + 1]) for e in ev) / steps * 1e3
-        return {"partition_kernel_with_local_merge_us": round(avg(0), 2), "all_gather_us": round(avg(1), 2),
-                "final_combine_us": round(avg(2), 2), "note": "measured one step at a time with events between the phases; "
-                "the all-gather is an NCCL call on the same stream (no call at one rank)"}
+        if self._exchange() is None:
+            return {"partition_kernel_with_local_merge_us": round(avg(0), 2), "all_gather_us": round(avg(1), 2),
+                    "final_combine_us": round(avg(2), 2), "note": "measured one step at a time with events between the "
+                    "phases; the all-gather is an NCCL call on the same stream (no call at one rank)"}
+        res = {"partition_kernel_with_local_merge_us": round(avg(0), 2), "exchange_and_combine_us": round(avg(2), 2),
+               "note": "measured one step at a time with events between the phases; the partials cross NVLink as peer "
+                       "stores inside the kernel that combines them (fa_b200_exchange_combine)"}
+        # the same step with an NCCL all-gather and a combine launch instead, for comparison
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+        for _ in range(3):
+            self._run(self.q, nccl=True)
+        torch.cuda.synchronize()
+        for e in ev:
+            self._run(self.q, e, nccl=True)
+        torch.cuda.synchronize()
+        res["nccl_path"] = {"all_gather_us": round(avg(1), 2), "final_combine_us": round(avg(2), 2)}
+        return res
 
     def step_e2e(self):
         out = self._run(self.q_host.to(self.q.device, non_blocking=True))

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libfa_b200.so")
 OUT_HOOKS = os.path.join(HERE, "libfa_b200_testhooks.so")
-SOURCES = ["fa_api.cu", "fa_combine.cu", "fa_decode.cu", "fa_prefill.cu", "fa_prefill_pair.cu", "fa_prefill_dense.cu", "fa_kv_append.cu", "fa_glue.cu", "fa_block_select.cu"]
+SOURCES = ["fa_api.cu", "fa_combine.cu", "fa_decode.cu", "fa_prefill.cu", "fa_prefill_pair.cu", "fa_prefill_dense.cu", "fa_kv_append.cu", "fa_glue.cu", "fa_block_select.cu", "fa_exchange.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]

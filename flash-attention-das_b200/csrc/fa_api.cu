@@ -531,6 +531,93 @@ int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
   return FA_B200_OK;
 }
 
+size_t fa_b200_exchange_bytes(int32_t world, int32_t rows, int32_t d) {
+  if (world <= 0 || rows <= 0 || d <= 0) return 0;
+  return 2 * exchange_region_bytes(world, rows, d);
+}
+
+int fa_b200_exchange_alloc(size_t bytes, void** buf, void* ipc_handle_out) {
+  if (!buf || !ipc_handle_out) return FA_B200_ERR_NULL;
+  if (bytes == 0) return FA_B200_ERR_SHAPE;
+  static_assert(sizeof(cudaIpcMemHandle_t) == FA_B200_IPC_HANDLE_BYTES, "IPC handle size");
+  void* ptr = nullptr;
+  cudaError_t e = cudaMalloc(&ptr, bytes);
+  if (e != cudaSuccess) return cuda_fail("exchange alloc", e);
+  e = cudaMemset(ptr, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) {
+    cudaFree(ptr);
+    return cuda_fail("exchange alloc", e);
+  }
+  memcpy(ipc_handle_out, &h, sizeof(h));
+  *buf = ptr;
+  return FA_B200_OK;
+}
+
+int fa_b200_exchange_open(const void* ipc_handle, void** peer) {
+  if (!ipc_handle || !peer) return FA_B200_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, ipc_handle, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(peer, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? FA_B200_OK : cuda_fail("exchange open", e);
+}
+
+int fa_b200_exchange_close(void* peer) {
+  if (!peer) return FA_B200_ERR_NULL;
+  cudaError_t e = cudaIpcCloseMemHandle(peer);
+  return e == cudaSuccess ? FA_B200_OK : cuda_fail("exchange close", e);
+}
+
+int fa_b200_exchange_free(void* buf) {
+  if (!buf) return FA_B200_ERR_NULL;
+  cudaError_t e = cudaFree(buf);
+  return e == cudaSuccess ? FA_B200_OK : cuda_fail("exchange free", e);
+}
+
+int fa_b200_exchange_combine(const fa_b200_exchange_params* p, void* stream) {
+  if (!p) return FA_B200_ERR_NULL;
+  if (p->struct_size != sizeof(fa_b200_exchange_params)) return FA_B200_ERR_ABI;
+  if (p->world <= 0 || p->world > FA_B200_MAX_EXCHANGE_RANKS || p->rank < 0 || p->rank >= p->world) return FA_B200_ERR_SHAPE;
+  if (p->rows < 0 || p->h <= 0 || p->rows % p->h != 0 || p->d <= 0 || p->d % 4 != 0 || p->epoch == 0) return FA_B200_ERR_SHAPE;
+  if (p->do_push && (!p->o_local || !p->lse_local)) return FA_B200_ERR_NULL;
+  for (int i = 0; i < p->world; ++i)
+    if (!p->peers[i]) return FA_B200_ERR_NULL;
+  if (!sink_dtype_ok(p->s_aux, p->s_aux_dtype)) return FA_B200_ERR_DTYPE;
+  if (p->out_dtype != FA_B200_F16 && p->out_dtype != FA_B200_BF16 && p->out_dtype >= 0) return FA_B200_ERR_DTYPE;
+  if ((p->o_local && !aligned16(p->o_local)) || (p->out && !aligned16(p->out))) return FA_B200_ERR_ALIGN;
+  if (p->out && (p->out_batch_stride % 4 != 0 || p->out_head_stride % 4 != 0 || p->out_tok_stride % 4 != 0)) return FA_B200_ERR_STRIDE;
+  ExchangeKernelParams k{};
+  k.status = status_ptr();
+  if (!k.status) return FA_B200_ERR_CUDA;
+  k.o_local = p->o_local;
+  k.lse_local = p->lse_local;
+  for (int i = 0; i < p->world; ++i) k.peers[i] = p->peers[i];
+  k.region_bytes = exchange_region_bytes(p->world, p->rows, p->d);
+  k.out = p->out;
+  k.lse = p->lse;
+  k.out_batch_stride = p->out_batch_stride;
+  k.out_row_stride = p->out_head_stride;
+  k.out_tok_stride = p->out_tok_stride;
+  k.world = p->world;
+  k.rank = p->rank;
+  k.rows = p->rows;
+  k.h = p->h;
+  k.sq = p->seqlen_q > 0 ? p->seqlen_q : 1;
+  k.d = p->d;
+  k.epoch = p->epoch;
+  k.out_dtype = p->out_dtype;
+  k.s_aux = p->s_aux;
+  k.s_aux_dtype = p->s_aux_dtype;
+  k.do_push = p->do_push;
+  k.do_wait = p->do_wait;
+  cudaError_t e = launch_exchange_combine(k, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("exchange launch", e);
+  if (p->rows > 0) g_launches++;
+  return FA_B200_OK;
+}
+
 int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   DecodePlan pl = plan_decode(p);

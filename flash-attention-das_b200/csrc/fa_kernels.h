@@ -80,6 +80,27 @@ struct CombineKernelParams {
 };
 cudaError_t launch_combine(const CombineKernelParams& p, cudaStream_t stream);
 
+// Exchange of the ranks' split-KV partials over peer memory, fused with their combine (fa_exchange.cu).
+constexpr int kMaxExchangeRanks = 16;
+struct ExchangeKernelParams {
+  int* status;               // device status word
+  const float* o_local;      // (rows, d) this rank's partial
+  const float* lse_local;    // (rows)
+  void* peers[kMaxExchangeRanks];   // every rank's exchange buffer as mapped on this GPU (peers[rank]: its own)
+  size_t region_bytes;       // one half of a buffer: exchange_region_bytes(world, rows, d)
+  void* out;
+  float* lse;
+  int64_t out_batch_stride, out_row_stride, out_tok_stride;
+  int32_t world, rank, rows, h, sq, d;
+  uint32_t epoch;            // > 0, one more on every call, the same on every rank
+  int32_t out_dtype;         // FA_B200_F16 / BF16, or -1 for fp32
+  const void* s_aux;
+  int32_t s_aux_dtype;
+  int32_t do_push, do_wait;  // both set in normal use; separately for single-GPU tests of the two halves
+};
+size_t exchange_region_bytes(int world, int rows, int d);
+cudaError_t launch_exchange_combine(const ExchangeKernelParams& p, cudaStream_t stream);
+
 // Prefill (dense / varlen / block-sparse) on tcgen05.
 struct PrefillKernelParams {
   int* status;         // device status word

@@ -93,14 +93,66 @@ def gather_partials(o_partial: torch.Tensor, lse_partial: torch.Tensor,
     return o_all, l_all
 
 
+class PartialExchange:
+    """Peer-memory exchange of the ranks' split-KV partials, fused with their combine (fa_b200_exchange_combine): one
+    launch per step instead of an all-gather and a combine launch.
+
+    Set-up (collective over ``group``; allocates and synchronises, so do it once, outside the step loop): every rank
+    lets the library allocate its exchange buffer, the 64-byte CUDA IPC handles travel through ``all_gather_object``,
+    and every rank maps the other ranks' buffers.  All ranks must be processes of one node with peer access between
+    their GPUs.  ``combine`` must then be called the same number of times on every rank (the call counter is the epoch
+    the kernels synchronise on).  ``close()`` unmaps and frees; call it on every rank after a barrier."""
+
+    def __init__(self, rows: int, d: int, device, group: Optional[dist.ProcessGroup] = None):
+        import flash_attn_2_cuda as cuda
+        self._cuda = cuda
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 16:
+            raise ValueError("PartialExchange takes at most 16 ranks")
+        self.rows, self.d, self.device = rows, d, torch.device(device)
+        self.epoch = 0
+        self._own, handle, self.bytes = cuda.exchange_alloc(self.world, rows, d, self.device)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self.peers = []
+        self._opened = []
+        for r, hd in enumerate(handles):
+            if r == self.rank:
+                self.peers.append(self._own)
+            else:
+                ptr = cuda.exchange_open(hd, self.device)
+                self._opened.append(ptr)
+                self.peers.append(ptr)
+        dist.barrier(group=group)
+
+    def combine(self, o_local: torch.Tensor, lse_local: torch.Tensor, h: int, out_dtype=torch.bfloat16, s_aux=None):
+        """o_local (rows, d) fp32, lse_local (rows) fp32 of this rank -> (out (rows, d), lse (rows)), identical on every
+        rank.  One launch on the current stream."""
+        self.epoch += 1
+        return self._cuda.exchange_combine(o_local, lse_local, self.peers, self.rank, self.epoch, h, out_dtype=out_dtype,
+                                           s_aux=s_aux)
+
+    def close(self):
+        for ptr in self._opened:
+            self._cuda.exchange_close(ptr)
+        self._opened = []
+        if self._own:
+            self._cuda.exchange_free(self._own)
+            self._own = 0
+
+
 def decode_split_across_gpus(q, k_cache_local, v_cache_local, local_seqlens, local_block_table, softmax_scale=None,
                              group: Optional[dist.ProcessGroup] = None, out_dtype=torch.bfloat16, q_descale=None,
                              k_descale=None, v_descale=None, s_aux=None, local_window_left: int = -1,
-                             phase_events: Optional[Sequence["torch.cuda.Event"]] = None):
+                             phase_events: Optional[Sequence["torch.cuda.Event"]] = None,
+                             exchange: Optional[PartialExchange] = None):
     """Decode where each rank holds a slice of every sequence's KV pages.  q: (b, 1, h, 128), identical on every
     rank; the caches, `local_seqlens` and `local_block_table` describe this rank's slice.  Attention sinks
     (``s_aux``, (h)) enter once, in the final combine; a sliding window is given per slice (``window_for_slice``).
     Returns (out (b, 1, h, 128) out_dtype, lse (b, h) fp32), identical on every rank.
+    ``exchange``: a PartialExchange for (b * h rows, d) set up over the same group: the partials then cross NVLink as
+    peer stores inside ONE kernel that also combines them, instead of an NCCL all-gather followed by a combine launch.
     ``phase_events``: four CUDA events recorded on the current stream before the local decode, after it (partition
     kernel with its in-kernel merge), after the all-gather and after the final combine (timing of the three phases)."""
     import flash_attn_2_cuda as cuda
@@ -113,6 +165,13 @@ def decode_split_across_gpus(q, k_cache_local, v_cache_local, local_seqlens, loc
                                          softmax_scale, q_descale, k_descale, v_descale, window_left=local_window_left)
     if phase_events is not None:
         phase_events[1].record()
+    if exchange is not None:
+        if phase_events is not None:
+            phase_events[2].record()    # no separate gather phase: the exchange is part of the kernel that combines
+        out, lse = exchange.combine(o_part.view(b * h, d), l_part.view(b * h), h, out_dtype=out_dtype, s_aux=s_aux)
+        if phase_events is not None:
+            phase_events[3].record()
+        return out.view(b, 1, h, d), lse.view(b, h)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         rows = b * h
         if (o_part.is_cuda and (rows * (d + 1)) % 4 == 0 and

@@ -16,7 +16,7 @@ eager fallback — if the shared library is missing the import fails.
 """
 import ctypes
 import os
-from typing import Optional
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -102,6 +102,21 @@ class DecodeParams(_SizedStruct):
     ]
 
 
+class ExchangeParams(_SizedStruct):
+    """struct fa_b200_exchange_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("struct_size", ctypes.c_uint32),
+        ("world", _c_i32), ("rank", _c_i32),
+        ("rows", _c_i32), ("h", _c_i32), ("seqlen_q", _c_i32), ("d", _c_i32),
+        ("o_local", _c_vp), ("lse_local", _c_vp),
+        ("peers", _c_vp * 16),
+        ("epoch", ctypes.c_uint32), ("do_push", _c_i32), ("do_wait", _c_i32),
+        ("out", _c_vp), ("lse", _c_vp),
+        ("out_batch_stride", _c_i64), ("out_head_stride", _c_i64), ("out_tok_stride", _c_i64),
+        ("out_dtype", _c_i32), ("s_aux", _c_vp), ("s_aux_dtype", _c_i32),
+    ]
+
+
 class CombineParams(_SizedStruct):
     """struct fa_b200_combine_params (include/fa_b200.h)."""
     _fields_ = [
@@ -178,6 +193,18 @@ _lib.fa_b200_last_cuda_error.restype = ctypes.c_char_p
 _lib.fa_b200_device_status.restype = ctypes.c_int
 _lib.fa_b200_abi_version.restype = ctypes.c_int
 _lib.fa_b200_launch_count.restype = ctypes.c_uint64
+_lib.fa_b200_exchange_bytes.argtypes = [_c_i32, _c_i32, _c_i32]
+_lib.fa_b200_exchange_bytes.restype = ctypes.c_size_t
+_lib.fa_b200_exchange_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
+_lib.fa_b200_exchange_alloc.restype = ctypes.c_int
+_lib.fa_b200_exchange_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+_lib.fa_b200_exchange_open.restype = ctypes.c_int
+_lib.fa_b200_exchange_close.argtypes = [_c_vp]
+_lib.fa_b200_exchange_close.restype = ctypes.c_int
+_lib.fa_b200_exchange_free.argtypes = [_c_vp]
+_lib.fa_b200_exchange_free.restype = ctypes.c_int
+_lib.fa_b200_exchange_combine.argtypes = [ctypes.POINTER(ExchangeParams), _c_vp]
+_lib.fa_b200_exchange_combine.restype = ctypes.c_int
 _lib.fa_b200_read_stream.argtypes = [_c_vp, _c_i64, _c_vp, _c_vp]
 _lib.fa_b200_read_stream.restype = ctypes.c_int
 _lib.fa_b200_set_print_param.argtypes = [ctypes.c_int]
@@ -866,6 +893,74 @@ def combine(o_partial, lse_partial, out_dtype=torch.bfloat16, h: Optional[int] =
     _set_sinks(p, s_aux, h or 1)
     with _on_device(o_partial.device):
         _check(_lib.fa_b200_combine(ctypes.byref(p), _stream(o_partial)), "combine")
+    return out, lse
+
+
+# ------------------------------------------------------------------------------------------------
+# exchange of split-KV partials between GPUs over peer memory, fused with the combine
+# ------------------------------------------------------------------------------------------------
+IPC_HANDLE_BYTES = 64
+
+
+def exchange_alloc(world: int, rows: int, d: int, device) -> Tuple[int, bytes, int]:
+    """This rank's exchange buffer for ``rows`` partial rows of ``d`` columns among ``world`` ranks, allocated and
+    zeroed by the library on ``device``: (device pointer, 64-byte CUDA IPC handle for the other ranks' processes, size).
+    A set-up call: it allocates and synchronises."""
+    n = int(_lib.fa_b200_exchange_bytes(world, rows, d))
+    _require(n > 0, "exchange_alloc: world, rows and d must be positive")
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(IPC_HANDLE_BYTES)
+    with _on_device(torch.device(device)):
+        _check(_lib.fa_b200_exchange_alloc(n, ctypes.byref(ptr), handle), "exchange_alloc")
+    return int(ptr.value), handle.raw, n
+
+
+def exchange_open(handle: bytes, device) -> int:
+    """Map another process's exchange buffer on ``device``; returns the device pointer."""
+    _require(len(handle) == IPC_HANDLE_BYTES, "exchange_open: a 64-byte IPC handle")
+    ptr = ctypes.c_void_p()
+    with _on_device(torch.device(device)):
+        _check(_lib.fa_b200_exchange_open(handle, ctypes.byref(ptr)), "exchange_open")
+    return int(ptr.value)
+
+
+def exchange_close(ptr: int) -> None:
+    _check(_lib.fa_b200_exchange_close(ptr), "exchange_close")
+
+
+def exchange_free(ptr: int) -> None:
+    _check(_lib.fa_b200_exchange_free(ptr), "exchange_free")
+
+
+def exchange_combine(o_local, lse_local, peers: Sequence[int], rank: int, epoch: int, h: int, out_dtype=torch.bfloat16,
+                     s_aux=None, seqlen_q: int = 1, push: bool = True, wait: bool = True, rows: Optional[int] = None,
+                     d: Optional[int] = None, device=None):
+    """One launch of fa_b200_exchange_combine on the current stream: this rank's partial (o_local (rows, d) fp32,
+    lse_local (rows) fp32) goes to slot ``rank`` of every buffer in ``peers`` (device pointers of ranks 0 .. world-1 as
+    mapped on this GPU), the kernel waits for every rank's partial of this ``epoch`` in its own buffer and combines.
+    Returns (out (rows, d) out_dtype, lse (rows) fp32).  ``push`` / ``wait`` run the two halves alone (tests)."""
+    world = len(peers)
+    if o_local is not None:
+        _require(o_local.dtype == torch.float32 and lse_local.dtype == torch.float32 and o_local.is_contiguous() and
+                 lse_local.is_contiguous() and o_local.dim() == 2, "exchange_combine: packed fp32 partials (rows, d) and (rows)")
+        rows, d = o_local.shape
+        device = o_local.device
+    device = torch.device(device)
+    out = torch.empty((rows, d), dtype=out_dtype, device=device)
+    lse = torch.empty((rows,), dtype=torch.float32, device=device)
+    p = ExchangeParams()
+    p.world, p.rank, p.rows, p.h, p.seqlen_q, p.d = world, rank, rows, h, seqlen_q, d
+    p.o_local, p.lse_local = _ptr(o_local), _ptr(lse_local)
+    for i, ptr in enumerate(peers):
+        p.peers[i] = ptr
+    p.epoch, p.do_push, p.do_wait = epoch, int(push), int(wait)
+    p.out, p.lse = out.data_ptr(), lse.data_ptr()
+    # rows are (b, h, token), packed
+    p.out_batch_stride, p.out_head_stride, p.out_tok_stride = h * seqlen_q * d, seqlen_q * d, d
+    p.out_dtype = -1 if out_dtype == torch.float32 else _DT[out_dtype]
+    _set_sinks(p, s_aux, h)
+    with _on_device(device):
+        _check(_lib.fa_b200_exchange_combine(ctypes.byref(p), ctypes.c_void_p(_stream_handle(device))), "exchange_combine")
     return out, lse
 
 

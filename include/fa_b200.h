@@ -321,6 +321,53 @@ typedef struct fa_b200_combine_params {
 FA_B200_API int fa_b200_combine(const fa_b200_combine_params* p, void* stream);
 
 /*
+ * Split-KV across GPUs without a collective library: exchange of the ranks' partial results over peer memory, fused
+ * with their combine.  The reference has no multi-GPU path; this replaces the all-gather + fa_b200_combine pair a caller
+ * would otherwise put after the per-rank decode (fa_b200_decode_params.o_partial_out).
+ *
+ * Set-up, once per process and problem shape (these calls allocate and synchronise; they are not for the hot path):
+ *   fa_b200_exchange_bytes(world, rows, d)        size of a rank's exchange buffer (rows = b * h * seqlen_q)
+ *   fa_b200_exchange_alloc(bytes, &buf, handle)   cudaMalloc + zero fill on the current device, and a 64-byte CUDA IPC
+ *                                                 handle of the buffer to hand to the other ranks' processes
+ *   fa_b200_exchange_open(handle, &peer)          maps another PROCESS's buffer on the current device (peer access is
+ *                                                 enabled as needed); a rank uses its own `buf` for itself
+ *   fa_b200_exchange_close(peer) / fa_b200_exchange_free(buf)
+ * Per step, on every rank, after the decode that produced (o_local, lse_local):
+ *   fa_b200_exchange_combine: one launch, one CTA per row.  It stores the row's partial into slot `rank` of every
+ *   rank's buffer, publishes it with a system-scope release of the row's flag, waits until all slots of its own buffer
+ *   carry the call's epoch, and writes the combined row (same arithmetic as fa_b200_combine, sinks included).
+ *   `epoch` starts at 1 and grows by one per call, the same value on every rank; the buffer is double and calls
+ *   alternate between its halves.  The wait is bounded: a rank whose peers never arrive returns, leaves `out` untouched
+ *   and reports FA_B200_ERR_DEVICE_TIMEOUT through fa_b200_device_status().  world <= 16, d a multiple of 4.
+ *   The kernels of the ranks wait for one another: run one rank per GPU, never two ranks' launches on one GPU.
+ *   do_push / do_wait (both 1 in normal use) run the two halves of the kernel separately, for tests on one GPU.
+ */
+#define FA_B200_IPC_HANDLE_BYTES 64
+#define FA_B200_MAX_EXCHANGE_RANKS 16
+typedef struct fa_b200_exchange_params {
+  uint32_t struct_size;                /* sizeof(fa_b200_exchange_params) */
+  int32_t world, rank;
+  int32_t rows, h, seqlen_q, d;        /* rows = b * h * seqlen_q, ordered (b, h, token) */
+  const float* o_local;                /* (rows, d) fp32: this rank's partial */
+  const float* lse_local;              /* (rows) fp32, natural log; +-inf = no keys on this rank */
+  void* peers[FA_B200_MAX_EXCHANGE_RANKS];   /* exchange buffers of ranks 0 .. world-1 as mapped on this GPU */
+  uint32_t epoch;
+  int32_t do_push, do_wait;
+  void* out;                           /* element offset of row (b, h, t): b*out_batch_stride + h*out_head_stride + t*out_tok_stride */
+  float* lse;                          /* optional (rows) */
+  int64_t out_batch_stride, out_head_stride, out_tok_stride;
+  int32_t out_dtype;                   /* FA_B200_F16 / FA_B200_BF16, or -1 for fp32 */
+  const void* s_aux;                   /* optional attention sinks (h) */
+  int32_t s_aux_dtype;
+} fa_b200_exchange_params;
+FA_B200_API size_t fa_b200_exchange_bytes(int32_t world, int32_t rows, int32_t d);
+FA_B200_API int fa_b200_exchange_alloc(size_t bytes, void** buf, void* ipc_handle_out);
+FA_B200_API int fa_b200_exchange_open(const void* ipc_handle, void** peer);
+FA_B200_API int fa_b200_exchange_close(void* peer);
+FA_B200_API int fa_b200_exchange_free(void* buf);
+FA_B200_API int fa_b200_exchange_combine(const fa_b200_exchange_params* p, void* stream);
+
+/*
  * Raw-pointer paged attention over a whole batch of requests, with the argument list of the reference's
  * extern "C" kv_cache_attention(q, seq_offsets, max_seqlen_q, max_seqlen_k, k_caches, v_caches, page_tables, cache_lens,
  * out, num_query, num_tokens, num_q_head, num_kv_head, num_dim, num_pages, page_size, dtype, layout)

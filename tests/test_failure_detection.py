@@ -7,7 +7,8 @@ FA_B200_ERR_DEVICE_TIMEOUT through fa_b200_device_status(), leave the context us
 next launch of the same kernel allocates all 512 columns again and must pass its parity check).
 
 CPU (gloo, world size 2): a rank that never joins the all-gather of the split-KV partials must not hang its peer: the
-peer leaves gather_partials with an error inside the group's timeout."""
+peer leaves gather_partials with an error inside the group's timeout.  The peer-memory exchange kernel is covered on
+the GPU by the same kind of test: a launch whose peers never push gives up, reports, and the buffer stays usable."""
 import os
 import socket
 import subprocess
@@ -78,6 +79,20 @@ _CHILD = textwrap.dedent('''
         out = run()
     assert cuda.device_status() == 0
     assert (out.cpu().float() - ref).abs().max().item() < 2e-2
+
+    # ---- exchange of split-KV partials between GPUs: the other ranks' partials never arrive
+    buf, _, _ = cuda.exchange_alloc(2, 8, 128, torch.device(dev))
+    o, l = torch.randn(8, 128, device=dev), torch.randn(8, device=dev)
+    cuda.exchange_combine(o, l, [buf, buf], 0, 1, 8)          # "rank 0" pushes and waits for a rank 1 that does not exist
+    st = cuda.device_status()                                  # the wait gave up after about a millisecond
+    assert st == TIMEOUT, ("exchange", st)
+    for r in (0, 1):                                           # the buffer is still usable: both ranks' pushes, then a wait
+        cuda.exchange_combine(o, l, [buf, buf], r, 2, 8, push=True, wait=False)
+    out, lse = cuda.exchange_combine(None, None, [buf, buf], 0, 2, 8, push=False, wait=True, rows=8, d=128, device=torch.device(dev),
+                                     out_dtype=torch.float32)
+    assert cuda.device_status() == 0
+    assert (out - o).abs().max().item() < 1e-5                 # two equal partials merge to themselves
+    cuda.exchange_free(buf)
     print("FAILURE-DETECTION-OK")
 ''')
 
