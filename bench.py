@@ -54,9 +54,9 @@ TRAFFIC_RATIO = {"decode_bf16": 1.007, "decode_bf16_replica": 1.007, "decode_fp8
 # prefill is tensor-bound, its algorithmic unit is FLOPs; DRAM traffic is reported in bytes per token of the
 # captured case: bf16 526.2 MB for 19,679 tokens (1.31x the compulsory q+k+v+out bytes), e4m3 188.7 MB for
 # 4 x 4096 tokens (0.80x: a third of the 134 MB bf16 output is still in L2 when the launch ends),
-# block-sparse 3.090 GB read + 0.237 GB written for the full configuration's 32,768 tokens.
+# block-sparse 0.406 GB read + 0.238 GB written for the full configuration's 32,768 tokens.
 PREFILL_TRAFFIC_BYTES_PER_TOKEN = {"prefill_bf16": 526.2e6 / 19679, "prefill_fp8": 188.7e6 / 16384,
-                                   "sparse_bf16": 3.3273e9 / 32768}
+                                   "sparse_bf16": 0.6447e9 / 32768}
 
 
 def load_peaks():
