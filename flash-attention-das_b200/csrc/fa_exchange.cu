@@ -48,18 +48,25 @@ __global__ void __launch_bounds__(kExchangeThreads) exchange_combine_kernel(cons
   const size_t my_slot = static_cast<size_t>(p.rank) * p.rows + row;
   if (tid == 0) sm_abort = 0;
 
+  // Launched with programmatic stream serialisation: the CTAs may be resident before the decode kernel that produces
+  // o_local / lse_local has finished; nothing above touched global memory.
+  griddep_wait();
   if (p.do_push) {
     const float4* src = reinterpret_cast<const float4*>(p.o_local) + static_cast<size_t>(row) * nv;
     const float my_lse = p.lse_local[row];
+    // each warp serves the ranks warp, warp + 4, ...: first all its stores, one system-wide fence for them together
+    // (a fence waits for the peers' acknowledgements, a round trip over NVLink), then the flags
     for (int dst = warp; dst < p.world; dst += kExchangeThreads / 32) {
       uint8_t* base = static_cast<uint8_t*>(p.peers[dst]);
       float4* od = reinterpret_cast<float4*>(base + o_off) + my_slot * nv;
       for (int c = lane; c < nv; c += 32) od[c] = src[c];
       if (lane == 0) reinterpret_cast<float*>(base + l_off)[my_slot] = my_lse;
-      __threadfence_system();
-      __syncwarp();
-      if (lane == 0) st_release_sys(reinterpret_cast<uint32_t*>(base + f_off) + my_slot, p.epoch);
     }
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0)
+      for (int dst = warp; dst < p.world; dst += kExchangeThreads / 32)
+        st_release_sys(reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p.peers[dst]) + f_off) + my_slot, p.epoch);
   }
   __syncthreads();
 
@@ -141,8 +148,16 @@ __global__ void __launch_bounds__(kExchangeThreads) exchange_combine_kernel(cons
 
 cudaError_t launch_exchange_combine(const ExchangeKernelParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return cudaSuccess;
-  exchange_combine_kernel<<<p.rows, kExchangeThreads, 0, stream>>>(p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.rows);
+  cfg.blockDim = dim3(kExchangeThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, exchange_combine_kernel, p);
 }
 
 }  // namespace fa
