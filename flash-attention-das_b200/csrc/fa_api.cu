@@ -966,18 +966,22 @@ static int fwd_common(const fa_b200_fwd_params* p, void* stream_, bool sparse) {
     k.num_m_blocks = (p->seqlen_q + 127) / 128;
   }
   // Kernel choice.  Dense / varlen prefill with an even GQA group: persistent CTAs that work on two heads of the
-  // group at once and share every K/V tile ("pair").  Other head layouts (MHA, odd groups): persistent CTAs with
-  // double-buffered scores ("dense").  Tile lists are per head and run one tile per CTA ("single").
+  // group at once and share every K/V tile ("pair").  Other head layouts (MHA, odd groups): one tile per CTA ("single"),
+  // and for long sequences persistent CTAs with double-buffered scores ("dense").  Tile lists are per head: "single".
   // kernel_choice / FA_B200_PREFILL_KERNEL override the choice where the chosen kernel can take the call.
   const bool even_group = (p->h / p->h_k) % 2 == 0;
-  // Tile lists and other head dimensions: the one-tile kernel.  Paged K/V (any pool layout): the two-tile kernel where
-  // the GQA group is even, else the one-tile kernel.
-  const bool one_tile_only = sparse || p->d != kHeadDim || (paged && !even_group);
-  int which = one_tile_only ? 0 : (even_group ? 1 : 2);
+  // Tile lists and other head dimensions: the one-tile kernel.  Paged K/V: the two-tile kernel where the GQA group is
+  // even (any pool layout), else the double-buffered kernel, which reads the block table too but no transposed V pool.
+  const bool one_tile_only = sparse || p->d != kHeadDim || (paged && !even_group && p->v_transposed);
+  // MHA and odd groups, measured (bf16, causal, 16 / 16 and 24 / 8 heads): the one-tile kernel with two CTAs per SM is
+  // ahead of the double-buffered persistent kernel up to a few thousand tokens per sequence (8 x 4096: 884 against 728
+  // TFLOP/s; 32 x 1024: 536 against 441; paged 8 x 4096: 850 against 705) and level or behind at 16384 (923 / 920 and
+  // 865 / 901), so the persistent kernel takes over above 8192 query tokens.
+  int which = one_tile_only ? 0 : (even_group ? 1 : (p->seqlen_q > 8192 ? 2 : 0));
   const int choice = p->kernel_choice > 0 ? p->kernel_choice : g_env.prefill_kernel;
   if (choice == 1) which = 0;
   else if (choice == 2 && !one_tile_only && even_group) which = 1;
-  else if (choice == 3 && !one_tile_only && !paged) which = 2;
+  else if (choice == 3 && !one_tile_only && !(paged && p->v_transposed)) which = 2;
 #ifdef FA_B200_TEST_HOOKS
   if (which == 1) k.test_withhold = g_test_withhold.exchange(0);
 #endif

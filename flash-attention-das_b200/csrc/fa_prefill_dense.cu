@@ -84,11 +84,19 @@ __device__ __forceinline__ bool get_item(const PrefillKernelParams& p, int L, It
   if (p.cu_seqlens_q) {
     it.q_row0 = p.cu_seqlens_q[it.bidb];
     sq = p.cu_seqlens_q[it.bidb + 1] - it.q_row0;
-    it.k_row0 = p.cu_seqlens_k[it.bidb];
-    it.sk = p.cu_seqlens_k[it.bidb + 1] - it.k_row0;
+    it.k_row0 = p.paged ? 0 : p.cu_seqlens_k[it.bidb];
+    it.sk = p.paged ? 0 : p.cu_seqlens_k[it.bidb + 1] - it.k_row0;
     it.coord_b = 0;
   } else {
     it.q_row0 = 0; it.k_row0 = 0; sq = p.seqlen_q; it.sk = p.seqlen_k; it.coord_b = it.bidb;
+  }
+  if (p.paged) {   // keys in a paged pool: their number comes with the block table, rows are addressed page by page
+    it.k_row0 = 0;
+    it.sk = p.seqused_k[it.bidb];
+    if (p.max_keys > 0 && it.sk > p.max_keys) {   // longer than the block table row: cut and report
+      it.sk = static_cast<int>(p.max_keys);
+      atomicOr(p.status, 0x10000);
+    }
   }
   it.m0 = m_block * kBlockM;
   if (it.m0 >= sq) return false;
@@ -188,6 +196,26 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         pos.advance(1);
         return true;
       };
+      // the same for a K or V tile whose 128 keys lie in a paged pool: one box of box_rows rows per page piece through
+      // the block table; boxes that start past the end of the sequence are not fetched (their table slots are not
+      // valid) and the softmax warps clear what the tile holds there
+      auto load_paged_tile = [&](const CUtensorMap* tm, const Item& it, int start) -> bool {
+        if (!mbar_wait(smem_u32(&ring_empty[pos.slot]), pos.phase ^ 1u, wctx)) return false;
+        const uint32_t bar = smem_u32(&ring_full[pos.slot]);
+        const int nbox = min(kBlockN / p.box_rows, (it.sk - start + p.box_rows - 1) / p.box_rows);
+        mbar_expect_tx(bar, static_cast<uint32_t>(nbox) * p.box_rows * 128u * T::kHalves);
+        const int32_t* bt = p.block_table + static_cast<int64_t>(it.bidb) * p.bt_stride;
+        for (int i = 0; i < nbox; ++i) {
+          const int tok = start + i * p.box_rows;
+          const int page = bt[tok / p.page_size], prow = tok % p.page_size;
+#pragma unroll
+          for (int hf = 0; hf < T::kHalves; ++hf)
+            tma_load_4d(ring_smem + pos.slot * T::kTileBytes + hf * T::kHalfBytes + i * p.box_rows * 128, tm, bar, hf * 64, it.hk,
+                        prow, page);
+        }
+        pos.advance(1);
+        return true;
+      };
       uint32_t pub = 0;
       auto publish = [&](int v) -> bool {
         const uint32_t slot = pub % kIdSlots;
@@ -206,8 +234,11 @@ prefill_dense_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (it.n_tiles == 0) continue;
         ok = load_tile(&tmap_q, it.head, it.q_row0 + it.m0, it.coord_b);
         for (int j = 0; ok && j < it.n_tiles; ++j) {
-          ok = load_tile(&tmap_k, it.hk, it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b) &&
-               load_tile(&tmap_v, it.hk, it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b);
+          if (p.paged)
+            ok = load_paged_tile(&tmap_k, it, (it.tile0 + j) * kBlockN) && load_paged_tile(&tmap_v, it, (it.tile0 + j) * kBlockN);
+          else
+            ok = load_tile(&tmap_k, it.hk, it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b) &&
+                 load_tile(&tmap_v, it.hk, it.k_row0 + (it.tile0 + j) * kBlockN, it.coord_b);
         }
       }
       if (ok) publish(-1);

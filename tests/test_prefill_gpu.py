@@ -342,6 +342,47 @@ def test_paged_prefill_reads_pages_directly(fa, page, dtype):
         _check_lse(lse[:, int(cq[i]):int(cq[i + 1])].cpu(), ref_lse[0])
 
 
+@pytest.mark.parametrize("kernel,h,h_k", [("dense", 4, 4), ("dense", 6, 2), ("dense", 8, 2), ("single", 6, 2), ("pair", 8, 2)])
+@pytest.mark.parametrize("page,dtype", [(16, torch.bfloat16), (64, torch.float8_e4m3fn), (256, torch.float16)])
+def test_paged_prefill_on_each_kernel(fa, monkeypatch, kernel, h, h_k, page, dtype):
+    """Every prefill kernel reads K/V through the block table: the persistent double-buffered kernel (MHA, odd and even
+    groups), the one-tile kernel and the two-tile kernel over NaN-poisoned pools, against the oracle."""
+    from _util import clean_nan, make_paged
+    flash_attn, cuda = fa
+    fp8 = dtype == torch.float8_e4m3fn
+    g = gen(700 + page + h)
+    lens_k = [300, 130, 1000, 64, 257]
+    lens_q = [300, 2, 129, 64, 200]
+    kc, vc, bt, sl = make_paged(g, lens_k, h_k, page, torch.bfloat16 if fp8 else dtype)
+    q = randn(g, sum(lens_q), h, 128, dtype=torch.bfloat16 if fp8 else dtype)
+    if fp8:   # NaN-poisoned e4m3 pools: every byte 0x7f outside the sequences
+        nan_k, nan_v = torch.isnan(kc), torch.isnan(vc)
+        kc, vc, q = [t.nan_to_num(0.0).to(dtype) for t in (kc, vc, q)]
+        kc.view(torch.uint8)[nan_k] = 0x7f
+        vc.view(torch.uint8)[nan_v] = 0x7f
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    monkeypatch.setenv("FA_B200_PREFILL_KERNEL", kernel)
+    out = flash_attn.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cq.cuda(), None, max(lens_q), max(lens_k),
+                                            seqused_k=sl.cuda(), causal=True, block_table=bt.cuda())
+    torch.cuda.synchronize()
+    assert cuda.device_status() == 0
+    assert ("prefill_" + kernel) in cuda.last_launch_info()
+    kcc, vcc = (kc.float().nan_to_num(0.0), vc.float().nan_to_num(0.0)) if fp8 else (clean_nan(kc), clean_nan(vc))
+    for i, (lq, lk) in enumerate(zip(lens_q, lens_k)):
+        qi = q[int(cq[i]):int(cq[i + 1])][None]
+        ki, vi = O.gather_paged_kv(kcc, bt[i], lk)[None], O.gather_paged_kv(vcc, bt[i], lk)[None]
+        got = out[int(cq[i]):int(cq[i + 1])].cpu()[None]
+        if fp8:
+            ref32, _ = O.attention_ref(qi.float(), ki, vi, causal=True, out_dtype=torch.float32)
+            ref_p, _ = O.attention_ref(qi.float(), ki, vi, causal=True, out_dtype=torch.float32,
+                                       intermediate_dtype=torch.float8_e4m3fn)
+            assert max_err(got, ref32) <= 2 * max_err(ref_p, ref32) + 2 ** -6, (kernel, i)
+        else:
+            ref32, _ = O.attention_ref(qi, ki, vi, causal=True, out_dtype=torch.float32)
+            ref_pt, _ = O.attention_ref(qi, ki, vi, causal=True, upcast=False, reorder_ops=True)
+            assert_close_to_oracle(got, ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"paged prefill {kernel} seq {i} page {page}")
+
+
 def test_kvcache_call_with_several_query_tokens(fa):
     """flash_attn_with_kvcache with seqlen_q > 1 (speculative / chunked decoding) over the paged cache."""
     from _util import clean_nan, make_paged
