@@ -873,6 +873,9 @@ def run_workload(name, args, dev, rank, world, shard, peaks, cpu_budget):
         res["host_us_per_call"] = host_us_per_call(wl, 100)
     if cpu_budget > 0 and rank == 0:
         res["cpu_baseline"] = cpu_baseline(name, args.seed, budget_s=cpu_budget)
+    if getattr(wl, "_ex", None) is not None:   # unmap the peers' exchange buffers once every rank is done with them
+        barrier(world)
+        wl._ex.close()
     del wl
     torch.cuda.empty_cache()
     return res
