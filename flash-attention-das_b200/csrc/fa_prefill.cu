@@ -6,7 +6,7 @@
 //   warp 4      TMA producer: Q once, then K_j / V_j tiles into a two-slot shared-memory ring (128B swizzle)
 //   warp 5      MMA issuer:   S = Q K_j^T and O += P V_j with tcgen05.mma, accumulators in TMEM
 //   warps 6-7   idle: they complete the second warpgroup, which hands its registers to the softmax warpgroup
-//               (setmaxnreg: 40 / 216 per thread; a row of 128 scores is live in registers at once)
+//               (setmaxnreg: 40 / 216 per thread, 248 above d = 128; a row of 128 scores is live in registers at once)
 // This kernel serves block-sparse lists (per-head tile lists cannot share K/V tiles between heads), K/V read through
 // a block table (pages in the bshd / bhsd layouts, or with V stored transposed), and the head dimensions other than
 // 128 (64, 192, 256, and 192 with 128 for v: fp16 / bf16; above 128 one CTA per SM, 512 TMEM columns); dense GQA
@@ -23,10 +23,14 @@ namespace fa {
 namespace {
 
 constexpr int kMaxSparseTiles = 512;
-constexpr int kSlots = 2;           // K/V ring
+constexpr int kMaxSlots = 3;        // K/V ring: barrier area laid out for this many
+// Ring slots of a head dimension: two, and three at 192 (48 KB tiles: Q + 3 slots = 192 KB), where the third slot lets
+// K_{j+1} arrive while K_j and V_j are still in use, so that the second S buffer is filled at once.
+__host__ __device__ constexpr int ring_slots(int hd) { return hd == 192 ? 3 : 2; }
 constexpr int kThreads = 32 * 8;
 constexpr int kProducerWarp = 4, kMmaWarp = 5;
-// TMEM columns: S (128) + O (head dimension), rounded up to a power of two
+// TMEM columns: S (128) + O (head dimension of v), rounded up to a power of two.  Above 128 a CTA has its SM to itself
+// and all 512 columns: two S buffers (256) + O (up to 256), see kTwoS in the kernel.
 __host__ __device__ constexpr int tmem_cols(int hd) { return 128 + hd <= 256 ? 256 : 512; }
 
 struct SmemLayoutInfo {
@@ -40,9 +44,9 @@ __host__ __device__ constexpr SmemLayoutInfo smem_layout() {
   SmemLayoutInfo s{};
   s.q_off = 0;
   s.ring_off = s.q_off + T::kTileBytes;
-  s.bar_off = s.ring_off + kSlots * T::kTileBytes;
-  // barriers: q_full, kv_full[kSlots], kv_empty[kSlots], s_full, p_full, o_full
-  s.tiles_off = s.bar_off + 8 * (4 + 2 * kSlots);
+  s.bar_off = s.ring_off + ring_slots(HD) * T::kTileBytes;
+  // barriers: q_full, kv_full[kMaxSlots], kv_empty[kMaxSlots], s_full[2], p_full[2], o_full
+  s.tiles_off = s.bar_off + 8 * (6 + 2 * kMaxSlots);
   s.misc_off = s.tiles_off + 4 * kMaxSparseTiles;
   s.total = s.misc_off + 32;
   return s;
@@ -62,15 +66,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   static_assert(!VT || (HD == kHeadDim && HDV == kHeadDim && !T::kFp8), "transposed V: 16-bit types, d = 128");
   constexpr SmemLayoutInfo L = smem_layout<DT, HD>();
   constexpr int kTmemCols = tmem_cols(HDV);
+  constexpr int kSlots = ring_slots(HD);
+  // Head dimensions above 128 (one CTA per SM, 512 TMEM columns): two S buffers.  Key tile j uses buffer j & 1, so
+  // S(j+1) = Q K_{j+1}^T is issued BEFORE P(j) V_j and runs while the softmax of tile j is still at work; with one buffer
+  // the products and the softmax of a CTA take turns and nothing else is resident on the SM to fill the gaps.
+  constexpr bool kTwoS = HD > kHeadDim;
+  constexpr uint32_t kColO = kTwoS ? 256 : 128;
+  static_assert(!kTwoS || 256 + HDV <= 512, "two S buffers and O must fit tensor memory");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bar_off);
   uint64_t* q_full = bars;
   uint64_t* kv_full = q_full + 1;
-  uint64_t* kv_empty = kv_full + kSlots;
-  uint64_t* s_full = kv_empty + kSlots;
-  uint64_t* p_full = s_full + 1;
-  uint64_t* o_full = p_full + 1;
+  uint64_t* kv_empty = kv_full + kMaxSlots;
+  uint64_t* s_full = kv_empty + kMaxSlots;   // [2]
+  uint64_t* p_full = s_full + 2;          // [2]
+  uint64_t* o_full = p_full + 2;
   int* sm_tiles = reinterpret_cast<int*>(smem + L.tiles_off);
   uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
   int* sm_ntiles = reinterpret_cast<int*>(smem + L.misc_off + 4);
@@ -163,8 +174,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   } else if (threadIdx.x == 32) {
     *abort_flag = 0;
     mbar_init(smem_u32(q_full), 1);
-    mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(p_full), 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&s_full[i]), 1);
+      mbar_init(smem_u32(&p_full[i]), 128);
+    }
     mbar_init(smem_u32(o_full), 1);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&kv_full[s]), 1);
@@ -201,7 +214,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t ring_smem = smem_u32(smem + L.ring_off);
 
   if (warp >= 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(HD > kHeadDim ? 128 : 40));   // above d = 128 there is room
   if (warp == kProducerWarp) {
     // ================================================================== TMA producer
     if (lane == 0) {
@@ -257,30 +270,40 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   } else if (warp == kMmaWarp) {
     // ================================================================== MMA issuer
     if (lane == 0) {
-      const uint32_t t_s = tmem_base, t_o = tmem_base + 128;
+      const uint32_t t_o = tmem_base + kColO;
+      // buffer, full barrier and phase of key tile j
+      auto s_col = [&](int j) -> uint32_t { return tmem_base + (kTwoS ? static_cast<uint32_t>(j & 1) * 128u : 0u); };
+      auto sp_idx = [&](int j) -> int { return kTwoS ? (j & 1) : 0; };
+      auto sp_phase = [&](int j) -> uint32_t { return static_cast<uint32_t>(kTwoS ? (j >> 1) : j) & 1u; };
       bool ok = mbar_wait(smem_u32(&kv_full[0]), 0, wctx) && mbar_wait(smem_u32(q_full), 0, wctx);
       if (ok) {
         tc_fence_after();
-        issue_qk<DT, HD>(q_smem, ring_smem, t_s);
-        tc_commit(smem_u32(s_full));
+        issue_qk<DT, HD>(q_smem, ring_smem, s_col(0));
+        tc_commit(smem_u32(&s_full[0]));
         tc_commit(smem_u32(&kv_empty[0]));   // K_0 is free once S(0) has completed
       }
+      auto next_qk = [&](int j) -> bool {    // S(j+1) = Q K_{j+1}^T
+        const int k_item = 2 * j + 2, k_slot = k_item % kSlots;
+        if (!mbar_wait(smem_u32(&kv_full[k_slot]), (k_item / kSlots) & 1, wctx)) return false;
+        tc_fence_after();
+        // the tensor pipe executes in issue order: this overwrite of a buffer follows the P V product that read it
+        // (one buffer: P(j) V_j just above; two buffers: P(j-1) V_{j-1} of the iteration before)
+        issue_qk<DT, HD>(q_smem, ring_smem + k_slot * T::kTileBytes, s_col(j + 1));
+        tc_commit(smem_u32(&s_full[sp_idx(j + 1)]));
+        tc_commit(smem_u32(&kv_empty[k_slot]));
+        return true;
+      };
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int v_item = 2 * j + 1, v_slot = v_item % kSlots;
-        const int k_item = 2 * j + 2, k_slot = k_item % kSlots;
+        if (kTwoS && j + 1 < n_tiles && !next_qk(j)) { ok = false; break; }
         if (!mbar_wait(smem_u32(&kv_full[v_slot]), (v_item / kSlots) & 1, wctx)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(p_full), j & 1, wctx)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&p_full[sp_idx(j)]), sp_phase(j), wctx)) { ok = false; break; }
         tc_fence_after();
-        if constexpr (VT) issue_pv_vt<DT>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
-        else issue_pv<DT, HDV>(t_s, ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
+        if constexpr (VT) issue_pv_vt<DT>(s_col(j), ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
+        else issue_pv<DT, HDV>(s_col(j), ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
         tc_commit(smem_u32(&kv_empty[v_slot]));
         if (j + 1 < n_tiles) {
-          if (!mbar_wait(smem_u32(&kv_full[k_slot]), (k_item / kSlots) & 1, wctx)) { ok = false; break; }
-          tc_fence_after();
-          // the tensor pipe executes in issue order: this overwrite of S/P follows the P V read above
-          issue_qk<DT, HD>(q_smem, ring_smem + k_slot * T::kTileBytes, t_s);
-          tc_commit(smem_u32(s_full));
-          tc_commit(smem_u32(&kv_empty[k_slot]));
+          if (!kTwoS && !next_qk(j)) { ok = false; break; }
         } else {
           tc_commit(smem_u32(o_full));
         }
@@ -290,11 +313,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   }
   } else {
     // ================================================================== softmax / correction / epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    // two CTAs per SM: 128 x (40 + 216) registers are exactly a CTA's half of the file; above d = 128 the CTA has the
+    // file to itself (the kernel is then launched with 248 registers per thread, and this request is already met)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(HD > kHeadDim ? 248 : 216));
     const int lane_grp = warp & 3;
     const int row = lane_grp * 32 + lane;
-    const uint32_t t_s = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16);
-    const uint32_t t_o = t_s + 128;
+    const uint32_t t_s0 = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16);
+    const uint32_t t_o = t_s0 + kColO;
     const int row_in_seq = m0 + row;
     // visible keys of this row [row_first, row_limit); the smallest limit and the largest first key among this warp's
     // rows decide (warp-uniformly) whether a tile needs masking
@@ -310,7 +335,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     RowState st{-INFINITY, 0.f};
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait(smem_u32(s_full), j & 1, wctx)) { ok = false; break; }
+      const int sp = kTwoS ? (j & 1) : 0;                       // S / P buffer of this tile and its barriers' phase
+      const uint32_t sp_ph = static_cast<uint32_t>(kTwoS ? (j >> 1) : j) & 1u;
+      const uint32_t t_s = t_s0 + static_cast<uint32_t>(sp) * 128u;
+      if (!mbar_wait(smem_u32(&s_full[sp]), sp_ph, wctx)) { ok = false; break; }
       tc_fence_after();
       int start = (tile0 + j) * kBlockN;
       bool half_tile = false;
@@ -361,7 +389,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         fence_proxy_async_smem();
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(p_full));
+      mbar_arrive(smem_u32(&p_full[sp]));
     }
     if (ok && mbar_wait(smem_u32(o_full), 0, wctx)) {
       tc_fence_after();
