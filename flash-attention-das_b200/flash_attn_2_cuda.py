@@ -616,17 +616,20 @@ def _decode_params(q, kcache, vcache, seqlens_k, block_table, softmax_scale, out
     p = DecodeParams()
     p.q, p.k_cache, p.v_cache = q.data_ptr(), kcache.data_ptr(), vcache.data_ptr()
     p.out, p.softmax_lse = _ptr(out), _ptr(lse)
-    p.q_batch_stride, p.q_head_stride, p.q_row_stride = q.stride(0), q.stride(2), q.stride(1)
+    # one stride() call per tensor: every Python -> torch call on this path is a good part of a microsecond
+    qs, ks, vs = q.stride(), kcache.stride(), vcache.stride()
+    p.q_batch_stride, p.q_row_stride, p.q_head_stride = qs[0], qs[1], qs[2]
     p.seqlen_q = sq
     if out is not None:
-        p.o_batch_stride, p.o_head_stride, p.o_row_stride = out.stride(0), out.stride(2), out.stride(1)
-    p.k_block_stride, p.k_row_stride, p.k_head_stride = kcache.stride(0), kcache.stride(1), kcache.stride(2)
-    if _is_transposed_v(vcache):
+        os_ = out.stride()
+        p.o_batch_stride, p.o_row_stride, p.o_head_stride = os_[0], os_[1], os_[2]
+    p.k_block_stride, p.k_row_stride, p.k_head_stride = ks[0], ks[1], ks[2]
+    if len(vs) == 4 and vs[3] != 1 and vs[1] == 1:
         # (num_blocks, page, h_k, d) view of a pool stored as (num_blocks, h_k, d, page): the tokens are the contiguous axis
         p.v_transposed = 1
-        p.v_block_stride, p.v_head_stride, p.v_row_stride = vcache.stride(0), vcache.stride(2), vcache.stride(3)
+        p.v_block_stride, p.v_head_stride, p.v_row_stride = vs[0], vs[2], vs[3]
     else:
-        p.v_block_stride, p.v_row_stride, p.v_head_stride = vcache.stride(0), vcache.stride(1), vcache.stride(2)
+        p.v_block_stride, p.v_row_stride, p.v_head_stride = vs[0], vs[1], vs[2]
     p.block_table, p.block_table_batch_stride = block_table.data_ptr(), block_table.stride(0)
     p.cache_seqlens = seqlens_k.data_ptr()
     p.b, p.h, p.h_k, p.d = b, h, h_k, d
