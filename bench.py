@@ -100,10 +100,12 @@ class ClockSampler:
     than a whole timed region); the samples whose monotonic timestamp falls inside the region are summarised."""
     REASON_BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, index):
+    def __init__(self, index, enabled=True):
         self.index = index
         self.proc = None
         self.t0 = self.t1 = 0
+        if not enabled or os.environ.get("FA_B200_BENCH_NO_CLOCKS"):
+            return
         try:
             uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
             self.proc = subprocess.Popen([sys.executable, "-c", _NVML_POLLER, uuid, str(index)], stdout=subprocess.PIPE,
@@ -739,7 +741,16 @@ def time_steps(fn, steps, warmup, world, dev, pipe=None):
         pipe.end()
     e1.record()
     barrier(world)
-    return max_over_ranks(e0.elapsed_time(e1), world, dev) / steps
+    mine = e0.elapsed_time(e1)
+    if world > 1:   # every rank's own time, for the record (the value is computed from the slowest)
+        import torch.distributed as dist
+        t = torch.tensor([mine], dtype=torch.float64, device=dev)
+        allt = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allt, t)
+        time_steps.by_rank = [round(float(x.item()) / steps, 4) for x in allt]
+    else:
+        time_steps.by_rank = [round(mine / steps, 4)]
+    return max_over_ranks(mine, world, dev) / steps
 
 
 def time_kernel_alone(wl, steps, warmup):
@@ -807,10 +818,12 @@ def run_workload(name, args, dev, rank, world, shard, peaks, cpu_budget):
     import flash_attn_2_cuda
     wl = make_workload(name, dev, args.seed, shard, world, args.scale)
     metric, unit, div = METRIC[wl.unit_name]
-    sampler = ClockSampler(dev.index)
+    # rank 0's GPU is sampled (its line is the one printed); a poller per rank would only add eight busy processes
+    sampler = ClockSampler(dev.index, enabled=(rank == 0))
     with sampler as cs:
         l0 = flash_attn_2_cuda.launch_count()
         ms = time_steps(wl.step, args.steps, args.warmup, world, dev)
+        ms_by_rank = list(time_steps.by_rank)
         launches = (flash_attn_2_cuda.launch_count() - l0) // (args.steps + args.warmup) * args.steps
         if hasattr(wl, "e2e_setup"):
             wl.e2e_setup()
@@ -838,7 +851,7 @@ def run_workload(name, args, dev, rank, world, shard, peaks, cpu_budget):
     replica = name.endswith("_replica")
     res = {
         "name": name, "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "ms_per_step_by_rank": ms_by_rank, "higher_is_better": True,
         "scaling": "weak" if replica else "strong",
         "vs_baseline": None, "dtype": "e4m3" if "fp8" in name else "bf16", "data": "synthetic (seeded)",
         "config": wl.desc,
@@ -1014,7 +1027,7 @@ def main():
     if rank == 0:
         line = results[0]
         if len(results) > 1:
-            line["also"] = [{k: r[k] for k in ("name", "metric", "value", "unit", "ms_per_step", "scaling", "dtype", "config",
+            line["also"] = [{k: r[k] for k in ("name", "metric", "value", "unit", "ms_per_step", "ms_per_step_by_rank", "scaling", "dtype", "config",
                                                  "e2e", "gpu_launches", "roofline", "check", "clocks", "kernel", "phases",
                                                  "host_us_per_call", "cpu_baseline") if k in r}
                             for r in results[1:]]
