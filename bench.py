@@ -1008,6 +1008,13 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+        # The first collectives of a process set NCCL up (channels, proxy threads, buffers); the steps timed right after
+        # the first barrier ran 6 us slower each than the same steps later on.  Get that over with before any workload.
+        for _ in range(3):
+            dist.barrier()
+            t = torch.ones(1, device=dev)
+            dist.all_reduce(t)
+        torch.cuda.synchronize()
     shard = (rank, world)
     if args.shard_of > 0:
         if world != 1:
