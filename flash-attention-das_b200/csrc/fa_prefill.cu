@@ -45,8 +45,8 @@ __host__ __device__ constexpr SmemLayoutInfo smem_layout() {
   s.q_off = 0;
   s.ring_off = s.q_off + T::kTileBytes;
   s.bar_off = s.ring_off + ring_slots(HD) * T::kTileBytes;
-  // barriers: q_full, kv_full[kMaxSlots], kv_empty[kMaxSlots], s_full[2], p_full[2], o_full
-  s.tiles_off = s.bar_off + 8 * (6 + 2 * kMaxSlots);
+  // barriers: q_full, kv_full[kMaxSlots], kv_empty[kMaxSlots], s_full[2], p_full[2], o_full, pv_done
+  s.tiles_off = s.bar_off + 8 * (7 + 2 * kMaxSlots);
   s.misc_off = s.tiles_off + 4 * kMaxSparseTiles;
   s.total = s.misc_off + 32;
   return s;
@@ -82,6 +82,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   uint64_t* s_full = kv_empty + kMaxSlots;   // [2]
   uint64_t* p_full = s_full + 2;          // [2]
   uint64_t* o_full = p_full + 2;
+  uint64_t* pv_done = o_full + 1;         // (two S buffers) P V of a key tile has finished accumulating into O
   int* sm_tiles = reinterpret_cast<int*>(smem + L.tiles_off);
   uint32_t* sm_tmem_base = reinterpret_cast<uint32_t*>(smem + L.misc_off);
   int* sm_ntiles = reinterpret_cast<int*>(smem + L.misc_off + 4);
@@ -179,6 +180,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       mbar_init(smem_u32(&p_full[i]), 128);
     }
     mbar_init(smem_u32(o_full), 1);
+    mbar_init(smem_u32(pv_done), 1);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&kv_full[s]), 1);
       mbar_init(smem_u32(&kv_empty[s]), 1);
@@ -302,6 +304,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if constexpr (VT) issue_pv_vt<DT>(s_col(j), ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
         else issue_pv<DT, HDV>(s_col(j), ring_smem + v_slot * T::kTileBytes, t_o, j == 0);
         tc_commit(smem_u32(&kv_empty[v_slot]));
+        if (kTwoS) tc_commit(smem_u32(pv_done));
         if (j + 1 < n_tiles) {
           if (!kTwoS && !next_qk(j)) { ok = false; break; }
         } else {
@@ -345,8 +348,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (p.sparse) { const int v = sm_tiles[j]; start = v & 0x7fffffff; half_tile = (v < 0); }
       int lim = row_limit - start;
       if (half_tile) lim = min(lim, 64);
-      softmax_tile<DT, HDV>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, lim,
-                       half_tile || start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st);
+      // two S buffers: S(j) was computed before P(j-1) V_{j-1} was issued, so a rescale of O has to wait for that product
+      if (!softmax_tile<DT, HDV>(t_s, t_o, scale_log2, kLeftWindow ? row_first - start : 0, lim,
+                                 half_tile || start + kBlockN > warp_limit || (kLeftWindow && start < warp_first), j == 0, st,
+                                 nullptr, (kTwoS && j > 0) ? smem_u32(pv_done) : 0u, static_cast<uint32_t>(j - 1) & 1u, &wctx)) {
+        ok = false;
+        break;
+      }
       // Key rows of this tile that exist and are selected: the sequence may end inside the tile, and a half tile of a
       // tile list uses its first 64 keys only.  The other rows hold whatever lies there (the next sequence of a packed
       // batch, the rest of a page, keys the list left out, or nothing that was fetched).  Their P is zero, but

@@ -282,9 +282,15 @@ struct RowState {
 //   lo, lim    the row sees columns lo <= c < lim of this tile (lo <= 0 and lim >= 128: all)
 //   need_mask  warp-uniform: some row of the warp has lim < 128 or lo > 0
 //   first      first tile of this row's sweep (O holds nothing yet)
+//   o_ready_bar  (kernels that issue Q K^T of the next key tile BEFORE P V of the current one) != 0: an mbarrier that
+//                completes when the previous tile's P V has finished accumulating into O; waited for with
+//                o_ready_parity before O is rescaled (elsewhere S is ready only after that product, nothing to wait for)
+// Returns false when that wait gave up.
 template <int DT, int HD = kHeadDim>
-__device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float scale_log2, int lo, int lim, bool need_mask,
-                                             bool first, RowState& st, [[maybe_unused]] uint32_t* prof = nullptr) {
+__device__ __forceinline__ bool softmax_tile(uint32_t t_s, uint32_t t_o, float scale_log2, int lo, int lim, bool need_mask,
+                                             bool first, RowState& st, [[maybe_unused]] uint32_t* prof = nullptr,
+                                             uint32_t o_ready_bar = 0, uint32_t o_ready_parity = 0,
+                                             const WaitCtx* wctx = nullptr) {
   using T = TileTraits<DT, HD>;
 #ifdef FA_B200_PHASE_TRACE
   uint32_t prof_t = prof ? clock_after(0) : 0u;
@@ -316,6 +322,10 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
   } else {
     const bool grow = mx_scaled > st.m_ref + kRescaleThreshold;
     if (__any_sync(0xffffffffu, grow)) {
+      if (o_ready_bar != 0) {
+        if (!mbar_wait(o_ready_bar, o_ready_parity, *wctx)) return false;
+        tc_fence_after();
+      }
       const float m_new = grow ? mx_scaled : st.m_ref;
       const float alpha = grow ? fast_exp2(st.m_ref - m_new) : 1.f;   // m_ref = -inf -> 0
       st.l_sum *= alpha;
@@ -388,6 +398,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint32_t t_o, float s
   FA_PROF(2, __float_as_uint(st.l_sum));
   tmem_wait_st();
   FA_PROF(3, 0);
+  return true;
 }
 
 // Byte pointer of output row `grow`, head `head`.

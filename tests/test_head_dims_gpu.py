@@ -254,3 +254,25 @@ def test_tile_lists_other_head_dims(fa, d):
     ref_pt, _ = O.attention_ref(q, k, v, causal=True, upcast=False, reorder_ops=True, extra_mask=mask)
     assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"tile lists d={d}")
     _check_lse(lse.cpu(), ref_lse)
+
+
+@pytest.mark.parametrize("d,dv", [(64, 64), (192, 192), (192, 128), (256, 256)])
+def test_scores_that_outgrow_the_running_maximum_at_other_head_dims(fa, d, dv):
+    """Keys whose scores grow by hundreds of log2 units from one key tile to the next: every tile rescales O.  Above
+    d = 128 the kernel computes S of the next key tile before P V of the current one, so the rescale has to wait for the
+    product that is still accumulating into O."""
+    flash_attn, cuda = fa
+    g = gen(61 + d)
+    b, s, h, h_k = 1, 1024, 4, 2
+    q = randn(g, b, s, h, d)
+    k = randn(g, b, s, h_k, d)
+    v = randn(g, b, s, h_k, dv)
+    ramp = (4.0 ** (torch.arange(s) // 128).float() / 16).view(1, s, 1, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    for causal, window in ((False, (-1, -1)), (True, (-1, -1)), (False, (200, 300)), (True, (17, 0))):
+        out = flash_attn.flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=causal, window_size=window)
+        torch.cuda.synchronize()
+        assert cuda.device_status() == 0
+        ref32, _ = O.attention_ref(q, k, v, causal=causal, window_size=window, out_dtype=torch.float32)
+        ref_pt, _ = O.attention_ref(q, k, v, causal=causal, window_size=window, upcast=False, reorder_ops=True)
+        assert_close_to_oracle(out.cpu(), ref32, ref_pt, mult=2.0, eps=2 ** -8, what=f"d={d}/{dv} causal={causal} window={window}")
