@@ -35,7 +35,8 @@ def test_struct_sizes_match_header(binding):
     hdr = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
     for struct, cls in (("fa_b200_fwd_params", binding.FwdParams), ("fa_b200_decode_params", binding.DecodeParams),
                         ("fa_b200_combine_params", binding.CombineParams),
-                        ("fa_b200_kv_append_params", binding.KvAppendParams)):
+                        ("fa_b200_kv_append_params", binding.KvAppendParams),
+                        ("fa_b200_exchange_params", binding.ExchangeParams)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), hdr, re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []
@@ -43,6 +44,7 @@ def test_struct_sizes_match_header(binding):
             stmt = stmt.strip()
             if not stmt:
                 continue
+            stmt = re.sub(r"\[\w+\]", "", stmt)       # array fields: the name without its extent
             fields += [re.findall(r"(\w+)\s*$", x.strip())[0] for x in stmt.split(",")]
         assert fields == [f[0] for f in cls._fields_], struct
 
@@ -53,7 +55,8 @@ def test_a_struct_of_another_size_is_refused(binding):
     lib = binding.lib()
     calls = ((binding.FwdParams, lib.fa_b200_fwd), (binding.FwdParams, lib.fa_b200_fwd_sparse),
              (binding.DecodeParams, lib.fa_b200_decode_paged), (binding.DecodeParams, lib.fa_b200_decode_paged_static),
-             (binding.CombineParams, lib.fa_b200_combine), (binding.KvAppendParams, lib.fa_b200_kv_append))
+             (binding.CombineParams, lib.fa_b200_combine), (binding.KvAppendParams, lib.fa_b200_kv_append),
+             (binding.ExchangeParams, lib.fa_b200_exchange_combine))
     for cls, fn in calls:
         p = cls()
         assert p.struct_size == ctypes.sizeof(cls)
@@ -168,3 +171,24 @@ def test_block_selection_entries_validate(binding):
     assert sel() == 9                      # neither a cdf threshold nor a top-k fraction
     assert sel(nk=5000, cdf=1) == 13       # more key blocks than the in-kernel sort takes
     assert sel(cdf=1) == 1                 # null pointers
+
+
+def test_exchange_entries_validate_before_touching_anything(binding):
+    """The multi-GPU exchange: buffer sizes are host arithmetic, and a call with a bad shape, epoch 0, a rank outside
+    the world or a missing peer pointer is refused with a status before any CUDA call."""
+    lib = binding.lib()
+    assert lib.fa_b200_exchange_bytes(0, 32, 128) == 0 and lib.fa_b200_exchange_bytes(8, 0, 128) == 0
+    n = lib.fa_b200_exchange_bytes(8, 32, 128)
+    assert n >= 2 * 8 * 32 * (128 + 2) * 4 and n % 512 == 0          # two halves, each a multiple of 256 bytes
+    p = binding.ExchangeParams()
+    p.world, p.rank, p.rows, p.h, p.seqlen_q, p.d, p.epoch = 2, 0, 32, 32, 1, 128, 1
+    p.do_push = p.do_wait = 1
+    NULL, SHAPE = 1, 6
+    assert lib.fa_b200_exchange_combine(ctypes.byref(p), None) == NULL       # no partial, no peers
+    p.o_local = p.lse_local = 4096
+    assert lib.fa_b200_exchange_combine(ctypes.byref(p), None) == NULL       # peers missing
+    p.peers[0] = p.peers[1] = 4096
+    for field, bad in (("epoch", 0), ("rank", 2), ("world", 17), ("d", 126), ("rows", 33)):
+        q = binding.ExchangeParams.from_buffer_copy(p)
+        setattr(q, field, bad)
+        assert lib.fa_b200_exchange_combine(ctypes.byref(q), None) == SHAPE, field
