@@ -194,7 +194,8 @@ bool stride_ok(int64_t s, int es) { return s >= 0 && (s * es) % 16 == 0; }
 //   FA_B200_PREFILL_KERNEL=single|pair|dense prefill kernel, where that kernel can take the call
 //   FA_B200_DECODE_MERGE=combine|kernel      split decode calls merge their partitions with the separate combine launch /
 //                                            in the decode kernel (unset: by grid size, see fa_b200_decode_paged)
-//   FA_B200_DEPENDENT_LAUNCH=0               decode kernels are launched without programmatic stream serialisation
+//   FA_B200_DEPENDENT_LAUNCH=0               the decode and exchange kernels are launched without programmatic stream
+//                                            serialisation
 //   FA_B200_PRINT_PARAM=1                    one line on stderr per attention call: kernel, grid, tiling
 //                                            (the reference: FLASH_ATTENTION_PRINT_PARAM, flash_api.cpp:219-222;
 //                                            PA_PRINT_PARAM, src/paged_attention.cu:40)
@@ -612,6 +613,7 @@ int fa_b200_exchange_combine(const fa_b200_exchange_params* p, void* stream) {
   k.s_aux_dtype = p->s_aux_dtype;
   k.do_push = p->do_push;
   k.do_wait = p->do_wait;
+  k.dependent_launch = g_env.dependent_launch;
   cudaError_t e = launch_exchange_combine(k, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("exchange launch", e);
   if (p->rows > 0) g_launches++;

@@ -156,7 +156,7 @@ cudaError_t launch_exchange_combine(const ExchangeKernelParams& p, cudaStream_t 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = p.dependent_launch ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, exchange_combine_kernel, p);
 }
 

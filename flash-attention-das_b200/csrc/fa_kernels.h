@@ -97,6 +97,7 @@ struct ExchangeKernelParams {
   const void* s_aux;
   int32_t s_aux_dtype;
   int32_t do_push, do_wait;  // both set in normal use; separately for single-GPU tests of the two halves
+  int32_t dependent_launch;  // launch with programmatic stream serialisation (the kernel waits by itself)
 };
 size_t exchange_region_bytes(int world, int rows, int d);
 cudaError_t launch_exchange_combine(const ExchangeKernelParams& p, cudaStream_t stream);
