@@ -194,7 +194,7 @@ bool stride_ok(int64_t s, int es) { return s >= 0 && (s * es) % 16 == 0; }
 //   FA_B200_PREFILL_KERNEL=single|pair|dense prefill kernel, where that kernel can take the call
 //   FA_B200_DECODE_MERGE=combine|kernel      split decode calls merge their partitions with the separate combine launch /
 //                                            in the decode kernel (unset: by grid size, see fa_b200_decode_paged)
-//   FA_B200_DEPENDENT_LAUNCH=0               the decode and exchange kernels are launched without programmatic stream
+//   FA_B200_DEPENDENT_LAUNCH=0               the decode, combine and exchange kernels are launched without programmatic stream
 //                                            serialisation
 //   FA_B200_PRINT_PARAM=1                    one line on stderr per attention call: kernel, grid, tiling
 //                                            (the reference: FLASH_ATTENTION_PRINT_PARAM, flash_api.cpp:219-222;
@@ -503,6 +503,7 @@ int fa_b200_combine(const fa_b200_combine_params* p, void* stream) {
   if (!aligned16(p->o_partial) || (p->out && !aligned16(p->out))) return FA_B200_ERR_ALIGN;
   if (p->out && p->out_row_stride % 8 != 0) return FA_B200_ERR_STRIDE;
   CombineKernelParams k{};
+  k.dependent_launch = g_env.dependent_launch;
   k.o_partial = p->o_partial;
   k.lse_partial = p->lse_partial;
   k.out = p->out;
@@ -752,6 +753,7 @@ int fa_b200_decode_paged(const fa_b200_decode_params* p, void* stream_) {
   g_launches++;
   if (pl.split && !merge_in_kernel) {
     CombineKernelParams c{};
+    c.dependent_launch = g_env.dependent_launch;
     c.o_partial = k.o_partial;
     c.lse_partial = k.lse_partial;
     c.seqlens = p->cache_seqlens;

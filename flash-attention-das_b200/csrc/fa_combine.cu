@@ -23,6 +23,9 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   __shared__ float4 red_acc[kCombineWarps][NV][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
+  // launched with programmatic stream serialisation: the partials come from the kernel before this one
+  griddep_wait();
+  griddep_launch_dependents();
   const int sq = p.sq > 0 ? p.sq : 1;
   const int bi = row / (p.h * sq), hi = (row / sq) % p.h, ti = row % sq;
   int nparts = p.num_parts;
@@ -145,10 +148,16 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
 
 cudaError_t launch_combine(const CombineKernelParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return cudaSuccess;
-  const int grid = p.rows;
-  if (p.d > 128) combine_kernel<2><<<grid, kCombineWarps * 32, 0, stream>>>(p);
-  else combine_kernel<1><<<grid, kCombineWarps * 32, 0, stream>>>(p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.rows);
+  cfg.blockDim = dim3(kCombineWarps * 32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.dependent_launch ? 1 : 0;
+  return p.d > 128 ? cudaLaunchKernelEx(&cfg, combine_kernel<2>, p) : cudaLaunchKernelEx(&cfg, combine_kernel<1>, p);
 }
 
 }  // namespace fa

@@ -77,6 +77,7 @@ struct CombineKernelParams {
   float out_scale;
   const void* s_aux;         // attention sinks (h): one more term of every row's sum
   int32_t s_aux_dtype;
+  int32_t dependent_launch;  // launch with programmatic stream serialisation (the kernel waits by itself)
 };
 cudaError_t launch_combine(const CombineKernelParams& p, cudaStream_t stream);
 
