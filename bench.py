@@ -604,7 +604,20 @@ class LongSeqWorkload:
             import torch.distributed as dist
             if self.real_world > 1 and dist.is_initialized() and os.environ.get("FA_B200_BENCH_LONGSEQ", "") != "nccl":
                 from flash_attn.split_kv_parallel import PartialExchange
-                self._ex = PartialExchange(H, D, self.q.device)
+                ex, err = None, ""
+                try:
+                    ex = PartialExchange(H, D, self.q.device)
+                except Exception as e:   # e.g. CUDA IPC not permitted between the ranks' processes
+                    err = repr(e)
+                # every rank must take the same path: the NCCL form unless the set-up worked everywhere
+                ok = torch.tensor([1.0 if ex is not None else 0.0], device=self.q.device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                if float(ok.item()) == 1.0:
+                    self._ex = ex
+                else:
+                    if ex is not None:
+                        ex.close()
+                    self.exchange_note = "peer-memory exchange not available (%s): NCCL all-gather + combine" % (err or "on another rank")
         return self._ex
 
     def _run(self, q, events=None, nccl=False):
@@ -883,6 +896,8 @@ def run_workload(name, args, dev, rank, world, shard, peaks, cpu_budget):
         res["host_us_per_call"] = host_us_per_call(wl)
     if name == "longseq":
         res["phases"] = wl.phases(max(args.steps, 10))
+        if getattr(wl, "exchange_note", None):
+            res["phases"]["exchange"] = wl.exchange_note
         res["host_us_per_call"] = host_us_per_call(wl, 100)
     if cpu_budget > 0 and rank == 0:
         res["cpu_baseline"] = cpu_baseline(name, args.seed, budget_s=cpu_budget)

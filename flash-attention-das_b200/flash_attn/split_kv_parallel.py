@@ -112,19 +112,32 @@ class PartialExchange:
             raise ValueError("PartialExchange takes at most 16 ranks")
         self.rows, self.d, self.device = rows, d, torch.device(device)
         self.epoch = 0
-        self._own, handle, self.bytes = cuda.exchange_alloc(self.world, rows, d, self.device)
+        self._own, self._opened, self.peers = 0, [], []
+        failed = None
+        # Every rank goes through the same collectives whatever fails locally, and raises only after the last one.
+        try:
+            self._own, handle, self.bytes = cuda.exchange_alloc(self.world, rows, d, self.device)
+        except Exception as e:
+            handle, failed = None, e
         handles = [None] * self.world
         dist.all_gather_object(handles, handle, group=group)
-        self.peers = []
-        self._opened = []
         for r, hd in enumerate(handles):
             if r == self.rank:
                 self.peers.append(self._own)
-            else:
+                continue
+            try:
+                if hd is None:
+                    raise RuntimeError("rank %d could not allocate its exchange buffer" % r)
                 ptr = cuda.exchange_open(hd, self.device)
                 self._opened.append(ptr)
                 self.peers.append(ptr)
+            except Exception as e:
+                failed = failed or e
+                self.peers.append(0)
         dist.barrier(group=group)
+        if failed is not None:
+            self.close()
+            raise RuntimeError("PartialExchange set-up failed on rank %d: %r" % (self.rank, failed))
 
     def combine(self, o_local: torch.Tensor, lse_local: torch.Tensor, h: int, out_dtype=torch.bfloat16, s_aux=None):
         """o_local (rows, d) fp32, lse_local (rows) fp32 of this rank -> (out (rows, d), lse (rows)), identical on every
